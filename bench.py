@@ -1,0 +1,254 @@
+#!/usr/bin/env python
+"""Headline benchmark: FLUX.1-dev-shaped 12B MMDiT, 1024x1024 (4096 image tokens + 512 text tokens), bf16,
+28-step Euler flow-matching denoise loop -> denoise iterations per second (one iteration = one full 57-block
+forward + sampler update), plus LoRA (rank 16) training samples per second on the same backbone.
+
+    python bench.py --gpus N --steps K --warmup W            # N > 1: launched by torch.distributed.run
+
+Timing: W untimed warm-up steps, then exactly K steps between CUDA events on the launching stream, bracketed by a
+barrier + synchronize; the reported time is the max over ranks. Inputs are synthetic N(0,1) tensors of the named
+shapes and the weights are random-init from seed 0 (no datasets or checkpoints exist offline). Each step streams
+24 GB of weights, far more than the 126 MB L2, so no explicit L2 flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+PUBLISHED_NEAREST = {"what": "Z-Image 6B 1024^2 denoise, RTX 3090 Ti (reference's nearest published analogue)",
+                     "it_per_s": 0.23}
+
+
+def _parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1, help="images per GPU")
+    ap.add_argument("--model", default="flux1-dev", choices=["flux1-dev", "tiny"])
+    ap.add_argument("--train-steps", type=int, default=-1, help="LoRA train steps to time (-1: min(steps, 4); 0: skip)")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=3)
+        except Exception:
+            pass
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main():
+    args = _parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "reference is Mojo/MAX source with no setup.py/pyproject.toml: pip reports "
+                                         "'/root/reference is not installable'; no mojo/pixi toolchain offline"}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from mojodiffusion_b200.models.mmdit import MMDiT, flux1_dev_config, tiny_mmdit_config
+    from mojodiffusion_b200.ops import native
+    from mojodiffusion_b200.parallel import dist as pdist
+    from mojodiffusion_b200.pipeline import FluxPipeline
+    from mojodiffusion_b200.sampling import flow_match as fm
+
+    world = pdist.env_world()
+    rank = pdist.env_rank()
+    local = pdist.env_local_rank()
+    assert torch.cuda.is_available(), "bench.py needs a GPU"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        pdist.init_from_env("nccl")
+    native.load(True)
+    launches = torch.ops.mdb200.launch_count
+
+    cfg = flux1_dev_config() if args.model == "flux1-dev" else tiny_mmdit_config()
+    S_img, S_txt = (4096, 512) if args.model == "flux1-dev" else (256, 64)
+    hw = (64, 64) if args.model == "flux1-dev" else (16, 16)
+    B = args.batch
+    model = MMDiT(cfg, dtype=torch.bfloat16, device=dev).init_weights(0)
+    model.eval()
+    pipe = FluxPipeline(model, dev)
+    g = torch.Generator().manual_seed(1234 + rank)
+    x_host = torch.randn(B, S_img, cfg.in_channels, generator=g).pin_memory()
+    txt_host = torch.randn(B, S_txt, cfg.context_dim, generator=g).to(torch.bfloat16).pin_memory()
+    y_host = torch.randn(B, cfg.vec_dim, generator=g).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    sigmas = fm.flux1_sigmas(28, S_img)
+    K, W = args.steps, max(args.warmup, 0)
+
+    # ------------------------------------------------------------------ device-timed denoise loop
+    x = x_host.to(dev)
+    txt = txt_host.to(dev)
+    y = y_host.to(dev)
+    xb = x.to(torch.bfloat16)
+    ids = MMDiT.make_ids(hw[0], hw[1], S_txt, dev)
+    gvec = torch.full((B,), 3.5, device=dev)
+    from mojodiffusion_b200 import ops
+
+    def denoise_step(i):
+        s, s_next = sigmas[i % 28], sigmas[i % 28 + 1]
+        t = torch.full((B,), float(s), device=dev)
+        with torch.no_grad():
+            v = model(xb, txt, t, y, gvec, ids=ids)
+            ops.cfg_euler(x, v, None, dt=float(s_next - s), mode=0, x_bf16=xb)
+
+    for i in range(W):
+        denoise_step(i)
+    torch.cuda.synchronize()
+    pdist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(K):
+        denoise_step(W + i)
+    e1.record()
+    torch.cuda.synchronize()
+    pdist.barrier()
+    n_launch = launches() - n0
+    clocks = sampler.stop() if rank == 0 else None
+    ms = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
+    native.check_status()
+    assert torch.isfinite(x).all(), "latents diverged"
+    it_per_s = world * B * 1000.0 / ms  # every rank denoises its own batch (data-parallel replicas)
+
+    # ------------------------------------------------------------------ end-to-end through the public API
+    e2e = None
+    if not args.no_e2e:
+        x_host.copy_(torch.randn(B, S_img, cfg.in_channels, generator=g))
+        for i in range(min(W, 2)):
+            pipe.step_from_host(x_host, txt_host, y_host, sigmas[i], sigmas[i + 1], 3.5, out_host, hw)
+        torch.cuda.synchronize()
+        pdist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        bi = bo = 0
+        for i in range(K):
+            bi, bo = pipe.step_from_host(x_host, txt_host, y_host, sigmas[i % 28], sigmas[i % 28 + 1], 3.5, out_host, hw)
+            torch.cuda.current_stream().synchronize()   # the caller reads the step's result on the host
+            x_host.copy_(out_host)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_e2e = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
+        e2e = {"value": world * B * 1000.0 / ms_e2e, "unit": "it/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo}
+
+    # ------------------------------------------------------------------ LoRA training samples/s
+    train = None
+    tsteps = min(K, 4) if args.train_steps < 0 else args.train_steps
+    if tsteps > 0:
+        from mojodiffusion_b200.parallel.dp import DataParallelGrads
+        from mojodiffusion_b200.training import lora as L
+        from mojodiffusion_b200.training.optim import FusedAdamW
+        from mojodiffusion_b200.training.trainer import FlowMatchTrainer
+        del xb
+        torch.cuda.empty_cache()
+        slots = L.inject_flux_lora(model, rank=16, alpha=16.0)
+        params = L.lora_parameters(slots)
+        model.gradient_checkpointing = True
+        model.train()
+        opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
+        dp = DataParallelGrads(params) if world > 1 else None
+        tr = FlowMatchTrainer(model, params, opt, dp)
+        x0 = torch.randn(B, S_img, cfg.in_channels, generator=g).to(dev)
+        for i in range(3):
+            tr.step(x0, txt, y, hw=hw)
+        torch.cuda.synchronize()
+        pdist.barrier()
+        t0n = launches()
+        e0.record()
+        for i in range(tsteps):
+            loss = tr.step(x0, txt, y, hw=hw)
+        e1.record()
+        torch.cuda.synchronize()
+        pdist.barrier()
+        ms_t = pdist.max_over_ranks(e0.elapsed_time(e1) / tsteps)
+        native.check_status()
+        train = {"metric": "lora_train_samples_per_s", "value": world * B * 1000.0 / ms_t, "unit": "samples/s",
+                 "ms_per_step": ms_t, "steps": tsteps, "warmup": 3, "loss": float(loss), "rank": 16,
+                 "gpu_launches": launches() - t0n, "gradient_checkpointing": True,
+                 "parallelism": f"dp{world}" if world > 1 else "single"}
+
+    if rank == 0:
+        line = {
+            "metric": "flux1-dev-shape 1024^2 denoise it/s (+ LoRA r16 train samples/s in 'lora_train')",
+            "value": it_per_s, "unit": "it/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": f"{cfg.name} 12B MMDiT (19 double + 38 single, D=3072, 24x128)" if args.model == "flux1-dev" else cfg.name,
+                       "global_batch": world * B, "seq_len": S_img + S_txt, "image_tokens": S_img, "text_tokens": S_txt,
+                       "sampler": "euler flow-match, 28-step BFL-shifted schedule, guidance 3.5 (distilled)",
+                       "parallelism": f"dp{world}" if world > 1 else "single", "weights": "random-init seed 0",
+                       "l2": "inputs larger than L2: 24 GB of weights stream every step"},
+            "clocks": clocks, "gpu_launches": n_launch, "e2e": e2e, "lora_train": train,
+            "published_nearest": PUBLISHED_NEAREST,
+            "vs_published_nearest": it_per_s / PUBLISHED_NEAREST["it_per_s"],
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,399 @@
+// Flash-style attention forward for sm_100a on the 5th-generation tensor cores.
+//
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that ping-pong: while one
+// softmax warpgroup works on its S tile, the tensor core runs the other tile's P*V and next Q*K^T.
+//   * Q (2 x 128 x Dh), K and V (128 x Dh, double buffered) arrive by TMA straight from the caller's
+//     [batch, seq, head, Dh] strides (4-D tensor maps, 128-byte swizzle): no head transpose pass exists.
+//   * S = Q K^T  : tcgen05.mma SS-form, fp32 accumulator in TMEM (128 columns per tile).
+//   * softmax    : one thread per query row (no shuffles), exp2 with the scale folded in, P written back
+//                  into TMEM as packed bf16 over the S columns it came from.
+//   * O_tile = P V: tcgen05.mma TS-form (A = P from TMEM, B = V MN-major from shared memory) into a second
+//                  TMEM region; the softmax warpgroup folds it into its fp32 register accumulator with the
+//                  running-max rescale, so the tensor core never waits for a correction step.
+//   * 512 TMEM columns: S0 S1 O0 O1. Register file rebalanced with setmaxnreg (80 / 208).
+// Keys beyond Skv or beyond kv_len[b] are masked; ragged Sq / Skv tiles are zero filled by TMA.
+//
+// Takes the place of the reference's math-mode SDPA (serenitymojo/ops/attention.mojo:68-520), its scalar
+// online-softmax kernels (:734-873,1109-1167) and its cuDNN flash shim (serenitymojo/ops/cshim/cudnn_sdpa.cpp:375,470;
+// Stats/LSE output as in the training forward there).
+#include "common.cuh"
+#include "gemm_api.h"
+#include "kernels_api.h"
+
+#include <string.h>
+
+namespace mdb {
+
+constexpr int ATT_THREADS = 384;
+constexpr int BQ = 128;   // rows per q tile
+constexpr int BKV = 128;  // keys per kv tile
+
+struct alignas(64) AttnMaps {
+  CUtensorMap q, k, v;
+};
+
+struct AttnParams {
+  __nv_bfloat16* o;
+  float* lse;
+  const int* kv_len;
+  int B, H, Sq, Skv;
+  long long o_strides[3];
+  float scale_log2;
+  int* status;
+};
+
+template <int REGS> __device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+template <int REGS> __device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
+template <int DH>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
+  constexpr int DBOX = DH / 64;               // 64-element (128 B) boxes along the head dim
+  constexpr int TILE_BYTES = BQ * DH * 2;     // one 128-row operand tile
+  constexpr int BOX_BYTES = BQ * 128;         // one 128-row x 128-B box
+  constexpr uint32_t S_COL0 = 0, S_COL1 = 128, O_COL0 = 256, O_COL1 = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
+  __shared__ uint64_t s_full[2], p_full[2], o_full[2], o_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sQ = smem;                       // 2 tiles
+  uint8_t* sK = sQ + 2 * TILE_BYTES;        // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;        // 2 stages
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_blk = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int q0 = q_blk * 2 * BQ;
+
+  int kv_valid = p.Skv;
+  if (p.kv_len != nullptr) kv_valid = min(kv_valid, p.kv_len[batch]);
+  if (kv_valid < 1) kv_valid = 1;
+  const int n_kv = (kv_valid + BKV - 1) / BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 128);
+      mbar_init(&o_full[s], 1);
+      mbar_init(&o_empty[s], 128);
+    }
+    abort_s = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&maps.q);
+    tma_prefetch_desc(&maps.k);
+    tma_prefetch_desc(&maps.v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp < 4) {
+    setmaxnreg_dec<80>();
+    if (warp == 0 && lane == 0) {
+      // ----------------------------- TMA producer -----------------------------
+      mbar_expect_tx(&q_full, 2 * TILE_BYTES);
+      for (int t = 0; t < 2; ++t)
+        for (int d = 0; d < DBOX; ++d)
+          tma_load_4d(sQ + t * TILE_BYTES + d * BOX_BYTES, &maps.q, &q_full, d * 64, q0 + t * BQ, head, batch);
+      bool ok = true;
+      uint64_t* last_bar = &q_full;
+      uint32_t last_par = 0;
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t par = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[st], par ^ 1u, &abort_s)) {
+          report_status(p.status, STATUS_TIMEOUT, 11, j);
+          ok = false;
+          break;
+        }
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        for (int d = 0; d < DBOX; ++d)
+          tma_load_4d(sK + st * TILE_BYTES + d * BOX_BYTES, &maps.k, &k_full[st], d * 64, j * BKV, head, batch);
+        last_bar = &k_full[st];
+        last_par = par;
+        if (!mbar_wait(&v_empty[st], par ^ 1u, &abort_s)) {
+          report_status(p.status, STATUS_TIMEOUT, 12, j);
+          ok = false;
+          break;
+        }
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        for (int d = 0; d < DBOX; ++d)
+          tma_load_4d(sV + st * TILE_BYTES + d * BOX_BYTES, &maps.v, &v_full[st], d * 64, j * BKV, head, batch);
+        last_bar = &v_full[st];
+        last_par = par;
+      }
+      if (!ok) {
+        uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(last_bar, last_par) && globaltimer_ns() - t0 < 5000000ull) {
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ----------------------------- UMMA issuer ------------------------------
+      constexpr uint32_t idesc_s = make_idesc(1, UMMA_BF16, UMMA_BF16, 0, 0, BQ, BKV);
+      constexpr uint32_t idesc_pv = make_idesc(1, UMMA_BF16, UMMA_BF16, 0, 1, BQ, DH);
+      const uint32_t s_cols[2] = {S_COL0, S_COL1};
+      const uint32_t o_cols[2] = {O_COL0, O_COL1};
+      auto issue_s = [&](int t, int st) {
+        const uint32_t qa = smem_u32(sQ + t * TILE_BYTES);
+        const uint32_t ka = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          const uint32_t off = (kk / 4) * BOX_BYTES + (kk % 4) * 32;
+          umma_f16_ss(tmem_base + s_cols[t], make_desc_kmajor_sw128(qa + off), make_desc_kmajor_sw128(ka + off),
+                      idesc_s, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int st) {
+        const uint32_t va = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          umma_f16_ts(tmem_base + o_cols[t], tmem_base + s_cols[t] + kk * 8,
+                      make_desc_mnmajor_sw128(va + kk * 2048, BOX_BYTES), idesc_pv, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&o_full[t]);
+      };
+      bool ok = mbar_wait(&q_full, 0, &abort_s) && mbar_wait(&k_full[0], 0, &abort_s);
+      if (!ok) report_status(p.status, STATUS_TIMEOUT, 21, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        issue_s(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t par = (j >> 1) & 1;
+        const bool more = (j + 1 < n_kv);
+        const int st_n = (j + 1) & 1;
+        const uint32_t par_n = ((j + 1) >> 1) & 1;
+        if (!mbar_wait(&v_full[st], par, &abort_s) || (more && !mbar_wait(&k_full[st_n], par_n, &abort_s))) {
+          report_status(p.status, STATUS_TIMEOUT, 22, j);
+          ok = false;
+          break;
+        }
+        for (int t = 0; t < 2; ++t) {
+          if (!mbar_wait(&p_full[t], j & 1, &abort_s) || !mbar_wait(&o_empty[t], (j & 1) ^ 1u, &abort_s)) {
+            report_status(p.status, STATUS_TIMEOUT, 23 + t, j);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_pv(t, st);
+          if (more) issue_s(t, st_n);
+        }
+        if (!ok) break;
+        umma_commit(&v_empty[st]);
+        if (more) umma_commit(&k_empty[st_n]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- softmax warpgroups ---------------------------
+    setmaxnreg_inc<208>();
+    const int t = (warp - 4) >> 2;        // q tile of this warpgroup
+    const int quad = warp & 3;            // TMEM lane quadrant
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
+    const uint32_t o_addr = tmem_base + lane_addr + (t ? O_COL1 : O_COL0);
+    const float sl2 = p.scale_log2;
+
+    float acc[DH];
+#pragma unroll
+    for (int i = 0; i < DH; ++i) acc[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_kv; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, &abort_s));
+      if (!ok) {
+        if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 31 + t, j);
+        break;
+      }
+      tc_fence_after();
+      const int kv0 = j * BKV;
+      const bool tail = kv0 + BKV > kv_valid;
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_wait_ld();
+        if (!tail) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kv0 + c * 32 + i < kv_valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m_run, mx * sl2);
+      const float alpha = exp2f(m_run - m_new);
+      // pass 2: p = exp2(s*scale - m), pack to bf16, write P over the S columns
+      float rowsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float a = exp2f(fmaf(__uint_as_float(r[i]), sl2, -m_new));
+          float b = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, -m_new));
+          if (tail) {
+            if (kv0 + c * 32 + i >= kv_valid) a = 0.f;
+            if (kv0 + c * 32 + i + 1 >= kv_valid) b = 0.f;
+          }
+          rowsum += a + b;
+          pk[i >> 1] = pack_bf16x2(a, b);
+        }
+        tmem_st_32x32b_x16(s_addr + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full[t]);
+      l_run = l_run * alpha + rowsum;
+      m_run = m_new;
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (j - 1) & 1, &abort_s));
+        if (!ok) {
+          if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 33 + t, j);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(o_addr + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(r[i])) * alpha;
+        }
+        tc_fence_before();
+        mbar_arrive(&o_empty[t]);
+      }
+    }
+    if (ok) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (n_kv - 1) & 1, &abort_s));
+      if (!ok && lane == 0) report_status(p.status, STATUS_TIMEOUT, 35 + t, n_kv);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = 1.f / l_run;
+      const int tok = q0 + t * BQ + row_in_tile;
+      __nv_bfloat16* orow = p.o + batch * p.o_strides[0] + static_cast<long long>(tok) * p.o_strides[1] +
+                            head * p.o_strides[2];
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(o_addr + c * 32, r);
+        tmem_wait_ld();
+        if (tok < p.Sq) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16x2((acc[c * 32 + i + 0] + __uint_as_float(r[i + 0])) * inv_l,
+                              (acc[c * 32 + i + 1] + __uint_as_float(r[i + 1])) * inv_l);
+            w.y = pack_bf16x2((acc[c * 32 + i + 2] + __uint_as_float(r[i + 2])) * inv_l,
+                              (acc[c * 32 + i + 3] + __uint_as_float(r[i + 3])) * inv_l);
+            w.z = pack_bf16x2((acc[c * 32 + i + 4] + __uint_as_float(r[i + 4])) * inv_l,
+                              (acc[c * 32 + i + 5] + __uint_as_float(r[i + 5])) * inv_l);
+            w.w = pack_bf16x2((acc[c * 32 + i + 6] + __uint_as_float(r[i + 6])) * inv_l,
+                              (acc[c * 32 + i + 7] + __uint_as_float(r[i + 7])) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+          }
+        }
+      }
+      if (p.lse != nullptr && tok < p.Sq)
+        p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq + tok] =
+            (m_run + log2f(l_run)) * 0.6931471805599453f;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int DH>
+static int launch_attn(const AttnMaps& maps, const AttnParams& p, cudaStream_t st) {
+  constexpr int SMEM = 6 * BQ * DH * 2 + 1024;
+  auto kern = attention_fwd_kernel<DH>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_done = true;
+  }
+  dim3 grid((p.Sq + 2 * BQ - 1) / (2 * BQ), p.H, p.B);
+  kern<<<grid, ATT_THREADS, SMEM, st>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+static int make_bshd_map(CUtensorMap* m, const void* ptr, int B, int S, int H, int Dh, const long long* strides) {
+  // dims innermost first: (d, seq, head, batch)
+  int64_t ext[4] = {Dh, S, H, B};
+  int64_t str[4] = {2, strides[1] * 2, strides[2] * 2, strides[0] * 2};
+  int box[4] = {64, 128, 1, 1};
+  return mdb_make_tmap(m, ptr, 2, 4, ext, str, box, 1);
+}
+
+}  // namespace mdb
+
+extern "C" int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st) {
+  using namespace mdb;
+  if (a->B <= 0 || a->H <= 0 || a->Sq <= 0 || a->Skv <= 0) return -1;
+  if (a->Dh != 128 && a->Dh != 64) return -2;
+  for (int i = 0; i < 3; ++i) {
+    if ((a->q_strides[i] % 8) || (a->k_strides[i] % 8) || (a->v_strides[i] % 8) || (a->o_strides[i] % 8)) return -3;
+  }
+  if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
+       reinterpret_cast<uintptr_t>(a->o)) & 15)
+    return -4;
+  AttnMaps maps;
+  int r = make_bshd_map(&maps.q, a->q, a->B, a->Sq, a->H, a->Dh, a->q_strides);
+  if (r) return 1000 + r;
+  r = make_bshd_map(&maps.k, a->k, a->B, a->Skv, a->H, a->Dh, a->k_strides);
+  if (r) return 2000 + r;
+  r = make_bshd_map(&maps.v, a->v, a->B, a->Skv, a->H, a->Dh, a->v_strides);
+  if (r) return 3000 + r;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.o = reinterpret_cast<__nv_bfloat16*>(a->o);
+  p.lse = a->lse;
+  p.kv_len = a->kv_len;
+  p.B = a->B; p.H = a->H; p.Sq = a->Sq; p.Skv = a->Skv;
+  for (int i = 0; i < 3; ++i) p.o_strides[i] = a->o_strides[i];
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.status = a->status;
+  if (a->Dh == 128) return launch_attn<128>(maps, p, st);
+  return launch_attn<64>(maps, p, st);
+}

@@ -1,0 +1,465 @@
+// torch.ops.mdb200.* : thin host bindings that unpack tensors into the C launch structs of the kernels.
+// No math happens here. Every kernel reports device-side failures (bounded waits that ran out) into one
+// per-device status block that `mdb200::check_status` reads back.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "gemm_api.h"
+#include "kernels_api.h"
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+std::mutex g_mu;
+std::atomic<long long> g_launches{0};
+std::map<int, Tensor> g_status;
+
+int* status_ptr(const Tensor& like) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  const int dev = like.get_device();
+  auto it = g_status.find(dev);
+  if (it == g_status.end()) {
+    Tensor t = at::zeros({4}, like.options().dtype(at::kInt));
+    it = g_status.emplace(dev, t).first;
+  }
+  return it->second.data_ptr<int>();
+}
+
+void check_rc(int rc, const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  TORCH_CHECK(rc == 0, "mdb200 kernel launch failed in ", what, ": code ", rc,
+              rc > 0 && rc < 1000 ? std::string(" (") + cudaGetErrorString(static_cast<cudaError_t>(rc)) + ")" : "");
+}
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+const void* opt_ptr(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+// ------------------------------------------------------------------------------------------
+// GEMM
+// ------------------------------------------------------------------------------------------
+Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tensor>& bias,
+            const optional<Tensor>& residual, const optional<Tensor>& gate, int64_t rows_per_group, int64_t act,
+            int64_t pair_offset, int64_t act_on_second, const optional<Tensor>& out_opt, bool out_fp32, bool a_mn,
+            bool b_mn, const optional<Tensor>& row_scale, const optional<Tensor>& col_scale, double alpha,
+            bool accumulate, int64_t bn) {
+  TORCH_CHECK(!As.empty() && As.size() == Bs.size() && As.size() <= MDB_GEMM_MAX_SEG, "gemm: 1..3 K segments");
+  const Tensor& A0 = As[0];
+  TORCH_CHECK(A0.is_cuda(), "gemm: CUDA tensors only");
+  c10::cuda::CUDAGuard guard(A0.device());
+  const bool fp8 = A0.scalar_type() == at::kFloat8_e4m3fn;
+  MdbGemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.kind = fp8 ? 1 : 0;
+  g.a_mn = a_mn;
+  g.b_mn = b_mn;
+  const int64_t M = a_mn ? A0.size(1) : A0.size(0);
+  const int64_t Nrows = b_mn ? Bs[0].size(1) : Bs[0].size(0);
+  const int64_t N = pair_offset > 0 ? pair_offset : Nrows;
+  TORCH_CHECK(pair_offset <= 0 || Nrows == 2 * pair_offset, "gemm: paired mode wants B with 2*pair_offset rows");
+  g.M = static_cast<int>(M);
+  g.N = static_cast<int>(N);
+  g.num_seg = static_cast<int>(As.size());
+  const int align = fp8 ? 16 : 8;
+  for (size_t s = 0; s < As.size(); ++s) {
+    const Tensor& A = As[s];
+    const Tensor& B = Bs[s];
+    TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.stride(1) == 1 && B.stride(1) == 1, "gemm: 2-D row-major operands");
+    TORCH_CHECK(A.scalar_type() == A0.scalar_type() && B.scalar_type() == A0.scalar_type(), "gemm: dtype mismatch");
+    TORCH_CHECK(fp8 || A.scalar_type() == at::kBFloat16, "gemm: bf16 or float8_e4m3fn operands");
+    const int64_t K = a_mn ? A.size(0) : A.size(1);
+    TORCH_CHECK((b_mn ? B.size(0) : B.size(1)) == K, "gemm: K mismatch in segment ", s);
+    TORCH_CHECK((a_mn ? A.size(1) : A.size(0)) == M, "gemm: M mismatch in segment ", s);
+    TORCH_CHECK((b_mn ? B.size(1) : B.size(0)) == Nrows, "gemm: N mismatch in segment ", s);
+    TORCH_CHECK(A.stride(0) % align == 0 && B.stride(0) % align == 0, "gemm: leading dims must be 16-byte multiples");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(A.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(B.data_ptr()) % 16 == 0,
+                "gemm: operands must be 16-byte aligned");
+    g.K[s] = K;
+    g.A[s] = A.data_ptr();
+    g.B[s] = B.data_ptr();
+    g.lda[s] = A.stride(0);
+    g.ldb[s] = B.stride(0);
+  }
+  Tensor out;
+  if (out_opt.has_value() && out_opt->defined()) {
+    out = *out_opt;
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "gemm: bad out shape");
+    TORCH_CHECK(out.scalar_type() == (out_fp32 ? at::kFloat : at::kBFloat16), "gemm: out dtype");
+  } else {
+    out = at::empty({M, N}, A0.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  }
+  TORCH_CHECK(!accumulate || out_fp32, "gemm: accumulate needs an fp32 output");
+  g.out = out.data_ptr();
+  g.ld_out = static_cast<int>(out.stride(0));
+  g.out_fp32 = out_fp32;
+  g.accumulate_out = accumulate;
+  g.bn = static_cast<int>(bn);
+  g.pair_offset = static_cast<int>(pair_offset > 0 ? pair_offset : 0);
+  g.act = static_cast<int>(act);
+  g.act_on_second = static_cast<int>(act_on_second);
+  g.alpha = static_cast<float>(alpha);
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == Nrows, "gemm: bias");
+    g.bias = bias->data_ptr();
+  }
+  if (row_scale.has_value() && row_scale->defined()) {
+    TORCH_CHECK(row_scale->scalar_type() == at::kFloat && row_scale->numel() == M, "gemm: row_scale");
+    g.row_scale = row_scale->data_ptr<float>();
+  }
+  if (col_scale.has_value() && col_scale->defined()) {
+    TORCH_CHECK(col_scale->scalar_type() == at::kFloat && col_scale->numel() == Nrows, "gemm: col_scale");
+    g.col_scale = col_scale->data_ptr<float>();
+  }
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == M &&
+                    residual->size(1) == N && residual->stride(1) == 1,
+                "gemm: residual");
+    g.residual = residual->data_ptr();
+    g.ld_res = static_cast<int>(residual->stride(0));
+  }
+  if (gate.has_value() && gate->defined()) {
+    TORCH_CHECK(gate->scalar_type() == at::kBFloat16 && gate->dim() == 2 && gate->size(1) == N && gate->stride(1) == 1,
+                "gemm: gate must be [groups, N] bf16");
+    TORCH_CHECK(rows_per_group > 0 && gate->size(0) * rows_per_group >= M, "gemm: gate groups do not cover M");
+    g.gate = gate->data_ptr();
+    g.gate_stride = static_cast<int>(gate->stride(0));
+  }
+  g.rows_per_group = static_cast<int>(rows_per_group > 0 ? rows_per_group : 1);
+  g.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  g.status = status_ptr(A0);
+  check_rc(mdb_gemm_launch(&g, cur_stream()), "gemm");
+  return out;
+}
+
+// ------------------------------------------------------------------------------------------
+// attention
+// ------------------------------------------------------------------------------------------
+std::tuple<Tensor, Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale,
+                                         const optional<Tensor>& kv_len, bool need_lse,
+                                         const optional<Tensor>& out_opt) {
+  // q: [B, Sq, H, Dh], k/v: [B, Skv, H, Dh] (any strides with contiguous Dh)
+  TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "attention: [B,S,H,Dh] tensors");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16,
+              "attention: bf16");
+  TORCH_CHECK(q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1, "attention: head dim must be contiguous");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t B = q.size(0), Sq = q.size(1), H = q.size(2), Dh = q.size(3), Skv = k.size(1);
+  TORCH_CHECK(k.size(0) == B && v.size(0) == B && k.size(2) == H && v.size(2) == H && k.size(3) == Dh &&
+                  v.size(3) == Dh && v.size(1) == Skv,
+              "attention: shape mismatch");
+  Tensor o = (out_opt.has_value() && out_opt->defined()) ? *out_opt : at::empty({B, Sq, H, Dh}, q.options());
+  TORCH_CHECK(o.dim() == 4 && o.stride(3) == 1 && o.size(1) == Sq && o.size(2) == H, "attention: bad out");
+  Tensor lse;
+  if (need_lse) lse = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
+  MdbAttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr();
+  a.lse = need_lse ? lse.data_ptr<float>() : nullptr;
+  if (kv_len.has_value() && kv_len->defined()) {
+    TORCH_CHECK(kv_len->scalar_type() == at::kInt && kv_len->numel() == B && kv_len->is_cuda(), "attention: kv_len");
+    a.kv_len = kv_len->data_ptr<int>();
+  }
+  a.B = (int)B; a.H = (int)H; a.Sq = (int)Sq; a.Skv = (int)Skv; a.Dh = (int)Dh;
+  for (int i = 0; i < 3; ++i) {
+    a.q_strides[i] = q.stride(i); a.k_strides[i] = k.stride(i); a.v_strides[i] = v.stride(i); a.o_strides[i] = o.stride(i);
+  }
+  a.scale = static_cast<float>(scale);
+  a.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  a.status = status_ptr(q);
+  check_rc(mdb_attention_fwd(&a, cur_stream()), "attention_fwd");
+  return {o, need_lse ? lse : Tensor()};
+}
+
+// ------------------------------------------------------------------------------------------
+// norm / rope
+// ------------------------------------------------------------------------------------------
+Tensor norm_modulate_fwd(const Tensor& x, const optional<Tensor>& weight, const optional<Tensor>& bias,
+                         const optional<Tensor>& scale, const optional<Tensor>& shift, int64_t rows_per_group,
+                         double eps, bool rms) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "norm: x [rows,D] bf16");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = at::empty({x.size(0), x.size(1)}, x.options());
+  int mod_stride = 0;
+  if (scale.has_value() && scale->defined()) {
+    TORCH_CHECK(scale->dim() == 2 && scale->stride(1) == 1 && scale->size(1) == x.size(1), "norm: scale [groups,D]");
+    mod_stride = (int)scale->stride(0);
+    if (shift.has_value() && shift->defined())
+      TORCH_CHECK(shift->stride(0) == scale->stride(0) && shift->stride(1) == 1, "norm: shift stride must match scale");
+  } else if (shift.has_value() && shift->defined()) {
+    mod_stride = (int)shift->stride(0);
+  }
+  check_rc(mdb_norm_modulate_fwd(x.data_ptr(), out.data_ptr(), opt_ptr(weight), opt_ptr(bias), opt_ptr(scale),
+                                 opt_ptr(shift), nullptr, (int)x.size(0), (int)x.size(1), (int)x.stride(0),
+                                 (int)out.stride(0), mod_stride, (int)rows_per_group, (float)eps, rms ? 1 : 0,
+                                 cur_stream()),
+           "norm_modulate_fwd");
+  return out;
+}
+
+Tensor norm_modulate_bwd(const Tensor& x, const Tensor& dy, const optional<Tensor>& weight,
+                         const optional<Tensor>& scale, int64_t rows_per_group, double eps, bool rms) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && dy.dim() == 2 && x.stride(1) == 1 && dy.stride(1) == 1, "norm bwd: 2-D");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = at::empty({x.size(0), x.size(1)}, x.options());
+  const int mod_stride = (scale.has_value() && scale->defined()) ? (int)scale->stride(0) : 0;
+  check_rc(mdb_norm_modulate_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), opt_ptr(weight), opt_ptr(scale),
+                                 (int)x.size(0), (int)x.size(1), (int)x.stride(0), (int)dy.stride(0), (int)dx.stride(0),
+                                 mod_stride, (int)rows_per_group, (float)eps, rms ? 1 : 0, cur_stream()),
+           "norm_modulate_bwd");
+  return dx;
+}
+
+// buf: [B, S, W] bf16 view (W contiguous), updated in place. q at column q_off, k at k_off, each H*Dh wide.
+// Token t of the view sits at sequence position t + pos_offset of the cos/sin tables.
+void qk_norm_rope(Tensor buf, const optional<Tensor>& wq, const optional<Tensor>& wk, const optional<Tensor>& cosv,
+                  const optional<Tensor>& sinv, int64_t H, int64_t Dh, int64_t q_off, int64_t k_off, double eps,
+                  bool interleaved, bool inverse, bool do_norm, int64_t rope_start, int64_t pos_offset) {
+  TORCH_CHECK(buf.is_cuda() && buf.scalar_type() == at::kBFloat16 && buf.dim() == 3 && buf.stride(2) == 1, "qk_norm_rope: buf [B,S,W]");
+  const int64_t tokens_per_batch = buf.size(1);
+  c10::cuda::CUDAGuard guard(buf.device());
+  if (cosv.has_value() && cosv->defined())
+    TORCH_CHECK(cosv->scalar_type() == at::kFloat && cosv->is_contiguous() && cosv->size(-1) == Dh / 2,
+                "qk_norm_rope: cos table [positions, Dh/2] fp32");
+  if (cosv.has_value() && cosv->defined())
+    TORCH_CHECK(cosv->numel() >= (tokens_per_batch + pos_offset) * (Dh / 2), "qk_norm_rope: table too short");
+  check_rc(mdb_qk_norm_rope(buf.data_ptr(), opt_ptr(wq), opt_ptr(wk), (const float*)opt_ptr(cosv),
+                            (const float*)opt_ptr(sinv), buf.size(0) * buf.size(1), (int)tokens_per_batch, (int)H,
+                            (int)Dh, (int)buf.stride(1), (int)q_off, (int)k_off, (float)eps, interleaved, inverse,
+                            do_norm, (int)rope_start, buf.stride(0), (int)pos_offset, cur_stream()),
+           "qk_norm_rope");
+}
+
+void qk_norm_rope_bwd(Tensor dbuf, const Tensor& xbuf, const optional<Tensor>& wq, const optional<Tensor>& wk,
+                      const optional<Tensor>& cosv, const optional<Tensor>& sinv, int64_t H, int64_t Dh, int64_t q_off,
+                      int64_t k_off, double eps, bool interleaved, bool do_norm, int64_t rope_start,
+                      int64_t pos_offset) {
+  TORCH_CHECK(dbuf.is_cuda() && dbuf.dim() == 3 && xbuf.dim() == 3 && dbuf.stride(0) == xbuf.stride(0) &&
+                  dbuf.stride(1) == xbuf.stride(1) && dbuf.stride(2) == 1 && xbuf.stride(2) == 1,
+              "qk_norm_rope_bwd: [B,S,W] views with equal strides");
+  const int64_t tokens_per_batch = dbuf.size(1);
+  c10::cuda::CUDAGuard guard(dbuf.device());
+  check_rc(mdb_qk_norm_rope_bwd(dbuf.data_ptr(), xbuf.data_ptr(), opt_ptr(wq), opt_ptr(wk), (const float*)opt_ptr(cosv),
+                                (const float*)opt_ptr(sinv), dbuf.size(0) * dbuf.size(1), (int)tokens_per_batch, (int)H,
+                                (int)Dh, (int)dbuf.stride(1), (int)q_off, (int)k_off, (float)eps, interleaved, do_norm,
+                                (int)rope_start, dbuf.stride(0), (int)pos_offset, cur_stream()),
+           "qk_norm_rope_bwd");
+}
+
+std::tuple<Tensor, Tensor> rope_table(const Tensor& pos, std::vector<int64_t> axes_dim, double theta) {
+  TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kFloat && pos.dim() == 2 && pos.is_contiguous(), "rope_table: pos [T, axes] fp32");
+  c10::cuda::CUDAGuard guard(pos.device());
+  TORCH_CHECK((int64_t)axes_dim.size() == pos.size(1), "rope_table: axes");
+  int ad[4] = {0, 0, 0, 0};
+  int64_t half = 0;
+  for (size_t i = 0; i < axes_dim.size(); ++i) {
+    ad[i] = (int)axes_dim[i];
+    half += axes_dim[i] / 2;
+  }
+  Tensor c = at::empty({pos.size(0), half}, pos.options());
+  Tensor s = at::empty({pos.size(0), half}, pos.options());
+  check_rc(mdb_rope_table(pos.data_ptr<float>(), c.data_ptr<float>(), s.data_ptr<float>(), (int)pos.size(0),
+                          (int)axes_dim.size(), ad, (float)theta, cur_stream()),
+           "rope_table");
+  return {c, s};
+}
+
+// ------------------------------------------------------------------------------------------
+// pointwise
+// ------------------------------------------------------------------------------------------
+Tensor act_fwd(const Tensor& x, const optional<Tensor>& bias, int64_t act) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "act_fwd: contiguous bf16");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  check_rc(mdb_act_fwd(x.data_ptr(), y.data_ptr(), opt_ptr(bias), x.numel(), (int)x.size(-1), (int)act, cur_stream()), "act_fwd");
+  return y;
+}
+Tensor act_bwd(const Tensor& x, const Tensor& dy, const optional<Tensor>& bias, int64_t act) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dy.is_contiguous() && x.scalar_type() == at::kBFloat16, "act_bwd");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = at::empty_like(x);
+  check_rc(mdb_act_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), opt_ptr(bias), x.numel(), (int)x.size(-1), (int)act,
+                       cur_stream()),
+           "act_bwd");
+  return dx;
+}
+Tensor glu_fwd(const Tensor& x, int64_t act, bool second) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kBFloat16, "glu_fwd");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t F = x.size(1) / 2;
+  Tensor y = at::empty({x.size(0), F}, x.options());
+  check_rc(mdb_glu_fwd(x.data_ptr(), y.data_ptr(), x.size(0), (int)F, (int)x.stride(0), (int)y.stride(0), (int)act, second,
+                       cur_stream()),
+           "glu_fwd");
+  return y;
+}
+Tensor glu_bwd(const Tensor& x, const Tensor& dy, int64_t act, bool second) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && dy.dim() == 2 && x.stride(1) == 1 && dy.stride(1) == 1, "glu_bwd");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = at::empty({x.size(0), x.size(1)}, x.options());
+  check_rc(mdb_glu_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.size(0), (int)(x.size(1) / 2), (int)x.stride(0),
+                       (int)dy.stride(0), (int)dx.stride(0), (int)act, second, cur_stream()),
+           "glu_bwd");
+  return dx;
+}
+Tensor gate_residual(const Tensor& x, const Tensor& y, const optional<Tensor>& gate, int64_t rows_per_group,
+                     bool tanh_gate) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && y.is_contiguous() && x.scalar_type() == at::kBFloat16, "gate_residual");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t D = x.size(-1);
+  Tensor out = at::empty_like(x);
+  int gs = 0;
+  if (gate.has_value() && gate->defined()) {
+    TORCH_CHECK(gate->dim() == 2 && gate->stride(1) == 1 && gate->size(1) == D, "gate_residual: gate [groups,D]");
+    gs = (int)gate->stride(0);
+  }
+  check_rc(mdb_gate_residual(x.data_ptr(), y.data_ptr(), opt_ptr(gate), out.data_ptr(), x.numel() / D, (int)D, gs,
+                             (int)rows_per_group, tanh_gate, cur_stream()),
+           "gate_residual");
+  return out;
+}
+void cfg_euler(Tensor x, const Tensor& vc, const optional<Tensor>& vu, const optional<Tensor>& x_bf16, double dt,
+               double s, int64_t mode) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous() && vc.is_contiguous() &&
+                  vc.scalar_type() == at::kBFloat16 && vc.numel() == x.numel(),
+              "cfg_euler");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(mdb_cfg_euler(x.data_ptr<float>(), vc.data_ptr(), opt_ptr(vu),
+                         x_bf16.has_value() && x_bf16->defined() ? x_bf16->data_ptr() : nullptr, x.numel(), (float)dt,
+                         (float)s, (int)mode, cur_stream()),
+           "cfg_euler");
+}
+std::tuple<Tensor, Tensor> flow_match(const Tensor& x0, const Tensor& eps, const Tensor& sigma) {
+  TORCH_CHECK(x0.is_cuda() && x0.scalar_type() == at::kFloat && eps.scalar_type() == at::kFloat &&
+                  sigma.scalar_type() == at::kFloat && x0.is_contiguous() && eps.is_contiguous(),
+              "flow_match: fp32 contiguous");
+  c10::cuda::CUDAGuard guard(x0.device());
+  Tensor xt = at::empty_like(x0, x0.options().dtype(at::kBFloat16));
+  Tensor tgt = at::empty_like(x0);
+  check_rc(mdb_flow_match(x0.data_ptr<float>(), eps.data_ptr<float>(), sigma.data_ptr<float>(), xt.data_ptr(),
+                          tgt.data_ptr<float>(), x0.numel(), x0.numel() / x0.size(0), cur_stream()),
+           "flow_match");
+  return {xt, tgt};
+}
+std::tuple<Tensor, Tensor> mse_loss(const Tensor& pred, const Tensor& target, bool need_grad, double grad_scale) {
+  TORCH_CHECK(pred.is_cuda() && pred.scalar_type() == at::kBFloat16 && target.scalar_type() == at::kFloat &&
+                  pred.is_contiguous() && target.is_contiguous() && pred.numel() == target.numel(),
+              "mse_loss");
+  c10::cuda::CUDAGuard guard(pred.device());
+  Tensor sum = at::zeros({}, target.options());
+  Tensor grad;
+  if (need_grad) grad = at::empty_like(pred);
+  const double n = (double)pred.numel();
+  check_rc(mdb_mse_loss(pred.data_ptr(), target.data_ptr<float>(), need_grad ? grad.data_ptr() : nullptr,
+                        sum.data_ptr<float>(), pred.numel(), (float)(2.0 / n * grad_scale), cur_stream()),
+           "mse_loss");
+  return {sum / n, grad};
+}
+Tensor randn(std::vector<int64_t> shape, int64_t seed, int64_t offset, bool bf16, const Tensor& like) {
+  c10::cuda::CUDAGuard guard(like.device());
+  Tensor out = at::empty(shape, like.options().dtype(bf16 ? at::kBFloat16 : at::kFloat));
+  check_rc(mdb_randn(bf16 ? nullptr : out.data_ptr<float>(), bf16 ? out.data_ptr() : nullptr, out.numel(),
+                     (unsigned long long)seed, (unsigned long long)offset, cur_stream()),
+           "randn");
+  return out;
+}
+std::tuple<Tensor, Tensor> fp8_quant_rows(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kBFloat16, "fp8_quant_rows");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor q = at::empty({x.size(0), x.size(1)}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor sc = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  check_rc(mdb_fp8_quant_rows(x.data_ptr(), q.data_ptr(), sc.data_ptr<float>(), x.size(0), (int)x.size(1),
+                              (int)x.stride(0), (int)q.stride(0), cur_stream()),
+           "fp8_quant_rows");
+  return {q, sc};
+}
+Tensor fp8_dequant(const Tensor& q, const optional<Tensor>& row_scale, double tensor_scale) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.is_contiguous() && q.scalar_type() == at::kFloat8_e4m3fn, "fp8_dequant");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor y = at::empty({q.size(0), q.size(1)}, q.options().dtype(at::kBFloat16));
+  check_rc(mdb_fp8_dequant(q.data_ptr(), (const float*)opt_ptr(row_scale), (float)tensor_scale, y.data_ptr(), q.size(0),
+                           (int)q.size(1), cur_stream()),
+           "fp8_dequant");
+  return y;
+}
+
+// ------------------------------------------------------------------------------------------
+// optimizer (tables are int64 device tensors laid out as MdbTensorEntry / int2)
+// ------------------------------------------------------------------------------------------
+void adamw_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, bool p_bf16, bool g_bf16, bool m_bf16,
+                 double lr, double beta1, double beta2, double eps, double wd, int64_t step, double grad_scale,
+                 const optional<Tensor>& norm_sq, double max_norm, int64_t seed, bool stochastic) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() && table.size(-1) == 6, "adamw: table [n,6] int64");
+  TORCH_CHECK(chunks.is_cuda() && chunks.scalar_type() == at::kInt && chunks.is_contiguous() && chunks.size(-1) == 2, "adamw: chunks [c,2] int32");
+  c10::cuda::CUDAGuard guard(table.device());
+  check_rc(mdb_adamw_multi((const MdbTensorEntry*)table.data_ptr(), chunks.data_ptr<int>(), (int)chunks.size(0),
+                           (int)chunk_elems, p_bf16, g_bf16, m_bf16, (float)lr, (float)beta1, (float)beta2, (float)eps,
+                           (float)wd, (int)step, (float)grad_scale, (const float*)opt_ptr(norm_sq), (float)max_norm,
+                           (unsigned int)seed, stochastic, cur_stream()),
+           "adamw_multi");
+}
+Tensor sumsq_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, bool g_bf16) {
+  c10::cuda::CUDAGuard guard(table.device());
+  Tensor out = at::zeros({}, table.options().dtype(at::kFloat));
+  check_rc(mdb_sumsq_multi((const MdbTensorEntry*)table.data_ptr(), chunks.data_ptr<int>(), (int)chunks.size(0),
+                           (int)chunk_elems, g_bf16, out.data_ptr<float>(), cur_stream()),
+           "sumsq_multi");
+  return out;
+}
+void ema_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, bool p_bf16, double decay) {
+  c10::cuda::CUDAGuard guard(table.device());
+  check_rc(mdb_ema_multi((const MdbTensorEntry*)table.data_ptr(), chunks.data_ptr<int>(), (int)chunks.size(0),
+                         (int)chunk_elems, p_bf16, (float)decay, cur_stream()),
+           "ema_multi");
+}
+
+// ------------------------------------------------------------------------------------------
+// status
+// ------------------------------------------------------------------------------------------
+std::vector<int64_t> read_status(const Tensor& like, bool reset) {
+  int* p = status_ptr(like);
+  int h[4];
+  C10_CUDA_CHECK(cudaMemcpy(h, p, sizeof(h), cudaMemcpyDeviceToHost));
+  if (reset && h[0] != 0) C10_CUDA_CHECK(cudaMemset(p, 0, sizeof(h)));
+  return {h[0], h[1], h[2], h[3]};
+}
+
+// number of kernel launches issued through this library since load
+int64_t launch_count() { return g_launches.load(); }
+
+}  // namespace
+
+TORCH_LIBRARY(mdb200, m) {
+  m.def("launch_count", &launch_count);
+  m.def("gemm", &gemm);
+  m.def("attention_fwd", &attention_fwd);
+  m.def("norm_modulate_fwd", &norm_modulate_fwd);
+  m.def("norm_modulate_bwd", &norm_modulate_bwd);
+  m.def("qk_norm_rope", &qk_norm_rope);
+  m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+  m.def("rope_table", &rope_table);
+  m.def("act_fwd", &act_fwd);
+  m.def("act_bwd", &act_bwd);
+  m.def("glu_fwd", &glu_fwd);
+  m.def("glu_bwd", &glu_bwd);
+  m.def("gate_residual", &gate_residual);
+  m.def("cfg_euler", &cfg_euler);
+  m.def("flow_match", &flow_match);
+  m.def("mse_loss", &mse_loss);
+  m.def("randn", &randn);
+  m.def("fp8_quant_rows", &fp8_quant_rows);
+  m.def("fp8_dequant", &fp8_dequant);
+  m.def("adamw_multi", &adamw_multi);
+  m.def("sumsq_multi", &sumsq_multi);
+  m.def("ema_multi", &ema_multi);
+  m.def("read_status", &read_status);
+}

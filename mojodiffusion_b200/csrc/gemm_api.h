@@ -1,0 +1,54 @@
+// C interface of the tcgen05 GEMM (gemm_tcgen05.cu). Plain pointers and a stream: no framework types,
+// so the kernels build in seconds and can be driven from C, ctypes or the torch binding alike.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MDB_GEMM_MAX_SEG 3
+
+enum {
+  MDB_ACT_NONE = 0,
+  MDB_ACT_GELU_TANH = 1,
+  MDB_ACT_SILU = 2,
+  MDB_ACT_GELU_ERF = 3,
+};
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct MdbGemmArgs {
+  int M, N;                        // output rows / cols (paired mode: N = cols of the combined output)
+  int num_seg;                     // number of K segments accumulated into one output
+  int64_t K[MDB_GEMM_MAX_SEG];     // contraction length per segment
+  const void* A[MDB_GEMM_MAX_SEG]; // K-major: [M, lda]; MN-major (a_mn): [K, lda] read transposed
+  const void* B[MDB_GEMM_MAX_SEG]; // K-major: [N, ldb]; MN-major (b_mn): [K, ldb] read transposed
+  int64_t lda[MDB_GEMM_MAX_SEG];   // leading dimensions in elements (multiples of 8 for bf16, 16 for fp8)
+  int64_t ldb[MDB_GEMM_MAX_SEG];
+  int a_mn, b_mn;                  // operand majors
+  int kind;                        // 0 bf16, 1 fp8 e4m3
+  int bn;                          // 0 = choose, else 64 / 128 / 256
+  int pair_offset;                 // >0: output col c combines B rows c and c + pair_offset (SwiGLU / GEGLU)
+  int act, act_on_second;
+  float alpha;
+  const float* row_scale;          // [M] fp32 or null
+  const float* col_scale;          // [N (+pair_offset)] fp32 or null
+  const void* bias;                // bf16 [N (+pair_offset)] or null
+  const void* residual;            // bf16 [M, ld_res] or null: out = residual + gate * value
+  const void* gate;                // bf16 [groups, gate_stride] or null
+  int ld_res, gate_stride, rows_per_group;
+  void* out;                       // bf16 or fp32 [M, ld_out]
+  int ld_out, out_fp32, accumulate_out;
+  int num_sms;
+  int* status;                     // device int[4], zero on entry; see common.cuh
+} MdbGemmArgs;
+
+int mdb_gemm_launch(const MdbGemmArgs* args, cudaStream_t stream);
+
+// rank-N tiled tensor map (extents/strides innermost first; strides_bytes[0] ignored)
+int mdb_make_tmap(void* out_map, const void* ptr, int elem_bytes, int rank, const int64_t* extents,
+                  const int64_t* strides_bytes, const int* box, int swizzle128);
+
+#ifdef __cplusplus
+}
+#endif

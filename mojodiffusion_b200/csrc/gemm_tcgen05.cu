@@ -1,0 +1,530 @@
+// Persistent warp-specialised GEMM for sm_100a: TMA (128-byte swizzle) -> shared memory ring ->
+// tcgen05.mma with the accumulator in TMEM (double buffered, so the epilogue of tile i overlaps the
+// main loop of tile i+1) -> tcgen05.ld epilogue with fused bias / activation / gated residual /
+// paired (SwiGLU, GEGLU) / dequant-scale math and direct vector stores.
+//
+//   out[M,N] = epi( sum_seg  A_seg[M,K_seg] * B_seg[N,K_seg]^T )
+//
+// Up to three K segments share one accumulator. That is how a LoRA up-projection (A2 = x*down^T,
+// B2 = up), a split input (FLUX single-block linear2 over [attn | gelu(mlp)]) or a beta=1
+// accumulate are folded into one launch without a concat.
+//
+// Operand majors: K-major (row-major [rows,K], the forward layout of x and of nn.Linear weights) and
+// MN-major (the same buffers read transposed: dx = dY*W uses W MN-major, dW = dY^T*x uses both).
+// Element kinds: bf16 (kind::f16) and fp8 e4m3 (kind::f8f6f4, scales applied in the epilogue).
+//
+// Covers the role of the reference's cuBLAS call + bias/cast kernels (serenitymojo/ops/linear.mojo:40-180,182,404),
+// its GEMM backward calls (serenitymojo/ops/linalg_backward.mojo:99-124) and its weight-only fp8 kernel
+// (serenitymojo/ops/fp8_gemm.mojo:28-73).
+#include "common.cuh"
+#include "gemm_api.h"
+
+#include <cudaTypedefs.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace mdb {
+
+constexpr int BM = 128;
+constexpr int BK_BYTES = 128;  // one swizzle atom row: 64 bf16 or 128 fp8
+constexpr int NUM_THREADS = 192;
+
+struct alignas(64) GemmMaps {
+  CUtensorMap a[MDB_GEMM_MAX_SEG];
+  CUtensorMap b[MDB_GEMM_MAX_SEG];
+};
+
+struct GemmParams {
+  int M, N;
+  int num_seg;
+  int kblocks[MDB_GEMM_MAX_SEG];
+  int pair_offset;  // paired mode (>0): second half of the B tile comes from rows n0 + pair_offset
+  int act;          // MDB_ACT_*
+  int act_on_second;  // paired mode: 0 -> act(first)*second (SwiGLU), 1 -> first*act(second) (GEGLU)
+  float alpha;
+  const float* row_scale;          // [M] or null
+  const float* col_scale;          // [N(+pair)] or null
+  const __nv_bfloat16* bias;       // [N(+pair)] or null
+  const __nv_bfloat16* residual;   // [M, ld_res] or null
+  const __nv_bfloat16* gate;       // [groups, gate_stride] or null; group = row / rows_per_group
+  int ld_res, gate_stride, rows_per_group;
+  void* out;
+  int ld_out;
+  int out_fp32;
+  int accumulate_out;  // out += result (fp32 out only)
+  int* status;
+};
+
+template <int ACT>
+__device__ __forceinline__ float apply_act(float x) {
+  if (ACT == MDB_ACT_GELU_TANH) return gelu_tanh_f(x);
+  if (ACT == MDB_ACT_SILU) return silu_f(x);
+  if (ACT == MDB_ACT_GELU_ERF) return gelu_erf_f(x);
+  return x;
+}
+__device__ __forceinline__ float apply_act_rt(int act, float x) {
+  switch (act) {
+    case MDB_ACT_GELU_TANH: return gelu_tanh_f(x);
+    case MDB_ACT_SILU: return silu_f(x);
+    case MDB_ACT_GELU_ERF: return gelu_erf_f(x);
+    default: return x;
+  }
+}
+
+// One 32-column slab of one output row: v[] holds the raw accumulators (and v2[] the paired half).
+__device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int col0, int pair_cols, float (&v)[32],
+                                               float (&v2)[32], bool paired) {
+  const int N = p.N;
+  if (row >= p.M || col0 >= N) return;
+  const float rs = (p.row_scale ? p.row_scale[row] : 1.f) * p.alpha;
+  const int ncols = min(32, N - col0);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (j < ncols) {
+      const int col = col0 + j;
+      float x = v[j] * rs;
+      if (p.col_scale) x *= p.col_scale[col];
+      if (p.bias) x += __bfloat162float(p.bias[col]);
+      if (paired) {
+        float y = v2[j] * rs;
+        if (p.col_scale) y *= p.col_scale[col + pair_cols];
+        if (p.bias) y += __bfloat162float(p.bias[col + pair_cols]);
+        x = p.act_on_second ? x * apply_act_rt(p.act, y) : apply_act_rt(p.act, x) * y;
+      } else {
+        x = apply_act_rt(p.act, x);
+      }
+      v[j] = x;
+    }
+  }
+  if (p.gate || p.residual) {
+    const __nv_bfloat16* g =
+        p.gate ? p.gate + static_cast<size_t>(row / p.rows_per_group) * p.gate_stride + col0 : nullptr;
+    const __nv_bfloat16* r = p.residual ? p.residual + static_cast<size_t>(row) * p.ld_res + col0 : nullptr;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < ncols) {
+        float x = v[j];
+        if (g) x *= __bfloat162float(g[j]);
+        if (r) x += __bfloat162float(r[j]);
+        v[j] = x;
+      }
+    }
+  }
+  if (p.out_fp32) {
+    float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
+    const bool vec = (ncols == 32) && ((reinterpret_cast<uintptr_t>(o) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 t = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (p.accumulate_out) {
+          float4 old = *reinterpret_cast<float4*>(o + j);
+          t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
+        }
+        *reinterpret_cast<float4*>(o + j) = t;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) o[j] = p.accumulate_out ? o[j] + v[j] : v[j];
+    }
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
+    const bool vec = (ncols == 32) && ((reinterpret_cast<uintptr_t>(o) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 t;
+        t.x = pack_bf16x2(v[j], v[j + 1]);
+        t.y = pack_bf16x2(v[j + 2], v[j + 3]);
+        t.z = pack_bf16x2(v[j + 4], v[j + 5]);
+        t.w = pack_bf16x2(v[j + 6], v[j + 7]);
+        *reinterpret_cast<uint4*>(o + j) = t;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) o[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+// KIND: 0 = bf16 operands (kind::f16), 1 = fp8 e4m3 operands (kind::f8f6f4)
+template <int BN, int STAGES, bool A_MN, bool B_MN, int KIND>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+  constexpr int A_BYTES = BM * BK_BYTES;
+  constexpr int B_BYTES = BN * BK_BYTES;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  constexpr int KSTEPS = 4;  // 128-byte rows / 32 bytes per UMMA K step
+  static_assert(!(KIND == 1 && (A_MN || B_MN)), "fp8 operands are K-major only");
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES];
+  __shared__ uint64_t empty_bar[STAGES];
+  __shared__ uint64_t tfull_bar[2];
+  __shared__ uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull_bar[s], 1);
+      mbar_init(&tempty_bar[s], 4);
+    }
+    abort_s = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < p.num_seg; ++s) {
+      tma_prefetch_desc(&maps.a[s]);
+      tma_prefetch_desc(&maps.b[s]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + (p.pair_offset > 0 ? BN / 2 : BN) - 1) / (p.pair_offset > 0 ? BN / 2 : BN);
+  const int num_tiles = tiles_m * tiles_n;
+  int total_kb = 0;
+  for (int s = 0; s < p.num_seg; ++s) total_kb += p.kblocks[s];
+  constexpr int K_ELEMS = (KIND == 0) ? 64 : 128;  // elements per 128-byte row
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int last_stage = -1;
+      uint32_t last_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM;
+        const int nblk = tile / tiles_m;
+        const int n0 = p.pair_offset > 0 ? nblk * (BN / 2) : nblk * BN;
+        for (int s = 0; ok && s < p.num_seg; ++s) {
+          for (int kb = 0; kb < p.kblocks[s]; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s)) {
+              report_status(p.status, STATUS_TIMEOUT, 1, stage);
+              ok = false;
+              break;
+            }
+            uint8_t* sa = smem + stage * STAGE_BYTES;
+            uint8_t* sb = sa + A_BYTES;
+            mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+            const int k0 = kb * K_ELEMS;
+            if (!A_MN) {
+              tma_load_2d(sa, &maps.a[s], &full_bar[stage], k0, m0);
+            } else {
+              // boxes [64 m-elements][64 k-rows], 8 KB each
+              tma_load_2d(sa, &maps.a[s], &full_bar[stage], m0, k0);
+              tma_load_2d(sa + 8192, &maps.a[s], &full_bar[stage], m0 + 64, k0);
+            }
+            if (!B_MN) {
+              constexpr int HALF_ROWS = BN / 2;
+              const int n1 = p.pair_offset > 0 ? n0 + p.pair_offset : n0 + HALF_ROWS;
+              tma_load_2d(sb, &maps.b[s], &full_bar[stage], k0, n0);
+              tma_load_2d(sb + HALF_ROWS * BK_BYTES, &maps.b[s], &full_bar[stage], k0, n1);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * 8192, &maps.b[s], &full_bar[stage], n0 + j * 64, k0);
+            }
+            last_stage = stage;
+            last_phase = phase;
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+      if (!ok && last_stage >= 0) {
+        // abandoned: let the copies already in flight land before the CTA goes away (bounded)
+        uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&full_bar[last_stage], last_phase) && globaltimer_ns() - t0 < 5000000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- UMMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc =
+          (KIND == 0) ? make_idesc(1, UMMA_BF16, UMMA_BF16, A_MN ? 1u : 0u, B_MN ? 1u : 0u, BM, BN)
+                      : make_idesc(1, UMMA_E4M3, UMMA_E4M3, 0u, 0u, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, &abort_s)) {
+          report_status(p.status, STATUS_TIMEOUT, 2, acc);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < total_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, &abort_s)) {
+            report_status(p.status, STATUS_TIMEOUT, 3, stage);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+          const uint64_t da = A_MN ? make_desc_mnmajor_sw128(sa, 8192) : make_desc_kmajor_sw128(sa);
+          const uint64_t db = B_MN ? make_desc_mnmajor_sw128(sb, 8192) : make_desc_kmajor_sw128(sb);
+#pragma unroll
+          for (int k = 0; k < KSTEPS; ++k) {
+            // K-major: 32 bytes along the row per step; MN-major: 16 K-rows of 128 B per step
+            const uint64_t a_k = da + static_cast<uint64_t>(A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+            const uint64_t b_k = db + static_cast<uint64_t>(B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+            if (KIND == 0)
+              umma_f16_ss(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f8_ss(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // smem slot free once these UMMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue (4 warps) -------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const bool paired = p.pair_offset > 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (tile % tiles_m) * BM;
+      const int nblk = tile / tiles_m;
+      const int n0 = paired ? nblk * (BN / 2) : nblk * BN;
+      // warp-uniform decision: the TMEM loads below are warp-collective
+      const bool got = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, &abort_s));
+      if (!got) {
+        if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 4, acc);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      const int out_cols = paired ? BN / 2 : BN;
+#pragma unroll 1
+      for (int c = 0; c < out_cols / 32; ++c) {
+        uint32_t r0[32];
+        float v[32], v2[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r0);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+        if (paired) {
+          tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, r0);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v2[j] = __uint_as_float(r0[j]);
+        }
+        epilogue_row32(p, row, n0 + c * 32, p.pair_offset, v, v2, paired);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(f);
+  }
+  return fn;
+}
+
+}  // namespace mdb
+
+extern "C" int mdb_make_tmap(void* out_map, const void* ptr, int elem_bytes, int rank, const int64_t* extents,
+                             const int64_t* strides_bytes, const int* box, int swizzle128) {
+  auto fn = mdb::get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[5];
+  cuuint32_t bdim[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = static_cast<cuuint64_t>(extents[i]);
+    bdim[i] = static_cast<cuuint32_t>(box[i]);
+    estr[i] = 1;
+    if (i > 0) gstr[i - 1] = static_cast<cuuint64_t>(strides_bytes[i]);
+  }
+  CUtensorMapDataType dt = elem_bytes == 1   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), dt, rank, const_cast<void*>(ptr), gdim, gstr, bdim, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+namespace mdb {
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, int KIND>
+static int launch_variant(const GemmMaps& maps, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = BM * BK_BYTES + BN * BK_BYTES;
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, KIND>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_done = true;
+  }
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int bn_eff = p.pair_offset > 0 ? BN / 2 : BN;
+  const int tiles_n = (p.N + bn_eff - 1) / bn_eff;
+  int grid = tiles_m * tiles_n;
+  if (grid > num_sms) grid = num_sms;
+  if (grid < 1) return 0;
+  kern<<<grid, NUM_THREADS, SMEM, stream>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace mdb
+
+extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
+  using namespace mdb;
+  if (a->M <= 0 || a->N <= 0 || a->num_seg < 1 || a->num_seg > MDB_GEMM_MAX_SEG) return -2;
+  const int eb = a->kind == 1 ? 1 : 2;
+  const int k_elems = BK_BYTES / eb;
+  const bool paired = a->pair_offset > 0;
+  const int sms = a->num_sms > 0 ? a->num_sms : 148;
+  int bn = a->bn;
+  if (bn != 64 && bn != 128 && bn != 256) {
+    // default tile choice: widest tile that still gives every SM work
+    const int tm = (a->M + BM - 1) / BM;
+    bn = 256;
+    if (!paired && tm * ((a->N + 255) / 256) < sms && a->N <= 4096) bn = 128;
+    if (!paired && a->N <= 64) bn = 64;
+  }
+  if (paired && bn != 256) bn = 256;
+  GemmMaps maps;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M;
+  p.N = a->N;
+  p.num_seg = a->num_seg;
+  const int n_rows_total = paired ? a->N + a->pair_offset : a->N;  // rows of B that exist
+  for (int s = 0; s < a->num_seg; ++s) {
+    const int64_t K = a->K[s];
+    if (K <= 0) return -3;
+    p.kblocks[s] = static_cast<int>((K + k_elems - 1) / k_elems);
+    // A
+    {
+      int64_t ext[2], str[2];
+      int box[2];
+      if (!a->a_mn) {  // [M rows][K] row-major
+        ext[0] = K; ext[1] = a->M; str[0] = eb; str[1] = a->lda[s] * eb; box[0] = k_elems; box[1] = BM;
+      } else {  // stored [K rows][M]
+        ext[0] = a->M; ext[1] = K; str[0] = eb; str[1] = a->lda[s] * eb; box[0] = 64; box[1] = 64;
+      }
+      int r = mdb_make_tmap(&maps.a[s], a->A[s], eb, 2, ext, str, box, 1);
+      if (r) return 1000 + r;
+    }
+    {
+      int64_t ext[2], str[2];
+      int box[2];
+      if (!a->b_mn) {  // [N rows][K]
+        ext[0] = K; ext[1] = n_rows_total; str[0] = eb; str[1] = a->ldb[s] * eb; box[0] = k_elems; box[1] = bn / 2;
+      } else {  // stored [K rows][N]
+        ext[0] = a->N; ext[1] = K; str[0] = eb; str[1] = a->ldb[s] * eb; box[0] = 64; box[1] = 64;
+      }
+      int r = mdb_make_tmap(&maps.b[s], a->B[s], eb, 2, ext, str, box, 1);
+      if (r) return 2000 + r;
+    }
+  }
+  p.pair_offset = a->pair_offset;
+  p.act = a->act;
+  p.act_on_second = a->act_on_second;
+  p.alpha = a->alpha;
+  p.row_scale = a->row_scale;
+  p.col_scale = a->col_scale;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
+  p.gate = reinterpret_cast<const __nv_bfloat16*>(a->gate);
+  p.ld_res = a->ld_res;
+  p.gate_stride = a->gate_stride;
+  p.rows_per_group = a->rows_per_group > 0 ? a->rows_per_group : 1;
+  p.out = a->out;
+  p.ld_out = a->ld_out;
+  p.out_fp32 = a->out_fp32;
+  p.accumulate_out = a->accumulate_out;
+  p.status = a->status;
+
+#define MDB_LAUNCH(BN_, ST_, AMN_, BMN_, KIND_) return launch_variant<BN_, ST_, AMN_, BMN_, KIND_>(maps, p, sms, stream)
+  if (a->kind == 1) {
+    if (a->a_mn || a->b_mn) return -4;
+    if (bn == 256) MDB_LAUNCH(256, 4, false, false, 1);
+    if (bn == 128) MDB_LAUNCH(128, 6, false, false, 1);
+    MDB_LAUNCH(64, 8, false, false, 1);
+  }
+  if (!a->a_mn && !a->b_mn) {
+    if (bn == 256) MDB_LAUNCH(256, 4, false, false, 0);
+    if (bn == 128) MDB_LAUNCH(128, 6, false, false, 0);
+    MDB_LAUNCH(64, 8, false, false, 0);
+  }
+  if (!a->a_mn && a->b_mn) {
+    if (bn == 256) MDB_LAUNCH(256, 4, false, true, 0);
+    if (bn == 128) MDB_LAUNCH(128, 6, false, true, 0);
+    MDB_LAUNCH(64, 8, false, true, 0);
+  }
+  if (a->a_mn && a->b_mn) {
+    if (bn == 256) MDB_LAUNCH(256, 4, true, true, 0);
+    if (bn == 128) MDB_LAUNCH(128, 6, true, true, 0);
+    MDB_LAUNCH(64, 8, true, true, 0);
+  }
+  if (bn == 256) MDB_LAUNCH(256, 4, true, false, 0);
+  if (bn == 128) MDB_LAUNCH(128, 6, true, false, 0);
+  MDB_LAUNCH(64, 8, true, false, 0);
+#undef MDB_LAUNCH
+}

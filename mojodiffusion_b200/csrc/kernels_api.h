@@ -1,0 +1,98 @@
+// C interface of the non-GEMM kernels of this package. Every function enqueues work on `st` and
+// returns 0 on success, a negative number for a rejected argument, or a positive cudaError_t.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+enum {
+  MDB_PW_IDENTITY = 0,
+  MDB_PW_GELU_TANH = 1,
+  MDB_PW_SILU = 2,
+  MDB_PW_GELU_ERF = 3,
+  MDB_PW_SIGMOID = 4,
+  MDB_PW_RELU = 5,
+  MDB_PW_TANH = 6,
+};
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// one entry per tensor for the multi-tensor kernels (device array)
+typedef struct MdbTensorEntry {
+  void* param;
+  void* grad;
+  void* exp_avg;
+  void* exp_avg_sq;
+  void* shadow;      // optional bf16 copy of an fp32 master
+  long long numel;
+} MdbTensorEntry;
+
+// ---- norm_rope.cu
+int mdb_norm_modulate_fwd(const void* x, void* out, const void* weight, const void* bias, const void* scale,
+                          const void* shift, float* stats, int rows, int D, int ldx, int ldo, int mod_stride,
+                          int rows_per_group, float eps, int rms, cudaStream_t st);
+int mdb_norm_modulate_bwd(const void* x, const void* dy, void* dx, const void* weight, const void* scale, int rows,
+                          int D, int ldx, int lddy, int lddx, int mod_stride, int rows_per_group, float eps, int rms,
+                          cudaStream_t st);
+int mdb_qk_norm_rope(void* buf, const void* wq, const void* wk, const float* cosv, const float* sinv, long long tokens,
+                     int tokens_per_batch, int H, int Dh, int row_stride, int q_off, int k_off, float eps,
+                     int interleaved, int inverse, int do_norm, int rope_start, long long batch_stride, int pos_offset,
+                     cudaStream_t st);
+int mdb_qk_norm_rope_bwd(void* dbuf, const void* xbuf, const void* wq, const void* wk, const float* cosv,
+                         const float* sinv, long long tokens, int tokens_per_batch, int H, int Dh, int row_stride,
+                         int q_off, int k_off, float eps, int interleaved, int do_norm, int rope_start,
+                         long long batch_stride, int pos_offset, cudaStream_t st);
+int mdb_rope_table(const float* pos, float* cosv, float* sinv, int tokens, int naxes, const int* axes_dim, float theta,
+                   cudaStream_t st);
+
+// ---- pointwise.cu
+int mdb_act_fwd(const void* x, void* y, const void* bias, long long n, int cols, int act, cudaStream_t st);
+int mdb_act_bwd(const void* x, const void* dy, void* dx, const void* bias, long long n, int cols, int act,
+                cudaStream_t st);
+int mdb_glu_fwd(const void* x, void* y, long long rows, int F, int ldx, int ldy, int act, int second, cudaStream_t st);
+int mdb_glu_bwd(const void* x, const void* dy, void* dx, long long rows, int F, int ldx, int lddy, int lddx, int act,
+                int second, cudaStream_t st);
+int mdb_gate_residual(const void* x, const void* y, const void* gate, void* out, long long rows, int D,
+                      int gate_stride, int rows_per_group, int tanh_gate, cudaStream_t st);
+int mdb_cfg_euler(float* x, const void* vc, const void* vu, void* x_bf16, long long n, float dt, float s, int mode,
+                  cudaStream_t st);
+int mdb_flow_match(const float* x0, const float* eps, const float* sigma, void* xt, float* target, long long n,
+                   long long per_sample, cudaStream_t st);
+int mdb_mse_loss(const void* pred, const float* target, void* grad, float* loss_sum, long long n, float grad_coef,
+                 cudaStream_t st);
+int mdb_randn(float* out_f32, void* out_bf16, long long n, unsigned long long seed, unsigned long long offset,
+              cudaStream_t st);
+int mdb_fp8_quant_rows(const void* x, void* q, float* scale, long long rows, int D, int ldx, int ldq, cudaStream_t st);
+int mdb_fp8_dequant(const void* q, const float* row_scale, float tensor_scale, void* y, long long rows, int D,
+                    cudaStream_t st);
+
+// ---- optim.cu
+int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
+                    int g_bf16, int m_bf16, float lr, float beta1, float beta2, float eps, float wd, int step,
+                    float grad_scale, const float* norm_sq, float max_norm, unsigned int seed, int stochastic,
+                    cudaStream_t st);
+int mdb_sumsq_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int g_bf16,
+                    float* out, cudaStream_t st);
+int mdb_ema_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
+                  float decay, cudaStream_t st);
+
+// ---- attention_tcgen05.cu
+// q,k,v,o: bf16 with element strides (batch, seq, head); head_dim contiguous (Dh = 128 or 64).
+// lse: optional fp32 [B, H, Sq] (natural-log-sum-exp of the scaled scores) for the backward pass.
+// kv_len: optional int32 [B] number of valid keys per batch entry (key padding mask).
+typedef struct MdbAttnArgs {
+  const void* q; const void* k; const void* v; void* o;
+  float* lse;
+  const int* kv_len;
+  int B, H, Sq, Skv, Dh;
+  long long q_strides[3], k_strides[3], v_strides[3], o_strides[3];  // (batch, seq, head) in elements
+  float scale;
+  int num_sms;
+  int* status;
+} MdbAttnArgs;
+int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,203 @@
+// Fused optimizer kernels for sm_100a: multi-tensor AdamW in ONE launch (fp32 or bf16 params, fp32 or
+// bf16 gradients, fp32 or bf16 moments, optional stochastic-rounding bf16 write-back and an optional bf16
+// shadow copy of fp32 masters), on-device global gradient norm, and the clip coefficient taken from
+// that norm on the device so no host sync sits between backward and the update.
+//
+// Update order is torch.optim.AdamW's: p *= 1 - lr*wd; m,v EMA; p -= lr/bc1 * m / (sqrt(v)/sqrt(bc2) + eps).
+// Reference behaviour matched: serenitymojo/training/optim.mojo:79-338, serenitymojo/training/fused_adamw_multitensor.mojo:45-285,
+// serenitymojo/training/lora_adamw_ot_fused.mojo:75-142 (bf16 moments + stochastic rounding),
+// serenitymojo/training/lora_adamw_plain_fused.mojo, serenitymojo/training/on_device_global_norm.mojo:1-169,
+// serenitymojo/util/bf16_stochastic_rounding.mojo:13-73.
+#include "common.cuh"
+#include "kernels_api.h"
+
+namespace mdb {
+
+__device__ __forceinline__ uint32_t hash_u32(uint32_t a, uint32_t b, uint32_t c) {
+  // 3-word mix (murmur-style finaliser rounds); good enough for rounding dither
+  uint32_t h = a * 0x9E3779B1u ^ (b + 0x7F4A7C15u) * 0x85EBCA77u ^ (c + 0x165667B1u) * 0xC2B2AE3Du;
+  h ^= h >> 16; h *= 0x85EBCA6Bu; h ^= h >> 13; h *= 0xC2B2AE35u; h ^= h >> 16;
+  return h;
+}
+// stochastic rounding fp32 -> bf16: add 16 uniform random bits below the kept mantissa, truncate
+__device__ __forceinline__ __nv_bfloat16 sr_bf16(float x, uint32_t rnd) {
+  uint32_t u = __float_as_uint(x);
+  if ((u & 0x7f800000u) == 0x7f800000u) return __float2bfloat16_rn(x);  // inf / nan unchanged
+  u += (rnd & 0xffffu);
+  __nv_bfloat16_raw r;
+  r.x = static_cast<unsigned short>(u >> 16);
+  return __nv_bfloat16(r);
+}
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p, long long i);
+template <> __device__ __forceinline__ float ldf<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+  return __bfloat162float(p[i]);
+}
+template <typename T> __device__ __forceinline__ void stf(T* p, long long i, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) {
+  p[i] = __float2bfloat16_rn(v);
+}
+
+struct AdamHyper {
+  float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt;  // bc1 = 1 - beta1^t ; bc2_sqrt = sqrt(1 - beta2^t)
+  float grad_scale;                                 // static multiplier on every gradient (1/world, 1/accum)
+  const float* norm_sq;                             // optional device scalar: sum of squares of the scaled grads
+  float max_norm;                                   // clip threshold (<=0: off)
+  unsigned int seed;                                // stochastic rounding stream
+  int stochastic;                                   // bf16 params only
+};
+
+__device__ __forceinline__ float clip_coef(const AdamHyper& h) {
+  if (h.norm_sq == nullptr || h.max_norm <= 0.f) return 1.f;
+  const float norm = sqrtf(*h.norm_sq) * h.grad_scale;
+  const float c = h.max_norm / (norm + 1e-6f);
+  return c < 1.f ? c : 1.f;
+}
+
+template <typename TP, typename TG, typename TM>
+__device__ __forceinline__ void adamw_elem(TP* p, const TG* g, TM* m, TM* v, __nv_bfloat16* shadow, long long i,
+                                           const AdamHyper& h, float gmul, uint32_t tensor_id) {
+  const float grad = ldf<TG>(g, i) * gmul;
+  float pv = ldf<TP>(p, i);
+  float mv = ldf<TM>(m, i);
+  float vv = ldf<TM>(v, i);
+  pv *= (1.f - h.lr * h.wd);
+  mv = h.beta1 * mv + (1.f - h.beta1) * grad;
+  vv = h.beta2 * vv + (1.f - h.beta2) * grad * grad;
+  const float denom = sqrtf(vv) / h.bc2_sqrt + h.eps;
+  pv -= (h.lr / h.bc1) * (mv / denom);
+  stf<TM>(m, i, mv);
+  stf<TM>(v, i, vv);
+  if constexpr (sizeof(TP) == 2) {
+    if (h.stochastic)
+      p[i] = sr_bf16(pv, hash_u32(h.seed, tensor_id, static_cast<uint32_t>(i)));
+    else
+      p[i] = __float2bfloat16_rn(pv);
+  } else {
+    p[i] = pv;
+    if (shadow) shadow[i] = __float2bfloat16_rn(pv);
+  }
+}
+
+// chunk table: each entry = (tensor index, first element); a block walks chunks grid-stride
+template <typename TP, typename TG, typename TM>
+__global__ void __launch_bounds__(256)
+adamw_multi_kernel(const MdbTensorEntry* __restrict__ tensors, const int2* __restrict__ chunks, int num_chunks,
+                   int chunk_elems, AdamHyper h) {
+  const float gmul = h.grad_scale * clip_coef(h);
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ch = chunks[c];
+    const MdbTensorEntry t = tensors[ch.x];
+    const long long start = static_cast<long long>(ch.y) * chunk_elems;
+    const long long end = min(start + static_cast<long long>(chunk_elems), t.numel);
+    TP* p = reinterpret_cast<TP*>(t.param);
+    const TG* g = reinterpret_cast<const TG*>(t.grad);
+    TM* m = reinterpret_cast<TM*>(t.exp_avg);
+    TM* v = reinterpret_cast<TM*>(t.exp_avg_sq);
+    __nv_bfloat16* sh = reinterpret_cast<__nv_bfloat16*>(t.shadow);
+    for (long long i = start + threadIdx.x; i < end; i += blockDim.x)
+      adamw_elem<TP, TG, TM>(p, g, m, v, sh, i, h, gmul, static_cast<uint32_t>(ch.x));
+  }
+}
+
+template <typename TG>
+__global__ void __launch_bounds__(256)
+sumsq_multi_kernel(const MdbTensorEntry* __restrict__ tensors, const int2* __restrict__ chunks, int num_chunks,
+                   int chunk_elems, float* __restrict__ out) {
+  float acc = 0.f;
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ch = chunks[c];
+    const MdbTensorEntry t = tensors[ch.x];
+    const long long start = static_cast<long long>(ch.y) * chunk_elems;
+    const long long end = min(start + static_cast<long long>(chunk_elems), t.numel);
+    const TG* g = reinterpret_cast<const TG*>(t.grad);
+    for (long long i = start + threadIdx.x; i < end; i += blockDim.x) {
+      const float x = ldf<TG>(g, i);
+      acc += x * x;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ float red[8];
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = acc;
+  __syncthreads();
+  if (w == 0) {
+    float t = l < 8 ? red[l] : 0.f;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (l == 0) atomicAdd(out, t);
+  }
+}
+
+// p_ema = decay * p_ema + (1 - decay) * p   (fp32 ema, any param dtype) over a chunk table
+template <typename TP>
+__global__ void __launch_bounds__(256)
+ema_multi_kernel(const MdbTensorEntry* __restrict__ tensors, const int2* __restrict__ chunks, int num_chunks,
+                 int chunk_elems, float decay) {
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ch = chunks[c];
+    const MdbTensorEntry t = tensors[ch.x];
+    const long long start = static_cast<long long>(ch.y) * chunk_elems;
+    const long long end = min(start + static_cast<long long>(chunk_elems), t.numel);
+    const TP* p = reinterpret_cast<const TP*>(t.param);
+    float* e = reinterpret_cast<float*>(t.exp_avg);
+    for (long long i = start + threadIdx.x; i < end; i += blockDim.x)
+      e[i] = decay * e[i] + (1.f - decay) * ldf<TP>(p, i);
+  }
+}
+
+}  // namespace mdb
+
+using namespace mdb;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems,
+                               int p_bf16, int g_bf16, int m_bf16, float lr, float beta1, float beta2, float eps,
+                               float wd, int step, float grad_scale, const float* norm_sq, float max_norm,
+                               unsigned int seed, int stochastic, cudaStream_t st) {
+  if (num_chunks <= 0) return 0;
+  AdamHyper h;
+  h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.wd = wd;
+  h.bc1 = 1.f - powf(beta1, (float)step);
+  h.bc2_sqrt = sqrtf(1.f - powf(beta2, (float)step));
+  h.grad_scale = grad_scale; h.norm_sq = norm_sq; h.max_norm = max_norm; h.seed = seed; h.stochastic = stochastic;
+  const int grid = num_chunks < 148 * 8 ? num_chunks : 148 * 8;
+  const int2* ch = reinterpret_cast<const int2*>(chunks);
+#define MDB_AD(TP, TG, TM) adamw_multi_kernel<TP, TG, TM><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, h)
+  if (p_bf16) {
+    if (g_bf16) { if (m_bf16) MDB_AD(bf16, bf16, bf16); else MDB_AD(bf16, bf16, float); }
+    else        { if (m_bf16) MDB_AD(bf16, float, bf16); else MDB_AD(bf16, float, float); }
+  } else {
+    if (g_bf16) { if (m_bf16) MDB_AD(float, bf16, bf16); else MDB_AD(float, bf16, float); }
+    else        { if (m_bf16) MDB_AD(float, float, bf16); else MDB_AD(float, float, float); }
+  }
+#undef MDB_AD
+  return (int)cudaGetLastError();
+}
+
+extern "C" int mdb_sumsq_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems,
+                               int g_bf16, float* out, cudaStream_t st) {
+  if (num_chunks <= 0) return 0;
+  const int grid = num_chunks < 148 * 8 ? num_chunks : 148 * 8;
+  const int2* ch = reinterpret_cast<const int2*>(chunks);
+  if (g_bf16)
+    sumsq_multi_kernel<bf16><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, out);
+  else
+    sumsq_multi_kernel<float><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, out);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int mdb_ema_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems,
+                             int p_bf16, float decay, cudaStream_t st) {
+  if (num_chunks <= 0) return 0;
+  const int grid = num_chunks < 148 * 8 ? num_chunks : 148 * 8;
+  const int2* ch = reinterpret_cast<const int2*>(chunks);
+  if (p_bf16)
+    ema_multi_kernel<bf16><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, decay);
+  else
+    ema_multi_kernel<float><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, decay);
+  return (int)cudaGetLastError();
+}

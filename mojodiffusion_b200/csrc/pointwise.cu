@@ -1,0 +1,449 @@
+// Bandwidth-bound pointwise kernels for sm_100a (128-bit accesses, grid-stride, fp32 math):
+// activations and their backward, gated residual, sampler steps (CFG combine + Euler update fused),
+// flow-matching noise/target construction, a counter-based normal RNG, and fp8 (e4m3) row quantisers.
+//
+// Reference behaviour matched: serenitymojo/ops/activations.mojo:59-458, serenitymojo/ops/fused_bias_gelu.mojo:77,
+// serenitymojo/ops/activation_backward.mojo, serenitymojo/ops/loss_swiglu_backward.mojo:209,
+// serenitymojo/ops/elementwise.mojo:313-474 (residual_gate), serenitymojo/sampling/flow_match.mojo:69-91 (CFG + Euler),
+// serenitymojo/training/schedule.mojo:394-413 (x_t and velocity target), serenitymojo/ops/random.mojo:208-250,
+// serenitymojo/ops/fp8_quant.mojo:100-183 and serenitymojo/ops/fp8.mojo:84-279.
+#include "common.cuh"
+#include "kernels_api.h"
+
+#include <cuda_fp8.h>
+
+namespace mdb {
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&v)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  return o;
+}
+
+__device__ __forceinline__ float act_fwd(int act, float x) {
+  switch (act) {
+    case MDB_PW_GELU_TANH: return gelu_tanh_f(x);
+    case MDB_PW_GELU_ERF: return gelu_erf_f(x);
+    case MDB_PW_SILU: return silu_f(x);
+    case MDB_PW_SIGMOID: return sigmoid_f(x);
+    case MDB_PW_RELU: return fmaxf(x, 0.f);
+    case MDB_PW_TANH: return tanhf(x);
+    default: return x;
+  }
+}
+__device__ __forceinline__ float act_grad(int act, float x) {
+  switch (act) {
+    case MDB_PW_GELU_TANH: {
+      const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+      float u = k0 * (x + k1 * x * x * x);
+      float t = tanhf(u);
+      float du = k0 * (1.f + 3.f * k1 * x * x);
+      return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
+    }
+    case MDB_PW_GELU_ERF: {
+      float cdf = 0.5f * (1.f + erff(x * 0.7071067811865476f));
+      float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+      return cdf + x * pdf;
+    }
+    case MDB_PW_SILU: {
+      float s = sigmoid_f(x);
+      return s * (1.f + x * (1.f - s));
+    }
+    case MDB_PW_SIGMOID: {
+      float s = sigmoid_f(x);
+      return s * (1.f - s);
+    }
+    case MDB_PW_RELU: return x > 0.f ? 1.f : 0.f;
+    case MDB_PW_TANH: {
+      float t = tanhf(x);
+      return 1.f - t * t;
+    }
+    default: return 1.f;
+  }
+}
+
+// y = act(x (+ bias[col]))
+__global__ void act_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, const uint4* __restrict__ bias,
+                               long long nvec, int cols_vec, int act) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float v[8];
+    unpack8(x[i], v);
+    if (bias) {
+      float b[8];
+      unpack8(bias[i % cols_vec], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += b[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = act_fwd(act, v[j]);
+    y[i] = pack8(v);
+  }
+}
+// dx = dy * act'(x (+bias))
+__global__ void act_bwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, uint4* __restrict__ dx,
+                               const uint4* __restrict__ bias, long long nvec, int cols_vec, int act) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float v[8], g[8];
+    unpack8(x[i], v);
+    unpack8(dy[i], g);
+    if (bias) {
+      float b[8];
+      unpack8(bias[i % cols_vec], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += b[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] *= act_grad(act, v[j]);
+    dx[i] = pack8(g);
+  }
+}
+
+// gated-linear-unit forward on a [rows, 2F] buffer (first half a, second half b):
+//   act_on_second = 0: y = act(a) * b (SwiGLU);  1: y = a * act(b) (GEGLU)
+__global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long rows,
+                               int F, int ldx, int ldy, int act, int second) {
+  const int fv = F >> 3;
+  const long long n = rows * fv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / fv;
+    const int c = static_cast<int>(i % fv) * 8;
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + r * ldx + c), a);
+    unpack8(*reinterpret_cast<const uint4*>(x + r * ldx + F + c), b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = second ? a[j] * act_fwd(act, b[j]) : act_fwd(act, a[j]) * b[j];
+    *reinterpret_cast<uint4*>(y + r * ldy + c) = pack8(a);
+  }
+}
+// backward: dx[rows, 2F] from dy[rows, F] and the saved pre-activation x
+__global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                               __nv_bfloat16* __restrict__ dx, long long rows, int F, int ldx, int lddy, int lddx,
+                               int act, int second) {
+  const int fv = F >> 3;
+  const long long n = rows * fv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / fv;
+    const int c = static_cast<int>(i % fv) * 8;
+    float a[8], b[8], g[8], da[8], db[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + r * ldx + c), a);
+    unpack8(*reinterpret_cast<const uint4*>(x + r * ldx + F + c), b);
+    unpack8(*reinterpret_cast<const uint4*>(dy + r * lddy + c), g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (second) {
+        da[j] = g[j] * act_fwd(act, b[j]);
+        db[j] = g[j] * a[j] * act_grad(act, b[j]);
+      } else {
+        da[j] = g[j] * b[j] * act_grad(act, a[j]);
+        db[j] = g[j] * act_fwd(act, a[j]);
+      }
+    }
+    *reinterpret_cast<uint4*>(dx + r * lddx + c) = pack8(da);
+    *reinterpret_cast<uint4*>(dx + r * lddx + F + c) = pack8(db);
+  }
+}
+
+// out = x + gate[group] * y   (gate may be null: plain add). tanh_gate: gate -> tanh(gate)
+__global__ void gate_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ y,
+                                     const __nv_bfloat16* __restrict__ gate, __nv_bfloat16* __restrict__ out,
+                                     long long rows, int D, int gate_stride, int rows_per_group, int tanh_gate) {
+  const int dv = D >> 3;
+  const long long n = rows * dv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / dv;
+    const int c = static_cast<int>(i % dv) * 8;
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + r * D + c), a);
+    unpack8(*reinterpret_cast<const uint4*>(y + r * D + c), b);
+    if (gate) {
+      float g[8];
+      unpack8(*reinterpret_cast<const uint4*>(gate + (r / rows_per_group) * gate_stride + c), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += (tanh_gate ? tanhf(g[j]) : g[j]) * b[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += b[j];
+    }
+    *reinterpret_cast<uint4*>(out + r * D + c) = pack8(a);
+  }
+}
+
+// Sampler step on an fp32 latent state:  v = CFG(v_cond, v_uncond);  x += dt * v;  x_bf16 = bf16(x)
+//   mode 0: no guidance (v = v_cond)           1: v = v_u + s (v_c - v_u)   (textbook)
+//   mode 2: v = v_c + s (v_c - v_u)            (cond-anchored)
+__global__ void cfg_euler_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ vc,
+                                 const __nv_bfloat16* __restrict__ vu, __nv_bfloat16* __restrict__ x_bf16, long long n,
+                                 float dt, float s, int mode) {
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    if (i + 4 <= n) {
+      float4 xv = *reinterpret_cast<float4*>(x + i);
+      uint2 c = *reinterpret_cast<const uint2*>(vc + i);
+      float2 c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y);
+      float v[4] = {c0.x, c0.y, c1.x, c1.y};
+      if (mode != 0) {
+        uint2 u = *reinterpret_cast<const uint2*>(vu + i);
+        float2 u0 = unpack_bf16x2(u.x), u1 = unpack_bf16x2(u.y);
+        float w[4] = {u0.x, u0.y, u1.x, u1.y};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = (mode == 1) ? w[j] + s * (v[j] - w[j]) : v[j] + s * (v[j] - w[j]);
+      }
+      xv.x += dt * v[0]; xv.y += dt * v[1]; xv.z += dt * v[2]; xv.w += dt * v[3];
+      *reinterpret_cast<float4*>(x + i) = xv;
+      if (x_bf16) {
+        uint2 o;
+        o.x = pack_bf16x2(xv.x, xv.y);
+        o.y = pack_bf16x2(xv.z, xv.w);
+        *reinterpret_cast<uint2*>(x_bf16 + i) = o;
+      }
+    } else {
+      for (long long k = i; k < n; ++k) {
+        float v = __bfloat162float(vc[k]);
+        if (mode != 0) {
+          float w = __bfloat162float(vu[k]);
+          v = (mode == 1) ? w + s * (v - w) : v + s * (v - w);
+        }
+        float xv = x[k] + dt * v;
+        x[k] = xv;
+        if (x_bf16) x_bf16[k] = __float2bfloat16_rn(xv);
+      }
+    }
+  }
+}
+
+// Flow matching: x_t = (1 - sigma_b) x0 + sigma_b eps ; target = eps - x0 ; sigma per sample
+__global__ void flow_match_kernel(const float* __restrict__ x0, const float* __restrict__ eps,
+                                  const float* __restrict__ sigma, __nv_bfloat16* __restrict__ xt,
+                                  float* __restrict__ target, long long n, long long per_sample) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float s = sigma[i / per_sample];
+    const float a = x0[i], e = eps[i];
+    xt[i] = __float2bfloat16_rn((1.f - s) * a + s * e);
+    target[i] = e - a;
+  }
+}
+
+// mean squared error partial sums + gradient: d = pred - target; grad = d * (2 / n) * grad_scale
+__global__ void mse_loss_kernel(const __nv_bfloat16* __restrict__ pred, const float* __restrict__ target,
+                                __nv_bfloat16* __restrict__ grad, float* __restrict__ loss_sum, long long n,
+                                float grad_coef) {
+  float acc = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float d = __bfloat162float(pred[i]) - target[i];
+    acc += d * d;
+    if (grad) grad[i] = __float2bfloat16_rn(d * grad_coef);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ float red[32];
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = acc;
+  __syncthreads();
+  if (w == 0) {
+    float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (l == 0) atomicAdd(loss_sum, t);
+  }
+}
+
+// Philox-4x32-10 counter RNG -> Box-Muller normals. Element i of a tensor drawn with (seed, offset)
+// depends only on (seed, offset + i/4): the stream is reproducible for any launch geometry.
+__device__ __forceinline__ void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+    const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
+    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+__global__ void randn_kernel(float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16, long long n,
+                             unsigned long long seed, unsigned long long offset) {
+  const long long groups = (n + 3) / 4;
+  for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups; g += (long long)gridDim.x * blockDim.x) {
+    const unsigned long long ctr = offset + static_cast<unsigned long long>(g);
+    uint32_t c[4] = {static_cast<uint32_t>(ctr), static_cast<uint32_t>(ctr >> 32), 0u, 0u};
+    philox4x32_10(c, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+    float z[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      // u1 in (0,1], u2 in [0,1)
+      const float u1 = (static_cast<float>(c[2 * h] >> 8) + 1.0f) * (1.0f / 16777216.0f);
+      const float u2 = static_cast<float>(c[2 * h + 1] >> 8) * (1.0f / 16777216.0f);
+      const float r = sqrtf(-2.0f * logf(u1));
+      float s, co;
+      sincospif(2.0f * u2, &s, &co);
+      z[2 * h] = r * co;
+      z[2 * h + 1] = r * s;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long i = g * 4 + j;
+      if (i < n) {
+        if (out_f32) out_f32[i] = z[j];
+        if (out_bf16) out_bf16[i] = __float2bfloat16_rn(z[j]);
+      }
+    }
+  }
+}
+
+// fp8 e4m3 per-row quantiser: scale[r] = absmax(row)/448 ; q = rne(x / scale). One warp per row.
+__global__ void fp8_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_storage_t* __restrict__ q,
+                                      float* __restrict__ scale, long long rows, int D, int ldx, int ldq) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * ldx;
+  float amax = 0.f;
+  for (int c = lane * 8; c < D; c += 256) {
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(xr + c), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float sc = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / sc;
+  if (lane == 0) scale[row] = sc;
+  __nv_fp8_storage_t* qr = q + row * ldq;
+  for (int c = lane * 8; c < D; c += 256) {
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(xr + c), v);
+    uint2 o;
+    uint32_t w[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t b = __nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, __NV_E4M3);
+      w[j >> 2] |= b << ((j & 3) * 8);
+    }
+    o.x = w[0];
+    o.y = w[1];
+    *reinterpret_cast<uint2*>(qr + c) = o;
+  }
+}
+// dequant: y = fp8 * (row_scale[r] or tensor_scale)
+__global__ void fp8_dequant_kernel(const __nv_fp8_storage_t* __restrict__ q, const float* __restrict__ row_scale,
+                                   float tensor_scale, __nv_bfloat16* __restrict__ y, long long rows, int D) {
+  const int dv = D >> 3;
+  const long long n = rows * dv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / dv;
+    const float sc = row_scale ? row_scale[r] : tensor_scale;
+    const uint2 u = *reinterpret_cast<const uint2*>(q + i * 8);
+    const uint32_t w[2] = {u.x, u.y};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const __nv_fp8_storage_t b = static_cast<__nv_fp8_storage_t>((w[j >> 2] >> ((j & 3) * 8)) & 0xffu);
+      const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
+      v[j] = __half2float(*reinterpret_cast<const __half*>(&h)) * sc;
+    }
+    *reinterpret_cast<uint4*>(y + i * 8) = pack8(v);
+  }
+}
+
+static inline int grid_for(long long n, int threads) {
+  long long b = (n + threads - 1) / threads;
+  const long long cap = 148ll * 16;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace mdb
+
+using namespace mdb;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int mdb_act_fwd(const void* x, void* y, const void* bias, long long n, int cols, int act, cudaStream_t st) {
+  if (n % 8 || (bias && cols % 8)) return -1;
+  if (n == 0) return 0;
+  act_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((const uint4*)x, (uint4*)y, (const uint4*)bias, n / 8,
+                                                       cols > 0 ? cols / 8 : 1, act);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_act_bwd(const void* x, const void* dy, void* dx, const void* bias, long long n, int cols, int act,
+                           cudaStream_t st) {
+  if (n % 8 || (bias && cols % 8)) return -1;
+  if (n == 0) return 0;
+  act_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((const uint4*)x, (const uint4*)dy, (uint4*)dx,
+                                                       (const uint4*)bias, n / 8, cols > 0 ? cols / 8 : 1, act);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_glu_fwd(const void* x, void* y, long long rows, int F, int ldx, int ldy, int act, int second,
+                           cudaStream_t st) {
+  if (F % 8 || ldx % 8 || ldy % 8) return -1;
+  if (rows == 0) return 0;
+  glu_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, rows, F, ldx, ldy, act, second);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_glu_bwd(const void* x, const void* dy, void* dx, long long rows, int F, int ldx, int lddy, int lddx,
+                           int act, int second, cudaStream_t st) {
+  if (F % 8 || ldx % 8 || lddy % 8 || lddx % 8) return -1;
+  if (rows == 0) return 0;
+  glu_bwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (bf16*)dx, rows, F,
+                                                                ldx, lddy, lddx, act, second);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_gate_residual(const void* x, const void* y, const void* gate, void* out, long long rows, int D,
+                                 int gate_stride, int rows_per_group, int tanh_gate, cudaStream_t st) {
+  if (D % 8 || (gate && gate_stride % 8)) return -1;
+  if (rows == 0) return 0;
+  if (rows_per_group <= 0) rows_per_group = 1;
+  gate_residual_kernel<<<grid_for(rows * (D / 8), 256), 256, 0, st>>>((const bf16*)x, (const bf16*)y, (const bf16*)gate,
+                                                                      (bf16*)out, rows, D, gate_stride, rows_per_group,
+                                                                      tanh_gate);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_cfg_euler(float* x, const void* vc, const void* vu, void* x_bf16, long long n, float dt, float s,
+                             int mode, cudaStream_t st) {
+  if (n == 0) return 0;
+  if (mode != 0 && vu == nullptr) return -1;
+  cfg_euler_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, st>>>(x, (const bf16*)vc, (const bf16*)vu, (bf16*)x_bf16, n, dt,
+                                                               s, mode);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_flow_match(const float* x0, const float* eps, const float* sigma, void* xt, float* target,
+                              long long n, long long per_sample, cudaStream_t st) {
+  if (n == 0) return 0;
+  flow_match_kernel<<<grid_for(n, 256), 256, 0, st>>>(x0, eps, sigma, (bf16*)xt, target, n, per_sample);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_mse_loss(const void* pred, const float* target, void* grad, float* loss_sum, long long n,
+                            float grad_coef, cudaStream_t st) {
+  if (n == 0) return 0;
+  mse_loss_kernel<<<grid_for(n, 256), 256, 0, st>>>((const bf16*)pred, target, (bf16*)grad, loss_sum, n, grad_coef);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_randn(float* out_f32, void* out_bf16, long long n, unsigned long long seed,
+                         unsigned long long offset, cudaStream_t st) {
+  if (n == 0) return 0;
+  randn_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, st>>>(out_f32, (bf16*)out_bf16, n, seed, offset);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_fp8_quant_rows(const void* x, void* q, float* scale, long long rows, int D, int ldx, int ldq,
+                                  cudaStream_t st) {
+  if (D % 8 || ldx % 8 || ldq % 8) return -1;
+  if (rows == 0) return 0;
+  const long long blocks = (rows * 32 + 255) / 256;
+  fp8_quant_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>((const bf16*)x, (__nv_fp8_storage_t*)q, scale, rows, D, ldx,
+                                                          ldq);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_fp8_dequant(const void* q, const float* row_scale, float tensor_scale, void* y, long long rows, int D,
+                               cudaStream_t st) {
+  if (D % 8) return -1;
+  if (rows == 0) return 0;
+  fp8_dequant_kernel<<<grid_for(rows * (D / 8), 256), 256, 0, st>>>((const __nv_fp8_storage_t*)q, row_scale,
+                                                                    tensor_scale, (bf16*)y, rows, D);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,143 @@
+"""Building blocks shared by the backbones: a Linear that runs the tcgen05 GEMM with fused epilogues and can
+carry LoRA adapters (whole-weight or per-row-range for fused projections), embedders and small helpers."""
+from __future__ import annotations
+
+import math
+import zlib
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+
+
+class LoRASlot(nn.Module):
+    """One low-rank adapter ``delta = (alpha / rank) * up @ down`` for rows [row0, row1) of a host weight.
+
+    ``down`` [rank, in] is initialised kaiming-uniform(a=sqrt(5)), ``up`` [rows, rank] with zeros, as in
+    serenitymojo/models/flux/flux_stack_lora.mojo:104-121. ``key`` is the checkpoint prefix of the adapter.
+    """
+
+    def __init__(self, key: str, in_features: int, rows: Tuple[int, int], rank: int, alpha: float, dtype, device,
+                 seed: int = 0):
+        super().__init__()
+        self.key = key
+        self.row0, self.row1 = rows
+        self.rank = rank
+        self.alpha = float(alpha)
+        # kaiming-uniform(a=sqrt(5)) == U(-1/sqrt(in), 1/sqrt(in)); drawn from a generator keyed by (seed, key) so
+        # every rank of a data-parallel job builds identical adapters without a broadcast
+        gen = torch.Generator().manual_seed((int(seed) * 1000003 + zlib.crc32(key.encode())) & 0x7FFFFFFFFFFF)
+        bound = 1.0 / math.sqrt(in_features)
+        down = (torch.rand(rank, in_features, generator=gen, dtype=torch.float32) * 2.0 - 1.0) * bound
+        self.down = nn.Parameter(down.to(dtype=dtype, device=device))
+        self.up = nn.Parameter(torch.zeros(self.row1 - self.row0, rank, dtype=dtype, device=device))
+
+    @property
+    def scale(self) -> float:
+        return self.alpha / self.rank
+
+
+class Linear(nn.Module):
+    """``y = x W^T + b`` on the tcgen05 GEMM, with optional fused activation / gated residual and LoRA slots."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        self.slots = nn.ModuleList()
+        self.lora_multiplier = 1.0
+        self.reset_parameters()
+
+    def reset_parameters(self, std: Optional[float] = None):
+        std = std if std is not None else 1.0 / math.sqrt(self.in_features)
+        with torch.no_grad():
+            self.weight.normal_(0.0, std)
+            if self.bias is not None:
+                self.bias.zero_()
+
+    # ---- LoRA -------------------------------------------------------------------------------
+    def add_lora(self, key: str, rank: int, alpha: float, rows: Optional[Tuple[int, int]] = None,
+                 seed: int = 0) -> LoRASlot:
+        rows = rows or (0, self.out_features)
+        slot = LoRASlot(key, self.in_features, rows, rank, alpha, self.weight.dtype, self.weight.device, seed)
+        self.slots.append(slot)
+        return slot
+
+    def _lora_operands(self):
+        """(down_cat [sum r, K], up_blk [N, sum r]) with each slot's scale folded into its up block."""
+        slots: List[LoRASlot] = list(self.slots)
+        if len(slots) == 1 and slots[0].row0 == 0 and slots[0].row1 == self.out_features:
+            s = slots[0]
+            return s.down, s.up * (s.scale * self.lora_multiplier)
+        down = torch.cat([s.down for s in slots], 0)
+        R = down.shape[0]
+        up = self.weight.new_zeros(self.out_features, R)
+        cols = 0
+        pieces = []
+        for s in slots:
+            pieces.append((s, cols))
+            cols += s.rank
+        if torch.is_grad_enabled() and any(s.up.requires_grad for s in slots):
+            rows = []
+            # assemble differentiably: pad each up block to full width, then stack rows in order
+            cover = sorted(pieces, key=lambda t: t[0].row0)
+            cur = 0
+            for s, c0 in cover:
+                if s.row0 > cur:
+                    rows.append(self.weight.new_zeros(s.row0 - cur, R))
+                blk = torch.nn.functional.pad(s.up * (s.scale * self.lora_multiplier), (c0, R - c0 - s.rank))
+                rows.append(blk)
+                cur = s.row1
+            if cur < self.out_features:
+                rows.append(self.weight.new_zeros(self.out_features - cur, R))
+            up = torch.cat(rows, 0)
+        else:
+            for s, c0 in pieces:
+                up[s.row0:s.row1, c0:c0 + s.rank] = s.up * (s.scale * self.lora_multiplier)
+        return down, up
+
+    # ---- forward ------------------------------------------------------------------------------
+    def forward(self, x, act=None, residual=None, gate=None, rows_per_group: int = 1, out=None):
+        if len(self.slots) == 0:
+            return ops.linear(x, self.weight, self.bias, act, residual, gate, rows_per_group, out=out)
+        down, up = self._lora_operands()
+        return ops.lora_linear(x, self.weight, self.bias, down, up, 1.0, act, residual, gate, rows_per_group, out)
+
+
+class MLPEmbedder(nn.Module):
+    """Linear -> SiLU -> Linear (timestep / guidance / pooled-vector embedders; serenitymojo/ops/embeddings.mojo:245-297)."""
+
+    def __init__(self, in_dim: int, hidden: int, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.in_layer = Linear(in_dim, hidden, True, dtype, device)
+        self.out_layer = Linear(hidden, hidden, True, dtype, device)
+
+    def forward(self, x):
+        return self.out_layer(self.in_layer(x, act="silu"))
+
+
+def timestep_embedding(t: torch.Tensor, dim: int, max_period: float = 10000.0, time_factor: float = 1000.0,
+                       cos_first: bool = True) -> torch.Tensor:
+    """Sinusoidal embedding [B, dim] (fp32). FLUX uses cos-first with t scaled by 1000
+    (serenitymojo/ops/embeddings.mojo:55-111; serenitymojo/models/dit/flux1_dit.mojo:412-457)."""
+    t = t.float() * time_factor
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half)
+    args = t[:, None] * freqs[None]
+    emb = torch.cat([torch.cos(args), torch.sin(args)] if cos_first else [torch.sin(args), torch.cos(args)], dim=-1)
+    if dim % 2:
+        emb = torch.cat([emb, torch.zeros_like(emb[:, :1])], dim=-1)
+    return emb
+
+
+def model_dtype(m: nn.Module):
+    return next(m.parameters()).dtype
+
+
+def iter_linears(module: nn.Module, prefix: str = ""):
+    for name, sub in module.named_modules():
+        if isinstance(sub, Linear):
+            yield name, sub

@@ -1,0 +1,241 @@
+"""Plain PyTorch references of every op in this package.
+
+They are the CPU path (autograd-capable, any dtype) and the numerics oracle of the CUDA kernels: the GPU
+tests run a kernel and compare against the function of the same name here evaluated in fp32.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+ACT_NONE, ACT_GELU_TANH, ACT_SILU, ACT_GELU_ERF, ACT_SIGMOID, ACT_RELU, ACT_TANH = range(7)
+
+_ACT_NAMES = {
+    None: ACT_NONE, "none": ACT_NONE, "identity": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU_ERF,
+    "gelu_erf": ACT_GELU_ERF, "silu": ACT_SILU, "swish": ACT_SILU, "sigmoid": ACT_SIGMOID, "relu": ACT_RELU,
+    "tanh": ACT_TANH,
+}
+
+
+def act_code(act) -> int:
+    if isinstance(act, int):
+        return act
+    return _ACT_NAMES[act]
+
+
+def activation(x: torch.Tensor, act) -> torch.Tensor:
+    a = act_code(act)
+    if a == ACT_NONE:
+        return x
+    if a == ACT_GELU_TANH:
+        return F.gelu(x, approximate="tanh")
+    if a == ACT_GELU_ERF:
+        return F.gelu(x)
+    if a == ACT_SILU:
+        return F.silu(x)
+    if a == ACT_SIGMOID:
+        return torch.sigmoid(x)
+    if a == ACT_RELU:
+        return F.relu(x)
+    if a == ACT_TANH:
+        return torch.tanh(x)
+    raise ValueError(a)
+
+
+def _group_expand(v: torch.Tensor, rows: int, rows_per_group: int) -> torch.Tensor:
+    """[groups, D] -> [rows, D] where row r uses group r // rows_per_group."""
+    if v.shape[0] == 1:
+        return v.expand(rows, -1)
+    idx = torch.arange(rows, device=v.device) // rows_per_group
+    return v[idx]
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
+           residual: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, rows_per_group: int = 1,
+           extra: Sequence[tuple] = (), out_dtype=None) -> torch.Tensor:
+    """``act(x @ w.T + sum_i a_i @ b_i.T + bias)``, then ``residual + gate[group] * value``. 2-D operands."""
+    y = x.float() @ w.float().t()
+    for a2, b2 in extra:
+        y = y + a2.float() @ b2.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    y = activation(y, act)
+    if gate is not None:
+        y = y * _group_expand(gate.float(), y.shape[0], rows_per_group)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(out_dtype or x.dtype)
+
+
+def linear_glu(x, w, bias=None, act="silu", act_on_second=False, out_dtype=None):
+    """Paired projection: ``h = x @ w.T + b``; halves (a, b) -> ``act(a) * b`` (SwiGLU) or ``a * act(b)`` (GEGLU)."""
+    h = x.float() @ w.float().t()
+    if bias is not None:
+        h = h + bias.float()
+    a, b = h.chunk(2, dim=-1)
+    y = a * activation(b, act) if act_on_second else activation(a, act) * b
+    return y.to(out_dtype or x.dtype)
+
+
+def glu(h, act="silu", act_on_second=False):
+    a, b = h.float().chunk(2, dim=-1)
+    y = a * activation(b, act) if act_on_second else activation(a, act) * b
+    return y.to(h.dtype)
+
+
+def norm_modulate(x, weight=None, bias=None, scale=None, shift=None, rows_per_group: int = 1, eps: float = 1e-6,
+                  rms: bool = False):
+    """LayerNorm or RMSNorm over the last dim, optional affine, then ``* (1 + scale[g]) + shift[g]``. x: [rows, D]."""
+    xf = x.float()
+    if rms:
+        y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    else:
+        mu = xf.mean(-1, keepdim=True)
+        var = (xf - mu).pow(2).mean(-1, keepdim=True)
+        y = (xf - mu) * torch.rsqrt(var + eps)
+    if weight is not None:
+        y = y * weight.float()
+    if bias is not None:
+        y = y + bias.float()
+    if scale is not None:
+        y = y * (1.0 + _group_expand(scale.float(), y.shape[0], rows_per_group))
+    if shift is not None:
+        y = y + _group_expand(shift.float(), y.shape[0], rows_per_group)
+    return y.to(x.dtype)
+
+
+def rope_table(pos: torch.Tensor, axes_dim: Sequence[int], theta: float = 10000.0):
+    """cos/sin [T, sum(axes_dim)/2] from per-token positions [T, n_axes] (fp64 angle, like the kernel)."""
+    cols_c, cols_s = [], []
+    for a, d in enumerate(axes_dim):
+        half = d // 2
+        i = torch.arange(half, dtype=torch.float64, device=pos.device)
+        freq = torch.exp(-math.log(theta) * i / half)
+        ang = pos[:, a].double()[:, None] * freq[None, :]
+        cols_c.append(torch.cos(ang))
+        cols_s.append(torch.sin(ang))
+    return torch.cat(cols_c, -1).float(), torch.cat(cols_s, -1).float()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool = True) -> torch.Tensor:
+    """x: [..., S, H, Dh]; cos/sin: [S, Dh/2]. Interleaved pairs (2i, 2i+1) or half-split pairs (i, i+Dh/2)."""
+    xf = x.float()
+    c = cos[:, None, :]
+    s = sin[:, None, :]
+    if interleaved:
+        a = xf[..., 0::2]
+        b = xf[..., 1::2]
+        ra = a * c - b * s
+        rb = a * s + b * c
+        out = torch.stack((ra, rb), dim=-1).flatten(-2)
+    else:
+        half = xf.shape[-1] // 2
+        a = xf[..., :half]
+        b = xf[..., half:]
+        out = torch.cat((a * c - b * s, b * c + a * s), dim=-1)
+    return out.to(x.dtype)
+
+
+def rms_norm_heads(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    if weight is not None:
+        y = y * weight.float()
+    return y.to(x.dtype)
+
+
+def qk_norm_rope(q, k, wq=None, wk=None, cos=None, sin=None, eps=1e-6, interleaved=True, do_norm=True,
+                 rope_start: int = 0):
+    """q, k: [B, S, H, Dh] -> per-head RMSNorm (weights [Dh]) then rotary on tokens >= rope_start."""
+    if do_norm:
+        q = rms_norm_heads(q, wq, eps)
+        k = rms_norm_heads(k, wk, eps)
+    if cos is not None:
+        if rope_start > 0:
+            q = torch.cat((q[:, :rope_start], apply_rope(q[:, rope_start:], cos[rope_start:], sin[rope_start:], interleaved)), 1)
+            k = torch.cat((k[:, :rope_start], apply_rope(k[:, rope_start:], cos[rope_start:], sin[rope_start:], interleaved)), 1)
+        else:
+            q = apply_rope(q, cos, sin, interleaved)
+            k = apply_rope(k, cos, sin, interleaved)
+    return q, k
+
+
+def attention(q, k, v, scale: Optional[float] = None, kv_len: Optional[torch.Tensor] = None,
+              return_lse: bool = False):
+    """q: [B, Sq, H, Dh], k/v: [B, Skv, H, Dh] -> [B, Sq, H, Dh]; keys >= kv_len[b] are masked."""
+    B, Sq, H, Dh = q.shape
+    Skv = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(Dh)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    if kv_len is not None:
+        mask = torch.arange(Skv, device=q.device)[None, :] >= kv_len.to(q.device)[:, None]
+        s = s.masked_fill(mask[:, None, None, :], float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse[..., None])
+    o = torch.einsum("bhqk,bkhd->bqhd", p, v.float()).to(q.dtype)
+    if return_lse:
+        return o, lse
+    return o
+
+
+def gate_residual(x, y, gate=None, rows_per_group: int = 1, tanh_gate: bool = False):
+    """x + gate[g] * y over [rows, D] (gate None: x + y)."""
+    if gate is None:
+        return (x.float() + y.float()).to(x.dtype)
+    g = gate.float()
+    if tanh_gate:
+        g = torch.tanh(g)
+    x2 = x.reshape(-1, x.shape[-1]).float()
+    y2 = y.reshape(-1, y.shape[-1]).float()
+    out = x2 + _group_expand(g, x2.shape[0], rows_per_group) * y2
+    return out.reshape(x.shape).to(x.dtype)
+
+
+def cfg_combine(vc, vu, s: float, mode: int):
+    """mode 0: vc; 1: vu + s (vc - vu) (textbook); 2: vc + s (vc - vu) (cond-anchored)."""
+    if mode == 0:
+        return vc.float()
+    if mode == 1:
+        return vu.float() + s * (vc.float() - vu.float())
+    return vc.float() + s * (vc.float() - vu.float())
+
+
+def cfg_euler(x: torch.Tensor, vc, vu, dt: float, s: float = 1.0, mode: int = 0):
+    """fp32 latent update: x + dt * CFG(vc, vu)."""
+    return x + dt * cfg_combine(vc, vu, s, mode)
+
+
+def flow_match(x0: torch.Tensor, eps: torch.Tensor, sigma: torch.Tensor):
+    """x_t = (1 - sigma) x0 + sigma eps (bf16 on GPU), target = eps - x0 (fp32)."""
+    s = sigma.reshape(-1, *([1] * (x0.dim() - 1))).float()
+    xt = (1.0 - s) * x0.float() + s * eps.float()
+    return xt, eps.float() - x0.float()
+
+
+def fp8_quant_rows(x: torch.Tensor):
+    """Per-row absmax e4m3 quantisation: returns (q float8_e4m3fn, scale fp32 [rows])."""
+    amax = x.float().abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    q = (x.float() / scale[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def fp8_dequant(q: torch.Tensor, row_scale=None, tensor_scale: float = 1.0):
+    y = q.float()
+    y = y * (row_scale.float()[:, None] if row_scale is not None else tensor_scale)
+    return y.to(torch.bfloat16)
+
+
+def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
+    """torch.optim.AdamW order, fp32 math; returns new (p, m, v)."""
+    g = g.float() * grad_scale
+    p = p.float() * (1.0 - lr * wd)
+    m = beta1 * m.float() + (1 - beta1) * g
+    v = beta2 * v.float() + (1 - beta2) * g * g
+    bc1 = 1 - beta1 ** step
+    bc2 = 1 - beta2 ** step
+    p = p - (lr / bc1) * (m / (v.sqrt() / math.sqrt(bc2) + eps))
+    return p, m, v

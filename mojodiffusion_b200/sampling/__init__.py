@@ -1,0 +1,2 @@
+"""Samplers: flow-matching and DDPM-family schedules, multistep solvers, guidance, sampler registry."""
+from .flow_match import *  # noqa: F401,F403

@@ -1,0 +1,196 @@
+"""LoRA injection, key layouts and checkpoint formats.
+
+Five key schemes are written / read (serenitymojo/training/lora_save.mojo:83-380):
+* OneTrainer raw layout (FLUX, Qwen-Image): ``<prefix>.alpha`` (scalar), ``<prefix>.lora_down.weight`` [rank, in],
+  ``<prefix>.lora_up.weight`` [out, rank]
+* PEFT layout (Klein, Z-Image, LTX-2): ``<module>.lora_A.weight`` [rank, in], ``<module>.lora_B.weight`` [out, rank]
+* train-state sidecar ``*.state.safetensors``: the PEFT pair in bf16 plus ``.lora_A.adam_m/.adam_v`` and
+  ``.lora_B.adam_m/.adam_v`` in fp32 per module.
+Prefix tables: FLUX.1 (serenitymojo/models/flux/flux_stack_lora.mojo:1232-1365), Klein
+(serenitymojo/models/klein/klein_stack_lora.mojo:2468-2511), Qwen-Image (serenitymojo/models/qwenimage/qwenimage_stack_lora.mojo:205-234),
+Z-Image (serenitymojo/models/zimage/zimage_stack_lora.mojo:1655-1700), LTX-2 (serenitymojo/training/ltx2/lora_surface.mojo:25-90).
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+
+from ..io.safetensors_io import SafeTensors, save_safetensors
+from ..models.layers import Linear, LoRASlot
+
+FLUX_DOUBLE_IMG = ("attn_to_q", "attn_to_k", "attn_to_v", "attn_to_out_0", "ff_net_0_proj", "ff_net_2")
+FLUX_DOUBLE_TXT = ("attn_add_q_proj", "attn_add_k_proj", "attn_add_v_proj", "attn_to_add_out",
+                   "ff_context_net_0_proj", "ff_context_net_2")
+FLUX_SINGLE = ("attn_to_q", "attn_to_k", "attn_to_v", "proj_mlp", "proj_out")
+
+
+def flux_lora_prefixes(depth_double: int = 19, depth_single: int = 38) -> List[str]:
+    """All FLUX.1 adapter prefixes in checkpoint order: doubles (img 6 then txt 6) then singles (5)."""
+    out = []
+    for i in range(depth_double):
+        out += [f"lora_transformer_transformer_blocks_{i}_{s}" for s in FLUX_DOUBLE_IMG]
+        out += [f"lora_transformer_transformer_blocks_{i}_{s}" for s in FLUX_DOUBLE_TXT]
+    for i in range(depth_single):
+        out += [f"lora_transformer_single_transformer_blocks_{i}_{s}" for s in FLUX_SINGLE]
+    return out
+
+
+def inject_flux_lora(model, rank: int = 16, alpha: float = 16.0, targets: Optional[Sequence[str]] = None,
+                     seed: int = 0) -> List[LoRASlot]:
+    """Attach adapters to every attention / MLP linear of an :class:`MMDiT`. Fused projections get one adapter
+    per logical matrix (to_q / to_k / to_v are row ranges of ``qkv``; single blocks split ``linear1`` into
+    q, k, v, proj_mlp). Base weights are frozen; returns the slots in checkpoint order."""
+    D = model.cfg.hidden
+    F_ = model.cfg.mlp_hidden
+    want = set(targets) if targets is not None else None
+    slots: List[LoRASlot] = []
+
+    def add(lin: Linear, key: str, rows=None):
+        short = key.split("_blocks_", 1)[1].split("_", 1)[1]
+        if want is not None and short not in want:
+            return
+        slots.append(lin.add_lora(key, rank, alpha, rows, seed))
+
+    for p in model.parameters():
+        p.requires_grad_(False)
+    for i, blk in enumerate(model.double_blocks):
+        pre = f"lora_transformer_transformer_blocks_{i}_"
+        add(blk.img_attn.qkv, pre + "attn_to_q", (0, D))
+        add(blk.img_attn.qkv, pre + "attn_to_k", (D, 2 * D))
+        add(blk.img_attn.qkv, pre + "attn_to_v", (2 * D, 3 * D))
+        add(blk.img_attn.proj, pre + "attn_to_out_0")
+        add(blk.img_mlp["0"], pre + "ff_net_0_proj")
+        add(blk.img_mlp["2"], pre + "ff_net_2")
+        add(blk.txt_attn.qkv, pre + "attn_add_q_proj", (0, D))
+        add(blk.txt_attn.qkv, pre + "attn_add_k_proj", (D, 2 * D))
+        add(blk.txt_attn.qkv, pre + "attn_add_v_proj", (2 * D, 3 * D))
+        add(blk.txt_attn.proj, pre + "attn_to_add_out")
+        add(blk.txt_mlp["0"], pre + "ff_context_net_0_proj")
+        add(blk.txt_mlp["2"], pre + "ff_context_net_2")
+    for i, blk in enumerate(model.single_blocks):
+        pre = f"lora_transformer_single_transformer_blocks_{i}_"
+        add(blk.linear1, pre + "attn_to_q", (0, D))
+        add(blk.linear1, pre + "attn_to_k", (D, 2 * D))
+        add(blk.linear1, pre + "attn_to_v", (2 * D, 3 * D))
+        add(blk.linear1, pre + "proj_mlp", (3 * D, 3 * D + F_))
+        add(blk.linear2, pre + "proj_out")
+    for s in slots:
+        s.down.requires_grad_(True)
+        s.up.requires_grad_(True)
+    return slots
+
+
+def inject_lora_by_name(model: nn.Module, name_to_key: Dict[str, str], rank: int, alpha: float) -> List[LoRASlot]:
+    """Generic injection: ``name_to_key`` maps a module path of a :class:`Linear` to its checkpoint prefix."""
+    for p in model.parameters():
+        p.requires_grad_(False)
+    mods = dict(model.named_modules())
+    slots = []
+    for name, key in name_to_key.items():
+        lin = mods[name]
+        assert isinstance(lin, Linear), name
+        slots.append(lin.add_lora(key, rank, alpha))
+    for s in slots:
+        s.down.requires_grad_(True)
+        s.up.requires_grad_(True)
+    return slots
+
+
+def collect_slots(model: nn.Module) -> List[LoRASlot]:
+    return [m for m in model.modules() if isinstance(m, LoRASlot)]
+
+
+def lora_parameters(slots: Iterable[LoRASlot]) -> List[nn.Parameter]:
+    out = []
+    for s in slots:
+        out += [s.down, s.up]
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# checkpoint formats
+# ------------------------------------------------------------------------------------------------
+def lora_state_onetrainer(slots: Sequence[LoRASlot]) -> "OrderedDict[str, torch.Tensor]":
+    sd: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+    for s in slots:
+        sd[f"{s.key}.alpha"] = torch.tensor(s.alpha, dtype=torch.bfloat16)
+        sd[f"{s.key}.lora_down.weight"] = s.down.detach().to(torch.bfloat16).cpu()
+        sd[f"{s.key}.lora_up.weight"] = s.up.detach().to(torch.bfloat16).cpu()
+    return sd
+
+
+def lora_state_peft(slots: Sequence[LoRASlot]) -> "OrderedDict[str, torch.Tensor]":
+    sd: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+    for s in slots:
+        sd[f"{s.key}.lora_A.weight"] = s.down.detach().to(torch.bfloat16).cpu()
+        sd[f"{s.key}.lora_B.weight"] = s.up.detach().to(torch.bfloat16).cpu()
+    return sd
+
+
+def save_lora(path, slots: Sequence[LoRASlot], layout: str = "onetrainer", metadata=None) -> None:
+    sd = lora_state_onetrainer(slots) if layout == "onetrainer" else lora_state_peft(slots)
+    save_safetensors(path, sd, metadata)
+
+
+def save_lora_state_sidecar(path, slots: Sequence[LoRASlot], optimizer, step: int) -> None:
+    """``*.state.safetensors``: adapters (bf16) + Adam moments (fp32) per module, plus the step counter."""
+    sd: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+    for s in slots:
+        sd[f"{s.key}.lora_A.weight"] = s.down.detach().to(torch.bfloat16).cpu()
+        sd[f"{s.key}.lora_B.weight"] = s.up.detach().to(torch.bfloat16).cpu()
+        for tag, p in (("lora_A", s.down), ("lora_B", s.up)):
+            m, v = optimizer.moments(p)
+            sd[f"{s.key}.{tag}.adam_m"] = m.detach().float().cpu()
+            sd[f"{s.key}.{tag}.adam_v"] = v.detach().float().cpu()
+    sd["__meta__"] = torch.tensor([float(step), 0.0], dtype=torch.float32)
+    save_safetensors(path, sd)
+
+
+def load_lora(path, slots: Sequence[LoRASlot], strict: bool = True) -> int:
+    """Load adapters from either key layout (also accepts ``.alpha``). Returns the number of slots restored."""
+    st = SafeTensors(path)
+    n = 0
+    with torch.no_grad():
+        for s in slots:
+            for dn, un in ((f"{s.key}.lora_down.weight", f"{s.key}.lora_up.weight"),
+                           (f"{s.key}.lora_A.weight", f"{s.key}.lora_B.weight")):
+                if dn in st and un in st:
+                    s.down.copy_(st.tensor(dn).to(s.down.dtype))
+                    s.up.copy_(st.tensor(un).to(s.up.dtype))
+                    if f"{s.key}.alpha" in st:
+                        s.alpha = float(st.tensor(f"{s.key}.alpha").float())
+                    n += 1
+                    break
+            else:
+                if strict:
+                    raise KeyError(f"{path}: no adapter for {s.key}")
+    return n
+
+
+def load_lora_state_sidecar(path, slots: Sequence[LoRASlot], optimizer) -> int:
+    """Faithful resume: adapters + moments + bias-correction step. Returns the restored step."""
+    st = SafeTensors(path)
+    with torch.no_grad():
+        for s in slots:
+            s.down.copy_(st.tensor(f"{s.key}.lora_A.weight").to(s.down.dtype))
+            s.up.copy_(st.tensor(f"{s.key}.lora_B.weight").to(s.up.dtype))
+            for tag, p in (("lora_A", s.down), ("lora_B", s.up)):
+                optimizer.set_moments(p, st.tensor(f"{s.key}.{tag}.adam_m"), st.tensor(f"{s.key}.{tag}.adam_v"))
+    step = int(st.tensor("__meta__")[0].item()) if "__meta__" in st else 0
+    optimizer.step_count = step
+    return step
+
+
+@torch.no_grad()
+def merge_lora_into_weights(model: nn.Module, multiplier: float = 1.0) -> None:
+    """Fold every adapter into a resident copy of its host weight and drop the slots (inference-time merge;
+    saved base checkpoints are never touched: serenitymojo/lora.mojo:680-722)."""
+    for m in model.modules():
+        if isinstance(m, Linear) and len(m.slots):
+            for s in m.slots:
+                delta = (s.up.float() @ s.down.float()) * (s.scale * multiplier)
+                m.weight[s.row0:s.row1] += delta.to(m.weight.dtype)
+            m.slots = nn.ModuleList()

@@ -1,0 +1,307 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op (non-degenerate random
+fills, small edge shapes and the real DiT shapes)."""
+import math
+
+import pytest
+import torch
+
+import mojodiffusion_b200.ops as O
+from mojodiffusion_b200.ops import native, reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0, seed=0, dtype=torch.bfloat16):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def _cos(a, b):
+    a, b = a.float().flatten(), b.float().flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-30))
+
+
+def _check(out, want, cos=0.9995, rel=2e-2, name=""):
+    native.check_status(out)
+    assert out.shape == want.shape, (name, out.shape, want.shape)
+    assert torch.isfinite(out.float()).all(), name
+    c = _cos(out, want)
+    err = float((out.float() - want.float()).abs().max())
+    ref_mag = float(want.float().abs().max()) + 1e-6
+    assert c >= cos, f"{name}: cos {c}"
+    assert err <= rel * ref_mag + 1e-3, f"{name}: max err {err} vs magnitude {ref_mag}"
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (200, 264, 72), (1, 64, 64), (4608, 3072, 3072), (512, 9216, 3072),
+               (333, 1000, 520), (4096, 64, 3072)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_plain(M, N, K):
+    x, w = _rand(M, K, seed=1), _rand(N, K, scale=1 / math.sqrt(K), seed=2)
+    out = O.linear(x, w)
+    _check(out, ref.linear(x, w, out_dtype=torch.float32), name=f"gemm {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_tile_variants(bn):
+    M, N, K = 384, 768, 320
+    x, w = _rand(M, K, seed=3), _rand(N, K, scale=1 / math.sqrt(K), seed=4)
+    out = torch.ops.mdb200.gemm([x], [w], None, None, None, 1, 0, 0, 0, None, False, False, False, None, None, 1.0,
+                                False, bn)
+    _check(out, ref.linear(x, w, out_dtype=torch.float32), name=f"bn{bn}")
+
+
+def test_gemm_epilogues():
+    B, S, K, N = 2, 300, 256, 512
+    x = _rand(B * S, K, seed=5)
+    w = _rand(N, K, scale=1 / math.sqrt(K), seed=6)
+    bias, gate, res = _rand(N, seed=7), _rand(B, N, seed=8), _rand(B * S, N, seed=9)
+    for act in ("gelu_tanh", "silu", "gelu", None):
+        out = O.linear(x, w, bias, act=act, residual=res, gate=gate, rows_per_group=S)
+        want = ref.linear(x, w, bias, act, res, gate, S, out_dtype=torch.float32)
+        _check(out, want, name=f"epilogue {act}")
+
+
+def test_gemm_segments_and_lora():
+    M, K1, K2, N, r = 520, 384, 1024, 640, 16
+    a1, a2 = _rand(M, K1, seed=10), _rand(M, K2, seed=11)
+    w = _rand(N, K1 + K2, scale=0.03, seed=12)
+    out = O.linear(a1, w[:, :K1], extra=[(a2, w[:, K1:])])
+    want = ref.linear(torch.cat((a1, a2), 1), w, out_dtype=torch.float32)
+    _check(out, want, name="two K segments")
+    A, Bm = _rand(r, K1, scale=0.05, seed=13), _rand(N, r, scale=0.05, seed=14)
+    out = O.lora_linear(a1, w[:, :K1].contiguous(), None, A, Bm, 0.5)
+    want = a1.float() @ w[:, :K1].float().t() + 0.5 * (a1.float() @ A.float().t()).bfloat16().float() @ Bm.float().t()
+    _check(out, want, name="lora fused", rel=3e-2)
+
+
+def test_gemm_paired_swiglu_geglu():
+    M, K, F_ = 300, 256, 384
+    x = _rand(M, K, seed=15)
+    w = _rand(2 * F_, K, scale=1 / math.sqrt(K), seed=16)
+    b = _rand(2 * F_, seed=17)
+    for act, second in (("silu", False), ("gelu", True)):
+        out = O.linear_glu(x, w, b, act, second)
+        _check(out, ref.linear_glu(x, w, b, act, second, out_dtype=torch.float32), name=f"glu {act}")
+
+
+def test_gemm_backward_majors():
+    M, N, K = 640, 384, 520
+    x = _rand(M, K, seed=18)
+    w = _rand(N, K, scale=0.05, seed=19)
+    dy = _rand(M, N, seed=20)
+    dx = torch.ops.mdb200.gemm([dy], [w], None, None, None, 1, 0, 0, 0, None, False, False, True, None, None, 1.0,
+                               False, 0)
+    _check(dx, dy.float() @ w.float(), name="dx (B MN-major)")
+    dw = torch.ops.mdb200.gemm([dy], [x], None, None, None, 1, 0, 0, 0, None, False, True, True, None, None, 1.0,
+                               False, 0)
+    _check(dw, dy.float().t() @ x.float(), name="dW (A,B MN-major)")
+    for bn in (64, 128, 256):
+        dx = torch.ops.mdb200.gemm([dy], [w], None, None, None, 1, 0, 0, 0, None, False, False, True, None, None, 1.0,
+                                   False, bn)
+        _check(dx, dy.float() @ w.float(), name=f"dx bn{bn}")
+
+
+def test_linear_autograd_matches_torch():
+    M, N, K, r = 256, 320, 192, 8
+    x = _rand(M, K, seed=21).requires_grad_(True)
+    w = _rand(N, K, scale=0.05, seed=22).requires_grad_(True)
+    b = _rand(N, seed=23).requires_grad_(True)
+    y = O.linear(x, w, b, act="gelu_tanh")
+    y.float().square().mean().backward()
+    xr, wr, br = [t.detach().float().requires_grad_(True) for t in (x, w, b)]
+    torch.nn.functional.gelu(xr @ wr.t() + br, approximate="tanh").square().mean().backward()
+    _check(x.grad, xr.grad, cos=0.995, rel=5e-2, name="dx")
+    _check(w.grad, wr.grad, cos=0.995, rel=5e-2, name="dw")
+    _check(b.grad, br.grad, cos=0.995, rel=5e-2, name="db")
+    A = _rand(r, K, scale=0.1, seed=24).requires_grad_(True)
+    Bm = _rand(N, r, scale=0.1, seed=25).requires_grad_(True)
+    x2 = x.detach().clone().requires_grad_(True)
+    y = O.lora_linear(x2, w.detach(), None, A, Bm, 2.0)
+    y.float().square().mean().backward()
+    xr, Ar, Br = [t.detach().float().requires_grad_(True) for t in (x2, A, Bm)]
+    (xr @ w.detach().float().t() + 2.0 * (xr @ Ar.t()) @ Br.t()).square().mean().backward()
+    _check(x2.grad, xr.grad, cos=0.995, rel=5e-2, name="lora dx")
+    _check(A.grad, Ar.grad, cos=0.99, rel=8e-2, name="lora dA")
+    _check(Bm.grad, Br.grad, cos=0.99, rel=8e-2, name="lora dB")
+
+
+def test_gemm_fp8():
+    M, N, K = 300, 512, 1024
+    x = _rand(M, K, seed=26)
+    w = _rand(N, K, scale=0.05, seed=27)
+    wq, ws = O.fp8_quant_rows(w)
+    out = O.fp8_linear(x, wq, ws)
+    xq, xs = ref.fp8_quant_rows(x)
+    want = (xq.float() * xs[:, None]) @ (wq.float() * ws[:, None]).t()
+    _check(out, want, name="fp8 gemm")
+    _check(out, x.float() @ w.float().t(), cos=0.995, rel=0.1, name="fp8 vs bf16 math")
+    _check(O.fp8_dequant(wq, ws), w.float(), cos=0.998, rel=0.08, name="fp8 dequant")
+
+
+ATT_SHAPES = [(1, 256, 256, 2, 128), (2, 300, 300, 3, 128), (1, 128, 77, 4, 64), (1, 1000, 520, 2, 64),
+              (1, 4608, 4608, 4, 128), (2, 640, 256, 2, 128)]
+
+
+@pytest.mark.parametrize("B,Sq,Skv,H,Dh", ATT_SHAPES)
+def test_attention_fwd(B, Sq, Skv, H, Dh):
+    q, k, v = _rand(B, Sq, H, Dh, seed=30), _rand(B, Skv, H, Dh, seed=31), _rand(B, Skv, H, Dh, seed=32)
+    out = O.attention(q, k, v)
+    _check(out, ref.attention(q, k, v).float(), cos=0.999, rel=3e-2, name=f"attn {B},{Sq},{Skv},{H},{Dh}")
+
+
+def test_attention_strided_and_masked():
+    B, S, H, Dh = 2, 520, 3, 128
+    qkv = _rand(B, S, 3 * H * Dh, seed=33)
+    D = H * Dh
+    q, k, v = [qkv[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3)]
+    out = O.attention(q, k, v)
+    _check(out, ref.attention(q, k, v).float(), cos=0.999, rel=3e-2, name="strided qkv")
+    kv_len = torch.tensor([200, 520], dtype=torch.int32, device=DEV)
+    out = O.attention(q, k, v, kv_len=kv_len)
+    _check(out, ref.attention(q, k, v, kv_len=kv_len).float(), cos=0.999, rel=3e-2, name="kv_len mask")
+
+
+def test_attention_lse_and_backward():
+    B, S, H, Dh = 1, 384, 2, 128
+    q, k, v = [_rand(B, S, H, Dh, seed=40 + i).requires_grad_(True) for i in range(3)]
+    o = O.attention(q, k, v)
+    o.float().square().mean().backward()
+    qr, kr, vr = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    ref.attention(qr, kr, vr).square().mean().backward()
+    _check(q.grad, qr.grad, cos=0.99, rel=8e-2, name="dq")
+    _check(k.grad, kr.grad, cos=0.99, rel=8e-2, name="dk")
+    _check(v.grad, vr.grad, cos=0.99, rel=8e-2, name="dv")
+    _, lse = torch.ops.mdb200.attention_fwd(q.detach(), k.detach(), v.detach(), 1 / math.sqrt(Dh), None, True, None)
+    _, lse_ref = ref.attention(q.detach(), k.detach(), v.detach(), return_lse=True)
+    _check(lse, lse_ref, cos=0.9999, rel=1e-2, name="lse")
+
+
+@pytest.mark.parametrize("rows,D", [(7, 64), (300, 256), (4608, 3072), (33, 4096), (5, 12288)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_modulate(rows, D, rms):
+    B = 1 if rows % 3 else 3
+    x = _rand(rows, D, seed=50, scale=2.0) + 0.5
+    w, b = _rand(D, seed=51), _rand(D, seed=52)
+    mod = _rand(B, 2 * D, seed=53, scale=0.3)
+    sc, sh = mod[:, :D], mod[:, D:]
+    rpg = rows // B
+    out = O.norm_modulate(x, w, b, sc, sh, rows_per_group=rpg, eps=1e-6, rms=rms)
+    want = ref.norm_modulate(x.float(), w.float(), b.float(), sc.float(), sh.float(), rpg, 1e-6, rms)
+    _check(out, want, name="norm fwd")
+    xg = x.clone().requires_grad_(True)
+    O.norm_modulate(xg, w, None, sc, sh, rows_per_group=rpg, rms=rms).float().square().mean().backward()
+    xr = x.float().requires_grad_(True)
+    ref.norm_modulate(xr, w.float(), None, sc.float(), sh.float(), rpg, 1e-6, rms).square().mean().backward()
+    _check(xg.grad, xr.grad, cos=0.995, rel=5e-2, name="norm dx")
+
+
+@pytest.mark.parametrize("Dh", [64, 128, 256])
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_qk_norm_rope(Dh, interleaved):
+    B, S, H = 2, 77, 3
+    D = H * Dh
+    qkv = _rand(B, S, 3 * D, seed=60)
+    wq, wk = _rand(Dh, seed=61) + 1.0, _rand(Dh, seed=62) + 1.0
+    pos = torch.stack([torch.zeros(S + 5), torch.arange(S + 5).float() // 9, torch.arange(S + 5).float() % 9], 1).to(DEV)
+    axes = (Dh // 8, 3 * Dh // 8, Dh // 2)
+    cos, sin = O.rope_table(pos, axes, 10000.0)
+    cr, sr = ref.rope_table(pos, axes, 10000.0)
+    _check(cos, cr, cos=0.99999, rel=1e-4, name="rope cos")
+    _check(sin, sr, cos=0.99999, rel=1e-4, name="rope sin")
+    want = ref.qk_norm_rope(qkv[..., :D].reshape(B, S, H, Dh).float(), qkv[..., D:2 * D].reshape(B, S, H, Dh).float(),
+                                         wq.float(), wk.float(), cr[5:], sr[5:], 1e-6, interleaved)
+    got = O.qk_norm_rope(qkv.clone(), H, Dh, wq, wk, cos, sin, interleaved=interleaved, pos_offset=5)
+    _check(got[..., :D].reshape(B, S, H, Dh), want[0], name="q rope")
+    _check(got[..., D:2 * D].reshape(B, S, H, Dh), want[1], name="k rope")
+    assert torch.equal(got[..., 2 * D:], qkv[..., 2 * D:])
+    # backward through norm + rope
+    xg = qkv.clone().requires_grad_(True)
+    O.qk_norm_rope(xg, H, Dh, wq, wk, cos, sin, interleaved=interleaved, pos_offset=5).float().square().mean().backward()
+    xr = qkv.float().requires_grad_(True)
+    q2, k2 = ref.qk_norm_rope(xr[..., :D].reshape(B, S, H, Dh), xr[..., D:2 * D].reshape(B, S, H, Dh), wq.float(),
+                              wk.float(), cr[5:], sr[5:], 1e-6, interleaved)
+    (torch.cat((q2.reshape(B, S, D), k2.reshape(B, S, D), xr[..., 2 * D:]), -1)).square().mean().backward()
+    _check(xg.grad, xr.grad, cos=0.995, rel=5e-2, name="qk_norm_rope dx")
+
+
+def test_pointwise_family():
+    x = _rand(333, 512, seed=70)
+    for act in ("gelu_tanh", "gelu", "silu", "sigmoid", "relu", "tanh"):
+        _check(O.activation(x, act), ref.activation(x.float(), act), name=act)
+        xg = x.clone().requires_grad_(True)
+        O.activation(xg, act).float().sum().backward()
+        xr = x.float().requires_grad_(True)
+        ref.activation(xr, act).sum().backward()
+        _check(xg.grad, xr.grad, cos=0.999, rel=3e-2, name=f"{act} grad")
+    h = _rand(100, 768, seed=71)
+    for act, second in (("silu", False), ("gelu", True)):
+        _check(O.glu(h, act, second), ref.glu(h.float(), act, second), name="glu")
+        hg = h.clone().requires_grad_(True)
+        O.glu(hg, act, second).float().square().sum().backward()
+        hr = h.float().requires_grad_(True)
+        ref.glu(hr, act, second).square().sum().backward()
+        _check(hg.grad, hr.grad, cos=0.999, rel=3e-2, name="glu grad")
+    a, y, g = _rand(2, 50, 256, seed=72), _rand(2, 50, 256, seed=73), _rand(2, 256, seed=74)
+    _check(O.gate_residual(a, y, g), ref.gate_residual(a.float(), y.float(), g.float(), 50), name="gate_residual")
+    _check(O.gate_residual(a, y, g, tanh_gate=True), ref.gate_residual(a.float(), y.float(), g.float(), 50, True),
+           name="tanh gate")
+
+
+def test_sampler_and_flow_kernels():
+    n = (3, 1000, 64)
+    x = _rand(*n, seed=80, dtype=torch.float32)
+    vc, vu = _rand(*n, seed=81), _rand(*n, seed=82)
+    for mode in (0, 1, 2):
+        xx = x.clone()
+        xb = torch.empty_like(xx, dtype=torch.bfloat16)
+        O.cfg_euler(xx, vc, vu, dt=-0.03, s=3.5, mode=mode, x_bf16=xb)
+        want = ref.cfg_euler(x, vc, vu, -0.03, 3.5, mode)
+        _check(xx, want, cos=0.99999, rel=1e-5, name=f"cfg_euler {mode}")
+        _check(xb, want, name="bf16 copy")
+    x0, eps = _rand(4, 500, 64, seed=83, dtype=torch.float32), _rand(4, 500, 64, seed=84, dtype=torch.float32)
+    sig = torch.tensor([0.1, 0.5, 0.9, 1.0], device=DEV)
+    xt, tgt = O.flow_match(x0, eps, sig)
+    xtr, tgtr = ref.flow_match(x0, eps, sig)
+    _check(xt, xtr, name="x_t")
+    _check(tgt, tgtr, cos=0.999999, rel=1e-6, name="target")
+    pred = _rand(4, 500, 64, seed=85)
+    _check(O.mse_loss(pred, tgt).reshape(1), (pred.float() - tgt).pow(2).mean().reshape(1), cos=0.9999, rel=1e-3, name="mse")
+    pg = pred.clone().requires_grad_(True)
+    O.mse_loss(pg, tgt).backward()
+    _check(pg.grad, 2 * (pred.float() - tgt) / pred.numel(), cos=0.999, rel=2e-2, name="mse grad")
+
+
+def test_randn_distribution_and_determinism():
+    a = O.randn((1 << 20,), seed=7, device=DEV)
+    b = O.randn((1 << 20,), seed=7, device=DEV)
+    c = O.randn((1 << 20,), seed=8, device=DEV)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    assert abs(float(a.mean())) < 5e-3 and abs(float(a.std()) - 1.0) < 5e-3
+    assert abs(float((a < 0).float().mean()) - 0.5) < 5e-3
+    assert float(a.abs().max()) < 7.0
+    # prefix property: a longer draw with the same seed starts with the shorter one
+    d = O.randn((1 << 10,), seed=7, device=DEV)
+    assert torch.equal(d, a[: 1 << 10])
+
+
+def test_fused_adamw_matches_torch():
+    from mojodiffusion_b200.training.optim import FusedAdamW
+    shapes = [(16, 3072), (3072, 16), (5,), (1000, 33)]
+    for pdt in (torch.float32, torch.bfloat16):
+        ps = [torch.nn.Parameter(_rand(*s, seed=90 + i, dtype=pdt)) for i, s in enumerate(shapes)]
+        rs = [torch.nn.Parameter(p.detach().float().clone()) for p in ps]
+        opt = FusedAdamW(ps, lr=1e-2, weight_decay=0.01, max_grad_norm=1.0)
+        topt = torch.optim.AdamW(rs, lr=1e-2, weight_decay=0.01, betas=(0.9, 0.999), eps=1e-8)
+        for step in range(3):
+            for i, (p, r) in enumerate(zip(ps, rs)):
+                g = _rand(*p.shape, seed=100 + 10 * step + i, dtype=pdt)
+                p.grad = g.clone()
+                r.grad = g.float().clone()
+            torch.nn.utils.clip_grad_norm_(rs, 1.0)
+            opt.step()
+            topt.step()
+        for p, r in zip(ps, rs):
+            _check(p.detach(), r.detach(), cos=0.9999, rel=2e-2 if pdt == torch.bfloat16 else 1e-4, name=f"adamw {pdt}")
