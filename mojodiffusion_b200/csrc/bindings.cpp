@@ -52,7 +52,7 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
             const optional<Tensor>& residual, const optional<Tensor>& gate, int64_t rows_per_group, int64_t act,
             int64_t pair_offset, int64_t act_on_second, const optional<Tensor>& out_opt, bool out_fp32, bool a_mn,
             bool b_mn, const optional<Tensor>& row_scale, const optional<Tensor>& col_scale, double alpha,
-            bool accumulate, int64_t bn) {
+            bool accumulate, int64_t bn, const optional<Tensor>& prof) {
   TORCH_CHECK(!As.empty() && As.size() == Bs.size() && As.size() <= MDB_GEMM_MAX_SEG, "gemm: 1..3 K segments");
   const Tensor& A0 = As[0];
   TORCH_CHECK(A0.is_cuda(), "gemm: CUDA tensors only");
@@ -137,6 +137,10 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
   g.rows_per_group = static_cast<int>(rows_per_group > 0 ? rows_per_group : 1);
   g.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   g.status = status_ptr(A0);
+  if (prof.has_value() && prof->defined()) {
+    TORCH_CHECK(prof->scalar_type() == at::kLong && prof->numel() >= 8 * g.num_sms, "gemm: prof [sms, 8] int64");
+    g.prof = reinterpret_cast<long long*>(prof->data_ptr());
+  }
   check_rc(mdb_gemm_launch(&g, cur_stream()), "gemm");
   return out;
 }
@@ -178,6 +182,39 @@ std::tuple<Tensor, Tensor> attention_fwd(const Tensor& q, const Tensor& k, const
   a.status = status_ptr(q);
   check_rc(mdb_attention_fwd(&a, cur_stream()), "attention_fwd");
   return {o, need_lse ? lse : Tensor()};
+}
+
+std::tuple<Tensor, Tensor, Tensor> attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                                 const Tensor& lse, const Tensor& dout, double scale,
+                                                 const optional<Tensor>& kv_len) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 4 && q.scalar_type() == at::kBFloat16, "attention_bwd: [B,S,H,Dh] bf16");
+  TORCH_CHECK(q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 && o.stride(3) == 1 && dout.stride(3) == 1,
+              "attention_bwd: head dim must be contiguous");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t B = q.size(0), Sq = q.size(1), H = q.size(2), Dh = q.size(3), Skv = k.size(1);
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == B * H * Sq, "attention_bwd: lse");
+  Tensor dq = at::empty({B, Sq, H, Dh}, q.options());
+  Tensor dk = at::empty({B, Skv, H, Dh}, q.options());
+  Tensor dv = at::empty({B, Skv, H, Dh}, q.options());
+  Tensor delta = at::empty({B, H, Sq}, lse.options());
+  MdbAttnBwdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr(); a.dout = dout.data_ptr();
+  a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+  a.lse = lse.data_ptr<float>();
+  a.delta = delta.data_ptr<float>();
+  if (kv_len.has_value() && kv_len->defined()) a.kv_len = kv_len->data_ptr<int>();
+  a.B = (int)B; a.H = (int)H; a.Sq = (int)Sq; a.Skv = (int)Skv; a.Dh = (int)Dh;
+  for (int i = 0; i < 3; ++i) {
+    a.q_strides[i] = q.stride(i); a.k_strides[i] = k.stride(i); a.v_strides[i] = v.stride(i);
+    a.o_strides[i] = o.stride(i); a.do_strides[i] = dout.stride(i);
+    a.dq_strides[i] = dq.stride(i); a.dk_strides[i] = dk.stride(i); a.dv_strides[i] = dv.stride(i);
+  }
+  a.scale = static_cast<float>(scale);
+  a.status = status_ptr(q);
+  g_launches.fetch_add(2, std::memory_order_relaxed);
+  check_rc(mdb_attention_bwd(&a, cur_stream()), "attention_bwd");
+  return {dq, dk, dv};
 }
 
 // ------------------------------------------------------------------------------------------
@@ -442,6 +479,7 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("launch_count", &launch_count);
   m.def("gemm", &gemm);
   m.def("attention_fwd", &attention_fwd);
+  m.def("attention_bwd", &attention_bwd);
   m.def("norm_modulate_fwd", &norm_modulate_fwd);
   m.def("norm_modulate_bwd", &norm_modulate_bwd);
   m.def("qk_norm_rope", &qk_norm_rope);

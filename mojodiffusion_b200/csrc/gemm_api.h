@@ -41,6 +41,8 @@ typedef struct MdbGemmArgs {
   int ld_out, out_fp32, accumulate_out;
   int num_sms;
   int* status;                     // device int[4], zero on entry; see common.cuh
+  long long* prof;                 // optional device [grid, 8] cycle counters: total, producer wait, mma wait-full,
+                                   // mma wait-accumulator, epilogue wait, epilogue work, tiles
 } MdbGemmArgs;
 
 int mdb_gemm_launch(const MdbGemmArgs* args, cudaStream_t stream);

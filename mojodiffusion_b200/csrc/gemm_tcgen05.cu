@@ -53,15 +53,9 @@ struct GemmParams {
   int out_fp32;
   int accumulate_out;  // out += result (fp32 out only)
   int* status;
+  long long* prof;  // optional [grid, 8] cycle counters (profiling builds of the caller)
 };
 
-template <int ACT>
-__device__ __forceinline__ float apply_act(float x) {
-  if (ACT == MDB_ACT_GELU_TANH) return gelu_tanh_f(x);
-  if (ACT == MDB_ACT_SILU) return silu_f(x);
-  if (ACT == MDB_ACT_GELU_ERF) return gelu_erf_f(x);
-  return x;
-}
 __device__ __forceinline__ float apply_act_rt(int act, float x) {
   switch (act) {
     case MDB_ACT_GELU_TANH: return gelu_tanh_f(x);
@@ -71,80 +65,159 @@ __device__ __forceinline__ float apply_act_rt(int act, float x) {
   }
 }
 
-// One 32-column slab of one output row: v[] holds the raw accumulators (and v2[] the paired half).
-__device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int col0, int pair_cols, float (&v)[32],
-                                               float (&v2)[32], bool paired) {
-  const int N = p.N;
-  if (row >= p.M || col0 >= N) return;
-  const float rs = (p.row_scale ? p.row_scale[row] : 1.f) * p.alpha;
-  const int ncols = min(32, N - col0);
+// 32 consecutive bf16 -> fp32 (64 bytes, 16-byte aligned)
+__device__ __forceinline__ void load32_bf16(const __nv_bfloat16* p, float (&f)[32]) {
+  const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 u = q[i];
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    f[i * 8 + 0] = a.x; f[i * 8 + 1] = a.y; f[i * 8 + 2] = b.x; f[i * 8 + 3] = b.y;
+    f[i * 8 + 4] = c.x; f[i * 8 + 5] = c.y; f[i * 8 + 6] = d.x; f[i * 8 + 7] = d.y;
+  }
+}
+__device__ __forceinline__ void load32_f32(const float* p, float (&f)[32]) {
+  const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 u = q[i];
+    f[i * 4 + 0] = u.x; f[i * 4 + 1] = u.y; f[i * 4 + 2] = u.z; f[i * 4 + 3] = u.w;
+  }
+}
+
+template <int ACT>
+__device__ __forceinline__ void act32(float (&v)[32]) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    if (j < ncols) {
-      const int col = col0 + j;
-      float x = v[j] * rs;
-      if (p.col_scale) x *= p.col_scale[col];
-      if (p.bias) x += __bfloat162float(p.bias[col]);
-      if (paired) {
-        float y = v2[j] * rs;
-        if (p.col_scale) y *= p.col_scale[col + pair_cols];
-        if (p.bias) y += __bfloat162float(p.bias[col + pair_cols]);
-        x = p.act_on_second ? x * apply_act_rt(p.act, y) : apply_act_rt(p.act, x) * y;
-      } else {
-        x = apply_act_rt(p.act, x);
-      }
-      v[j] = x;
+    if (ACT == MDB_ACT_GELU_TANH) v[j] = gelu_tanh_f(v[j]);
+    if (ACT == MDB_ACT_SILU) v[j] = silu_f(v[j]);
+    if (ACT == MDB_ACT_GELU_ERF) v[j] = gelu_erf_f(v[j]);
+  }
+}
+__device__ __forceinline__ void act32_rt(int act, float (&v)[32]) {
+  // the flag is tested once per 32 values; each case is a tight unrolled loop
+  if (act == MDB_ACT_GELU_TANH) act32<MDB_ACT_GELU_TANH>(v);
+  else if (act == MDB_ACT_SILU) act32<MDB_ACT_SILU>(v);
+  else if (act == MDB_ACT_GELU_ERF) act32<MDB_ACT_GELU_ERF>(v);
+}
+
+// Ragged edge (fewer than 32 columns left, or an unaligned pointer): scalar, rarely taken.
+__device__ __noinline__ void epilogue_row32_slow(const GemmParams& p, int row, int col0, int ncols, const uint32_t* r,
+                                                 const uint32_t* r2, bool paired) {
+  const float rs = (p.row_scale ? p.row_scale[row] : 1.f) * p.alpha;
+  for (int j = 0; j < ncols; ++j) {
+    const int col = col0 + j;
+    float x = __uint_as_float(r[j]) * rs;
+    if (p.col_scale) x *= p.col_scale[col];
+    if (p.bias) x += __bfloat162float(p.bias[col]);
+    if (paired) {
+      float y = __uint_as_float(r2[j]) * rs;
+      if (p.col_scale) y *= p.col_scale[col + p.pair_offset];
+      if (p.bias) y += __bfloat162float(p.bias[col + p.pair_offset]);
+      x = p.act_on_second ? x * apply_act_rt(p.act, y) : apply_act_rt(p.act, x) * y;
+    } else {
+      x = apply_act_rt(p.act, x);
+    }
+    if (p.gate) x *= __bfloat162float(p.gate[static_cast<size_t>(row / p.rows_per_group) * p.gate_stride + col]);
+    if (p.residual) x += __bfloat162float(p.residual[static_cast<size_t>(row) * p.ld_res + col]);
+    if (p.out_fp32) {
+      float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col;
+      *o = p.accumulate_out ? *o + x : x;
+    } else {
+      reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(row) * p.ld_out + col] = __float2bfloat16_rn(x);
     }
   }
-  if (p.gate || p.residual) {
-    const __nv_bfloat16* g =
-        p.gate ? p.gate + static_cast<size_t>(row / p.rows_per_group) * p.gate_stride + col0 : nullptr;
-    const __nv_bfloat16* r = p.residual ? p.residual + static_cast<size_t>(row) * p.ld_res + col0 : nullptr;
+}
+
+// One 32-column slab of one output row. r[] holds the raw accumulators (r2[] the paired half).
+__device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
+                                               const uint32_t (&r2)[32], bool paired, bool aligned) {
+  if (row >= p.M || col0 >= p.N) return;
+  const int ncols = min(32, p.N - col0);
+  if (ncols < 32 || !aligned) {
+    // copies live in local memory only on this branch, so the fast path keeps its accumulators in registers
+    uint32_t t0[32], t1[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      if (j < ncols) {
-        float x = v[j];
-        if (g) x *= __bfloat162float(g[j]);
-        if (r) x += __bfloat162float(r[j]);
-        v[j] = x;
-      }
+      t0[j] = r[j];
+      t1[j] = paired ? r2[j] : 0u;
     }
+    epilogue_row32_slow(p, row, col0, ncols, t0, t1, paired);
+    return;
+  }
+  float v[32];
+  const float rs = (p.row_scale ? p.row_scale[row] : 1.f) * p.alpha;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * rs;
+  if (p.col_scale) {
+    float t[32];
+    load32_f32(p.col_scale + col0, t);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= t[j];
+  }
+  if (p.bias) {
+    float t[32];
+    load32_bf16(p.bias + col0, t);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += t[j];
+  }
+  if (paired) {
+    float w[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = __uint_as_float(r2[j]) * rs;
+    if (p.col_scale) {
+      float t[32];
+      load32_f32(p.col_scale + col0 + p.pair_offset, t);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) w[j] *= t[j];
+    }
+    if (p.bias) {
+      float t[32];
+      load32_bf16(p.bias + col0 + p.pair_offset, t);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) w[j] += t[j];
+    }
+    if (p.act_on_second) act32_rt(p.act, w); else act32_rt(p.act, v);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= w[j];
+  } else if (p.act != MDB_ACT_NONE) {
+    act32_rt(p.act, v);
+  }
+  if (p.gate) {
+    float t[32];
+    load32_bf16(p.gate + static_cast<size_t>(row / p.rows_per_group) * p.gate_stride + col0, t);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= t[j];
+  }
+  if (p.residual) {
+    float t[32];
+    load32_bf16(p.residual + static_cast<size_t>(row) * p.ld_res + col0, t);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += t[j];
   }
   if (p.out_fp32) {
-    float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
-    const bool vec = (ncols == 32) && ((reinterpret_cast<uintptr_t>(o) & 15) == 0);
-    if (vec) {
+    float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0);
+    if (p.accumulate_out) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 t = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        if (p.accumulate_out) {
-          float4 old = *reinterpret_cast<float4*>(o + j);
-          t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
-        }
-        *reinterpret_cast<float4*>(o + j) = t;
+      for (int j = 0; j < 8; ++j) {
+        float4 old = o[j];
+        o[j] = make_float4(old.x + v[4 * j], old.y + v[4 * j + 1], old.z + v[4 * j + 2], old.w + v[4 * j + 3]);
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) o[j] = p.accumulate_out ? o[j] + v[j] : v[j];
+      for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
   } else {
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
-    const bool vec = (ncols == 32) && ((reinterpret_cast<uintptr_t>(o) & 15) == 0);
-    if (vec) {
+    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ld_out +
+                                        col0);
 #pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        uint4 t;
-        t.x = pack_bf16x2(v[j], v[j + 1]);
-        t.y = pack_bf16x2(v[j + 2], v[j + 3]);
-        t.z = pack_bf16x2(v[j + 4], v[j + 5]);
-        t.w = pack_bf16x2(v[j + 6], v[j + 7]);
-        *reinterpret_cast<uint4*>(o + j) = t;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) o[j] = __float2bfloat16_rn(v[j]);
+    for (int j = 0; j < 4; ++j) {
+      uint4 t;
+      t.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+      t.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+      t.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+      t.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+      o[j] = t;
     }
   }
 }
@@ -216,17 +289,20 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       int last_stage = -1;
       uint32_t last_phase = 0;
       bool ok = true;
+      long long t_wait = 0;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * BM;
         const int nblk = tile / tiles_m;
         const int n0 = p.pair_offset > 0 ? nblk * (BN / 2) : nblk * BN;
         for (int s = 0; ok && s < p.num_seg; ++s) {
           for (int kb = 0; kb < p.kblocks[s]; ++kb) {
+            const long long tw0 = p.prof ? clock64() : 0;
             if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s)) {
               report_status(p.status, STATUS_TIMEOUT, 1, stage);
               ok = false;
               break;
             }
+            if (p.prof) t_wait += clock64() - tw0;
             uint8_t* sa = smem + stage * STAGE_BYTES;
             uint8_t* sb = sa + A_BYTES;
             mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
@@ -257,6 +333,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           }
         }
       }
+      if (p.prof) p.prof[blockIdx.x * 8 + 1] = t_wait;
       if (!ok && last_stage >= 0) {
         // abandoned: let the copies already in flight land before the CTA goes away (bounded)
         uint64_t t0 = globaltimer_ns();
@@ -275,21 +352,27 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      long long t_full = 0, t_tempty = 0;
+      const long long t_begin = p.prof ? clock64() : 0;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        const long long te0 = p.prof ? clock64() : 0;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, &abort_s)) {
           report_status(p.status, STATUS_TIMEOUT, 2, acc);
           break;
         }
+        if (p.prof) t_tempty += clock64() - te0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < total_kb; ++kb) {
+          const long long tf0 = p.prof ? clock64() : 0;
           if (!mbar_wait(&full_bar[stage], phase, &abort_s)) {
             report_status(p.status, STATUS_TIMEOUT, 3, stage);
             ok = false;
             break;
           }
+          if (p.prof) t_full += clock64() - tf0;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -313,19 +396,34 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         }
         if (ok) umma_commit(&tfull_bar[acc]);
       }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = clock64() - t_begin;
+        p.prof[blockIdx.x * 8 + 2] = t_full;
+        p.prof[blockIdx.x * 8 + 3] = t_tempty;
+        p.prof[blockIdx.x * 8 + 6] = it;
+      }
     }
     __syncwarp();
   } else {
     // ------------------------------- epilogue (4 warps) -------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     const bool paired = p.pair_offset > 0;
+    // the vector epilogue needs 16-byte aligned rows in every tensor it touches (columns advance in 64-byte steps)
+    const int esz = p.out_fp32 ? 4 : 2;
+    bool aligned = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(static_cast<size_t>(p.ld_out) * esz)) & 15) == 0;
+    if (p.bias) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.bias) | static_cast<uintptr_t>(p.pair_offset * 2)) & 15) == 0;
+    if (p.col_scale) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.col_scale) | static_cast<uintptr_t>(p.pair_offset * 4)) & 15) == 0;
+    if (p.gate) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.gate) | static_cast<uintptr_t>(p.gate_stride * 2)) & 15) == 0;
+    if (p.residual) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.residual) | static_cast<uintptr_t>(static_cast<size_t>(p.ld_res) * 2)) & 15) == 0;
     int it = 0;
+    long long t_twait = 0, t_work = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int m0 = (tile % tiles_m) * BM;
       const int nblk = tile / tiles_m;
       const int n0 = paired ? nblk * (BN / 2) : nblk * BN;
+      const long long tq0 = p.prof ? clock64() : 0;
       // warp-uniform decision: the TMEM loads below are warp-collective
       const bool got = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, &abort_s));
       if (!got) {
@@ -333,28 +431,27 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         break;
       }
       tc_fence_after();
+      const long long tq1 = p.prof ? clock64() : 0;
+      t_twait += tq1 - tq0;
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const int out_cols = paired ? BN / 2 : BN;
 #pragma unroll 1
       for (int c = 0; c < out_cols / 32; ++c) {
-        uint32_t r0[32];
-        float v[32], v2[32];
+        uint32_t r0[32], r1[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r0);
+        if (paired) tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, r1);
         tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
-        if (paired) {
-          tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, r0);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v2[j] = __uint_as_float(r0[j]);
-        }
-        epilogue_row32(p, row, n0 + c * 32, p.pair_offset, v, v2, paired);
+        epilogue_row32(p, row, n0 + c * 32, r0, r1, paired, aligned);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (p.prof) t_work += clock64() - tq1;
+    }
+    if (p.prof && warp == 2 && lane == 0) {
+      p.prof[blockIdx.x * 8 + 4] = t_twait;
+      p.prof[blockIdx.x * 8 + 5] = t_work;
     }
   }
 
@@ -500,6 +597,7 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   p.out_fp32 = a->out_fp32;
   p.accumulate_out = a->accumulate_out;
   p.status = a->status;
+  p.prof = a->prof;
 
 #define MDB_LAUNCH(BN_, ST_, AMN_, BMN_, KIND_) return launch_variant<BN_, ST_, AMN_, BMN_, KIND_>(maps, p, sms, stream)
   if (a->kind == 1) {

@@ -93,6 +93,22 @@ typedef struct MdbAttnArgs {
 } MdbAttnArgs;
 int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st);
 
+// ---- attention_bwd_tcgen05.cu
+// delta: fp32 workspace [B, H, Sq] filled by the call (rowsum(dO o O)); lse from the forward.
+typedef struct MdbAttnBwdArgs {
+  const void* q; const void* k; const void* v; const void* o; const void* dout;
+  void* dq; void* dk; void* dv;
+  const float* lse;
+  float* delta;
+  const int* kv_len;
+  int B, H, Sq, Skv, Dh;
+  long long q_strides[3], k_strides[3], v_strides[3], o_strides[3], do_strides[3];
+  long long dq_strides[3], dk_strides[3], dv_strides[3];
+  float scale;
+  int* status;
+} MdbAttnBwdArgs;
+int mdb_attention_bwd(const MdbAttnBwdArgs* a, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

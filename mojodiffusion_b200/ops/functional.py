@@ -36,9 +36,9 @@ def _flat2d(x: torch.Tensor) -> torch.Tensor:
 
 def _gemm(As, Bs, bias=None, residual=None, gate=None, rows_per_group=1, act=0, pair_offset=0, act_on_second=0,
           out=None, out_fp32=False, a_mn=False, b_mn=False, row_scale=None, col_scale=None, alpha=1.0,
-          accumulate=False, bn=0):
+          accumulate=False, bn=0, prof=None):
     return _ops().gemm(list(As), list(Bs), bias, residual, gate, rows_per_group, act, pair_offset, act_on_second, out,
-                       out_fp32, a_mn, b_mn, row_scale, col_scale, alpha, accumulate, bn)
+                       out_fp32, a_mn, b_mn, row_scale, col_scale, alpha, accumulate, bn, prof)
 
 
 # --------------------------------------------------------------------------------------------

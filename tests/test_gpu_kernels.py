@@ -10,6 +10,8 @@ from mojodiffusion_b200.ops import native, reference as ref
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+if torch.cuda.is_available():
+    native.load(True)
 
 
 def _rand(*shape, scale=1.0, seed=0, dtype=torch.bfloat16):
@@ -49,7 +51,7 @@ def test_gemm_tile_variants(bn):
     M, N, K = 384, 768, 320
     x, w = _rand(M, K, seed=3), _rand(N, K, scale=1 / math.sqrt(K), seed=4)
     out = torch.ops.mdb200.gemm([x], [w], None, None, None, 1, 0, 0, 0, None, False, False, False, None, None, 1.0,
-                                False, bn)
+                                False, bn, None)
     _check(out, ref.linear(x, w, out_dtype=torch.float32), name=f"bn{bn}")
 
 
@@ -93,14 +95,14 @@ def test_gemm_backward_majors():
     w = _rand(N, K, scale=0.05, seed=19)
     dy = _rand(M, N, seed=20)
     dx = torch.ops.mdb200.gemm([dy], [w], None, None, None, 1, 0, 0, 0, None, False, False, True, None, None, 1.0,
-                               False, 0)
+                               False, 0, None)
     _check(dx, dy.float() @ w.float(), name="dx (B MN-major)")
     dw = torch.ops.mdb200.gemm([dy], [x], None, None, None, 1, 0, 0, 0, None, False, True, True, None, None, 1.0,
-                               False, 0)
+                               False, 0, None)
     _check(dw, dy.float().t() @ x.float(), name="dW (A,B MN-major)")
     for bn in (64, 128, 256):
         dx = torch.ops.mdb200.gemm([dy], [w], None, None, None, 1, 0, 0, 0, None, False, False, True, None, None, 1.0,
-                                   False, bn)
+                                   False, bn, None)
         _check(dx, dy.float() @ w.float(), name=f"dx bn{bn}")
 
 
