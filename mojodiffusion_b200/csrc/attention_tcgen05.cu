@@ -7,10 +7,11 @@
 //   * S = Q K^T  : tcgen05.mma SS-form, fp32 accumulator in TMEM (128 columns per tile).
 //   * softmax    : one thread per query row (no shuffles), exp2 with the scale folded in, P written back
 //                  into TMEM as packed bf16 over the S columns it came from.
-//   * O_tile = P V: tcgen05.mma TS-form (A = P from TMEM, B = V MN-major from shared memory) into a second
-//                  TMEM region; the softmax warpgroup folds it into its fp32 register accumulator with the
-//                  running-max rescale, so the tensor core never waits for a correction step.
-//   * 512 TMEM columns: S0 S1 O0 O1. Register file rebalanced with setmaxnreg (80 / 208).
+//   * O += P V   : tcgen05.mma TS-form (A = P from TMEM, B = V MN-major from shared memory) accumulating in a
+//                  second TMEM region across all key tiles. The running maximum used for the exponent is only
+//                  raised when a row's true maximum exceeds it by more than 2^8 ("lazy rescale"): then, and
+//                  only then, the warp scales its 32 rows of O in TMEM. P stays below 256, exact in fp32 sums.
+//   * 512 TMEM columns: S0 S1 O0 O1.
 // Keys beyond Skv or beyond kv_len[b] are masked; ragged Sq / Skv tiles are zero filled by TMA.
 //
 // Takes the place of the reference's math-mode SDPA (serenitymojo/ops/attention.mojo:68-520), its scalar
@@ -24,7 +25,12 @@
 
 namespace mdb {
 
-constexpr int ATT_THREADS = 384;
+constexpr int ATT_THREADS = 384;  // warps 0-3: control warpgroup (TMA, UMMA issue, 2 idle); 4-11: two softmax warpgroups
+#ifndef MDB_ATT_CTRL_REGS
+#define MDB_ATT_CTRL_REGS 88
+#define MDB_ATT_SOFTMAX_REGS 208
+#endif
+constexpr int CTRL_REGS = MDB_ATT_CTRL_REGS, SOFTMAX_REGS = MDB_ATT_SOFTMAX_REGS;  // 128*ctrl + 256*softmax <= 384*168
 constexpr int BQ = 128;   // rows per q tile
 constexpr int BKV = 128;  // keys per kv tile
 
@@ -59,7 +65,7 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
-  __shared__ uint64_t s_full[2], p_full[2], o_full[2], o_empty[2];
+  __shared__ uint64_t s_full[2], p_full[2], o_full[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
@@ -89,7 +95,6 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 128);
       mbar_init(&o_full[s], 1);
-      mbar_init(&o_empty[s], 128);
     }
     abort_s = 0;
     fence_mbar_init();
@@ -109,7 +114,7 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < 4) {
-    setmaxnreg_dec<80>();
+    setmaxnreg_dec<CTRL_REGS>();
     if (warp == 0 && lane == 0) {
       // ----------------------------- TMA producer -----------------------------
       mbar_expect_tx(&q_full, 2 * TILE_BYTES);
@@ -165,12 +170,12 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
         }
         umma_commit(&s_full[t]);
       };
-      auto issue_pv = [&](int t, int st) {
+      auto issue_pv = [&](int t, int st, bool first) {
         const uint32_t va = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
           umma_f16_ts(tmem_base + o_cols[t], tmem_base + s_cols[t] + kk * 8,
-                      make_desc_mnmajor_sw128(va + kk * 2048, BOX_BYTES), idesc_pv, kk != 0 ? 1u : 0u);
+                      make_desc_mnmajor_sw128(va + kk * 2048, BOX_BYTES), idesc_pv, (first && kk == 0) ? 0u : 1u);
         }
         umma_commit(&o_full[t]);
       };
@@ -194,13 +199,13 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
           break;
         }
         for (int t = 0; t < 2; ++t) {
-          if (!mbar_wait(&p_full[t], j & 1, &abort_s) || !mbar_wait(&o_empty[t], (j & 1) ^ 1u, &abort_s)) {
+          if (!mbar_wait(&p_full[t], j & 1, &abort_s)) {
             report_status(p.status, STATUS_TIMEOUT, 23 + t, j);
             ok = false;
             break;
           }
           tc_fence_after();
-          issue_pv(t, st);
+          issue_pv(t, st, j == 0);
           if (more) issue_s(t, st_n);
         }
         if (!ok) break;
@@ -211,7 +216,7 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
     __syncwarp();
   } else {
     // ------------------------------- softmax warpgroups ---------------------------
-    setmaxnreg_inc<208>();
+    setmaxnreg_inc<SOFTMAX_REGS>();
     const int t = (warp - 4) >> 2;        // q tile of this warpgroup
     const int quad = warp & 3;            // TMEM lane quadrant
     const int row_in_tile = quad * 32 + lane;
@@ -220,10 +225,7 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
     const uint32_t o_addr = tmem_base + lane_addr + (t ? O_COL1 : O_COL0);
     const float sl2 = p.scale_log2;
 
-    float acc[DH];
-#pragma unroll
-    for (int i = 0; i < DH; ++i) acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
     for (int j = 0; j < n_kv; ++j) {
@@ -235,68 +237,76 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
       tc_fence_after();
       const int kv0 = j * BKV;
       const bool tail = kv0 + BKV > kv_valid;
-      // pass 1: row max
-      float mx = -INFINITY;
+      // the whole S row in registers: four loads in flight, one wait
+      uint32_t s0[32], s1[32], s2[32], s3[32];
+      tmem_ld_32x32b_x32(s_addr + 0, s0);
+      tmem_ld_32x32b_x32(s_addr + 32, s1);
+      tmem_ld_32x32b_x32(s_addr + 64, s2);
+      tmem_ld_32x32b_x32(s_addr + 96, s3);
+      tmem_wait_ld();
+      if (tail) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_wait_ld();
-        if (!tail) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (kv0 + c * 32 + i < kv_valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < 32; ++i) {
+          if (kv0 + i >= kv_valid) s0[i] = 0xff800000u;        // -inf
+          if (kv0 + 32 + i >= kv_valid) s1[i] = 0xff800000u;
+          if (kv0 + 64 + i >= kv_valid) s2[i] = 0xff800000u;
+          if (kv0 + 96 + i >= kv_valid) s3[i] = 0xff800000u;
         }
       }
-      const float m_new = fmaxf(m_run, mx * sl2);
-      const float alpha = exp2f(m_run - m_new);
-      // pass 2: p = exp2(s*scale - m), pack to bf16, write P over the S columns
-      float rowsum = 0.f;
+      float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_wait_ld();
+      for (int i = 0; i < 32; ++i) {
+        mx = fmaxf(mx, fmaxf(fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])),
+                             fmaxf(__uint_as_float(s2[i]), __uint_as_float(s3[i]))));
+      }
+      mx *= sl2;
+      if (j == 0) {
+        m_used = mx;
+      } else {
+        // lazy rescale: raise the exponent reference only when a row outgrew it by more than 2^8
+        const bool need = mx > m_used + 8.0f;
+        if (__any_sync(0xffffffffu, need)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (j - 1) & 1, &abort_s));
+          if (!ok) {
+            if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 33 + t, j);
+            break;
+          }
+          tc_fence_after();
+          const float alpha = need ? exp2f(m_used - mx) : 1.0f;
+          if (need) m_used = mx;
+          l_run *= alpha;
+#pragma unroll
+          for (int c = 0; c < DH / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(o_addr + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(o_addr + c * 32, r);
+          }
+          tmem_wait_st();
+        }
+      }
+      float rowsum = 0.f;
+      auto emit = [&](const uint32_t (&sv)[32], int c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float a = exp2f(fmaf(__uint_as_float(r[i]), sl2, -m_new));
-          float b = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, -m_new));
-          if (tail) {
-            if (kv0 + c * 32 + i >= kv_valid) a = 0.f;
-            if (kv0 + c * 32 + i + 1 >= kv_valid) b = 0.f;
-          }
+          const float a = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -m_used));
+          const float b = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_used));
           rowsum += a + b;
           pk[i >> 1] = pack_bf16x2(a, b);
         }
         tmem_st_32x32b_x16(s_addr + c * 16, pk);
-      }
+      };
+      emit(s0, 0);
+      emit(s1, 1);
+      emit(s2, 2);
+      emit(s3, 3);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
-      l_run = l_run * alpha + rowsum;
-      m_run = m_new;
-      if (j > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (j - 1) & 1, &abort_s));
-        if (!ok) {
-          if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 33 + t, j);
-          break;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < DH / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(o_addr + c * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(r[i])) * alpha;
-        }
-        tc_fence_before();
-        mbar_arrive(&o_empty[t]);
-      }
+      l_run += rowsum;
     }
     if (ok) {
       ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (n_kv - 1) & 1, &abort_s));
@@ -317,21 +327,17 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 w;
-            w.x = pack_bf16x2((acc[c * 32 + i + 0] + __uint_as_float(r[i + 0])) * inv_l,
-                              (acc[c * 32 + i + 1] + __uint_as_float(r[i + 1])) * inv_l);
-            w.y = pack_bf16x2((acc[c * 32 + i + 2] + __uint_as_float(r[i + 2])) * inv_l,
-                              (acc[c * 32 + i + 3] + __uint_as_float(r[i + 3])) * inv_l);
-            w.z = pack_bf16x2((acc[c * 32 + i + 4] + __uint_as_float(r[i + 4])) * inv_l,
-                              (acc[c * 32 + i + 5] + __uint_as_float(r[i + 5])) * inv_l);
-            w.w = pack_bf16x2((acc[c * 32 + i + 6] + __uint_as_float(r[i + 6])) * inv_l,
-                              (acc[c * 32 + i + 7] + __uint_as_float(r[i + 7])) * inv_l);
+            w.x = pack_bf16x2(__uint_as_float(r[i + 0]) * inv_l, __uint_as_float(r[i + 1]) * inv_l);
+            w.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l);
+            w.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l);
+            w.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l);
             *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
           }
         }
       }
       if (p.lse != nullptr && tok < p.Sq)
         p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq + tok] =
-            (m_run + log2f(l_run)) * 0.6931471805599453f;
+            (m_used + log2f(l_run)) * 0.6931471805599453f;
     }
   }
 
