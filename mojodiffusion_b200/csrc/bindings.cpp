@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "comm_api.h"
 #include "gemm_api.h"
 #include "kernels_api.h"
 
@@ -460,6 +461,60 @@ void ema_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, b
 }
 
 // ------------------------------------------------------------------------------------------
+// peer-memory communication (addresses come from symmetric-memory handles: one entry per rank)
+// ------------------------------------------------------------------------------------------
+MdbPeerTable peer_table(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(!ptrs.empty() && ptrs.size() <= MDB_MAX_RANKS, "peer table: 1..8 ranks");
+  MdbPeerTable t;
+  memset(&t, 0, sizeof(t));
+  for (size_t i = 0; i < ptrs.size(); ++i) t.p[i] = reinterpret_cast<void*>(ptrs[i]);
+  return t;
+}
+void flag_signal(std::vector<int64_t> flag_ptrs, int64_t slot, int64_t rank, int64_t value, const Tensor& like) {
+  c10::cuda::CUDAGuard guard(like.device());
+  MdbPeerTable f = peer_table(flag_ptrs);
+  check_rc(mdb_flag_signal(&f, (int)slot, (int)rank, (int)flag_ptrs.size(), (int)value, cur_stream()), "flag_signal");
+}
+void flag_wait(const Tensor& my_flags, int64_t slot, int64_t world, int64_t value) {
+  c10::cuda::CUDAGuard guard(my_flags.device());
+  check_rc(mdb_flag_wait(my_flags.data_ptr<int>(), (int)slot, (int)world, (int)value, status_ptr(my_flags), cur_stream()),
+           "flag_wait");
+}
+void dp_reduce_shard(std::vector<int64_t> grad_ptrs, int64_t grads_mc, const Tensor& my_flags, int64_t ready_slot,
+                     int64_t epoch, int64_t lo, int64_t hi, Tensor red, Tensor sumsq) {
+  c10::cuda::CUDAGuard guard(red.device());
+  MdbPeerTable g = peer_table(grad_ptrs);
+  TORCH_CHECK(red.scalar_type() == at::kFloat && red.numel() >= hi - lo && sumsq.scalar_type() == at::kFloat, "dp_reduce_shard");
+  check_rc(mdb_dp_reduce_shard(&g, reinterpret_cast<const void*>(grads_mc), my_flags.data_ptr<int>(), (int)ready_slot,
+                               (int)epoch, (int)grad_ptrs.size(), lo, hi, red.data_ptr<float>(), sumsq.data_ptr<float>(),
+                               status_ptr(red), cur_stream()),
+           "dp_reduce_shard");
+}
+void publish_scalar(std::vector<int64_t> scalar_ptrs, std::vector<int64_t> flag_ptrs, const Tensor& value, int64_t slot,
+                    int64_t rank, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(value.device());
+  MdbPeerTable sc = peer_table(scalar_ptrs), f = peer_table(flag_ptrs);
+  check_rc(mdb_publish_scalar(&sc, &f, value.data_ptr<float>(), (int)slot, (int)rank, (int)flag_ptrs.size(), (int)epoch,
+                              cur_stream()),
+           "publish_scalar");
+}
+void dp_adamw_shard(std::vector<int64_t> param_ptrs, int64_t params_mc, std::vector<int64_t> flag_ptrs,
+                    const Tensor& my_flags, const Tensor& my_scalars, int64_t norm_slot, int64_t done_slot, int64_t epoch,
+                    int64_t rank, int64_t lo, int64_t hi, const Tensor& red, Tensor m, Tensor v, double lr, double beta1,
+                    double beta2, double eps, double wd, int64_t step, double grad_scale, double max_norm, Tensor norm_out,
+                    Tensor done_counter) {
+  c10::cuda::CUDAGuard guard(red.device());
+  MdbPeerTable p = peer_table(param_ptrs), f = peer_table(flag_ptrs);
+  check_rc(mdb_dp_adamw_shard(&p, reinterpret_cast<void*>(params_mc), &f, my_flags.data_ptr<int>(),
+                              my_scalars.data_ptr<float>(), (int)norm_slot, (int)done_slot, (int)epoch, (int)rank,
+                              (int)param_ptrs.size(), lo, hi, red.data_ptr<float>(), m.data_ptr<float>(),
+                              v.data_ptr<float>(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step,
+                              (float)grad_scale, (float)max_norm, norm_out.data_ptr<float>(), done_counter.data_ptr<int>(),
+                              status_ptr(red), cur_stream()),
+           "dp_adamw_shard");
+}
+
+// ------------------------------------------------------------------------------------------
 // status
 // ------------------------------------------------------------------------------------------
 std::vector<int64_t> read_status(const Tensor& like, bool reset) {
@@ -499,5 +554,10 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("adamw_multi", &adamw_multi);
   m.def("sumsq_multi", &sumsq_multi);
   m.def("ema_multi", &ema_multi);
+  m.def("flag_signal", &flag_signal);
+  m.def("flag_wait", &flag_wait);
+  m.def("dp_reduce_shard", &dp_reduce_shard);
+  m.def("publish_scalar", &publish_scalar);
+  m.def("dp_adamw_shard", &dp_adamw_shard);
   m.def("read_status", &read_status);
 }

@@ -1,0 +1,33 @@
+// C interface of the peer-memory communication kernels (comm_kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MDB_MAX_RANKS 8
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// device-visible addresses of the same symmetric buffer on every rank (index = rank)
+typedef struct MdbPeerTable {
+  void* p[MDB_MAX_RANKS];
+} MdbPeerTable;
+
+// flags buffers: int32 [slots][MDB_MAX_RANKS] per rank, monotonic epochs
+int mdb_flag_signal(const MdbPeerTable* flags, int slot, int rank, int world, int value, cudaStream_t st);
+int mdb_flag_wait(const int* my_flags, int slot, int world, int value, int* status, cudaStream_t st);
+
+int mdb_dp_reduce_shard(const MdbPeerTable* grads, const void* grads_mc, const int* my_flags, int ready_slot, int epoch,
+                        int world, long long lo, long long hi, float* red, float* sumsq, int* status, cudaStream_t st);
+int mdb_publish_scalar(const MdbPeerTable* scalars, const MdbPeerTable* flags, const float* value, int slot, int rank,
+                       int world, int epoch, cudaStream_t st);
+int mdb_dp_adamw_shard(const MdbPeerTable* params, void* params_mc, const MdbPeerTable* flags, const int* my_flags,
+                       const float* my_scalars, int norm_slot, int done_slot, int epoch, int rank, int world,
+                       long long lo, long long hi, const float* red, float* m, float* v, float lr, float beta1,
+                       float beta2, float eps, float wd, int step, float grad_scale, float max_norm, float* norm_out,
+                       int* done_counter, int* status, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif
