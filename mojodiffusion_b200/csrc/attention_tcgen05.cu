@@ -46,6 +46,9 @@ struct AttnParams {
   long long o_strides[3];
   float scale_log2;
   int* status;
+  void* o_route_a[8];
+  void* o_route_b[8];
+  int route_rows_a, route_split, route_rows_b;
 };
 
 template <int REGS> __device__ __forceinline__ void setmaxnreg_inc() {
@@ -316,8 +319,21 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
       tc_fence_after();
       const float inv_l = 1.f / l_run;
       const int tok = q0 + t * BQ + row_in_tile;
-      __nv_bfloat16* orow = p.o + batch * p.o_strides[0] + static_cast<long long>(tok) * p.o_strides[1] +
-                            head * p.o_strides[2];
+      __nv_bfloat16* obase = p.o;
+      long long otok = tok;
+      if (p.route_rows_a > 0 && tok < p.Sq) {
+        if (tok < p.route_split) {
+          const int owner = tok / p.route_rows_a;
+          obase = reinterpret_cast<__nv_bfloat16*>(p.o_route_a[owner]);
+          otok = tok - owner * p.route_rows_a;
+        } else {
+          const int u = tok - p.route_split;
+          const int owner = u / p.route_rows_b;
+          obase = reinterpret_cast<__nv_bfloat16*>(p.o_route_b[owner]);
+          otok = u - owner * p.route_rows_b;
+        }
+      }
+      __nv_bfloat16* orow = obase + batch * p.o_strides[0] + otok * p.o_strides[1] + head * p.o_strides[2];
 #pragma unroll
       for (int c = 0; c < DH / 32; ++c) {
         uint32_t r[32];
@@ -382,7 +398,7 @@ extern "C" int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st) {
     if ((a->q_strides[i] % 8) || (a->k_strides[i] % 8) || (a->v_strides[i] % 8) || (a->o_strides[i] % 8)) return -3;
   }
   if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
-       reinterpret_cast<uintptr_t>(a->o)) & 15)
+       (a->route_rows_a > 0 ? 0 : reinterpret_cast<uintptr_t>(a->o))) & 15)
     return -4;
   AttnMaps maps;
   int r = make_bshd_map(&maps.q, a->q, a->B, a->Sq, a->H, a->Dh, a->q_strides);
@@ -400,6 +416,13 @@ extern "C" int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st) {
   for (int i = 0; i < 3; ++i) p.o_strides[i] = a->o_strides[i];
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.status = a->status;
+  for (int i = 0; i < 8; ++i) {
+    p.o_route_a[i] = a->o_route_a[i];
+    p.o_route_b[i] = a->o_route_b[i];
+  }
+  p.route_rows_a = a->route_rows_a;
+  p.route_split = a->route_rows_a > 0 ? (a->o_route_b[0] ? a->route_split : a->Sq) : 0;
+  p.route_rows_b = a->route_rows_b > 0 ? a->route_rows_b : 1;
   if (a->Dh == 128) return launch_attn<128>(maps, p, st);
   return launch_attn<64>(maps, p, st);
 }

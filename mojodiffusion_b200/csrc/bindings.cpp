@@ -53,7 +53,8 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
             const optional<Tensor>& residual, const optional<Tensor>& gate, int64_t rows_per_group, int64_t act,
             int64_t pair_offset, int64_t act_on_second, const optional<Tensor>& out_opt, bool out_fp32, bool a_mn,
             bool b_mn, const optional<Tensor>& row_scale, const optional<Tensor>& col_scale, double alpha,
-            bool accumulate, int64_t bn, const optional<Tensor>& prof) {
+            bool accumulate, int64_t bn, const optional<Tensor>& prof, std::vector<int64_t> route_ptrs,
+            std::vector<int64_t> route_cfg) {
   TORCH_CHECK(!As.empty() && As.size() == Bs.size() && As.size() <= MDB_GEMM_MAX_SEG, "gemm: 1..3 K segments");
   const Tensor& A0 = As[0];
   TORCH_CHECK(A0.is_cuda(), "gemm: CUDA tensors only");
@@ -92,7 +93,9 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
     g.ldb[s] = B.stride(0);
   }
   Tensor out;
-  if (out_opt.has_value() && out_opt->defined()) {
+  if (!route_ptrs.empty()) {
+    out = at::empty({0}, A0.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  } else if (out_opt.has_value() && out_opt->defined()) {
     out = *out_opt;
     TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "gemm: bad out shape");
     TORCH_CHECK(out.scalar_type() == (out_fp32 ? at::kFloat : at::kBFloat16), "gemm: out dtype");
@@ -101,7 +104,7 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
   }
   TORCH_CHECK(!accumulate || out_fp32, "gemm: accumulate needs an fp32 output");
   g.out = out.data_ptr();
-  g.ld_out = static_cast<int>(out.stride(0));
+  g.ld_out = out.dim() == 2 ? static_cast<int>(out.stride(0)) : 0;
   g.out_fp32 = out_fp32;
   g.accumulate_out = accumulate;
   g.bn = static_cast<int>(bn);
@@ -142,6 +145,19 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
     TORCH_CHECK(prof->scalar_type() == at::kLong && prof->numel() >= 8 * g.num_sms, "gemm: prof [sms, 8] int64");
     g.prof = reinterpret_cast<long long*>(prof->data_ptr());
   }
+  if (!route_ptrs.empty()) {
+    // route_cfg = {owner_cols, part_cols, row_offset, rows_per_batch, batch_rows, ld_out}
+    TORCH_CHECK(route_ptrs.size() <= MDB_GEMM_MAX_PEERS && route_cfg.size() == 6, "gemm: route arguments");
+    for (size_t i = 0; i < route_ptrs.size(); ++i) g.route_out[i] = reinterpret_cast<void*>(route_ptrs[i]);
+    g.route_owner_cols = (int)route_cfg[0];
+    g.route_part_cols = (int)route_cfg[1];
+    g.route_row_offset = (int)route_cfg[2];
+    g.route_rows_per_batch = (int)route_cfg[3];
+    g.route_batch_rows = (int)route_cfg[4];
+    g.ld_out = (int)route_cfg[5];
+    TORCH_CHECK((int64_t)route_ptrs.size() * g.route_owner_cols == g.route_part_cols && N % g.route_part_cols == 0,
+                "gemm: route blocks do not tile the output columns");
+  }
   check_rc(mdb_gemm_launch(&g, cur_stream()), "gemm");
   return out;
 }
@@ -151,7 +167,8 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
 // ------------------------------------------------------------------------------------------
 std::tuple<Tensor, Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale,
                                          const optional<Tensor>& kv_len, bool need_lse,
-                                         const optional<Tensor>& out_opt) {
+                                         const optional<Tensor>& out_opt, std::vector<int64_t> route_a,
+                                         std::vector<int64_t> route_b, std::vector<int64_t> route_cfg) {
   // q: [B, Sq, H, Dh], k/v: [B, Skv, H, Dh] (any strides with contiguous Dh)
   TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "attention: [B,S,H,Dh] tensors");
   TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16,
@@ -162,8 +179,10 @@ std::tuple<Tensor, Tensor> attention_fwd(const Tensor& q, const Tensor& k, const
   TORCH_CHECK(k.size(0) == B && v.size(0) == B && k.size(2) == H && v.size(2) == H && k.size(3) == Dh &&
                   v.size(3) == Dh && v.size(1) == Skv,
               "attention: shape mismatch");
-  Tensor o = (out_opt.has_value() && out_opt->defined()) ? *out_opt : at::empty({B, Sq, H, Dh}, q.options());
-  TORCH_CHECK(o.dim() == 4 && o.stride(3) == 1 && o.size(1) == Sq && o.size(2) == H, "attention: bad out");
+  const bool routed = !route_a.empty();
+  Tensor o = (out_opt.has_value() && out_opt->defined()) ? *out_opt
+             : routed ? at::empty({0}, q.options()) : at::empty({B, Sq, H, Dh}, q.options());
+  TORCH_CHECK(routed || (o.dim() == 4 && o.stride(3) == 1 && o.size(1) == Sq && o.size(2) == H), "attention: bad out");
   Tensor lse;
   if (need_lse) lse = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
   MdbAttnArgs a;
@@ -176,7 +195,21 @@ std::tuple<Tensor, Tensor> attention_fwd(const Tensor& q, const Tensor& k, const
   }
   a.B = (int)B; a.H = (int)H; a.Sq = (int)Sq; a.Skv = (int)Skv; a.Dh = (int)Dh;
   for (int i = 0; i < 3; ++i) {
-    a.q_strides[i] = q.stride(i); a.k_strides[i] = k.stride(i); a.v_strides[i] = v.stride(i); a.o_strides[i] = o.stride(i);
+    a.q_strides[i] = q.stride(i); a.k_strides[i] = k.stride(i); a.v_strides[i] = v.stride(i);
+    a.o_strides[i] = routed ? 0 : o.stride(i);
+  }
+  if (routed) {
+    // route_cfg = {rows_a, split, rows_b, o_stride_batch, o_stride_seq, o_stride_head}
+    TORCH_CHECK(route_a.size() <= 8 && route_cfg.size() == 6 && (route_b.empty() || route_b.size() == route_a.size()),
+                "attention: route arguments");
+    for (size_t i = 0; i < route_a.size(); ++i) {
+      a.o_route_a[i] = reinterpret_cast<void*>(route_a[i]);
+      a.o_route_b[i] = route_b.empty() ? nullptr : reinterpret_cast<void*>(route_b[i]);
+    }
+    a.route_rows_a = (int)route_cfg[0];
+    a.route_split = (int)route_cfg[1];
+    a.route_rows_b = (int)route_cfg[2];
+    a.o_strides[0] = route_cfg[3]; a.o_strides[1] = route_cfg[4]; a.o_strides[2] = route_cfg[5];
   }
   a.scale = static_cast<float>(scale);
   a.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;

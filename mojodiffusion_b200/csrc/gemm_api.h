@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #define MDB_GEMM_MAX_SEG 3
+#define MDB_GEMM_MAX_PEERS 8
 
 enum {
   MDB_ACT_NONE = 0,
@@ -43,6 +44,13 @@ typedef struct MdbGemmArgs {
   int* status;                     // device int[4], zero on entry; see common.cuh
   long long* prof;                 // optional device [grid, 8] cycle counters: total, producer wait, mma wait-full,
                                    // mma wait-accumulator, epilogue wait, epilogue work, tiles
+  // Peer-routed output (route_owner_cols > 0). The N output columns are `parts` of route_part_cols columns; inside
+  // a part, consecutive blocks of route_owner_cols columns belong to ranks 0, 1, ... Block (part, owner) of output
+  // row r is stored into route_out[owner] (that rank's buffer, leading dimension ld_out) at row
+  // (r / route_rows_per_batch) * route_batch_rows + route_row_offset + r % route_rows_per_batch and column
+  // part * route_owner_cols. This is the Ulysses head-scatter done by the projection's own epilogue.
+  void* route_out[MDB_GEMM_MAX_PEERS];
+  int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
 } MdbGemmArgs;
 
 int mdb_gemm_launch(const MdbGemmArgs* args, cudaStream_t stream);

@@ -54,6 +54,9 @@ struct GemmParams {
   int accumulate_out;  // out += result (fp32 out only)
   int* status;
   long long* prof;  // optional [grid, 8] cycle counters (profiling builds of the caller)
+  // peer-routed output (sequence-parallel all-to-all in the epilogue): see MdbGemmArgs
+  void* route_out[MDB_GEMM_MAX_PEERS];
+  int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
 };
 
 __device__ __forceinline__ float apply_act_rt(int act, float x) {
@@ -101,6 +104,21 @@ __device__ __forceinline__ void act32_rt(int act, float (&v)[32]) {
   else if (act == MDB_ACT_GELU_ERF) act32<MDB_ACT_GELU_ERF>(v);
 }
 
+// Where a 32-column slab of output row `row` starting at column `col0` goes. Plain GEMM: the local output.
+// Routed mode: columns are (part, owner, local) blocks; the slab is stored into the owner rank's buffer at
+// row  batch * route_batch_rows + route_row_offset + row_in_batch  and column  part * owner_cols + local.
+__device__ __forceinline__ void* out_slab_ptr(const GemmParams& p, int row, int col0, int esz) {
+  if (p.route_owner_cols <= 0)
+    return reinterpret_cast<char*>(p.out) + (static_cast<size_t>(row) * p.ld_out + col0) * esz;
+  const int part = col0 / p.route_part_cols;
+  const int within = col0 - part * p.route_part_cols;
+  const int owner = within / p.route_owner_cols;
+  const int lcol = part * p.route_owner_cols + (within - owner * p.route_owner_cols);
+  const int b = row / p.route_rows_per_batch;
+  const size_t orow = static_cast<size_t>(b) * p.route_batch_rows + p.route_row_offset + (row - b * p.route_rows_per_batch);
+  return reinterpret_cast<char*>(p.route_out[owner]) + (orow * p.ld_out + lcol) * esz;
+}
+
 // Ragged edge (fewer than 32 columns left, or an unaligned pointer): scalar, rarely taken.
 __device__ __noinline__ void epilogue_row32_slow(const GemmParams& p, int row, int col0, int ncols, const uint32_t* r,
                                                  const uint32_t* r2, bool paired) {
@@ -121,10 +139,10 @@ __device__ __noinline__ void epilogue_row32_slow(const GemmParams& p, int row, i
     if (p.gate) x *= __bfloat162float(p.gate[static_cast<size_t>(row / p.rows_per_group) * p.gate_stride + col]);
     if (p.residual) x += __bfloat162float(p.residual[static_cast<size_t>(row) * p.ld_res + col]);
     if (p.out_fp32) {
-      float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col;
+      float* o = reinterpret_cast<float*>(out_slab_ptr(p, row, col0, 4)) + j;
       *o = p.accumulate_out ? *o + x : x;
     } else {
-      reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(row) * p.ld_out + col] = __float2bfloat16_rn(x);
+      reinterpret_cast<__nv_bfloat16*>(out_slab_ptr(p, row, col0, 2))[j] = __float2bfloat16_rn(x);
     }
   }
 }
@@ -196,7 +214,7 @@ __device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int
     for (int j = 0; j < 32; ++j) v[j] += t[j];
   }
   if (p.out_fp32) {
-    float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0);
+    float4* o = reinterpret_cast<float4*>(out_slab_ptr(p, row, col0, 4));
     if (p.accumulate_out) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -208,8 +226,7 @@ __device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int
       for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
   } else {
-    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ld_out +
-                                        col0);
+    uint4* o = reinterpret_cast<uint4*>(out_slab_ptr(p, row, col0, 2));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       uint4 t;
@@ -598,6 +615,13 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   p.accumulate_out = a->accumulate_out;
   p.status = a->status;
   p.prof = a->prof;
+  for (int i = 0; i < MDB_GEMM_MAX_PEERS; ++i) p.route_out[i] = a->route_out[i];
+  p.route_owner_cols = a->route_owner_cols;
+  p.route_part_cols = a->route_part_cols > 0 ? a->route_part_cols : a->N;
+  p.route_row_offset = a->route_row_offset;
+  p.route_rows_per_batch = a->route_rows_per_batch > 0 ? a->route_rows_per_batch : a->M;
+  p.route_batch_rows = a->route_batch_rows;
+  if (a->route_owner_cols > 0 && ((a->route_owner_cols % 32) || (p.route_part_cols % a->route_owner_cols))) return -5;
 
 #define MDB_LAUNCH(BN_, ST_, AMN_, BMN_, KIND_) return launch_variant<BN_, ST_, AMN_, BMN_, KIND_>(maps, p, sms, stream)
   if (a->kind == 1) {

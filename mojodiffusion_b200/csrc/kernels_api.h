@@ -90,6 +90,14 @@ typedef struct MdbAttnArgs {
   float scale;
   int num_sms;
   int* status;
+  // Peer-routed output (route_rows_a > 0): query row t < route_split belongs to rank t / route_rows_a and is stored
+  // at row t % route_rows_a of o_route_a[rank]; row t >= route_split belongs to rank (t - route_split) / route_rows_b
+  // and goes to o_route_b[rank]. Each table entry already points at this rank's head block inside the owner's
+  // buffer; o_strides then describe the OWNER's buffer. This is the inverse Ulysses all-to-all done by the
+  // attention kernel's own epilogue.
+  void* o_route_a[8];
+  void* o_route_b[8];
+  int route_rows_a, route_split, route_rows_b;
 } MdbAttnArgs;
 int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st);
 

@@ -116,7 +116,7 @@ class DoubleStreamBlock(nn.Module):
         self.txt_attn = SelfAttentionParams(cfg, dtype, device)
         self.txt_mlp = _mlp(cfg, dtype, device)
 
-    def forward(self, img, txt, vec_silu, cos, sin):
+    def forward(self, img, txt, vec_silu, cos, sin, sp=None):
         cfg = self.cfg
         B, S_img, D = img.shape
         S_txt = txt.shape[1]
@@ -130,7 +130,15 @@ class DoubleStreamBlock(nn.Module):
         txt_n = ops.norm_modulate(txt, scale=t_scale1, shift=t_shift1, eps=1e-6)
         wqi, wki = self.img_attn.norm.query_norm.scale, self.img_attn.norm.key_norm.scale
         wqt, wkt = self.txt_attn.norm.query_norm.scale, self.txt_attn.norm.key_norm.scale
-        if _fused_path(img):
+        if sp is not None:
+            # sequence parallel: the projections scatter heads to their owners, attention returns this rank's rows
+            sp.scatter_qkv(txt_n, self.txt_attn.qkv.weight, self.txt_attn.qkv.bias, "txt")
+            sp.scatter_qkv(img_n, self.img_attn.qkv.weight, self.img_attn.qkv.bias, "img")
+            sp.finish_scatter()
+            sp.attention(wqt, wkt, wqi, wki, cos, sin)
+            attn = sp.finish_attention()
+            qkv = None
+        elif _fused_path(img):
             qkv = torch.empty(B, S, 3 * D, dtype=img.dtype, device=img.device)
             for b in range(B):
                 self.txt_attn.qkv(txt_n[b], out=qkv[b, :S_txt])
@@ -141,10 +149,11 @@ class DoubleStreamBlock(nn.Module):
             qt = ops.qk_norm_rope(self.txt_attn.qkv(txt_n), H, Dh, wqt, wkt, cos, sin, pos_offset=0)
             qi = ops.qk_norm_rope(self.img_attn.qkv(img_n), H, Dh, wqi, wki, cos, sin, pos_offset=S_txt)
             qkv = torch.cat((qt, qi), dim=1)
-        q = qkv[..., 0:D].unflatten(-1, (H, Dh))
-        k = qkv[..., D:2 * D].unflatten(-1, (H, Dh))
-        v = qkv[..., 2 * D:3 * D].unflatten(-1, (H, Dh))
-        attn = ops.attention(q, k, v).reshape(B, S, D)
+        if qkv is not None:
+            q = qkv[..., 0:D].unflatten(-1, (H, Dh))
+            k = qkv[..., D:2 * D].unflatten(-1, (H, Dh))
+            v = qkv[..., 2 * D:3 * D].unflatten(-1, (H, Dh))
+            attn = ops.attention(q, k, v).reshape(B, S, D)
         txt_a, img_a = attn[:, :S_txt], attn[:, S_txt:]
         img = self.img_attn.proj(img_a, residual=img, gate=i_gate1, rows_per_group=S_img)
         txt = self.txt_attn.proj(txt_a, residual=txt, gate=t_gate1, rows_per_group=S_txt)
@@ -165,7 +174,7 @@ class SingleStreamBlock(nn.Module):
         self.norm = QKNorm(cfg.head_dim, dtype, device)
         self.modulation = Modulation(D, 3, dtype, device)
 
-    def forward(self, x, vec_silu, cos, sin):
+    def forward(self, x, vec_silu, cos, sin, sp=None):
         cfg = self.cfg
         B, S, D = x.shape
         H, Dh, F_ = cfg.heads, cfg.head_dim, cfg.mlp_hidden
@@ -174,6 +183,17 @@ class SingleStreamBlock(nn.Module):
         xn = ops.norm_modulate(x, scale=scale, shift=shift, eps=1e-6)
         wq, wk = self.norm.query_norm.scale, self.norm.key_norm.scale
         fused = _fused_path(x) and len(self.linear1.slots) == 0 and len(self.linear2.slots) == 0
+        if sp is not None:
+            w1, b1, w2 = self.linear1.weight, self.linear1.bias, self.linear2.weight
+            bq = b1[:3 * D] if b1 is not None else None
+            sp.scatter_qkv(xn[:, :sp.St], w1[:3 * D], bq, "txt")
+            sp.scatter_qkv(xn[:, sp.St:], w1[:3 * D], bq, "img")
+            mlp = ops.linear(xn, w1[3 * D:], b1[3 * D:] if b1 is not None else None, act="gelu_tanh")
+            sp.finish_scatter()
+            sp.attention(wq, wk, wq, wk, cos, sin)
+            attn = sp.finish_attention()
+            return ops.linear(attn, w2[:, :D], self.linear2.bias, residual=x, gate=gate, rows_per_group=S,
+                              extra=[(mlp, w2[:, D:])])
         if fused:
             w1, b1 = self.linear1.weight, self.linear1.bias
             qkv = ops.linear(xn, w1[:3 * D], b1[:3 * D] if b1 is not None else None)
@@ -258,11 +278,14 @@ class MMDiT(nn.Module):
         return vec
 
     def forward(self, img, txt, timesteps, y, guidance=None, ids: Optional[torch.Tensor] = None,
-                hw: Optional[Tuple[int, int]] = None):
+                hw: Optional[Tuple[int, int]] = None, sp=None):
         """img: [B, S_img, in_channels] packed latents, txt: [B, S_txt, context_dim], timesteps/guidance: [B] in
         [0, 1] (scaled by 1000 inside), y: [B, vec_dim]. ``ids`` [S_txt+S_img, 3] or ``hw`` latent grid."""
         cfg = self.cfg
         S_txt, S_img = txt.shape[1], img.shape[1]
+        if sp is not None:
+            # sequence parallel (inference): img / txt are this rank's token shards, ids cover the global sequence
+            assert not torch.is_grad_enabled() and ids is not None and ids.shape[0] == sp.S
         if ids is None:
             if hw is None:
                 side = int(round(S_img ** 0.5))
@@ -279,13 +302,13 @@ class MMDiT(nn.Module):
             if ckpt:
                 img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, vec_silu, cos, sin, use_reentrant=False)
             else:
-                img, txt = blk(img, txt, vec_silu, cos, sin)
+                img, txt = blk(img, txt, vec_silu, cos, sin, sp)
         x = torch.cat((txt, img), dim=1)
         for blk in self.single_blocks:
             if ckpt:
                 x = torch.utils.checkpoint.checkpoint(blk, x, vec_silu, cos, sin, use_reentrant=False)
             else:
-                x = blk(x, vec_silu, cos, sin)
+                x = blk(x, vec_silu, cos, sin, sp)
         x = x[:, S_txt:]
         return self.final_layer(x, vec_silu)
 

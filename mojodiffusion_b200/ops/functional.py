@@ -36,9 +36,10 @@ def _flat2d(x: torch.Tensor) -> torch.Tensor:
 
 def _gemm(As, Bs, bias=None, residual=None, gate=None, rows_per_group=1, act=0, pair_offset=0, act_on_second=0,
           out=None, out_fp32=False, a_mn=False, b_mn=False, row_scale=None, col_scale=None, alpha=1.0,
-          accumulate=False, bn=0, prof=None):
+          accumulate=False, bn=0, prof=None, route_ptrs=(), route_cfg=()):
     return _ops().gemm(list(As), list(Bs), bias, residual, gate, rows_per_group, act, pair_offset, act_on_second, out,
-                       out_fp32, a_mn, b_mn, row_scale, col_scale, alpha, accumulate, bn, prof)
+                       out_fp32, a_mn, b_mn, row_scale, col_scale, alpha, accumulate, bn, prof, list(route_ptrs),
+                       list(route_cfg))
 
 
 # --------------------------------------------------------------------------------------------
@@ -255,7 +256,7 @@ def fp8_linear(x, wq, w_scale, bias=None, act=None, residual=None, gate=None, ro
 class _AttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, scale, kv_len):
-        o, lse = _ops().attention_fwd(q, k, v, scale, kv_len, True, None)
+        o, lse = _ops().attention_fwd(q, k, v, scale, kv_len, True, None, [], [], [])
         ctx.save_for_backward(q, k, v, o, lse, kv_len if kv_len is not None else torch.empty(0))
         ctx.scale = scale
         ctx.has_len = kv_len is not None
@@ -289,7 +290,7 @@ def attention(q, k, v, scale: Optional[float] = None, kv_len: Optional[torch.Ten
             out.copy_(o)
             return out
         return o
-    o, _ = _ops().attention_fwd(q, k, v, scale, kv_len, False, out)
+    o, _ = _ops().attention_fwd(q, k, v, scale, kv_len, False, out, [], [], [])
     return o
 
 
