@@ -34,6 +34,8 @@ def _parse():
     ap.add_argument("--model", default="flux1-dev", choices=["flux1-dev", "tiny"])
     ap.add_argument("--train-steps", type=int, default=-1, help="LoRA train steps to time (-1: min(steps, 4); 0: skip)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the forward eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--sp-mode", default="fused", choices=["fused", "nccl"], help="Ulysses all-to-all: fused peer stores or NCCL baseline")
     return ap.parse_args()
 
 
@@ -124,11 +126,19 @@ def main():
     B = args.batch
     model = MMDiT(cfg, dtype=torch.bfloat16, device=dev).init_weights(0)
     model.eval()
-    pipe = FluxPipeline(model, dev)
-    g = torch.Generator().manual_seed(1234 + rank)
-    x_host = torch.randn(B, S_img, cfg.in_channels, generator=g).pin_memory()
-    txt_host = torch.randn(B, S_txt, cfg.context_dim, generator=g).to(torch.bfloat16).pin_memory()
-    y_host = torch.randn(B, cfg.vec_dim, generator=g).to(torch.bfloat16).pin_memory()
+    sp = None
+    if world > 1:
+        from mojodiffusion_b200.parallel.ulysses import UlyssesContext
+        sp = UlyssesContext(B, S_txt, S_img, cfg.heads, cfg.head_dim, mode=args.sp_mode, device=dev)
+    pipe = FluxPipeline(model, dev, sp=sp, use_cuda_graph=not args.no_graph)
+    g = torch.Generator().manual_seed(1234)          # same stream on every rank: shards of one global sample
+    x_full = torch.randn(B, S_img, cfg.in_channels, generator=g)
+    txt_full = torch.randn(B, S_txt, cfg.context_dim, generator=g).to(torch.bfloat16)
+    y_full = torch.randn(B, cfg.vec_dim, generator=g).to(torch.bfloat16)
+    Sl_img, Sl_txt = S_img // world, S_txt // world
+    x_host = x_full[:, rank * Sl_img:(rank + 1) * Sl_img].contiguous().pin_memory()
+    txt_host = txt_full[:, rank * Sl_txt:(rank + 1) * Sl_txt].contiguous().pin_memory()
+    y_host = y_full.pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
     sigmas = fm.flux1_sigmas(28, S_img)
     K, W = args.steps, max(args.warmup, 0)
@@ -140,16 +150,17 @@ def main():
     xb = x.to(torch.bfloat16)
     ids = MMDiT.make_ids(hw[0], hw[1], S_txt, dev)
     gvec = torch.full((B,), 3.5, device=dev)
+    tvec = torch.empty((B,), device=dev)
     from mojodiffusion_b200 import ops
 
     def denoise_step(i):
         s, s_next = sigmas[i % 28], sigmas[i % 28 + 1]
-        t = torch.full((B,), float(s), device=dev)
+        tvec.fill_(float(s))
         with torch.no_grad():
-            v = model(xb, txt, t, y, gvec, ids=ids)
+            v = pipe._forward(xb, txt, tvec, y, gvec, ids)
             ops.cfg_euler(x, v, None, dt=float(s_next - s), mode=0, x_bf16=xb)
 
-    for i in range(W):
+    for i in range(max(W, 1)):
         denoise_step(i)
     torch.cuda.synchronize()
     pdist.barrier()
@@ -170,13 +181,23 @@ def main():
     ms = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
     native.check_status()
     assert torch.isfinite(x).all(), "latents diverged"
-    it_per_s = world * B * 1000.0 / ms  # every rank denoises its own batch (data-parallel replicas)
+    it_per_s = B * 1000.0 / ms  # N > 1: the ranks share ONE batch (Ulysses sequence parallel, strong scaling)
+    launches_per_step = None
+    if not args.no_graph:
+        # kernels inside the replayed graph are not re-counted by the host-side counter: count one eager step
+        pipe_eager = FluxPipeline(model, dev, sp=sp, use_cuda_graph=False)
+        nb = launches()
+        with torch.no_grad():
+            pipe_eager._forward(xb, txt, tvec, y, gvec, ids)
+        torch.cuda.synchronize()
+        pdist.barrier()
+        launches_per_step = launches() - nb + 1
+        n_launch = launches_per_step * K
 
     # ------------------------------------------------------------------ end-to-end through the public API
     e2e = None
     if not args.no_e2e:
-        x_host.copy_(torch.randn(B, S_img, cfg.in_channels, generator=g))
-        for i in range(min(W, 2)):
+        for i in range(min(max(W, 1), 2)):
             pipe.step_from_host(x_host, txt_host, y_host, sigmas[i], sigmas[i + 1], 3.5, out_host, hw)
         torch.cuda.synchronize()
         pdist.barrier()
@@ -190,8 +211,8 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         ms_e2e = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
-        e2e = {"value": world * B * 1000.0 / ms_e2e, "unit": "it/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo}
+        e2e = {"value": B * 1000.0 / ms_e2e, "unit": "it/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": bi * world, "d2h_bytes_per_step": bo * world}
 
     # ------------------------------------------------------------------ LoRA training samples/s
     train = None
@@ -201,16 +222,22 @@ def main():
         from mojodiffusion_b200.training import lora as L
         from mojodiffusion_b200.training.optim import FusedAdamW
         from mojodiffusion_b200.training.trainer import FlowMatchTrainer
-        del xb
+        del pipe
         torch.cuda.empty_cache()
         slots = L.inject_flux_lora(model, rank=16, alpha=16.0)
         params = L.lora_parameters(slots)
         model.gradient_checkpointing = True
         model.train()
-        opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
-        dp = DataParallelGrads(params) if world > 1 else None
-        tr = FlowMatchTrainer(model, params, opt, dp)
-        x0 = torch.randn(B, S_img, cfg.in_channels, generator=g).to(dev)
+        if world > 1:
+            from mojodiffusion_b200.parallel.fused_dp import FusedDPAdamW
+            opt = FusedDPAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
+        else:
+            opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
+        tr = FlowMatchTrainer(model, params, opt, None)
+        gt = torch.Generator().manual_seed(99 + rank)   # data parallel: every rank trains on its own samples
+        x0 = torch.randn(B, S_img, cfg.in_channels, generator=gt).to(dev)
+        txt = torch.randn(B, S_txt, cfg.context_dim, generator=gt).to(dev, torch.bfloat16)
+        y = torch.randn(B, cfg.vec_dim, generator=gt).to(dev, torch.bfloat16)
         for i in range(3):
             tr.step(x0, txt, y, hw=hw)
         torch.cuda.synchronize()
@@ -227,18 +254,22 @@ def main():
         train = {"metric": "lora_train_samples_per_s", "value": world * B * 1000.0 / ms_t, "unit": "samples/s",
                  "ms_per_step": ms_t, "steps": tsteps, "warmup": 3, "loss": float(loss), "rank": 16,
                  "gpu_launches": launches() - t0n, "gradient_checkpointing": True,
-                 "parallelism": f"dp{world}" if world > 1 else "single"}
+                 "parallelism": (f"dp{world}, grad reduce-scatter + clip + AdamW + param all-gather fused in peer-memory "
+                                 f"kernels (multicast {'on' if getattr(opt, 'symm', None) is not None and opt.symm.mc_ptr else 'off'})")
+                 if world > 1 else "single"}
 
     if rank == 0:
         line = {
             "metric": "flux1-dev-shape 1024^2 denoise it/s (+ LoRA r16 train samples/s in 'lora_train')",
             "value": it_per_s, "unit": "it/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {"model": f"{cfg.name} 12B MMDiT (19 double + 38 single, D=3072, 24x128)" if args.model == "flux1-dev" else cfg.name,
-                       "global_batch": world * B, "seq_len": S_img + S_txt, "image_tokens": S_img, "text_tokens": S_txt,
+                       "global_batch": B, "seq_len": S_img + S_txt, "image_tokens": S_img, "text_tokens": S_txt,
                        "sampler": "euler flow-match, 28-step BFL-shifted schedule, guidance 3.5 (distilled)",
-                       "parallelism": f"dp{world}" if world > 1 else "single", "weights": "random-init seed 0",
+                       "parallelism": (f"sp{world} (Ulysses; all-to-all {args.sp_mode})" if world > 1 else "single"),
+                       "cuda_graph": not args.no_graph, "launches_per_step": launches_per_step,
+                       "weights": "random-init seed 0",
                        "l2": "inputs larger than L2: 24 GB of weights stream every step"},
             "clocks": clocks, "gpu_launches": n_launch, "e2e": e2e, "lora_train": train,
             "published_nearest": PUBLISHED_NEAREST,

@@ -503,14 +503,18 @@ MdbPeerTable peer_table(const std::vector<int64_t>& ptrs) {
   for (size_t i = 0; i < ptrs.size(); ++i) t.p[i] = reinterpret_cast<void*>(ptrs[i]);
   return t;
 }
-void flag_signal(std::vector<int64_t> flag_ptrs, int64_t slot, int64_t rank, int64_t value, const Tensor& like) {
+void flag_signal(std::vector<int64_t> flag_ptrs, int64_t slot, int64_t rank, int64_t value, const Tensor& like,
+                 const optional<Tensor>& counters) {
   c10::cuda::CUDAGuard guard(like.device());
   MdbPeerTable f = peer_table(flag_ptrs);
-  check_rc(mdb_flag_signal(&f, (int)slot, (int)rank, (int)flag_ptrs.size(), (int)value, cur_stream()), "flag_signal");
+  int* c = counters.has_value() && counters->defined() ? counters->data_ptr<int>() : nullptr;
+  check_rc(mdb_flag_signal(&f, (int)slot, (int)rank, (int)flag_ptrs.size(), (int)value, c, cur_stream()), "flag_signal");
 }
-void flag_wait(const Tensor& my_flags, int64_t slot, int64_t world, int64_t value) {
+void flag_wait(const Tensor& my_flags, int64_t slot, int64_t world, int64_t value, const optional<Tensor>& counters) {
   c10::cuda::CUDAGuard guard(my_flags.device());
-  check_rc(mdb_flag_wait(my_flags.data_ptr<int>(), (int)slot, (int)world, (int)value, status_ptr(my_flags), cur_stream()),
+  int* c = counters.has_value() && counters->defined() ? counters->data_ptr<int>() : nullptr;
+  check_rc(mdb_flag_wait(my_flags.data_ptr<int>(), (int)slot, (int)world, (int)value, c, status_ptr(my_flags),
+                         cur_stream()),
            "flag_wait");
 }
 void dp_reduce_shard(std::vector<int64_t> grad_ptrs, int64_t grads_mc, const Tensor& my_flags, int64_t ready_slot,

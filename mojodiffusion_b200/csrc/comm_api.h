@@ -4,6 +4,7 @@
 #include <stdint.h>
 
 #define MDB_MAX_RANKS 8
+#define MDB_FLAG_SLOTS 8
 
 #ifdef __cplusplus
 extern "C" {
@@ -15,8 +16,10 @@ typedef struct MdbPeerTable {
 } MdbPeerTable;
 
 // flags buffers: int32 [slots][MDB_MAX_RANKS] per rank, monotonic epochs
-int mdb_flag_signal(const MdbPeerTable* flags, int slot, int rank, int world, int value, cudaStream_t st);
-int mdb_flag_wait(const int* my_flags, int slot, int world, int value, int* status, cudaStream_t st);
+// value > 0: explicit epoch. value == 0: epoch from device counters (int[2 * MDB_FLAG_SLOTS], local, zero-initialised)
+int mdb_flag_signal(const MdbPeerTable* flags, int slot, int rank, int world, int value, int* counters,
+                    cudaStream_t st);
+int mdb_flag_wait(const int* my_flags, int slot, int world, int value, int* counters, int* status, cudaStream_t st);
 
 int mdb_dp_reduce_shard(const MdbPeerTable* grads, const void* grads_mc, const int* my_flags, int ready_slot, int epoch,
                         int world, long long lo, long long hi, float* red, float* sumsq, int* status, cudaStream_t st);

@@ -56,11 +56,20 @@ __device__ __forceinline__ bool wait_all(const int* my_flags, int slot, int worl
   return true;
 }
 
-__global__ void flag_signal_kernel(MdbPeerTable flags, int slot, int rank, int world, int value) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) signal_all(flags, slot, rank, world, value);
+// value > 0: publish / wait for that epoch. value == 0: the epoch is a device-side counter that the kernel itself
+// advances (counters[slot] for signals, counters[slots + slot] for waits), so a captured CUDA graph that replays the
+// same signal / wait sequence keeps producing fresh epochs without any host-side argument changing.
+__global__ void flag_signal_kernel(MdbPeerTable flags, int slot, int rank, int world, int value, int* counters) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    if (value <= 0) value = ++counters[slot];
+    signal_all(flags, slot, rank, world, value);
+  }
 }
-__global__ void flag_wait_kernel(const int* my_flags, int slot, int world, int value, int* status) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) wait_all(my_flags, slot, world, value, status, 100 + slot);
+__global__ void flag_wait_kernel(const int* my_flags, int slot, int world, int value, int* counters, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    if (value <= 0) value = ++counters[MDB_FLAG_SLOTS + slot];
+    wait_all(my_flags, slot, world, value, status, 100 + slot);
+  }
 }
 
 // block-wide: thread 0 waits, everyone learns the outcome
@@ -230,12 +239,16 @@ static inline int clamp_grid(long long n, int threads) {
 
 using namespace mdb;
 
-extern "C" int mdb_flag_signal(const MdbPeerTable* flags, int slot, int rank, int world, int value, cudaStream_t st) {
-  flag_signal_kernel<<<1, 32, 0, st>>>(*flags, slot, rank, world, value);
+extern "C" int mdb_flag_signal(const MdbPeerTable* flags, int slot, int rank, int world, int value, int* counters,
+                               cudaStream_t st) {
+  if (slot < 0 || slot >= MDB_FLAG_SLOTS || (value <= 0 && counters == nullptr)) return -1;
+  flag_signal_kernel<<<1, 32, 0, st>>>(*flags, slot, rank, world, value, counters);
   return (int)cudaGetLastError();
 }
-extern "C" int mdb_flag_wait(const int* my_flags, int slot, int world, int value, int* status, cudaStream_t st) {
-  flag_wait_kernel<<<1, 32, 0, st>>>(my_flags, slot, world, value, status);
+extern "C" int mdb_flag_wait(const int* my_flags, int slot, int world, int value, int* counters, int* status,
+                             cudaStream_t st) {
+  if (slot < 0 || slot >= MDB_FLAG_SLOTS || (value <= 0 && counters == nullptr)) return -1;
+  flag_wait_kernel<<<1, 32, 0, st>>>(my_flags, slot, world, value, counters, status);
   return (int)cudaGetLastError();
 }
 extern "C" int mdb_dp_reduce_shard(const MdbPeerTable* grads, const void* grads_mc, const int* my_flags, int ready_slot,

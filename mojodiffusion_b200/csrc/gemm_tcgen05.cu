@@ -555,10 +555,16 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   const int sms = a->num_sms > 0 ? a->num_sms : 148;
   int bn = a->bn;
   if (bn != 64 && bn != 128 && bn != 256) {
-    // default tile choice: widest tile that still gives every SM work
+    // default tile choice: 128x256 unless the narrower 128x128 tile fills the machine noticeably better
+    // (fewer idle SMs in the last wave); 128x64 only for very skinny outputs
     const int tm = (a->M + BM - 1) / BM;
+    auto wave_eff = [&](int w) {
+      const long long tiles = static_cast<long long>(tm) * ((a->N + w - 1) / w);
+      const long long waves = (tiles + sms - 1) / sms;
+      return static_cast<double>(tiles) / static_cast<double>(waves * sms);
+    };
     bn = 256;
-    if (!paired && tm * ((a->N + 255) / 256) < sms && a->N <= 4096) bn = 128;
+    if (!paired && wave_eff(128) > 1.12 * wave_eff(256)) bn = 128;
     if (!paired && a->N <= 64) bn = 64;
   }
   if (paired && bn != 256) bn = 256;

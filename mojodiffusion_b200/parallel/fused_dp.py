@@ -89,7 +89,7 @@ class FusedDPAdamW:
         o = native.ops()
         self.sumsq.zero_()
         self.done_counter.zero_()
-        o.flag_signal(self.symm.ptrs_at(self.off_flags), SLOT_READY, self.rank, self.epoch, self.flags)
+        o.flag_signal(self.symm.ptrs_at(self.off_flags), SLOT_READY, self.rank, self.epoch, self.flags, None)
 
     def phase_reduce(self):
         native.ops().dp_reduce_shard(self.symm.ptrs_at(self.off_grads), self.symm.mc_at(self.off_grads), self.flags,
@@ -108,7 +108,7 @@ class FusedDPAdamW:
                                     1.0 / self.world, self.max_norm, self.norm_out, self.done_counter)
 
     def phase_finish(self):
-        native.ops().flag_wait(self.flags, SLOT_DONE, self.world, self.epoch)
+        native.ops().flag_wait(self.flags, SLOT_DONE, self.world, self.epoch, None)
 
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0, lr: Optional[float] = None):

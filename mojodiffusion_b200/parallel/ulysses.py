@@ -62,6 +62,8 @@ class UlyssesContext:
             self.symm = symm if symm is not None else SymmetricBuffer.create(total, group, self.device, False)
             assert self.symm.local.numel() >= total
             self.flags = self.symm.view(0, 64, torch.int32)
+            # device-side epoch counters (signals | waits): the flag sequence survives CUDA-graph replay
+            self.counters = torch.zeros(16, dtype=torch.int32, device=self.device)
             self.qkv_g = self.symm.view(self.off_qkv, B * self.S * 3 * self.Dl, dtype).view(B, self.S, 3 * self.Dl)
             self.attn_x = self.symm.view(self.off_att, B * self.Sl * self.D, dtype).view(B, self.Sl, self.D)
         else:
@@ -91,8 +93,7 @@ class UlyssesContext:
     def finish_scatter(self) -> None:
         """Publish "my projections have landed everywhere" (fused) / run the all-to-all (nccl)."""
         if self.mode == "fused":
-            self.epoch += 1
-            native.ops().flag_signal(self.symm.ptrs_at(0), SLOT_QKV, self.rank, self.epoch, self.flags)
+            native.ops().flag_signal(self.symm.ptrs_at(0), SLOT_QKV, self.rank, 0, self.flags, self.counters)
             return
         N = self.world
         for part, Sp, base in (("txt", self.St, 0), ("img", self.Si, self.S_txt)):
@@ -110,7 +111,7 @@ class UlyssesContext:
     def attention(self, wq_txt, wk_txt, wq_img, wk_img, cos, sin, interleaved: bool = True) -> None:
         Hl, Dh, Dl = self.Hl, self.Dh, self.Dl
         if self.mode == "fused":
-            native.ops().flag_wait(self.flags, SLOT_QKV, self.world, self.epoch)
+            native.ops().flag_wait(self.flags, SLOT_QKV, self.world, 0, self.counters)
         g = self.qkv_g
         ops.qk_norm_rope(g[:, :self.S_txt], Hl, Dh, wq_txt, wk_txt, cos, sin, interleaved=interleaved, pos_offset=0)
         ops.qk_norm_rope(g[:, self.S_txt:], Hl, Dh, wq_img, wk_img, cos, sin, interleaved=interleaved,
@@ -126,7 +127,7 @@ class UlyssesContext:
             rb = [p + self.St * self.D * 2 + col for p in base]
             native.ops().attention_fwd(q, k, v, scale, None, False, None, ra, rb,
                                        [self.St, self.S_txt, self.Si, self.Sl * self.D, self.D, Dh])
-            native.ops().flag_signal(self.symm.ptrs_at(0), SLOT_ATTN, self.rank, self.epoch, self.flags)
+            native.ops().flag_signal(self.symm.ptrs_at(0), SLOT_ATTN, self.rank, 0, self.flags, self.counters)
         else:
             o = ops.attention(q, k, v, scale).reshape(self.B, self.S, Dl)
             N = self.world
@@ -142,7 +143,7 @@ class UlyssesContext:
     def finish_attention(self) -> torch.Tensor:
         """Wait until every rank's heads have landed; returns this rank's [B, S_txt/N + S_img/N, D] attention rows."""
         if self.mode == "fused":
-            native.ops().flag_wait(self.flags, SLOT_ATTN, self.world, self.epoch)
+            native.ops().flag_wait(self.flags, SLOT_ATTN, self.world, 0, self.counters)
         return self.attn_x
 
     # ---- helpers ------------------------------------------------------------------------------------------------
