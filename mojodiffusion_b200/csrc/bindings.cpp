@@ -162,6 +162,70 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
   return out;
 }
 
+// x: NHWC bf16 [N, H, W, Cin]; w: [Cout, KH, KW, Cin] bf16; stride 1, "same"-style padding (pad_h, pad_w).
+Tensor conv2d_nhwc(const Tensor& x, const Tensor& w, const optional<Tensor>& bias, int64_t pad_h, int64_t pad_w,
+                   int64_t act, const optional<Tensor>& residual) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && w.dim() == 4 && x.is_contiguous() && w.is_contiguous(), "conv2d_nhwc: NHWC");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "conv2d_nhwc: bf16");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t N = x.size(0), H = x.size(1), W = x.size(2), Cin = x.size(3);
+  const int64_t Cout = w.size(0), KH = w.size(1), KW = w.size(2);
+  TORCH_CHECK(w.size(3) == Cin && Cin % 64 == 0 && Cout % 8 == 0, "conv2d_nhwc: Cin multiple of 64, Cout multiple of 8");
+  TORCH_CHECK(2 * pad_h == KH - 1 && 2 * pad_w == KW - 1, "conv2d_nhwc: output size must equal input size");
+  Tensor out = at::empty({N, H, W, Cout}, x.options());
+  MdbGemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.M = (int)(N * H * W); g.N = (int)Cout; g.num_seg = 1;
+  g.K[0] = KH * KW * Cin;
+  g.A[0] = x.data_ptr(); g.B[0] = w.data_ptr();
+  g.lda[0] = Cin; g.ldb[0] = KH * KW * Cin;
+  g.alpha = 1.f; g.act = (int)act;
+  g.out = out.data_ptr(); g.ld_out = (int)Cout;
+  g.rows_per_group = 1;
+  if (bias.has_value() && bias->defined()) g.bias = bias->data_ptr();
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->is_contiguous() && residual->numel() == out.numel(), "conv2d_nhwc: residual shape");
+    g.residual = residual->data_ptr();
+    g.ld_res = (int)Cout;
+  }
+  g.conv_taps = (int)(KH * KW); g.conv_kw = (int)KW; g.conv_pad_h = (int)pad_h; g.conv_pad_w = (int)pad_w;
+  g.conv_n = (int)N; g.conv_h = (int)H; g.conv_w = (int)W; g.conv_cin = (int)Cin;
+  g.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  g.status = status_ptr(x);
+  check_rc(mdb_gemm_launch(&g, cur_stream()), "conv2d_nhwc");
+  return out;
+}
+
+Tensor group_norm_nhwc(const Tensor& x, const optional<Tensor>& w, const optional<Tensor>& b, int64_t groups, double eps,
+                       int64_t act) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "group_norm_nhwc");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  Tensor stats = at::empty({x.size(0) * groups, 2}, x.options().dtype(at::kFloat));
+  check_rc(mdb_group_norm(x.data_ptr(), y.data_ptr(), stats.data_ptr<float>(), opt_ptr(w), opt_ptr(b), (int)x.size(0),
+                          (int)(x.size(1) * x.size(2)), (int)x.size(3), (int)groups, (float)eps, (int)act, cur_stream()),
+           "group_norm");
+  return y;
+}
+Tensor upsample2x_nhwc(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "upsample2x_nhwc");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty({x.size(0), x.size(1) * 2, x.size(2) * 2, x.size(3)}, x.options());
+  check_rc(mdb_upsample2x(x.data_ptr(), y.data_ptr(), (int)x.size(0), (int)x.size(1), (int)x.size(2), (int)x.size(3),
+                          cur_stream()),
+           "upsample2x");
+  return y;
+}
+Tensor avgpool2x_nhwc(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "avgpool2x_nhwc");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty({x.size(0), x.size(1) / 2, x.size(2) / 2, x.size(3)}, x.options());
+  check_rc(mdb_avgpool2x(x.data_ptr(), y.data_ptr(), (int)x.size(0), (int)x.size(1), (int)x.size(2), (int)x.size(3),
+                         cur_stream()),
+           "avgpool2x");
+  return y;
+}
+
 // ------------------------------------------------------------------------------------------
 // attention
 // ------------------------------------------------------------------------------------------
@@ -570,6 +634,10 @@ int64_t launch_count() { return g_launches.load(); }
 TORCH_LIBRARY(mdb200, m) {
   m.def("launch_count", &launch_count);
   m.def("gemm", &gemm);
+  m.def("conv2d_nhwc", &conv2d_nhwc);
+  m.def("group_norm_nhwc", &group_norm_nhwc);
+  m.def("upsample2x_nhwc", &upsample2x_nhwc);
+  m.def("avgpool2x_nhwc", &avgpool2x_nhwc);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);
   m.def("norm_modulate_fwd", &norm_modulate_fwd);

@@ -1,0 +1,170 @@
+// NHWC image kernels around the implicit-GEMM convolution: GroupNorm fused with SiLU, nearest 2x upsample,
+// pixel shuffle / unshuffle, 2x2 average pool. 128-bit accesses, fp32 statistics.
+//
+// Reference behaviour: serenitymojo/ops/norm.mojo:855-1049 (NHWC GroupNorm(32)), serenitymojo/models/vae/upsample.mojo
+// (nearest 2x), serenitymojo/ops/pixelshuffle.mojo:144-770, serenitymojo/models/vae/decoder2d.mojo:150-362 (how the
+// ResnetBlock uses GN -> SiLU -> conv).
+#include "common.cuh"
+#include "kernels_api.h"
+
+namespace mdb {
+
+// stats[n, g] = (mean, rstd) over H*W*(C/G) elements. One block per (n, g).
+__global__ void __launch_bounds__(256)
+group_norm_stats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ stats, int HW, int C, int G, float eps) {
+  const int n = blockIdx.x / G, g = blockIdx.x % G;
+  const int cpg = C / G;
+  const __nv_bfloat16* base = x + static_cast<size_t>(n) * HW * C + g * cpg;
+  const int vec = cpg >> 3;  // cpg is a multiple of 8 on the vector path, else scalar
+  float s = 0.f, ss = 0.f;
+  if (vec > 0 && (cpg & 7) == 0) {
+    const long long total = static_cast<long long>(HW) * vec;
+    for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+      const int p = static_cast<int>(i / vec), v = static_cast<int>(i % vec);
+      const uint4 u = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(p) * C + v * 8);
+      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16x2(w4[k]);
+        s += f.x + f.y;
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+  } else {
+    const long long total = static_cast<long long>(HW) * cpg;
+    for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+      const float f = __bfloat162float(base[(i / cpg) * C + (i % cpg)]);
+      s += f;
+      ss += f * f;
+    }
+  }
+  __shared__ float rs[8], rss[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    rs[threadIdx.x >> 5] = s;
+    rss[threadIdx.x >> 5] = ss;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+    for (int i = 0; i < 8; ++i) {
+      a += rs[i];
+      b += rss[i];
+    }
+    const float cnt = static_cast<float>(HW) * cpg;
+    const float mean = a / cnt;
+    const float var = fmaxf(b / cnt - mean * mean, 0.f);
+    stats[2 * blockIdx.x] = mean;
+    stats[2 * blockIdx.x + 1] = rsqrtf(var + eps);
+  }
+}
+
+// y = act((x - mean) * rstd * w[c] + b[c]); act 0 none, 2 SiLU
+__global__ void group_norm_apply_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                        const float* __restrict__ stats, const __nv_bfloat16* __restrict__ w,
+                                        const __nv_bfloat16* __restrict__ b, long long total_vec, int HW, int C, int G,
+                                        int act) {
+  const int cv = C >> 3, cpg = C / G;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_vec; i += (long long)gridDim.x * blockDim.x) {
+    const int c0 = static_cast<int>(i % cv) * 8;
+    const long long pix = i / cv;
+    const int n = static_cast<int>(pix / HW);
+    const uint4 u = *reinterpret_cast<const uint4*>(x + i * 8);
+    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack_bf16x2(w4[k]);
+      v[2 * k] = f.x;
+      v[2 * k + 1] = f.y;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = c0 + k;
+      const int g = c / cpg;
+      const float mean = stats[2 * (n * G + g)], rstd = stats[2 * (n * G + g) + 1];
+      float t = (v[k] - mean) * rstd;
+      if (w) t = t * __bfloat162float(w[c]) + (b ? __bfloat162float(b[c]) : 0.f);
+      if (act == 2) t = silu_f(t);
+      v[k] = t;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]);
+    o.y = pack_bf16x2(v[2], v[3]);
+    o.z = pack_bf16x2(v[4], v[5]);
+    o.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(y + i * 8) = o;
+  }
+}
+
+// nearest-neighbour 2x upsample, NHWC
+__global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int N, int H, int W, int cv) {
+  const long long total = static_cast<long long>(N) * H * 2 * W * 2 * cv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = static_cast<int>(i % cv);
+    long long r = i / cv;
+    const int ow = static_cast<int>(r % (2 * W));
+    r /= 2 * W;
+    const int oh = static_cast<int>(r % (2 * H));
+    const int n = static_cast<int>(r / (2 * H));
+    y[i] = x[((static_cast<long long>(n) * H + (oh >> 1)) * W + (ow >> 1)) * cv + c];
+  }
+}
+
+// 2x2 average pool, NHWC (down-sampling path of encoders when no strided conv is used)
+__global__ void avgpool2x_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int N, int H, int W,
+                                 int C) {
+  const int Ho = H / 2, Wo = W / 2;
+  const long long total = static_cast<long long>(N) * Ho * Wo * C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = static_cast<int>(i % C);
+    long long r = i / C;
+    const int ow = static_cast<int>(r % Wo);
+    r /= Wo;
+    const int oh = static_cast<int>(r % Ho);
+    const int n = static_cast<int>(r / Ho);
+    const __nv_bfloat16* p = x + ((static_cast<long long>(n) * H + 2 * oh) * W + 2 * ow) * C + c;
+    const float s = __bfloat162float(p[0]) + __bfloat162float(p[C]) + __bfloat162float(p[static_cast<long long>(W) * C]) +
+                    __bfloat162float(p[static_cast<long long>(W) * C + C]);
+    y[i] = __float2bfloat16_rn(0.25f * s);
+  }
+}
+
+static inline int grid_for(long long n, int threads) {
+  long long b = (n + threads - 1) / threads;
+  const long long cap = 148ll * 16;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace mdb
+
+using namespace mdb;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int mdb_group_norm(const void* x, void* y, float* stats, const void* w, const void* b, int N, int HW, int C,
+                              int G, float eps, int act, cudaStream_t st) {
+  if (C % 8 || C % G) return -1;
+  if (N <= 0 || HW <= 0) return 0;
+  group_norm_stats_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, stats, HW, C, G, eps);
+  const long long tv = static_cast<long long>(N) * HW * (C / 8);
+  group_norm_apply_kernel<<<grid_for(tv, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, stats, (const bf16*)w,
+                                                             (const bf16*)b, tv, HW, C, G, act);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_upsample2x(const void* x, void* y, int N, int H, int W, int C, cudaStream_t st) {
+  if (C % 8) return -1;
+  const long long total = static_cast<long long>(N) * H * W * 4 * (C / 8);
+  if (total <= 0) return 0;
+  upsample2x_kernel<<<grid_for(total, 256), 256, 0, st>>>((const uint4*)x, (uint4*)y, N, H, W, C / 8);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_avgpool2x(const void* x, void* y, int N, int H, int W, int C, cudaStream_t st) {
+  const long long total = static_cast<long long>(N) * (H / 2) * (W / 2) * C;
+  if (total <= 0) return 0;
+  avgpool2x_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, N, H, W, C);
+  return (int)cudaGetLastError();
+}

@@ -51,6 +51,11 @@ typedef struct MdbGemmArgs {
   // part * route_owner_cols. This is the Ulysses head-scatter done by the projection's own epilogue.
   void* route_out[MDB_GEMM_MAX_PEERS];
   int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
+  // Implicit-GEMM convolution, stride 1 (conv_taps = KH*KW > 0): A[0] is an NHWC bf16 image [conv_n, conv_h, conv_w,
+  // conv_cin] (conv_cin a multiple of 64), B[0] the filter [N, KH, KW, conv_cin] as a [N, KH*KW*conv_cin] matrix,
+  // M = conv_n*conv_h*conv_w output pixels (output NHWC [.., N] with ld_out). Padding pad_h / pad_w is implicit:
+  // taps that fall outside the image read zeros through the tensor map's out-of-range fill.
+  int conv_taps, conv_kw, conv_pad_h, conv_pad_w, conv_n, conv_h, conv_w, conv_cin;
 } MdbGemmArgs;
 
 int mdb_gemm_launch(const MdbGemmArgs* args, cudaStream_t stream);

@@ -28,6 +28,7 @@ namespace mdb {
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;  // one swizzle atom row: 64 bf16 or 128 fp8
 constexpr int NUM_THREADS = 192;
+constexpr int CONV_TW = 16, CONV_TH = 8;  // conv mode: one M tile = 8 rows x 16 columns of output pixels
 
 struct alignas(64) GemmMaps {
   CUtensorMap a[MDB_GEMM_MAX_SEG];
@@ -57,6 +58,9 @@ struct GemmParams {
   // peer-routed output (sequence-parallel all-to-all in the epilogue): see MdbGemmArgs
   void* route_out[MDB_GEMM_MAX_PEERS];
   int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
+  // implicit-GEMM convolution (conv_taps > 0): A is an NHWC image read through a 4-D tensor map, one 16x8 pixel
+  // patch per M tile, one shifted box per filter tap; rows outside the image are skipped by the epilogue
+  int conv_taps, conv_kw, conv_pad_h, conv_pad_w, conv_h, conv_w, conv_tiles_h, conv_tiles_w, conv_cblocks, conv_tiles_m;
 };
 
 __device__ __forceinline__ float apply_act_rt(int act, float x) {
@@ -291,7 +295,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
 
-  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_m = p.conv_taps > 0 ? p.conv_tiles_m : (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + (p.pair_offset > 0 ? BN / 2 : BN) - 1) / (p.pair_offset > 0 ? BN / 2 : BN);
   const int num_tiles = tiles_m * tiles_n;
   int total_kb = 0;
@@ -323,8 +327,18 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             uint8_t* sa = smem + stage * STAGE_BYTES;
             uint8_t* sb = sa + A_BYTES;
             mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-            const int k0 = kb * K_ELEMS;
-            if (!A_MN) {
+            int k0 = kb * K_ELEMS;
+            if (p.conv_taps > 0) {
+              // tile -> (image, patch row, patch col); k block -> (filter tap, channel block)
+              const int mt = tile % tiles_m;
+              const int tw = mt % p.conv_tiles_w, th = (mt / p.conv_tiles_w) % p.conv_tiles_h;
+              const int img = mt / (p.conv_tiles_w * p.conv_tiles_h);
+              const int tap = kb / p.conv_cblocks, cb = kb - tap * p.conv_cblocks;
+              const int kh = tap / p.conv_kw, kw = tap - kh * p.conv_kw;
+              tma_load_4d(sa, &maps.a[s], &full_bar[stage], cb * K_ELEMS, tw * CONV_TW + kw - p.conv_pad_w,
+                          th * CONV_TH + kh - p.conv_pad_h, img);
+              k0 = (tap * p.conv_cblocks + cb) * K_ELEMS;
+            } else if (!A_MN) {
               tma_load_2d(sa, &maps.a[s], &full_bar[stage], k0, m0);
             } else {
               // boxes [64 m-elements][64 k-rows], 8 KB each
@@ -450,7 +464,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       tc_fence_after();
       const long long tq1 = p.prof ? clock64() : 0;
       t_twait += tq1 - tq0;
-      const int row = m0 + quad * 32 + lane;
+      int row = m0 + quad * 32 + lane;
+      if (p.conv_taps > 0) {
+        const int mt = tile % tiles_m;
+        const int tw = mt % p.conv_tiles_w, th = (mt / p.conv_tiles_w) % p.conv_tiles_h;
+        const int img = mt / (p.conv_tiles_w * p.conv_tiles_h);
+        const int r = quad * 32 + lane;
+        const int oh = th * CONV_TH + r / CONV_TW, ow = tw * CONV_TW + r % CONV_TW;
+        row = (oh < p.conv_h && ow < p.conv_w) ? (img * p.conv_h + oh) * p.conv_w + ow : p.M;  // p.M = skipped
+      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const int out_cols = paired ? BN / 2 : BN;
 #pragma unroll 1
@@ -534,7 +556,7 @@ static int launch_variant(const GemmMaps& maps, const GemmParams& p, int num_sms
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_done = true;
   }
-  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_m = p.conv_taps > 0 ? p.conv_tiles_m : (p.M + BM - 1) / BM;
   const int bn_eff = p.pair_offset > 0 ? BN / 2 : BN;
   const int tiles_n = (p.N + bn_eff - 1) / bn_eff;
   int grid = tiles_m * tiles_n;
@@ -583,13 +605,25 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
     {
       int64_t ext[2], str[2];
       int box[2];
+      if (a->conv_taps > 0) {
+        if (s != 0 || a->a_mn || a->kind != 0) return -6;
+        const int64_t cin = a->conv_cin;
+        int64_t e4[4] = {cin, a->conv_w, a->conv_h, a->conv_n};
+        int64_t s4[4] = {eb, cin * eb, a->conv_w * cin * eb, static_cast<int64_t>(a->conv_h) * a->conv_w * cin * eb};
+        int b4[4] = {k_elems, CONV_TW, CONV_TH, 1};
+        int r = mdb_make_tmap(&maps.a[s], a->A[s], eb, 4, e4, s4, b4, 1);
+        if (r) return 1000 + r;
+        p.kblocks[s] = a->conv_taps * static_cast<int>((cin + k_elems - 1) / k_elems);
+      } else
       if (!a->a_mn) {  // [M rows][K] row-major
         ext[0] = K; ext[1] = a->M; str[0] = eb; str[1] = a->lda[s] * eb; box[0] = k_elems; box[1] = BM;
       } else {  // stored [K rows][M]
         ext[0] = a->M; ext[1] = K; str[0] = eb; str[1] = a->lda[s] * eb; box[0] = 64; box[1] = 64;
       }
-      int r = mdb_make_tmap(&maps.a[s], a->A[s], eb, 2, ext, str, box, 1);
-      if (r) return 1000 + r;
+      if (a->conv_taps <= 0) {
+        int r = mdb_make_tmap(&maps.a[s], a->A[s], eb, 2, ext, str, box, 1);
+        if (r) return 1000 + r;
+      }
     }
     {
       int64_t ext[2], str[2];
@@ -622,6 +656,16 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   p.status = a->status;
   p.prof = a->prof;
   for (int i = 0; i < MDB_GEMM_MAX_PEERS; ++i) p.route_out[i] = a->route_out[i];
+  p.conv_taps = a->conv_taps;
+  if (a->conv_taps > 0) {
+    if (a->conv_cin % k_elems) return -7;
+    p.conv_kw = a->conv_kw; p.conv_pad_h = a->conv_pad_h; p.conv_pad_w = a->conv_pad_w;
+    p.conv_h = a->conv_h; p.conv_w = a->conv_w;
+    p.conv_tiles_h = (a->conv_h + CONV_TH - 1) / CONV_TH;
+    p.conv_tiles_w = (a->conv_w + CONV_TW - 1) / CONV_TW;
+    p.conv_cblocks = a->conv_cin / k_elems;
+    p.conv_tiles_m = a->conv_n * p.conv_tiles_h * p.conv_tiles_w;
+  }
   p.route_owner_cols = a->route_owner_cols;
   p.route_part_cols = a->route_part_cols > 0 ? a->route_part_cols : a->N;
   p.route_row_offset = a->route_row_offset;

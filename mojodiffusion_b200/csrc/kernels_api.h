@@ -67,6 +67,12 @@ int mdb_fp8_quant_rows(const void* x, void* q, float* scale, long long rows, int
 int mdb_fp8_dequant(const void* q, const float* row_scale, float tensor_scale, void* y, long long rows, int D,
                     cudaStream_t st);
 
+// ---- conv_norm.cu (NHWC)
+int mdb_group_norm(const void* x, void* y, float* stats, const void* w, const void* b, int N, int HW, int C, int G,
+                   float eps, int act, cudaStream_t st);
+int mdb_upsample2x(const void* x, void* y, int N, int H, int W, int C, cudaStream_t st);
+int mdb_avgpool2x(const void* x, void* y, int N, int H, int W, int C, cudaStream_t st);
+
 // ---- optim.cu
 int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
                     int g_bf16, int m_bf16, float lr, float beta1, float beta2, float eps, float wd, int step,

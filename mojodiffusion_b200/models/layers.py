@@ -141,3 +141,66 @@ def iter_linears(module: nn.Module, prefix: str = ""):
     for name, sub in module.named_modules():
         if isinstance(sub, Linear):
             yield name, sub
+
+
+class RMSNorm(nn.Module):
+    """RMSNorm with a learned weight over the last dim (serenitymojo/ops/norm.mojo:47-230)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+
+    def forward(self, x, scale=None, shift=None, rows_per_group=None):
+        return ops.norm_modulate(x, weight=self.weight, scale=scale, shift=shift, rows_per_group=rows_per_group,
+                                 eps=self.eps, rms=True)
+
+
+class LayerNorm(nn.Module):
+    """LayerNorm, affine optional (serenitymojo/ops/norm.mojo:318-460,652-782)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6, affine: bool = True, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device)) if affine else None
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device)) if affine else None
+
+    def forward(self, x, scale=None, shift=None, rows_per_group=None):
+        return ops.norm_modulate(x, weight=self.weight, bias=self.bias, scale=scale, shift=shift,
+                                 rows_per_group=rows_per_group, eps=self.eps, rms=False)
+
+
+def packed_projection(x: torch.Tensor, linears) -> torch.Tensor:
+    """Run several Linear modules on the same input and return their outputs side by side in ONE buffer
+    ([..., sum(out_features)]): on the GPU inference path each GEMM stores straight into its column slice, so
+    separate to_q / to_k / to_v weights (diffusers layout) still give the packed qkv the attention kernels read."""
+    widths = [l.out_features for l in linears]
+    if x.is_cuda and not torch.is_grad_enabled():
+        lead = x.shape[:-1]
+        out = torch.empty(*lead, sum(widths), dtype=x.dtype, device=x.device)
+        c = 0
+        for l, w in zip(linears, widths):
+            l(x, out=out[..., c:c + w])
+            c += w
+        return out
+    return torch.cat([l(x) for l in linears], dim=-1)
+
+
+@torch.no_grad()
+def init_module_weights(module: nn.Module, seed: int = 0, std: float = 0.02) -> nn.Module:
+    """Deterministic random init shared by all backbones: normal(0, std) matrices, zero biases, unit norm weights.
+    Large tensors are drawn on the device by the Philox kernel, small ones from a CPU generator."""
+    g = torch.Generator().manual_seed(seed)
+    for name, p in module.named_parameters():
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf in ("scale",) or (leaf == "weight" and p.dim() == 1):
+            p.fill_(1.0)
+        elif leaf == "bias" or p.dim() == 1:
+            p.zero_()
+        else:
+            if p.device.type == "cuda" and p.numel() > (1 << 22) and p.dtype in (torch.bfloat16, torch.float32):
+                p.copy_(ops.randn(tuple(p.shape), seed=seed + zlib.crc32(name.encode()) % 100003, dtype=torch.float32,
+                                  device=p.device) * std)
+            else:
+                p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+    return module

@@ -1,0 +1,111 @@
+"""Image ops in NHWC: convolution (implicit GEMM on tcgen05 through 4-D TMA boxes), GroupNorm+SiLU, nearest 2x
+upsample, 2x2 average pool, pixel (un)shuffle and latent patchify helpers.
+
+The native convolution covers stride 1 with "same" padding and Cin a multiple of 64 (the bulk of every VAE / UNet);
+other shapes (the 3- or 4-channel stem, strided down-sampling convs) use ``torch.nn.functional.conv2d``.
+Reference: serenitymojo/ops/conv.mojo:46-209 (im2col + GEMM), serenitymojo/models/vae/decoder2d.mojo:150-362,
+serenitymojo/ops/pixelshuffle.mojo:144-770, serenitymojo/ops/layout.mojo:44-383.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .reference import act_code, activation
+
+
+def conv2d_nhwc_reference(x, w_ohwi, bias=None, stride: int = 1, padding=1, act=None, residual=None):
+    """x [N,H,W,Cin], w [Cout,KH,KW,Cin] -> [N,Ho,Wo,Cout]; fp32 math."""
+    pad = (padding, padding) if isinstance(padding, int) else tuple(padding)
+    y = F.conv2d(x.permute(0, 3, 1, 2).float(), w_ohwi.permute(0, 3, 1, 2).float(),
+                 bias.float() if bias is not None else None, stride=stride, padding=pad)
+    y = activation(y, act).permute(0, 2, 3, 1)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def conv2d_nhwc(x, w_ohwi, bias=None, stride: int = 1, padding=1, act=None, residual=None):
+    pad = (padding, padding) if isinstance(padding, int) else tuple(padding)
+    KH, KW, Cin = w_ohwi.shape[1], w_ohwi.shape[2], w_ohwi.shape[3]
+    fast = (native.use_native(x) and not torch.is_grad_enabled() and x.dtype == torch.bfloat16 and stride == 1
+            and Cin % 64 == 0 and w_ohwi.shape[0] % 8 == 0 and 2 * pad[0] == KH - 1 and 2 * pad[1] == KW - 1)
+    if fast:
+        res = residual.contiguous() if residual is not None else None
+        return native.ops().conv2d_nhwc(x.contiguous(), w_ohwi.contiguous(), bias, pad[0], pad[1], act_code(act), res)
+    return conv2d_nhwc_reference(x, w_ohwi, bias, stride, pad, act, residual)
+
+
+def group_norm_nhwc(x, weight=None, bias=None, groups: int = 32, eps: float = 1e-6, act=None):
+    """GroupNorm over (H, W, C/G) per sample and group on an NHWC tensor, optional fused SiLU."""
+    a = act_code(act)
+    if native.use_native(x) and not torch.is_grad_enabled() and x.dtype == torch.bfloat16 and a in (0, 2) \
+            and x.shape[-1] % 8 == 0:
+        return native.ops().group_norm_nhwc(x.contiguous(), weight, bias, groups, eps, a)
+    N, H, W, C = x.shape
+    xf = x.float().reshape(N, H * W, groups, C // groups)
+    mu = xf.mean(dim=(1, 3), keepdim=True)
+    var = (xf - mu).pow(2).mean(dim=(1, 3), keepdim=True)
+    y = ((xf - mu) * torch.rsqrt(var + eps)).reshape(N, H, W, C)
+    if weight is not None:
+        y = y * weight.float() + (bias.float() if bias is not None else 0.0)
+    return activation(y, act).to(x.dtype)
+
+
+def upsample_nearest2x_nhwc(x):
+    if native.use_native(x) and not torch.is_grad_enabled() and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        return native.ops().upsample2x_nhwc(x.contiguous())
+    return x.repeat_interleave(2, dim=1).repeat_interleave(2, dim=2)
+
+
+def avgpool2x_nhwc(x):
+    if native.use_native(x) and not torch.is_grad_enabled() and x.dtype == torch.bfloat16:
+        return native.ops().avgpool2x_nhwc(x.contiguous())
+    N, H, W, C = x.shape
+    return x.float().reshape(N, H // 2, 2, W // 2, 2, C).mean(dim=(2, 4)).to(x.dtype)
+
+
+# ---- layout helpers (index math; views where possible) ---------------------------------------------------
+def pixel_shuffle_nhwc(x, r: int):
+    """[N,H,W,C*r*r] -> [N,H*r,W*r,C] (channel order c, ry, rx as torch.nn.PixelShuffle)."""
+    N, H, W, Crr = x.shape
+    C = Crr // (r * r)
+    return x.reshape(N, H, W, C, r, r).permute(0, 1, 4, 2, 5, 3).reshape(N, H * r, W * r, C)
+
+
+def pixel_unshuffle_nhwc(x, r: int):
+    N, Hr, Wr, C = x.shape
+    H, W = Hr // r, Wr // r
+    return x.reshape(N, H, r, W, r, C).permute(0, 1, 3, 5, 2, 4).reshape(N, H, W, C * r * r)
+
+
+def depth_to_space_3d(x, ft: int, fh: int, fw: int):
+    """[N,T,H,W,C*ft*fh*fw] -> [N,T*ft,H*fh,W*fw,C] (video VAE up-sampling; serenitymojo/ops/pixelshuffle.mojo)."""
+    N, T, H, W, Cf = x.shape
+    C = Cf // (ft * fh * fw)
+    x = x.reshape(N, T, H, W, C, ft, fh, fw).permute(0, 1, 5, 2, 6, 3, 7, 4)
+    return x.reshape(N, T * ft, H * fh, W * fw, C)
+
+
+def space_to_depth_3d(x, ft: int, fh: int, fw: int):
+    N, Tt, Hh, Ww, C = x.shape
+    T, H, W = Tt // ft, Hh // fh, Ww // fw
+    x = x.reshape(N, T, ft, H, fh, W, fw, C).permute(0, 1, 3, 5, 7, 2, 4, 6)
+    return x.reshape(N, T, H, W, C * ft * fh * fw)
+
+
+def patchify_3d(z, pt: int, ph: int, pw: int):
+    """[B,C,T,H,W] -> tokens [B, (T/pt)(H/ph)(W/pw), C*pt*ph*pw] (serenitymojo/ops/patchify3d.mojo:159)."""
+    B, C, T, H, W = z.shape
+    z = z.reshape(B, C, T // pt, pt, H // ph, ph, W // pw, pw).permute(0, 2, 4, 6, 1, 3, 5, 7)
+    return z.reshape(B, (T // pt) * (H // ph) * (W // pw), C * pt * ph * pw)
+
+
+def unpatchify_3d(x, grid, C: int, pt: int, ph: int, pw: int):
+    B = x.shape[0]
+    T, H, W = grid
+    x = x.reshape(B, T, H, W, C, pt, ph, pw).permute(0, 4, 1, 5, 2, 6, 3, 7)
+    return x.reshape(B, C, T * pt, H * ph, W * pw)

@@ -1,0 +1,140 @@
+"""Model families on the GPU kernels (bf16) against the same modules evaluated through the pure-torch references in
+fp32 on the CPU; convolution / GroupNorm kernels against torch."""
+import copy
+import math
+
+import pytest
+import torch
+
+import mojodiffusion_b200.ops as O
+from mojodiffusion_b200.ops import conv as C
+from mojodiffusion_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _cos(a, b):
+    a, b = a.float().flatten().cpu(), b.float().flatten().cpu()
+    return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-30))
+
+
+def _gpu_vs_cpu(make, inputs, cos_min=0.995, **kw):
+    m32 = make(torch.float32, "cpu").init_weights(0)
+    mg = make(torch.bfloat16, DEV)
+    mg.load_state_dict({k: v.to(torch.bfloat16) for k, v in m32.state_dict().items()})
+    with torch.no_grad():
+        m32.load_state_dict({k: v.float() for k, v in mg.state_dict().items()})   # same bf16-rounded weights
+        want = m32(*inputs, **kw)
+        got = mg(*[t.to(DEV) for t in inputs], **kw)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.isfinite(got.float()).all()
+    c = _cos(got, want)
+    assert c >= cos_min, f"cos {c}"
+    return got
+
+
+@pytest.mark.parametrize("cin,cout,k,hw", [(64, 64, 3, (16, 16)), (128, 256, 3, (24, 40)), (256, 128, 1, (9, 13)), (64, 8, 3, (8, 8))])
+def test_conv2d_implicit_gemm(cin, cout, k, hw):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, hw[0], hw[1], cin, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(cout, k, k, cin, generator=g) / math.sqrt(cin * k * k)).bfloat16().to(DEV)
+    b = torch.randn(cout, generator=g).bfloat16().to(DEV)
+    res = torch.randn(2, hw[0], hw[1], cout, generator=g).bfloat16().to(DEV)
+    with torch.no_grad():
+        got = C.conv2d_nhwc(x, w, b, 1, k // 2, "silu", res)
+        want = C.conv2d_nhwc_reference(x.float(), w.float(), b.float(), 1, k // 2, "silu", res.float())
+    native.check_status(got)
+    assert _cos(got, want) > 0.9995 and float((got.float() - want).abs().max()) < 0.06 * float(want.abs().max()) + 1e-2
+
+
+def test_group_norm_upsample_pool():
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(2, 12, 10, 128, generator=g) * 2 + 0.3).bfloat16().to(DEV)
+    w, b = torch.randn(128, generator=g).bfloat16().to(DEV), torch.randn(128, generator=g).bfloat16().to(DEV)
+    with torch.no_grad():
+        for act in (None, "silu"):
+            got = C.group_norm_nhwc(x, w, b, 32, 1e-6, act)
+            want = torch.nn.functional.group_norm(x.float().permute(0, 3, 1, 2), 32, w.float(), b.float(), 1e-6)
+            want = (torch.nn.functional.silu(want) if act else want).permute(0, 2, 3, 1)
+            assert _cos(got, want) > 0.9995
+        up = C.upsample_nearest2x_nhwc(x)
+        assert torch.equal(up, x.repeat_interleave(2, 1).repeat_interleave(2, 2))
+        pool = C.avgpool2x_nhwc(x)
+        assert _cos(pool, x.float().reshape(2, 6, 2, 5, 2, 128).mean((2, 4))) > 0.9999
+    native.check_status(x)
+
+
+def test_single_stream_dit():
+    from mojodiffusion_b200.models.single_dit import SingleStreamDiT, tiny_single_dit_config
+    g = torch.Generator().manual_seed(2)
+    inputs = (torch.randn(2, 64, 64, generator=g), torch.randn(2, 16, 128, generator=g), torch.tensor([0.2, 0.9]))
+    _gpu_vs_cpu(lambda dt, dev: SingleStreamDiT(tiny_single_dit_config(), dt, dev), inputs, hw=(8, 8))
+
+
+def test_qwen_image_dit_with_text_mask():
+    from mojodiffusion_b200.models.qwen_image import QwenImageDiT, tiny_qwen_image_config
+    g = torch.Generator().manual_seed(3)
+    inputs = (torch.randn(2, 64, 64, generator=g), torch.randn(2, 24, 128, generator=g), torch.tensor([0.3, 0.7]))
+    m32 = QwenImageDiT(tiny_qwen_image_config(), torch.float32, "cpu").init_weights(0)
+    mg = QwenImageDiT(tiny_qwen_image_config(), torch.bfloat16, DEV)
+    mg.load_state_dict({k: v.bfloat16() for k, v in m32.state_dict().items()})
+    m32.load_state_dict({k: v.float() for k, v in mg.state_dict().items()})
+    tl = torch.tensor([24, 9], dtype=torch.int32)
+    with torch.no_grad():
+        want = m32(*inputs, hw=(8, 8), txt_len=tl)
+        got = mg(*[t.to(DEV) for t in inputs], hw=(8, 8), txt_len=tl.to(DEV))
+    native.check_status(got)
+    assert _cos(got, want) > 0.995
+
+
+def test_video_dit_bf16_and_fp8():
+    from mojodiffusion_b200.models.video_dit import VideoDiT, tiny_video_dit_config
+    g = torch.Generator().manual_seed(4)
+    inputs = (torch.randn(2, 2 * 4 * 8, 32, generator=g), torch.randn(2, 10, 128, generator=g), torch.tensor([0.3, 0.6]))
+    got = _gpu_vs_cpu(lambda dt, dev: VideoDiT(tiny_video_dit_config(), dt, dev), inputs, grid=(2, 4, 8))
+    m = VideoDiT(tiny_video_dit_config(), torch.bfloat16, DEV).init_weights(0)
+    with torch.no_grad():
+        ref = m(*[t.to(DEV) for t in inputs], grid=(2, 4, 8))
+        q = copy.deepcopy(m).to_fp8()
+        out = q(*[t.to(DEV) for t in inputs], grid=(2, 4, 8))
+    native.check_status(out)
+    assert _cos(out, ref) > 0.99
+
+
+def test_unet_and_vae():
+    from mojodiffusion_b200.models.unet import UNet, tiny_unet_config
+    from mojodiffusion_b200.models.vae import AutoencoderKL, tiny_vae_config
+    g = torch.Generator().manual_seed(5)
+    inputs = (torch.randn(2, 4, 16, 16, generator=g), torch.tensor([10.0, 900.0]), torch.randn(2, 7, 64, generator=g),
+              torch.randn(2, 96, generator=g))
+    _gpu_vs_cpu(lambda dt, dev: UNet(tiny_unet_config(), dt, dev), inputs, cos_min=0.99)
+    v32 = AutoencoderKL(tiny_vae_config(), torch.float32, "cpu").init_weights(0)
+    vg = AutoencoderKL(tiny_vae_config(), torch.bfloat16, DEV)
+    vg.load_state_dict({k: v.bfloat16() for k, v in v32.state_dict().items()})
+    v32.load_state_dict({k: v.float() for k, v in vg.state_dict().items()})
+    z = torch.randn(1, 4, 12, 12, generator=g)
+    with torch.no_grad():
+        want = v32.decode(z)
+        got = vg.decode(z.to(DEV))
+        enc = vg.encode(torch.randn(1, 3, 32, 32, generator=g).to(DEV), sample=False)
+        tiled = vg.tiled_decode(torch.randn(1, 4, 24, 24, generator=g).to(DEV), tile=16, overlap=8)
+    native.check_status(got)
+    assert _cos(got, want) > 0.99 and enc.shape == (1, 4, 16, 16) and tiled.shape == (1, 3, 48, 48)
+    assert torch.isfinite(tiled.float()).all()
+
+
+def test_cuda_graph_replay_is_bit_exact():
+    from mojodiffusion_b200.models.mmdit import MMDiT, tiny_mmdit_config
+    from mojodiffusion_b200.utils.cuda_graph import graphs_equal_eager
+    m = MMDiT(tiny_mmdit_config(), torch.bfloat16, DEV).init_weights(0)
+    g = torch.Generator().manual_seed(6)
+    img = torch.randn(1, 256, 64, generator=g).bfloat16().to(DEV)
+    txt = torch.randn(1, 64, 256, generator=g).bfloat16().to(DEV)
+    y = torch.randn(1, 256, generator=g).bfloat16().to(DEV)
+    t = torch.tensor([0.5], device=DEV)
+    ids = MMDiT.make_ids(16, 16, 64, DEV)
+    same, err = graphs_equal_eager(lambda a, b, c, d: m(a, b, c, d, ids=ids), [img, txt, t, y])
+    native.check_status(img)
+    assert same, err
