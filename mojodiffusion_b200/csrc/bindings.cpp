@@ -54,7 +54,8 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
             int64_t pair_offset, int64_t act_on_second, const optional<Tensor>& out_opt, bool out_fp32, bool a_mn,
             bool b_mn, const optional<Tensor>& row_scale, const optional<Tensor>& col_scale, double alpha,
             bool accumulate, int64_t bn, const optional<Tensor>& prof, std::vector<int64_t> route_ptrs,
-            std::vector<int64_t> route_cfg) {
+            std::vector<int64_t> route_cfg, std::vector<int64_t> gather_ptrs, std::vector<int64_t> gather_cfg,
+            const optional<Tensor>& gather_dst, const optional<Tensor>& gather_ready) {
   TORCH_CHECK(!As.empty() && As.size() == Bs.size() && As.size() <= MDB_GEMM_MAX_SEG, "gemm: 1..3 K segments");
   const Tensor& A0 = As[0];
   TORCH_CHECK(A0.is_cuda(), "gemm: CUDA tensors only");
@@ -145,7 +146,27 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
     TORCH_CHECK(prof->scalar_type() == at::kLong && prof->numel() >= 8 * g.num_sms, "gemm: prof [sms, 8] int64");
     g.prof = reinterpret_cast<long long*>(prof->data_ptr());
   }
-  if (!route_ptrs.empty()) {
+  if (!gather_ptrs.empty()) {
+    // gather_cfg = {rank, operand (0 A / 1 B), chunk_rows, chunk_bytes}
+    TORCH_CHECK(gather_ptrs.size() <= MDB_GEMM_MAX_PEERS && gather_cfg.size() == 4 && gather_dst.has_value() &&
+                    gather_ready.has_value() && gather_ready->scalar_type() == at::kInt && gather_ready->numel() >= 8,
+                "gemm: gather arguments");
+    for (size_t i = 0; i < gather_ptrs.size(); ++i) g.gather_src[i] = reinterpret_cast<const void*>(gather_ptrs[i]);
+    g.gather_world = (int)gather_ptrs.size();
+    g.gather_rank = (int)gather_cfg[0];
+    g.gather_operand = (int)gather_cfg[1];
+    g.gather_chunk_rows = (int)gather_cfg[2];
+    g.gather_chunk_bytes = gather_cfg[3];
+    g.gather_dst = gather_dst->data_ptr();
+    g.gather_ready = gather_ready->data_ptr<int>();
+  }
+  if (!route_ptrs.empty() && route_cfg.size() == 2) {
+    // reduce-scatter epilogue: route_cfg = {rows_per_owner, ld_out}
+    TORCH_CHECK(out_fp32, "gemm: reduce-scatter epilogue accumulates in fp32");
+    for (size_t i = 0; i < route_ptrs.size(); ++i) g.route_out[i] = reinterpret_cast<void*>(route_ptrs[i]);
+    g.reduce_rows_per_owner = (int)route_cfg[0];
+    g.ld_out = (int)route_cfg[1];
+  } else if (!route_ptrs.empty()) {
     // route_cfg = {owner_cols, part_cols, row_offset, rows_per_batch, batch_rows, ld_out}
     TORCH_CHECK(route_ptrs.size() <= MDB_GEMM_MAX_PEERS && route_cfg.size() == 6, "gemm: route arguments");
     for (size_t i = 0; i < route_ptrs.size(); ++i) g.route_out[i] = reinterpret_cast<void*>(route_ptrs[i]);

@@ -51,6 +51,18 @@ typedef struct MdbGemmArgs {
   // part * route_owner_cols. This is the Ulysses head-scatter done by the projection's own epilogue.
   void* route_out[MDB_GEMM_MAX_PEERS];
   int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
+  // All-gather fused GEMM (gather_world > 1): the operand selected by gather_operand (0 = A, 1 = B) is read from
+  // the local buffer gather_dst = [gather_world chunks of gather_chunk_rows rows]; chunk r is fetched inside the
+  // kernel from gather_src[r] (rank r's shard in peer memory, gather_chunk_bytes bytes); chunk gather_rank must
+  // already be in place. gather_ready: local int[8] scratch (zeroed by the launcher).
+  const void* gather_src[MDB_GEMM_MAX_PEERS];
+  void* gather_dst;
+  int* gather_ready;
+  long long gather_chunk_bytes;
+  int gather_world, gather_rank, gather_operand, gather_chunk_rows;
+  // Reduce-scatter fused GEMM (reduce_rows_per_owner > 0, fp32 output): output row r is ADDED into
+  // route_out[r / reduce_rows_per_owner] (that rank's fp32 [rows_per_owner, ld_out] buffer) with red.global.add.
+  int reduce_rows_per_owner;
   // Implicit-GEMM convolution, stride 1 (conv_taps = KH*KW > 0): A[0] is an NHWC bf16 image [conv_n, conv_h, conv_w,
   // conv_cin] (conv_cin a multiple of 64), B[0] the filter [N, KH, KW, conv_cin] as a [N, KH*KW*conv_cin] matrix,
   // M = conv_n*conv_h*conv_w output pixels (output NHWC [.., N] with ld_out). Padding pad_h / pad_w is implicit:

@@ -27,7 +27,7 @@ namespace mdb {
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;  // one swizzle atom row: 64 bf16 or 128 fp8
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 224;  // warps: 0 TMA, 1 UMMA issue, 2-5 epilogue, 6 peer gather (all-gather fused GEMM)
 constexpr int CONV_TW = 16, CONV_TH = 8;  // conv mode: one M tile = 8 rows x 16 columns of output pixels
 
 struct alignas(64) GemmMaps {
@@ -58,6 +58,18 @@ struct GemmParams {
   // peer-routed output (sequence-parallel all-to-all in the epilogue): see MdbGemmArgs
   void* route_out[MDB_GEMM_MAX_PEERS];
   int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
+  // all-gather fused into the GEMM (gather_world > 1): operand A (gather_operand 0) or B (1) lives in a local
+  // buffer of `gather_world` equal row chunks; chunk r is rank r's shard. Warp 6 of every CTA copies its slice of
+  // each remote chunk from the owner's memory (peer loads) and bumps ready[chunk]; the TMA producer waits for
+  // ready[chunk] == gridDim.x before it loads a tile of that chunk. Tiles are visited local chunk first.
+  const void* gather_src[MDB_GEMM_MAX_PEERS];
+  void* gather_dst;
+  int* gather_ready;
+  long long gather_chunk_bytes;
+  int gather_world, gather_rank, gather_operand, gather_chunk_rows;
+  // reduce-scatter fused into the epilogue (route_owner_cols == 0 && reduce_rows_per_owner > 0): fp32 partial
+  // results are added (red.global.add) into the row owner's fp32 buffer route_out[row / reduce_rows_per_owner]
+  int reduce_rows_per_owner;
   // implicit-GEMM convolution (conv_taps > 0): A is an NHWC image read through a 4-D tensor map, one 16x8 pixel
   // patch per M tile, one shifted box per filter tap; rows outside the image are skipped by the epilogue
   int conv_taps, conv_kw, conv_pad_h, conv_pad_w, conv_h, conv_w, conv_tiles_h, conv_tiles_w, conv_cblocks, conv_tiles_m;
@@ -112,6 +124,11 @@ __device__ __forceinline__ void act32_rt(int act, float (&v)[32]) {
 // Routed mode: columns are (part, owner, local) blocks; the slab is stored into the owner rank's buffer at
 // row  batch * route_batch_rows + route_row_offset + row_in_batch  and column  part * owner_cols + local.
 __device__ __forceinline__ void* out_slab_ptr(const GemmParams& p, int row, int col0, int esz) {
+  if (p.reduce_rows_per_owner > 0) {
+    const int owner = row / p.reduce_rows_per_owner;
+    const size_t orow = static_cast<size_t>(row - owner * p.reduce_rows_per_owner);
+    return reinterpret_cast<char*>(p.route_out[owner]) + (orow * p.ld_out + col0) * esz;
+  }
   if (p.route_owner_cols <= 0)
     return reinterpret_cast<char*>(p.out) + (static_cast<size_t>(row) * p.ld_out + col0) * esz;
   const int part = col0 / p.route_part_cols;
@@ -144,7 +161,8 @@ __device__ __noinline__ void epilogue_row32_slow(const GemmParams& p, int row, i
     if (p.residual) x += __bfloat162float(p.residual[static_cast<size_t>(row) * p.ld_res + col]);
     if (p.out_fp32) {
       float* o = reinterpret_cast<float*>(out_slab_ptr(p, row, col0, 4)) + j;
-      *o = p.accumulate_out ? *o + x : x;
+      if (p.reduce_rows_per_owner > 0) atomicAdd(o, x);
+      else *o = p.accumulate_out ? *o + x : x;
     } else {
       reinterpret_cast<__nv_bfloat16*>(out_slab_ptr(p, row, col0, 2))[j] = __float2bfloat16_rn(x);
     }
@@ -219,7 +237,13 @@ __device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int
   }
   if (p.out_fp32) {
     float4* o = reinterpret_cast<float4*>(out_slab_ptr(p, row, col0, 4));
-    if (p.accumulate_out) {
+    if (p.reduce_rows_per_owner > 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                     "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                     : "memory");
+    } else if (p.accumulate_out) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float4 old = o[j];
@@ -241,6 +265,33 @@ __device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int
       o[j] = t;
     }
   }
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Tile -> (m block, n block). Plain GEMM: m fastest. With a fused all-gather the gathered operand's blocks are
+// visited starting at the local chunk (already present), then in the order the gather warps fetch the peers.
+__device__ __forceinline__ int tile_m_index(const GemmParams& p, int tile, int tiles_m, int tiles_n) {
+  if (p.gather_world > 1 && p.gather_operand == 1) return tile % tiles_m;
+  int m = tile % tiles_m;
+  if (p.gather_world > 1) {
+    const int shift = (p.gather_rank * p.gather_chunk_rows) / BM;
+    m = (m + shift) % tiles_m;
+  }
+  return m;
+}
+__device__ __forceinline__ int tile_n_index(const GemmParams& p, int tile, int tiles_m, int tiles_n) {
+  int n = tile / tiles_m;
+  if (p.gather_world > 1 && p.gather_operand == 1) {
+    const int bn_rows = (p.N + tiles_n - 1) / tiles_n;
+    const int shift = (p.gather_rank * p.gather_chunk_rows) / max(bn_rows, 1);
+    n = (n + shift) % tiles_n;
+  }
+  return n;
 }
 
 // KIND: 0 = bf16 operands (kind::f16), 1 = fp8 e4m3 operands (kind::f8f6f4)
@@ -311,10 +362,34 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       uint32_t last_phase = 0;
       bool ok = true;
       long long t_wait = 0;
+      unsigned chunk_seen = 1u << p.gather_rank;   // chunks whose arrival this CTA has already observed
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM;
-        const int nblk = tile / tiles_m;
+        const int m0 = tile_m_index(p, tile, tiles_m, tiles_n) * BM;
+        const int nblk = tile_n_index(p, tile, tiles_m, tiles_n);
         const int n0 = p.pair_offset > 0 ? nblk * (BN / 2) : nblk * BN;
+        if (p.gather_world > 1) {
+          // every chunk this tile touches must have landed (a tile may straddle two chunks)
+          const int r0 = p.gather_operand == 0 ? m0 : n0;
+          const int r1 = r0 + (p.gather_operand == 0 ? BM : BN) - 1;
+          const int c_lo = min(r0 / p.gather_chunk_rows, p.gather_world - 1);
+          const int c_hi = min(r1 / p.gather_chunk_rows, p.gather_world - 1);
+          for (int c = c_lo; ok && c <= c_hi; ++c) {
+            if (chunk_seen & (1u << c)) continue;
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(p.gather_ready + c) < static_cast<int>(gridDim.x)) {
+              if ((++spins & 0xffu) == 0 && (abort_s || globaltimer_ns() - t0 > MDB_WAIT_LIMIT_NS)) {
+                abort_s = 1;
+                report_status(p.status, STATUS_TIMEOUT, 5, c);
+                ok = false;
+                break;
+              }
+            }
+            chunk_seen |= 1u << c;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");   // peer-copied bytes -> visible to the TMA reads
+        }
         for (int s = 0; ok && s < p.num_seg; ++s) {
           for (int kb = 0; kb < p.kblocks[s]; ++kb) {
             const long long tw0 = p.prof ? clock64() : 0;
@@ -435,6 +510,28 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       }
     }
     __syncwarp();
+  } else if (warp == 6) {
+    // ------------------------------- peer gather (all-gather fused GEMM) --------
+    if (p.gather_world > 1) {
+      const long long vec_total = p.gather_chunk_bytes >> 4;                       // 16-byte vectors per chunk
+      const long long per_cta = (vec_total + gridDim.x - 1) / gridDim.x;
+      const long long v0 = static_cast<long long>(blockIdx.x) * per_cta;
+      const long long v1 = min(v0 + per_cta, vec_total);
+      for (int i = 1; i < p.gather_world; ++i) {
+        const int c = (p.gather_rank + i) % p.gather_world;
+        const uint4* src = reinterpret_cast<const uint4*>(p.gather_src[c]);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.gather_dst) + c * p.gather_chunk_bytes);
+        long long v = v0 + lane;
+        for (; v + 96 < v1; v += 128) {                                           // 4 peer loads in flight per lane
+          const uint4 a = src[v], b = src[v + 32], cc = src[v + 64], d = src[v + 96];
+          dst[v] = a; dst[v + 32] = b; dst[v + 64] = cc; dst[v + 96] = d;
+        }
+        for (; v < v1; v += 32) dst[v] = src[v];
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.gather_ready + c, 1);
+      }
+    }
   } else {
     // ------------------------------- epilogue (4 warps) -------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
@@ -451,8 +548,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (tile % tiles_m) * BM;
-      const int nblk = tile / tiles_m;
+      const int m0 = tile_m_index(p, tile, tiles_m, tiles_n) * BM;
+      const int nblk = tile_n_index(p, tile, tiles_m, tiles_n);
       const int n0 = paired ? nblk * (BN / 2) : nblk * BN;
       const long long tq0 = p.prof ? clock64() : 0;
       // warp-uniform decision: the TMEM loads below are warp-collective
@@ -656,6 +753,21 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   p.status = a->status;
   p.prof = a->prof;
   for (int i = 0; i < MDB_GEMM_MAX_PEERS; ++i) p.route_out[i] = a->route_out[i];
+  for (int i = 0; i < MDB_GEMM_MAX_PEERS; ++i) p.gather_src[i] = a->gather_src[i];
+  p.gather_dst = a->gather_dst;
+  p.gather_ready = a->gather_ready;
+  p.gather_chunk_bytes = a->gather_chunk_bytes;
+  p.gather_world = a->gather_world;
+  p.gather_rank = a->gather_rank;
+  p.gather_operand = a->gather_operand;
+  p.gather_chunk_rows = a->gather_chunk_rows > 0 ? a->gather_chunk_rows : 1;
+  p.reduce_rows_per_owner = a->reduce_rows_per_owner;
+  if (a->gather_world > 1) {
+    if (a->gather_ready == nullptr || a->gather_dst == nullptr || (a->gather_chunk_bytes & 15) || a->conv_taps > 0) return -8;
+    cudaError_t e = cudaMemsetAsync(a->gather_ready, 0, sizeof(int) * MDB_GEMM_MAX_PEERS, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  if (a->reduce_rows_per_owner > 0 && !a->out_fp32) return -9;
   p.conv_taps = a->conv_taps;
   if (a->conv_taps > 0) {
     if (a->conv_cin % k_elems) return -7;

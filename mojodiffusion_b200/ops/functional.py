@@ -36,10 +36,11 @@ def _flat2d(x: torch.Tensor) -> torch.Tensor:
 
 def _gemm(As, Bs, bias=None, residual=None, gate=None, rows_per_group=1, act=0, pair_offset=0, act_on_second=0,
           out=None, out_fp32=False, a_mn=False, b_mn=False, row_scale=None, col_scale=None, alpha=1.0,
-          accumulate=False, bn=0, prof=None, route_ptrs=(), route_cfg=()):
+          accumulate=False, bn=0, prof=None, route_ptrs=(), route_cfg=(), gather_ptrs=(), gather_cfg=(),
+          gather_dst=None, gather_ready=None):
     return _ops().gemm(list(As), list(Bs), bias, residual, gate, rows_per_group, act, pair_offset, act_on_second, out,
                        out_fp32, a_mn, b_mn, row_scale, col_scale, alpha, accumulate, bn, prof, list(route_ptrs),
-                       list(route_cfg))
+                       list(route_cfg), list(gather_ptrs), list(gather_cfg), gather_dst, gather_ready)
 
 
 # --------------------------------------------------------------------------------------------

@@ -51,7 +51,7 @@ def test_gemm_tile_variants(bn):
     M, N, K = 384, 768, 320
     x, w = _rand(M, K, seed=3), _rand(N, K, scale=1 / math.sqrt(K), seed=4)
     out = torch.ops.mdb200.gemm([x], [w], None, None, None, 1, 0, 0, 0, None, False, False, False, None, None, 1.0,
-                                False, bn, None, [], [])
+                                False, bn, None, [], [], [], [], None, None)
     _check(out, ref.linear(x, w, out_dtype=torch.float32), name=f"bn{bn}")
 
 
@@ -95,14 +95,14 @@ def test_gemm_backward_majors():
     w = _rand(N, K, scale=0.05, seed=19)
     dy = _rand(M, N, seed=20)
     dx = torch.ops.mdb200.gemm([dy], [w], None, None, None, 1, 0, 0, 0, None, False, False, True, None, None, 1.0,
-                               False, 0, None, [], [])
+                               False, 0, None, [], [], [], [], None, None)
     _check(dx, dy.float() @ w.float(), name="dx (B MN-major)")
     dw = torch.ops.mdb200.gemm([dy], [x], None, None, None, 1, 0, 0, 0, None, False, True, True, None, None, 1.0,
-                               False, 0, None, [], [])
+                               False, 0, None, [], [], [], [], None, None)
     _check(dw, dy.float().t() @ x.float(), name="dW (A,B MN-major)")
     for bn in (64, 128, 256):
         dx = torch.ops.mdb200.gemm([dy], [w], None, None, None, 1, 0, 0, 0, None, False, False, True, None, None, 1.0,
-                                   False, bn, None, [], [])
+                                   False, bn, None, [], [], [], [], None, None)
         _check(dx, dy.float() @ w.float(), name=f"dx bn{bn}")
 
 
