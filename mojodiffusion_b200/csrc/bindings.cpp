@@ -602,6 +602,13 @@ void flag_wait(const Tensor& my_flags, int64_t slot, int64_t world, int64_t valu
                          cur_stream()),
            "flag_wait");
 }
+void peer_gather(std::vector<int64_t> src_ptrs, Tensor dst, int64_t chunk_bytes, int64_t rank, bool copy_local) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  MdbPeerTable s = peer_table(src_ptrs);
+  TORCH_CHECK(dst.is_contiguous() && dst.numel() * dst.element_size() >= chunk_bytes * (int64_t)src_ptrs.size(), "peer_gather: dst too small");
+  check_rc(mdb_peer_gather(&s, dst.data_ptr(), chunk_bytes, (int)rank, (int)src_ptrs.size(), copy_local, cur_stream()),
+           "peer_gather");
+}
 void dp_reduce_shard(std::vector<int64_t> grad_ptrs, int64_t grads_mc, const Tensor& my_flags, int64_t ready_slot,
                      int64_t epoch, int64_t lo, int64_t hi, Tensor red, Tensor sumsq) {
   c10::cuda::CUDAGuard guard(red.device());
@@ -682,6 +689,7 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("ema_multi", &ema_multi);
   m.def("flag_signal", &flag_signal);
   m.def("flag_wait", &flag_wait);
+  m.def("peer_gather", &peer_gather);
   m.def("dp_reduce_shard", &dp_reduce_shard);
   m.def("publish_scalar", &publish_scalar);
   m.def("dp_adamw_shard", &dp_adamw_shard);

@@ -21,6 +21,10 @@ int mdb_flag_signal(const MdbPeerTable* flags, int slot, int rank, int world, in
                     cudaStream_t st);
 int mdb_flag_wait(const int* my_flags, int slot, int world, int value, int* counters, int* status, cudaStream_t st);
 
+// all-gather by peer loads into dst = [world][chunk_bytes]
+int mdb_peer_gather(const MdbPeerTable* src, void* dst, long long chunk_bytes, int rank, int world, int copy_local,
+                    cudaStream_t st);
+
 int mdb_dp_reduce_shard(const MdbPeerTable* grads, const void* grads_mc, const int* my_flags, int ready_slot, int epoch,
                         int world, long long lo, long long hi, float* red, float* sumsq, int* status, cudaStream_t st);
 int mdb_publish_scalar(const MdbPeerTable* scalars, const MdbPeerTable* flags, const float* value, int slot, int rank,

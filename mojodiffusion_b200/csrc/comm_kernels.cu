@@ -229,6 +229,19 @@ dp_adamw_shard_kernel(MdbPeerTable params, void* params_mc, MdbPeerTable flags, 
   }
 }
 
+// plain all-gather by peer loads: dst = [world chunks]; chunk r comes from src.p[r] (rank r's shard); the local chunk
+// is copied too when `copy_local` (otherwise it is expected to be in place already)
+__global__ void __launch_bounds__(256)
+peer_gather_kernel(MdbPeerTable src, uint4* __restrict__ dst, long long chunk_vec, int rank, int world, int copy_local) {
+  for (int i = copy_local ? 0 : 1; i < world; ++i) {
+    const int c = (rank + i) % world;
+    const uint4* s = reinterpret_cast<const uint4*>(src.p[c]);
+    uint4* d = dst + c * chunk_vec;
+    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < chunk_vec; v += (long long)gridDim.x * blockDim.x)
+      d[v] = s[v];
+  }
+}
+
 static inline int clamp_grid(long long n, int threads) {
   long long b = (n + threads - 1) / threads;
   const long long cap = 148ll * 4;
@@ -249,6 +262,14 @@ extern "C" int mdb_flag_wait(const int* my_flags, int slot, int world, int value
                              cudaStream_t st) {
   if (slot < 0 || slot >= MDB_FLAG_SLOTS || (value <= 0 && counters == nullptr)) return -1;
   flag_wait_kernel<<<1, 32, 0, st>>>(my_flags, slot, world, value, counters, status);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_peer_gather(const MdbPeerTable* src, void* dst, long long chunk_bytes, int rank, int world,
+                               int copy_local, cudaStream_t st) {
+  if (chunk_bytes & 15) return -1;
+  if (chunk_bytes == 0) return 0;
+  peer_gather_kernel<<<clamp_grid(chunk_bytes / 16, 256), 256, 0, st>>>(*src, reinterpret_cast<uint4*>(dst),
+                                                                        chunk_bytes / 16, rank, world, copy_local);
   return (int)cudaGetLastError();
 }
 extern "C" int mdb_dp_reduce_shard(const MdbPeerTable* grads, const void* grads_mc, const int* my_flags, int ready_slot,

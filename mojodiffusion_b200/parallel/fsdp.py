@@ -1,0 +1,218 @@
+"""Fully-sharded data parallel linears for full finetuning, with the collectives fused into the GEMMs.
+
+Every ``FSDPLinear`` keeps only 1/N of its weight rows: the bf16 shard lives in symmetric memory (peers read it),
+the fp32 master copy and the AdamW moments exist for the shard only.
+
+* forward  : ``y = x @ W^T`` where W is re-assembled INSIDE the consuming GEMM: warp 6 of every CTA pulls its slice of
+             each remote weight shard over NVLink into a transient full-weight buffer while the tensor core already
+             works on the output columns of the local shard (parameter all-gather fused into the first consumer).
+* backward : ``dx = dy @ W`` from the gathered buffer (re-gathered by peer loads if another layer has reused it);
+             ``dW = dy^T x`` whose fp32 tiles the GEMM epilogue adds straight into the OWNER's gradient shard
+             (``red.global.add`` on peer memory: gradient reduce-scatter fused into the producing GEMM).
+* step     : after one flag barrier, a single multi-tensor AdamW launch updates every local master shard and writes
+             the new bf16 shard back into symmetric memory (fp32 masters, bf16 shadows: csrc/optim.cu).
+
+The reference has no FSDP; its closest analogue keeps fp32 masters and 8-bit moments on the host
+(serenitymojo/training/full_finetune_zimage.mojo:1-36). ``mode="nccl"`` is the all_gather / reduce_scatter baseline.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..ops import native
+from ..ops.functional import _flat2d, _gemm
+from .symm import SymmetricBuffer
+
+SLOT_BWD_DONE, SLOT_STEP_DONE = 6, 7
+_FLAG_BYTES = 512
+
+
+class FSDPContext:
+    """Owns the symmetric arena (weight shards + gradient shards of all layers), the transient gather buffer and the
+    flags. Layers register themselves; ``finalize()`` allocates."""
+
+    def __init__(self, group=None, mode: str = "fused", device=None):
+        self.group, self.mode = group, mode
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.layers: List["FSDPLinear"] = []
+        self.symm: Optional[SymmetricBuffer] = None
+        self.gathered_owner = None
+        self.step_count = 0
+
+    def register(self, layer: "FSDPLinear"):
+        self.layers.append(layer)
+
+    def finalize(self):
+        off = _FLAG_BYTES
+        for l in self.layers:
+            l.off_w = off
+            off += (l.rows_local * l.in_features * 2 + 255) // 256 * 256
+            l.off_g = off
+            off += (l.rows_local * l.in_features * 4 + 255) // 256 * 256
+        native.load(True)
+        if self.mode == "fused" and self.world > 1:
+            self.symm = SymmetricBuffer.create(off, self.group, self.device, False)
+            arena = self.symm.local
+        else:
+            arena = torch.zeros(off, dtype=torch.uint8, device=self.device)
+        self.arena = arena
+        self.flags = arena[:256].view(torch.int32)
+        self.counters = torch.zeros(16, dtype=torch.int32, device=self.device)
+        self.ready = torch.zeros(8, dtype=torch.int32, device=self.device)
+        big = max(l.out_features * l.in_features for l in self.layers)
+        self.wbuf = torch.empty(big, dtype=torch.bfloat16, device=self.device)
+        for l in self.layers:
+            n = l.rows_local * l.in_features
+            l.w_shard = arena[l.off_w:l.off_w + n * 2].view(torch.bfloat16).view(l.rows_local, l.in_features)
+            l.g_shard = arena[l.off_g:l.off_g + n * 4].view(torch.float32).view(l.rows_local, l.in_features)
+            l.w_shard.copy_(l.master.to(torch.bfloat16))
+            l.g_shard.zero_()
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)
+        return self
+
+    # ---- flag barriers (stream ordered, no host sync) ----------------------------------------------------
+    def barrier(self, slot: int):
+        if self.world == 1:
+            return
+        if self.symm is not None:
+            o = native.ops()
+            o.flag_signal(self.symm.ptrs_at(0), slot, self.rank, 0, self.flags, self.counters)
+            o.flag_wait(self.flags, slot, self.world, 0, self.counters)
+        else:
+            dist.barrier(self.group)
+
+    def full_weight(self, layer: "FSDPLinear") -> torch.Tensor:
+        return self.wbuf[:layer.out_features * layer.in_features].view(layer.out_features, layer.in_features)
+
+    def ensure_gathered(self, layer: "FSDPLinear") -> torch.Tensor:
+        """Full weight in the transient buffer (plain peer-load all-gather; used by backward when needed)."""
+        W = self.full_weight(layer)
+        if self.gathered_owner is layer:
+            return W
+        if self.world == 1:
+            W.copy_(layer.w_shard)
+        elif self.symm is not None:
+            native.ops().peer_gather(self.symm.ptrs_at(layer.off_w), W, layer.rows_local * layer.in_features * 2,
+                                     self.rank, True)
+        else:
+            dist.all_gather_into_tensor(W, layer.w_shard.contiguous(), group=self.group)
+        self.gathered_owner = layer
+        return W
+
+    # ---- optimizer ---------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, grad_scale: Optional[float] = None):
+        """AdamW on every local master shard (one launch), bf16 shards refreshed for the next all-gather."""
+        self.barrier(SLOT_BWD_DONE)                       # every rank's dW tiles have been added into my shards
+        self.step_count += 1
+        scale = (1.0 / self.world) if grad_scale is None else grad_scale
+        from ..training.optim import CHUNK
+        if getattr(self, "_table", None) is None:
+            rows, chunks = [], []
+            for i, l in enumerate(self.layers):
+                n = l.master.numel()
+                rows.append([l.master.data_ptr(), l.g_shard.data_ptr(), l.m.data_ptr(), l.v.data_ptr(), l.w_shard.data_ptr(), n])
+                chunks += [[i, c] for c in range((n + CHUNK - 1) // CHUNK)]
+            self._table = (torch.tensor(rows, dtype=torch.int64).to(self.device),
+                           torch.tensor(chunks, dtype=torch.int32).to(self.device))
+        table, chunks = self._table
+        native.ops().adamw_multi(table, chunks, CHUNK, False, False, False, lr, betas[0], betas[1], eps, weight_decay,
+                                 self.step_count, scale, None, 0.0, 0, False)
+        for l in self.layers:
+            l.g_shard.zero_()
+        self.gathered_owner = None
+        self.barrier(SLOT_STEP_DONE)                      # new shards visible everywhere before the next gather
+
+
+class _FSDPLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x2, layer):
+        c = layer.ctx
+        W = c.full_weight(layer)
+        if c.world > 1 and c.symm is not None:
+            rl = layer.rows_local
+            W[c.rank * rl:(c.rank + 1) * rl].copy_(layer.w_shard)
+            y = _gemm([x2], [W], bias=layer.bias, gather_ptrs=c.symm.ptrs_at(layer.off_w),
+                      gather_cfg=[c.rank, 1, rl, rl * layer.in_features * 2], gather_dst=W, gather_ready=c.ready)
+            c.gathered_owner = layer
+        else:
+            W = c.ensure_gathered(layer)
+            y = _gemm([x2], [W], bias=layer.bias)
+        ctx.layer = layer
+        ctx.save_for_backward(x2)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        layer = ctx.layer
+        c = layer.ctx
+        dy = _flat2d(dy)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            W = c.ensure_gathered(layer)
+            dx = _gemm([dy], [W], b_mn=True)
+        # dW = dy^T x, reduce-scattered over ranks into the owners' fp32 gradient shards
+        if c.world > 1 and c.symm is not None:
+            _gemm([dy], [x2], a_mn=True, b_mn=True, out_fp32=True, route_ptrs=c.symm.ptrs_at(layer.off_g),
+                  route_cfg=[layer.rows_local, layer.in_features])
+        else:
+            dw = _gemm([dy], [x2], a_mn=True, b_mn=True, out_fp32=True)
+            if c.world > 1:
+                part = torch.empty_like(layer.g_shard)
+                dist.reduce_scatter_tensor(part, dw.contiguous(), group=c.group)
+                layer.g_shard += part
+            else:
+                layer.g_shard += dw
+        if layer.bias is not None and layer.bias.requires_grad:
+            g = dy.float().sum(0)
+            layer.bias.grad = g.to(layer.bias.dtype) if layer.bias.grad is None else layer.bias.grad + g.to(layer.bias.dtype)
+        return dx, None
+
+
+class FSDPLinear(nn.Module):
+    def __init__(self, ctx: FSDPContext, in_features: int, out_features: int, bias: bool = True, full_weight=None,
+                 seed: int = 0):
+        super().__init__()
+        assert out_features % ctx.world == 0 and in_features % 8 == 0
+        self.ctx = ctx
+        self.in_features, self.out_features = in_features, out_features
+        self.rows_local = out_features // ctx.world
+        r = ctx.rank
+        if full_weight is None:
+            g = torch.Generator().manual_seed(seed)
+            full_weight = torch.randn(out_features, in_features, generator=g) / math.sqrt(in_features)
+        shard = full_weight[r * self.rows_local:(r + 1) * self.rows_local].float().to(ctx.device)
+        self.master = shard.contiguous()                                  # fp32 master (shard)
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=torch.bfloat16, device=ctx.device)) if bias else None
+        self.w_shard = self.g_shard = None
+        self.off_w = self.off_g = 0
+        ctx.register(self)
+
+    def forward(self, x):
+        lead = x.shape[:-1]
+        x2 = _flat2d(x)
+        if not x2.requires_grad and torch.is_grad_enabled():
+            x2 = x2.detach().requires_grad_(True)            # dW must be produced even for the first layer
+        y = _FSDPLinearFn.apply(x2, self)
+        return y.reshape(*lead, self.out_features)
+
+    def full_master(self) -> torch.Tensor:
+        """All-gather of the fp32 master shards (checkpointing)."""
+        if self.ctx.world == 1:
+            return self.master.clone()
+        parts = [torch.empty_like(self.master) for _ in range(self.ctx.world)]
+        dist.all_gather(parts, self.master, group=self.ctx.group)
+        return torch.cat(parts, 0)

@@ -63,3 +63,74 @@ def test_tp_mlp_matches_single_gpu(tmp_path):
     world = 2 if torch.cuda.device_count() < 4 else 4
     mp.spawn(_tp_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert (tmp_path / "ok").exists()
+
+
+def _fsdp_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from mojodiffusion_b200.ops import native
+    from mojodiffusion_b200.parallel.fsdp import FSDPContext, FSDPLinear
+    dev = torch.device("cuda", rank)
+    g = torch.Generator().manual_seed(0)
+    D, F, rows = 512, 1024, 384
+    w1 = torch.randn(F, D, generator=g) * 0.04
+    w2 = torch.randn(D, F, generator=g) * 0.03
+    xs = [torch.randn(rows, D, generator=g).bfloat16() for _ in range(world)]     # one micro-batch per rank
+    ts = [torch.randn(rows, D, generator=g) for _ in range(world)]
+
+    # single-process reference: fp32 masters, bf16 compute, mean gradient over the N micro-batches, AdamW
+    W1, W2 = w1.clone().to(dev), w2.clone().to(dev)
+    m1, v1, m2, v2 = [torch.zeros_like(t) for t in (W1, W1, W2, W2)]
+    lr, steps = 1e-3, 3
+    for t in range(steps):
+        g1, g2 = torch.zeros_like(W1), torch.zeros_like(W2)
+        for x, tgt in zip(xs, ts):
+            a = W1.bfloat16().float().requires_grad_(True)
+            b = W2.bfloat16().float().requires_grad_(True)
+            xx = x.to(dev).float()
+            h = torch.nn.functional.gelu(xx @ a.t(), approximate="tanh")
+            loss = ((h @ b.t()) - tgt.to(dev)).pow(2).mean()
+            loss.backward()
+            g1 += a.grad / world
+            g2 += b.grad / world
+        for W, gg, m, v in ((W1, g1, m1, v1), (W2, g2, m2, v2)):
+            W.mul_(1 - lr * 0.01)
+            m.mul_(0.9).add_(gg, alpha=0.1)
+            v.mul_(0.999).addcmul_(gg, gg, value=0.001)
+            W.sub_((lr / (1 - 0.9 ** (t + 1))) * m / (v.sqrt() / (1 - 0.999 ** (t + 1)) ** 0.5 + 1e-8))
+
+    for mode in ("nccl", "fused"):
+        ctx = FSDPContext(mode=mode, device=dev)
+        l1 = FSDPLinear(ctx, D, F, bias=False, full_weight=w1)
+        l2 = FSDPLinear(ctx, F, D, bias=False, full_weight=w2)
+        ctx.finalize()
+        import mojodiffusion_b200.ops as O
+        for t in range(steps):
+            x = xs[rank].to(dev)
+            h = O.activation(l1(x), "gelu_tanh")
+            out = l2(h)
+            loss = (out.float() - ts[rank].to(dev)).pow(2).mean()
+            loss.backward()
+            ctx.step(lr=lr, weight_decay=0.01)
+        torch.cuda.synchronize()
+        native.check_status()
+        for lay, W in ((l1, W1), (l2, W2)):
+            got = lay.full_master()
+            err = float((got - W).abs().max())
+            upd = float((W - (w1 if lay is l1 else w2).to(dev)).abs().max())
+            assert err <= 0.15 * upd + 1e-5, f"rank {rank} mode {mode}: err {err} vs update {upd}"
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        open(os.path.join(out_dir, "ok2"), "w").write("ok")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fsdp_linear_training_matches_reference(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    mp.spawn(_fsdp_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert (tmp_path / "ok2").exists()
