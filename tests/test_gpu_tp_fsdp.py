@@ -119,9 +119,14 @@ def _fsdp_worker(rank, world, port, out_dir):
         native.check_status()
         for lay, W in ((l1, W1), (l2, W2)):
             got = lay.full_master()
-            err = float((got - W).abs().max())
-            upd = float((W - (w1 if lay is l1 else w2).to(dev)).abs().max())
-            assert err <= 0.15 * upd + 1e-5, f"rank {rank} mode {mode}: err {err} vs update {upd}"
+            w0 = (w1 if lay is l1 else w2).to(dev)
+            du, dr = (got - w0).flatten(), (W - w0).flatten()
+            # Adam normalises every element's step to ~lr, so compare the update DIRECTION (bf16 gradient noise flips
+            # the sign of near-zero gradients) and the update size
+            cos = float(torch.dot(du, dr) / (du.norm() * dr.norm() + 1e-30))
+            assert cos > 0.9, f"rank {rank} mode {mode}: update cosine {cos}"
+            assert abs(float(du.norm() / dr.norm()) - 1.0) < 0.1
+            assert float((got - W).abs().mean()) < 0.35 * float(dr.abs().mean())
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:
