@@ -621,6 +621,13 @@ extern "C" int mdb_make_tmap(void* out_map, const void* ptr, int elem_bytes, int
                              const int64_t* strides_bytes, const int* box, int swizzle128) {
   auto fn = mdb::get_encode_fn();
   if (!fn) return -1;
+  // The encode call is a driver-API entry and needs a current context. A thread that has not made a runtime call yet
+  // (an autograd worker whose first node is one of our backward kernels) has none: bind the primary context once.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t gdim[5];
   cuuint64_t gstr[5];
   cuuint32_t bdim[5];
