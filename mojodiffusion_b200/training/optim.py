@@ -25,9 +25,12 @@ CHUNK = 4096 * 4
 class FusedAdamW:
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-4, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, moment_dtype=torch.float32, stochastic_rounding: bool = False,
-                 max_grad_norm: float = 0.0, seed: int = 0):
+                 max_grad_norm: float = 0.0, seed: int = 0, master_weights: bool = False):
         self.params: List[torch.nn.Parameter] = [p for p in params]
         assert self.params, "no parameters"
+        # full fine-tune: fp32 masters are what the kernel updates; the bf16 model tensors are rewritten from them
+        # in the same pass (the table's shadow slot)
+        self.masters = [p.detach().float().clone() for p in self.params] if master_weights else None
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.moment_dtype = moment_dtype
         self.stochastic_rounding = stochastic_rounding
@@ -69,7 +72,11 @@ class FusedAdamW:
         rows, chunks = [], []
         for i, (p, g) in enumerate(zip(self.params, grads)):
             assert p.is_contiguous() and g.is_contiguous()
-            rows.append([p.data_ptr(), g.data_ptr(), self.m[i].data_ptr(), self.v[i].data_ptr(), 0, p.numel()])
+            if self.masters is not None:
+                rows.append([self.masters[i].data_ptr(), g.data_ptr(), self.m[i].data_ptr(), self.v[i].data_ptr(),
+                             p.data_ptr() if p.dtype == torch.bfloat16 else 0, p.numel()])
+            else:
+                rows.append([p.data_ptr(), g.data_ptr(), self.m[i].data_ptr(), self.v[i].data_ptr(), 0, p.numel()])
             for c in range((p.numel() + CHUNK - 1) // CHUNK):
                 chunks.append([i, c])
         table = torch.tensor(rows, dtype=torch.int64).to(dev)
@@ -95,7 +102,7 @@ class FusedAdamW:
             if self.max_grad_norm > 0:
                 norm_sq = o.sumsq_multi(table, chunks, CHUNK, g_bf16)
                 self.last_grad_norm = norm_sq
-            o.adamw_multi(table, chunks, CHUNK, p0.dtype == torch.bfloat16, g_bf16,
+            o.adamw_multi(table, chunks, CHUNK, p0.dtype == torch.bfloat16 and self.masters is None, g_bf16,
                           self.moment_dtype == torch.bfloat16, lr, b1, b2, self.eps, self.weight_decay,
                           self.step_count, grad_scale, norm_sq, self.max_grad_norm,
                           (self.seed * 1000003 + self.step_count) & 0x7FFFFFFF, self.stochastic_rounding)
@@ -107,8 +114,11 @@ class FusedAdamW:
             self.last_grad_norm = torch.tensor(total * total / (grad_scale * grad_scale) if grad_scale else 0.0)
             clip = min(1.0, self.max_grad_norm / (total + 1e-6))
         for i, (p, g) in enumerate(zip(self.params, grads)):
-            pn, mn, vn = ref.adamw_step(p, g, self.m[i], self.v[i], lr, b1, b2, self.eps, self.weight_decay,
+            src = p if self.masters is None else self.masters[i]
+            pn, mn, vn = ref.adamw_step(src, g, self.m[i], self.v[i], lr, b1, b2, self.eps, self.weight_decay,
                                         self.step_count, grad_scale * clip)
+            if self.masters is not None:
+                self.masters[i].copy_(pn)
             p.copy_(pn.to(p.dtype))
             self.m[i].copy_(mn.to(self.m[i].dtype))
             self.v[i].copy_(vn.to(self.v[i].dtype))
@@ -121,3 +131,16 @@ class FusedAdamW:
 
     def state_dict(self):
         return {"step": self.step_count, "m": self.m, "v": self.v}
+
+
+def build_tensor_table(shadows, params):
+    """Device table for the multi-tensor EMA kernel: one row [param, 0, shadow, 0, 0, numel] per tensor plus the
+    (tensor, chunk) work list."""
+    rows, chunks = [], []
+    for i, (s_, p_) in enumerate(zip(shadows, params)):
+        assert s_.is_contiguous() and p_.is_contiguous()
+        rows.append([p_.data_ptr(), 0, s_.data_ptr(), 0, 0, p_.numel()])
+        for c in range((p_.numel() + CHUNK - 1) // CHUNK):
+            chunks.append([i, c])
+    dev = params[0].device
+    return torch.tensor(rows, dtype=torch.int64).to(dev), torch.tensor(chunks, dtype=torch.int32).to(dev)
