@@ -168,3 +168,59 @@ extern "C" int mdb_avgpool2x(const void* x, void* y, int N, int H, int W, int C,
   avgpool2x_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, N, H, W, C);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// GroupNorm with a built-in workspace (see the declaration for the contract a caller relies on).
+// The statistics buffer is a file-scope device array, so the address is fixed for the life of the module on each device
+// and the call has nothing to allocate or free.
+// ---------------------------------------------------------------------------------------------------------------
+#include <cstdio>
+
+static __device__ __align__(256) float g_group_norm_static_stats[2 * MDB_GROUP_NORM_STATIC_MAX_GROUPS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_stats_addr[kMaxDevices];   // per device; written once, always with the same value for that device
+
+// Address of the array on the current device. cudaGetSymbolAddress answers for whichever device is current, so the
+// cache is indexed by device ordinal. Two threads that get here together store the same pointer.
+int static_stats_ptr(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return -21;
+  float* p = g_static_stats_addr[dev];
+  if (p == nullptr) {
+    void* sym = nullptr;
+    e = cudaGetSymbolAddress(&sym, g_group_norm_static_stats);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    p = static_cast<float*>(sym);
+    g_static_stats_addr[dev] = p;
+  }
+  *out = p;
+  return 0;
+}
+}  // namespace
+
+extern "C" int mdb_group_norm_static_ws(const void* x, void* y, const void* w, const void* b, int N, int HW, int C,
+                                        int G, float eps, int act, cudaStream_t st) {
+  if (G <= 0 || C <= 0 || C % 8 || C % G) return -1;
+  if (N <= 0 || HW <= 0) return 0;
+  const long long groups = static_cast<long long>(N) * G;
+  if (groups > MDB_GROUP_NORM_STATIC_MAX_GROUPS) {
+    fprintf(stderr,
+            "mdb_group_norm_static_ws: N * G = %lld exceeds the built-in workspace of %d (sample, group) pairs; "
+            "split the batch or call mdb_group_norm with a buffer of your own\n",
+            groups, MDB_GROUP_NORM_STATIC_MAX_GROUPS);
+    return MDB_ERR_STATIC_WS_TOO_SMALL;
+  }
+  float* stats = nullptr;
+  const int rc = static_stats_ptr(&stats);
+  if (rc) return rc;
+  // same two launches as mdb_group_norm; the first fills stats[0 .. 2 * N * G), the second reads exactly that range
+  group_norm_stats_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, stats, HW, C, G, eps);
+  const long long tv = static_cast<long long>(N) * HW * (C / 8);
+  group_norm_apply_kernel<<<grid_for(tv, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, stats, (const bf16*)w,
+                                                             (const bf16*)b, tv, HW, C, G, act);
+  return (int)cudaGetLastError();
+}

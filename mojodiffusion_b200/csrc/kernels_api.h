@@ -73,6 +73,30 @@ int mdb_group_norm(const void* x, void* y, float* stats, const void* w, const vo
 int mdb_upsample2x(const void* x, void* y, int N, int H, int W, int C, cudaStream_t st);
 int mdb_avgpool2x(const void* x, void* y, int N, int H, int W, int C, cudaStream_t st);
 
+// GroupNorm (+ optional SiLU) that brings its own workspace. This entry point has no counterpart in the reference
+// project; it exists for hosts that must not allocate while they run:
+//   * a C/C++ or ctypes host that drives these kernels without a tensor library, so there is no caching allocator
+//     to ask for the small per-(sample, group) statistics buffer that mdb_group_norm needs;
+//   * a serving process that sized all of its device memory up front and wants a call that cannot fail, fragment
+//     or synchronise the device by asking the CUDA allocator for more.
+// The (mean, rstd) pairs live in a fixed array inside the library's device image:
+// MDB_GROUP_NORM_STATIC_MAX_GROUPS pairs (64 KiB) per device. N * G beyond that is refused with
+// MDB_ERR_STATIC_WS_TOO_SMALL and a line on stderr; nothing is launched in that case.
+// The call itself never calls cudaMalloc, cudaFree or any routine that allocates.
+// What the caller has to know:
+//   * The first call on each device looks up the array's address (and may make the driver load the module). Make that
+//     first call once, on an ordinary stream, before starting any stream capture.
+//   * Every call on a device uses the same array. Calls that overlap in time (two streams, two host threads) race on
+//     it and give wrong results; order them on one stream or with events.
+//   * Nothing in the array has to start at zero: each call first writes every pair that it later reads, so whatever an
+//     earlier call left behind is never seen.
+// x, y: bf16 NHWC [N, H*W, C]; w, b: bf16 [C] or NULL; C % 8 == 0 and C % G == 0; act: 0 none, 2 SiLU (the activation codes used across this library).
+// Returns 0, a negative argument error, or a positive cudaError_t value.
+#define MDB_GROUP_NORM_STATIC_MAX_GROUPS 8192
+#define MDB_ERR_STATIC_WS_TOO_SMALL (-20)
+int mdb_group_norm_static_ws(const void* x, void* y, const void* w, const void* b, int N, int HW, int C, int G,
+                             float eps, int act, cudaStream_t st);
+
 // ---- optim.cu
 int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
                     int g_bf16, int m_bf16, float lr, float beta1, float beta2, float eps, float wd, int step,
