@@ -307,3 +307,31 @@ def test_fused_adamw_matches_torch():
             topt.step()
         for p, r in zip(ps, rs):
             _check(p.detach(), r.detach(), cos=0.9999, rel=2e-2 if pdt == torch.bfloat16 else 1e-4, name=f"adamw {pdt}")
+
+
+def test_adamw_master_weights_and_ema_kernel():
+    """Full fine-tune mode: fp32 masters are updated, bf16 model tensors rewritten from them in the same launch; the
+    multi-tensor EMA kernel equals shadow = d * shadow + (1 - d) * live."""
+    from mojodiffusion_b200.training.ema import EMA
+    from mojodiffusion_b200.training.optim import FusedAdamW
+    shapes = [(64, 300), (7,), (513, 33)]
+    ps = [torch.nn.Parameter(_rand(*s, seed=200 + i, dtype=torch.bfloat16)) for i, s in enumerate(shapes)]
+    rs = [torch.nn.Parameter(p.detach().float().clone()) for p in ps]
+    opt = FusedAdamW(ps, lr=1e-3, weight_decay=0.01, master_weights=True)
+    topt = torch.optim.AdamW(rs, lr=1e-3, weight_decay=0.01)
+    ema = EMA(ps, decay=0.9)
+    shadow_ref = [p.detach().float().clone() for p in ps]
+    for step in range(4):
+        for i, (p, r) in enumerate(zip(ps, rs)):
+            g = _rand(*p.shape, seed=300 + 10 * step + i, dtype=torch.bfloat16)
+            p.grad, r.grad = g.clone(), g.float().clone()
+        opt.step()
+        topt.step()
+        ema.update(step + 1)
+        for s, p in zip(shadow_ref, ps):
+            s.mul_(0.9).add_(p.detach().float(), alpha=0.1)
+    for p, r, m in zip(ps, rs, opt.masters):
+        _check(m, r.detach(), cos=0.999999, rel=1e-4, name="fp32 master")
+        assert torch.equal(p.detach(), m.bfloat16())             # the model tensor is the rounded master
+    for s, sr in zip(ema.shadow, shadow_ref):
+        _check(s, sr, cos=0.999999, rel=1e-5, name="ema")
