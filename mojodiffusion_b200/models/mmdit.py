@@ -245,6 +245,7 @@ class MMDiT(nn.Module):
         self.single_blocks = nn.ModuleList([SingleStreamBlock(cfg, dtype, device) for _ in range(cfg.depth_single)])
         self.final_layer = LastLayer(D, cfg.out_channels or cfg.in_channels, dtype, device)
         self.gradient_checkpointing = False
+        self.streamer = None          # offload.StreamedStack over double + single blocks (block-swap weights)
         self._rope_cache = {}
 
     # ---- positions ---------------------------------------------------------------------------
@@ -298,6 +299,17 @@ class MMDiT(nn.Module):
         vec = self.embed_vec(timesteps, y, guidance)
         vec_silu = ops.activation(vec, "silu")
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
+        st = self.streamer
+        if st is not None:
+            # streamed weights: block i's parameters are views of a device slot while it runs; under autograd each
+            # block is a recompute boundary (serenitymojo/models/flux/flux_stack_lora.mojo:1619-2019)
+            nd = len(self.double_blocks)
+            for i in range(nd):
+                img, txt = st.step(i, lambda b, im, tx, v: b(im, tx, v, cos, sin, sp), img, txt, vec_silu)
+            x = torch.cat((txt, img), dim=1)
+            for i in range(len(self.single_blocks)):
+                x = st.step(nd + i, lambda b, h, v: b(h, v, cos, sin, sp), x, vec_silu)
+            return self.final_layer(x[:, S_txt:], vec_silu)
         for blk in self.double_blocks:
             if ckpt:
                 img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, vec_silu, cos, sin, use_reentrant=False)
@@ -311,6 +323,26 @@ class MMDiT(nn.Module):
                 x = blk(x, vec_silu, cos, sin, sp)
         x = x[:, S_txt:]
         return self.final_layer(x, vec_silu)
+
+    def enable_block_swap(self, device, resident_budget_bytes: int = 0, slot_count: int = 2, pin: bool = True):
+        """Moves the transformer blocks' weights into a pinned host store and streams them through ``slot_count``
+        device slots; the first blocks that fit ``resident_budget_bytes`` stay on the device. Adapter parameters
+        (the ``slots`` of a linear) stay with the module. Returns the loader (telemetry lives there)."""
+        from ..offload import BlockSwapLoader, OffloadConfig, PinnedBlockStore, StreamedStack
+        from ..offload.plan import flux_plan
+        plan = flux_plan(len(self.double_blocks), len(self.single_blocks), OffloadConfig(slot_count, min(1, slot_count - 1)))
+        blocks = list(self.double_blocks) + list(self.single_blocks)
+        tensors = {}
+        for spec, blk in zip(plan.blocks, blocks):
+            for n, p in blk.named_parameters():
+                if ".slots." not in n:
+                    tensors[spec.prefix + n] = p.detach()
+        loader = BlockSwapLoader(PinnedBlockStore(plan, tensors, pin=pin), device)
+        if resident_budget_bytes > 0:
+            loader.pin_residents(resident_budget_bytes)
+        self.streamer = StreamedStack(blocks, loader)
+        self.streamer.detach_weights()
+        return loader
 
     # ---- initialisation ------------------------------------------------------------------------------
     @torch.no_grad()

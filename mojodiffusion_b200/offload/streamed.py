@@ -57,11 +57,18 @@ class StreamedStack:
             state = out if isinstance(out, tuple) else (out,)
         return state if len(state) > 1 else state[0]
 
+    def step(self, i: int, call: Callable, *inputs):
+        """One block, ``call(block, *inputs)``: plain streamed run without autograd, recompute boundary with it.
+        Tensors that need gradients must be passed in ``inputs`` (not captured by ``call``)."""
+        if not torch.is_grad_enabled():
+            return self.run_block(i, call, *inputs)
+        extra = [p for p in self.blocks[i].parameters() if p.requires_grad]
+        return _StreamedBlockFn.apply(self, i, call, len(inputs), *inputs, *extra)
+
     def forward_train(self, call: Callable, *state):
         """Training: every block is a recompute boundary (see module docstring)."""
         for i in range(len(self.blocks)):
-            extra = [p for p in self.blocks[i].parameters() if p.requires_grad]
-            out = _StreamedBlockFn.apply(self, i, call, len(state), *state, *extra)
+            out = self.step(i, call, *state)
             state = out if isinstance(out, tuple) else (out,)
         return state if len(state) > 1 else state[0]
 
@@ -80,7 +87,7 @@ class _StreamedBlockFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         stack, i = ctx.stack, ctx.i
-        state = [s.detach().requires_grad_(s.is_floating_point()) for s in ctx.saved_tensors]
+        state = [s.detach().requires_grad_(need) for s, need in zip(ctx.saved_tensors, ctx.needs)]
         extra = [p for p in stack.blocks[i].parameters() if p.requires_grad]
         with torch.enable_grad():
             out = stack.run_block(i, ctx.call, *state, reverse=True)
