@@ -114,5 +114,31 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB
 
 
+SERVE = PKG / "serve"
+
+
+def build_control_plane(force: bool = False):
+    """Compile the serving control plane (``serve/control_plane/*.cpp``, C++17, no dependencies beyond libc/pthread)
+    into ``serve/bin/mdb-server`` and ``serve/bin/mdb-lower``. Returns the two paths."""
+    src = SERVE / "control_plane"
+    out_dir = SERVE / "bin"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    headers = sorted(src.glob("*.hpp"))
+    outs = []
+    for name, main in (("mdb-server", "server.cpp"), ("mdb-lower", "lower_main.cpp")):
+        out = out_dir / name
+        tag = _hash([src / main, *headers], "c++17 O2")
+        stamp = out_dir / f".{name}.stamp"
+        if not (out.exists() and stamp.exists() and stamp.read_text() == tag and not force):
+            cmd = ["g++", "-std=c++17", "-O2", "-pthread", "-o", str(out), str(src / main)]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"g++ failed for {main}:\n{r.stdout}\n{r.stderr}")
+            stamp.write_text(tag)
+        outs.append(out)
+    return outs
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    print(*build_control_plane(force="-f" in sys.argv))
