@@ -41,7 +41,17 @@ def _hash(paths, extra: str) -> str:
     return h.hexdigest()[:16]
 
 
+def _flags_for(src: Path):
+    """A source whose first line is ``// build: precise-math`` is compiled without fast-math and without
+    multiply-add contraction (bit-stable fp32 arithmetic for the image filters)."""
+    first = src.read_text().split("\n", 1)[0]
+    if "build: precise-math" in first:
+        return [f for f in NVCC_FLAGS if f != "--use_fast_math"] + ["-fmad=false"]
+    return NVCC_FLAGS
+
+
 def _compile_cu(src: Path, headers, verbose: bool) -> Path:
+    NVCC_FLAGS = _flags_for(src)
     tag = _hash([src, *headers], " ".join(NVCC_FLAGS))
     out = OBJ / f"{src.stem}.{tag}.o"
     if out.exists():

@@ -228,6 +228,25 @@ Tensor group_norm_nhwc(const Tensor& x, const optional<Tensor>& w, const optiona
            "group_norm");
   return y;
 }
+Tensor image_filter(int64_t op, const Tensor& img, const std::vector<double>& params, const optional<Tensor>& aux) {
+  TORCH_CHECK(img.is_cuda() && img.dim() == 3 && img.size(2) == 4 && img.is_contiguous() && img.scalar_type() == at::kFloat,
+              "image_filter: fp32 contiguous [H, W, 4] expected");
+  c10::cuda::CUDAGuard guard(img.device());
+  Tensor out = at::empty_like(img);
+  Tensor tmp;
+  if (op == 2) tmp = at::empty({4, img.size(0), img.size(1), 4}, img.options());
+  if (op == 6) tmp = at::empty({2, img.size(0), img.size(1), 4}, img.options());
+  std::vector<float> p(params.begin(), params.end());
+  const void* aux_ptr = nullptr;
+  if (aux.has_value()) {
+    TORCH_CHECK(aux->is_cuda() && aux->is_contiguous(), "image_filter: aux must be a contiguous device tensor");
+    aux_ptr = aux->data_ptr();
+  }
+  check_rc(mdb_image_filter((int)op, img.data_ptr<float>(), out.data_ptr<float>(), tmp.defined() ? tmp.data_ptr<float>() : nullptr,
+                            (int)img.size(0), (int)img.size(1), p.data(), (int)p.size(), aux_ptr, cur_stream()),
+           "image_filter");
+  return out;
+}
 Tensor upsample2x_nhwc(const Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "upsample2x_nhwc");
   c10::cuda::CUDAGuard guard(x.device());
@@ -664,6 +683,7 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("gemm", &gemm);
   m.def("conv2d_nhwc", &conv2d_nhwc);
   m.def("group_norm_nhwc", &group_norm_nhwc);
+  m.def("image_filter", &image_filter);
   m.def("upsample2x_nhwc", &upsample2x_nhwc);
   m.def("avgpool2x_nhwc", &avgpool2x_nhwc);
   m.def("attention_fwd", &attention_fwd);

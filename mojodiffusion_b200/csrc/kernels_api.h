@@ -131,6 +131,10 @@ typedef struct MdbAttnArgs {
 } MdbAttnArgs;
 int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st);
 
+// ---- shader_filters.cu: RGBA fp32 image filters (op codes and parameter layout documented at the definition)
+int mdb_image_filter(int op, const float* in, float* out, float* tmp, int H, int W, const float* params, int nparams,
+                     const void* aux, cudaStream_t st);
+
 // ---- attention_bwd_tcgen05.cu
 // delta: fp32 workspace [B, H, Sq] filled by the call (rowsum(dO o O)); lse from the forward.
 typedef struct MdbAttnBwdArgs {
