@@ -44,7 +44,7 @@ def test_streamed_bytes_equal_resident_bytes():
                 assert v.dtype == tensors[k].dtype and torch.equal(v, tensors[k]), k
             loader.mark_done(i)
     torch.cuda.synchronize()
-    assert loader.tel.hit_rate() > 0.9 and loader.tel.h2d_bytes > 0
+    assert loader.tel.await_misses == 1 and loader.tel.h2d_bytes > 0      # only the very first block was not prefetched
 
 
 def test_streamed_inference_and_lora_training_match_resident():
