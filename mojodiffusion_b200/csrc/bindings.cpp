@@ -160,7 +160,16 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
     g.gather_dst = gather_dst->data_ptr();
     g.gather_ready = gather_ready->data_ptr<int>();
   }
-  if (!route_ptrs.empty() && route_cfg.size() == 2) {
+  g.reduce_src_rank = -1;
+  if (!route_ptrs.empty() && route_cfg.size() == 3) {
+    // staged reduce-scatter epilogue: route_cfg = {rows_per_owner, ld_out, this rank}; bf16 rows go to slot `rank` of
+    // the owner's [world, rows_per_owner, ld_out] staging buffer
+    TORCH_CHECK(!out_fp32, "gemm: the staged reduce-scatter epilogue stores bf16");
+    for (size_t i = 0; i < route_ptrs.size(); ++i) g.route_out[i] = reinterpret_cast<void*>(route_ptrs[i]);
+    g.reduce_rows_per_owner = (int)route_cfg[0];
+    g.ld_out = (int)route_cfg[1];
+    g.reduce_src_rank = (int)route_cfg[2];
+  } else if (!route_ptrs.empty() && route_cfg.size() == 2) {
     // reduce-scatter epilogue: route_cfg = {rows_per_owner, ld_out}
     TORCH_CHECK(out_fp32, "gemm: reduce-scatter epilogue accumulates in fp32");
     for (size_t i = 0; i < route_ptrs.size(); ++i) g.route_out[i] = reinterpret_cast<void*>(route_ptrs[i]);
@@ -621,6 +630,36 @@ void flag_wait(const Tensor& my_flags, int64_t slot, int64_t world, int64_t valu
                          cur_stream()),
            "flag_wait");
 }
+void flag_barrier(std::vector<int64_t> flag_ptrs, const Tensor& my_flags, int64_t slot, int64_t rank, int64_t value,
+                  const optional<Tensor>& counters) {
+  c10::cuda::CUDAGuard guard(my_flags.device());
+  MdbPeerTable f = peer_table(flag_ptrs);
+  int* c = counters.has_value() && counters->defined() ? counters->data_ptr<int>() : nullptr;
+  check_rc(mdb_flag_barrier(&f, my_flags.data_ptr<int>(), (int)slot, (int)rank, (int)flag_ptrs.size(), (int)value, c,
+                            status_ptr(my_flags), cur_stream()),
+           "flag_barrier");
+}
+Tensor rs_finalize(std::vector<int64_t> flag_ptrs, const Tensor& my_flags, int64_t slot, int64_t epoch, int64_t rank,
+                   const Tensor& stage, const optional<Tensor>& bias, const optional<Tensor>& residual,
+                   const optional<Tensor>& gate, int64_t rows_per_group) {
+  TORCH_CHECK(stage.is_cuda() && stage.dim() == 3 && stage.is_contiguous() && stage.scalar_type() == at::kBFloat16,
+              "rs_finalize: stage must be bf16 [world, rows, D]");
+  TORCH_CHECK((int64_t)flag_ptrs.size() == stage.size(0), "rs_finalize: one staging slot per rank");
+  c10::cuda::CUDAGuard guard(stage.device());
+  MdbPeerTable f = peer_table(flag_ptrs);
+  Tensor out = at::empty({stage.size(1), stage.size(2)}, stage.options());
+  int64_t gate_stride = 0;
+  if (gate.has_value()) {
+    TORCH_CHECK(gate->dim() == 2 && gate->stride(1) == 1 && gate->size(1) == stage.size(2), "rs_finalize: gate [groups, D]");
+    gate_stride = gate->stride(0);
+  }
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->numel() == out.numel(), "rs_finalize: residual");
+  check_rc(mdb_rs_finalize(&f, my_flags.data_ptr<int>(), (int)slot, (int)epoch, (int)rank, (int)stage.size(0), stage.data_ptr(),
+                           stage.size(1), (int)stage.size(2), opt_ptr(bias), opt_ptr(residual), opt_ptr(gate),
+                           (int)rows_per_group, gate_stride, out.data_ptr(), status_ptr(stage), cur_stream()),
+           "rs_finalize");
+  return out;
+}
 void peer_gather(std::vector<int64_t> src_ptrs, Tensor dst, int64_t chunk_bytes, int64_t rank, bool copy_local) {
   c10::cuda::CUDAGuard guard(dst.device());
   MdbPeerTable s = peer_table(src_ptrs);
@@ -709,6 +748,8 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("ema_multi", &ema_multi);
   m.def("flag_signal", &flag_signal);
   m.def("flag_wait", &flag_wait);
+  m.def("flag_barrier", &flag_barrier);
+  m.def("rs_finalize", &rs_finalize);
   m.def("peer_gather", &peer_gather);
   m.def("dp_reduce_shard", &dp_reduce_shard);
   m.def("publish_scalar", &publish_scalar);

@@ -72,6 +72,17 @@ __global__ void flag_wait_kernel(const int* my_flags, int slot, int world, int v
   }
 }
 
+// signal, then wait, in one launch (an all-rank barrier on `slot`); epochs as in the two kernels above
+__global__ void flag_barrier_kernel(MdbPeerTable flags, const int* my_flags, int slot, int rank, int world, int value,
+                                    int* counters, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int v = value;
+    if (v <= 0) { v = ++counters[slot]; counters[MDB_FLAG_SLOTS + slot] = v; }
+    signal_all(flags, slot, rank, world, v);
+    wait_all(my_flags, slot, world, v, status, 100 + slot);
+  }
+}
+
 // block-wide: thread 0 waits, everyone learns the outcome
 __device__ __forceinline__ bool block_wait_all(const int* my_flags, int slot, int world, int value, int* status,
                                                int where) {
@@ -248,9 +259,75 @@ static inline int clamp_grid(long long n, int threads) {
   return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
+// Tail of a staged reduce-scatter: every rank has stored its bf16 partial rows into slot [src] of the row owner's staging
+// buffer stage[world][rows][D]. This kernel (1) tells all peers "my partials have landed" (block 0), (2) waits until all
+// peers said the same, (3) sums the slots in fp32 and applies bias / gate / residual: out = residual + gate * (sum + bias).
+__global__ void __launch_bounds__(256)
+rs_finalize_kernel(MdbPeerTable flags, const int* my_flags, int slot, int epoch, int rank, int world,
+                   const __nv_bfloat16* __restrict__ stage, long long rows, int D, const __nv_bfloat16* __restrict__ bias,
+                   const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gate, int rows_per_group,
+                   long long gate_stride, __nv_bfloat16* __restrict__ out, int* status) {
+  if (world > 1) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(flags, slot, rank, world, epoch);
+    if (!block_wait_all(my_flags, slot, world, epoch, status, 120 + slot)) return;
+  }
+  const long long vec_per_row = D / 8;
+  const long long total = rows * vec_per_row;
+  const long long slot_elems = rows * static_cast<long long>(D);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / vec_per_row;
+    const int col = static_cast<int>(i - row * vec_per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < world; ++s)
+      add8_bf16(*reinterpret_cast<const uint4*>(stage + s * slot_elems + row * D + col), acc);
+    if (bias) {
+      float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      add8_bf16(*reinterpret_cast<const uint4*>(bias + col), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += b[j];
+    }
+    if (gate) {
+      float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      add8_bf16(*reinterpret_cast<const uint4*>(gate + (row / rows_per_group) * gate_stride + col), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] *= g[j];
+    }
+    if (residual) add8_bf16(*reinterpret_cast<const uint4*>(residual + row * D + col), acc);
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + row * D + col) = o;
+  }
+}
+
 }  // namespace mdb
 
 using namespace mdb;
+
+extern "C" int mdb_flag_barrier(const MdbPeerTable* flags, const int* my_flags, int slot, int rank, int world, int value,
+                                int* counters, int* status, cudaStream_t st) {
+  if (slot < 0 || slot >= MDB_FLAG_SLOTS || (value <= 0 && counters == nullptr)) return -1;
+  flag_barrier_kernel<<<1, 32, 0, st>>>(*flags, my_flags, slot, rank, world, value, counters, status);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_rs_finalize(const MdbPeerTable* flags, const int* my_flags, int slot, int epoch, int rank, int world,
+                               const void* stage, long long rows, int D, const void* bias, const void* residual,
+                               const void* gate, int rows_per_group, long long gate_stride, void* out, int* status,
+                               cudaStream_t st) {
+  if (D % 8 || rows < 0 || slot < 0 || slot >= MDB_FLAG_SLOTS || epoch <= 0) return -1;
+  if (rows == 0) return 0;
+  // every block must be resident at once (each waits for the peers): one wave of 148 SMs x 8 blocks at most
+  const long long want = (rows * (D / 8) + 255) / 256;
+  const int grid = static_cast<int>(want < 148 * 4 ? want : 148 * 4);
+  rs_finalize_kernel<<<grid, 256, 0, st>>>(*flags, my_flags, slot, epoch, rank, world,
+                                           reinterpret_cast<const __nv_bfloat16*>(stage), rows, D,
+                                           reinterpret_cast<const __nv_bfloat16*>(bias),
+                                           reinterpret_cast<const __nv_bfloat16*>(residual),
+                                           reinterpret_cast<const __nv_bfloat16*>(gate), rows_per_group > 0 ? rows_per_group : 1,
+                                           gate_stride, reinterpret_cast<__nv_bfloat16*>(out), status);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int mdb_flag_signal(const MdbPeerTable* flags, int slot, int rank, int world, int value, int* counters,
                                cudaStream_t st) {

@@ -63,6 +63,9 @@ typedef struct MdbGemmArgs {
   // Reduce-scatter fused GEMM (reduce_rows_per_owner > 0, fp32 output): output row r is ADDED into
   // route_out[r / reduce_rows_per_owner] (that rank's fp32 [rows_per_owner, ld_out] buffer) with red.global.add.
   int reduce_rows_per_owner;
+  // With a bf16 output (out_fp32 == 0) the reduce-scatter is STAGED instead: the row is stored (plain vector stores) into
+  // slot reduce_src_rank of the owner's bf16 [world, rows_per_owner, ld_out] staging buffer; the owner sums the slots.
+  int reduce_src_rank;
   // Implicit-GEMM convolution, stride 1 (conv_taps = KH*KW > 0): A[0] is an NHWC bf16 image [conv_n, conv_h, conv_w,
   // conv_cin] (conv_cin a multiple of 64), B[0] the filter [N, KH, KW, conv_cin] as a [N, KH*KW*conv_cin] matrix,
   // M = conv_n*conv_h*conv_w output pixels (output NHWC [.., N] with ld_out). Padding pad_h / pad_w is implicit:

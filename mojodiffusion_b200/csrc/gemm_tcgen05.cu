@@ -27,6 +27,8 @@ namespace mdb {
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;  // one swizzle atom row: 64 bf16 or 128 fp8
+constexpr int GATHER_STAGES = 2;          // shared-memory stages of the fused all-gather (bulk copies)
+constexpr int GATHER_PIECE = 16384;       // bytes per stage
 constexpr int NUM_THREADS = 224;  // warps: 0 TMA, 1 UMMA issue, 2-5 epilogue, 6 peer gather (all-gather fused GEMM)
 constexpr int CONV_TW = 16, CONV_TH = 8;  // conv mode: one M tile = 8 rows x 16 columns of output pixels
 
@@ -70,6 +72,7 @@ struct GemmParams {
   // reduce-scatter fused into the epilogue (route_owner_cols == 0 && reduce_rows_per_owner > 0): fp32 partial
   // results are added (red.global.add) into the row owner's fp32 buffer route_out[row / reduce_rows_per_owner]
   int reduce_rows_per_owner;
+  int reduce_src_rank;   // staged bf16 variant: slot of the owner's staging buffer this rank writes
   // implicit-GEMM convolution (conv_taps > 0): A is an NHWC image read through a 4-D tensor map, one 16x8 pixel
   // patch per M tile, one shifted box per filter tap; rows outside the image are skipped by the epilogue
   int conv_taps, conv_kw, conv_pad_h, conv_pad_w, conv_h, conv_w, conv_tiles_h, conv_tiles_w, conv_cblocks, conv_tiles_m;
@@ -126,7 +129,8 @@ __device__ __forceinline__ void act32_rt(int act, float (&v)[32]) {
 __device__ __forceinline__ void* out_slab_ptr(const GemmParams& p, int row, int col0, int esz) {
   if (p.reduce_rows_per_owner > 0) {
     const int owner = row / p.reduce_rows_per_owner;
-    const size_t orow = static_cast<size_t>(row - owner * p.reduce_rows_per_owner);
+    size_t orow = static_cast<size_t>(row - owner * p.reduce_rows_per_owner);
+    if (!p.out_fp32) orow += static_cast<size_t>(p.reduce_src_rank) * p.reduce_rows_per_owner;
     return reinterpret_cast<char*>(p.route_out[owner]) + (orow * p.ld_out + col0) * esz;
   }
   if (p.route_owner_cols <= 0)
@@ -161,7 +165,7 @@ __device__ __noinline__ void epilogue_row32_slow(const GemmParams& p, int row, i
     if (p.residual) x += __bfloat162float(p.residual[static_cast<size_t>(row) * p.ld_res + col]);
     if (p.out_fp32) {
       float* o = reinterpret_cast<float*>(out_slab_ptr(p, row, col0, 4)) + j;
-      if (p.reduce_rows_per_owner > 0) atomicAdd(o, x);
+      if (p.reduce_rows_per_owner > 0) atomicAdd(o, x);   // (fp32 reduce mode; the staged bf16 mode takes the store below)
       else *o = p.accumulate_out ? *o + x : x;
     } else {
       reinterpret_cast<__nv_bfloat16*>(out_slab_ptr(p, row, col0, 2))[j] = __float2bfloat16_rn(x);
@@ -312,6 +316,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   __shared__ uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ uint64_t gather_bar[GATHER_STAGES];
 
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -328,6 +333,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       mbar_init(&tfull_bar[s], 1);
       mbar_init(&tempty_bar[s], 4);
     }
+    for (int s = 0; s < GATHER_STAGES; ++s) mbar_init(&gather_bar[s], 1);
     abort_s = 0;
     fence_mbar_init();
   }
@@ -512,24 +518,57 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     __syncwarp();
   } else if (warp == 6) {
     // ------------------------------- peer gather (all-gather fused GEMM) --------
-    if (p.gather_world > 1) {
-      const long long vec_total = p.gather_chunk_bytes >> 4;                       // 16-byte vectors per chunk
-      const long long per_cta = (vec_total + gridDim.x - 1) / gridDim.x;
-      const long long v0 = static_cast<long long>(blockIdx.x) * per_cta;
-      const long long v1 = min(v0 + per_cta, vec_total);
-      for (int i = 1; i < p.gather_world; ++i) {
+    if (p.gather_world > 1 && lane == 0) {
+      // One thread streams this CTA's share of every peer chunk through two 16 KB shared-memory stages with bulk copies:
+      // peer memory -> shared (completion on an mbarrier), shared -> the local gathered buffer (bulk group). 32 KB are in
+      // flight per CTA, which keeps NVLink busy from all SMs together; nothing passes through registers.
+      uint8_t* gs = smem + STAGES * STAGE_BYTES;
+      const long long pieces = (p.gather_chunk_bytes + GATHER_PIECE - 1) / GATHER_PIECE;
+      uint32_t ph[GATHER_STAGES] = {0, 0};
+      bool ok = true;
+      for (int i = 1; i < p.gather_world && ok; ++i) {
         const int c = (p.gather_rank + i) % p.gather_world;
-        const uint4* src = reinterpret_cast<const uint4*>(p.gather_src[c]);
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.gather_dst) + c * p.gather_chunk_bytes);
-        long long v = v0 + lane;
-        for (; v + 96 < v1; v += 128) {                                           // 4 peer loads in flight per lane
-          const uint4 a = src[v], b = src[v + 32], cc = src[v + 64], d = src[v + 96];
-          dst[v] = a; dst[v + 32] = b; dst[v + 64] = cc; dst[v + 96] = d;
+        const char* src = reinterpret_cast<const char*>(p.gather_src[c]);
+        char* dst = reinterpret_cast<char*>(p.gather_dst) + c * p.gather_chunk_bytes;
+        const long long mine = blockIdx.x < pieces ? (pieces - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        auto piece_off = [&](long long k) { return (static_cast<long long>(blockIdx.x) + k * gridDim.x) * GATHER_PIECE; };
+        auto piece_len = [&](long long k) {
+          const long long rem = p.gather_chunk_bytes - piece_off(k);
+          return static_cast<uint32_t>(rem < GATHER_PIECE ? rem : GATHER_PIECE);
+        };
+        auto issue = [&](long long k) {
+          const int sgi = static_cast<int>(k % GATHER_STAGES);
+          mbar_expect_tx(&gather_bar[sgi], piece_len(k));
+          bulk_load_g2s(gs + sgi * GATHER_PIECE, src + piece_off(k), piece_len(k), &gather_bar[sgi]);
+        };
+        long long issued = 0;
+        for (; issued < mine && issued < GATHER_STAGES; ++issued) issue(issued);
+        for (long long k = 0; k < mine; ++k) {
+          const int sgi = static_cast<int>(k % GATHER_STAGES);
+          if (!mbar_wait(&gather_bar[sgi], ph[sgi], &abort_s)) {
+            report_status(p.status, STATUS_TIMEOUT, 70, c);
+            ok = false;
+            // bounded drain of the loads still in flight (jobs k .. issued-1), so that nothing lands in shared memory
+            // after this CTA has left
+            for (long long j = k; j < issued; ++j) {
+              const int sj = static_cast<int>(j % GATHER_STAGES);
+              const uint64_t t0 = globaltimer_ns();
+              while (!mbar_try_wait(&gather_bar[sj], ph[sj]) && globaltimer_ns() - t0 < MDB_WAIT_LIMIT_NS) {}
+            }
+            break;
+          }
+          ph[sgi] ^= 1;
+          bulk_store_s2g(dst + piece_off(k), gs + sgi * GATHER_PIECE, piece_len(k));
+          tma_store_commit();
+          if (issued < mine) {
+            tma_store_wait_read<0>();                      // the stage has been read out: it may be refilled
+            issue(issued++);
+          }
         }
-        for (; v < v1; v += 32) dst[v] = src[v];
+        tma_store_wait<0>();                               // this CTA's share of chunk c is in the gathered buffer
+        if (!ok) break;
         __threadfence();
-        __syncwarp();
-        if (lane == 0) atomicAdd(p.gather_ready + c, 1);
+        atomicAdd(p.gather_ready + c, 1);
       }
     }
   } else {
@@ -652,11 +691,14 @@ namespace mdb {
 template <int BN, int STAGES, bool A_MN, bool B_MN, int KIND>
 static int launch_variant(const GemmMaps& maps, const GemmParams& p, int num_sms, cudaStream_t stream) {
   constexpr int STAGE_BYTES = BM * BK_BYTES + BN * BK_BYTES;
-  constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
+  constexpr int SMEM_BASE = STAGES * STAGE_BYTES + 1024;
+  constexpr int SMEM_GATHER = SMEM_BASE + GATHER_STAGES * GATHER_PIECE;
+  static_assert(SMEM_GATHER <= 227 * 1024, "pipeline + gather stages exceed the shared memory of an SM");
+  const int SMEM = p.gather_world > 1 ? SMEM_GATHER : SMEM_BASE;
   auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, KIND>;
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GATHER);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_done = true;
   }
@@ -774,7 +816,8 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
     cudaError_t e = cudaMemsetAsync(a->gather_ready, 0, sizeof(int) * MDB_GEMM_MAX_PEERS, stream);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  if (a->reduce_rows_per_owner > 0 && !a->out_fp32) return -9;
+  p.reduce_src_rank = a->reduce_src_rank;
+  if (a->reduce_rows_per_owner > 0 && !a->out_fp32 && (a->reduce_src_rank < 0 || a->reduce_src_rank >= MDB_GEMM_MAX_PEERS)) return -9;
   p.conv_taps = a->conv_taps;
   if (a->conv_taps > 0) {
     if (a->conv_cin % k_elems) return -7;

@@ -3,12 +3,15 @@
     x_local [rows/N, D] --all-gather--> [rows, D] @ W1_shard^T (+b1, act) -> h [rows, F/N]         (AG -> GEMM)
     h @ W2_shard^T -> partial [rows, D] --reduce-scatter--> y_local [rows/N, D]                     (GEMM -> RS)
 
-* AG -> GEMM is ONE kernel: warp 6 of every CTA of the tcgen05 GEMM pulls its slice of each remote activation chunk
-  out of the owner's symmetric buffer (peer loads over NVLink) into the local gathered operand and bumps that chunk's
-  arrival counter; the TMA producer starts with the local chunk's tiles and waits (bounded) only for chunks that
-  have not landed yet. Each remote byte crosses NVLink once and lands in local HBM, from where TMA reads it.
-* GEMM -> RS is ONE kernel: the epilogue adds each fp32 partial 32-column slab into the row owner's fp32 buffer with
-  ``red.global.add.v4.f32`` on peer memory; a small finalise step applies bias / gate / residual and re-zeroes.
+* AG -> GEMM is ONE kernel: one thread of warp 6 in every CTA of the tcgen05 GEMM streams its share of each remote
+  activation chunk out of the owner's symmetric buffer through two 16 KB shared-memory stages with bulk copies (peer
+  memory -> shared -> the local gathered operand) and bumps that chunk's arrival counter; the TMA producer starts with
+  the local chunk's tiles and waits (bounded) only for chunks that have not landed yet. Each remote byte crosses
+  NVLink once and lands in local HBM, from where TMA reads it.
+* GEMM -> RS is ONE kernel plus a tail: the epilogue stores each bf16 partial 32-column slab into slot [this rank] of
+  the row owner's staging buffer (plain 16-byte stores over NVLink: half the bytes of fp32 atomics and no read-modify-
+  write at the far end); the tail kernel does the all-rank barrier, sums the N slots in fp32 and applies
+  bias / gate / residual in the same pass.
 * ``mode="nccl"`` does the same with all_gather_into_tensor / reduce_scatter_tensor: baseline and oracle.
 
 The reference has no tensor parallelism (serenitymojo/docs/AUDIT_SIMPLETUNER_PARITY_2026-06-11.md:81-110).
@@ -44,33 +47,27 @@ class TPContext:
         self.rows, self.rl, self.D = rows_total, rows_total // N, dim
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.dtype = dtype
-        xs_bytes = self.rl * dim * 2
-        acc_bytes = self.rl * dim * 4
+        x_bytes = rows_total * dim * 2                 # gathered activations: my rows are my shard, the rest arrive
+        stage_bytes = N * self.rl * dim * 2            # reduce-scatter staging: one bf16 slot per source rank
         self.off_x = _FLAG_BYTES
-        self.off_acc = self.off_x + (xs_bytes + 255) // 256 * 256
-        total = self.off_acc + acc_bytes
+        self.off_stage = self.off_x + (x_bytes + 255) // 256 * 256
+        total = self.off_stage + stage_bytes
         self.calls = 0
         if mode == "fused":
             native.load(True)
             self.symm = symm if symm is not None else SymmetricBuffer.create(total, group, self.device, False)
+            assert self.symm.local.numel() >= total
             self.flags = self.symm.view(0, 64, torch.int32)
-            self.counters = torch.zeros(16, dtype=torch.int32, device=self.device)
-            self.x_shard = self.symm.view(self.off_x, self.rl * dim, dtype).view(self.rl, dim)
-            self.acc = self.symm.view(self.off_acc, self.rl * dim, torch.float32).view(self.rl, dim)
-            self.acc.zero_()
-            self.x_gathered = torch.empty(rows_total, dim, dtype=dtype, device=self.device)
+            self.x_all = self.symm.view(self.off_x, rows_total * dim, dtype).view(rows_total, dim)
+            self.stage = self.symm.view(self.off_stage, N * self.rl * dim, dtype).view(N, self.rl, dim)
             self.ready = torch.zeros(8, dtype=torch.int32, device=self.device)
+            chunk = self.rl * dim * 2
+            base = self.symm.ptrs_at(self.off_x)
+            self.gather_ptrs = [base[c] + c * chunk for c in range(N)]      # rank c's own rows inside ITS buffer
 
     @staticmethod
     def symm_bytes(rows_total, dim, world) -> int:
-        rl = rows_total // world
-        return _FLAG_BYTES + (rl * dim * 2 + 255) // 256 * 256 + rl * dim * 4 + 256
-
-    def _signal(self, slot):
-        native.ops().flag_signal(self.symm.ptrs_at(0), slot, self.rank, 0, self.flags, self.counters)
-
-    def _wait(self, slot):
-        native.ops().flag_wait(self.flags, slot, self.world, 0, self.counters)
+        return _FLAG_BYTES + (rows_total * dim * 2 + 255) // 256 * 256 + rows_total * dim * 2 + 256
 
     @torch.no_grad()
     def mlp(self, x_local, w1_shard, b1_shard, w2_shard, b2, act="gelu_tanh", residual=None, gate=None,
@@ -93,22 +90,23 @@ class TPContext:
             else:
                 y = part
         else:
+            o = native.ops()
+            fptrs = self.symm.ptrs_at(0)
             if self.calls > 0:
-                self._wait(SLOT_X_DONE)                       # peers finished reading my previous x shard
+                o.flag_wait(self.flags, SLOT_X_DONE, N, self.calls, None)      # peers finished reading my previous rows
             self.calls += 1
-            self.x_shard.copy_(x2)
-            self.x_gathered[r * rl:(r + 1) * rl].copy_(x2)
-            self._signal(SLOT_X_READY)
-            self._wait(SLOT_X_READY)
-            h = _gemm([self.x_gathered], [w1_shard], bias=b1_shard, act=act_code(act),
-                      gather_ptrs=self.symm.ptrs_at(self.off_x), gather_cfg=[r, 0, rl, rl * self.D * 2],
-                      gather_dst=self.x_gathered, gather_ready=self.ready)
-            self._signal(SLOT_X_DONE)
-            _gemm([h], [w2_shard], out_fp32=True, route_ptrs=self.symm.ptrs_at(self.off_acc), route_cfg=[rl, self.D])
-            self._signal(SLOT_RS_DONE)
-            self._wait(SLOT_RS_DONE)
-            y = self.acc.clone()
-            self.acc.zero_()
+            ep = self.calls
+            self.x_all[r * rl:(r + 1) * rl].copy_(x2)
+            o.flag_barrier(fptrs, self.flags, SLOT_X_READY, r, ep, None)
+            h = _gemm([self.x_all], [w1_shard], bias=b1_shard, act=act_code(act),
+                      gather_ptrs=self.gather_ptrs, gather_cfg=[r, 0, rl, rl * self.D * 2],
+                      gather_dst=self.x_all, gather_ready=self.ready)
+            o.flag_signal(fptrs, SLOT_X_DONE, r, ep, self.flags, None)
+            # partial rows go straight into slot r of the row owner's staging buffer (bf16 vector stores over NVLink)
+            _gemm([h], [w2_shard], route_ptrs=self.symm.ptrs_at(self.off_stage), route_cfg=[rl, self.D, r])
+            res = _flat2d(residual).contiguous() if residual is not None else None
+            y = o.rs_finalize(fptrs, self.flags, SLOT_RS_DONE, ep, r, self.stage, b2, res, gate, rows_per_group)
+            return y.reshape(x_local.shape)
         if b2 is not None:
             y = y + b2.float()
         y = y.to(x2.dtype)
