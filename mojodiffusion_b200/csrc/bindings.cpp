@@ -641,22 +641,32 @@ void flag_barrier(std::vector<int64_t> flag_ptrs, const Tensor& my_flags, int64_
 }
 Tensor rs_finalize(std::vector<int64_t> flag_ptrs, const Tensor& my_flags, int64_t slot, int64_t epoch, int64_t rank,
                    const Tensor& stage, const optional<Tensor>& bias, const optional<Tensor>& residual,
-                   const optional<Tensor>& gate, int64_t rows_per_group) {
+                   const optional<Tensor>& gate, int64_t rows_per_group, const optional<Tensor>& accum) {
   TORCH_CHECK(stage.is_cuda() && stage.dim() == 3 && stage.is_contiguous() && stage.scalar_type() == at::kBFloat16,
               "rs_finalize: stage must be bf16 [world, rows, D]");
   TORCH_CHECK((int64_t)flag_ptrs.size() == stage.size(0), "rs_finalize: one staging slot per rank");
   c10::cuda::CUDAGuard guard(stage.device());
   MdbPeerTable f = peer_table(flag_ptrs);
-  Tensor out = at::empty({stage.size(1), stage.size(2)}, stage.options());
+  Tensor out;
+  float* acc_ptr = nullptr;
+  if (accum.has_value() && accum->defined()) {
+    TORCH_CHECK(accum->scalar_type() == at::kFloat && accum->is_contiguous() && accum->numel() == stage.size(1) * stage.size(2),
+                "rs_finalize: accum must be fp32 [rows, D]");
+    acc_ptr = accum->data_ptr<float>();
+    out = *accum;
+  } else {
+    out = at::empty({stage.size(1), stage.size(2)}, stage.options());
+  }
   int64_t gate_stride = 0;
   if (gate.has_value()) {
     TORCH_CHECK(gate->dim() == 2 && gate->stride(1) == 1 && gate->size(1) == stage.size(2), "rs_finalize: gate [groups, D]");
     gate_stride = gate->stride(0);
   }
-  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->numel() == out.numel(), "rs_finalize: residual");
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->numel() == stage.size(1) * stage.size(2), "rs_finalize: residual");
   check_rc(mdb_rs_finalize(&f, my_flags.data_ptr<int>(), (int)slot, (int)epoch, (int)rank, (int)stage.size(0), stage.data_ptr(),
                            stage.size(1), (int)stage.size(2), opt_ptr(bias), opt_ptr(residual), opt_ptr(gate),
-                           (int)rows_per_group, gate_stride, out.data_ptr(), status_ptr(stage), cur_stream()),
+                           (int)rows_per_group, gate_stride, acc_ptr ? nullptr : out.data_ptr(), acc_ptr, status_ptr(stage),
+                           cur_stream()),
            "rs_finalize");
   return out;
 }

@@ -25,10 +25,11 @@ int mdb_flag_wait(const int* my_flags, int slot, int world, int value, int* coun
 int mdb_flag_barrier(const MdbPeerTable* flags, const int* my_flags, int slot, int rank, int world, int value, int* counters,
                      int* status, cudaStream_t st);
 // staged reduce-scatter tail: barrier on `slot` (explicit epoch > 0), then out = residual + gate * (sum of the `world`
-// bf16 slots of stage[world][rows][D] + bias). bias / residual / gate may be NULL.
+// bf16 slots of stage[world][rows][D] + bias). bias / residual / gate may be NULL. Exactly one of out (bf16 [rows, D]) and
+// accum (fp32 [rows, D], += the result: gradient accumulation) is given.
 int mdb_rs_finalize(const MdbPeerTable* flags, const int* my_flags, int slot, int epoch, int rank, int world,
                     const void* stage, long long rows, int D, const void* bias, const void* residual, const void* gate,
-                    int rows_per_group, long long gate_stride, void* out, int* status, cudaStream_t st);
+                    int rows_per_group, long long gate_stride, void* out, float* accum, int* status, cudaStream_t st);
 
 // all-gather by peer loads into dst = [world][chunk_bytes]
 int mdb_peer_gather(const MdbPeerTable* src, void* dst, long long chunk_bytes, int rank, int world, int copy_local,

@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(256)
 rs_finalize_kernel(MdbPeerTable flags, const int* my_flags, int slot, int epoch, int rank, int world,
                    const __nv_bfloat16* __restrict__ stage, long long rows, int D, const __nv_bfloat16* __restrict__ bias,
                    const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gate, int rows_per_group,
-                   long long gate_stride, __nv_bfloat16* __restrict__ out, int* status) {
+                   long long gate_stride, __nv_bfloat16* __restrict__ out, float* __restrict__ accum, int* status) {
   if (world > 1) {
     if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(flags, slot, rank, world, epoch);
     if (!block_wait_all(my_flags, slot, world, epoch, status, 120 + slot)) return;
@@ -294,6 +294,14 @@ rs_finalize_kernel(MdbPeerTable flags, const int* my_flags, int slot, int epoch,
       for (int j = 0; j < 8; ++j) acc[j] *= g[j];
     }
     if (residual) add8_bf16(*reinterpret_cast<const uint4*>(residual + row * D + col), acc);
+    if (accum) {                                        // gradient accumulation: fp32 shard += reduced partials
+      float4* a4 = reinterpret_cast<float4*>(accum + row * D + col);
+      float4 lo = a4[0], hi = a4[1];
+      lo.x += acc[0]; lo.y += acc[1]; lo.z += acc[2]; lo.w += acc[3];
+      hi.x += acc[4]; hi.y += acc[5]; hi.z += acc[6]; hi.w += acc[7];
+      a4[0] = lo; a4[1] = hi;
+      continue;
+    }
     uint4 o;
     o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
     o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
@@ -313,9 +321,9 @@ extern "C" int mdb_flag_barrier(const MdbPeerTable* flags, const int* my_flags, 
 }
 extern "C" int mdb_rs_finalize(const MdbPeerTable* flags, const int* my_flags, int slot, int epoch, int rank, int world,
                                const void* stage, long long rows, int D, const void* bias, const void* residual,
-                               const void* gate, int rows_per_group, long long gate_stride, void* out, int* status,
-                               cudaStream_t st) {
-  if (D % 8 || rows < 0 || slot < 0 || slot >= MDB_FLAG_SLOTS || epoch <= 0) return -1;
+                               const void* gate, int rows_per_group, long long gate_stride, void* out, float* accum,
+                               int* status, cudaStream_t st) {
+  if (D % 8 || rows < 0 || slot < 0 || slot >= MDB_FLAG_SLOTS || epoch <= 0 || (out == nullptr) == (accum == nullptr)) return -1;
   if (rows == 0) return 0;
   // every block must be resident at once (each waits for the peers): one wave of 148 SMs x 8 blocks at most
   const long long want = (rows * (D / 8) + 255) / 256;
@@ -325,7 +333,7 @@ extern "C" int mdb_rs_finalize(const MdbPeerTable* flags, const int* my_flags, i
                                            reinterpret_cast<const __nv_bfloat16*>(bias),
                                            reinterpret_cast<const __nv_bfloat16*>(residual),
                                            reinterpret_cast<const __nv_bfloat16*>(gate), rows_per_group > 0 ? rows_per_group : 1,
-                                           gate_stride, reinterpret_cast<__nv_bfloat16*>(out), status);
+                                           gate_stride, reinterpret_cast<__nv_bfloat16*>(out), accum, status);
   return (int)cudaGetLastError();
 }
 

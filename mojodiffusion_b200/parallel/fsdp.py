@@ -3,12 +3,14 @@
 Every ``FSDPLinear`` keeps only 1/N of its weight rows: the bf16 shard lives in symmetric memory (peers read it),
 the fp32 master copy and the AdamW moments exist for the shard only.
 
-* forward  : ``y = x @ W^T`` where W is re-assembled INSIDE the consuming GEMM: warp 6 of every CTA pulls its slice of
-             each remote weight shard over NVLink into a transient full-weight buffer while the tensor core already
-             works on the output columns of the local shard (parameter all-gather fused into the first consumer).
+* forward  : ``y = x @ W^T`` where W is re-assembled INSIDE the consuming GEMM: warp 6 of every CTA streams its share
+             of each remote weight shard over NVLink (bulk copies through shared memory) into a transient full-weight
+             buffer while the tensor core already works on the output columns of the local shard (parameter
+             all-gather fused into the first consumer).
 * backward : ``dx = dy @ W`` from the gathered buffer (re-gathered by peer loads if another layer has reused it);
-             ``dW = dy^T x`` whose fp32 tiles the GEMM epilogue adds straight into the OWNER's gradient shard
-             (``red.global.add`` on peer memory: gradient reduce-scatter fused into the producing GEMM).
+             ``dW = dy^T x`` whose bf16 tiles the GEMM epilogue stores straight into slot [rank] of the row OWNER's
+             staging buffer (gradient reduce-scatter fused into the producing GEMM); a tail kernel does the all-rank
+             barrier and adds the N slots into the owner's fp32 gradient shard.
 * step     : after one flag barrier, a single multi-tensor AdamW launch updates every local master shard and writes
              the new bf16 shard back into symmetric memory (fp32 masters, bf16 shadows: csrc/optim.cu).
 
@@ -29,7 +31,7 @@ from ..ops import native
 from ..ops.functional import _flat2d, _gemm
 from .symm import SymmetricBuffer
 
-SLOT_BWD_DONE, SLOT_STEP_DONE = 6, 7
+SLOT_BWD_DONE, SLOT_STEP_DONE, SLOT_RS = 6, 7, 5
 _FLAG_BYTES = 512
 
 
@@ -57,6 +59,13 @@ class FSDPContext:
             off += (l.rows_local * l.in_features * 2 + 255) // 256 * 256
             l.off_g = off
             off += (l.rows_local * l.in_features * 4 + 255) // 256 * 256
+        big = max(l.out_features * l.in_features for l in self.layers)
+        # two staging buffers for the reduce-scatter of dW (bf16 partial rows from every rank), used alternately so a rank
+        # that is one layer ahead never writes into a buffer that is still being summed
+        self.off_stage = []
+        for _ in range(2):
+            self.off_stage.append(off)
+            off += (big * 2 + 255) // 256 * 256
         native.load(True)
         if self.mode == "fused" and self.world > 1:
             self.symm = SymmetricBuffer.create(off, self.group, self.device, False)
@@ -67,7 +76,7 @@ class FSDPContext:
         self.flags = arena[:256].view(torch.int32)
         self.counters = torch.zeros(16, dtype=torch.int32, device=self.device)
         self.ready = torch.zeros(8, dtype=torch.int32, device=self.device)
-        big = max(l.out_features * l.in_features for l in self.layers)
+        self.rs_calls = 0
         self.wbuf = torch.empty(big, dtype=torch.bfloat16, device=self.device)
         for l in self.layers:
             n = l.rows_local * l.in_features
@@ -164,8 +173,15 @@ class _FSDPLinearFn(torch.autograd.Function):
             dx = _gemm([dy], [W], b_mn=True)
         # dW = dy^T x, reduce-scattered over ranks into the owners' fp32 gradient shards
         if c.world > 1 and c.symm is not None:
-            _gemm([dy], [x2], a_mn=True, b_mn=True, out_fp32=True, route_ptrs=c.symm.ptrs_at(layer.off_g),
-                  route_cfg=[layer.rows_local, layer.in_features])
+            # bf16 partial rows go into slot [rank] of the row owner's staging buffer; the tail kernel does the barrier and
+            # adds the N slots into the owner's fp32 gradient shard
+            c.rs_calls += 1
+            off = c.off_stage[c.rs_calls % 2]
+            rl, K = layer.rows_local, layer.in_features
+            _gemm([dy], [x2], a_mn=True, b_mn=True, route_ptrs=c.symm.ptrs_at(off), route_cfg=[rl, K, c.rank])
+            stage = c.arena[off:off + c.world * rl * K * 2].view(torch.bfloat16).view(c.world, rl, K)
+            native.ops().rs_finalize(c.symm.ptrs_at(0), c.flags, SLOT_RS, c.rs_calls, c.rank, stage, None, None, None, 1,
+                                     layer.g_shard)
         else:
             dw = _gemm([dy], [x2], a_mn=True, b_mn=True, out_fp32=True)
             if c.world > 1:

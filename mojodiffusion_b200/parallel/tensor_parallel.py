@@ -105,7 +105,7 @@ class TPContext:
             # partial rows go straight into slot r of the row owner's staging buffer (bf16 vector stores over NVLink)
             _gemm([h], [w2_shard], route_ptrs=self.symm.ptrs_at(self.off_stage), route_cfg=[rl, self.D, r])
             res = _flat2d(residual).contiguous() if residual is not None else None
-            y = o.rs_finalize(fptrs, self.flags, SLOT_RS_DONE, ep, r, self.stage, b2, res, gate, rows_per_group)
+            y = o.rs_finalize(fptrs, self.flags, SLOT_RS_DONE, ep, r, self.stage, b2, res, gate, rows_per_group, None)
             return y.reshape(x_local.shape)
         if b2 is not None:
             y = y + b2.float()
