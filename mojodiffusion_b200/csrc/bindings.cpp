@@ -55,7 +55,7 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
             bool b_mn, const optional<Tensor>& row_scale, const optional<Tensor>& col_scale, double alpha,
             bool accumulate, int64_t bn, const optional<Tensor>& prof, std::vector<int64_t> route_ptrs,
             std::vector<int64_t> route_cfg, std::vector<int64_t> gather_ptrs, std::vector<int64_t> gather_cfg,
-            const optional<Tensor>& gather_dst, const optional<Tensor>& gather_ready) {
+            const optional<Tensor>& gather_dst, const optional<Tensor>& gather_ready, int64_t split_k) {
   TORCH_CHECK(!As.empty() && As.size() == Bs.size() && As.size() <= MDB_GEMM_MAX_SEG, "gemm: 1..3 K segments");
   const Tensor& A0 = As[0];
   TORCH_CHECK(A0.is_cuda(), "gemm: CUDA tensors only");
@@ -109,6 +109,8 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
   g.out_fp32 = out_fp32;
   g.accumulate_out = accumulate;
   g.bn = static_cast<int>(bn);
+  g.split_k = static_cast<int>(split_k);
+  TORCH_CHECK(split_k <= 1 || (out_fp32 && out_opt.has_value()), "gemm: split-K adds into a caller-zeroed fp32 out");
   g.pair_offset = static_cast<int>(pair_offset > 0 ? pair_offset : 0);
   g.act = static_cast<int>(act);
   g.act_on_second = static_cast<int>(act_on_second);
@@ -333,16 +335,24 @@ std::tuple<Tensor, Tensor> attention_fwd(const Tensor& q, const Tensor& k, const
 
 std::tuple<Tensor, Tensor, Tensor> attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
                                                  const Tensor& lse, const Tensor& dout, double scale,
-                                                 const optional<Tensor>& kv_len) {
+                                                 const optional<Tensor>& kv_len, std::vector<Tensor> outs) {
   TORCH_CHECK(q.is_cuda() && q.dim() == 4 && q.scalar_type() == at::kBFloat16, "attention_bwd: [B,S,H,Dh] bf16");
   TORCH_CHECK(q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 && o.stride(3) == 1 && dout.stride(3) == 1,
               "attention_bwd: head dim must be contiguous");
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t B = q.size(0), Sq = q.size(1), H = q.size(2), Dh = q.size(3), Skv = k.size(1);
   TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == B * H * Sq, "attention_bwd: lse");
-  Tensor dq = at::empty({B, Sq, H, Dh}, q.options());
-  Tensor dk = at::empty({B, Skv, H, Dh}, q.options());
-  Tensor dv = at::empty({B, Skv, H, Dh}, q.options());
+  // outs: empty, or {dq, dk, dv} views to write into (e.g. the three column ranges of one packed gradient buffer)
+  TORCH_CHECK(outs.empty() || outs.size() == 3, "attention_bwd: outs must be {dq, dk, dv}");
+  Tensor dq = outs.empty() ? at::empty({B, Sq, H, Dh}, q.options()) : outs[0];
+  Tensor dk = outs.empty() ? at::empty({B, Skv, H, Dh}, q.options()) : outs[1];
+  Tensor dv = outs.empty() ? at::empty({B, Skv, H, Dh}, q.options()) : outs[2];
+  if (!outs.empty()) {
+    TORCH_CHECK(dq.sizes() == q.sizes() && dk.sizes() == k.sizes() && dv.sizes() == v.sizes() && dq.stride(3) == 1 &&
+                    dk.stride(3) == 1 && dv.stride(3) == 1 && dq.scalar_type() == at::kBFloat16 &&
+                    dk.scalar_type() == at::kBFloat16 && dv.scalar_type() == at::kBFloat16,
+                "attention_bwd: outs must match q / k / v with a contiguous head dim");
+  }
   Tensor delta = at::empty({B, H, Sq}, lse.options());
   MdbAttnBwdArgs a;
   memset(&a, 0, sizeof(a));
@@ -427,7 +437,7 @@ void qk_norm_rope_bwd(Tensor dbuf, const Tensor& xbuf, const optional<Tensor>& w
                       const optional<Tensor>& cosv, const optional<Tensor>& sinv, int64_t H, int64_t Dh, int64_t q_off,
                       int64_t k_off, double eps, bool interleaved, bool do_norm, int64_t rope_start,
                       int64_t pos_offset) {
-  TORCH_CHECK(dbuf.is_cuda() && dbuf.dim() == 3 && xbuf.dim() == 3 && dbuf.stride(0) == xbuf.stride(0) &&
+  TORCH_CHECK(dbuf.is_cuda() && dbuf.dim() == 3 && xbuf.dim() == 3 && (dbuf.size(0) == 1 || dbuf.stride(0) == xbuf.stride(0)) &&
                   dbuf.stride(1) == xbuf.stride(1) && dbuf.stride(2) == 1 && xbuf.stride(2) == 1,
               "qk_norm_rope_bwd: [B,S,W] views with equal strides");
   const int64_t tokens_per_batch = dbuf.size(1);

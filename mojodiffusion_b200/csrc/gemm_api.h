@@ -66,6 +66,9 @@ typedef struct MdbGemmArgs {
   // With a bf16 output (out_fp32 == 0) the reduce-scatter is STAGED instead: the row is stored (plain vector stores) into
   // slot reduce_src_rank of the owner's bf16 [world, rows_per_owner, ld_out] staging buffer; the owner sums the slots.
   int reduce_src_rank;
+  // Split-K (split_k > 1): the K range is cut into split_k parts, each a separate work item of the persistent grid; the
+  // parts are added (red.global.add) into the fp32 output, which the caller has zeroed. One K segment, no epilogue math.
+  int split_k;
   // Implicit-GEMM convolution, stride 1 (conv_taps = KH*KW > 0): A[0] is an NHWC bf16 image [conv_n, conv_h, conv_w,
   // conv_cin] (conv_cin a multiple of 64), B[0] the filter [N, KH, KW, conv_cin] as a [N, KH*KW*conv_cin] matrix,
   // M = conv_n*conv_h*conv_w output pixels (output NHWC [.., N] with ld_out). Padding pad_h / pad_w is implicit:

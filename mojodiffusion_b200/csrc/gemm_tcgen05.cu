@@ -72,6 +72,8 @@ struct GemmParams {
   // reduce-scatter fused into the epilogue (route_owner_cols == 0 && reduce_rows_per_owner > 0): fp32 partial
   // results are added (red.global.add) into the row owner's fp32 buffer route_out[row / reduce_rows_per_owner]
   int reduce_rows_per_owner;
+  int split_k;           // > 1: the K range of the single segment is cut into split_k parts, one work item each;
+                         // parts are added into a zero-initialised fp32 output with red.global.add (skinny GEMMs)
   int reduce_src_rank;   // staged bf16 variant: slot of the owner's staging buffer this rank writes
   // implicit-GEMM convolution (conv_taps > 0): A is an NHWC image read through a 4-D tensor map, one 16x8 pixel
   // patch per M tile, one shifted box per filter tap; rows outside the image are skipped by the epilogue
@@ -165,7 +167,7 @@ __device__ __noinline__ void epilogue_row32_slow(const GemmParams& p, int row, i
     if (p.residual) x += __bfloat162float(p.residual[static_cast<size_t>(row) * p.ld_res + col]);
     if (p.out_fp32) {
       float* o = reinterpret_cast<float*>(out_slab_ptr(p, row, col0, 4)) + j;
-      if (p.reduce_rows_per_owner > 0) atomicAdd(o, x);   // (fp32 reduce mode; the staged bf16 mode takes the store below)
+      if (p.reduce_rows_per_owner > 0 || p.split_k > 1) atomicAdd(o, x);   // fp32 reduce mode / split-K parts
       else *o = p.accumulate_out ? *o + x : x;
     } else {
       reinterpret_cast<__nv_bfloat16*>(out_slab_ptr(p, row, col0, 2))[j] = __float2bfloat16_rn(x);
@@ -241,7 +243,7 @@ __device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int
   }
   if (p.out_fp32) {
     float4* o = reinterpret_cast<float4*>(out_slab_ptr(p, row, col0, 4));
-    if (p.reduce_rows_per_owner > 0) {
+    if (p.reduce_rows_per_owner > 0 || p.split_k > 1) {
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j), "f"(v[4 * j]), "f"(v[4 * j + 1]),
@@ -355,8 +357,13 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   const int tiles_m = p.conv_taps > 0 ? p.conv_tiles_m : (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + (p.pair_offset > 0 ? BN / 2 : BN) - 1) / (p.pair_offset > 0 ? BN / 2 : BN);
   const int num_tiles = tiles_m * tiles_n;
+  const int splits = p.split_k > 1 ? p.split_k : 1;
+  const int num_items = num_tiles * splits;          // work item = (tile, K part); part = item / num_tiles
   int total_kb = 0;
   for (int s = 0; s < p.num_seg; ++s) total_kb += p.kblocks[s];
+  // K blocks [kb_lo, kb_hi) of segment 0 that work item `item` covers (the whole segment without split-K)
+  auto kb_lo_of = [&](int item) { return splits > 1 ? static_cast<int>(static_cast<long long>(item / num_tiles) * p.kblocks[0] / splits) : 0; };
+  auto kb_hi_of = [&](int item) { return splits > 1 ? static_cast<int>(static_cast<long long>(item / num_tiles + 1) * p.kblocks[0] / splits) : p.kblocks[0]; };
   constexpr int K_ELEMS = (KIND == 0) ? 64 : 128;  // elements per 128-byte row
 
   if (warp == 0) {
@@ -369,7 +376,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       bool ok = true;
       long long t_wait = 0;
       unsigned chunk_seen = 1u << p.gather_rank;   // chunks whose arrival this CTA has already observed
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+        const int tile = item % num_tiles;
         const int m0 = tile_m_index(p, tile, tiles_m, tiles_n) * BM;
         const int nblk = tile_n_index(p, tile, tiles_m, tiles_n);
         const int n0 = p.pair_offset > 0 ? nblk * (BN / 2) : nblk * BN;
@@ -397,7 +405,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           asm volatile("fence.proxy.async.global;" ::: "memory");   // peer-copied bytes -> visible to the TMA reads
         }
         for (int s = 0; ok && s < p.num_seg; ++s) {
-          for (int kb = 0; kb < p.kblocks[s]; ++kb) {
+          const int kb_begin = s == 0 ? kb_lo_of(item) : 0, kb_end = s == 0 ? kb_hi_of(item) : p.kblocks[s];
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
             const long long tw0 = p.prof ? clock64() : 0;
             if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s)) {
               report_status(p.status, STATUS_TIMEOUT, 1, stage);
@@ -466,7 +475,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       bool ok = true;
       long long t_full = 0, t_tempty = 0;
       const long long t_begin = p.prof ? clock64() : 0;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+      for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++it) {
+        const int item_kb = splits > 1 ? kb_hi_of(item) - kb_lo_of(item) : total_kb;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         const long long te0 = p.prof ? clock64() : 0;
@@ -477,7 +487,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         if (p.prof) t_tempty += clock64() - te0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < total_kb; ++kb) {
+        for (int kb = 0; kb < item_kb; ++kb) {
           const long long tf0 = p.prof ? clock64() : 0;
           if (!mbar_wait(&full_bar[stage], phase, &abort_s)) {
             report_status(p.status, STATUS_TIMEOUT, 3, stage);
@@ -584,7 +594,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     if (p.residual) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.residual) | static_cast<uintptr_t>(static_cast<size_t>(p.ld_res) * 2)) & 15) == 0;
     int it = 0;
     long long t_twait = 0, t_work = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++it) {
+      const int tile = item % num_tiles;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int m0 = tile_m_index(p, tile, tiles_m, tiles_n) * BM;
@@ -705,7 +716,8 @@ static int launch_variant(const GemmMaps& maps, const GemmParams& p, int num_sms
   const int tiles_m = p.conv_taps > 0 ? p.conv_tiles_m : (p.M + BM - 1) / BM;
   const int bn_eff = p.pair_offset > 0 ? BN / 2 : BN;
   const int tiles_n = (p.N + bn_eff - 1) / bn_eff;
-  int grid = tiles_m * tiles_n;
+  if (p.split_k > 1 && p.kblocks[0] < p.split_k) return -10;
+  int grid = tiles_m * tiles_n * (p.split_k > 1 ? p.split_k : 1);
   if (grid > num_sms) grid = num_sms;
   if (grid < 1) return 0;
   kern<<<grid, NUM_THREADS, SMEM, stream>>>(maps, p);
@@ -817,6 +829,14 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   p.reduce_src_rank = a->reduce_src_rank;
+  p.split_k = a->split_k > 1 ? a->split_k : 1;
+  if (p.split_k > 1) {
+    // parts are summed with red.add into a zeroed fp32 output: no epilogue math, one K segment, plain output
+    if (!a->out_fp32 || a->num_seg != 1 || a->bias || a->residual || a->gate || a->act || a->row_scale || a->col_scale ||
+        a->pair_offset > 0 || a->conv_taps > 0 || a->gather_world > 1 || a->reduce_rows_per_owner > 0 ||
+        a->route_owner_cols > 0 || a->accumulate_out)
+      return -10;
+  }
   if (a->reduce_rows_per_owner > 0 && !a->out_fp32 && (a->reduce_src_rank < 0 || a->reduce_src_rank >= MDB_GEMM_MAX_PEERS)) return -9;
   p.conv_taps = a->conv_taps;
   if (a->conv_taps > 0) {

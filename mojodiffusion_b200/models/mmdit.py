@@ -146,9 +146,10 @@ class DoubleStreamBlock(nn.Module):
             ops.qk_norm_rope(qkv[:, :S_txt], H, Dh, wqt, wkt, cos, sin, pos_offset=0)
             ops.qk_norm_rope(qkv[:, S_txt:], H, Dh, wqi, wki, cos, sin, pos_offset=S_txt)
         else:
-            qt = ops.qk_norm_rope(self.txt_attn.qkv(txt_n), H, Dh, wqt, wkt, cos, sin, pos_offset=0)
-            qi = ops.qk_norm_rope(self.img_attn.qkv(img_n), H, Dh, wqi, wki, cos, sin, pos_offset=S_txt)
-            qkv = torch.cat((qt, qi), dim=1)
+            # training path: one packed projection buffer, norm/rope + attention as a single autograd node
+            qkv = torch.cat((self.txt_attn.qkv(txt_n), self.img_attn.qkv(img_n)), dim=1)
+            attn = ops.qkv_attention(qkv, H, Dh, wqi, wki, cos, sin, split=S_txt, wq_first=wqt, wk_first=wkt)
+            qkv = None
         if qkv is not None:
             q = qkv[..., 0:D].unflatten(-1, (H, Dh))
             k = qkv[..., D:2 * D].unflatten(-1, (H, Dh))
@@ -200,9 +201,10 @@ class SingleStreamBlock(nn.Module):
             mlp = ops.linear(xn, w1[3 * D:], b1[3 * D:] if b1 is not None else None, act="gelu_tanh")
             ops.qk_norm_rope(qkv, H, Dh, wq, wk, cos, sin)
         else:
-            h = self.linear1(xn)
-            qkv = ops.qk_norm_rope(h[..., :3 * D], H, Dh, wq, wk, cos, sin)
-            mlp = ops.activation(h[..., 3 * D:].contiguous(), "gelu_tanh")
+            qkv_pre, mlp_pre = ops.split_cols(self.linear1(xn), 3 * D)
+            attn = ops.qkv_attention(qkv_pre, H, Dh, wq, wk, cos, sin)
+            mlp = ops.activation(mlp_pre, "gelu_tanh")
+            return self.linear2(torch.cat((attn, mlp), dim=-1), residual=x, gate=gate, rows_per_group=S)
         q = qkv[..., 0:D].unflatten(-1, (H, Dh))
         k = qkv[..., D:2 * D].unflatten(-1, (H, Dh))
         v = qkv[..., 2 * D:3 * D].unflatten(-1, (H, Dh))

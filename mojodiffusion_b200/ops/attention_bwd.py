@@ -40,7 +40,14 @@ def backward_math(q, k, v, o, lse, do, scale, kv_len=None):
     return dq, dk, dv
 
 
-def backward(q, k, v, o, lse, do, scale, kv_len=None):
+def backward(q, k, v, o, lse, do, scale, kv_len=None, outs=None):
+    """``outs``: optional (dq, dk, dv) views to fill (e.g. the column ranges of one packed gradient buffer)."""
     if q.is_cuda and native.available() and hasattr(torch.ops.mdb200, "attention_bwd"):
-        return torch.ops.mdb200.attention_bwd(q, k, v, o, lse, do.contiguous(), scale, kv_len)
-    return backward_math(q, k, v, o, lse, do, scale, kv_len)
+        if do.stride(-1) != 1:
+            do = do.contiguous()
+        return torch.ops.mdb200.attention_bwd(q, k, v, o, lse, do, scale, kv_len, list(outs) if outs is not None else [])
+    dq, dk, dv = backward_math(q, k, v, o, lse, do, scale, kv_len)
+    if outs is not None:
+        outs[0].copy_(dq), outs[1].copy_(dk), outs[2].copy_(dv)
+        return outs
+    return dq, dk, dv

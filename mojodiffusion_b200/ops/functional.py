@@ -19,7 +19,7 @@ from .reference import act_code
 __all__ = [
     "linear", "linear_glu", "lora_linear", "attention", "norm_modulate", "qk_norm_rope", "rope_table", "activation",
     "glu", "gate_residual", "cfg_euler", "flow_match", "mse_loss", "randn", "fp8_quant_rows", "fp8_dequant",
-    "fp8_linear",
+    "fp8_linear", "qkv_attention", "split_cols",
 ]
 
 
@@ -37,10 +37,29 @@ def _flat2d(x: torch.Tensor) -> torch.Tensor:
 def _gemm(As, Bs, bias=None, residual=None, gate=None, rows_per_group=1, act=0, pair_offset=0, act_on_second=0,
           out=None, out_fp32=False, a_mn=False, b_mn=False, row_scale=None, col_scale=None, alpha=1.0,
           accumulate=False, bn=0, prof=None, route_ptrs=(), route_cfg=(), gather_ptrs=(), gather_cfg=(),
-          gather_dst=None, gather_ready=None):
+          gather_dst=None, gather_ready=None, split_k=0):
     return _ops().gemm(list(As), list(Bs), bias, residual, gate, rows_per_group, act, pair_offset, act_on_second, out,
                        out_fp32, a_mn, b_mn, row_scale, col_scale, alpha, accumulate, bn, prof, list(route_ptrs),
-                       list(route_cfg), list(gather_ptrs), list(gather_cfg), gather_dst, gather_ready)
+                       list(route_cfg), list(gather_ptrs), list(gather_cfg), gather_dst, gather_ready, split_k)
+
+
+_NUM_SMS = 148
+
+
+def _gemm_skinny(A, B, a_mn=False, b_mn=False, alpha=1.0):
+    """GEMM whose output has far fewer tiles than the GPU has SMs (LoRA down-projections and their gradients: N or M
+    of 16..64 against a long reduction): the reduction is split across the idle SMs and the parts are added in fp32."""
+    M = A.shape[1] if a_mn else A.shape[0]
+    N = B.shape[1] if b_mn else B.shape[0]
+    K = A.shape[0] if a_mn else A.shape[1]
+    tiles = ((M + 127) // 128) * ((N + 63) // 64)
+    kblocks = (K + 63) // 64
+    split = min(_NUM_SMS // max(tiles, 1), kblocks // 4, 16)
+    if split <= 1:
+        return _gemm([A], [B], a_mn=a_mn, b_mn=b_mn, alpha=alpha)
+    out = torch.zeros(M, N, dtype=torch.float32, device=A.device)
+    _gemm([A], [B], a_mn=a_mn, b_mn=b_mn, alpha=alpha, out=out, out_fp32=True, split_k=split, bn=64)
+    return out.to(A.dtype)
 
 
 # --------------------------------------------------------------------------------------------
@@ -72,7 +91,7 @@ class _LoraLinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x2, w, bias, A, B, scale):
-        t = _gemm([x2], [A])                       # [M, r]
+        t = _gemm_skinny(x2, A)                    # [M, r]
         Bs = (B.float() * scale).to(B.dtype)       # [N, r]
         y = _gemm([x2, t], [w, Bs], bias=bias)
         ctx.save_for_backward(x2, w, A, B, t, Bs)
@@ -85,7 +104,7 @@ class _LoraLinearFn(torch.autograd.Function):
         x2, w, A, B, t, Bs = ctx.saved_tensors
         dy = _flat2d(dy)
         dx = dw = db = dA = dB = None
-        dt = _gemm([dy], [Bs], b_mn=True)          # [M, r] (already scaled)
+        dt = _gemm_skinny(dy, Bs, b_mn=True)       # [M, r] (already scaled)
         if ctx.needs_input_grad[0]:
             dx = _gemm([dy, dt], [w, A], b_mn=True)
         if ctx.needs_input_grad[1]:
@@ -93,9 +112,9 @@ class _LoraLinearFn(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy.float().sum(0).to(dy.dtype)
         if ctx.needs_input_grad[3]:
-            dA = _gemm([dt], [x2], a_mn=True, b_mn=True)              # [r, K]
+            dA = _gemm_skinny(dt, x2, a_mn=True, b_mn=True)           # [r, K]
         if ctx.needs_input_grad[4]:
-            dB = _gemm([dy], [t], a_mn=True, b_mn=True, alpha=ctx.scale)  # [N, r]
+            dB = _gemm_skinny(dy, t, a_mn=True, b_mn=True, alpha=ctx.scale)  # [N, r]
         return dx, dw, db, dA, dB, None
 
 
@@ -269,6 +288,89 @@ class _AttentionFn(torch.autograd.Function):
         from . import attention_bwd
         dq, dk, dv = attention_bwd.backward(q, k, v, o, lse, do, ctx.scale, kv_len if ctx.has_len else None)
         return dq, dk, dv, None, None
+
+
+class _QKVAttentionFn(torch.autograd.Function):
+    """Packed projection buffer -> per-head QK-RMSNorm + RoPE -> attention, as ONE autograd node: the backward writes
+    dq / dk / dv straight into the three column ranges of a single gradient buffer and runs the norm/rope backward in
+    place on it, so no slice, cat or zero-fill kernels appear around the attention of a training step."""
+
+    @staticmethod
+    def forward(ctx, qkv, wq_a, wk_a, wq_b, wk_b, cos, sin, H, Dh, split, interleaved, scale, eps):
+        B, S, W = qkv.shape
+        D = H * Dh
+        post = qkv.clone(memory_format=torch.contiguous_format)
+        o_ = _ops()
+        if split > 0:
+            o_.qk_norm_rope(post[:, :split], wq_a, wk_a, cos, sin, H, Dh, 0, D, eps, interleaved, False, True, 0, 0)
+        if split < S:
+            o_.qk_norm_rope(post[:, split:], wq_b, wk_b, cos, sin, H, Dh, 0, D, eps, interleaved, False, True, 0, split)
+        q, k, v = (post[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3))
+        out, lse = o_.attention_fwd(q, k, v, scale, None, True, None, [], [], [])
+        ctx.save_for_backward(qkv, post, out, lse, wq_a, wk_a, wq_b, wk_b, cos, sin)
+        ctx.cfg = (H, Dh, split, interleaved, scale, eps)
+        return out.reshape(B, S, D)
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, post, out, lse, wq_a, wk_a, wq_b, wk_b, cos, sin = ctx.saved_tensors
+        H, Dh, split, interleaved, scale, eps = ctx.cfg
+        B, S, W = post.shape
+        D = H * Dh
+        from . import attention_bwd
+        q, k, v = (post[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3))
+        d = torch.empty_like(post)
+        outs = [d[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3)]
+        attention_bwd.backward(q, k, v, out, lse, do.reshape(B, S, H, Dh), scale, None, outs)
+        pre = qkv if qkv.stride() == d.stride() else qkv.contiguous()
+        o_ = _ops()
+        if split > 0:
+            o_.qk_norm_rope_bwd(d[:, :split], pre[:, :split], wq_a, wk_a, cos, sin, H, Dh, 0, D, eps, interleaved, True, 0, 0)
+        if split < S:
+            o_.qk_norm_rope_bwd(d[:, split:], pre[:, split:], wq_b, wk_b, cos, sin, H, Dh, 0, D, eps, interleaved, True, 0, split)
+        return (d,) + (None,) * 12
+
+
+def qkv_attention(qkv: torch.Tensor, H: int, Dh: int, wq, wk, cos, sin, split: int = 0, wq_first=None, wk_first=None,
+                  interleaved: bool = True, scale: Optional[float] = None, eps: float = 1e-6) -> torch.Tensor:
+    """Joint attention on a packed projection buffer qkv [B, S, 3*H*Dh] (q | k | v, each (head, Dh)): QK-RMSNorm + RoPE
+    then attention; returns [B, S, H*Dh]. Rows before ``split`` use the norm weights ``wq_first`` / ``wk_first`` (the text
+    stream of a joint block), the rest ``wq`` / ``wk``. Token t uses rotary row t."""
+    B, S, W = qkv.shape
+    D = H * Dh
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(Dh)
+    wq_first = wq if wq_first is None else wq_first
+    wk_first = wk if wk_first is None else wk_first
+    if native.use_native(qkv) and torch.is_grad_enabled() and qkv.requires_grad:
+        return _QKVAttentionFn.apply(qkv, wq_first, wk_first, wq, wk, cos, sin, H, Dh, split, interleaved, scale, eps)
+    if split > 0:
+        a = qk_norm_rope(qkv[:, :split], H, Dh, wq_first, wk_first, cos, sin, eps, interleaved, pos_offset=0)
+        b = qk_norm_rope(qkv[:, split:], H, Dh, wq, wk, cos, sin, eps, interleaved, pos_offset=split)
+        # without autograd the GPU kernel has normalised the two row ranges of ``qkv`` in place
+        post = qkv if (native.use_native(qkv) and not (torch.is_grad_enabled() and qkv.requires_grad)) else torch.cat((a, b), dim=1)
+    else:
+        post = qk_norm_rope(qkv, H, Dh, wq, wk, cos, sin, eps, interleaved)
+    q, k, v = (post[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3))
+    return attention(q, k, v, scale).reshape(B, S, D)
+
+
+class _SplitColsFn(torch.autograd.Function):
+    """[.., a + b] -> contiguous ([.., a], [.., b]); the backward is one concatenation (no zero-filled buffers)."""
+
+    @staticmethod
+    def forward(ctx, x, a):
+        ctx.a = a
+        return x[..., :a].contiguous(), x[..., a:].contiguous()
+
+    @staticmethod
+    def backward(ctx, ga, gb):
+        return torch.cat((ga, gb), dim=-1), None
+
+
+def split_cols(x: torch.Tensor, a: int):
+    if torch.is_grad_enabled() and x.requires_grad:
+        return _SplitColsFn.apply(x, a)
+    return x[..., :a], x[..., a:]
 
 
 def attention(q, k, v, scale: Optional[float] = None, kv_len: Optional[torch.Tensor] = None,

@@ -51,7 +51,7 @@ def test_gemm_tile_variants(bn):
     M, N, K = 384, 768, 320
     x, w = _rand(M, K, seed=3), _rand(N, K, scale=1 / math.sqrt(K), seed=4)
     out = torch.ops.mdb200.gemm([x], [w], None, None, None, 1, 0, 0, 0, None, False, False, False, None, None, 1.0,
-                                False, bn, None, [], [], [], [], None, None)
+                                False, bn, None, [], [], [], [], None, None, 0)
     _check(out, ref.linear(x, w, out_dtype=torch.float32), name=f"bn{bn}")
 
 
@@ -95,14 +95,14 @@ def test_gemm_backward_majors():
     w = _rand(N, K, scale=0.05, seed=19)
     dy = _rand(M, N, seed=20)
     dx = torch.ops.mdb200.gemm([dy], [w], None, None, None, 1, 0, 0, 0, None, False, False, True, None, None, 1.0,
-                               False, 0, None, [], [], [], [], None, None)
+                               False, 0, None, [], [], [], [], None, None, 0)
     _check(dx, dy.float() @ w.float(), name="dx (B MN-major)")
     dw = torch.ops.mdb200.gemm([dy], [x], None, None, None, 1, 0, 0, 0, None, False, True, True, None, None, 1.0,
-                               False, 0, None, [], [], [], [], None, None)
+                               False, 0, None, [], [], [], [], None, None, 0)
     _check(dw, dy.float().t() @ x.float(), name="dW (A,B MN-major)")
     for bn in (64, 128, 256):
         dx = torch.ops.mdb200.gemm([dy], [w], None, None, None, 1, 0, 0, 0, None, False, False, True, None, None, 1.0,
-                                   False, bn, None, [], [], [], [], None, None)
+                                   False, bn, None, [], [], [], [], None, None, 0)
         _check(dx, dy.float() @ w.float(), name=f"dx bn{bn}")
 
 
@@ -335,3 +335,47 @@ def test_adamw_master_weights_and_ema_kernel():
         assert torch.equal(p.detach(), m.bfloat16())             # the model tensor is the rounded master
     for s, sr in zip(ema.shadow, shadow_ref):
         _check(s, sr, cos=0.999999, rel=1e-5, name="ema")
+
+
+def test_gemm_split_k_skinny_shapes():
+    """Skinny GEMMs (LoRA down-projection and its gradients) with the reduction split over idle SMs."""
+    from mojodiffusion_b200.ops.functional import _gemm_skinny
+    M, K, r, N = 1152, 3072, 16, 3072
+    x, A = _rand(M, K, seed=11), _rand(r, K, scale=1 / math.sqrt(K), seed=12)
+    _check(_gemm_skinny(x, A), ref.linear(x, A, out_dtype=torch.float32), name="down x@A^T")
+    dy, t = _rand(M, N, seed=13), _rand(M, r, seed=14)
+    Bs = _rand(N, r, scale=1 / math.sqrt(r), seed=15)
+    _check(_gemm_skinny(dy, Bs, b_mn=True), dy.float() @ Bs.float(), name="dt = dy@B")
+    _check(_gemm_skinny(t, x, a_mn=True, b_mn=True), t.float().t() @ x.float(), rel=3e-2, name="dA = t^T x")
+    _check(_gemm_skinny(dy, t, a_mn=True, b_mn=True, alpha=0.5), 0.5 * (dy.float().t() @ t.float()), rel=3e-2, name="dB = dy^T t")
+
+
+def test_packed_qkv_attention_matches_composed_ops():
+    """The single-node norm/rope + attention path: forward and gradient equal the composed differentiable ops."""
+    B, S_txt, S_img, H, Dh = 1, 64, 192, 4, 128
+    S, D = S_txt + S_img, H * Dh
+    qkv0 = _rand(B, S, 3 * D, seed=21)
+    wqa, wka, wqb, wkb = (1.0 + 0.1 * _rand(Dh, seed=22 + i) for i in range(4))
+    pos = torch.stack([torch.zeros(S), torch.arange(S).float(), torch.arange(S).float() * 0.5], 1).to(DEV)
+    cos, sin = O.rope_table(pos, [16, 56, 56], 10000.0)
+    go = _rand(B, S, D, seed=30)
+    outs, grads = [], []
+    for packed in (True, False):
+        qkv = qkv0.clone().requires_grad_(True)
+        if packed:
+            o = O.qkv_attention(qkv, H, Dh, wqb, wkb, cos, sin, split=S_txt, wq_first=wqa, wk_first=wka)
+        else:
+            a = O.qk_norm_rope(qkv[:, :S_txt], H, Dh, wqa, wka, cos, sin, pos_offset=0)
+            b = O.qk_norm_rope(qkv[:, S_txt:], H, Dh, wqb, wkb, cos, sin, pos_offset=S_txt)
+            p = torch.cat((a, b), 1)
+            q, k, v = (p[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3))
+            o = O.attention(q, k, v).reshape(B, S, D)
+        o.backward(go)
+        outs.append(o.detach())
+        grads.append(qkv.grad.detach())
+    assert torch.equal(outs[0], outs[1])
+    _check(grads[0], grads[1].float(), cos=0.99999, rel=1e-2, name="packed dqkv")
+    h = _rand(B, S, 3 * D + 256, seed=40).requires_grad_(True)
+    a, b = O.split_cols(h, 3 * D)
+    (a.float().sum() * 2 + b.float().sum() * 3).backward()
+    assert a.is_contiguous() and torch.equal(h.grad[..., :3 * D], torch.full_like(a, 2)) and torch.equal(h.grad[..., 3 * D:], torch.full_like(b, 3))
