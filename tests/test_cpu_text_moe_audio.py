@@ -1,0 +1,139 @@
+"""Text encoders against the Hugging Face implementations (tiny random configs, same weights), tokenizers on synthetic
+vocabularies, MoE primitives against a per-token loop, audio ops identities."""
+import json
+
+import pytest
+import torch
+
+from mojodiffusion_b200.models.text import (ByteLevelBPE, CLIPTextConfig, CLIPTextEncoder, CLIPTokenizer, Qwen3Config, Qwen3Encoder,
+                                            T5Config, T5Encoder)
+from mojodiffusion_b200.models.text.tokenizers import bytes_to_unicode
+from mojodiffusion_b200.models.vocoder import Vocoder, tiny_vocoder_config
+from mojodiffusion_b200.ops import audio, moe
+
+transformers = pytest.importorskip("transformers")
+
+
+def test_clip_text_encoder_matches_hf():
+    torch.manual_seed(0)
+    hc = transformers.CLIPTextConfig(vocab_size=99, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                                     max_position_embeddings=16, eos_token_id=98, bos_token_id=97, pad_token_id=98)
+    hf = transformers.CLIPTextModel(hc).eval()
+    mine = CLIPTextEncoder(CLIPTextConfig(99, 32, 64, 3, 4, 16, "quick_gelu", 1e-5, 98))
+    missing, unexpected = mine.load_state_dict(hf.state_dict(), strict=False)
+    assert not missing and all("position_ids" in u for u in unexpected)
+    ids = torch.tensor([[97, 5, 6, 7, 98, 98, 98, 98], [97, 9, 98, 98, 98, 98, 98, 98]])
+    with torch.no_grad():
+        ref = hf(ids)
+    last, pooled = mine(ids)
+    assert torch.allclose(last, ref.last_hidden_state, atol=1e-5) and torch.allclose(pooled, ref.pooler_output, atol=1e-5)
+
+
+def test_t5_encoder_matches_hf():
+    torch.manual_seed(0)
+    hc = transformers.T5Config(vocab_size=64, d_model=32, d_kv=8, d_ff=48, num_layers=3, num_heads=4, feed_forward_proj="gated-gelu",
+                               relative_attention_num_buckets=8, relative_attention_max_distance=16)
+    hf = transformers.T5EncoderModel(hc).eval()
+    mine = T5Encoder(T5Config(64, 32, 8, 48, 3, 4, 8, 16, 1e-6))
+    missing, unexpected = mine.load_state_dict(hf.state_dict(), strict=False)
+    assert not missing and all("embed_tokens" in u for u in unexpected)
+    ids = torch.randint(2, 64, (2, 11))
+    mask = torch.ones(2, 11, dtype=torch.long)
+    mask[1, 7:] = 0
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=mask).last_hidden_state
+    out = mine(ids, mask)
+    assert torch.allclose(out[0], ref[0], atol=2e-5) and torch.allclose(out[1, :7], ref[1, :7], atol=2e-5)
+
+
+def test_qwen3_encoder_matches_hf():
+    if not hasattr(transformers, "Qwen3Model"):
+        pytest.skip("transformers without Qwen3")
+    torch.manual_seed(0)
+    hc = transformers.Qwen3Config(vocab_size=80, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                                  num_key_value_heads=2, head_dim=8, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=64)
+    hf = transformers.Qwen3Model(hc).eval()
+    mine = Qwen3Encoder(Qwen3Config(80, 32, 64, 3, 4, 2, 8, 1e-6, 10000.0))
+    sd = {"model." + k: v for k, v in hf.state_dict().items()}
+    missing, unexpected = mine.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 80, (2, 9))
+    with torch.no_grad():
+        ref = hf(input_ids=ids, output_hidden_states=True)
+    assert torch.allclose(mine(ids), ref.last_hidden_state, atol=2e-5)
+    assert torch.allclose(mine(ids, layer=-2, final_norm=False), ref.hidden_states[-2], atol=2e-5)
+
+
+def test_tokenizers_on_synthetic_vocab(tmp_path):
+    b2u = bytes_to_unicode()
+    assert len(b2u) == 256 and len(set(b2u.values())) == 256
+    base = [b2u[b] for b in range(256)]
+    vocab = {}
+    for s in base + [c + "</w>" for c in base]:
+        vocab.setdefault(s, len(vocab))
+    merges = [("c", "a"), ("ca", "t</w>"), ("d", "o"), ("do", "g</w>")]
+    for a, b in merges:
+        vocab.setdefault(a + b, len(vocab))
+    vocab["<|startoftext|>"], vocab["<|endoftext|>"] = len(vocab), len(vocab) + 1
+    json.dump(vocab, open(tmp_path / "vocab.json", "w"))
+    open(tmp_path / "merges.txt", "w").write("#version: 0.2\n" + "\n".join(f"{a} {b}" for a, b in merges) + "\n")
+    tok = CLIPTokenizer.from_files(str(tmp_path / "vocab.json"), str(tmp_path / "merges.txt"), max_length=12)
+    ids, mask = tok("A  Cat, dog!")
+    assert ids[0] == vocab["<|startoftext|>"] and len(ids) == 12 and sum(mask) == 7
+    assert vocab["cat</w>"] in ids and vocab["dog</w>"] in ids and ids[sum(mask) - 1] == vocab["<|endoftext|>"]
+    assert tok.decode(ids[:sum(mask)]) == "a cat , dog !"
+    bv = {s: i for i, s in enumerate(base)}
+    bm = [("h", "e"), ("l", "l"), ("he", "ll"), ("Ġ", "w")]
+    for a, b in bm:
+        bv.setdefault(a + b, len(bv))
+    bl = ByteLevelBPE(bv, bm, {"<|im_start|>": 1000, "<|im_end|>": 1001})
+    text = "<|im_start|>hello wörld\n<|im_end|>"
+    enc = bl.encode(text)
+    assert enc[0] == 1000 and enc[-1] == 1001 and bv["hell"] in enc and bv["Ġw"] in enc
+    assert bl.decode(enc) == text
+    assert "<|im_start|>user\nhi<|im_end|>" in bl.chat_template("hi")
+
+
+def test_moe_primitives():
+    torch.manual_seed(0)
+    T, H, E, Fd, k = 37, 16, 4, 24, 2
+    x, rw = torch.randn(T, H), torch.randn(E, H)
+    gw, uw, dw = torch.randn(E, Fd, H) * 0.2, torch.randn(E, Fd, H) * 0.2, torch.randn(E, H, Fd) * 0.2
+    ids, gating = moe.top_k_router(torch.tensor([[1.0, 3.0, 3.0, 0.0]]), 2)
+    assert ids.tolist() == [1, 2] and torch.allclose(gating, torch.tensor([0.5, 0.5]))      # tie -> lower expert first
+    y = moe.moe_ffn(x, rw, gw, uw, dw, k)
+    top = (x @ rw.T).topk(k, dim=1)
+    g = torch.softmax(top.values, 1)
+    ref = torch.zeros_like(x)
+    for t in range(T):
+        for j in range(k):
+            e = int(top.indices[t, j])
+            ref[t] += g[t, j] * ((torch.nn.functional.silu(x[t] @ gw[e].T) * (x[t] @ uw[e].T)) @ dw[e].T)
+    assert torch.allclose(y, ref, atol=1e-5)
+    acc = torch.zeros(3, 2)
+    moe.gated_scatter_add(torch.ones(4, 2), torch.tensor([1.0, 2.0, 3.0, 4.0]), torch.tensor([0, 0, 2, 7]), acc)
+    assert acc.tolist() == [[3.0, 3.0], [0.0, 0.0], [3.0, 3.0]]
+
+
+def test_audio_ops_and_vocoder():
+    torch.manual_seed(0)
+    x, w = torch.randn(2, 8, 50), torch.randn(8, 4, 5)
+    a = audio.conv_transpose1d(x, w, None, stride=3, padding=1)
+    b = audio.conv_transpose1d(x, w, None, stride=3, padding=1, zero_insert=True)
+    assert a.shape == b.shape == (2, 4, 150) and torch.allclose(a, b, atol=1e-4)
+    assert audio.zero_insert1d(torch.ones(1, 1, 3), 2).flatten().tolist() == [1, 0, 1, 0, 1]
+    assert audio.replicate_pad1d(torch.tensor([[[1.0, 2.0]]]), 2, 1).flatten().tolist() == [1, 1, 1, 2, 2]
+    sig = torch.randn(1, 1024)
+    m, p = audio.stft(sig, 64, 16)
+    assert torch.allclose(audio.istft(m, p, 64, 16, length=1024), sig, atol=1e-4)
+    fb = audio.mel_filterbank(10, 64, 16000)
+    assert fb.shape == (10, 33) and (fb >= 0).all() and (fb.sum(1) > 0).all()
+    assert audio.log_mel(sig, 64, 16, 10, 16000).shape[1] == 10
+    s = audio.snake(torch.tensor([[[0.5]]]), torch.zeros(1), None)
+    assert abs(float(s) - (0.5 + torch.sin(torch.tensor(0.5)) ** 2)) < 1e-6
+    v = Vocoder(tiny_vocoder_config())
+    wav = v(torch.randn(1, 16, 10))
+    assert wav.shape == (1, 10 * v.hop) and wav.abs().max() <= 1.0
+    import dataclasses
+    v2 = Vocoder(dataclasses.replace(tiny_vocoder_config(), istft_head=True))
+    assert v2(torch.randn(1, 16, 10)).dim() == 2
