@@ -17,7 +17,7 @@ from mojodiffusion_b200.ops import native  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
     ap.add_argument("--shape", default="")
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
@@ -58,6 +58,60 @@ def main():
         torch.cuda.synchronize()
         native.check_status()
         print("MARK end", torch.ops.mdb200.launch_count())
+        print("ok")
+        return
+    if a.op in ("tp_fused_local", "ulysses_fused_local", "dp_fused_local"):
+        # The fused compute+collective kernels of one rank of a 4-rank group, with every "peer" buffer living on this
+        # GPU (a profiler is never put around a multi-rank run): same code paths, pointer tables and byte counts as
+        # rank 0 of a real group; the transfers go through local memory instead of NVLink.
+        from mojodiffusion_b200.ops.functional import _gemm
+        world, r = 4, 0
+        if a.op == "tp_fused_local":
+            rows, D, Fh = dims or [6144, 4096, 16384]
+            rl, fl = rows // world, Fh // world
+            x_all = [torch.randn(rows, D, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+            stage = [torch.empty(world, rl, D, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+            w1 = torch.randn(fl, D, device=dev, dtype=torch.bfloat16) * 0.02
+            w2 = torch.randn(D, fl, device=dev, dtype=torch.bfloat16) * 0.02
+            ready = torch.zeros(8, dtype=torch.int32, device=dev)
+            chunk = rl * D * 2
+            gptrs = [x_all[c].data_ptr() + c * chunk for c in range(world)]
+
+            def fn():
+                h = _gemm([x_all[r]], [w1], act=1, gather_ptrs=gptrs, gather_cfg=[r, 0, rl, chunk], gather_dst=x_all[r], gather_ready=ready)
+                _gemm([h], [w2], route_ptrs=[s_.data_ptr() for s_ in stage], route_cfg=[rl, D, r])
+        elif a.op == "ulysses_fused_local":
+            B, S_txt, S_img, H, Dh = 1, 512, 4096, 24, 128
+            S, D, Hl = S_txt + S_img, 24 * 128, 24 // world
+            Dl, Si = Hl * Dh, S_img // world
+            qkv_g = [torch.zeros(B, S, 3 * Dl, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+            attn_x = [torch.zeros(B, (S_txt + S_img) // world, D, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+            x = torch.randn(Si, D, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(3 * D, D, device=dev, dtype=torch.bfloat16) * 0.02
+            g = qkv_g[r]
+            g.copy_(torch.randn_like(g))
+            q, k, v = (g[..., i * Dl:(i + 1) * Dl].unflatten(-1, (Hl, Dh)) for i in range(3))
+            St = S_txt // world
+            ra = [t.data_ptr() + r * Dl * 2 for t in attn_x]
+            rb = [t.data_ptr() + St * D * 2 + r * Dl * 2 for t in attn_x]
+
+            def fn():
+                _gemm([x], [w], route_ptrs=[t.data_ptr() for t in qkv_g], route_cfg=[Dl, D, S_txt + r * Si, Si, S, 3 * Dl])
+                torch.ops.mdb200.attention_fwd(q, k, v, 1.0 / Dh ** 0.5, None, False, None, ra, rb,
+                                               [St, S_txt, Si, (St + Si) * D, D, Dh])
+        else:
+            from mojodiffusion_b200.parallel.fused_dp import emulate_ranks, emulated_step
+            numel = dims[0] if dims else 88473600
+            sets = [[torch.nn.Parameter(torch.randn(numel, device=dev, dtype=torch.bfloat16))] for _ in range(world)]
+            ranks = emulate_ranks(sets, lr=1e-4, max_grad_norm=1.0)
+            for rk in ranks:
+                rk.flat_grads.normal_()
+            fn = lambda: emulated_step(ranks)
+        for _ in range(a.iters):
+            flush.zero_()
+            fn()
+        torch.cuda.synchronize()
+        native.check_status()
         print("ok")
         return
     if a.op in ("gemm", "gemm_fp8"):
