@@ -29,7 +29,9 @@ def _parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"],
+                    help="ours: the sm_100a kernels; reference: the upstream project (not installable offline); torch: the same "
+                         "model code with every op routed to PyTorch library kernels (cuBLAS, SDPA, NCCL) as a same-box baseline")
     ap.add_argument("--batch", type=int, default=1, help="images per GPU")
     ap.add_argument("--model", default="flux1-dev", choices=["flux1-dev", "tiny"])
     ap.add_argument("--train-steps", type=int, default=-1, help="LoRA train steps to time (-1: min(steps, 4); 0: skip)")
@@ -97,8 +99,12 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
                           "unavailable": "reference is Mojo/MAX source with no setup.py/pyproject.toml: pip reports "
-                                         "'/root/reference is not installable'; no mojo/pixi toolchain offline"}))
+                                         "'Directory is not installable'; no mojo/pixi toolchain offline"}))
         return 0
+    lib_baseline = args.impl == "torch"
+    if lib_baseline:
+        os.environ["MDB200_FORCE_REFERENCE"] = "1"
+        args.sp_mode = "nccl"
 
     import torch
     import torch.distributed as dist
@@ -119,6 +125,8 @@ def main():
         pdist.init_from_env("nccl")
     native.load(True)
     launches = torch.ops.mdb200.launch_count
+    if lib_baseline and world > 1 and args.train_steps != 0:
+        args.no_e2e = True   # library baseline at N > 1: data-parallel training only (no library Ulysses path is kept)
 
     cfg = flux1_dev_config() if args.model == "flux1-dev" else tiny_mmdit_config()
     S_img, S_txt = (4096, 512) if args.model == "flux1-dev" else (256, 64)
@@ -127,7 +135,7 @@ def main():
     model = MMDiT(cfg, dtype=torch.bfloat16, device=dev).init_weights(0)
     model.eval()
     sp = None
-    if world > 1:
+    if world > 1 and not lib_baseline:
         from mojodiffusion_b200.parallel.ulysses import UlyssesContext
         sp = UlyssesContext(B, S_txt, S_img, cfg.heads, cfg.head_dim, mode=args.sp_mode, device=dev)
     pipe = FluxPipeline(model, dev, sp=sp, use_cuda_graph=not args.no_graph)
@@ -144,6 +152,9 @@ def main():
     K, W = args.steps, max(args.warmup, 0)
 
     # ------------------------------------------------------------------ device-timed denoise loop
+    do_denoise = not (lib_baseline and world > 1)
+    ms = it_per_s = clocks = launches_per_step = None
+    n_launch = 0
     x = x_host.to(dev)
     txt = txt_host.to(dev)
     y = y_host.to(dev)
@@ -160,43 +171,43 @@ def main():
             v = pipe._forward(xb, txt, tvec, y, gvec, ids)
             ops.cfg_euler(x, v, None, dt=float(s_next - s), mode=0, x_bf16=xb)
 
-    for i in range(max(W, 1)):
-        denoise_step(i)
-    torch.cuda.synchronize()
-    pdist.barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    n0 = launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for i in range(K):
-        denoise_step(W + i)
-    e1.record()
-    torch.cuda.synchronize()
-    pdist.barrier()
-    n_launch = launches() - n0
-    clocks = sampler.stop() if rank == 0 else None
-    ms = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
-    native.check_status()
-    assert torch.isfinite(x).all(), "latents diverged"
-    it_per_s = B * 1000.0 / ms  # N > 1: the ranks share ONE batch (Ulysses sequence parallel, strong scaling)
-    launches_per_step = None
-    if not args.no_graph:
-        # kernels inside the replayed graph are not re-counted by the host-side counter: count one eager step
-        pipe_eager = FluxPipeline(model, dev, sp=sp, use_cuda_graph=False)
-        nb = launches()
-        with torch.no_grad():
-            pipe_eager._forward(xb, txt, tvec, y, gvec, ids)
+    if do_denoise:
+        for i in range(max(W, 1)):
+            denoise_step(i)
         torch.cuda.synchronize()
         pdist.barrier()
-        launches_per_step = launches() - nb + 1
-        n_launch = launches_per_step * K
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        n0 = launches()
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(K):
+            denoise_step(W + i)
+        e1.record()
+        torch.cuda.synchronize()
+        pdist.barrier()
+        n_launch = launches() - n0
+        clocks = sampler.stop() if rank == 0 else None
+        ms = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
+        native.check_status()
+        assert torch.isfinite(x).all(), "latents diverged"
+        it_per_s = B * 1000.0 / ms  # N > 1: the ranks share ONE batch (Ulysses sequence parallel, strong scaling)
+        if not args.no_graph and not lib_baseline:
+            # kernels inside the replayed graph are not re-counted by the host-side counter: count one eager step
+            pipe_eager = FluxPipeline(model, dev, sp=sp, use_cuda_graph=False)
+            nb = launches()
+            with torch.no_grad():
+                pipe_eager._forward(xb, txt, tvec, y, gvec, ids)
+            torch.cuda.synchronize()
+            pdist.barrier()
+            launches_per_step = launches() - nb + 1
+            n_launch = launches_per_step * K
 
     # ------------------------------------------------------------------ end-to-end through the public API
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and do_denoise:
         for i in range(min(max(W, 1), 2)):
             pipe.step_from_host(x_host, txt_host, y_host, sigmas[i], sigmas[i + 1], 3.5, out_host, hw)
         torch.cuda.synchronize()
@@ -228,12 +239,32 @@ def main():
         params = L.lora_parameters(slots)
         model.gradient_checkpointing = True
         model.train()
-        if world > 1:
+        dp = None
+        if lib_baseline:
+            class _TorchAdamW:
+                """torch.optim.AdamW (fused) + clip_grad_norm_ behind the trainer's optimizer interface."""
+
+                def __init__(self, ps):
+                    self.ps = ps
+                    self.opt = torch.optim.AdamW(ps, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, fused=True)
+
+                def zero_grad(self, set_to_none=True):
+                    self.opt.zero_grad(set_to_none=set_to_none)
+
+                def step(self, grad_scale=1.0, lr=None):
+                    if grad_scale != 1.0:
+                        torch._foreach_mul_([p.grad for p in self.ps if p.grad is not None], grad_scale)
+                    torch.nn.utils.clip_grad_norm_(self.ps, 1.0)
+                    self.opt.step()
+
+            opt = _TorchAdamW(params)
+            dp = DataParallelGrads(params) if world > 1 else None
+        elif world > 1:
             from mojodiffusion_b200.parallel.fused_dp import FusedDPAdamW
             opt = FusedDPAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
         else:
             opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
-        tr = FlowMatchTrainer(model, params, opt, None)
+        tr = FlowMatchTrainer(model, params, opt, dp)
         gt = torch.Generator().manual_seed(99 + rank)   # data parallel: every rank trains on its own samples
         x0 = torch.randn(B, S_img, cfg.in_channels, generator=gt).to(dev)
         txt = torch.randn(B, S_txt, cfg.context_dim, generator=gt).to(dev, torch.bfloat16)
@@ -254,7 +285,7 @@ def main():
         train = {"metric": "lora_train_samples_per_s", "value": world * B * 1000.0 / ms_t, "unit": "samples/s",
                  "ms_per_step": ms_t, "steps": tsteps, "warmup": 3, "loss": float(loss), "rank": 16,
                  "gpu_launches": launches() - t0n, "gradient_checkpointing": True,
-                 "parallelism": (f"dp{world}, grad reduce-scatter + clip + AdamW + param all-gather fused in peer-memory "
+                 "parallelism": f"dp{world}, NCCL all-reduce + torch AdamW" if (lib_baseline and world > 1) else (f"dp{world}, grad reduce-scatter + clip + AdamW + param all-gather fused in peer-memory "
                                  f"kernels (multicast {'on' if getattr(opt, 'symm', None) is not None and opt.symm.mc_ptr else 'off'})")
                  if world > 1 else "single"}
 
@@ -263,7 +294,7 @@ def main():
             "metric": "flux1-dev-shape 1024^2 denoise it/s (+ LoRA r16 train samples/s in 'lora_train')",
             "value": it_per_s, "unit": "it/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": "ours",
+            "impl": "torch library kernels (cuBLAS, SDPA, NCCL), eager" if lib_baseline else "ours",
             "config": {"model": f"{cfg.name} 12B MMDiT (19 double + 38 single, D=3072, 24x128)" if args.model == "flux1-dev" else cfg.name,
                        "global_batch": B, "seq_len": S_img + S_txt, "image_tokens": S_img, "text_tokens": S_txt,
                        "sampler": "euler flow-match, 28-step BFL-shifted schedule, guidance 3.5 (distilled)",
@@ -273,7 +304,7 @@ def main():
                        "l2": "inputs larger than L2: 24 GB of weights stream every step"},
             "clocks": clocks, "gpu_launches": n_launch, "e2e": e2e, "lora_train": train,
             "published_nearest": PUBLISHED_NEAREST,
-            "vs_published_nearest": it_per_s / PUBLISHED_NEAREST["it_per_s"],
+            "vs_published_nearest": it_per_s / PUBLISHED_NEAREST["it_per_s"] if it_per_s else None,
         }
         print(json.dumps(line))
     if world > 1:

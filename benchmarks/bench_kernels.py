@@ -40,6 +40,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--gemm-only", action="store_true")
     args = ap.parse_args()
     dev = "cuda"
     native.load(True)
@@ -58,13 +59,22 @@ def main():
     for M, N, K in shapes:
         x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        from mojodiffusion_b200.ops.functional import _gemm
         t_ours = timeit(lambda: O.linear(x, w), flush=flush)
+        t_one = timeit(lambda: _gemm([x], [w], bn=256), flush=flush)     # one CTA per 128 x 256 tile
+        t_pair = timeit(lambda: _gemm([x], [w], bn=512), flush=flush)    # CTA pair per 256 x 256 tile
         t_lib = timeit(lambda: torch.matmul(x, w.t()), flush=flush)
         fl = 2.0 * M * N * K
         rows.append({"op": "gemm_bf16", "shape": [M, N, K], "ms": t_ours, "tflops": fl / t_ours / 1e9,
-                     "frac_of_measured_peak": fl / t_ours / 1e9 / peak_tf, "cublas_ms": t_lib,
+                     "frac_of_measured_peak": fl / t_ours / 1e9 / peak_tf, "one_cta_128x256_tflops": fl / t_one / 1e9,
+                     "cta_pair_256x256_tflops": fl / t_pair / 1e9, "cublas_ms": t_lib,
                      "cublas_tflops": fl / t_lib / 1e9})
         print(rows[-1], flush=True)
+    if args.gemm_only:
+        native.check_status()
+        if args.json:
+            json.dump(rows, open(args.json, "w"), indent=1)
+        return
     for B, S, H, Dh in [(1, 4608, 24, 128), (1, 6144, 32, 128), (2, 4096, 24, 128)][: 1 if args.quick else 3]:
         q, k, v = [torch.randn(B, S, H, Dh, device=dev, dtype=torch.bfloat16) for _ in range(3)]
         t_ours = timeit(lambda: O.attention(q, k, v), flush=flush)

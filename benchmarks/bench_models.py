@@ -1,0 +1,209 @@
+#!/usr/bin/env python
+"""Per-model-family step timing on one GPU at the real architecture sizes (random-init weights, synthetic inputs).
+
+Each row is one denoise iteration (model forward + sampler update, no_grad, bf16 unless noted) or one training step,
+device-timed with CUDA events after warm-up; every step streams far more weight bytes than the L2 holds. Counterpart of
+the reference's per-model sampler smokes and trainer step reports (serenitymojo/docs/MODEL_RENDER_CAMPAIGN_2026-06-15.md,
+BEAT_FLAME_SCOREBOARD_2026-06-10.md), which time the same loops on its hardware.
+
+    python benchmarks/bench_models.py [--only ltx2,qwen,zimage,sdxl,vae,zimage_train] [--tiny] [--json out.json]
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from mojodiffusion_b200 import ops  # noqa: E402
+from mojodiffusion_b200.ops import native  # noqa: E402
+
+
+def timed(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def nparams(m):
+    return sum(p.numel() for p in m.parameters()) + sum(b.numel() for b in m.buffers())
+
+
+def bench_ltx2(dev, tiny, steps, warmup, fp8):
+    """LTX-2-shaped 48-layer video DiT, 6144 latent tokens (8 frames x 24 x 32), 256 context tokens, Euler update."""
+    from mojodiffusion_b200.models.video_dit import VideoDiT, ltx2_config, tiny_video_dit_config
+    cfg = tiny_video_dit_config() if tiny else ltx2_config()
+    grid = (2, 4, 8) if tiny else (8, 24, 32)
+    S = grid[0] * grid[1] * grid[2]
+    m = VideoDiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    if fp8:
+        m.to_fp8(0 if tiny else 4, None if tiny else 46)
+    x = torch.randn(1, S, cfg.in_channels, device=dev)
+    xb = x.to(torch.bfloat16)
+    ctx = torch.randn(1, 16 if tiny else 256, cfg.context_dim, device=dev, dtype=torch.bfloat16)
+    t = torch.full((1,), 0.7, device=dev)
+
+    def step():
+        with torch.no_grad():
+            v = m(xb, ctx, t, grid)
+            ops.cfg_euler(x, v, None, dt=-0.025, mode=0, x_bf16=xb)
+
+    ms = timed(step, steps, warmup)
+    return {"model": cfg.name + (" fp8 blocks 4-46" if fp8 else " bf16"), "params_b": nparams(m) / 1e9, "tokens": S,
+            "metric": "denoise it/s", "ms_per_step": ms, "value": 1000.0 / ms}
+
+
+def bench_qwen(dev, tiny, steps, warmup):
+    """Qwen-Image-shaped 60-layer MMDiT (20 B parameters), 1024^2 = 4096 image tokens + 512 text tokens."""
+    from mojodiffusion_b200.models.qwen_image import QwenImageDiT, qwen_image_config, tiny_qwen_image_config
+    cfg = tiny_qwen_image_config() if tiny else qwen_image_config()
+    hw, S_txt = ((8, 8), 16) if tiny else ((64, 64), 512)
+    m = QwenImageDiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    x = torch.randn(1, hw[0] * hw[1], cfg.in_channels, device=dev)
+    xb = x.to(torch.bfloat16)
+    txt = torch.randn(1, S_txt, cfg.context_dim, device=dev, dtype=torch.bfloat16)
+    t = torch.full((1,), 0.7, device=dev)
+
+    def step():
+        with torch.no_grad():
+            v = m(xb, txt, t, hw)
+            ops.cfg_euler(x, v, None, dt=-0.03, mode=0, x_bf16=xb)
+
+    ms = timed(step, steps, warmup)
+    return {"model": cfg.name, "params_b": nparams(m) / 1e9, "tokens": hw[0] * hw[1] + S_txt, "metric": "denoise it/s",
+            "ms_per_step": ms, "value": 1000.0 / ms}
+
+
+def bench_zimage(dev, tiny, steps, warmup, train):
+    """Z-Image-shaped 6 B single-stream DiT: 1024^2 denoise (CFG: two forwards per step), or a 512^2 LoRA r16 step."""
+    from mojodiffusion_b200.models.single_dit import SingleStreamDiT, tiny_single_dit_config, zimage_config
+    cfg = tiny_single_dit_config() if tiny else zimage_config()
+    side = 8 if tiny else (32 if train else 64)
+    S_cap = 16 if tiny else 128
+    m = SingleStreamDiT(cfg, torch.bfloat16, dev).init_weights(0)
+    x = torch.randn(1, side * side, cfg.in_channels, device=dev)
+    cap = torch.randn(1, S_cap, cfg.cap_dim, device=dev, dtype=torch.bfloat16)
+    t = torch.full((1,), 0.6, device=dev)
+    if not train:
+        m.eval()
+        xb = x.to(torch.bfloat16)
+        neg = torch.randn_like(cap)
+
+        def step():
+            with torch.no_grad():
+                vc = m(xb, cap, t, (side, side))
+                vu = m(xb, neg, t, (side, side))
+                ops.cfg_euler(x, vc, vu, dt=-0.03, s=3.5, mode=1, x_bf16=xb)
+
+        ms = timed(step, steps, warmup)
+        return {"model": cfg.name + " CFG 3.5 (2 forwards/step)", "params_b": nparams(m) / 1e9, "tokens": side * side + S_cap,
+                "metric": "denoise it/s", "ms_per_step": ms, "value": 1000.0 / ms}
+    from mojodiffusion_b200.training import lora as L
+    from mojodiffusion_b200.training.optim import FusedAdamW
+    from mojodiffusion_b200.models.layers import Linear
+    names = {n: n for n, mod in m.named_modules() if n.startswith("layers.") and isinstance(mod, Linear) and "adaLN" not in n}
+    slots = L.inject_lora_by_name(m, names, rank=16, alpha=16.0)
+    params = L.lora_parameters(slots)
+    opt = FusedAdamW(params, lr=1e-4, max_grad_norm=1.0)
+    m.gradient_checkpointing = True
+    m.train()
+    eps = torch.randn_like(x)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        xt, target = ops.flow_match(x, eps, t)
+        pred = m(xt.to(torch.bfloat16), cap, t, (side, side))
+        loss = ops.mse_loss(pred, target)
+        loss.backward()
+        opt.step()
+
+    ms = timed(step, steps, warmup)
+    return {"model": cfg.name + f" LoRA r16 ({len(slots)} adapters), {side * 16}^2, grad ckpt", "params_b": nparams(m) / 1e9,
+            "tokens": side * side + S_cap, "metric": "train samples/s", "ms_per_step": ms, "value": 1000.0 / ms}
+
+
+def bench_sdxl(dev, tiny, steps, warmup):
+    """SDXL UNet, 1024^2 (128 x 128 latent), eps-prediction Euler step with CFG (batch of 2 = cond + uncond)."""
+    from mojodiffusion_b200.models.unet import UNet, sdxl_config, tiny_unet_config
+    cfg = tiny_unet_config() if tiny else sdxl_config()
+    side = 16 if tiny else 128
+    m = UNet(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    x = torch.randn(2, cfg.in_channels, side, side, device=dev)
+    ctx = torch.randn(2, 77, cfg.context_dim, device=dev, dtype=torch.bfloat16)
+    y = torch.randn(2, cfg.adm_in_channels, device=dev, dtype=torch.bfloat16)
+    ts = torch.full((2,), 500.0, device=dev)
+
+    def step():
+        with torch.no_grad():
+            eps = m(x.to(torch.bfloat16), ts, ctx, y).float()
+            e = eps[1:] + 7.0 * (eps[:1] - eps[1:])
+            x.add_(e.expand_as(x), alpha=-0.01)
+
+    ms = timed(step, steps, warmup)
+    return {"model": cfg.name, "params_b": nparams(m) / 1e9, "tokens": side * side,
+            "metric": "denoise it/s (CFG, cond+uncond batched)", "ms_per_step": ms, "value": 1000.0 / ms}
+
+
+def bench_vae(dev, tiny, steps, warmup):
+    """FLUX VAE decode of one 1024^2 image (128 x 128 x 16 latent)."""
+    from mojodiffusion_b200.models.vae import AutoencoderKL, flux_vae_config, tiny_vae_config
+    cfg = tiny_vae_config() if tiny else flux_vae_config()
+    side = 16 if tiny else 128
+    m = AutoencoderKL(cfg, torch.bfloat16, dev, with_encoder=False).init_weights(0).eval()
+    z = torch.randn(1, cfg.z_channels, side, side, device=dev)
+
+    def step():
+        with torch.no_grad():
+            m.decode(z)
+
+    ms = timed(step, steps, warmup)
+    return {"model": "flux-vae decode" if not tiny else "tiny-vae decode", "params_b": nparams(m) / 1e9,
+            "tokens": side * side, "metric": "images/s", "ms_per_step": ms, "value": 1000.0 / ms}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="ltx2,ltx2_fp8,qwen,zimage,zimage_train,sdxl,vae")
+    ap.add_argument("--tiny", action="store_true", help="tiny architectures (seconds; for checking the script)")
+    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    native.load(True)
+    table = {
+        "ltx2": lambda: bench_ltx2(dev, args.tiny, args.steps, args.warmup, False),
+        "ltx2_fp8": lambda: bench_ltx2(dev, args.tiny, args.steps, args.warmup, True),
+        "qwen": lambda: bench_qwen(dev, args.tiny, args.steps, args.warmup),
+        "zimage": lambda: bench_zimage(dev, args.tiny, args.steps, args.warmup, False),
+        "zimage_train": lambda: bench_zimage(dev, args.tiny, args.steps, args.warmup, True),
+        "sdxl": lambda: bench_sdxl(dev, args.tiny, args.steps, args.warmup),
+        "vae": lambda: bench_vae(dev, args.tiny, args.steps, args.warmup),
+    }
+    rows = []
+    for name in args.only.split(","):
+        t0 = time.time()
+        row = table[name]()
+        native.check_status()
+        row["case"] = name
+        row["peak_gib"] = torch.cuda.max_memory_allocated() / 2 ** 30
+        row["wall_s_incl_init"] = time.time() - t0
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+    if args.json:
+        json.dump(rows, open(args.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -21,6 +21,7 @@
 
 #include <cudaTypedefs.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace mdb {
@@ -650,6 +651,232 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
 }
 
 // ---------------------------------------------------------------------------------
+// CTA-pair variant: one 256 x 256 output tile per cluster of two CTAs (tcgen05 cta_group::2). Each CTA stages its
+// own 128 rows of A and its own 128 rows of B per K block (32 KB instead of the 48 KB a lone 128 x 256 CTA needs for
+// the same MMA time), so the shared-memory fill rate, which bounds the one-CTA kernel on DiT shapes, drops by a third
+// and the ring is 6 stages deep. The even CTA issues the MMAs for both; each CTA reads its own 128 x 256 fp32
+// accumulator from its own TMEM and runs the same fused epilogue. bf16 operands, any operand majors, paired (GLU)
+// mode, routed / staged-reduce epilogues; no fused gather, convolution or split-K (those stay on the one-CTA kernel).
+// ---------------------------------------------------------------------------------
+constexpr int PAIR_THREADS = 192;  // warps: 0 TMA, 1 UMMA issue (leader only), 2-5 epilogue
+
+template <int STAGES, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+  constexpr int BN = 256;               // accumulator columns per CTA (the whole tile width)
+  constexpr int BNH = 128;              // B rows staged by one CTA
+  constexpr int A_BYTES = BM * BK_BYTES;
+  constexpr int B_BYTES = BNH * BK_BYTES;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN;
+  constexpr int KSTEPS = 4;
+  constexpr int K_ELEMS = 64;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES];    // used in the leader: both CTAs' loads of a stage have landed
+  __shared__ uint64_t empty_bar[STAGES];   // in each CTA: the MMAs that read this stage are done
+  __shared__ uint64_t tfull_bar[2];        // in each CTA: accumulator complete
+  __shared__ uint64_t tempty_bar[2];       // used in the leader: 8 epilogue warps (4 per CTA) have drained the accumulator
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull_bar[s], 1);
+      mbar_init(&tempty_bar[s], 8);
+    }
+    abort_s = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < p.num_seg; ++s) {
+      tma_prefetch_desc(&maps.a[s]);
+      tma_prefetch_desc(&maps.b[s]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();   // the peer's barriers exist before anything is sent to them
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t peer_abort = mapa_shared(smem_u32(&abort_s), rank ^ 1u);
+
+  const bool paired = p.pair_offset > 0;
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + (paired ? BNH : BN) - 1) / (paired ? BNH : BN);
+  const int num_tiles = tiles_m * tiles_n;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  int total_kb = 0;
+  for (int s = 0; s < p.num_seg; ++s) total_kb += p.kblocks[s];
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) -------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int last_stage = -1;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+        const int m0 = (tile % tiles_m) * (2 * BM) + static_cast<int>(rank) * BM;
+        const int nblk = tile / tiles_m;
+        // this CTA's 128 rows of B: the lower / upper half of the tile, or in paired mode the first / second operand
+        const int n0 = paired ? nblk * BNH + (leader ? 0 : p.pair_offset) : nblk * BN + static_cast<int>(rank) * BNH;
+        for (int s = 0; ok && s < p.num_seg; ++s) {
+          for (int kb = 0; kb < p.kblocks[s]; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s)) {
+              report_status(p.status, STATUS_TIMEOUT, 21, stage);
+              st_shared_cluster_u32(peer_abort, 1u);
+              ok = false;
+              break;
+            }
+            uint8_t* sa = smem + stage * STAGE_BYTES;
+            uint8_t* sb = sa + A_BYTES;
+            const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0u);
+            if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+            const int k0 = kb * K_ELEMS;
+            if (!A_MN) {
+              tma_load_2d_pair(sa, &maps.a[s], bar, k0, m0);
+            } else {
+              tma_load_2d_pair(sa, &maps.a[s], bar, m0, k0);
+              tma_load_2d_pair(sa + 8192, &maps.a[s], bar, m0 + 64, k0);
+            }
+            if (!B_MN) {
+              tma_load_2d_pair(sb, &maps.b[s], bar, k0, n0);
+            } else {
+              tma_load_2d_pair(sb, &maps.b[s], bar, n0, k0);
+              tma_load_2d_pair(sb + 8192, &maps.b[s], bar, n0 + 64, k0);
+            }
+            last_stage = stage;
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+      if (!ok && last_stage >= 0) {
+        // abandoned: give the copies already in flight time to land before the CTA goes away (bounded)
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- UMMA issuer (leader CTA only) --------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1, UMMA_BF16, UMMA_BF16, A_MN ? 1u : 0u, B_MN ? 1u : 0u, 2 * BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, &abort_s)) {
+          report_status(p.status, STATUS_TIMEOUT, 22, acc);
+          st_shared_cluster_u32(peer_abort, 1u);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < total_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, &abort_s)) {
+            report_status(p.status, STATUS_TIMEOUT, 23, stage);
+            st_shared_cluster_u32(peer_abort, 1u);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+          const uint64_t da = A_MN ? make_desc_mnmajor_sw128(sa, 8192) : make_desc_kmajor_sw128(sa);
+          const uint64_t db = B_MN ? make_desc_mnmajor_sw128(sb, 8192) : make_desc_kmajor_sw128(sb);
+#pragma unroll
+          for (int k = 0; k < KSTEPS; ++k) {
+            const uint64_t a_k = da + static_cast<uint64_t>(A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+            const uint64_t b_k = db + static_cast<uint64_t>(B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+            umma_f16_ss_pair(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage], 3);   // the stage is free in both CTAs once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit_pair(&tfull_bar[acc], 3);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue (4 warps per CTA) -----------------
+    const int quad = warp & 3;
+    const int esz = p.out_fp32 ? 4 : 2;
+    bool aligned = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(static_cast<size_t>(p.ld_out) * esz)) & 15) == 0;
+    if (p.bias) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.bias) | static_cast<uintptr_t>(p.pair_offset * 2)) & 15) == 0;
+    if (p.col_scale) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.col_scale) | static_cast<uintptr_t>(p.pair_offset * 4)) & 15) == 0;
+    if (p.gate) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.gate) | static_cast<uintptr_t>(p.gate_stride * 2)) & 15) == 0;
+    if (p.residual) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.residual) | static_cast<uintptr_t>(static_cast<size_t>(p.ld_res) * 2)) & 15) == 0;
+    int it = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (tile % tiles_m) * (2 * BM) + static_cast<int>(rank) * BM;
+      const int nblk = tile / tiles_m;
+      const int n0 = paired ? nblk * BNH : nblk * BN;
+      const bool got = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, &abort_s));
+      if (!got) {
+        if (lane == 0) {
+          report_status(p.status, STATUS_TIMEOUT, 24, acc);
+          st_shared_cluster_u32(peer_abort, 1u);
+        }
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      const int out_cols = paired ? BNH : BN;
+#pragma unroll 1
+      for (int c = 0; c < out_cols / 32; ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r0);
+        if (paired) tmem_ld_32x32b_x32(taddr + BNH + c * 32, r1);
+        tmem_wait_ld();
+        epilogue_row32(p, row, n0 + c * 32, r0, r1, paired, aligned);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0u));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();   // neither CTA frees TMEM or leaves while its partner may still signal or read
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
@@ -724,7 +951,60 @@ static int launch_variant(const GemmMaps& maps, const GemmParams& p, int num_sms
   return static_cast<int>(cudaGetLastError());
 }
 
+template <int STAGES, bool A_MN, bool B_MN>
+static int launch_pair_variant(const GemmMaps& maps, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * (BM * BK_BYTES + 128 * BK_BYTES) + 1024;
+  static_assert(SMEM <= 227 * 1024, "pipeline exceeds the shared memory of an SM");
+  auto kern = gemm_tcgen05_pair_kernel<STAGES, A_MN, B_MN>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_done = true;
+  }
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + (p.pair_offset > 0 ? 128 : 256) - 1) / (p.pair_offset > 0 ? 128 : 256);
+  // how many CTA pairs the device can hold at once (an SM whose partner is unavailable cannot host half a pair): a
+  // persistent grid must not exceed it, or the surplus pairs would run their whole tile list after the others finish
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(num_sms & ~1), 1, 1);
+    cfg.blockDim = dim3(PAIR_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = num_sms / 2;
+    }
+    max_pairs = n < num_sms / 2 ? n : num_sms / 2;
+  }
+  int clusters = tiles_m * tiles_n;
+  if (clusters > max_pairs) clusters = max_pairs;
+  if (clusters < 1) return 0;
+  kern<<<2 * clusters, PAIR_THREADS, SMEM, stream>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace mdb
+
+// MDB200_GEMM_PAIR=1 lets automatically tiled GEMMs choose the CTA-pair kernel; default: one-CTA kernel only.
+static int pair_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("MDB200_GEMM_PAIR");
+    mode = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return mode;
+}
 
 extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   using namespace mdb;
@@ -734,6 +1014,11 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   const bool paired = a->pair_offset > 0;
   const int sms = a->num_sms > 0 ? a->num_sms : 148;
   int bn = a->bn;
+  // bn == 512 asks for the CTA-pair kernel (256 x 256 tile over two SMs); it shares the tensor maps of the 128 x 256 tile
+  const bool pair_ok = a->kind == 0 && a->conv_taps <= 0 && a->gather_world <= 1 && a->split_k <= 1;
+  bool use_pair = bn == 512 && pair_ok;
+  if (bn == 512) bn = 256;
+  const bool auto_tile = bn != 64 && bn != 128 && bn != 256;
   if (bn != 64 && bn != 128 && bn != 256) {
     // default tile choice: 128x256 unless the narrower 128x128 tile fills the machine noticeably better
     // (fewer idle SMs in the last wave); 128x64 only for very skinny outputs
@@ -748,6 +1033,21 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
     if (!paired && a->N <= 64) bn = 64;
   }
   if (paired && bn != 256) bn = 256;
+  if (auto_tile && pair_ok && a->M > BM && pair_mode() != 0) {
+    // CTA pair (256 x 256 tile on two SMs) or lone CTAs? Compare waves x time per tile; a pair tile costs each SM the MMA
+    // time of a 128 x 256 tile but a third less shared-memory fill, measured as about 0.87 of its time on DiT shapes.
+    const int n_tile = paired ? 128 : 256;
+    const long long t2 = static_cast<long long>((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + n_tile - 1) / n_tile);
+    const long long w2 = (t2 + sms / 2 - 1) / (sms / 2);
+    const long long t1 = static_cast<long long>((a->M + BM - 1) / BM) * ((a->N + (paired ? 128 : bn) - 1) / (paired ? 128 : bn));
+    const long long w1 = (t1 + sms - 1) / sms;
+    const double cost1 = static_cast<double>(w1) * (bn == 256 ? 1.0 : bn == 128 ? 0.55 : 0.32);
+    const double cost2 = static_cast<double>(w2) * 0.87;
+    if (cost2 <= cost1) {
+      use_pair = true;
+      bn = 256;
+    }
+  }
   GemmMaps maps;
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -856,6 +1156,12 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   if (a->route_owner_cols > 0 && ((a->route_owner_cols % 32) || (p.route_part_cols % a->route_owner_cols))) return -5;
 
 #define MDB_LAUNCH(BN_, ST_, AMN_, BMN_, KIND_) return launch_variant<BN_, ST_, AMN_, BMN_, KIND_>(maps, p, sms, stream)
+  if (use_pair) {
+    if (!a->a_mn && !a->b_mn) return launch_pair_variant<6, false, false>(maps, p, sms, stream);
+    if (!a->a_mn && a->b_mn) return launch_pair_variant<6, false, true>(maps, p, sms, stream);
+    if (a->a_mn && a->b_mn) return launch_pair_variant<6, true, true>(maps, p, sms, stream);
+    return launch_pair_variant<6, true, false>(maps, p, sms, stream);
+  }
   if (a->kind == 1) {
     if (a->a_mn || a->b_mn) return -4;
     if (bn == 256) MDB_LAUNCH(256, 4, false, false, 1);

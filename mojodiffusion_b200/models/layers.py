@@ -10,6 +10,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
+from ..ops import native
 
 
 class LoRASlot(nn.Module):
@@ -175,7 +176,7 @@ def packed_projection(x: torch.Tensor, linears) -> torch.Tensor:
     ([..., sum(out_features)]): on the GPU inference path each GEMM stores straight into its column slice, so
     separate to_q / to_k / to_v weights (diffusers layout) still give the packed qkv the attention kernels read."""
     widths = [l.out_features for l in linears]
-    if x.is_cuda and not torch.is_grad_enabled():
+    if native.use_native(x) and not torch.is_grad_enabled():
         lead = x.shape[:-1]
         out = torch.empty(*lead, sum(widths), dtype=x.dtype, device=x.device)
         c = 0

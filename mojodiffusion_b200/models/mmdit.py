@@ -24,6 +24,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from ..ops import native
 from .layers import Linear, MLPEmbedder, timestep_embedding
 
 
@@ -101,7 +102,7 @@ def _mlp(cfg: MMDiTConfig, dtype, device) -> nn.ModuleDict:
 
 
 def _fused_path(x: torch.Tensor) -> bool:
-    return x.is_cuda and not torch.is_grad_enabled()
+    return native.use_native(x) and not torch.is_grad_enabled()
 
 
 class DoubleStreamBlock(nn.Module):

@@ -169,6 +169,11 @@ def attention(q, k, v, scale: Optional[float] = None, kv_len: Optional[torch.Ten
     B, Sq, H, Dh = q.shape
     Skv = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(Dh)
+    if q.is_cuda and kv_len is None and not return_lse:
+        # library baseline on a GPU: the flash / cuDNN kernel torch selects, not an S x S fp32 score matrix
+        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                             scale=scale)
+        return o.transpose(1, 2).contiguous()
     s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
     if kv_len is not None:
         mask = torch.arange(Skv, device=q.device)[None, :] >= kv_len.to(q.device)[:, None]

@@ -106,6 +106,42 @@ def test_gemm_backward_majors():
         _check(dx, dy.float() @ w.float(), name=f"dx bn{bn}")
 
 
+def _gemm_bn(As, Bs, bn, **kw):
+    from mojodiffusion_b200.ops.functional import _gemm
+    return _gemm(As, Bs, bn=bn, **kw)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (300, 384, 200), (4608, 3072, 3072), (1000, 1288, 520)])
+def test_gemm_cta_pair_plain(M, N, K):
+    """256 x 256 tiles computed by two CTAs (bn=512 forces the CTA-pair kernel), ragged M / N / K included."""
+    x, w = _rand(M, K, seed=41), _rand(N, K, scale=1 / math.sqrt(K), seed=42)
+    _check(_gemm_bn([x], [w], 512), ref.linear(x, w, out_dtype=torch.float32), name=f"pair {M}x{N}x{K}")
+
+
+def test_gemm_cta_pair_epilogues_segments_majors():
+    B, S, K, N = 2, 300, 256, 512
+    x = _rand(B * S, K, seed=43)
+    w = _rand(N, K, scale=1 / math.sqrt(K), seed=44)
+    bias, gate, res = _rand(N, seed=45), _rand(B, N, seed=46), _rand(B * S, N, seed=47)
+    out = _gemm_bn([x], [w], 512, bias=bias, residual=res, gate=gate, rows_per_group=S, act=ref.act_code("gelu_tanh"))
+    _check(out, ref.linear(x, w, bias, "gelu_tanh", res, gate, S, out_dtype=torch.float32), name="pair epilogue")
+    # two K segments into one accumulator
+    a2, w2 = _rand(B * S, 128, seed=48), _rand(N, 128, scale=0.05, seed=49)
+    out = _gemm_bn([x, a2], [w, w2], 512)
+    _check(out, x.float() @ w.float().t() + a2.float() @ w2.float().t(), name="pair two segments")
+    # paired (GLU) mode: the second CTA stages the second operand's rows
+    F_ = 384
+    wg, bg = _rand(2 * F_, K, scale=1 / math.sqrt(K), seed=50), _rand(2 * F_, seed=51)
+    out = _gemm_bn([x], [wg], 512, bias=bg, act=ref.act_code("silu"), pair_offset=F_)
+    _check(out, ref.linear_glu(x, wg, bg, "silu", False, out_dtype=torch.float32), name="pair swiglu")
+    # gradient layouts: dx = dy W (B MN-major), dW = dy^T x (both MN-major), fp32 output
+    M, Nn, Kk = 640, 384, 520
+    xx, ww, dy = _rand(M, Kk, seed=52), _rand(Nn, Kk, scale=0.05, seed=53), _rand(M, Nn, seed=54)
+    _check(_gemm_bn([dy], [ww], 512, b_mn=True), dy.float() @ ww.float(), name="pair dx")
+    _check(_gemm_bn([dy], [xx], 512, a_mn=True, b_mn=True), dy.float().t() @ xx.float(), name="pair dW")
+    _check(_gemm_bn([dy], [xx], 512, a_mn=True, b_mn=True, out_fp32=True), dy.float().t() @ xx.float(), name="pair dW fp32")
+
+
 def test_linear_autograd_matches_torch():
     M, N, K, r = 256, 320, 192, 8
     x = _rand(M, K, seed=21).requires_grad_(True)
