@@ -1,35 +1,286 @@
-"""Backends for the remaining model kinds. Each kind maps to the model class and sampler of this package; without a
-checkpoint directory (``MDB_MODEL_DIR``) a kind whose architecture needs tens of GB is refused at ``start`` with a
-message that names the missing file, instead of silently generating from random weights
-(serenitymojo/serve/{zimage,qwenimage,sdxl,sd3,klein}_backend.mojo: residency and admission rules)."""
+"""Serving backends for the Z-Image, Qwen-Image and SDXL families: the same cooperative state machine as the FLUX
+backend (ENCODE -> LOAD -> DENOISE x N -> DECODE, one ``step()`` per unit, phase announced before the tick that performs
+it), each with its own model class, latent layout, schedule and guidance rule:
+
+* ``zimage``   single-stream DiT, 16-channel VAE, 2x2 patch tokens, shifted flow-matching Euler, textbook CFG with a
+  negative prompt (two forwards per step), model timestep ``1 - sigma`` (serenitymojo/serve/zimage_backend.mojo,
+  pipeline/zimage_sample_cli.mojo).
+* ``qwenimage`` 60-layer MMDiT, dynamic-shift schedule with terminal 0.02, true CFG with norm rescale
+  (serenitymojo/serve/qwenimage_backend.mojo).
+* ``sdxl``     UNet, eps-prediction Euler over the scaled-linear DDPM grid, CFG, ``y`` = pooled text + six sinusoidal
+  size / crop ids (serenitymojo/serve/sdxl_backend.mojo).
+
+Weights are read from ``MDB_MODEL_DIR`` (``<model>.safetensors`` with the key names of the model classes, VAE from the
+request's ``vae`` or the family default). Without a checkpoint the backend runs the same path on deterministic random
+weights and says so in its result sidecar (``"weights": "random-init"``); ``MDB_ARCH=tiny`` selects the tiny
+architectures (CPU tests). Text conditioning comes from pre-encoded caption files (``sample_caps_pos`` / ``_neg``:
+``text_embedding`` [1,T,D], optional ``pooled``) or, failing that, from a deterministic embedding of the prompt hash.
+``ltx2`` (video) is admitted by the control plane but refused here with a clear message: the video VAE decoder that turns
+its latents into frames is not part of this package yet."""
 from __future__ import annotations
 
+import dataclasses
+import json
+import math
 import os
+import time
+from typing import List, Optional
 
-from .backend import GenBackend, JobParams, StepResult, reject_unsupported_common
+import torch
 
-_CHECKPOINT_HINT = {"zimage": "z_image_turbo_bf16.safetensors", "qwenimage": "qwen_image_bf16.safetensors",
-                    "sdxl": "sd_xl_base_1.0.safetensors", "sd3": "sd3.5_large.safetensors", "sd15": "v1-5-pruned.safetensors",
-                    "ltx2": "ltx-2-19b-dev-fp8.safetensors"}
+from ..io.png import encode_png, tensor_to_uint8
+from ..io.safetensors_io import load_safetensors
+from ..sampling import flow_match as fm
+from ..sampling.guidance import cfg_textbook, cfg_true_with_norm_rescale
+from .backend import GenBackend, JobParams, StepResult, UnsupportedParam, reject_unsupported_common
+from .flux_backend import prompt_embedding
+
+KINDS = ("zimage", "qwenimage", "sdxl")
+_REFUSED = {"ltx2": "video generation needs the LTX video VAE decoder, which this package does not ship yet",
+            "sd3": "the SD3 MMDiT variant is not wired to a serving loop", "sd15": "the SD 1.5 UNet variant is not wired"}
+
+
+def _size_ids(values, dim: int = 256) -> torch.Tensor:
+    """SDXL micro-conditioning: each scalar -> sinusoidal(dim), concatenated."""
+    half = dim // 2
+    freqs = torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32) / half)
+    out = []
+    for v in values:
+        a = float(v) * freqs
+        out.append(torch.cat((torch.cos(a), torch.sin(a))))
+    return torch.cat(out)[None]
 
 
 class GenericBackend(GenBackend):
-    def __init__(self, kind: str):
-        if kind not in _CHECKPOINT_HINT:
+    def __init__(self, kind: str, device: Optional[str] = None):
+        if kind in _REFUSED:
+            self._refusal = f"{kind}: {_REFUSED[kind]}"
+        elif kind not in KINDS:
             raise ValueError(f"no backend for kind '{kind}'")
+        else:
+            self._refusal = ""
         self.kind = self.name = kind
-        self.p = None
+        self.tiny = os.environ.get("MDB_ARCH", "") == "tiny"
+        self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        self.model = self.vae = None
+        self.loaded_name = ""
+        self.weights_kind = ""
+        self.p: Optional[JobParams] = None
         self._cancel = False
+        self.phase = "idle"
+        self.stage_s = {}
 
+    def resident_model(self) -> str:
+        return self.loaded_name
+
+    # ---- job -----------------------------------------------------------------------------------------------
     def start(self, params: JobParams) -> None:
-        reject_unsupported_common(params)
-        root = os.environ.get("MDB_MODEL_DIR", "")
-        name = params.model if params.model.endswith(".safetensors") else params.model + ".safetensors"
-        if not root or not os.path.isfile(os.path.join(root, name)):
-            raise FileNotFoundError(f"{self.kind}: checkpoint '{name}' not found under MDB_MODEL_DIR "
-                                    f"(expected e.g. {_CHECKPOINT_HINT[self.kind]})")
-        raise NotImplementedError(f"{self.kind}: serving loop for this family is not wired to the worker yet; "
-                                  f"use the FLUX kinds or the Python pipelines directly")
+        if self._refusal:
+            raise NotImplementedError(self._refusal)
+        reject_unsupported_common(params, img2img=False, inpaint=False, lora=False, variation=False)
+        s = (params.sampler or "euler").lower()
+        if s not in ("euler", "flowmatch_euler", "flow_match_euler"):
+            raise UnsupportedParam(f"{self.kind}: the serving loop implements the euler sampler, not '{params.sampler}'")
+        self.p, self._cancel, self.phase, self.i = params, False, "encode", 0
+        self.stage_s = {}
+
+    def cancel(self) -> None:
+        self._cancel = True
 
     def step(self) -> StepResult:
-        return StepResult("failed", error=f"{self.kind}: no active job")
+        p = self.p
+        if p is None:
+            return StepResult("failed", error=f"{self.kind}: no active job")
+        if self._cancel:
+            self.p, self.phase = None, "idle"
+            return StepResult("cancelled")
+        t0 = time.perf_counter()
+        if self.phase == "encode":
+            self._encode(p)
+            self.stage_s["encode"] = time.perf_counter() - t0
+            self.phase = "load"
+            return StepResult("progress", 0, p.steps, "load")
+        if self.phase == "load":
+            self._load(p)
+            self._prepare(p)
+            self.stage_s["load"] = time.perf_counter() - t0
+            self.phase = "denoise"
+            return StepResult("progress", 0, p.steps, "denoise")
+        if self.phase == "denoise":
+            self._denoise_step(p)
+            self.stage_s["denoise"] = self.stage_s.get("denoise", 0.0) + time.perf_counter() - t0
+            self.i += 1
+            if self.i >= p.steps:
+                self.phase = "decode"
+                return StepResult("progress", p.steps, p.steps, "decode")
+            return StepResult("progress", self.i, p.steps, "denoise")
+        path = self._decode_and_save(p)
+        self.stage_s["decode"] = time.perf_counter() - t0
+        self._write_sidecar(p, path)
+        self.p, self.phase = None, "idle"
+        return StepResult("done", output_path=path)
+
+    def trim(self) -> None:
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    # ---- family tables ---------------------------------------------------------------------------------------
+    def _model_config(self):
+        if self.kind == "zimage":
+            from ..models import single_dit as M
+            return M.tiny_single_dit_config() if self.tiny else M.zimage_config()
+        if self.kind == "qwenimage":
+            from ..models import qwen_image as M
+            return M.tiny_qwen_image_config() if self.tiny else M.qwen_image_config()
+        from ..models import unet as M
+        return M.tiny_unet_config() if self.tiny else M.sdxl_config()
+
+    def _vae_config(self):
+        from ..models import vae as V
+        zc = 4 if self.kind == "sdxl" else 16
+        if self.tiny:
+            return dataclasses.replace(V.tiny_vae_config(), z_channels=zc)
+        return V.sdxl_vae_config() if self.kind == "sdxl" else V.flux_vae_config()
+
+    def _text_shape(self, cfg):
+        if self.kind == "zimage":
+            return (32 if self.tiny else 128), cfg.cap_dim, 0
+        if self.kind == "qwenimage":
+            return (32 if self.tiny else 256), cfg.context_dim, 0
+        return 77, cfg.context_dim, cfg.adm_in_channels - 6 * 256 if not self.tiny else cfg.adm_in_channels
+
+    # ---- phases -------------------------------------------------------------------------------------------------
+    def _read_caps(self, path: str, prompt: str, T: int, D: int, P: int):
+        if path and os.path.isfile(path):
+            d = load_safetensors(path)
+            pooled = d["pooled"].float() if "pooled" in d else torch.zeros(1, max(P, 1))
+            return d["text_embedding"].float(), pooled, "pre-encoded"
+        txt, pooled = prompt_embedding(prompt, T, D, max(P, 1))
+        return txt, pooled, "hash-embedding"
+
+    def _encode(self, p: JobParams) -> None:
+        self.cfg = cfg = self._model_config()
+        T, D, P = self._text_shape(cfg)
+        self.txt, self.pooled, self.text_kind = self._read_caps(p.sample_caps_pos, p.prompt, T, D, P)
+        self.use_cfg = p.cfg > 1.0
+        if self.use_cfg:
+            self.txt_neg, self.pooled_neg, _ = self._read_caps(p.sample_caps_neg, p.negative, self.txt.shape[1], D, P)
+
+    def _load(self, p: JobParams) -> None:
+        from ..models.vae import AutoencoderKL
+        if self.model is not None and self.loaded_name == p.model:
+            return
+        self.model = self.vae = None
+        self.trim()
+        if self.kind == "zimage":
+            from ..models.single_dit import SingleStreamDiT as Cls
+        elif self.kind == "qwenimage":
+            from ..models.qwen_image import QwenImageDiT as Cls
+        else:
+            from ..models.unet import UNet as Cls
+        model = Cls(self.cfg, self.dtype, self.device)
+        root = os.environ.get("MDB_MODEL_DIR", "")
+        path = os.path.join(root, p.model if p.model.endswith(".safetensors") else p.model + ".safetensors")
+        if root and os.path.isfile(path):
+            sd = load_safetensors(path, device=str(self.device), dtype=self.dtype)
+            missing = [k for k in model.state_dict() if k not in sd]
+            if missing:
+                raise KeyError(f"checkpoint lacks {len(missing)} tensors, e.g. {missing[:3]}")
+            model.load_state_dict(sd, strict=False)
+            self.weights_kind = "checkpoint"
+        else:
+            model.init_weights(seed=0)
+            self.weights_kind = "random-init"
+        vae = AutoencoderKL(self._vae_config(), self.dtype, self.device, with_encoder=False)
+        vpath = os.path.join(root, p.vae) if (root and p.vae) else ""
+        if vpath and os.path.isfile(vpath):
+            vae.load_state_dict(load_safetensors(vpath, device=str(self.device), dtype=self.dtype), strict=False)
+        else:
+            vae.init_weights(seed=1)
+        self.model, self.vae = model.eval(), vae.eval()
+        self.loaded_name = p.model
+
+    def _prepare(self, p: JobParams) -> None:
+        from ..models.mmdit import pack_latents
+        f = self.vae.spatial_factor
+        C = self.vae.cfg.z_channels
+        h, w = p.height // f, p.width // f
+        g = torch.Generator().manual_seed(int(p.seed) & 0x7FFFFFFFFFFFFFFF)
+        noise = torch.randn(1, C, h, w, generator=g)
+        dev, dt = self.device, self.dtype
+        self.txt_d = self.txt.to(dev, dt)
+        if self.use_cfg:
+            self.txt_neg_d = self.txt_neg.to(dev, dt)
+        self.t = torch.empty(1, device=dev)
+        if self.kind == "sdxl":
+            from ..sampling.ddpm import SDXLEulerScheduler
+            self.sched = SDXLEulerScheduler(p.steps)
+            self.x = (noise * self.sched.init_noise_sigma).float().to(dev)
+            if self.tiny:
+                self.y = self.pooled.to(dev, dt)
+                self.y_neg = self.pooled_neg.to(dev, dt) if self.use_cfg else None
+            else:
+                ids = _size_ids((p.height, p.width, 0, 0, p.height, p.width))
+                self.y = torch.cat((self.pooled, ids), 1).to(dev, dt)
+                self.y_neg = torch.cat((self.pooled_neg, ids), 1).to(dev, dt) if self.use_cfg else None
+            return
+        self.hw = (h // 2, w // 2)
+        S_img = self.hw[0] * self.hw[1]
+        if self.kind == "qwenimage":
+            self.sigmas = fm.qwen_image_sigmas(p.steps, S_img)
+        else:
+            self.sigmas = fm.shifted_sigmas(p.steps, p.sigma_shift if p.sigma_shift > 0 else 3.0)
+        self.x = pack_latents(noise).float().to(dev)
+
+    @torch.no_grad()
+    def _denoise_step(self, p: JobParams) -> None:
+        i = self.i
+        if self.kind == "sdxl":
+            t = self.sched.timesteps[i]
+            self.t.fill_(float(t))
+            xin = self.sched.scale_model_input(self.x, i).to(self.dtype)
+            eps = self.model(xin, self.t, self.txt_d, self.y).float()
+            if self.use_cfg:
+                eu = self.model(xin, self.t, self.txt_neg_d, self.y_neg).float()
+                eps = cfg_textbook(eps, eu, p.cfg)
+            self.x = self.sched.step(self.x, eps, i)
+            return
+        s, s_next = float(self.sigmas[i]), float(self.sigmas[i + 1])
+        xb = self.x.to(self.dtype)
+        if self.kind == "zimage":
+            self.t.fill_(1.0 - s)                         # the model's clock runs from noise (0) to image (1)
+            v = -self.model(xb, self.txt_d, self.t, self.hw).float()
+            if self.use_cfg:
+                vu = -self.model(xb, self.txt_neg_d, self.t, self.hw).float()
+                v = cfg_textbook(v, vu, p.cfg)
+        else:
+            self.t.fill_(s)
+            v = self.model(xb, self.txt_d, self.t, self.hw).float()
+            if self.use_cfg:
+                vu = self.model(xb, self.txt_neg_d, self.t, self.hw).float()
+                v = cfg_true_with_norm_rescale(v, vu, p.cfg)
+        self.x = self.x + (s_next - s) * v
+
+    @torch.no_grad()
+    def _decode_and_save(self, p: JobParams) -> str:
+        from ..models.mmdit import unpack_latents
+        z = self.x if self.kind == "sdxl" else unpack_latents(self.x, self.hw[0], self.hw[1])
+        img = self.vae.tiled_decode(z) if max(z.shape[-2:]) > 96 else self.vae.decode(z)
+        arr = tensor_to_uint8(img[0].float().permute(1, 2, 0).cpu()).numpy()
+        os.makedirs(p.out_dir or ".", exist_ok=True)
+        path = p.output_path()
+        tmp = path + ".tmp"
+        with open(tmp, "wb") as f:
+            f.write(encode_png(arr, {"serenity.genparams.v1": p.genparams_text()}))
+        os.replace(tmp, path)
+        return path
+
+    def _write_sidecar(self, p: JobParams, path: str) -> None:
+        peak = torch.cuda.max_memory_allocated() if self.device.type == "cuda" else 0
+        side = {"schema": f"serenity.{self.kind}.daemon_result.v1", "job_id": p.job_id, "model": p.model,
+                "weights": self.weights_kind, "text": self.text_kind, "cfg": p.cfg if self.use_cfg else 1.0,
+                "stage_seconds": {k: round(v, 4) for k, v in self.stage_s.items()}, "peak_device_bytes": int(peak),
+                "steps_run": p.steps, "sampler": "euler", "device": str(self.device)}
+        with open(path + ".worker_result.json", "w") as f:
+            json.dump(side, f)

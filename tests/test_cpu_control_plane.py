@@ -405,3 +405,25 @@ def test_model_swap_restarts_worker_with_flux_kind(bins, tmp_path):
         assert s.call("GET", f"/v1/job/{r['job_id']}/result")[1]["result"]["worker_sidecar_present"] is True
     finally:
         s.close()
+
+
+@pytest.mark.parametrize("model,backend,cfg", [("z-image-tiny", "zimage", 4.0), ("qwen-image-tiny", "qwenimage", 1.0),
+                                               ("sd_xl_tiny", "sdxl", 5.0)])
+def test_other_families_serve_through_the_worker(bins, tmp_path, model, backend, cfg):
+    """Z-Image, Qwen-Image and SDXL jobs run their own phase machines in the worker (tiny architectures, random weights),
+    with classifier-free guidance when cfg > 1; the result carries the parameters and a sidecar naming the family."""
+    s = Server(bins, str(tmp_path / "out"), {"MDB_ARCH": "tiny"})
+    try:
+        st, r = s.call("POST", "/v1/generate", {"model": model, "prompt": "a lighthouse", "negative": "blurry", "steps": 2,
+                                                 "width": 64, "height": 64, "seed": 9, "cfg": cfg})
+        assert st == 200, r
+        ev = s.ws_events(r["job_id"], timeout=300)
+        assert ev[-1]["ev"] == "done", ev[-1]
+        img, text = load_png(ev[-1]["output_path"])
+        assert img.shape == (64, 64, 3) and json.loads(text["serenity.genparams.v1"])["prompt"] == "a lighthouse"
+        side = json.load(open(ev[-1]["output_path"] + ".worker_result.json"))
+        assert side["schema"] == f"serenity.{backend}.daemon_result.v1" and side["weights"] == "random-init"
+        assert side["cfg"] == (cfg if cfg > 1 else 1.0) and side["steps_run"] == 2
+        assert s.call("GET", "/v1/health")[1]["backend"] == backend
+    finally:
+        s.close()
