@@ -6,7 +6,7 @@ device-timed with CUDA events after warm-up; every step streams far more weight 
 the reference's per-model sampler smokes and trainer step reports (serenitymojo/docs/MODEL_RENDER_CAMPAIGN_2026-06-15.md,
 BEAT_FLAME_SCOREBOARD_2026-06-10.md), which time the same loops on its hardware.
 
-    python benchmarks/bench_models.py [--only ltx2,qwen,zimage,sdxl,vae,zimage_train] [--tiny] [--json out.json]
+    python benchmarks/bench_models.py [--only ltx2,ltx2_fp8,qwen,zimage,zimage_train,klein,klein_train,sdxl,vae] [--tiny] [--json out.json]
 """
 import argparse
 import json
@@ -131,6 +131,51 @@ def bench_zimage(dev, tiny, steps, warmup, train):
             "tokens": side * side + S_cap, "metric": "train samples/s", "ms_per_step": ms, "value": 1000.0 / ms}
 
 
+def bench_klein(dev, tiny, steps, warmup, train):
+    """FLUX.2 Klein-9B-shaped MMDiT: 1024^2 denoise (4096 + 512 tokens), or the reference's headline training case:
+    LoRA r16 on every block projection, 512^2 (1024 image + 512 text tokens = 1536), batch 1, gradient checkpointing."""
+    from mojodiffusion_b200.models.flux2 import Flux2DiT, klein_9b_config, tiny_flux2_config
+    cfg = tiny_flux2_config() if tiny else klein_9b_config()
+    side = 8 if tiny else (32 if train else 64)
+    S_txt = 16 if tiny else 512
+    m = Flux2DiT(cfg, torch.bfloat16, dev).init_weights(0)
+    x = torch.randn(1, side * side, cfg.in_channels, device=dev)
+    txt = torch.randn(1, S_txt, cfg.context_dim, device=dev, dtype=torch.bfloat16)
+    t = torch.full((1,), 0.6, device=dev)
+    if not train:
+        m.eval()
+        xb = x.to(torch.bfloat16)
+
+        def step():
+            with torch.no_grad():
+                v = m(xb, txt, t, (side, side))
+                ops.cfg_euler(x, v, None, dt=-0.03, mode=0, x_bf16=xb)
+
+        ms = timed(step, steps, warmup)
+        return {"model": cfg.name, "params_b": nparams(m) / 1e9, "tokens": side * side + S_txt, "metric": "denoise it/s",
+                "ms_per_step": ms, "value": 1000.0 / ms}
+    from mojodiffusion_b200.training import lora as L
+    from mojodiffusion_b200.training.optim import FusedAdamW
+    slots = L.inject_lora_by_name(m, {n: n for n in m.lora_target_names()}, rank=16, alpha=16.0)
+    params = L.lora_parameters(slots)
+    opt = FusedAdamW(params, lr=1e-4, max_grad_norm=1.0)
+    m.gradient_checkpointing = True
+    m.train()
+    eps = torch.randn_like(x)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        xt, target = ops.flow_match(x, eps, t)
+        loss = ops.mse_loss(m(xt.to(torch.bfloat16), txt, t, (side, side)), target)
+        loss.backward()
+        opt.step()
+
+    ms = timed(step, steps, warmup)
+    return {"model": cfg.name + f" LoRA r16 ({len(slots)} adapters), 512^2, S=1536, batch 1, grad ckpt",
+            "params_b": nparams(m) / 1e9, "tokens": side * side + S_txt, "metric": "train samples/s", "ms_per_step": ms,
+            "value": 1000.0 / ms}
+
+
 def bench_sdxl(dev, tiny, steps, warmup):
     """SDXL UNet, 1024^2 (128 x 128 latent), eps-prediction Euler step with CFG (batch of 2 = cond + uncond)."""
     from mojodiffusion_b200.models.unet import UNet, sdxl_config, tiny_unet_config
@@ -172,7 +217,7 @@ def bench_vae(dev, tiny, steps, warmup):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="ltx2,ltx2_fp8,qwen,zimage,zimage_train,sdxl,vae")
+    ap.add_argument("--only", default="ltx2,ltx2_fp8,qwen,zimage,zimage_train,klein,klein_train,sdxl,vae")
     ap.add_argument("--tiny", action="store_true", help="tiny architectures (seconds; for checking the script)")
     ap.add_argument("--steps", type=int, default=6)
     ap.add_argument("--warmup", type=int, default=3)
@@ -186,6 +231,8 @@ def main():
         "qwen": lambda: bench_qwen(dev, args.tiny, args.steps, args.warmup),
         "zimage": lambda: bench_zimage(dev, args.tiny, args.steps, args.warmup, False),
         "zimage_train": lambda: bench_zimage(dev, args.tiny, args.steps, args.warmup, True),
+        "klein": lambda: bench_klein(dev, args.tiny, args.steps, args.warmup, False),
+        "klein_train": lambda: bench_klein(dev, args.tiny, args.steps, args.warmup, True),
         "sdxl": lambda: bench_sdxl(dev, args.tiny, args.steps, args.warmup),
         "vae": lambda: bench_vae(dev, args.tiny, args.steps, args.warmup),
     }

@@ -73,6 +73,32 @@ def test_single_stream_dit():
     _gpu_vs_cpu(lambda dt, dev: SingleStreamDiT(tiny_single_dit_config(), dt, dev), inputs, hw=(8, 8))
 
 
+def test_flux2_klein_dit_forward_and_lora_grads():
+    """FLUX.2 Klein-shaped MMDiT: inference path (GLU-epilogue GEMMs, packed attention) against the fp32 CPU modules, and
+    the LoRA gradients of the training path against the CPU autograd result."""
+    from mojodiffusion_b200.models.flux2 import Flux2DiT, tiny_flux2_config
+    from mojodiffusion_b200.training import lora as L
+    g = torch.Generator().manual_seed(5)
+    cfg = tiny_flux2_config()
+    inputs = (torch.randn(2, 64, cfg.in_channels, generator=g), torch.randn(2, 16, cfg.context_dim, generator=g), torch.tensor([0.2, 0.9]))
+    _gpu_vs_cpu(lambda dt, dev: Flux2DiT(cfg, dt, dev), inputs, hw=(8, 8))
+    grads = []
+    for dt, dev in ((torch.float32, "cpu"), (torch.bfloat16, DEV)):
+        m = Flux2DiT(cfg, torch.float32, "cpu").init_weights(0)
+        slots = L.inject_lora_by_name(m, {n: n for n in m.lora_target_names()}, rank=8, alpha=8.0)
+        gg = torch.Generator().manual_seed(6)
+        for s_ in slots:
+            s_.up.data.copy_(torch.randn(s_.up.shape, generator=gg) * 0.05)
+        m = m.to(dev, dt)
+        m.gradient_checkpointing = True
+        m.train()
+        out = m(*[t.to(dev) for t in inputs], hw=(8, 8))
+        out.float().pow(2).mean().backward()
+        grads.append(torch.cat([p.grad.float().flatten().cpu() for p in L.lora_parameters(L.collect_slots(m))]))
+    native.check_status()
+    assert _cos(grads[1], grads[0]) > 0.98, _cos(grads[1], grads[0])
+
+
 def test_qwen_image_dit_with_text_mask():
     from mojodiffusion_b200.models.qwen_image import QwenImageDiT, tiny_qwen_image_config
     g = torch.Generator().manual_seed(3)
