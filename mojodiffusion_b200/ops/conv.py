@@ -109,3 +109,44 @@ def unpatchify_3d(x, grid, C: int, pt: int, ph: int, pw: int):
     T, H, W = grid
     x = x.reshape(B, T, H, W, C, pt, ph, pw).permute(0, 4, 1, 5, 2, 6, 3, 7)
     return x.reshape(B, C, T * pt, H * ph, W * pw)
+
+
+def conv3d_ndhwc(x, w_otohwi, bias=None, act=None, temporal_pad: str = "replicate"):
+    """3-D convolution on [N, T, H, W, Cin] with weights [Cout, KT, KH, KW, Cin], stride 1, "same" output size.
+
+    The spatial taps run in the 2-D implicit-GEMM kernel with all N*T frames as its batch; the KT temporal taps are KT such
+    launches over time-shifted views that accumulate through the kernel's residual input, so no im2col volume is ever
+    materialised. ``temporal_pad``: "replicate" repeats the first and last frame (the non-causal video-VAE rule,
+    serenitymojo/models/vae/ltx2_vae_decoder.mojo:52-59), "zeros" pads with zero frames
+    (serenitymojo/models/vae/conv3d.mojo)."""
+    N, T, H, W, Cin = x.shape
+    Cout, KT, KH, KW, _ = w_otohwi.shape
+    pt = (KT - 1) // 2
+    if pt > 0:
+        if temporal_pad == "replicate":
+            xp = torch.cat([x[:, :1]] * pt + [x] + [x[:, -1:]] * pt, dim=1)
+        else:
+            z = x.new_zeros(N, pt, H, W, Cin)
+            xp = torch.cat((z, x, z), dim=1)
+    else:
+        xp = x
+    acc = None
+    for dt in range(KT):
+        frames = xp[:, dt:dt + T].reshape(N * T, H, W, Cin)
+        last = dt == KT - 1
+        acc = conv2d_nhwc(frames, w_otohwi[:, dt], bias if dt == 0 else None, 1, (KH // 2, KW // 2), None, acc)
+        if last and act is not None:
+            acc = activation(acc.float(), act).to(acc.dtype)
+    return acc.reshape(N, T, H, W, Cout)
+
+
+def conv3d_ndhwc_reference(x, w_otohwi, bias=None, act=None, temporal_pad: str = "replicate"):
+    """The same operation through ``torch.nn.functional.conv3d`` in fp32."""
+    KT, KH, KW = w_otohwi.shape[1:4]
+    xc = x.permute(0, 4, 1, 2, 3).float()
+    pt = (KT - 1) // 2
+    if pt > 0:
+        xc = F.pad(xc, (0, 0, 0, 0, pt, pt), mode="replicate" if temporal_pad == "replicate" else "constant")
+    y = F.conv3d(xc, w_otohwi.permute(0, 4, 1, 2, 3).float(), bias.float() if bias is not None else None,
+                 padding=(0, KH // 2, KW // 2))
+    return activation(y, act).permute(0, 2, 3, 4, 1).to(x.dtype)

@@ -1,4 +1,4 @@
-"""Serving backends for the Z-Image, Qwen-Image and SDXL families: the same cooperative state machine as the FLUX
+"""Serving backends for the Z-Image, Qwen-Image, SDXL and LTX-2 families: the same cooperative state machine as the FLUX
 backend (ENCODE -> LOAD -> DENOISE x N -> DECODE, one ``step()`` per unit, phase announced before the tick that performs
 it), each with its own model class, latent layout, schedule and guidance rule:
 
@@ -9,14 +9,17 @@ it), each with its own model class, latent layout, schedule and guidance rule:
   (serenitymojo/serve/qwenimage_backend.mojo).
 * ``sdxl``     UNet, eps-prediction Euler over the scaled-linear DDPM grid, CFG, ``y`` = pooled text + six sinusoidal
   size / crop ids (serenitymojo/serve/sdxl_backend.mojo).
+* ``ltx2``     48-layer video DiT over [frames x h x w] latent tokens, linear-quadratic (distilled) sigmas, Euler with
+  the last step landing on ``x - v * sigma``, textbook CFG; the 128-channel video VAE expands 8x in time and 32x in space;
+  frames are written as ``<job>.frames/NNNN.png`` and the first frame as the job's output image; the frame count comes
+  from ``"frames"`` in the request's parameter JSON (default 9) (serenitymojo/pipeline/ltx2_sample_cli.mojo,
+  sampling/ltx2_sampling.mojo).
 
 Weights are read from ``MDB_MODEL_DIR`` (``<model>.safetensors`` with the key names of the model classes, VAE from the
 request's ``vae`` or the family default). Without a checkpoint the backend runs the same path on deterministic random
 weights and says so in its result sidecar (``"weights": "random-init"``); ``MDB_ARCH=tiny`` selects the tiny
 architectures (CPU tests). Text conditioning comes from pre-encoded caption files (``sample_caps_pos`` / ``_neg``:
-``text_embedding`` [1,T,D], optional ``pooled``) or, failing that, from a deterministic embedding of the prompt hash.
-``ltx2`` (video) is admitted by the control plane but refused here with a clear message: the video VAE decoder that turns
-its latents into frames is not part of this package yet."""
+``text_embedding`` [1,T,D], optional ``pooled``) or, failing that, from a deterministic embedding of the prompt hash."""
 from __future__ import annotations
 
 import dataclasses
@@ -35,9 +38,8 @@ from ..sampling.guidance import cfg_textbook, cfg_true_with_norm_rescale
 from .backend import GenBackend, JobParams, StepResult, UnsupportedParam, reject_unsupported_common
 from .flux_backend import prompt_embedding
 
-KINDS = ("zimage", "qwenimage", "sdxl")
-_REFUSED = {"ltx2": "video generation needs the LTX video VAE decoder, which this package does not ship yet",
-            "sd3": "the SD3 MMDiT variant is not wired to a serving loop", "sd15": "the SD 1.5 UNet variant is not wired"}
+KINDS = ("zimage", "qwenimage", "sdxl", "ltx2")
+_REFUSED = {"sd3": "the SD3 MMDiT variant is not wired to a serving loop", "sd15": "the SD 1.5 UNet variant is not wired"}
 
 
 def _size_ids(values, dim: int = 256) -> torch.Tensor:
@@ -133,6 +135,9 @@ class GenericBackend(GenBackend):
         if self.kind == "qwenimage":
             from ..models import qwen_image as M
             return M.tiny_qwen_image_config() if self.tiny else M.qwen_image_config()
+        if self.kind == "ltx2":
+            from ..models import video_dit as M
+            return M.tiny_video_dit_config() if self.tiny else M.ltx2_config()
         from ..models import unet as M
         return M.tiny_unet_config() if self.tiny else M.sdxl_config()
 
@@ -146,7 +151,7 @@ class GenericBackend(GenBackend):
     def _text_shape(self, cfg):
         if self.kind == "zimage":
             return (32 if self.tiny else 128), cfg.cap_dim, 0
-        if self.kind == "qwenimage":
+        if self.kind in ("qwenimage", "ltx2"):
             return (32 if self.tiny else 256), cfg.context_dim, 0
         return 77, cfg.context_dim, cfg.adm_in_channels - 6 * 256 if not self.tiny else cfg.adm_in_channels
 
@@ -177,6 +182,8 @@ class GenericBackend(GenBackend):
             from ..models.single_dit import SingleStreamDiT as Cls
         elif self.kind == "qwenimage":
             from ..models.qwen_image import QwenImageDiT as Cls
+        elif self.kind == "ltx2":
+            from ..models.video_dit import VideoDiT as Cls
         else:
             from ..models.unet import UNet as Cls
         model = Cls(self.cfg, self.dtype, self.device)
@@ -192,7 +199,12 @@ class GenericBackend(GenBackend):
         else:
             model.init_weights(seed=0)
             self.weights_kind = "random-init"
-        vae = AutoencoderKL(self._vae_config(), self.dtype, self.device, with_encoder=False)
+        if self.kind == "ltx2":
+            from ..models.video_vae import VideoVAE, ltx2_vae_config, tiny_video_vae_config
+            vcfg = dataclasses.replace(tiny_video_vae_config(), latent_channels=self.cfg.in_channels) if self.tiny else ltx2_vae_config()
+            vae = VideoVAE(vcfg, self.dtype, self.device)
+        else:
+            vae = AutoencoderKL(self._vae_config(), self.dtype, self.device, with_encoder=False)
         vpath = os.path.join(root, p.vae) if (root and p.vae) else ""
         if vpath and os.path.isfile(vpath):
             vae.load_state_dict(load_safetensors(vpath, device=str(self.device), dtype=self.dtype), strict=False)
@@ -203,16 +215,32 @@ class GenericBackend(GenBackend):
 
     def _prepare(self, p: JobParams) -> None:
         from ..models.mmdit import pack_latents
-        f = self.vae.spatial_factor
-        C = self.vae.cfg.z_channels
-        h, w = p.height // f, p.width // f
-        g = torch.Generator().manual_seed(int(p.seed) & 0x7FFFFFFFFFFFFFFF)
-        noise = torch.randn(1, C, h, w, generator=g)
         dev, dt = self.device, self.dtype
+        g = torch.Generator().manual_seed(int(p.seed) & 0x7FFFFFFFFFFFFFFF)
         self.txt_d = self.txt.to(dev, dt)
         if self.use_cfg:
             self.txt_neg_d = self.txt_neg.to(dev, dt)
         self.t = torch.empty(1, device=dev)
+        if self.kind == "ltx2":
+            ft, fs = self.vae.expansion()
+            frames = 9
+            try:
+                frames = int(json.loads(p.params_json).get("frames", frames)) if p.params_json else frames
+            except (ValueError, AttributeError):
+                pass
+            if p.width % fs or p.height % fs:
+                raise UnsupportedParam(f"ltx2: width/height must be multiples of {fs}")
+            F_lat = 1 + max(frames - 1, 0) // ft
+            self.grid = (F_lat, p.height // fs, p.width // fs)
+            C = self.cfg.in_channels
+            noise = torch.randn(1, self.grid[0] * self.grid[1] * self.grid[2], C, generator=g)
+            self.sigmas = fm.ltx2_linear_quadratic_sigmas(p.steps)
+            self.x = noise.float().to(dev)
+            return
+        f = self.vae.spatial_factor
+        C = self.vae.cfg.z_channels
+        h, w = p.height // f, p.width // f
+        noise = torch.randn(1, C, h, w, generator=g)
         if self.kind == "sdxl":
             from ..sampling.ddpm import SDXLEulerScheduler
             self.sched = SDXLEulerScheduler(p.steps)
@@ -248,6 +276,14 @@ class GenericBackend(GenBackend):
             return
         s, s_next = float(self.sigmas[i]), float(self.sigmas[i + 1])
         xb = self.x.to(self.dtype)
+        if self.kind == "ltx2":
+            self.t.fill_(s)
+            v = self.model(xb, self.txt_d, self.t, self.grid).float()
+            if self.use_cfg:
+                v = cfg_textbook(v, self.model(xb, self.txt_neg_d, self.t, self.grid).float(), p.cfg)
+            last = i == p.steps - 1
+            self.x = self.x + ((0.0 - s) if last else (s_next - s)) * v       # the final step lands on x - v * sigma
+            return
         if self.kind == "zimage":
             self.t.fill_(1.0 - s)                         # the model's clock runs from noise (0) to image (1)
             v = -self.model(xb, self.txt_d, self.t, self.hw).float()
@@ -265,6 +301,8 @@ class GenericBackend(GenBackend):
     @torch.no_grad()
     def _decode_and_save(self, p: JobParams) -> str:
         from ..models.mmdit import unpack_latents
+        if self.kind == "ltx2":
+            return self._decode_video(p)
         z = self.x if self.kind == "sdxl" else unpack_latents(self.x, self.hw[0], self.hw[1])
         img = self.vae.tiled_decode(z) if max(z.shape[-2:]) > 96 else self.vae.decode(z)
         arr = tensor_to_uint8(img[0].float().permute(1, 2, 0).cpu()).numpy()
@@ -276,11 +314,33 @@ class GenericBackend(GenBackend):
         os.replace(tmp, path)
         return path
 
+    def _decode_video(self, p: JobParams) -> str:
+        Fl, H, W = self.grid
+        z = self.x.reshape(1, Fl, H, W, -1).permute(0, 4, 1, 2, 3)
+        vid = self.vae.decode(z.to(self.dtype))[0].float().permute(1, 2, 3, 0).cpu()       # [T, H, W, 3]
+        os.makedirs(p.out_dir or ".", exist_ok=True)
+        path = p.output_path()
+        fdir = path[:-4] + ".frames"
+        os.makedirs(fdir, exist_ok=True)
+        self.frames_written = int(vid.shape[0])
+        for t in range(vid.shape[0]):
+            arr = tensor_to_uint8(vid[t]).numpy()
+            with open(os.path.join(fdir, f"{t:04d}.png"), "wb") as f:
+                f.write(encode_png(arr, {}))
+        tmp = path + ".tmp"
+        with open(tmp, "wb") as f:
+            f.write(encode_png(tensor_to_uint8(vid[0]).numpy(), {"serenity.genparams.v1": p.genparams_text()}))
+        os.replace(tmp, path)
+        return path
+
     def _write_sidecar(self, p: JobParams, path: str) -> None:
         peak = torch.cuda.max_memory_allocated() if self.device.type == "cuda" else 0
         side = {"schema": f"serenity.{self.kind}.daemon_result.v1", "job_id": p.job_id, "model": p.model,
                 "weights": self.weights_kind, "text": self.text_kind, "cfg": p.cfg if self.use_cfg else 1.0,
                 "stage_seconds": {k: round(v, 4) for k, v in self.stage_s.items()}, "peak_device_bytes": int(peak),
                 "steps_run": p.steps, "sampler": "euler", "device": str(self.device)}
+        if self.kind == "ltx2":
+            side["frames"] = self.frames_written
+            side["frames_dir"] = path[:-4] + ".frames"
         with open(path + ".worker_result.json", "w") as f:
             json.dump(side, f)

@@ -408,7 +408,7 @@ def test_model_swap_restarts_worker_with_flux_kind(bins, tmp_path):
 
 
 @pytest.mark.parametrize("model,backend,cfg", [("z-image-tiny", "zimage", 4.0), ("qwen-image-tiny", "qwenimage", 1.0),
-                                               ("sd_xl_tiny", "sdxl", 5.0)])
+                                               ("sd_xl_tiny", "sdxl", 5.0), ("ltx-2-tiny", "ltx2", 3.0)])
 def test_other_families_serve_through_the_worker(bins, tmp_path, model, backend, cfg):
     """Z-Image, Qwen-Image and SDXL jobs run their own phase machines in the worker (tiny architectures, random weights),
     with classifier-free guidance when cfg > 1; the result carries the parameters and a sidecar naming the family."""
@@ -425,5 +425,7 @@ def test_other_families_serve_through_the_worker(bins, tmp_path, model, backend,
         assert side["schema"] == f"serenity.{backend}.daemon_result.v1" and side["weights"] == "random-init"
         assert side["cfg"] == (cfg if cfg > 1 else 1.0) and side["steps_run"] == 2
         assert s.call("GET", "/v1/health")[1]["backend"] == backend
+        if backend == "ltx2":                       # video: frames beside the poster image
+            assert side["frames"] == 9 and len(os.listdir(side["frames_dir"])) == 9
     finally:
         s.close()
