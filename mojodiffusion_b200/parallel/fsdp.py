@@ -232,3 +232,60 @@ class FSDPLinear(nn.Module):
         parts = [torch.empty_like(self.master) for _ in range(self.ctx.world)]
         dist.all_gather(parts, self.master, group=self.ctx.group)
         return torch.cat(parts, 0)
+
+
+class ShardedLinear(nn.Module):
+    """Drop-in for ``models.layers.Linear`` inside a fully-sharded model: the projection is an :class:`FSDPLinear` (weight
+    rows sharded over the ranks, collectives inside the GEMMs), the activation / gated residual that ``Linear`` fuses into
+    its epilogue run as the differentiable element-wise ops after it."""
+
+    def __init__(self, ctx: FSDPContext, lin):
+        super().__init__()
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+        self.inner = FSDPLinear(ctx, lin.in_features, lin.out_features, bias=lin.bias is not None,
+                                full_weight=lin.weight.detach())
+        if lin.bias is not None:
+            with torch.no_grad():
+                self.inner.bias.copy_(lin.bias)
+        self.slots = nn.ModuleList()
+
+    @property
+    def bias(self):
+        return self.inner.bias
+
+    def forward(self, x, act=None, residual=None, gate=None, rows_per_group: int = 1, out=None):
+        y = self.inner(x)
+        if act is not None:
+            y = ops.activation(y, act)
+        if residual is not None:
+            y = ops.gate_residual(residual, y, gate, rows_per_group)
+        elif gate is not None:
+            raise ValueError("a gate needs a residual")
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+
+def shard_model(model: nn.Module, ctx: FSDPContext, min_params: int = 1 << 16, skip=()) -> int:
+    """Replace every ``Linear`` of ``model`` whose weight has at least ``min_params`` elements and whose row count
+    divides by the world size with a :class:`ShardedLinear` (the full weight is released as soon as its shard has been
+    cut), then allocate the context. Returns the number of sharded layers; the remaining parameters (norm scales, biases,
+    small embedders) stay replicated and are the caller's to all-reduce."""
+    from ..models.layers import Linear
+    todo = []
+    for name, mod in model.named_modules():
+        for cname, child in mod.named_children():
+            full = f"{name}.{cname}" if name else cname
+            if isinstance(child, Linear) and child.weight.numel() >= min_params and child.out_features % ctx.world == 0 \
+                    and child.in_features % 8 == 0 and len(child.slots) == 0 and not any(full.startswith(s) for s in skip):
+                todo.append((mod, cname, child))
+    for mod, cname, child in todo:
+        sharded = ShardedLinear(ctx, child)
+        child.weight.data = torch.empty(0, dtype=child.weight.dtype, device=child.weight.device)
+        if isinstance(mod, (nn.ModuleList, nn.ModuleDict)):
+            mod[int(cname) if isinstance(mod, nn.ModuleList) else cname] = sharded
+        else:
+            setattr(mod, cname, sharded)
+    ctx.finalize()
+    return len(todo)
