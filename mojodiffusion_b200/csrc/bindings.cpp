@@ -616,6 +616,24 @@ void ema_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, b
            "ema_multi");
 }
 
+void adamw8bit(Tensor p, const Tensor& g, Tensor qm, Tensor qv, Tensor am, Tensor av, const Tensor& code_s,
+               const Tensor& code_u, double lr, double b1, double b2, double eps, double wd, int64_t step, double grad_scale) {
+  c10::cuda::CUDAGuard guard(p.device());
+  const int64_t n = p.numel();
+  TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && g.numel() == n, "adamw8bit: contiguous p / g of one size");
+  TORCH_CHECK(qm.scalar_type() == at::kByte && qv.scalar_type() == at::kByte && qm.numel() == n && qv.numel() == n, "adamw8bit: codes");
+  TORCH_CHECK(am.scalar_type() == at::kFloat && av.scalar_type() == at::kFloat && am.numel() == (n + 255) / 256 && av.numel() == am.numel(),
+              "adamw8bit: one fp32 maximum per 256 elements");
+  TORCH_CHECK(code_s.scalar_type() == at::kFloat && code_s.numel() == 256 && code_u.scalar_type() == at::kFloat && code_u.numel() == 256,
+              "adamw8bit: 256-entry code books");
+  const bool pb = p.scalar_type() == at::kBFloat16, gb = g.scalar_type() == at::kBFloat16;
+  TORCH_CHECK((pb || p.scalar_type() == at::kFloat) && (gb || g.scalar_type() == at::kFloat), "adamw8bit: bf16 or fp32");
+  check_rc(mdb_adamw8bit(p.data_ptr(), g.data_ptr(), qm.data_ptr(), qv.data_ptr(), am.data_ptr<float>(), av.data_ptr<float>(),
+                         code_s.data_ptr<float>(), code_u.data_ptr<float>(), n, pb, gb, (float)lr, (float)b1, (float)b2,
+                         (float)eps, (float)wd, (int)step, (float)grad_scale, cur_stream()),
+           "adamw8bit");
+}
+
 // ------------------------------------------------------------------------------------------
 // peer-memory communication (addresses come from symmetric-memory handles: one entry per rank)
 // ------------------------------------------------------------------------------------------
@@ -766,6 +784,7 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("adamw_multi", &adamw_multi);
   m.def("sumsq_multi", &sumsq_multi);
   m.def("ema_multi", &ema_multi);
+  m.def("adamw8bit", &adamw8bit);
   m.def("flag_signal", &flag_signal);
   m.def("flag_wait", &flag_wait);
   m.def("flag_barrier", &flag_barrier);

@@ -107,6 +107,12 @@ int mdb_sumsq_multi(const MdbTensorEntry* tensors, const int* chunks, int num_ch
 int mdb_ema_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
                   float decay, cudaStream_t st);
 
+// AdamW with block-wise (256 elements) 8-bit moments: qm / qv hold code-book indices, am / av one fp32 maximum per
+// block; code_s / code_u are the 256-entry signed / unsigned code books (ascending). step == 1 starts from zero moments.
+int mdb_adamw8bit(void* p, const void* g, void* qm, void* qv, float* am, float* av, const float* code_s,
+                  const float* code_u, long long n, int p_bf16, int g_bf16, float lr, float b1, float b2, float eps,
+                  float wd, int step, float grad_scale, cudaStream_t st);
+
 // ---- attention_tcgen05.cu
 // q,k,v,o: bf16 with element strides (batch, seq, head); head_dim contiguous (Dh = 128 or 64).
 // lse: optional fp32 [B, H, Sq] (natural-log-sum-exp of the scaled scores) for the backward pass.

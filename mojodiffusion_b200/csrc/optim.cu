@@ -201,3 +201,110 @@ extern "C" int mdb_ema_multi(const MdbTensorEntry* tensors, const int* chunks, i
     ema_multi_kernel<float><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, decay);
   return (int)cudaGetLastError();
 }
+
+
+// ---------------------------------------------------------------------------------
+// AdamW with 8-bit block-wise quantised moments: each block of 256 elements stores its two moments as indices into a
+// 256-entry non-uniform code book (signed for the first moment, unsigned for the second) plus one fp32 absolute maximum
+// per block and moment. One CTA = one block: de-quantise through the code books staged in shared memory, update, write
+// the parameter, find the new block maxima, re-quantise to the nearest code (binary search, ties to the smaller code).
+// Role of the reference's serenitymojo/training/adamw8bit.mojo (32 KB of fp32 optimizer state per million parameters
+// instead of 8 MB).
+// ---------------------------------------------------------------------------------
+namespace mdb {
+__device__ __forceinline__ int nearest_code(const float* code, float x) {
+  // smallest idx with code[idx] >= x, clamped to [1, 255]  (matches a left bisection)
+  int lo = 0, hi = 256;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int mid = (lo + hi) >> 1;
+    if (code[mid] < x) lo = mid + 1; else hi = mid;
+  }
+  int idx = lo < 1 ? 1 : (lo > 255 ? 255 : lo);
+  const float a = code[idx - 1], b = code[idx];
+  return (fabsf(x - a) <= fabsf(b - x)) ? idx - 1 : idx;
+}
+
+template <typename PT, typename GT>
+__global__ void __launch_bounds__(256) adamw8bit_kernel(PT* __restrict__ p, const GT* __restrict__ g,
+                                                        uint8_t* __restrict__ qm, uint8_t* __restrict__ qv,
+                                                        float* __restrict__ am, float* __restrict__ av,
+                                                        const float* __restrict__ code_s, const float* __restrict__ code_u,
+                                                        long long n, float lr, float b1, float b2, float eps, float wd,
+                                                        float bc1, float bc2_sqrt, float grad_scale, int first) {
+  __shared__ float cs[256], cu[256];
+  __shared__ float red_m[8], red_v[8];
+  cs[threadIdx.x] = code_s[threadIdx.x];
+  cu[threadIdx.x] = code_u[threadIdx.x];
+  __syncthreads();
+  for (long long blk = blockIdx.x; blk * 256 < n; blk += gridDim.x) {
+    const long long i = blk * 256 + threadIdx.x;
+    const bool in = i < n;
+    float m = 0.f, v = 0.f, gv = 0.f;
+    if (in) {
+      gv = static_cast<float>(g[i]) * grad_scale;
+      if (!first) {
+        m = cs[qm[i]] * am[blk];
+        v = cu[qv[i]] * av[blk];
+      }
+      m = b1 * m + (1.f - b1) * gv;
+      v = b2 * v + (1.f - b2) * gv * gv;
+      float pf = static_cast<float>(p[i]) * (1.f - lr * wd);
+      pf -= (lr / bc1) * m / (sqrtf(v) / bc2_sqrt + eps);
+      p[i] = static_cast<PT>(pf);
+    }
+    float mx = in ? fabsf(m) : 0.f, vx = in ? fabsf(v) : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      vx = fmaxf(vx, __shfl_xor_sync(0xffffffffu, vx, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+      red_m[threadIdx.x >> 5] = mx;
+      red_v[threadIdx.x >> 5] = vx;
+    }
+    __syncthreads();
+    mx = red_m[0];
+    vx = red_v[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) {
+      mx = fmaxf(mx, red_m[w]);
+      vx = fmaxf(vx, red_v[w]);
+    }
+    mx = fmaxf(mx, 1e-30f);
+    vx = fmaxf(vx, 1e-30f);
+    if (in) {
+      qm[i] = static_cast<uint8_t>(nearest_code(cs, m / mx));
+      qv[i] = static_cast<uint8_t>(nearest_code(cu, v / vx));
+    }
+    if (threadIdx.x == 0) {
+      am[blk] = mx;
+      av[blk] = vx;
+    }
+    __syncthreads();
+  }
+}
+}  // namespace mdb
+
+extern "C" int mdb_adamw8bit(void* p, const void* g, void* qm, void* qv, float* am, float* av, const float* code_s,
+                             const float* code_u, long long n, int p_bf16, int g_bf16, float lr, float b1, float b2, float eps,
+                             float wd, int step, float grad_scale, cudaStream_t st) {
+  using namespace mdb;
+  if (n <= 0) return 0;
+  const long long blocks = (n + 255) / 256;
+  const int grid = blocks < 148 * 16 ? static_cast<int>(blocks) : 148 * 16;
+  const float bc1 = 1.f - powf(b1, static_cast<float>(step));
+  const float bc2s = sqrtf(1.f - powf(b2, static_cast<float>(step)));
+  const int first = step <= 1;
+  uint8_t* a = static_cast<uint8_t*>(qm);
+  uint8_t* b = static_cast<uint8_t*>(qv);
+#define MDB_A8(PT, GT)                                                                                               \
+  adamw8bit_kernel<PT, GT><<<grid, 256, 0, st>>>(static_cast<PT*>(p), static_cast<const GT*>(g), a, b, am, av, code_s, \
+                                                 code_u, n, lr, b1, b2, eps, wd, bc1, bc2s, grad_scale, first)
+  if (p_bf16 && g_bf16) MDB_A8(__nv_bfloat16, __nv_bfloat16);
+  else if (p_bf16) MDB_A8(__nv_bfloat16, float);
+  else if (g_bf16) MDB_A8(float, __nv_bfloat16);
+  else MDB_A8(float, float);
+#undef MDB_A8
+  return static_cast<int>(cudaGetLastError());
+}

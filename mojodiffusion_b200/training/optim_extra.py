@@ -252,7 +252,31 @@ class AdamW8bit(_Base):
         self.step_count += 1
         t = self.step_count
         b1, b2 = self.betas
-        for p, g in self._grads(grad_scale):
+        from ..ops import native
+        for p in self.params:
+            if p.grad is None or not (p.is_cuda and native.use_native(p)) or p.dtype not in (torch.bfloat16, torch.float32):
+                continue
+            # GPU: one kernel per tensor de-quantises, updates and re-quantises block by block (csrc/optim.cu)
+            st = self.state.get(id(p))
+            n = p.numel()
+            if st is None:
+                nb = (n + self.block - 1) // self.block
+                st = {"qm": torch.zeros(n, dtype=torch.uint8, device=p.device), "qv": torch.zeros(n, dtype=torch.uint8, device=p.device),
+                      "am": torch.zeros(nb, device=p.device), "av": torch.zeros(nb, device=p.device), "t": 0}
+                self.state[id(p)] = st
+                self._codes = getattr(self, "_codes", {})
+                if p.device not in self._codes:
+                    self._codes[p.device] = (self.code_s.to(p.device).contiguous(), self.code_u.to(p.device).contiguous())
+            cs, cu = self._codes[p.device]
+            st["t"] += 1
+            g = p.grad if p.grad.dtype in (torch.bfloat16, torch.float32) else p.grad.float()
+            assert self.block == 256 and p.is_contiguous()
+            native.ops().adamw8bit(p.data, g.contiguous(), st["qm"], st["qv"], st["am"], st["av"], cs, cu, lr, b1, b2, self.eps,
+                                   self.wd, st["t"], grad_scale)
+        for p in self.params:
+            if p.grad is None or (p.is_cuda and native.use_native(p) and p.dtype in (torch.bfloat16, torch.float32)):
+                continue
+            g = p.grad.float() * grad_scale
             st = self.state.get(id(p))
             if st is None:
                 m, v = torch.zeros_like(g), torch.zeros_like(g)
