@@ -9,6 +9,9 @@ it), each with its own model class, latent layout, schedule and guidance rule:
   (serenitymojo/serve/qwenimage_backend.mojo).
 * ``sdxl``     UNet, eps-prediction Euler over the scaled-linear DDPM grid, CFG, ``y`` = pooled text + six sinusoidal
   size / crop ids (serenitymojo/serve/sdxl_backend.mojo).
+* ``sd3``      SD3.5 joint-block MMDiT on [1,16,h,w] latents (patch embedding inside the model), shift-3 flow-matching
+  Euler, textbook CFG, context = CLIP (77) + T5 (256) tokens with a 2048-wide pooled vector
+  (serenitymojo/serve/sd3_backend.mojo).
 * ``ltx2``     48-layer video DiT over [frames x h x w] latent tokens, linear-quadratic (distilled) sigmas, Euler with
   the last step landing on ``x - v * sigma``, textbook CFG; the 128-channel video VAE expands 8x in time and 32x in space;
   frames are written as ``<job>.frames/NNNN.png`` and the first frame as the job's output image; the frame count comes
@@ -38,8 +41,8 @@ from ..sampling.guidance import cfg_textbook, cfg_true_with_norm_rescale
 from .backend import GenBackend, JobParams, StepResult, UnsupportedParam, reject_unsupported_common
 from .flux_backend import prompt_embedding
 
-KINDS = ("zimage", "qwenimage", "sdxl", "ltx2")
-_REFUSED = {"sd3": "the SD3 MMDiT variant is not wired to a serving loop", "sd15": "the SD 1.5 UNet variant is not wired"}
+KINDS = ("zimage", "qwenimage", "sdxl", "ltx2", "sd3")
+_REFUSED = {"sd15": "the SD 1.5 UNet variant is not wired"}
 
 
 def _size_ids(values, dim: int = 256) -> torch.Tensor:
@@ -138,6 +141,9 @@ class GenericBackend(GenBackend):
         if self.kind == "ltx2":
             from ..models import video_dit as M
             return M.tiny_video_dit_config() if self.tiny else M.ltx2_config()
+        if self.kind == "sd3":
+            from ..models import sd3 as M
+            return M.tiny_sd3_config() if self.tiny else M.sd35_large_config()
         from ..models import unet as M
         return M.tiny_unet_config() if self.tiny else M.sdxl_config()
 
@@ -145,7 +151,9 @@ class GenericBackend(GenBackend):
         from ..models import vae as V
         zc = 4 if self.kind == "sdxl" else 16
         if self.tiny:
-            return dataclasses.replace(V.tiny_vae_config(), z_channels=zc)
+            return dataclasses.replace(V.tiny_vae_config(), z_channels=self.cfg.in_channels if self.kind == "sd3" else zc)
+        if self.kind == "sd3":
+            return V.sd3_vae_config()
         return V.sdxl_vae_config() if self.kind == "sdxl" else V.flux_vae_config()
 
     def _text_shape(self, cfg):
@@ -153,6 +161,8 @@ class GenericBackend(GenBackend):
             return (32 if self.tiny else 128), cfg.cap_dim, 0
         if self.kind in ("qwenimage", "ltx2"):
             return (32 if self.tiny else 256), cfg.context_dim, 0
+        if self.kind == "sd3":
+            return (24 if self.tiny else 333), cfg.context_dim, cfg.pooled_dim
         return 77, cfg.context_dim, cfg.adm_in_channels - 6 * 256 if not self.tiny else cfg.adm_in_channels
 
     # ---- phases -------------------------------------------------------------------------------------------------
@@ -184,6 +194,8 @@ class GenericBackend(GenBackend):
             from ..models.qwen_image import QwenImageDiT as Cls
         elif self.kind == "ltx2":
             from ..models.video_dit import VideoDiT as Cls
+        elif self.kind == "sd3":
+            from ..models.sd3 import SD3MMDiT as Cls
         else:
             from ..models.unet import UNet as Cls
         model = Cls(self.cfg, self.dtype, self.device)
@@ -253,6 +265,12 @@ class GenericBackend(GenBackend):
                 self.y = torch.cat((self.pooled, ids), 1).to(dev, dt)
                 self.y_neg = torch.cat((self.pooled_neg, ids), 1).to(dev, dt) if self.use_cfg else None
             return
+        if self.kind == "sd3":
+            self.sigmas = fm.sd3_sigmas(p.steps, p.sigma_shift if p.sigma_shift > 0 else 3.0)
+            self.x = noise.float().to(dev)
+            self.y = self.pooled.to(dev, dt)
+            self.y_neg = self.pooled_neg.to(dev, dt) if self.use_cfg else None
+            return
         self.hw = (h // 2, w // 2)
         S_img = self.hw[0] * self.hw[1]
         if self.kind == "qwenimage":
@@ -284,6 +302,13 @@ class GenericBackend(GenBackend):
             last = i == p.steps - 1
             self.x = self.x + ((0.0 - s) if last else (s_next - s)) * v       # the final step lands on x - v * sigma
             return
+        if self.kind == "sd3":
+            self.t.fill_(s)
+            v = self.model(xb, self.txt_d, self.t, self.y).float()
+            if self.use_cfg:
+                v = cfg_textbook(v, self.model(xb, self.txt_neg_d, self.t, self.y_neg).float(), p.cfg)
+            self.x = self.x + (s_next - s) * v
+            return
         if self.kind == "zimage":
             self.t.fill_(1.0 - s)                         # the model's clock runs from noise (0) to image (1)
             v = -self.model(xb, self.txt_d, self.t, self.hw).float()
@@ -303,7 +328,7 @@ class GenericBackend(GenBackend):
         from ..models.mmdit import unpack_latents
         if self.kind == "ltx2":
             return self._decode_video(p)
-        z = self.x if self.kind == "sdxl" else unpack_latents(self.x, self.hw[0], self.hw[1])
+        z = self.x if self.kind in ("sdxl", "sd3") else unpack_latents(self.x, self.hw[0], self.hw[1])
         img = self.vae.tiled_decode(z) if max(z.shape[-2:]) > 96 else self.vae.decode(z)
         arr = tensor_to_uint8(img[0].float().permute(1, 2, 0).cpu()).numpy()
         os.makedirs(p.out_dir or ".", exist_ok=True)
