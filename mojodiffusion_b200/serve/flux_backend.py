@@ -24,7 +24,7 @@ from ..io.safetensors_io import load_safetensors
 from ..sampling import flow_match as fm
 from .backend import GenBackend, JobParams, StepResult, reject_unsupported_common
 
-_CONFIGS = {"flux": "flux1_dev_config", "chroma": "flux1_dev_config", "klein": "flux1_dev_config", "tiny": "tiny_mmdit_config"}
+_CONFIGS = {"flux": "flux1_dev_config", "tiny": "tiny_mmdit_config"}
 
 
 def prompt_embedding(prompt: str, tokens: int, dim: int, pooled_dim: int):

@@ -12,6 +12,10 @@ it), each with its own model class, latent layout, schedule and guidance rule:
 * ``sd3``      SD3.5 joint-block MMDiT on [1,16,h,w] latents (patch embedding inside the model), shift-3 flow-matching
   Euler, textbook CFG, context = CLIP (77) + T5 (256) tokens with a 2048-wide pooled vector
   (serenitymojo/serve/sd3_backend.mojo).
+* ``klein``    FLUX.2 Klein MMDiT (shared modulation, SwiGLU), 32-channel VAE packed 2x2 into 128-wide tokens, the
+  empirical-mu schedule of FLUX.2, textbook CFG for the non-distilled checkpoints (serenitymojo/serve/klein_backend.mojo).
+* ``chroma``   Chroma MMDiT (one distilled guidance layer instead of per-block modulation), 16-channel VAE, T5 text,
+  shift-1.15 schedule, textbook CFG (serenitymojo/pipeline/chroma_sample_cli.mojo).
 * ``ltx2``     48-layer video DiT over [frames x h x w] latent tokens, linear-quadratic (distilled) sigmas, Euler with
   the last step landing on ``x - v * sigma``, textbook CFG; the 128-channel video VAE expands 8x in time and 32x in space;
   frames are written as ``<job>.frames/NNNN.png`` and the first frame as the job's output image; the frame count comes
@@ -41,7 +45,7 @@ from ..sampling.guidance import cfg_textbook, cfg_true_with_norm_rescale
 from .backend import GenBackend, JobParams, StepResult, UnsupportedParam, reject_unsupported_common
 from .flux_backend import prompt_embedding
 
-KINDS = ("zimage", "qwenimage", "sdxl", "ltx2", "sd3")
+KINDS = ("zimage", "qwenimage", "sdxl", "ltx2", "sd3", "klein", "chroma")
 _REFUSED = {"sd15": "the SD 1.5 UNet variant is not wired"}
 
 
@@ -144,6 +148,12 @@ class GenericBackend(GenBackend):
         if self.kind == "sd3":
             from ..models import sd3 as M
             return M.tiny_sd3_config() if self.tiny else M.sd35_large_config()
+        if self.kind == "klein":
+            from ..models import flux2 as M
+            return M.tiny_flux2_config() if self.tiny else M.klein_9b_config()
+        if self.kind == "chroma":
+            from ..models import chroma as M
+            return M.tiny_chroma_config() if self.tiny else M.chroma_config()
         from ..models import unet as M
         return M.tiny_unet_config() if self.tiny else M.sdxl_config()
 
@@ -151,9 +161,13 @@ class GenericBackend(GenBackend):
         from ..models import vae as V
         zc = 4 if self.kind == "sdxl" else 16
         if self.tiny:
+            if self.kind in ("klein", "chroma"):
+                zc = self.cfg.in_channels // 4
             return dataclasses.replace(V.tiny_vae_config(), z_channels=self.cfg.in_channels if self.kind == "sd3" else zc)
         if self.kind == "sd3":
             return V.sd3_vae_config()
+        if self.kind == "klein":
+            return V.flux2_vae_config()
         return V.sdxl_vae_config() if self.kind == "sdxl" else V.flux_vae_config()
 
     def _text_shape(self, cfg):
@@ -161,6 +175,8 @@ class GenericBackend(GenBackend):
             return (32 if self.tiny else 128), cfg.cap_dim, 0
         if self.kind in ("qwenimage", "ltx2"):
             return (32 if self.tiny else 256), cfg.context_dim, 0
+        if self.kind in ("klein", "chroma"):
+            return (32 if self.tiny else 512), cfg.context_dim, 0
         if self.kind == "sd3":
             return (24 if self.tiny else 333), cfg.context_dim, cfg.pooled_dim
         return 77, cfg.context_dim, cfg.adm_in_channels - 6 * 256 if not self.tiny else cfg.adm_in_channels
@@ -196,6 +212,10 @@ class GenericBackend(GenBackend):
             from ..models.video_dit import VideoDiT as Cls
         elif self.kind == "sd3":
             from ..models.sd3 import SD3MMDiT as Cls
+        elif self.kind == "klein":
+            from ..models.flux2 import Flux2DiT as Cls
+        elif self.kind == "chroma":
+            from ..models.chroma import ChromaDiT as Cls
         else:
             from ..models.unet import UNet as Cls
         model = Cls(self.cfg, self.dtype, self.device)
@@ -275,6 +295,10 @@ class GenericBackend(GenBackend):
         S_img = self.hw[0] * self.hw[1]
         if self.kind == "qwenimage":
             self.sigmas = fm.qwen_image_sigmas(p.steps, S_img)
+        elif self.kind == "klein":
+            self.sigmas = fm.flux2_klein_sigmas(p.steps, S_img)
+        elif self.kind == "chroma":
+            self.sigmas = fm.shifted_sigmas(p.steps, 1.15)
         else:
             self.sigmas = fm.shifted_sigmas(p.steps, p.sigma_shift if p.sigma_shift > 0 else 3.0)
         self.x = pack_latents(noise).float().to(dev)
@@ -320,7 +344,7 @@ class GenericBackend(GenBackend):
             v = self.model(xb, self.txt_d, self.t, self.hw).float()
             if self.use_cfg:
                 vu = self.model(xb, self.txt_neg_d, self.t, self.hw).float()
-                v = cfg_true_with_norm_rescale(v, vu, p.cfg)
+                v = cfg_true_with_norm_rescale(v, vu, p.cfg) if self.kind == "qwenimage" else cfg_textbook(v, vu, p.cfg)
         self.x = self.x + (s_next - s) * v
 
     @torch.no_grad()

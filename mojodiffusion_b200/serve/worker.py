@@ -22,7 +22,7 @@ def make_backend(kind: str) -> GenBackend:
     if kind == "stub":
         from .stub_backend import StubBackend
         return StubBackend()
-    if kind in ("flux", "chroma", "klein"):
+    if kind == "flux":
         from .flux_backend import FluxBackend
         return FluxBackend(kind)
     from .generic_backend import GenericBackend
