@@ -105,6 +105,8 @@ def main():
     if lib_baseline:
         os.environ["MDB200_FORCE_REFERENCE"] = "1"
         args.sp_mode = "nccl"
+        if args.train_steps < 0:
+            args.train_steps = 0     # the library arm times the denoise loop; its training step is opt-in (--train-steps K)
 
     import torch
     import torch.distributed as dist

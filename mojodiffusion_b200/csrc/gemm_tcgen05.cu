@@ -996,12 +996,12 @@ static int launch_pair_variant(const GemmMaps& maps, const GemmParams& p, int nu
 
 }  // namespace mdb
 
-// MDB200_GEMM_PAIR=1 lets automatically tiled GEMMs choose the CTA-pair kernel; default: one-CTA kernel only.
+// MDB200_GEMM_PAIR=0 keeps every automatically tiled GEMM on the one-CTA kernel (A/B measurements); default: choose.
 static int pair_mode() {
   static int mode = -1;
   if (mode < 0) {
     const char* e = getenv("MDB200_GEMM_PAIR");
-    mode = (e != nullptr && e[0] == '1') ? 1 : 0;
+    mode = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
   return mode;
 }
@@ -1016,8 +1016,9 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   int bn = a->bn;
   // bn == 512 asks for the CTA-pair kernel (256 x 256 tile over two SMs); it shares the tensor maps of the 128 x 256 tile
   const bool pair_ok = a->kind == 0 && a->conv_taps <= 0 && a->gather_world <= 1 && a->split_k <= 1;
-  bool use_pair = bn == 512 && pair_ok;
-  if (bn == 512) bn = 256;
+  bool use_pair = (bn == 512 || bn == 513) && pair_ok;
+  const bool pair_deep = bn == 513;          // 7-stage ring (measurement variant of the K-major kernel)
+  if (bn == 512 || bn == 513) bn = 256;
   const bool auto_tile = bn != 64 && bn != 128 && bn != 256;
   if (bn != 64 && bn != 128 && bn != 256) {
     // default tile choice: 128x256 unless the narrower 128x128 tile fills the machine noticeably better
@@ -1035,14 +1036,14 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   if (paired && bn != 256) bn = 256;
   if (auto_tile && pair_ok && a->M > BM && pair_mode() != 0) {
     // CTA pair (256 x 256 tile on two SMs) or lone CTAs? Compare waves x time per tile; a pair tile costs each SM the MMA
-    // time of a 128 x 256 tile but a third less shared-memory fill, measured as about 0.87 of its time on DiT shapes.
+    // time of a 128 x 256 tile but a third less shared-memory fill, measured as about 0.91 of its time on DiT shapes.
     const int n_tile = paired ? 128 : 256;
     const long long t2 = static_cast<long long>((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + n_tile - 1) / n_tile);
     const long long w2 = (t2 + sms / 2 - 1) / (sms / 2);
     const long long t1 = static_cast<long long>((a->M + BM - 1) / BM) * ((a->N + (paired ? 128 : bn) - 1) / (paired ? 128 : bn));
     const long long w1 = (t1 + sms - 1) / sms;
     const double cost1 = static_cast<double>(w1) * (bn == 256 ? 1.0 : bn == 128 ? 0.55 : 0.32);
-    const double cost2 = static_cast<double>(w2) * 0.87;
+    const double cost2 = static_cast<double>(w2) * 0.91;
     if (cost2 <= cost1) {
       use_pair = true;
       bn = 256;
@@ -1157,6 +1158,7 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
 
 #define MDB_LAUNCH(BN_, ST_, AMN_, BMN_, KIND_) return launch_variant<BN_, ST_, AMN_, BMN_, KIND_>(maps, p, sms, stream)
   if (use_pair) {
+    if (!a->a_mn && !a->b_mn && pair_deep) return launch_pair_variant<7, false, false>(maps, p, sms, stream);
     if (!a->a_mn && !a->b_mn) return launch_pair_variant<6, false, false>(maps, p, sms, stream);
     if (!a->a_mn && a->b_mn) return launch_pair_variant<6, false, true>(maps, p, sms, stream);
     if (a->a_mn && a->b_mn) return launch_pair_variant<6, true, true>(maps, p, sms, stream);

@@ -171,8 +171,8 @@ def attention(q, k, v, scale: Optional[float] = None, kv_len: Optional[torch.Ten
     scale = scale if scale is not None else 1.0 / math.sqrt(Dh)
     if q.is_cuda and kv_len is None and not return_lse:
         # library baseline on a GPU: the flash / cuDNN kernel torch selects, not an S x S fp32 score matrix
-        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                                             scale=scale)
+        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2).contiguous(), k.transpose(1, 2).contiguous(),
+                                                             v.transpose(1, 2).contiguous(), scale=scale)
         return o.transpose(1, 2).contiguous()
     s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
     if kv_len is not None:
