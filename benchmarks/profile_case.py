@@ -17,7 +17,7 @@ from mojodiffusion_b200.ops import native  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
     ap.add_argument("--shape", default="")
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
@@ -58,6 +58,30 @@ def main():
         torch.cuda.synchronize()
         native.check_status()
         print("MARK end", torch.ops.mdb200.launch_count())
+        print("ok")
+        return
+    if a.op == "gemm_prof":
+        # in-kernel cycle counters of both GEMM kernels (one CTA per 128 x 256 tile; CTA pair per 256 x 256 tile)
+        from mojodiffusion_b200.ops.functional import _gemm
+        M, N, K = dims or [4608, 3072, 3072]
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        names = ["mma_total", "producer_wait_empty", "mma_wait_full", "mma_wait_tmem_empty", "epi_wait_tmem_full", "epi_work", "tiles", "-"]
+        for bn in (256, 512, 513):
+            for _ in range(2):
+                _gemm([x], [w], bn=bn)
+            prof = torch.zeros(148, 8, dtype=torch.int64, device=dev)
+            flush.zero_()
+            _gemm([x], [w], bn=bn, prof=prof)
+            torch.cuda.synchronize()
+            pr = prof.cpu().double()
+            lead = pr[pr[:, 0] > 0]
+            print(f"bn={bn} shape={M}x{N}x{K} CTAs with an MMA role: {lead.shape[0]}")
+            for i, nm in enumerate(names[:7]):
+                col = pr[:, i][pr[:, i] > 0]
+                if col.numel():
+                    print(f"  {nm:24s} mean {col.mean():12.0f}  max {col.max():12.0f}  (n={col.numel()})")
+        native.check_status()
         print("ok")
         return
     if a.op in ("tp_fused_local", "ulysses_fused_local", "dp_fused_local"):

@@ -732,6 +732,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
       uint32_t phase = 0;
       int last_stage = -1;
       bool ok = true;
+      long long t_wait = 0;
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
         const int m0 = (tile % tiles_m) * (2 * BM) + static_cast<int>(rank) * BM;
         const int nblk = tile / tiles_m;
@@ -739,12 +740,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
         const int n0 = paired ? nblk * BNH + (leader ? 0 : p.pair_offset) : nblk * BN + static_cast<int>(rank) * BNH;
         for (int s = 0; ok && s < p.num_seg; ++s) {
           for (int kb = 0; kb < p.kblocks[s]; ++kb) {
+            const long long tw0 = p.prof ? clock64() : 0;
             if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s)) {
               report_status(p.status, STATUS_TIMEOUT, 21, stage);
               st_shared_cluster_u32(peer_abort, 1u);
               ok = false;
               break;
             }
+            if (p.prof) t_wait += clock64() - tw0;
             uint8_t* sa = smem + stage * STAGE_BYTES;
             uint8_t* sb = sa + A_BYTES;
             const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0u);
@@ -770,6 +773,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
           }
         }
       }
+      if (p.prof) p.prof[blockIdx.x * 8 + 1] = t_wait;
       if (!ok && last_stage >= 0) {
         // abandoned: give the copies already in flight time to land before the CTA goes away (bounded)
         const uint64_t t0 = globaltimer_ns();
@@ -786,23 +790,29 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      long long t_full = 0, t_tempty = 0;
+      const long long t_begin = p.prof ? clock64() : 0;
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        const long long te0 = p.prof ? clock64() : 0;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, &abort_s)) {
           report_status(p.status, STATUS_TIMEOUT, 22, acc);
           st_shared_cluster_u32(peer_abort, 1u);
           break;
         }
+        if (p.prof) t_tempty += clock64() - te0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < total_kb; ++kb) {
+          const long long tf0 = p.prof ? clock64() : 0;
           if (!mbar_wait(&full_bar[stage], phase, &abort_s)) {
             report_status(p.status, STATUS_TIMEOUT, 23, stage);
             st_shared_cluster_u32(peer_abort, 1u);
             ok = false;
             break;
           }
+          if (p.prof) t_full += clock64() - tf0;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -822,6 +832,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
         }
         if (ok) umma_commit_pair(&tfull_bar[acc], 3);
       }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = clock64() - t_begin;
+        p.prof[blockIdx.x * 8 + 2] = t_full;
+        p.prof[blockIdx.x * 8 + 3] = t_tempty;
+        p.prof[blockIdx.x * 8 + 6] = it;
+      }
     }
     __syncwarp();
   } else {
@@ -834,12 +850,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
     if (p.gate) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.gate) | static_cast<uintptr_t>(p.gate_stride * 2)) & 15) == 0;
     if (p.residual) aligned = aligned && ((reinterpret_cast<uintptr_t>(p.residual) | static_cast<uintptr_t>(static_cast<size_t>(p.ld_res) * 2)) & 15) == 0;
     int it = 0;
+    long long t_twait = 0, t_work = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int m0 = (tile % tiles_m) * (2 * BM) + static_cast<int>(rank) * BM;
       const int nblk = tile / tiles_m;
       const int n0 = paired ? nblk * BNH : nblk * BN;
+      const long long tq0 = p.prof ? clock64() : 0;
       const bool got = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, &abort_s));
       if (!got) {
         if (lane == 0) {
@@ -849,6 +867,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
         break;
       }
       tc_fence_after();
+      const long long tq1 = p.prof ? clock64() : 0;
+      t_twait += tq1 - tq0;
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const int out_cols = paired ? BNH : BN;
@@ -863,6 +883,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0u));
+      if (p.prof) t_work += clock64() - tq1;
+    }
+    if (p.prof && warp == 2 && lane == 0) {
+      p.prof[blockIdx.x * 8 + 4] = t_twait;
+      p.prof[blockIdx.x * 8 + 5] = t_work;
     }
   }
 

@@ -211,14 +211,14 @@ class ChromaDiT(nn.Module):
         for i, blk in enumerate(self.transformer_blocks):
             mi, mt = mod[:, i0 + 6 * i:i0 + 6 * i + 6], mod[:, t0 + 6 * i:t0 + 6 * i + 6]
             if ckpt:
-                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, mi, mt, cos, sin, use_reentrant=False)
+                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, mi, mt, cos, sin, use_reentrant=False, preserve_rng_state=False)
             else:
                 img, txt = blk(img, txt, mi, mt, cos, sin)
         x = torch.cat((txt, img), dim=1)
         for i, blk in enumerate(self.single_transformer_blocks):
             m = mod[:, 3 * i:3 * i + 3]
             if ckpt:
-                x = torch.utils.checkpoint.checkpoint(blk, x, m, cos, sin, use_reentrant=False)
+                x = torch.utils.checkpoint.checkpoint(blk, x, m, cos, sin, use_reentrant=False, preserve_rng_state=False)
             else:
                 x = blk(x, m, cos, sin)
         rows = cfg.mod_rows

@@ -218,13 +218,13 @@ class Flux2DiT(nn.Module):
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
         for blk in self.double_blocks:
             if ckpt:
-                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, mod_img, mod_txt, cos, sin, use_reentrant=False)
+                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, mod_img, mod_txt, cos, sin, use_reentrant=False, preserve_rng_state=False)
             else:
                 img, txt = blk(img, txt, mod_img, mod_txt, cos, sin)
         x = torch.cat((txt, img), dim=1)
         for blk in self.single_blocks:
             if ckpt:
-                x = torch.utils.checkpoint.checkpoint(blk, x, mod_single, cos, sin, use_reentrant=False)
+                x = torch.utils.checkpoint.checkpoint(blk, x, mod_single, cos, sin, use_reentrant=False, preserve_rng_state=False)
             else:
                 x = blk(x, mod_single, cos, sin)
         return self.final_layer(x[:, S_txt:], vec_silu)

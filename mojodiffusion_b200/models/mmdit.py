@@ -315,13 +315,13 @@ class MMDiT(nn.Module):
             return self.final_layer(x[:, S_txt:], vec_silu)
         for blk in self.double_blocks:
             if ckpt:
-                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, vec_silu, cos, sin, use_reentrant=False)
+                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, vec_silu, cos, sin, use_reentrant=False, preserve_rng_state=False)
             else:
                 img, txt = blk(img, txt, vec_silu, cos, sin, sp)
         x = torch.cat((txt, img), dim=1)
         for blk in self.single_blocks:
             if ckpt:
-                x = torch.utils.checkpoint.checkpoint(blk, x, vec_silu, cos, sin, use_reentrant=False)
+                x = torch.utils.checkpoint.checkpoint(blk, x, vec_silu, cos, sin, use_reentrant=False, preserve_rng_state=False)
             else:
                 x = blk(x, vec_silu, cos, sin, sp)
         x = x[:, S_txt:]

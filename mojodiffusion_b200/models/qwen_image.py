@@ -154,7 +154,7 @@ class QwenImageDiT(nn.Module):
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
         for blk in self.transformer_blocks:
             if ckpt:
-                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, temb_silu, cos, sin, kv_len, use_reentrant=False)
+                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, temb_silu, cos, sin, kv_len, use_reentrant=False, preserve_rng_state=False)
             else:
                 img, txt = blk(img, txt, temb_silu, cos, sin, kv_len)
         D = cfg.hidden

@@ -200,7 +200,7 @@ class SD3MMDiT(nn.Module):
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
         for blk in self.joint_blocks:
             if ckpt:
-                ctx, x = torch.utils.checkpoint.checkpoint(blk, ctx, x, c_silu, use_reentrant=False)
+                ctx, x = torch.utils.checkpoint.checkpoint(blk, ctx, x, c_silu, use_reentrant=False, preserve_rng_state=False)
             else:
                 ctx, x = blk(ctx, x, c_silu)
         D = cfg.hidden

@@ -183,7 +183,7 @@ class SingleStreamDiT(nn.Module):
 
         def run(blk, *a):
             if ckpt:
-                return torch.utils.checkpoint.checkpoint(blk, *a, use_reentrant=False)
+                return torch.utils.checkpoint.checkpoint(blk, *a, use_reentrant=False, preserve_rng_state=False)
             return blk(*a)
 
         for blk in self.context_refiner:

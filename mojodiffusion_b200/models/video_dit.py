@@ -197,7 +197,7 @@ class VideoDiT(nn.Module):
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
         for blk in self.transformer_blocks:
             if ckpt:
-                h = torch.utils.checkpoint.checkpoint(blk, h, ctx, temb6, cos, sin, ctx_len, use_reentrant=False)
+                h = torch.utils.checkpoint.checkpoint(blk, h, ctx, temb6, cos, sin, ctx_len, use_reentrant=False, preserve_rng_state=False)
             else:
                 h = blk(h, ctx, temb6, cos, sin, ctx_len)
         m = (self.scale_shift_table[None].float() + emb[:, None].float()).to(h.dtype)

@@ -30,7 +30,12 @@ class FlowMatchTrainer:
     """Drives ``model(img, txt, t, y, guidance)`` towards the rectified-flow velocity ``eps - x0``."""
 
     def __init__(self, model, params: Sequence[torch.nn.Parameter], optimizer: FusedAdamW,
-                 dp: Optional[DataParallelGrads] = None, cfg: Optional[StepConfig] = None):
+                 dp: Optional[DataParallelGrads] = None, cfg: Optional[StepConfig] = None, use_cuda_graph: bool = False):
+        """``use_cuda_graph``: forward + backward of the step are captured once (fixed shapes) and replayed; sigma and
+        noise are drawn outside the graph into its static inputs, the optimizer runs after the replay."""
+        self.use_cuda_graph = use_cuda_graph
+        self._graphed = None
+        self._graph_key = None
         self.model = model
         self.params = list(params)
         self.opt = optimizer
@@ -63,7 +68,34 @@ class FlowMatchTrainer:
         (loss * loss_scale).backward()
         return loss.detach()
 
+    def _graphed_loss_and_backward(self, x0, txt, y, sigma, noise, hw) -> torch.Tensor:
+        from ..utils.cuda_graph import GraphedTrainStep
+        B, dev = x0.shape[0], x0.device
+        if sigma is None:
+            sigma = sample_sigmas(B, self._gen, self.cfg.timestep_kind, self.cfg.timestep_shift).to(dev)
+        if noise is None:
+            noise = ops.randn(tuple(x0.shape), seed=self.cfg.seed * 7919 + self.step_index, device=dev)
+        inputs = [x0.float(), txt, y, sigma.float(), noise.float()]
+        key = (tuple(x0.shape), tuple(txt.shape), tuple(y.shape), hw)
+        if self._graphed is None or self._graph_key != key:
+            dt = next(self.model.parameters()).dtype
+            guidance = torch.full((B,), self.cfg.guidance, device=dev) if self.model.cfg.guidance_embed else None
+
+            def loss_fn(x0_, txt_, y_, sigma_, noise_):
+                xt, target = ops.flow_match(x0_, noise_, sigma_)
+                pred = self.model(xt.to(dt), txt_.to(dt), sigma_, y_.to(dt), guidance, hw=hw)
+                return ops.mse_loss(pred, target)
+
+            self._graphed = GraphedTrainStep(loss_fn, self.params, inputs).capture()
+            self._graph_key = key
+        return self._graphed(*inputs).detach()
+
     def step(self, x0, txt, y, sigma=None, noise=None, hw=None, lr: Optional[float] = None) -> torch.Tensor:
+        if self.use_cuda_graph and x0.is_cuda and self.dp is None and type(self.opt) is FusedAdamW:
+            loss = self._graphed_loss_and_backward(x0, txt, y, sigma, noise, hw)
+            self.opt.step(grad_scale=1.0, lr=lr)
+            self.step_index += 1
+            return loss
         self.zero_grad()
         loss = self.loss_and_backward(x0, txt, y, sigma, noise, hw)
         scale = self.dp.sync() if self.dp is not None else 1.0

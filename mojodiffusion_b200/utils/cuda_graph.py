@@ -58,3 +58,53 @@ def graphs_equal_eager(fn: Callable, inputs: Sequence[torch.Tensor]) -> Tuple[bo
     flat_o = out if isinstance(out, (tuple, list)) else [out]
     err = max(float((a.float() - b.float()).abs().max()) for a, b in zip(flat_e, flat_o))
     return all(torch.equal(a, b) for a, b in zip(flat_e, flat_o)), err
+
+
+class GraphedTrainStep:
+    """Forward + backward of a training step as one CUDA graph.
+
+    ``loss_fn(*inputs) -> scalar loss`` is warmed up eagerly, then captured together with ``loss.backward()`` while every
+    trainable parameter's ``.grad`` is None, so the gradient buffers are created inside the capture and stay at fixed
+    addresses: each replay overwrites them. The optimizer (and any gradient collective) runs after the replay on those
+    static gradients. Inputs are copied into the captured input tensors before a replay; everything ``loss_fn`` reads
+    besides its inputs and the parameters must itself be static. The capture covers the recompute of checkpointed blocks
+    (their forward runs again inside the captured backward), which is why the block checkpoints of this package do not
+    stash RNG state (serenitymojo/autograd_v2/capture.mojo:34-180: 5,774 forward + 21,036 backward graph nodes per step)."""
+
+    def __init__(self, loss_fn: Callable, params: Sequence[torch.nn.Parameter], example_inputs: Sequence[torch.Tensor],
+                 warmup: int = 3):
+        self.loss_fn = loss_fn
+        self.params = [p for p in params]
+        self.static_in = [t.clone() for t in example_inputs]
+        self.warmup = warmup
+        self.graph = None
+        self.static_loss = None
+
+    def _clear(self):
+        for p in self.params:
+            p.grad = None
+
+    def capture(self):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(self.warmup):
+                self._clear()
+                self.loss_fn(*self.static_in).backward()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self._clear()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.static_loss = self.loss_fn(*self.static_in)
+            self.static_loss.backward()
+        return self
+
+    def __call__(self, *inputs) -> torch.Tensor:
+        if self.graph is None:
+            self.capture()
+        for dst, src in zip(self.static_in, inputs):
+            if dst.data_ptr() != src.data_ptr():
+                dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        return self.static_loss
