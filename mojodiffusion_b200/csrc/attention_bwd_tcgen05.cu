@@ -321,7 +321,8 @@ attention_bwd_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
               dl = my_delta;
               valid = (i * CB + col) < kv_valid;
             }
-            float pe = exp2f(fmaf(__uint_as_float(xr[e + u]), p.scale_log2, -l2));
+            const float ex = fmaf(__uint_as_float(xr[e + u]), p.scale_log2, -l2);
+            float pe = u ? ex2_alt(ex) : exp2f(ex);     // every other exponential off the special-function unit
             if (!valid) pe = 0.f;
             pv[u] = pe;
             dv[u] = pe * (__uint_as_float(yr[e + u]) - dl);

@@ -296,7 +296,7 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float a = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -m_used));
-          const float b = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_used));
+          const float b = ex2_alt(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_used));   // every other one off the SFU
           rowsum += a + b;
           pk[i >> 1] = pack_bf16x2(a, b);
         }
