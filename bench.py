@@ -9,6 +9,11 @@ Timing: W untimed warm-up steps, then exactly K steps between CUDA events on the
 barrier + synchronize; the reported time is the max over ranks. Inputs are synthetic N(0,1) tensors of the named
 shapes and the weights are random-init from seed 0 (no datasets or checkpoints exist offline). Each step streams
 24 GB of weights, far more than the 126 MB L2, so no explicit L2 flush is needed between iterations.
+
+On N > 1 GPUs the headline value is throughput under weak scaling: every GPU denoises its own sample (global batch N),
+iterations per second summed over the GPUs. The same run also times ONE sample sharded over the N GPUs (Ulysses sequence
+parallel with the all-to-alls fused into the QKV GEMM and attention epilogues) and reports it as ``strong_scaling_sp``;
+LoRA training is data parallel with the gradient reduce-scatter, AdamW and parameter all-gather in one peer-memory pass.
 """
 from __future__ import annotations
 
@@ -137,45 +142,39 @@ def main():
     B = args.batch
     model = MMDiT(cfg, dtype=torch.bfloat16, device=dev).init_weights(0)
     model.eval()
-    sp = None
-    if world > 1 and not lib_baseline:
-        from mojodiffusion_b200.parallel.ulysses import UlyssesContext
-        sp = UlyssesContext(B, S_txt, S_img, cfg.heads, cfg.head_dim, mode=args.sp_mode, device=dev)
-    pipe = FluxPipeline(model, dev, sp=sp, use_cuda_graph=not args.no_graph)
-    g = torch.Generator().manual_seed(1234)          # same stream on every rank: shards of one global sample
-    x_full = torch.randn(B, S_img, cfg.in_channels, generator=g)
-    txt_full = torch.randn(B, S_txt, cfg.context_dim, generator=g).to(torch.bfloat16)
-    y_full = torch.randn(B, cfg.vec_dim, generator=g).to(torch.bfloat16)
-    Sl_img, Sl_txt = S_img // world, S_txt // world
-    x_host = x_full[:, rank * Sl_img:(rank + 1) * Sl_img].contiguous().pin_memory()
-    txt_host = txt_full[:, rank * Sl_txt:(rank + 1) * Sl_txt].contiguous().pin_memory()
-    y_host = y_full.pin_memory()
-    out_host = torch.empty_like(x_host).pin_memory()
     sigmas = fm.flux1_sigmas(28, S_img)
     K, W = args.steps, max(args.warmup, 0)
-
-    # ------------------------------------------------------------------ device-timed denoise loop
-    do_denoise = not (lib_baseline and world > 1)
-    ms = it_per_s = clocks = launches_per_step = None
-    n_launch = 0
-    x = x_host.to(dev)
-    txt = txt_host.to(dev)
-    y = y_host.to(dev)
-    xb = x.to(torch.bfloat16)
-    ids = MMDiT.make_ids(hw[0], hw[1], S_txt, dev)
-    gvec = torch.full((B,), 3.5, device=dev)
-    tvec = torch.empty((B,), device=dev)
     from mojodiffusion_b200 import ops
-
-    def denoise_step(i):
-        s, s_next = sigmas[i % 28], sigmas[i % 28 + 1]
-        tvec.fill_(float(s))
-        with torch.no_grad():
-            v = pipe._forward(xb, txt, tvec, y, gvec, ids)
-            ops.cfg_euler(x, v, None, dt=float(s_next - s), mode=0, x_bf16=xb)
-
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if do_denoise:
+    ids = MMDiT.make_ids(hw[0], hw[1], S_txt, dev)
+
+    def measure(sp, seed, shard, with_e2e):
+        """Times K denoise steps (device events, max over ranks) and, optionally, K steps through the public API with the
+        step's inputs coming from pinned host memory and its result read back. ``shard``: this rank holds 1/world of the
+        tokens of ONE shared sample (sequence parallel); otherwise every rank denoises its own sample."""
+        pipe = FluxPipeline(model, dev, sp=sp, use_cuda_graph=not args.no_graph)
+        g = torch.Generator().manual_seed(seed)
+        x_full = torch.randn(B, S_img, cfg.in_channels, generator=g)
+        txt_full = torch.randn(B, S_txt, cfg.context_dim, generator=g).to(torch.bfloat16)
+        y_full = torch.randn(B, cfg.vec_dim, generator=g).to(torch.bfloat16)
+        if shard:
+            Sl_img, Sl_txt = S_img // world, S_txt // world
+            x_full = x_full[:, rank * Sl_img:(rank + 1) * Sl_img]
+            txt_full = txt_full[:, rank * Sl_txt:(rank + 1) * Sl_txt]
+        x_host, txt_host, y_host = x_full.contiguous().pin_memory(), txt_full.contiguous().pin_memory(), y_full.pin_memory()
+        out_host = torch.empty_like(x_host).pin_memory()
+        x, txt, y = x_host.to(dev), txt_host.to(dev), y_host.to(dev)
+        xb = x.to(torch.bfloat16)
+        gvec = torch.full((B,), 3.5, device=dev)
+        tvec = torch.empty((B,), device=dev)
+
+        def denoise_step(i):
+            s_, s_next = sigmas[i % 28], sigmas[i % 28 + 1]
+            tvec.fill_(float(s_))
+            with torch.no_grad():
+                v = pipe._forward(xb, txt, tvec, y, gvec, ids)
+                ops.cfg_euler(x, v, None, dt=float(s_next - s_), mode=0, x_bf16=xb)
+
         for i in range(max(W, 1)):
             denoise_step(i)
         torch.cuda.synchronize()
@@ -191,12 +190,11 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         pdist.barrier()
-        n_launch = launches() - n0
-        clocks = sampler.stop() if rank == 0 else None
-        ms = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
+        res = {"n_launch": launches() - n0, "launches_per_step": None}
+        res["clocks"] = sampler.stop() if rank == 0 else None
+        res["ms"] = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
         native.check_status()
         assert torch.isfinite(x).all(), "latents diverged"
-        it_per_s = B * 1000.0 / ms  # N > 1: the ranks share ONE batch (Ulysses sequence parallel, strong scaling)
         if not args.no_graph and not lib_baseline:
             # kernels inside the replayed graph are not re-counted by the host-side counter: count one eager step
             pipe_eager = FluxPipeline(model, dev, sp=sp, use_cuda_graph=False)
@@ -205,28 +203,49 @@ def main():
                 pipe_eager._forward(xb, txt, tvec, y, gvec, ids)
             torch.cuda.synchronize()
             pdist.barrier()
-            launches_per_step = launches() - nb + 1
-            n_launch = launches_per_step * K
+            res["launches_per_step"] = launches() - nb + 1
+            res["n_launch"] = res["launches_per_step"] * K
+        res["e2e"] = None
+        if with_e2e:
+            for i in range(min(max(W, 1), 2)):
+                pipe.step_from_host(x_host, txt_host, y_host, sigmas[i], sigmas[i + 1], 3.5, out_host, hw)
+            torch.cuda.synchronize()
+            pdist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            bi = bo = 0
+            for i in range(K):
+                bi, bo = pipe.step_from_host(x_host, txt_host, y_host, sigmas[i % 28], sigmas[i % 28 + 1], 3.5, out_host, hw)
+                torch.cuda.current_stream().synchronize()   # the caller reads the step's result on the host
+                x_host.copy_(out_host)
+            e1.record()
+            torch.cuda.synchronize()
+            ms_e2e = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
+            images = B if shard else B * world
+            res["e2e"] = {"value": images * 1000.0 / ms_e2e, "unit": "it/s", "ms_per_step": ms_e2e,
+                          "h2d_bytes_per_step": bi * world, "d2h_bytes_per_step": bo * world}
+        del pipe
+        return res
 
-    # ------------------------------------------------------------------ end-to-end through the public API
-    e2e = None
-    if not args.no_e2e and do_denoise:
-        for i in range(min(max(W, 1), 2)):
-            pipe.step_from_host(x_host, txt_host, y_host, sigmas[i], sigmas[i + 1], 3.5, out_host, hw)
-        torch.cuda.synchronize()
-        pdist.barrier()
-        torch.cuda.synchronize()
-        e0.record()
-        bi = bo = 0
-        for i in range(K):
-            bi, bo = pipe.step_from_host(x_host, txt_host, y_host, sigmas[i % 28], sigmas[i % 28 + 1], 3.5, out_host, hw)
-            torch.cuda.current_stream().synchronize()   # the caller reads the step's result on the host
-            x_host.copy_(out_host)
-        e1.record()
-        torch.cuda.synchronize()
-        ms_e2e = pdist.max_over_ranks(e0.elapsed_time(e1) / K)
-        e2e = {"value": B * 1000.0 / ms_e2e, "unit": "it/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": bi * world, "d2h_bytes_per_step": bo * world}
+    # ------------------------------------------------------------------ denoise loop
+    # N = 1: one sample on one GPU. N > 1, headline (weak scaling): every GPU denoises its own sample, global batch = N x B.
+    # N > 1, also reported (strong scaling): ONE sample, its tokens sharded over the ranks (Ulysses sequence parallel,
+    # all-to-alls fused into the QKV GEMM and attention epilogues).
+    do_denoise = not (lib_baseline and world > 1)
+    ms = it_per_s = clocks = launches_per_step = e2e = strong = None
+    n_launch = 0
+    if do_denoise:
+        head = measure(None, 1234 + rank, False, not args.no_e2e)
+        ms, clocks, launches_per_step, n_launch, e2e = head["ms"], head["clocks"], head["launches_per_step"], head["n_launch"], head["e2e"]
+        it_per_s = world * B * 1000.0 / ms
+        if world > 1 and not lib_baseline:
+            from mojodiffusion_b200.parallel.ulysses import UlyssesContext
+            sp = UlyssesContext(B, S_txt, S_img, cfg.heads, cfg.head_dim, mode=args.sp_mode, device=dev)
+            st = measure(sp, 1234, True, not args.no_e2e)
+            strong = {"what": "one sample sharded over the ranks (Ulysses sequence parallel, all-to-all " + args.sp_mode + ")",
+                      "value": B * 1000.0 / st["ms"], "unit": "it/s", "ms_per_step": st["ms"], "scaling": "strong",
+                      "launches_per_step": st["launches_per_step"], "e2e": st["e2e"]}
+            del sp
 
     # ------------------------------------------------------------------ LoRA training samples/s
     train = None
@@ -236,7 +255,6 @@ def main():
         from mojodiffusion_b200.training import lora as L
         from mojodiffusion_b200.training.optim import FusedAdamW
         from mojodiffusion_b200.training.trainer import FlowMatchTrainer
-        del pipe
         torch.cuda.empty_cache()
         slots = L.inject_flux_lora(model, rank=16, alpha=16.0)
         params = L.lora_parameters(slots)
@@ -296,16 +314,17 @@ def main():
         line = {
             "metric": "flux1-dev-shape 1024^2 denoise it/s (+ LoRA r16 train samples/s in 'lora_train')",
             "value": it_per_s, "unit": "it/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "torch library kernels (cuBLAS, SDPA, NCCL), eager" if lib_baseline else "ours",
             "config": {"model": f"{cfg.name} 12B MMDiT (19 double + 38 single, D=3072, 24x128)" if args.model == "flux1-dev" else cfg.name,
-                       "global_batch": B, "seq_len": S_img + S_txt, "image_tokens": S_img, "text_tokens": S_txt,
+                       "global_batch": B * world, "seq_len": S_img + S_txt, "image_tokens": S_img, "text_tokens": S_txt,
                        "sampler": "euler flow-match, 28-step BFL-shifted schedule, guidance 3.5 (distilled)",
-                       "parallelism": (f"sp{world} (Ulysses; all-to-all {args.sp_mode})" if world > 1 else "single"),
+                       "parallelism": (f"dp{world} (one sample per GPU); single-sample latency with sp{world} in 'strong_scaling_sp'"
+                                       if world > 1 else "single"),
                        "cuda_graph": not args.no_graph, "launches_per_step": launches_per_step,
                        "weights": "random-init seed 0",
                        "l2": "inputs larger than L2: 24 GB of weights stream every step"},
-            "clocks": clocks, "gpu_launches": n_launch, "e2e": e2e, "lora_train": train,
+            "clocks": clocks, "gpu_launches": n_launch, "e2e": e2e, "strong_scaling_sp": strong, "lora_train": train,
             "published_nearest": PUBLISHED_NEAREST,
             "vs_published_nearest": it_per_s / PUBLISHED_NEAREST["it_per_s"] if it_per_s else None,
         }
