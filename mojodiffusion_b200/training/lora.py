@@ -83,6 +83,108 @@ def inject_flux_lora(model, rank: int = 16, alpha: float = 16.0, targets: Option
     return slots
 
 
+KLEIN_DOUBLE = ("attn.to_q", "attn.to_k", "attn.to_v", "attn.to_out.0", "ff.linear_in", "ff.linear_out", "attn.add_q_proj",
+                "attn.add_k_proj", "attn.add_v_proj", "attn.to_add_out", "ff_context.linear_in", "ff_context.linear_out")
+KLEIN_SINGLE = ("attn.to_qkv_mlp_proj", "attn.to_out")
+QWEN_BLOCK = ("attn.to_q", "attn.to_k", "attn.to_v", "attn.to_out.0", "img_mlp.net.0.proj", "img_mlp.net.2", "attn.add_q_proj",
+              "attn.add_k_proj", "attn.add_v_proj", "attn.to_add_out", "txt_mlp.net.0.proj", "txt_mlp.net.2")
+ZIMAGE_BLOCK = ("attention.to_q", "attention.to_k", "attention.to_v", "attention.to_out.0", "feed_forward.w1",
+                "feed_forward.w3", "feed_forward.w2")
+LTX2_ATTN = ("to_q", "to_k", "to_v", "to_out.0")
+
+
+def _finish(model: nn.Module, slots: List[LoRASlot]) -> List[LoRASlot]:
+    for s in slots:
+        s.down.requires_grad_(True)
+        s.up.requires_grad_(True)
+    return slots
+
+
+def _freeze(model: nn.Module) -> None:
+    for p in model.parameters():
+        p.requires_grad_(False)
+
+
+def inject_klein_lora(model, rank: int = 16, alpha: float = 16.0, seed: int = 0) -> List[LoRASlot]:
+    """FLUX.2 Klein adapters under the diffusers-style names the reference saves
+    (``transformer.transformer_blocks.{i}.attn.to_q`` ... ``transformer.single_transformer_blocks.{i}.attn.to_qkv_mlp_proj``);
+    to_q / to_k / to_v are row ranges of the fused ``qkv`` weight, the single block's whole ``linear1`` is one adapter."""
+    D = model.cfg.hidden
+    _freeze(model)
+    slots: List[LoRASlot] = []
+    for i, b in enumerate(model.double_blocks):
+        pre = f"transformer.transformer_blocks.{i}."
+        table = {"attn.to_q": (b.img_attn.qkv, (0, D)), "attn.to_k": (b.img_attn.qkv, (D, 2 * D)), "attn.to_v": (b.img_attn.qkv, (2 * D, 3 * D)),
+                 "attn.to_out.0": (b.img_attn.proj, None), "ff.linear_in": (b.img_mlp["0"], None), "ff.linear_out": (b.img_mlp["2"], None),
+                 "attn.add_q_proj": (b.txt_attn.qkv, (0, D)), "attn.add_k_proj": (b.txt_attn.qkv, (D, 2 * D)),
+                 "attn.add_v_proj": (b.txt_attn.qkv, (2 * D, 3 * D)), "attn.to_add_out": (b.txt_attn.proj, None),
+                 "ff_context.linear_in": (b.txt_mlp["0"], None), "ff_context.linear_out": (b.txt_mlp["2"], None)}
+        for n in KLEIN_DOUBLE:
+            lin, rows = table[n]
+            slots.append(lin.add_lora(pre + n, rank, alpha, rows, seed))
+    for i, b in enumerate(model.single_blocks):
+        pre = f"transformer.single_transformer_blocks.{i}."
+        slots.append(b.linear1.add_lora(pre + "attn.to_qkv_mlp_proj", rank, alpha, None, seed))
+        slots.append(b.linear2.add_lora(pre + "attn.to_out", rank, alpha, None, seed))
+    return _finish(model, slots)
+
+
+def klein_lora_prefixes(depth_double: int, depth_single: int) -> List[str]:
+    out = []
+    for i in range(depth_double):
+        out += [f"transformer.transformer_blocks.{i}.{n}" for n in KLEIN_DOUBLE]
+    for i in range(depth_single):
+        out += [f"transformer.single_transformer_blocks.{i}.{n}" for n in KLEIN_SINGLE]
+    return out
+
+
+def inject_qwen_lora(model, rank: int = 16, alpha: float = 16.0, seed: int = 0) -> List[LoRASlot]:
+    """Qwen-Image adapters: twelve per block under ``transformer.transformer_blocks.{i}.<module path>``."""
+    _freeze(model)
+    mods = dict(model.named_modules())
+    slots = []
+    for i in range(len(model.transformer_blocks)):
+        for n in QWEN_BLOCK:
+            slots.append(mods[f"transformer_blocks.{i}.{n}"].add_lora(f"transformer.transformer_blocks.{i}.{n}", rank, alpha, None, seed))
+    return _finish(model, slots)
+
+
+def inject_zimage_lora(model, rank: int = 16, alpha: float = 16.0, refiners: bool = False, seed: int = 0) -> List[LoRASlot]:
+    """Z-Image adapters on the attention and feed-forward projections of the main ``layers`` (210 for 30 layers); the
+    noise / context refiners only when asked for (the reference's production surface leaves them out)."""
+    _freeze(model)
+    mods = dict(model.named_modules())
+    groups = [("layers", len(model.layers))]
+    if refiners:
+        groups = [("noise_refiner", len(model.noise_refiner)), ("context_refiner", len(model.context_refiner))] + groups
+    slots = []
+    for g, n_ in groups:
+        for i in range(n_):
+            for n in ZIMAGE_BLOCK:
+                slots.append(mods[f"{g}.{i}.{n}"].add_lora(f"{g}.{i}.{n}", rank, alpha, None, seed))
+    return _finish(model, slots)
+
+
+def zimage_kohya_name(prefix: str) -> str:
+    """``layers.3.attention.to_q`` -> ``lora_unet_layers_3_attention_to_q`` (the Kohya export spelling)."""
+    return "lora_unet_" + prefix.replace(".", "_")
+
+
+def inject_ltx2_lora(model, rank: int = 16, alpha: float = 16.0, cross_attention: bool = True, seed: int = 0) -> List[LoRASlot]:
+    """LTX-2 video adapters: ``diffusion_model.transformer_blocks.{i}.{attn1,attn2}.{to_q,to_k,to_v,to_out.0}`` and
+    ``ff.net.{0.proj,2}``; saved in the PEFT layout where the scale is the load-time strength (alpha = rank)."""
+    _freeze(model)
+    mods = dict(model.named_modules())
+    slots = []
+    for i in range(len(model.transformer_blocks)):
+        pre = f"transformer_blocks.{i}."
+        names = [f"attn1.{n}" for n in LTX2_ATTN] + ([f"attn2.{n}" for n in LTX2_ATTN] if cross_attention else [])
+        names += ["ff.net.0.proj", "ff.net.2"]
+        for n in names:
+            slots.append(mods[pre + n].add_lora("diffusion_model." + pre + n, rank, alpha, None, seed))
+    return _finish(model, slots)
+
+
 def inject_lora_by_name(model: nn.Module, name_to_key: Dict[str, str], rank: int, alpha: float) -> List[LoRASlot]:
     """Generic injection: ``name_to_key`` maps a module path of a :class:`Linear` to its checkpoint prefix."""
     for p in model.parameters():

@@ -363,3 +363,55 @@ def test_cadence_names_and_resume(tmp_path):
     shutil.rmtree(os.path.join(ws, "backup", "T-backup-6-2-0"))
     with pytest.raises(FileNotFoundError):
         loop.read_backup(os.path.join(ws, "backup", "T-backup-4-1-1"))
+
+
+def test_lora_key_schemes_of_the_other_families(tmp_path):
+    """Klein (diffusers-style names over fused BFL weights), Qwen-Image, Z-Image and LTX-2 adapter inventories; the PEFT
+    file of each has exactly <prefix>.lora_A.weight / .lora_B.weight per adapter, and a zero-initialised up matrix leaves
+    the model output unchanged."""
+    import torch
+    from mojodiffusion_b200.io.safetensors_io import SafeTensors
+    from mojodiffusion_b200.models.flux2 import Flux2DiT, tiny_flux2_config
+    from mojodiffusion_b200.models.qwen_image import QwenImageDiT, tiny_qwen_image_config
+    from mojodiffusion_b200.models.single_dit import SingleStreamDiT, tiny_single_dit_config
+    from mojodiffusion_b200.models.video_dit import VideoDiT, tiny_video_dit_config
+    from mojodiffusion_b200.training import lora as L
+
+    g = torch.Generator().manual_seed(0)
+    cfg = tiny_flux2_config()
+    m = Flux2DiT(cfg, torch.float32, "cpu").init_weights(0)
+    img, txt, t = torch.randn(1, 16, cfg.in_channels, generator=g), torch.randn(1, 4, cfg.context_dim, generator=g), torch.tensor([0.5])
+    with torch.no_grad():
+        base = m(img, txt, t, (4, 4))
+    slots = L.inject_klein_lora(m, rank=4, alpha=4.0)
+    assert [s.key for s in slots] == L.klein_lora_prefixes(cfg.depth_double, cfg.depth_single)
+    assert len(slots) == 12 * cfg.depth_double + 2 * cfg.depth_single
+    q = next(s for s in slots if s.key.endswith("transformer_blocks.0.attn.to_k"))
+    assert (q.row0, q.row1) == (cfg.hidden, 2 * cfg.hidden) and tuple(q.up.shape) == (cfg.hidden, 4)
+    with torch.no_grad():
+        assert torch.allclose(m(img, txt, t, (4, 4)), base, atol=1e-6)
+    path = tmp_path / "klein.safetensors"
+    L.save_lora(str(path), slots, layout="peft")
+    keys = set(SafeTensors(str(path)).keys())
+    assert keys == {f"{p}.lora_{ab}.weight" for p in L.klein_lora_prefixes(cfg.depth_double, cfg.depth_single) for ab in "AB"}
+
+    qm = QwenImageDiT(tiny_qwen_image_config(), torch.float32, "cpu").init_weights(0)
+    qs = L.inject_qwen_lora(qm, rank=4)
+    assert len(qs) == 12 * len(qm.transformer_blocks)
+    assert qs[4].key == "transformer.transformer_blocks.0.img_mlp.net.0.proj" and qs[-1].key.endswith("txt_mlp.net.2")
+
+    zm = SingleStreamDiT(tiny_single_dit_config(), torch.float32, "cpu").init_weights(0)
+    zs = L.inject_zimage_lora(zm, rank=4)
+    assert len(zs) == 7 * len(zm.layers) and all(s.key.startswith("layers.") for s in zs)
+    zr = L.inject_zimage_lora(SingleStreamDiT(tiny_single_dit_config(), torch.float32, "cpu"), rank=4, refiners=True)
+    assert len(zr) == 7 * (len(zm.layers) + len(zm.noise_refiner) + len(zm.context_refiner))
+    assert L.zimage_kohya_name("layers.3.attention.to_out.0") == "lora_unet_layers_3_attention_to_out_0"
+    from mojodiffusion_b200.models.single_dit import zimage_config
+    with torch.device("meta"):
+        full = SingleStreamDiT(zimage_config(), torch.float32, "meta")
+        assert len(L.inject_zimage_lora(full, rank=16)) == 210
+
+    vm = VideoDiT(tiny_video_dit_config(), torch.float32, "cpu").init_weights(0)
+    vs = L.inject_ltx2_lora(vm, rank=4)
+    assert len(vs) == 10 * len(vm.transformer_blocks)
+    assert vs[0].key == "diffusion_model.transformer_blocks.0.attn1.to_q" and vs[9].key == "diffusion_model.transformer_blocks.0.ff.net.2"
