@@ -51,6 +51,7 @@ def main():
     peak_tf = peaks.get("bf16_tflops", 1590.0)
     peak_bw = peaks.get("hbm_gbs", 6650.0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    print("CTA pairs the device holds at once:", torch.ops.mdb200.gemm_pair_capacity(), flush=True)
     rows = []
     shapes = [(4608, 3072, 3072), (4608, 9216, 3072), (4608, 12288, 3072), (4608, 3072, 12288), (4608, 21504, 3072),
               (4608, 3072, 15360), (4096, 16384, 4096), (8192, 8192, 8192)]

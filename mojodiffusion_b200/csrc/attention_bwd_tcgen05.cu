@@ -16,6 +16,7 @@
 // Math matched: serenitymojo/ops/attention_backward.mojo:249-349 (7-step decomposed backward) and the cuDNN
 // flash backward the reference binds (serenitymojo/ops/cshim/cudnn_sdpa_bwd.cpp:325).
 #include "common.cuh"
+#include <stdlib.h>
 #include "gemm_api.h"
 #include "kernels_api.h"
 
@@ -41,6 +42,7 @@ struct BwdParams {
   const int* kv_len;
   int B, H, Sq, Skv;
   float scale, scale_log2;
+  int exp_poly;
   int* status;
 };
 
@@ -322,7 +324,7 @@ attention_bwd_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
               valid = (i * CB + col) < kv_valid;
             }
             const float ex = fmaf(__uint_as_float(xr[e + u]), p.scale_log2, -l2);
-            float pe = u ? ex2_alt(ex) : exp2f(ex);     // every other exponential off the special-function unit
+            float pe = (u && p.exp_poly) ? ex2_poly(ex) : exp2f(ex);   // every other exponential off the special-function unit
             if (!valid) pe = 0.f;
             pv[u] = pe;
             dv[u] = pe * (__uint_as_float(yr[e + u]) - dl);
@@ -444,6 +446,14 @@ extern "C" int mdb_attention_bwd(const MdbAttnBwdArgs* a, cudaStream_t st) {
   p.B = a->B; p.H = a->H; p.Sq = a->Sq; p.Skv = a->Skv;
   p.scale = a->scale;
   p.scale_log2 = a->scale * 1.4426950408889634f;
+  {
+    static int mode = -1;
+    if (mode < 0) {
+      const char* e = getenv("MDB200_ATTN_EXP_POLY");
+      mode = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    p.exp_poly = mode;
+  }
   p.status = a->status;
   int r;
   // ---- dQ: resident Q, dO ; streamed K, V

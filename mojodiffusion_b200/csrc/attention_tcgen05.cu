@@ -18,6 +18,7 @@
 // online-softmax kernels (:734-873,1109-1167) and its cuDNN flash shim (serenitymojo/ops/cshim/cudnn_sdpa.cpp:375,470;
 // Stats/LSE output as in the training forward there).
 #include "common.cuh"
+#include <stdlib.h>
 #include "gemm_api.h"
 #include "kernels_api.h"
 
@@ -45,6 +46,7 @@ struct AttnParams {
   int B, H, Sq, Skv;
   long long o_strides[3];
   float scale_log2;
+  int exp_poly;   // every other exponential through the polynomial on the FMA pipe (MDB200_ATTN_EXP_POLY=0 turns it off)
   int* status;
   void* o_route_a[8];
   void* o_route_b[8];
@@ -291,14 +293,25 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
         }
       }
       float rowsum = 0.f;
+      const bool poly = p.exp_poly != 0;
       auto emit = [&](const uint32_t (&sv)[32], int c) {
         uint32_t pk[16];
+        if (poly) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float a = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -m_used));
-          const float b = ex2_alt(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_used));   // every other one off the SFU
-          rowsum += a + b;
-          pk[i >> 1] = pack_bf16x2(a, b);
+          for (int i = 0; i < 32; i += 2) {
+            const float a = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -m_used));
+            const float b = ex2_poly(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_used));   // every other one off the SFU
+            rowsum += a + b;
+            pk[i >> 1] = pack_bf16x2(a, b);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float a = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -m_used));
+            const float b = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_used));
+            rowsum += a + b;
+            pk[i >> 1] = pack_bf16x2(a, b);
+          }
         }
         tmem_st_32x32b_x16(s_addr + c * 16, pk);
       };
@@ -415,6 +428,14 @@ extern "C" int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st) {
   p.B = a->B; p.H = a->H; p.Sq = a->Sq; p.Skv = a->Skv;
   for (int i = 0; i < 3; ++i) p.o_strides[i] = a->o_strides[i];
   p.scale_log2 = a->scale * 1.4426950408889634f;
+  {
+    static int mode = -1;
+    if (mode < 0) {
+      const char* e = getenv("MDB200_ATTN_EXP_POLY");
+      mode = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    p.exp_poly = mode;
+  }
   p.status = a->status;
   for (int i = 0; i < 8; ++i) {
     p.o_route_a[i] = a->o_route_a[i];

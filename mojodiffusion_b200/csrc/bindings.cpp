@@ -752,11 +752,13 @@ std::vector<int64_t> read_status(const Tensor& like, bool reset) {
 
 // number of kernel launches issued through this library since load
 int64_t launch_count() { return g_launches.load(); }
+int64_t gemm_pair_capacity() { return mdb_gemm_pair_capacity(148); }
 
 }  // namespace
 
 TORCH_LIBRARY(mdb200, m) {
   m.def("launch_count", &launch_count);
+  m.def("gemm_pair_capacity", &gemm_pair_capacity);
   m.def("gemm", &gemm);
   m.def("conv2d_nhwc", &conv2d_nhwc);
   m.def("group_norm_nhwc", &group_norm_nhwc);

@@ -430,9 +430,6 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf
 // 1.5 * 2^23 rounded toward minus infinity (the integer lands in the low mantissa bits), 2^frac from a degree-3
 // polynomial (maximum relative error 8.6e-5, far below the bf16 rounding of the probabilities), the integer part is
 // added to the exponent field. Valid for -125 <= x <= 100; smaller inputs (masked scores) return about 2^-125.
-#ifndef MDB_EXP2_POLY
-#define MDB_EXP2_POLY 1
-#endif
 __device__ __forceinline__ float ex2_poly(float x) {
   x = fmaxf(x, -125.f);
   const float y = __fadd_rd(x, 12582912.f);
@@ -442,14 +439,6 @@ __device__ __forceinline__ float ex2_poly(float x) {
   pz = fmaf(pz, f, 1.0f);
   return __int_as_float(__float_as_int(pz) + (__float_as_int(y) << 23));
 }
-__device__ __forceinline__ float ex2_alt(float x) {
-#if MDB_EXP2_POLY
-  return ex2_poly(x);
-#else
-  return exp2f(x);
-#endif
-}
-
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -78,6 +78,10 @@ typedef struct MdbGemmArgs {
 
 int mdb_gemm_launch(const MdbGemmArgs* args, cudaStream_t stream);
 
+// number of two-CTA clusters of the 256 x 256 GEMM kernel the current device can hold at once (74 on a B200 whose 148 SMs
+// all have their TPC partner, fewer otherwise)
+int mdb_gemm_pair_capacity(int num_sms);
+
 // rank-N tiled tensor map (extents/strides innermost first; strides_bytes[0] ignored)
 int mdb_make_tmap(void* out_map, const void* ptr, int elem_bytes, int rank, const int64_t* extents,
                   const int64_t* strides_bytes, const int* box, int swizzle128);

@@ -976,6 +976,39 @@ static int launch_variant(const GemmMaps& maps, const GemmParams& p, int num_sms
   return static_cast<int>(cudaGetLastError());
 }
 
+// How many CTA pairs the device can hold at once: an SM whose partner in the same TPC is not available cannot host half
+// a pair, so the number differs from chip to chip. A persistent grid must not exceed it (surplus pairs would run their
+// whole tile list after the others finish) and the tile-shape choice uses it as the pair kernel's width.
+template <int STAGES, bool A_MN, bool B_MN>
+__global__ void gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p);
+
+static int pair_capacity(int num_sms) {
+  static int cached = 0;
+  if (cached > 0) return cached;
+  constexpr int SMEM = 6 * (BM * BK_BYTES + 128 * BK_BYTES) + 1024;
+  auto kern = gemm_tcgen05_pair_kernel<6, false, false>;
+  int n = 0;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) == cudaSuccess) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(num_sms & ~1), 1, 1);
+    cfg.blockDim = dim3(PAIR_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) n = 0;
+  }
+  cudaGetLastError();
+  if (n < 1 || n > num_sms / 2) n = num_sms / 2;
+  cached = n;
+  return cached;
+}
+
 template <int STAGES, bool A_MN, bool B_MN>
 static int launch_pair_variant(const GemmMaps& maps, const GemmParams& p, int num_sms, cudaStream_t stream) {
   constexpr int SMEM = STAGES * (BM * BK_BYTES + 128 * BK_BYTES) + 1024;
@@ -989,29 +1022,7 @@ static int launch_pair_variant(const GemmMaps& maps, const GemmParams& p, int nu
   }
   const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
   const int tiles_n = (p.N + (p.pair_offset > 0 ? 128 : 256) - 1) / (p.pair_offset > 0 ? 128 : 256);
-  // how many CTA pairs the device can hold at once (an SM whose partner is unavailable cannot host half a pair): a
-  // persistent grid must not exceed it, or the surplus pairs would run their whole tile list after the others finish
-  static int max_pairs = 0;
-  if (max_pairs == 0) {
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(static_cast<unsigned>(num_sms & ~1), 1, 1);
-    cfg.blockDim = dim3(PAIR_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = SMEM;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
-      cudaGetLastError();
-      n = num_sms / 2;
-    }
-    max_pairs = n < num_sms / 2 ? n : num_sms / 2;
-  }
+  const int max_pairs = pair_capacity(num_sms);
   int clusters = tiles_m * tiles_n;
   if (clusters > max_pairs) clusters = max_pairs;
   if (clusters < 1) return 0;
@@ -1020,6 +1031,8 @@ static int launch_pair_variant(const GemmMaps& maps, const GemmParams& p, int nu
 }
 
 }  // namespace mdb
+
+extern "C" int mdb_gemm_pair_capacity(int num_sms) { return mdb::pair_capacity(num_sms > 0 ? num_sms : 148); }
 
 // MDB200_GEMM_PAIR=0 keeps every automatically tiled GEMM on the one-CTA kernel (A/B measurements); default: choose.
 static int pair_mode() {
@@ -1064,7 +1077,8 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
     // time of a 128 x 256 tile but a third less shared-memory fill, measured as about 0.91 of its time on DiT shapes.
     const int n_tile = paired ? 128 : 256;
     const long long t2 = static_cast<long long>((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + n_tile - 1) / n_tile);
-    const long long w2 = (t2 + sms / 2 - 1) / (sms / 2);
+    const int pairs = pair_capacity(sms);
+    const long long w2 = (t2 + pairs - 1) / pairs;
     const long long t1 = static_cast<long long>((a->M + BM - 1) / BM) * ((a->N + (paired ? 128 : bn) - 1) / (paired ? 128 : bn));
     const long long w1 = (t1 + sms - 1) / sms;
     const double cost1 = static_cast<double>(w1) * (bn == 256 ? 1.0 : bn == 128 ? 0.55 : 0.32);

@@ -6,6 +6,7 @@ tests run a kernel and compare against the function of the same name here evalua
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -45,6 +46,18 @@ def activation(x: torch.Tensor, act) -> torch.Tensor:
     raise ValueError(a)
 
 
+def _library_mode(x: torch.Tensor, out_dtype=None) -> bool:
+    """bf16 tensors on a GPU while the package is forced off its own kernels (``MDB200_FORCE_REFERENCE=1``): the hot
+    ops then run as an ordinary PyTorch bf16 program (cuBLAS ``F.linear``, fused SDPA, ``F.layer_norm``, element-wise
+    ops in bf16) instead of the fp32 oracle arithmetic below. That is the same-box library baseline of ``bench.py``."""
+    return x.is_cuda and x.dtype == torch.bfloat16 and out_dtype is None and os.environ.get("MDB200_FORCE_REFERENCE") == "1"
+
+
+def _grouped(v: torch.Tensor, y: torch.Tensor, rows_per_group: int) -> torch.Tensor:
+    """View of y [rows, D] as [groups, rows_per_group, D] beside v [groups, 1, D] (no gather)."""
+    return y.view(v.shape[0], -1, y.shape[-1]) if v.shape[0] > 1 else y.view(1, -1, y.shape[-1])
+
+
 def _group_expand(v: torch.Tensor, rows: int, rows_per_group: int) -> torch.Tensor:
     """[groups, D] -> [rows, D] where row r uses group r // rows_per_group."""
     if v.shape[0] == 1:
@@ -57,6 +70,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
            residual: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, rows_per_group: int = 1,
            extra: Sequence[tuple] = (), out_dtype=None) -> torch.Tensor:
     """``act(x @ w.T + sum_i a_i @ b_i.T + bias)``, then ``residual + gate[group] * value``. 2-D operands."""
+    if _library_mode(x, out_dtype):
+        y = F.linear(x, w, bias)
+        for a2, b2 in extra:
+            y = y + F.linear(a2, b2)
+        y = activation(y, act)
+        if gate is not None:
+            g = gate.to(y.dtype)
+            y = (_grouped(g, y, rows_per_group) * g[:, None, :]).view(y.shape)
+        if residual is not None:
+            y = y + residual
+        return y
     y = x.float() @ w.float().t()
     for a2, b2 in extra:
         y = y + a2.float() @ b2.float().t()
@@ -72,6 +96,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 
 def linear_glu(x, w, bias=None, act="silu", act_on_second=False, out_dtype=None):
     """Paired projection: ``h = x @ w.T + b``; halves (a, b) -> ``act(a) * b`` (SwiGLU) or ``a * act(b)`` (GEGLU)."""
+    if _library_mode(x, out_dtype):
+        a, b = F.linear(x, w, bias).chunk(2, dim=-1)
+        return a * activation(b, act) if act_on_second else activation(a, act) * b
     h = x.float() @ w.float().t()
     if bias is not None:
         h = h + bias.float()
@@ -89,6 +116,21 @@ def glu(h, act="silu", act_on_second=False):
 def norm_modulate(x, weight=None, bias=None, scale=None, shift=None, rows_per_group: int = 1, eps: float = 1e-6,
                   rms: bool = False):
     """LayerNorm or RMSNorm over the last dim, optional affine, then ``* (1 + scale[g]) + shift[g]``. x: [rows, D]."""
+    if _library_mode(x):
+        D = x.shape[-1]
+        if rms:
+            y = F.rms_norm(x, (D,), weight, eps)
+            if bias is not None:
+                y = y + bias
+        else:
+            y = F.layer_norm(x, (D,), weight, bias, eps)
+        if scale is not None:
+            sc = scale.to(y.dtype)
+            y = (_grouped(sc, y, rows_per_group) * (1 + sc[:, None, :])).view(y.shape)
+        if shift is not None:
+            sh = shift.to(y.dtype)
+            y = (_grouped(sh, y, rows_per_group) + sh[:, None, :]).view(y.shape)
+        return y
     xf = x.float()
     if rms:
         y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
@@ -188,6 +230,12 @@ def attention(q, k, v, scale: Optional[float] = None, kv_len: Optional[torch.Ten
 
 def gate_residual(x, y, gate=None, rows_per_group: int = 1, tanh_gate: bool = False):
     """x + gate[g] * y over [rows, D] (gate None: x + y)."""
+    if _library_mode(x) and not tanh_gate:
+        if gate is None:
+            return x + y
+        g = gate.to(y.dtype).reshape(-1, y.shape[-1])
+        y2 = y.reshape(-1, y.shape[-1])
+        return x + (_grouped(g, y2, rows_per_group) * g[:, None, :]).view(y.shape)
     if gate is None:
         return (x.float() + y.float()).to(x.dtype)
     g = gate.float()
