@@ -76,3 +76,50 @@ def test_ltx2_vae_shape_contract():
     assert tuple(sd["decoder.up_blocks.7.conv.conv.weight"].shape) == (512, 256, 3, 3, 3)
     assert tuple(sd["decoder.conv_out.conv.weight"].shape) == (48, 128, 3, 3, 3)
     assert "per_channel_statistics.std-of-means" in sd and "decoder.up_blocks.6.res_blocks.5.conv2.conv.bias" in sd
+
+
+def _plain_upsample(sd, cfg, z):
+    def c3(x, k):
+        return F.conv3d(x, sd[k + ".weight"], sd[k + ".bias"], padding=1)
+
+    def gn(x, k):
+        return F.group_norm(x, cfg.groups, sd[k + ".weight"], sd[k + ".bias"], eps=1e-5)
+
+    def res(x, p):
+        h = F.silu(gn(c3(x, p + ".conv1"), p + ".norm1"))
+        return F.silu(gn(c3(h, p + ".conv2"), p + ".norm2") + x)
+
+    x = F.silu(gn(c3(z, "initial_conv"), "initial_norm"))
+    for i in range(cfg.blocks):
+        x = res(x, f"res_blocks.{i}")
+    B, Cc, T, H, W = x.shape
+    if cfg.temporal:
+        y = c3(x, "upsampler.0")
+        y = y.reshape(B, Cc, 2, T, H, W).permute(0, 1, 3, 2, 4, 5).reshape(B, Cc, 2 * T, H, W)
+        x = y[:, :, 1:]
+    else:
+        y = x.permute(0, 2, 1, 3, 4).reshape(B * T, Cc, H, W)
+        y = F.pixel_shuffle(F.conv2d(y, sd["upsampler.conv.weight"], sd["upsampler.conv.bias"], padding=1), 2)
+        x = y.reshape(B, T, Cc, 2 * H, 2 * W).permute(0, 2, 1, 3, 4)
+    for i in range(cfg.blocks):
+        x = res(x, f"post_upsample_res_blocks.{i}")
+    return c3(x, "final_conv")
+
+
+def test_latent_upsampler_spatial_and_temporal_match_plain_statement():
+    from mojodiffusion_b200.models.latent_upsampler import (LatentUpsampler, ltx2_spatial_upsampler_config,
+                                                           ltx2_temporal_upsampler_config, tiny_upsampler_config)
+    g = torch.Generator().manual_seed(3)
+    for temporal in (False, True):
+        cfg = tiny_upsampler_config(temporal)
+        m = LatentUpsampler(cfg, torch.float32, "cpu").init_weights(7, std=0.08)
+        z = torch.randn(1, cfg.channels, 3, 4, 5, generator=g)
+        got = m(z)
+        assert got.shape == ((1, cfg.channels, 5, 4, 5) if temporal else (1, cfg.channels, 3, 8, 10))
+        want = _plain_upsample(m.state_dict(), cfg, z)
+        assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (temporal, float((got - want).abs().max()))
+    with torch.device("meta"):
+        sd = LatentUpsampler(ltx2_spatial_upsampler_config(), torch.bfloat16, "meta").state_dict()
+        st = LatentUpsampler(ltx2_temporal_upsampler_config(), torch.bfloat16, "meta").state_dict()
+    assert tuple(sd["upsampler.conv.weight"].shape) == (4096, 1024, 3, 3) and tuple(sd["initial_conv.weight"].shape) == (1024, 128, 3, 3, 3)
+    assert tuple(st["upsampler.0.weight"].shape) == (1024, 512, 3, 3, 3) and "post_upsample_res_blocks.3.norm2.bias" in st
