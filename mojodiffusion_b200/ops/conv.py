@@ -125,6 +125,8 @@ def conv3d_ndhwc(x, w_otohwi, bias=None, act=None, temporal_pad: str = "replicat
     if pt > 0:
         if temporal_pad == "replicate":
             xp = torch.cat([x[:, :1]] * pt + [x] + [x[:, -1:]] * pt, dim=1)
+        elif temporal_pad == "causal":
+            xp = torch.cat([x[:, :1]] * (KT - 1) + [x], dim=1)              # only the past: first frame repeated
         else:
             z = x.new_zeros(N, pt, H, W, Cin)
             xp = torch.cat((z, x, z), dim=1)
@@ -145,7 +147,9 @@ def conv3d_ndhwc_reference(x, w_otohwi, bias=None, act=None, temporal_pad: str =
     KT, KH, KW = w_otohwi.shape[1:4]
     xc = x.permute(0, 4, 1, 2, 3).float()
     pt = (KT - 1) // 2
-    if pt > 0:
+    if pt > 0 and temporal_pad == "causal":
+        xc = torch.cat([xc[:, :, :1]] * (KT - 1) + [xc], dim=2)
+    elif pt > 0:
         xc = F.pad(xc, (0, 0, 0, 0, pt, pt), mode="replicate" if temporal_pad == "replicate" else "constant")
     y = F.conv3d(xc, w_otohwi.permute(0, 4, 1, 2, 3).float(), bias.float() if bias is not None else None,
                  padding=(0, KH // 2, KW // 2))

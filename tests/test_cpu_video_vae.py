@@ -123,3 +123,60 @@ def test_latent_upsampler_spatial_and_temporal_match_plain_statement():
         st = LatentUpsampler(ltx2_temporal_upsampler_config(), torch.bfloat16, "meta").state_dict()
     assert tuple(sd["upsampler.conv.weight"].shape) == (4096, 1024, 3, 3) and tuple(sd["initial_conv.weight"].shape) == (1024, 128, 3, 3, 3)
     assert tuple(st["upsampler.0.weight"].shape) == (1024, 512, 3, 3, 3) and "post_upsample_res_blocks.3.norm2.bias" in st
+
+
+def _plain_encode(sd, cfg, video):
+    def conv(x, name):                                     # causal: two copies of the first frame on the left
+        x = torch.cat((x[:, :, :1], x[:, :, :1], x), 2)
+        return F.conv3d(x, sd[name + ".conv.weight"], sd[name + ".conv.bias"], padding=(0, 1, 1))
+
+    def pn(x, eps=1e-6):
+        return x * torch.rsqrt(x.pow(2).mean(1, keepdim=True) + eps)
+
+    def s2d(x, ft, fh, fw):
+        B, Cc, T, H, W = x.shape
+        x = x.reshape(B, Cc, T // ft, ft, H // fh, fh, W // fw, fw).permute(0, 1, 3, 5, 7, 2, 4, 6)
+        return x.reshape(B, Cc * ft * fh * fw, T // ft, H // fh, W // fw)
+
+    B, Cc, T, H, W = video.shape
+    p = cfg.patch
+    x = video.reshape(B, Cc, T, H // p, p, W // p, p).permute(0, 1, 6, 4, 2, 3, 5).reshape(B, Cc * p * p, T, H // p, W // p)
+    h = conv(x, "encoder.conv_in")
+    for i, b in enumerate(cfg.enc_blocks):
+        pre = f"encoder.down_blocks.{i}"
+        if b[0] == "mid":
+            for r in range(b[2]):
+                t = conv(F.silu(pn(h)), f"{pre}.res_blocks.{r}.conv1")
+                h = h + conv(F.silu(pn(t)), f"{pre}.res_blocks.{r}.conv2")
+        else:
+            cin, cout, ft, fh, fw = b[1:]
+            if ft == 2:
+                h = torch.cat((h[:, :, :1], h), 2)
+            skip = s2d(h, ft, fh, fw)
+            g = cin * ft * fh * fw // cout
+            if g > 1:
+                skip = skip.unflatten(1, (cout, g)).mean(2)
+            h = s2d(conv(h, pre + ".conv"), ft, fh, fw) + skip
+    h = conv(F.silu(pn(h, 1e-8)), "encoder.conv_out")[:, :cfg.latent_channels]
+    return (h - sd["per_channel_statistics.mean-of-means"].view(1, -1, 1, 1, 1)) / sd["per_channel_statistics.std-of-means"].view(1, -1, 1, 1, 1)
+
+
+def test_video_vae_encoder_matches_plain_statement_and_shapes():
+    cfg = tiny_video_vae_config()
+    m = VideoVAE(cfg, torch.float32, "cpu", with_encoder=True).init_weights(4, std=0.08)
+    g = torch.Generator().manual_seed(2)
+    getattr(m.per_channel_statistics, "std-of-means").copy_(torch.rand(cfg.latent_channels, generator=g) + 0.5)
+    getattr(m.per_channel_statistics, "mean-of-means").copy_(torch.randn(cfg.latent_channels, generator=g) * 0.2)
+    video = torch.randn(1, 3, 5, 16, 24, generator=g)                        # 1 + 2k frames for the tiny 2x temporal factor
+    got = m.encode(video)
+    assert got.shape == (1, cfg.latent_channels, 3, 2, 3)
+    want = _plain_encode(m.state_dict(), cfg, video)
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-3), float((got - want).abs().max())
+    assert m.decode(got).shape == (1, 3, 5, 16, 24)                            # the decoder inverts the shape
+    with torch.device("meta"):
+        sd = VideoVAE(ltx2_vae_config(), torch.bfloat16, "meta", with_encoder=True).state_dict()
+    assert tuple(sd["encoder.conv_in.conv.weight"].shape) == (128, 48, 3, 3, 3)
+    assert tuple(sd["encoder.down_blocks.1.conv.conv.weight"].shape) == (64, 128, 3, 3, 3)
+    assert tuple(sd["encoder.down_blocks.5.conv.conv.weight"].shape) == (128, 512, 3, 3, 3)
+    assert tuple(sd["encoder.down_blocks.7.conv.conv.weight"].shape) == (128, 1024, 3, 3, 3)
+    assert tuple(sd["encoder.conv_out.conv.weight"].shape) == (129, 1024, 3, 3, 3)
