@@ -450,7 +450,7 @@ extern "C" int mdb_attention_bwd(const MdbAttnBwdArgs* a, cudaStream_t st) {
     static int mode = -1;
     if (mode < 0) {
       const char* e = getenv("MDB200_ATTN_EXP_POLY");
-      mode = (e != nullptr && e[0] == '0') ? 0 : 1;
+      mode = (e != nullptr && e[0] == '1') ? 1 : 0;
     }
     p.exp_poly = mode;
   }

@@ -46,7 +46,8 @@ struct AttnParams {
   int B, H, Sq, Skv;
   long long o_strides[3];
   float scale_log2;
-  int exp_poly;   // every other exponential through the polynomial on the FMA pipe (MDB200_ATTN_EXP_POLY=0 turns it off)
+  int exp_poly;   // MDB200_ATTN_EXP_POLY=1: every other exponential through a polynomial on the FMA pipe. Off by default:
+                  // measured 0.41 ms against 0.27 ms at S=4608 (the softmax warps are issue bound, not SFU bound).
   int* status;
   void* o_route_a[8];
   void* o_route_b[8];
@@ -432,7 +433,7 @@ extern "C" int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st) {
     static int mode = -1;
     if (mode < 0) {
       const char* e = getenv("MDB200_ATTN_EXP_POLY");
-      mode = (e != nullptr && e[0] == '0') ? 0 : 1;
+      mode = (e != nullptr && e[0] == '1') ? 1 : 0;
     }
     p.exp_poly = mode;
   }

@@ -425,8 +425,8 @@ __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 
-// 2^x on the FMA / integer pipes instead of the special-function unit (16 results per clock per SM), for kernels whose
-// softmax is bound by that unit: half of the exponentials go here, half to ex2.approx. floor(x) comes from an add of
+// 2^x on the FMA / integer pipes instead of the special-function unit (16 results per clock per SM): an option of the
+// attention kernels (off by default, it costs more issue slots than it frees on the special-function unit). floor(x) comes from an add of
 // 1.5 * 2^23 rounded toward minus infinity (the integer lands in the low mantissa bits), 2^frac from a degree-3
 // polynomial (maximum relative error 8.6e-5, far below the bf16 rounding of the probabilities), the integer part is
 // added to the exponent field. Valid for -125 <= x <= 100; smaller inputs (masked scores) return about 2^-125.

@@ -253,6 +253,11 @@ class ShardedLinear(nn.Module):
     def bias(self):
         return self.inner.bias
 
+    @property
+    def weight(self):
+        """This rank's bf16 rows of the weight (callers read its dtype / device; the full matrix exists only transiently)."""
+        return self.inner.w_shard
+
     def forward(self, x, act=None, residual=None, gate=None, rows_per_group: int = 1, out=None):
         y = self.inner(x)
         if act is not None:
