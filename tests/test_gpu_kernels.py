@@ -440,3 +440,23 @@ def test_adamw8bit_kernel_matches_blockwise_reference():
         mg = dequantize_blockwise(sg["qm"].cpu(), sg["am"].cpu(), o_cpu.code_s, pc.shape, 256)
         assert _cos(mg, mc) > 0.9995
         assert (sg["qm"].cpu() != sc["qm"]).float().mean() < 0.02       # a code may differ by one where rounding ties
+
+
+def test_bounded_wait_runs_out_and_reports_status():
+    """Failure detection on the device: a kernel waits for a peer flag that nothing ever sets. Its wait is bounded (one
+    second of wall clock), so it returns, records TIMEOUT with the place and the silent rank in the status word, and the
+    host raises from check_status; the context stays usable (a GEMM right after gives the right answer)."""
+    import time
+    flags = torch.zeros(8 * 8, dtype=torch.int32, device=DEV)              # [slots, ranks]: this rank's arrival flags
+    flags[3 * 8 + 0] = 5                                                    # rank 0 arrived at epoch 5, rank 1 never does
+    native.check_status(flags)                                             # clean slate
+    t0 = time.time()
+    torch.ops.mdb200.flag_wait(flags, 3, 2, 5, None)
+    with pytest.raises(RuntimeError) as e:
+        native.check_status(flags)
+    dt = time.time() - t0
+    assert "TIMEOUT" in str(e.value) and "where=103" in str(e.value) and "extra=1" in str(e.value)
+    assert 0.9 < dt < 5.0, dt                                              # gave up after about a second, not earlier
+    native.check_status(flags)                                             # the status word was reset by the read
+    x, w = _rand(256, 128, seed=61), _rand(192, 128, scale=0.1, seed=62)
+    _check(O.linear(x, w), ref.linear(x, w, out_dtype=torch.float32), name="gemm after a timed-out wait")
