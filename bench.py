@@ -41,7 +41,7 @@ def _parse():
     ap.add_argument("--model", default="flux1-dev", choices=["flux1-dev", "tiny"])
     ap.add_argument("--train-steps", type=int, default=-1, help="LoRA train steps to time (-1: min(steps, 4); 0: skip)")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--train-graph", action="store_true", help="replay the training step's forward + backward as one CUDA graph (N = 1)")
+    ap.add_argument("--no-train-graph", action="store_true", help="launch the training step's forward + backward eagerly instead of replaying one CUDA graph")
     ap.add_argument("--no-graph", action="store_true", help="launch the forward eagerly instead of replaying a CUDA graph")
     ap.add_argument("--sp-mode", default="fused", choices=["fused", "nccl"], help="Ulysses all-to-all: fused peer stores or NCCL baseline")
     return ap.parse_args()
@@ -285,12 +285,33 @@ def main():
             opt = FusedDPAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
         else:
             opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
-        tr = FlowMatchTrainer(model, params, opt, dp, use_cuda_graph=args.train_graph and world == 1 and not lib_baseline)
+        tr = FlowMatchTrainer(model, params, opt, dp, use_cuda_graph=not args.no_train_graph and not lib_baseline)
         gt = torch.Generator().manual_seed(99 + rank)   # data parallel: every rank trains on its own samples
         x0 = torch.randn(B, S_img, cfg.in_channels, generator=gt).to(dev)
         txt = torch.randn(B, S_txt, cfg.context_dim, generator=gt).to(dev, torch.bfloat16)
         y = torch.randn(B, cfg.vec_dim, generator=gt).to(dev, torch.bfloat16)
-        for i in range(3):
+        want_graph = tr.use_cuda_graph
+        tr.use_cuda_graph = False
+        l0 = launches()
+        tr.step(x0, txt, y, hw=hw)                       # one eager step: also counts the kernels of a step
+        torch.cuda.synchronize()
+        train_launches_per_step = launches() - l0
+        if want_graph:
+            ok_graph = 1
+            tr.use_cuda_graph = True
+            try:
+                tr.step(x0, txt, y, hw=hw)               # warms up, captures forward + backward, replays once
+                torch.cuda.synchronize()
+            except Exception as ex:                      # capture refused: report it and time the eager step instead
+                ok_graph = 0
+                sys.stderr.write(f"[bench] training graph capture failed, timing the eager step: {ex}\n")
+            if world > 1:
+                flag = torch.tensor([ok_graph], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                ok_graph = int(flag.item())
+            if not ok_graph:
+                tr.use_cuda_graph, tr._graphed = False, None
+        for i in range(2):
             tr.step(x0, txt, y, hw=hw)
         torch.cuda.synchronize()
         pdist.barrier()
@@ -305,7 +326,8 @@ def main():
         native.check_status()
         train = {"metric": "lora_train_samples_per_s", "value": world * B * 1000.0 / ms_t, "unit": "samples/s",
                  "ms_per_step": ms_t, "steps": tsteps, "warmup": 3, "loss": float(loss), "rank": 16,
-                 "gpu_launches": launches() - t0n, "gradient_checkpointing": True, "cuda_graph": bool(tr._graphed is not None),
+                 "gpu_launches": (train_launches_per_step * tsteps if tr._graphed is not None else launches() - t0n),
+                 "launches_per_step": train_launches_per_step, "gradient_checkpointing": True, "cuda_graph": bool(tr._graphed is not None),
                  "parallelism": f"dp{world}, NCCL all-reduce + torch AdamW" if (lib_baseline and world > 1) else (f"dp{world}, grad reduce-scatter + clip + AdamW + param all-gather fused in peer-memory "
                                  f"kernels (multicast {'on' if getattr(opt, 'symm', None) is not None and opt.symm.mc_ptr else 'off'})")
                  if world > 1 else "single"}

@@ -86,12 +86,13 @@ class FlowMatchTrainer:
                 pred = self.model(xt.to(dt), txt_.to(dt), sigma_, y_.to(dt), guidance, hw=hw)
                 return ops.mse_loss(pred, target)
 
-            self._graphed = GraphedTrainStep(loss_fn, self.params, inputs).capture()
+            flat = getattr(self.opt, "flat_grads", None) is not None      # gradients are views of one buffer: clear it in the graph
+            self._graphed = GraphedTrainStep(loss_fn, self.params, inputs, zero_grad=self.opt.zero_grad if flat else None).capture()
             self._graph_key = key
         return self._graphed(*inputs).detach()
 
     def step(self, x0, txt, y, sigma=None, noise=None, hw=None, lr: Optional[float] = None) -> torch.Tensor:
-        if self.use_cuda_graph and x0.is_cuda and self.dp is None and type(self.opt) is FusedAdamW:
+        if self.use_cuda_graph and x0.is_cuda and self.dp is None and (type(self.opt) is FusedAdamW or hasattr(self.opt, "flat_grads")):
             loss = self._graphed_loss_and_backward(x0, txt, y, sigma, noise, hw)
             self.opt.step(grad_scale=1.0, lr=lr)
             self.step_index += 1

@@ -72,7 +72,11 @@ class GraphedTrainStep:
     stash RNG state (serenitymojo/autograd_v2/capture.mojo:34-180: 5,774 forward + 21,036 backward graph nodes per step)."""
 
     def __init__(self, loss_fn: Callable, params: Sequence[torch.nn.Parameter], example_inputs: Sequence[torch.Tensor],
-                 warmup: int = 3):
+                 warmup: int = 3, zero_grad: Callable = None):
+        """``zero_grad``: for optimizers whose gradients are views of one flat buffer (the fused data-parallel AdamW): it is
+        called INSIDE the capture before the forward, so every replay clears the buffer and the backward accumulates into
+        the same views. Without it the gradients are created by the captured backward itself."""
+        self.zero_grad = zero_grad
         self.loss_fn = loss_fn
         self.params = [p for p in params]
         self.static_in = [t.clone() for t in example_inputs]
@@ -89,13 +93,16 @@ class GraphedTrainStep:
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             for _ in range(self.warmup):
-                self._clear()
+                self.zero_grad() if self.zero_grad is not None else self._clear()
                 self.loss_fn(*self.static_in).backward()
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
-        self._clear()
+        if self.zero_grad is None:
+            self._clear()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
+            if self.zero_grad is not None:
+                self.zero_grad()
             self.static_loss = self.loss_fn(*self.static_in)
             self.static_loss.backward()
         return self
