@@ -145,3 +145,26 @@ def test_streamed_training_matches_resident_gradients():
     for b, g in zip(blocks, ref_gl):
         assert torch.allclose(b.lora.grad, g, atol=1e-6)
     assert loader.tel.await_calls == 10                      # every block streamed once forward, once backward
+
+
+def test_parallel_video_dit_single_rank_equals_model():
+    """The token-sharded video DiT driver with one rank (no communication) restates the model's forward exactly."""
+    import torch
+    from mojodiffusion_b200.models.video_dit import VideoDiT, tiny_video_dit_config
+    from mojodiffusion_b200.parallel.video_parallel import ParallelVideoDiT
+    cfg = tiny_video_dit_config()
+    m = VideoDiT(cfg, torch.float32, "cpu").init_weights(0)
+    with torch.no_grad():
+        for blk in m.transformer_blocks:
+            blk.scale_shift_table.copy_(0.1 * torch.randn(blk.scale_shift_table.shape, generator=torch.Generator().manual_seed(3)))
+    g = torch.Generator().manual_seed(1)
+    grid = (2, 4, 4)
+    x = torch.randn(1, 32, cfg.in_channels, generator=g)
+    ctx = torch.randn(1, 8, cfg.context_dim, generator=g)
+    t = torch.tensor([0.6])
+
+    par = ParallelVideoDiT(m, grid, mode="nccl", device=torch.device("cpu"))
+    with torch.no_grad():
+        want = m(x, ctx, t, grid)
+        got = par.forward(x, ctx, t)
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-5), float((got - want).abs().max())
