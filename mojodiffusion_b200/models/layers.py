@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import math
 import zlib
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.nn as nn

@@ -16,8 +16,8 @@ Two execution styles share the same modules:
 from __future__ import annotations
 
 import zlib
-from dataclasses import dataclass, field
-from typing import Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn

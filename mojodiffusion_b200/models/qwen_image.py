@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from .layers import LayerNorm, Linear, RMSNorm, init_module_weights, packed_projection, timestep_embedding
+from .layers import Linear, RMSNorm, init_module_weights, packed_projection, timestep_embedding
 
 
 @dataclass

@@ -15,7 +15,6 @@ layer, unpatchify order); serenitymojo/models/dit/sd3_contract.mojo:11-81 (sizes
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Tuple
 
 import torch
 import torch.nn as nn

@@ -4,7 +4,7 @@ block weights on the device (serenitymojo/offload/conductor_policy.mojo:9-59).""
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Sequence
+from typing import Sequence
 
 
 @dataclass(frozen=True)

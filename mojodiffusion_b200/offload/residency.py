@@ -4,7 +4,7 @@ never go) (serenitymojo/offload/residency.mojo:40-526)."""
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 UNLOADED, HOST_STAGED, PREFETCHING, GPU_READY, EVICTING, GPU_FREEING = (
     "unloaded", "host_staged", "prefetching", "gpu_ready", "evicting", "gpu_freeing")

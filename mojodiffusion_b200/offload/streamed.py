@@ -8,7 +8,7 @@ weights nor inner activations are held between the two passes
 (serenitymojo/models/flux/flux_stack_lora.mojo:1619-2019 offload variants; training/checkpoint_block.mojo:245-485)."""
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Sequence
+from typing import Callable, Dict, Sequence
 
 import torch
 from torch import nn

@@ -2,7 +2,7 @@
 to wait for copies, bytes moved (serenitymojo/offload/telemetry.mojo:10-131)."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict
 
 

@@ -10,7 +10,7 @@ the multi-rank kernels with it, rank by rank, over all ranks' data (no kernel ev
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional
 
 import torch

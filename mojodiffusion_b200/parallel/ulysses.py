@@ -16,7 +16,7 @@ and the correctness oracle of the fused path.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Optional
 
 import torch
 import torch.distributed as dist

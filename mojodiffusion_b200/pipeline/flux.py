@@ -9,12 +9,12 @@ progress payload of serenitymojo/serve/flux_backend.mojo:482-512).
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Sequence
+from typing import Callable, Optional
 
 import torch
 
 from .. import ops
-from ..models.mmdit import MMDiT, pack_latents, unpack_latents
+from ..models.mmdit import MMDiT, pack_latents
 from ..sampling import flow_match as fm
 
 

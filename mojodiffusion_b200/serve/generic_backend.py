@@ -34,7 +34,7 @@ import json
 import math
 import os
 import time
-from typing import List, Optional
+from typing import Optional
 
 import torch
 

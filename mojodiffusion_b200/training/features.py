@@ -5,7 +5,7 @@ timestep_bias.mojo:1-70, grad_accum.mojo, grad_coverage.mojo)."""
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Optional
+from typing import Iterable, List, Optional
 
 import torch
 

@@ -15,7 +15,7 @@ from typing import Dict, List, Sequence, Tuple
 import torch
 from torch import nn
 
-from ..io.safetensors_io import SafeTensors, load_safetensors, save_safetensors
+from ..io.safetensors_io import load_safetensors, save_safetensors
 from .optim import FusedAdamW
 
 MANIFEST_KEY = "__full_finetune_tensor_names_utf8__"

@@ -13,7 +13,7 @@ Z-Image (serenitymojo/models/zimage/zimage_stack_lora.mojo:1655-1700), LTX-2 (se
 from __future__ import annotations
 
 from collections import OrderedDict
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, Iterable, List, Optional, Sequence
 
 import torch
 import torch.nn as nn

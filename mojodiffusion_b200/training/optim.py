@@ -13,7 +13,7 @@ serenitymojo/training/on_device_global_norm.mojo.
 from __future__ import annotations
 
 import math
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Iterable, List, Optional, Tuple
 
 import torch
 

@@ -5,7 +5,7 @@ adamw_schedulefree.mojo, adamw8bit.mojo (bitsandbytes block-256 dynamic map pari
 from __future__ import annotations
 
 import math
-from typing import Iterable, List, Optional
+from typing import Iterable, Optional
 
 import torch
 

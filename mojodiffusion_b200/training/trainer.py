@@ -8,7 +8,7 @@ tensor resident on the device and no host round trip inside the step except the 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 
