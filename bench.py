@@ -238,14 +238,6 @@ def main():
         head = measure(None, 1234 + rank, False, not args.no_e2e)
         ms, clocks, launches_per_step, n_launch, e2e = head["ms"], head["clocks"], head["launches_per_step"], head["n_launch"], head["e2e"]
         it_per_s = world * B * 1000.0 / ms
-        if world > 1 and not lib_baseline:
-            from mojodiffusion_b200.parallel.ulysses import UlyssesContext
-            sp = UlyssesContext(B, S_txt, S_img, cfg.heads, cfg.head_dim, mode=args.sp_mode, device=dev)
-            st = measure(sp, 1234, True, not args.no_e2e)
-            strong = {"what": "one sample sharded over the ranks (Ulysses sequence parallel, all-to-all " + args.sp_mode + ")",
-                      "value": B * 1000.0 / st["ms"], "unit": "it/s", "ms_per_step": st["ms"], "scaling": "strong",
-                      "launches_per_step": st["launches_per_step"], "e2e": st["e2e"]}
-            del sp
 
     # ------------------------------------------------------------------ LoRA training samples/s
     train = None
@@ -331,6 +323,24 @@ def main():
                  "parallelism": f"dp{world}, NCCL all-reduce + torch AdamW" if (lib_baseline and world > 1) else (f"dp{world}, grad reduce-scatter + clip + AdamW + param all-gather fused in peer-memory "
                                  f"kernels (multicast {'on' if getattr(opt, 'symm', None) is not None and opt.symm.mc_ptr else 'off'})")
                  if world > 1 else "single"}
+
+    # ------------------------------------------------------------------ one sample over all GPUs (strong scaling)
+    # Runs last and guarded: a failure here must not cost the numbers above.
+    if do_denoise and world > 1 and not lib_baseline:
+        try:
+            from mojodiffusion_b200.parallel.ulysses import UlyssesContext
+            model.eval()
+            for mod in model.modules():                   # drop the adapters the training section attached
+                if hasattr(mod, "slots") and len(mod.slots):
+                    mod.slots = torch.nn.ModuleList()
+            torch.cuda.empty_cache()
+            sp = UlyssesContext(B, S_txt, S_img, cfg.heads, cfg.head_dim, mode=args.sp_mode, device=dev)
+            st = measure(sp, 1234, True, not args.no_e2e)
+            strong = {"what": "one sample sharded over the ranks (Ulysses sequence parallel, all-to-all " + args.sp_mode + ")",
+                      "value": B * 1000.0 / st["ms"], "unit": "it/s", "ms_per_step": st["ms"], "scaling": "strong",
+                      "launches_per_step": st["launches_per_step"], "e2e": st["e2e"]}
+        except Exception as ex:
+            strong = {"error": str(ex)[:300]}
 
     if rank == 0:
         line = {
