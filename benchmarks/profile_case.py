@@ -17,7 +17,7 @@ from mojodiffusion_b200.ops import native  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "gemm_trace", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
     ap.add_argument("--shape", default="")
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
@@ -82,6 +82,49 @@ def main():
                 col = pr[:, i][pr[:, i] > 0]
                 if col.numel():
                     print(f"  {nm:24s} mean {col.mean():12.0f}  max {col.max():12.0f}  (n={col.numel()})")
+        native.check_status()
+        print("ok")
+        return
+    if a.op == "gemm_trace":
+        # per-K-block time line of CTA 0 (clock64): when the producer saw a free stage and issued its loads, when the MMA
+        # issuer saw the operands, when the epilogue saw / drained each accumulator
+        from mojodiffusion_b200.ops.functional import _gemm
+        M, N, K = dims or [4608, 3072, 3072]
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        T = 2048
+        kb_per_tile = (K + 63) // 64
+        for bn in (256, 512):
+            for _ in range(2):
+                _gemm([x], [w], bn=bn)
+            prof = torch.zeros(8 * sms + 6 * T, dtype=torch.int64, device=dev)
+            flush.zero_()
+            _gemm([x], [w], bn=bn, prof=prof)
+            torch.cuda.synchronize()
+            tr = prof[8 * sms:].view(2, 3, T).cpu()
+            prod, mma, epi = tr[0, 0], tr[0, 1], tr[0, 2]
+            n = int((mma > 0).sum())
+            t0 = int(prod[0])
+            print(f"bn={bn} shape={M}x{N}x{K}: {n} K blocks traced in CTA 0, {kb_per_tile} per tile")
+            mm = (mma[:n] - t0).tolist()
+            pp = (prod[:n] - t0).tolist()
+            print("  first 24 K blocks: producer issue | operands seen | seen - issue")
+            for i in range(min(24, n)):
+                print(f"    kb {i:3d}  {pp[i]:8d}  {mm[i]:8d}  {mm[i] - pp[i]:6d}")
+            for tile in range((n + kb_per_tile - 1) // kb_per_tile):
+                lo, hi = tile * kb_per_tile, min(n, (tile + 1) * kb_per_tile)
+                d = [mm[i + 1] - mm[i] for i in range(lo, hi - 1)]
+                dp = [pp[i + 1] - pp[i] for i in range(lo, hi - 1)]
+                lat = [mm[i] - pp[i] for i in range(lo, hi)]
+                d.sort(); dp.sort(); lat.sort()
+                print(f"  tile {tile}: span {mm[hi - 1] - mm[lo]} cycles for {hi - lo} blocks; MMA-seen step median {d[len(d) // 2]} "
+                      f"p90 {d[int(len(d) * .9)]} max {d[-1]}; producer step median {dp[len(dp) // 2]} max {dp[-1]}; "
+                      f"seen-issue median {lat[len(lat) // 2]} min {lat[0]} max {lat[-1]}")
+            ne = int((epi > 0).sum())
+            print("  epilogue (accumulator seen, drained) per tile:", [(int(epi[2 * i] - t0), int(epi[2 * i + 1] - t0)) for i in range(ne // 2)])
+            pr = prof[:8 * sms].view(sms, 8).cpu()
+            print("  CTA 0 counters: mma_total %d producer_wait %d mma_wait_full %d mma_wait_acc %d epi_wait %d epi_work %d" % tuple(int(v) for v in pr[0, :6]))
         native.check_status()
         print("ok")
         return

@@ -487,3 +487,5 @@ extern "C" int mdb_attention_bwd(const MdbAttnBwdArgs* a, cudaStream_t st) {
   }
   return 0;
 }
+
+MDB_DEFINE_WAIT_LIMIT_SETTER(mdb_set_wait_limit_attn_bwd)

@@ -448,3 +448,5 @@ extern "C" int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st) {
   if (a->Dh == 128) return launch_attn<128>(maps, p, st);
   return launch_attn<64>(maps, p, st);
 }
+
+MDB_DEFINE_WAIT_LIMIT_SETTER(mdb_set_wait_limit_attn_fwd)

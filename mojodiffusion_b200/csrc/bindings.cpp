@@ -147,6 +147,11 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
   if (prof.has_value() && prof->defined()) {
     TORCH_CHECK(prof->scalar_type() == at::kLong && prof->numel() >= 8 * g.num_sms, "gemm: prof [sms, 8] int64");
     g.prof = reinterpret_cast<long long*>(prof->data_ptr());
+    const int64_t extra = prof->numel() - 8 * g.num_sms;
+    if (extra >= 6 * 64) {                       // room behind the counters: per-K-block time line of CTAs 0 and 1
+      g.trace = g.prof + 8 * g.num_sms;
+      g.trace_len = static_cast<int>(extra / 6);
+    }
   }
   if (!gather_ptrs.empty()) {
     // gather_cfg = {rank, operand (0 A / 1 B), chunk_rows, chunk_bytes}
@@ -720,7 +725,7 @@ void publish_scalar(std::vector<int64_t> scalar_ptrs, std::vector<int64_t> flag_
   c10::cuda::CUDAGuard guard(value.device());
   MdbPeerTable sc = peer_table(scalar_ptrs), f = peer_table(flag_ptrs);
   check_rc(mdb_publish_scalar(&sc, &f, value.data_ptr<float>(), (int)slot, (int)rank, (int)flag_ptrs.size(), (int)epoch,
-                              cur_stream()),
+                              status_ptr(value), cur_stream()),
            "publish_scalar");
 }
 void dp_adamw_shard(std::vector<int64_t> param_ptrs, int64_t params_mc, std::vector<int64_t> flag_ptrs,
@@ -748,6 +753,15 @@ std::vector<int64_t> read_status(const Tensor& like, bool reset) {
   C10_CUDA_CHECK(cudaMemcpy(h, p, sizeof(h), cudaMemcpyDeviceToHost));
   if (reset && h[0] != 0) C10_CUDA_CHECK(cudaMemset(p, 0, sizeof(h)));
   return {h[0], h[1], h[2], h[3]};
+}
+
+// limit of every bounded device-side wait on the current device, in nanoseconds (default 1e9)
+void set_wait_limit_ns(int64_t ns) {
+  TORCH_CHECK(ns > 0, "set_wait_limit_ns: positive nanoseconds");
+  const unsigned long long v = static_cast<unsigned long long>(ns);
+  const int rc = mdb_set_wait_limit_gemm(v) | mdb_set_wait_limit_attn_fwd(v) | mdb_set_wait_limit_attn_bwd(v) |
+                 mdb_set_wait_limit_comm(v);
+  TORCH_CHECK(rc == 0, "set_wait_limit_ns failed: ", rc);
 }
 
 // number of kernel launches issued through this library since load
@@ -796,4 +810,5 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("publish_scalar", &publish_scalar);
   m.def("dp_adamw_shard", &dp_adamw_shard);
   m.def("read_status", &read_status);
+  m.def("set_wait_limit_ns", &set_wait_limit_ns);
 }

@@ -37,13 +37,21 @@ int mdb_peer_gather(const MdbPeerTable* src, void* dst, long long chunk_bytes, i
 
 int mdb_dp_reduce_shard(const MdbPeerTable* grads, const void* grads_mc, const int* my_flags, int ready_slot, int epoch,
                         int world, long long lo, long long hi, float* red, float* sumsq, int* status, cudaStream_t st);
+// status (may be NULL): when the device's status word is not OK the rank publishes NaN, which makes every peer skip its update
 int mdb_publish_scalar(const MdbPeerTable* scalars, const MdbPeerTable* flags, const float* value, int slot, int rank,
-                       int world, int epoch, cudaStream_t st);
+                       int world, int epoch, const int* status, cudaStream_t st);
 int mdb_dp_adamw_shard(const MdbPeerTable* params, void* params_mc, const MdbPeerTable* flags, const int* my_flags,
                        const float* my_scalars, int norm_slot, int done_slot, int epoch, int rank, int world,
                        long long lo, long long hi, const float* red, float* m, float* v, float lr, float beta1,
                        float beta2, float eps, float wd, int step, float grad_scale, float max_norm, float* norm_out,
                        int* done_counter, int* status, cudaStream_t st);
+
+// Wall-clock limit (nanoseconds) of every bounded device-side wait, per translation unit; one second by default. Applies to
+// the current device.
+int mdb_set_wait_limit_gemm(unsigned long long ns);
+int mdb_set_wait_limit_attn_fwd(unsigned long long ns);
+int mdb_set_wait_limit_attn_bwd(unsigned long long ns);
+int mdb_set_wait_limit_comm(unsigned long long ns);
 
 #ifdef __cplusplus
 }

@@ -156,10 +156,13 @@ dp_reduce_shard_kernel(MdbPeerTable grads, const void* grads_mc, const int* my_f
 }
 
 // scalars: symmetric fp32 [MDB_MAX_RANKS] per rank; rank writes its partial into slot `rank` on every peer
+// A rank whose status word is not OK (its reduce wait ran out, so *value is incomplete) publishes NaN instead: every
+// peer's update kernel then sees a non-finite norm, skips its own update and records the failure on its own device.
 __global__ void publish_scalar_kernel(MdbPeerTable scalars, MdbPeerTable flags, const float* value, int slot, int rank,
-                                      int world, int epoch) {
+                                      int world, int epoch, const int* status) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
-    const float v = *value;
+    float v = *value;
+    if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != STATUS_OK) v = __int_as_float(0x7fc00000);
     for (int r = 0; r < world; ++r) reinterpret_cast<float*>(scalars.p[r])[rank] = v;
     signal_all(flags, slot, rank, world, epoch);
   }
@@ -176,9 +179,17 @@ dp_adamw_shard_kernel(MdbPeerTable params, void* params_mc, MdbPeerTable flags, 
                       const float* my_scalars, int norm_slot, int done_slot, int epoch, int rank, int world,
                       long long lo, long long hi, const float* __restrict__ red, float* __restrict__ m,
                       float* __restrict__ v, DpAdam h, float* __restrict__ norm_out, int* done_counter, int* status) {
-  if (!block_wait_all(my_flags, norm_slot, world, epoch, status, 202)) return;
+  // A wait that ran out anywhere on this device since the host last read the status word (this kernel's own wait, the
+  // reduce kernel before it, a GEMM of the step) means `red` may be stale: skip the update, but still publish the done
+  // flag so that the peers' waits end. The host sees the status at its next check and fails the step.
+  bool healthy = block_wait_all(my_flags, norm_slot, world, epoch, status, 202);
+  healthy = healthy && (status == nullptr || *reinterpret_cast<volatile int*>(status) == STATUS_OK);
   float total = 0.f;
   for (int r = 0; r < world; ++r) total += my_scalars[r];
+  if (healthy && !(total == total)) {              // a peer published NaN: its reduce failed
+    healthy = false;
+    if (threadIdx.x == 0) report_status(status, STATUS_TIMEOUT, 203, 0);
+  }
   const float norm = sqrtf(total) * h.grad_scale;
   float clip = 1.f;
   if (h.max_norm > 0.f) {
@@ -189,7 +200,7 @@ dp_adamw_shard_kernel(MdbPeerTable params, void* params_mc, MdbPeerTable flags, 
   const float gmul = h.grad_scale * clip;
   const long long nvec = (hi - lo) >> 3;
   __nv_bfloat16* my_params = reinterpret_cast<__nv_bfloat16*>(params.p[rank]);
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; healthy && i < nvec; i += (long long)gridDim.x * blockDim.x) {
     const long long e = lo + i * 8;
     const uint4 pu = *reinterpret_cast<const uint4*>(my_params + e);
     const uint32_t pw[4] = {pu.x, pu.y, pu.z, pu.w};
@@ -271,6 +282,9 @@ rs_finalize_kernel(MdbPeerTable flags, const int* my_flags, int slot, int epoch,
     if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(flags, slot, rank, world, epoch);
     if (!block_wait_all(my_flags, slot, world, epoch, status, 120 + slot)) return;
   }
+  // a wait that ran out earlier in this step (status not yet read by the host): the partial sums may be incomplete, so
+  // nothing is written (the peers were signalled above and do not wait for this rank)
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != STATUS_OK) return;
   const long long vec_per_row = D / 8;
   const long long total = rows * vec_per_row;
   const long long slot_elems = rows * static_cast<long long>(D);
@@ -367,8 +381,8 @@ extern "C" int mdb_dp_reduce_shard(const MdbPeerTable* grads, const void* grads_
   return (int)cudaGetLastError();
 }
 extern "C" int mdb_publish_scalar(const MdbPeerTable* scalars, const MdbPeerTable* flags, const float* value, int slot,
-                                  int rank, int world, int epoch, cudaStream_t st) {
-  publish_scalar_kernel<<<1, 32, 0, st>>>(*scalars, *flags, value, slot, rank, world, epoch);
+                                  int rank, int world, int epoch, const int* status, cudaStream_t st) {
+  publish_scalar_kernel<<<1, 32, 0, st>>>(*scalars, *flags, value, slot, rank, world, epoch, status);
   return (int)cudaGetLastError();
 }
 extern "C" int mdb_dp_adamw_shard(const MdbPeerTable* params, void* params_mc, const MdbPeerTable* flags,
@@ -387,3 +401,5 @@ extern "C" int mdb_dp_adamw_shard(const MdbPeerTable* params, void* params_mc, c
                                               epoch, rank, world, lo, hi, red, m, v, h, norm_out, done_counter, status);
   return (int)cudaGetLastError();
 }
+
+MDB_DEFINE_WAIT_LIMIT_SETTER(mdb_set_wait_limit_comm)

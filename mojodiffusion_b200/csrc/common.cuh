@@ -24,10 +24,16 @@ enum : int {
   STATUS_BOUNDS = 3,       // a bounds-checked build saw an out-of-range index
 };
 
-// wall-clock limit of every device-side wait (nanoseconds)
-#ifndef MDB_WAIT_LIMIT_NS
-#define MDB_WAIT_LIMIT_NS 1000000000ull
-#endif
+// Wall-clock limit of every device-side wait (nanoseconds): a device variable per translation unit, one second unless the
+// host changes it through that unit's setter (see MDB_DEFINE_WAIT_LIMIT_SETTER; `torch.ops.mdb200.set_wait_limit_ns`
+// calls them all). A run whose ranks are legitimately far apart (rank 0 saving a checkpoint) can raise it; a test of the
+// time-out path can lower it.
+static __device__ unsigned long long g_wait_limit_ns = 1000000000ull;
+#define MDB_WAIT_LIMIT_NS (::mdb::g_wait_limit_ns)
+#define MDB_DEFINE_WAIT_LIMIT_SETTER(name)                                                        \
+  extern "C" int name(unsigned long long ns) {                                                    \
+    return static_cast<int>(cudaMemcpyToSymbol(::mdb::g_wait_limit_ns, &ns, sizeof(ns)));         \
+  }
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;

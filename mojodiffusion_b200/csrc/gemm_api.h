@@ -44,6 +44,8 @@ typedef struct MdbGemmArgs {
   int* status;                     // device int[4], zero on entry; see common.cuh
   long long* prof;                 // optional device [grid, 8] cycle counters: total, producer wait, mma wait-full,
                                    // mma wait-accumulator, epilogue wait, epilogue work, tiles
+  long long* trace;                // optional device [2 CTAs][3 roles][trace_len] clock64 time line (producer: stage free seen;
+  int trace_len;                   // MMA issuer: operands seen; epilogue: accumulator seen / drained, alternating)
   // Peer-routed output (route_owner_cols > 0). The N output columns are `parts` of route_part_cols columns; inside
   // a part, consecutive blocks of route_owner_cols columns belong to ranks 0, 1, ... Block (part, owner) of output
   // row r is stored into route_out[owner] (that rank's buffer, leading dimension ld_out) at row

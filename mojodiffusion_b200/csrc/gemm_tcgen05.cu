@@ -58,6 +58,8 @@ struct GemmParams {
   int accumulate_out;  // out += result (fp32 out only)
   int* status;
   long long* prof;  // optional [grid, 8] cycle counters (profiling builds of the caller)
+  long long* trace;  // optional per-K-block time line of CTAs 0 and 1: [2 CTAs][3 roles][trace_len] clock64 values
+  int trace_len;
   // peer-routed output (sequence-parallel all-to-all in the epilogue): see MdbGemmArgs
   void* route_out[MDB_GEMM_MAX_PEERS];
   int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
@@ -369,7 +371,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
-    if (lane == 0) {
+    // The whole warp runs the loop (waits included) and elect.sync picks the lane that issues: tcgen05 / TMA instructions
+    // issued from a convergent warp cost about 120 cycles each, from inside a one-lane branch about 190 (measured), which
+    // is more than the 128 cycles a 128 x 256 x 16 MMA takes.
+    {
       int stage = 0;
       uint32_t phase = 0;
       int last_stage = -1;
@@ -377,6 +382,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       bool ok = true;
       long long t_wait = 0;
       unsigned chunk_seen = 1u << p.gather_rank;   // chunks whose arrival this CTA has already observed
+      int n_trace = 0;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const int tile = item % num_tiles;
         const int m0 = tile_m_index(p, tile, tiles_m, tiles_n) * BM;
@@ -392,13 +398,18 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             if (chunk_seen & (1u << c)) continue;
             const uint64_t t0 = globaltimer_ns();
             uint32_t spins = 0;
+            bool mine = true;
             while (ld_acquire_gpu(p.gather_ready + c) < static_cast<int>(gridDim.x)) {
               if ((++spins & 0xffu) == 0 && (abort_s || globaltimer_ns() - t0 > MDB_WAIT_LIMIT_NS)) {
                 abort_s = 1;
-                report_status(p.status, STATUS_TIMEOUT, 5, c);
-                ok = false;
+                mine = false;
                 break;
               }
+            }
+            if (!__all_sync(0xffffffffu, mine)) {
+              if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 5, c);
+              ok = false;
+              break;
             }
             chunk_seen |= 1u << c;
           }
@@ -409,43 +420,47 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           const int kb_begin = s == 0 ? kb_lo_of(item) : 0, kb_end = s == 0 ? kb_hi_of(item) : p.kblocks[s];
           for (int kb = kb_begin; kb < kb_end; ++kb) {
             const long long tw0 = p.prof ? clock64() : 0;
-            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s)) {
-              report_status(p.status, STATUS_TIMEOUT, 1, stage);
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s))) {
+              if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 1, stage);
               ok = false;
               break;
             }
             if (p.prof) t_wait += clock64() - tw0;
+            if (p.trace && lane == 0 && blockIdx.x < 2 && n_trace < p.trace_len) p.trace[(blockIdx.x * 3 + 0) * p.trace_len + n_trace++] = clock64();
             uint8_t* sa = smem + stage * STAGE_BYTES;
             uint8_t* sb = sa + A_BYTES;
-            mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
             int k0 = kb * K_ELEMS;
-            if (p.conv_taps > 0) {
-              // tile -> (image, patch row, patch col); k block -> (filter tap, channel block)
-              const int mt = tile % tiles_m;
-              const int tw = mt % p.conv_tiles_w, th = (mt / p.conv_tiles_w) % p.conv_tiles_h;
-              const int img = mt / (p.conv_tiles_w * p.conv_tiles_h);
-              const int tap = kb / p.conv_cblocks, cb = kb - tap * p.conv_cblocks;
-              const int kh = tap / p.conv_kw, kw = tap - kh * p.conv_kw;
-              tma_load_4d(sa, &maps.a[s], &full_bar[stage], cb * K_ELEMS, tw * CONV_TW + kw - p.conv_pad_w,
-                          th * CONV_TH + kh - p.conv_pad_h, img);
-              k0 = (tap * p.conv_cblocks + cb) * K_ELEMS;
-            } else if (!A_MN) {
-              tma_load_2d(sa, &maps.a[s], &full_bar[stage], k0, m0);
-            } else {
-              // boxes [64 m-elements][64 k-rows], 8 KB each
-              tma_load_2d(sa, &maps.a[s], &full_bar[stage], m0, k0);
-              tma_load_2d(sa + 8192, &maps.a[s], &full_bar[stage], m0 + 64, k0);
-            }
-            if (!B_MN) {
-              constexpr int HALF_ROWS = BN / 2;
-              const int n1 = p.pair_offset > 0 ? n0 + p.pair_offset : n0 + HALF_ROWS;
-              tma_load_2d(sb, &maps.b[s], &full_bar[stage], k0, n0);
-              tma_load_2d(sb + HALF_ROWS * BK_BYTES, &maps.b[s], &full_bar[stage], k0, n1);
-            } else {
+            if (elect_one()) {
+              mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+              if (p.conv_taps > 0) {
+                // tile -> (image, patch row, patch col); k block -> (filter tap, channel block)
+                const int mt = tile % tiles_m;
+                const int tw = mt % p.conv_tiles_w, th = (mt / p.conv_tiles_w) % p.conv_tiles_h;
+                const int img = mt / (p.conv_tiles_w * p.conv_tiles_h);
+                const int tap = kb / p.conv_cblocks, cb = kb - tap * p.conv_cblocks;
+                const int kh = tap / p.conv_kw, kw = tap - kh * p.conv_kw;
+                tma_load_4d(sa, &maps.a[s], &full_bar[stage], cb * K_ELEMS, tw * CONV_TW + kw - p.conv_pad_w,
+                            th * CONV_TH + kh - p.conv_pad_h, img);
+                k0 = (tap * p.conv_cblocks + cb) * K_ELEMS;
+              } else if (!A_MN) {
+                tma_load_2d(sa, &maps.a[s], &full_bar[stage], k0, m0);
+              } else {
+                // boxes [64 m-elements][64 k-rows], 8 KB each
+                tma_load_2d(sa, &maps.a[s], &full_bar[stage], m0, k0);
+                tma_load_2d(sa + 8192, &maps.a[s], &full_bar[stage], m0 + 64, k0);
+              }
+              if (!B_MN) {
+                constexpr int HALF_ROWS = BN / 2;
+                const int n1 = p.pair_offset > 0 ? n0 + p.pair_offset : n0 + HALF_ROWS;
+                tma_load_2d(sb, &maps.b[s], &full_bar[stage], k0, n0);
+                tma_load_2d(sb + HALF_ROWS * BK_BYTES, &maps.b[s], &full_bar[stage], k0, n1);
+              } else {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_2d(sb + j * 8192, &maps.b[s], &full_bar[stage], n0 + j * 64, k0);
+                for (int j = 0; j < BN / 64; ++j)
+                  tma_load_2d(sb + j * 8192, &maps.b[s], &full_bar[stage], n0 + j * 64, k0);
+              }
             }
+            __syncwarp();
             last_stage = stage;
             last_phase = phase;
             if (++stage == STAGES) {
@@ -455,7 +470,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           }
         }
       }
-      if (p.prof) p.prof[blockIdx.x * 8 + 1] = t_wait;
+      if (p.prof && lane == 0) p.prof[blockIdx.x * 8 + 1] = t_wait;
       if (!ok && last_stage >= 0) {
         // abandoned: let the copies already in flight land before the CTA goes away (bounded)
         uint64_t t0 = globaltimer_ns();
@@ -466,7 +481,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- UMMA issuer --------------------------------
-    if (lane == 0) {
+    // whole warp in the loop, elect.sync for the issuing lane (see the producer)
+    {
       constexpr uint32_t idesc =
           (KIND == 0) ? make_idesc(1, UMMA_BF16, UMMA_BF16, A_MN ? 1u : 0u, B_MN ? 1u : 0u, BM, BN)
                       : make_idesc(1, UMMA_E4M3, UMMA_E4M3, 0u, 0u, BM, BN);
@@ -475,14 +491,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       int it = 0;
       bool ok = true;
       long long t_full = 0, t_tempty = 0;
+      int n_trace = 0;
       const long long t_begin = p.prof ? clock64() : 0;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++it) {
         const int item_kb = splits > 1 ? kb_hi_of(item) - kb_lo_of(item) : total_kb;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         const long long te0 = p.prof ? clock64() : 0;
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, &abort_s)) {
-          report_status(p.status, STATUS_TIMEOUT, 2, acc);
+        if (!__all_sync(0xffffffffu, mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, &abort_s))) {
+          if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 2, acc);
           break;
         }
         if (p.prof) t_tempty += clock64() - te0;
@@ -490,36 +507,40 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < item_kb; ++kb) {
           const long long tf0 = p.prof ? clock64() : 0;
-          if (!mbar_wait(&full_bar[stage], phase, &abort_s)) {
-            report_status(p.status, STATUS_TIMEOUT, 3, stage);
+          if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, &abort_s))) {
+            if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 3, stage);
             ok = false;
             break;
           }
           if (p.prof) t_full += clock64() - tf0;
+          if (p.trace && lane == 0 && blockIdx.x < 2 && n_trace < p.trace_len) p.trace[(blockIdx.x * 3 + 1) * p.trace_len + n_trace++] = clock64();
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
           const uint64_t da = A_MN ? make_desc_mnmajor_sw128(sa, 8192) : make_desc_kmajor_sw128(sa);
           const uint64_t db = B_MN ? make_desc_mnmajor_sw128(sb, 8192) : make_desc_kmajor_sw128(sb);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < KSTEPS; ++k) {
-            // K-major: 32 bytes along the row per step; MN-major: 16 K-rows of 128 B per step
-            const uint64_t a_k = da + static_cast<uint64_t>(A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
-            const uint64_t b_k = db + static_cast<uint64_t>(B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
-            if (KIND == 0)
-              umma_f16_ss(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
-            else
-              umma_f8_ss(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < KSTEPS; ++k) {
+              // K-major: 32 bytes along the row per step; MN-major: 16 K-rows of 128 B per step
+              const uint64_t a_k = da + static_cast<uint64_t>(A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+              const uint64_t b_k = db + static_cast<uint64_t>(B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+              if (KIND == 0)
+                umma_f16_ss(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+              else
+                umma_f8_ss(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[stage]);  // smem slot free once these UMMAs have read it
+            if (kb == item_kb - 1) umma_commit(&tfull_bar[acc]);
           }
-          umma_commit(&empty_bar[stage]);  // smem slot free once these UMMAs have read it
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(&tfull_bar[acc]);
       }
-      if (p.prof) {
+      if (p.prof && lane == 0) {
         p.prof[blockIdx.x * 8 + 0] = clock64() - t_begin;
         p.prof[blockIdx.x * 8 + 2] = t_full;
         p.prof[blockIdx.x * 8 + 3] = t_tempty;
@@ -612,6 +633,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       tc_fence_after();
       const long long tq1 = p.prof ? clock64() : 0;
       t_twait += tq1 - tq0;
+      if (p.trace && blockIdx.x < 2 && warp == 2 && lane == 0 && 2 * it + 1 < p.trace_len) p.trace[(blockIdx.x * 3 + 2) * p.trace_len + 2 * it] = clock64();
       int row = m0 + quad * 32 + lane;
       if (p.conv_taps > 0) {
         const int mt = tile % tiles_m;
@@ -635,6 +657,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (p.prof) t_work += clock64() - tq1;
+      if (p.trace && blockIdx.x < 2 && warp == 2 && lane == 0 && 2 * it + 1 < p.trace_len) p.trace[(blockIdx.x * 3 + 2) * p.trace_len + 2 * it + 1] = clock64();
     }
     if (p.prof && warp == 2 && lane == 0) {
       p.prof[blockIdx.x * 8 + 4] = t_twait;
@@ -727,12 +750,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) -------------------
-    if (lane == 0) {
+    // whole warp in the loop, elect.sync for the issuing lane (see the one-CTA kernel)
+    {
       int stage = 0;
       uint32_t phase = 0;
       int last_stage = -1;
       bool ok = true;
       long long t_wait = 0;
+      int n_trace = 0;
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
         const int m0 = (tile % tiles_m) * (2 * BM) + static_cast<int>(rank) * BM;
         const int nblk = tile / tiles_m;
@@ -741,30 +766,36 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
         for (int s = 0; ok && s < p.num_seg; ++s) {
           for (int kb = 0; kb < p.kblocks[s]; ++kb) {
             const long long tw0 = p.prof ? clock64() : 0;
-            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s)) {
-              report_status(p.status, STATUS_TIMEOUT, 21, stage);
-              st_shared_cluster_u32(peer_abort, 1u);
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_s))) {
+              if (lane == 0) {
+                report_status(p.status, STATUS_TIMEOUT, 21, stage);
+                st_shared_cluster_u32(peer_abort, 1u);
+              }
               ok = false;
               break;
             }
             if (p.prof) t_wait += clock64() - tw0;
+            if (p.trace && lane == 0 && blockIdx.x < 2 && n_trace < p.trace_len) p.trace[(blockIdx.x * 3 + 0) * p.trace_len + n_trace++] = clock64();
             uint8_t* sa = smem + stage * STAGE_BYTES;
             uint8_t* sb = sa + A_BYTES;
             const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0u);
-            if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
             const int k0 = kb * K_ELEMS;
-            if (!A_MN) {
-              tma_load_2d_pair(sa, &maps.a[s], bar, k0, m0);
-            } else {
-              tma_load_2d_pair(sa, &maps.a[s], bar, m0, k0);
-              tma_load_2d_pair(sa + 8192, &maps.a[s], bar, m0 + 64, k0);
+            if (elect_one()) {
+              if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+              if (!A_MN) {
+                tma_load_2d_pair(sa, &maps.a[s], bar, k0, m0);
+              } else {
+                tma_load_2d_pair(sa, &maps.a[s], bar, m0, k0);
+                tma_load_2d_pair(sa + 8192, &maps.a[s], bar, m0 + 64, k0);
+              }
+              if (!B_MN) {
+                tma_load_2d_pair(sb, &maps.b[s], bar, k0, n0);
+              } else {
+                tma_load_2d_pair(sb, &maps.b[s], bar, n0, k0);
+                tma_load_2d_pair(sb + 8192, &maps.b[s], bar, n0 + 64, k0);
+              }
             }
-            if (!B_MN) {
-              tma_load_2d_pair(sb, &maps.b[s], bar, k0, n0);
-            } else {
-              tma_load_2d_pair(sb, &maps.b[s], bar, n0, k0);
-              tma_load_2d_pair(sb + 8192, &maps.b[s], bar, n0 + 64, k0);
-            }
+            __syncwarp();
             last_stage = stage;
             if (++stage == STAGES) {
               stage = 0;
@@ -773,7 +804,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
           }
         }
       }
-      if (p.prof) p.prof[blockIdx.x * 8 + 1] = t_wait;
+      if (p.prof && lane == 0) p.prof[blockIdx.x * 8 + 1] = t_wait;
       if (!ok && last_stage >= 0) {
         // abandoned: give the copies already in flight time to land before the CTA goes away (bounded)
         const uint64_t t0 = globaltimer_ns();
@@ -784,21 +815,24 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- UMMA issuer (leader CTA only) --------------
-    if (leader && lane == 0) {
+    if (leader) {
       constexpr uint32_t idesc = make_idesc(1, UMMA_BF16, UMMA_BF16, A_MN ? 1u : 0u, B_MN ? 1u : 0u, 2 * BM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
       long long t_full = 0, t_tempty = 0;
+      int n_trace = 0;
       const long long t_begin = p.prof ? clock64() : 0;
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         const long long te0 = p.prof ? clock64() : 0;
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, &abort_s)) {
-          report_status(p.status, STATUS_TIMEOUT, 22, acc);
-          st_shared_cluster_u32(peer_abort, 1u);
+        if (!__all_sync(0xffffffffu, mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, &abort_s))) {
+          if (lane == 0) {
+            report_status(p.status, STATUS_TIMEOUT, 22, acc);
+            st_shared_cluster_u32(peer_abort, 1u);
+          }
           break;
         }
         if (p.prof) t_tempty += clock64() - te0;
@@ -806,33 +840,39 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < total_kb; ++kb) {
           const long long tf0 = p.prof ? clock64() : 0;
-          if (!mbar_wait(&full_bar[stage], phase, &abort_s)) {
-            report_status(p.status, STATUS_TIMEOUT, 23, stage);
-            st_shared_cluster_u32(peer_abort, 1u);
+          if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, &abort_s))) {
+            if (lane == 0) {
+              report_status(p.status, STATUS_TIMEOUT, 23, stage);
+              st_shared_cluster_u32(peer_abort, 1u);
+            }
             ok = false;
             break;
           }
           if (p.prof) t_full += clock64() - tf0;
+          if (p.trace && lane == 0 && blockIdx.x < 2 && n_trace < p.trace_len) p.trace[(blockIdx.x * 3 + 1) * p.trace_len + n_trace++] = clock64();
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
           const uint64_t da = A_MN ? make_desc_mnmajor_sw128(sa, 8192) : make_desc_kmajor_sw128(sa);
           const uint64_t db = B_MN ? make_desc_mnmajor_sw128(sb, 8192) : make_desc_kmajor_sw128(sb);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < KSTEPS; ++k) {
-            const uint64_t a_k = da + static_cast<uint64_t>(A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
-            const uint64_t b_k = db + static_cast<uint64_t>(B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
-            umma_f16_ss_pair(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < KSTEPS; ++k) {
+              const uint64_t a_k = da + static_cast<uint64_t>(A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+              const uint64_t b_k = db + static_cast<uint64_t>(B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+              umma_f16_ss_pair(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit_pair(&empty_bar[stage], 3);   // the stage is free in both CTAs once these MMAs have read it
+            if (kb == total_kb - 1) umma_commit_pair(&tfull_bar[acc], 3);
           }
-          umma_commit_pair(&empty_bar[stage], 3);   // the stage is free in both CTAs once these MMAs have read it
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit_pair(&tfull_bar[acc], 3);
       }
-      if (p.prof) {
+      if (p.prof && lane == 0) {
         p.prof[blockIdx.x * 8 + 0] = clock64() - t_begin;
         p.prof[blockIdx.x * 8 + 2] = t_full;
         p.prof[blockIdx.x * 8 + 3] = t_tempty;
@@ -869,6 +909,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
       tc_fence_after();
       const long long tq1 = p.prof ? clock64() : 0;
       t_twait += tq1 - tq0;
+      if (p.trace && blockIdx.x < 2 && warp == 2 && lane == 0 && 2 * it + 1 < p.trace_len) p.trace[(blockIdx.x * 3 + 2) * p.trace_len + 2 * it] = clock64();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const int out_cols = paired ? BNH : BN;
@@ -884,6 +925,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0u));
       if (p.prof) t_work += clock64() - tq1;
+      if (p.trace && blockIdx.x < 2 && warp == 2 && lane == 0 && 2 * it + 1 < p.trace_len) p.trace[(blockIdx.x * 3 + 2) * p.trace_len + 2 * it + 1] = clock64();
     }
     if (p.prof && warp == 2 && lane == 0) {
       p.prof[blockIdx.x * 8 + 4] = t_twait;
@@ -1153,6 +1195,8 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   p.accumulate_out = a->accumulate_out;
   p.status = a->status;
   p.prof = a->prof;
+  p.trace = a->trace;
+  p.trace_len = a->trace_len;
   for (int i = 0; i < MDB_GEMM_MAX_PEERS; ++i) p.route_out[i] = a->route_out[i];
   for (int i = 0; i < MDB_GEMM_MAX_PEERS; ++i) p.gather_src[i] = a->gather_src[i];
   p.gather_dst = a->gather_dst;
@@ -1229,3 +1273,5 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   MDB_LAUNCH(64, 8, true, false, 0);
 #undef MDB_LAUNCH
 }
+
+MDB_DEFINE_WAIT_LIMIT_SETTER(mdb_set_wait_limit_gemm)
