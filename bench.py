@@ -10,10 +10,12 @@ barrier + synchronize; the reported time is the max over ranks. Inputs are synth
 shapes and the weights are random-init from seed 0 (no datasets or checkpoints exist offline). Each step streams
 24 GB of weights, far more than the 126 MB L2, so no explicit L2 flush is needed between iterations.
 
-On N > 1 GPUs the headline value is throughput under weak scaling: every GPU denoises its own sample (global batch N),
-iterations per second summed over the GPUs. The same run also times ONE sample sharded over the N GPUs (Ulysses sequence
-parallel with the all-to-alls fused into the QKV GEMM and attention epilogues) and reports it as ``strong_scaling_sp``;
-LoRA training is data parallel with the gradient reduce-scatter, AdamW and parameter all-gather in one peer-memory pass.
+On N > 1 GPUs the headline value is throughput under weak scaling with every step crossing NVLink: a global batch of N
+samples, each sample's tokens sharded over the N ranks (Ulysses sequence parallel, the all-to-alls fused into the QKV GEMM
+and attention epilogues), so that every GPU does the work of one sample per step (N x S/N token rows in the linears, N
+samples x H/N heads in attention). The same run also reports N independent replicas (one sample per GPU, no collective:
+``replicas_no_comm``) and ONE sample sharded over the N GPUs (``strong_scaling_sp``). LoRA training is data parallel with
+the gradient reduce-scatter, AdamW and parameter all-gather in one peer-memory pass.
 """
 from __future__ import annotations
 
@@ -148,10 +150,10 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ids = MMDiT.make_ids(hw[0], hw[1], S_txt, dev)
 
-    def measure(sp, seed, shard, with_e2e):
+    def measure(sp, seed, shard, with_e2e, B=B):
         """Times K denoise steps (device events, max over ranks) and, optionally, K steps through the public API with the
         step's inputs coming from pinned host memory and its result read back. ``shard``: this rank holds 1/world of the
-        tokens of ONE shared sample (sequence parallel); otherwise every rank denoises its own sample."""
+        tokens of each of the B shared samples (sequence parallel); otherwise every rank denoises its own B samples."""
         pipe = FluxPipeline(model, dev, sp=sp, use_cuda_graph=not args.no_graph)
         g = torch.Generator().manual_seed(seed)
         x_full = torch.randn(B, S_img, cfg.in_channels, generator=g)
@@ -228,13 +230,30 @@ def main():
         return res
 
     # ------------------------------------------------------------------ denoise loop
-    # N = 1: one sample on one GPU. N > 1, headline (weak scaling): every GPU denoises its own sample, global batch = N x B.
-    # N > 1, also reported (strong scaling): ONE sample, its tokens sharded over the ranks (Ulysses sequence parallel,
-    # all-to-alls fused into the QKV GEMM and attention epilogues).
+    # N = 1: one sample on one GPU. N > 1, headline (weak scaling): global batch N x B, every sample's tokens sharded over the
+    # N ranks (Ulysses sequence parallel, all-to-alls fused into the QKV GEMM and attention epilogues): per-GPU work equals
+    # the one-GPU run and every attention layer crosses NVLink twice. Also reported: N replicas without communication, and
+    # (strong scaling) ONE sample sharded over the ranks.
     do_denoise = not (lib_baseline and world > 1)
-    ms = it_per_s = clocks = launches_per_step = e2e = strong = None
+    ms = it_per_s = clocks = launches_per_step = e2e = strong = replicas = None
     n_launch = 0
-    if do_denoise:
+    headline_sp = do_denoise and world > 1 and not lib_baseline
+    if headline_sp:
+        from mojodiffusion_b200.parallel.ulysses import UlyssesContext
+        GB = B * world
+        sp_w = UlyssesContext(GB, S_txt, S_img, cfg.heads, cfg.head_dim, mode=args.sp_mode, device=dev)
+        head = measure(sp_w, 1234, True, not args.no_e2e, B=GB)
+        ms, clocks, launches_per_step, n_launch, e2e = head["ms"], head["clocks"], head["launches_per_step"], head["n_launch"], head["e2e"]
+        it_per_s = GB * 1000.0 / ms
+        del sp_w
+        torch.cuda.empty_cache()
+        try:
+            rep = measure(None, 1234 + rank, False, False)
+            replicas = {"what": "one independent sample per GPU, no communication inside the step", "value": world * B * 1000.0 / rep["ms"],
+                        "unit": "it/s", "ms_per_step": rep["ms"]}
+        except Exception as ex:
+            replicas = {"error": str(ex)[:300]}
+    elif do_denoise:
         head = measure(None, 1234 + rank, False, not args.no_e2e)
         ms, clocks, launches_per_step, n_launch, e2e = head["ms"], head["clocks"], head["launches_per_step"], head["n_launch"], head["e2e"]
         it_per_s = world * B * 1000.0 / ms
@@ -335,7 +354,7 @@ def main():
                     mod.slots = torch.nn.ModuleList()
             torch.cuda.empty_cache()
             sp = UlyssesContext(B, S_txt, S_img, cfg.heads, cfg.head_dim, mode=args.sp_mode, device=dev)
-            st = measure(sp, 1234, True, not args.no_e2e)
+            st = measure(sp, 1234, True, False)
             strong = {"what": "one sample sharded over the ranks (Ulysses sequence parallel, all-to-all " + args.sp_mode + ")",
                       "value": B * 1000.0 / st["ms"], "unit": "it/s", "ms_per_step": st["ms"], "scaling": "strong",
                       "launches_per_step": st["launches_per_step"], "e2e": st["e2e"]}
@@ -351,12 +370,15 @@ def main():
             "config": {"model": f"{cfg.name} 12B MMDiT (19 double + 38 single, D=3072, 24x128)" if args.model == "flux1-dev" else cfg.name,
                        "global_batch": B * world, "seq_len": S_img + S_txt, "image_tokens": S_img, "text_tokens": S_txt,
                        "sampler": "euler flow-match, 28-step BFL-shifted schedule, guidance 3.5 (distilled)",
-                       "parallelism": (f"dp{world} (one sample per GPU); single-sample latency with sp{world} in 'strong_scaling_sp'"
-                                       if world > 1 else "single"),
+                       "parallelism": (f"ulysses sp{world}: global batch {B * world}, every sample's tokens sharded over the {world} GPUs, "
+                                       f"all-to-all ({args.sp_mode}) inside the QKV GEMM and attention epilogues; replicas without "
+                                       "communication in 'replicas_no_comm', one sample over all GPUs in 'strong_scaling_sp'"
+                                       if headline_sp else (f"dp{world} replicas" if world > 1 else "single")),
                        "cuda_graph": not args.no_graph, "launches_per_step": launches_per_step,
                        "weights": "random-init seed 0",
                        "l2": "inputs larger than L2: 24 GB of weights stream every step"},
-            "clocks": clocks, "gpu_launches": n_launch, "e2e": e2e, "strong_scaling_sp": strong, "lora_train": train,
+            "clocks": clocks, "gpu_launches": n_launch, "e2e": e2e, "replicas_no_comm": replicas, "strong_scaling_sp": strong,
+            "lora_train": train,
             "published_nearest": PUBLISHED_NEAREST,
             "vs_published_nearest": it_per_s / PUBLISHED_NEAREST["it_per_s"] if it_per_s else None,
         }

@@ -68,7 +68,7 @@ def main():
         w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
         print("CTA pairs the device holds at once:", torch.ops.mdb200.gemm_pair_capacity())
         names = ["mma_total", "producer_wait_empty", "mma_wait_full", "mma_wait_tmem_empty", "epi_wait_tmem_full", "epi_work", "tiles", "-"]
-        for bn in (256, 512, 513):
+        for bn in (256, 512):
             for _ in range(2):
                 _gemm([x], [w], bn=bn)
             prof = torch.zeros(148, 8, dtype=torch.int64, device=dev)

@@ -603,7 +603,7 @@ void adamw_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems,
   check_rc(mdb_adamw_multi((const MdbTensorEntry*)table.data_ptr(), chunks.data_ptr<int>(), (int)chunks.size(0),
                            (int)chunk_elems, p_bf16, g_bf16, m_bf16, (float)lr, (float)beta1, (float)beta2, (float)eps,
                            (float)wd, (int)step, (float)grad_scale, (const float*)opt_ptr(norm_sq), (float)max_norm,
-                           (unsigned int)seed, stochastic, cur_stream()),
+                           (unsigned int)seed, stochastic, status_ptr(table), cur_stream()),
            "adamw_multi");
 }
 Tensor sumsq_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, bool g_bf16) {

@@ -179,8 +179,12 @@ __device__ __noinline__ void epilogue_row32_slow(const GemmParams& p, int row, i
 }
 
 // One 32-column slab of one output row. r[] holds the raw accumulators (r2[] the paired half).
+// stage_row (optional): this lane's 256-byte row of the warp's shared-memory staging buffer; the packed bf16 slab then
+// goes there (16-byte chunks stage_chunk0 .. +3, XOR-swizzled by the lane so that neither the row-wise writes nor the
+// later chunk-wise reads conflict) instead of to global memory.
 __device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
-                                               const uint32_t (&r2)[32], bool paired, bool aligned) {
+                                               const uint32_t (&r2)[32], bool paired, bool aligned,
+                                               uint4* stage_row = nullptr, int stage_chunk0 = 0, int swz = 0) {
   if (row >= p.M || col0 >= p.N) return;
   const int ncols = min(32, p.N - col0);
   if (ncols < 32 || !aligned) {
@@ -263,7 +267,7 @@ __device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int
       for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
   } else {
-    uint4* o = reinterpret_cast<uint4*>(out_slab_ptr(p, row, col0, 2));
+    uint4* o = stage_row ? stage_row : reinterpret_cast<uint4*>(out_slab_ptr(p, row, col0, 2));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       uint4 t;
@@ -271,8 +275,53 @@ __device__ __forceinline__ void epilogue_row32(const GemmParams& p, int row, int
       t.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
       t.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
       t.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
-      o[j] = t;
+      o[stage_row ? ((stage_chunk0 + j) ^ swz) : j] = t;
     }
+  }
+}
+
+// Epilogue of one accumulator tile for one warp (its 32 TMEM lanes = 32 output rows). bf16 outputs whose tile lies fully
+// inside the matrix go through an 8 KB per-warp staging buffer in shared memory, 128 columns at a time: every lane packs
+// its row's slabs into the buffer, then the warp stores whole 256-byte row segments (16 lanes x 16 bytes per row, two
+// rows per instruction). Local stores become full cache lines and peer-routed stores (sequence-parallel scatter, staged
+// reduce-scatter) cross NVLink as 256-byte writes instead of 64-byte fragments of 32 different rows. Everything else
+// (fp32 outputs, ragged edges, unaligned pointers) keeps the direct per-lane stores.
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, int pair_col_off, int row, int n0,
+                                              int out_cols, bool paired, bool aligned, uint8_t* stage_warp, int lane) {
+  const bool staged = stage_warp != nullptr && aligned && !p.out_fp32 && (out_cols & 127) == 0 && n0 + out_cols <= p.N;
+  if (!staged) {
+#pragma unroll 1
+    for (int c = 0; c < out_cols / 32; ++c) {
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(taddr + c * 32, r0);
+      if (paired) tmem_ld_32x32b_x32(taddr + pair_col_off + c * 32, r1);
+      tmem_wait_ld();
+      epilogue_row32(p, row, n0 + c * 32, r0, r1, paired, aligned);
+    }
+    return;
+  }
+  uint4* my_row = reinterpret_cast<uint4*>(stage_warp + lane * 256);
+  const int swz = lane & 15;
+#pragma unroll 1
+  for (int g = 0; g < out_cols / 128; ++g) {
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(taddr + g * 128 + c * 32, r0);
+      if (paired) tmem_ld_32x32b_x32(taddr + pair_col_off + g * 128 + c * 32, r1);
+      tmem_wait_ld();
+      epilogue_row32(p, row, n0 + g * 128 + c * 32, r0, r1, paired, true, my_row, c * 4, swz);
+    }
+    __syncwarp();
+    const int chunk = lane & 15;
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      const int rl = 2 * i + (lane >> 4);                       // row of the warp this lane copies in this round
+      const int rr = __shfl_sync(0xffffffffu, row, rl);         // its global output row (p.M or more: not stored)
+      const uint4 v = reinterpret_cast<const uint4*>(stage_warp + rl * 256)[chunk ^ (rl & 15)];
+      if (rr < p.M) *reinterpret_cast<uint4*>(out_slab_ptr(p, rr, n0 + g * 128 + chunk * 8, 2)) = v;
+    }
+    __syncwarp();
   }
 }
 
@@ -645,14 +694,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const int out_cols = paired ? BN / 2 : BN;
-#pragma unroll 1
-      for (int c = 0; c < out_cols / 32; ++c) {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r0);
-        if (paired) tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, r1);
-        tmem_wait_ld();
-        epilogue_row32(p, row, n0 + c * 32, r0, r1, paired, aligned);
-      }
+      // the staging buffers share their 32 KB with the stages of the fused all-gather, which therefore stores directly
+      uint8_t* stage_warp = p.gather_world > 1 ? nullptr : smem + STAGES * STAGE_BYTES + quad * 8192;
+      epilogue_tile(p, taddr, BN / 2, row, n0, out_cols, paired, aligned, stage_warp, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -913,14 +957,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const int out_cols = paired ? BNH : BN;
-#pragma unroll 1
-      for (int c = 0; c < out_cols / 32; ++c) {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r0);
-        if (paired) tmem_ld_32x32b_x32(taddr + BNH + c * 32, r1);
-        tmem_wait_ld();
-        epilogue_row32(p, row, n0 + c * 32, r0, r1, paired, aligned);
-      }
+      epilogue_tile(p, taddr, BNH, row, n0, out_cols, paired, aligned, smem + STAGES * STAGE_BYTES + quad * 8192, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0u));
@@ -996,10 +1033,12 @@ namespace mdb {
 template <int BN, int STAGES, bool A_MN, bool B_MN, int KIND>
 static int launch_variant(const GemmMaps& maps, const GemmParams& p, int num_sms, cudaStream_t stream) {
   constexpr int STAGE_BYTES = BM * BK_BYTES + BN * BK_BYTES;
-  constexpr int SMEM_BASE = STAGES * STAGE_BYTES + 1024;
-  constexpr int SMEM_GATHER = SMEM_BASE + GATHER_STAGES * GATHER_PIECE;
-  static_assert(SMEM_GATHER <= 227 * 1024, "pipeline + gather stages exceed the shared memory of an SM");
-  const int SMEM = p.gather_world > 1 ? SMEM_GATHER : SMEM_BASE;
+  // operand ring + 32 KB that serve as the epilogue's staging buffers (4 warps x 8 KB) or, with a fused all-gather, as its
+  // two bulk-copy stages
+  constexpr int SMEM_GATHER = STAGES * STAGE_BYTES + 1024 + GATHER_STAGES * GATHER_PIECE;
+  static_assert(GATHER_STAGES * GATHER_PIECE == 4 * 8192, "staging buffers and gather stages share one region");
+  static_assert(SMEM_GATHER <= 227 * 1024, "pipeline + staging exceed the shared memory of an SM");
+  const int SMEM = SMEM_GATHER;
   auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, KIND>;
   static bool attr_done = false;
   if (!attr_done) {
@@ -1027,7 +1066,7 @@ __global__ void gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, 
 static int pair_capacity(int num_sms) {
   static int cached = 0;
   if (cached > 0) return cached;
-  constexpr int SMEM = 6 * (BM * BK_BYTES + 128 * BK_BYTES) + 1024;
+  constexpr int SMEM = 6 * (BM * BK_BYTES + 128 * BK_BYTES) + 4 * 8192 + 1024;
   auto kern = gemm_tcgen05_pair_kernel<6, false, false>;
   int n = 0;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) == cudaSuccess) {
@@ -1053,7 +1092,7 @@ static int pair_capacity(int num_sms) {
 
 template <int STAGES, bool A_MN, bool B_MN>
 static int launch_pair_variant(const GemmMaps& maps, const GemmParams& p, int num_sms, cudaStream_t stream) {
-  constexpr int SMEM = STAGES * (BM * BK_BYTES + 128 * BK_BYTES) + 1024;
+  constexpr int SMEM = STAGES * (BM * BK_BYTES + 128 * BK_BYTES) + 4 * 8192 + 1024;   // ring + epilogue staging (4 warps x 8 KB)
   static_assert(SMEM <= 227 * 1024, "pipeline exceeds the shared memory of an SM");
   auto kern = gemm_tcgen05_pair_kernel<STAGES, A_MN, B_MN>;
   static bool attr_done = false;
@@ -1096,9 +1135,8 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   int bn = a->bn;
   // bn == 512 asks for the CTA-pair kernel (256 x 256 tile over two SMs); it shares the tensor maps of the 128 x 256 tile
   const bool pair_ok = a->kind == 0 && a->conv_taps <= 0 && a->gather_world <= 1 && a->split_k <= 1;
-  bool use_pair = (bn == 512 || bn == 513) && pair_ok;
-  const bool pair_deep = bn == 513;          // 7-stage ring (measurement variant of the K-major kernel)
-  if (bn == 512 || bn == 513) bn = 256;
+  bool use_pair = bn == 512 && pair_ok;
+  if (bn == 512) bn = 256;
   const bool auto_tile = bn != 64 && bn != 128 && bn != 256;
   if (bn != 64 && bn != 128 && bn != 256) {
     // default tile choice: 128x256 unless the narrower 128x128 tile fills the machine noticeably better
@@ -1115,8 +1153,9 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   }
   if (paired && bn != 256) bn = 256;
   if (auto_tile && pair_ok && a->M > BM && pair_mode() != 0) {
-    // CTA pair (256 x 256 tile on two SMs) or lone CTAs? Compare waves x time per tile; a pair tile costs each SM the MMA
-    // time of a 128 x 256 tile but a third less shared-memory fill, measured as about 0.91 of its time on DiT shapes.
+    // CTA pair (256 x 256 tile on two SMs) or lone CTAs? Compare waves x time per tile. A lone CTA's 128 x 256 tile moves
+    // 96 KB through shared memory per K block (48 KB written by TMA, 48 KB read by the tensor core): 726 cycles measured,
+    // bound by the 128 B/clk of shared memory. A pair tile moves 64 KB per SM and runs at the tensor rate: 523 cycles.
     const int n_tile = paired ? 128 : 256;
     const long long t2 = static_cast<long long>((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + n_tile - 1) / n_tile);
     const int pairs = pair_capacity(sms);
@@ -1124,7 +1163,7 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
     const long long t1 = static_cast<long long>((a->M + BM - 1) / BM) * ((a->N + (paired ? 128 : bn) - 1) / (paired ? 128 : bn));
     const long long w1 = (t1 + sms - 1) / sms;
     const double cost1 = static_cast<double>(w1) * (bn == 256 ? 1.0 : bn == 128 ? 0.55 : 0.32);
-    const double cost2 = static_cast<double>(w2) * 0.91;
+    const double cost2 = static_cast<double>(w2) * 0.72;
     if (cost2 <= cost1) {
       use_pair = true;
       bn = 256;
@@ -1241,7 +1280,6 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
 
 #define MDB_LAUNCH(BN_, ST_, AMN_, BMN_, KIND_) return launch_variant<BN_, ST_, AMN_, BMN_, KIND_>(maps, p, sms, stream)
   if (use_pair) {
-    if (!a->a_mn && !a->b_mn && pair_deep) return launch_pair_variant<7, false, false>(maps, p, sms, stream);
     if (!a->a_mn && !a->b_mn) return launch_pair_variant<6, false, false>(maps, p, sms, stream);
     if (!a->a_mn && a->b_mn) return launch_pair_variant<6, false, true>(maps, p, sms, stream);
     if (a->a_mn && a->b_mn) return launch_pair_variant<6, true, true>(maps, p, sms, stream);

@@ -101,7 +101,7 @@ int mdb_group_norm_static_ws(const void* x, void* y, const void* w, const void* 
 int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
                     int g_bf16, int m_bf16, float lr, float beta1, float beta2, float eps, float wd, int step,
                     float grad_scale, const float* norm_sq, float max_norm, unsigned int seed, int stochastic,
-                    cudaStream_t st);
+                    const int* status, cudaStream_t st);   // status (may be NULL): device status word; not OK -> no update
 int mdb_sumsq_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int g_bf16,
                     float* out, cudaStream_t st);
 int mdb_ema_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,

@@ -47,6 +47,8 @@ struct AdamHyper {
   float max_norm;                                   // clip threshold (<=0: off)
   unsigned int seed;                                // stochastic rounding stream
   int stochastic;                                   // bf16 params only
+  const int* status;                                // optional device status word: not OK (a bounded wait of this step
+                                                    // ran out, gradients may be incomplete) -> nothing is updated
 };
 
 __device__ __forceinline__ float clip_coef(const AdamHyper& h) {
@@ -86,6 +88,7 @@ template <typename TP, typename TG, typename TM>
 __global__ void __launch_bounds__(256)
 adamw_multi_kernel(const MdbTensorEntry* __restrict__ tensors, const int2* __restrict__ chunks, int num_chunks,
                    int chunk_elems, AdamHyper h) {
+  if (h.status != nullptr && *reinterpret_cast<const volatile int*>(h.status) != STATUS_OK) return;
   const float gmul = h.grad_scale * clip_coef(h);
   for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
     const int2 ch = chunks[c];
@@ -157,9 +160,10 @@ typedef __nv_bfloat16 bf16;
 extern "C" int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems,
                                int p_bf16, int g_bf16, int m_bf16, float lr, float beta1, float beta2, float eps,
                                float wd, int step, float grad_scale, const float* norm_sq, float max_norm,
-                               unsigned int seed, int stochastic, cudaStream_t st) {
+                               unsigned int seed, int stochastic, const int* status, cudaStream_t st) {
   if (num_chunks <= 0) return 0;
   AdamHyper h;
+  h.status = status;
   h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.wd = wd;
   h.bc1 = 1.f - powf(beta1, (float)step);
   h.bc2_sqrt = sqrtf(1.f - powf(beta2, (float)step));

@@ -141,6 +141,14 @@ class FSDPContext:
             l.g_shard.zero_()
         self.gathered_owner = None
         self.barrier(SLOT_STEP_DONE)                      # new shards visible everywhere before the next gather
+        if self.step_count % getattr(self, "check_every", 16) == 0:
+            self.check()
+
+    def check(self) -> None:
+        """Raise if a bounded wait of the fused kernels ran out on this device since the last check (the AdamW launch of
+        such a step leaves the shards untouched). Synchronises the stream: called every ``check_every`` (16) steps by
+        ``step()`` and meant to be called before every save or backup."""
+        native.check_status(self.layers[0].master if self.layers else None)
 
 
 class _FSDPLinearFn(torch.autograd.Function):

@@ -37,7 +37,10 @@ class FusedDPAdamW:
 
     def __init__(self, params: Sequence[torch.nn.Parameter], lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
                  max_grad_norm: float = 0.0, group=None, symm: Optional[SymmetricBuffer] = None,
-                 use_multicast: bool = True):
+                 use_multicast: bool = True, check_every: int = 16):
+        """``check_every``: every that many steps ``step()`` reads the device status word (one small synchronising copy)
+        and raises if a bounded wait of the fused kernels ran out; a step after such a time-out leaves the parameters
+        untouched on the device. ``check()`` does the same on demand (call it before every save or backup)."""
         self.params = list(params)
         p0 = self.params[0]
         assert p0.is_cuda and all(p.dtype == torch.bfloat16 for p in self.params), "bf16 CUDA parameters"
@@ -73,6 +76,9 @@ class FusedDPAdamW:
         self.done_counter = torch.zeros((), dtype=torch.int32, device=dev)
         self.epoch = 0
         self.step_count = 0
+        self.check_every = max(1, int(check_every))
+        self.group = group
+        self._state_cache = None          # (step_count, m_full, v_full) from the last gather_state()
 
     def attach_grads(self):
         for p, o in zip(self.params, self.offsets):
@@ -118,25 +124,61 @@ class FusedDPAdamW:
         self.phase_publish()
         self.phase_update(lr)
         self.phase_finish()
+        if self.step_count % self.check_every == 0:
+            self.check()
+
+    def check(self) -> None:
+        """Raise if any bounded wait ran out on this device since the last check (synchronises the stream)."""
+        native.check_status(self.red)
 
     def grad_norm(self) -> float:
         return float(self.norm_out)
 
-    # ---- optimizer-state access for checkpoints (moments are sharded; gather on demand) ----------------
-    def gather_moments(self):
+    # ---- optimizer-state access for checkpoints (moments are sharded) ---------------------------------------
+    def gather_state(self):
+        """COLLECTIVE: every rank calls it, once, before the rank-0-only save branch. All-gathers the sharded moments
+        (two collectives in total) and caches the full vectors; ``moments(p)`` then slices the cache without communicating."""
+        self.check()
         if self.world == 1 or not dist.is_initialized():
-            return self.m.clone(), self.v.clone()
-        ms = [torch.empty_like(self.m) for _ in range(self.world)]
-        vs = [torch.empty_like(self.v) for _ in range(self.world)]
-        dist.all_gather(ms, self.m)
-        dist.all_gather(vs, self.v)
-        return torch.cat(ms), torch.cat(vs)
+            m, v = self.m.clone(), self.v.clone()
+        else:
+            m = torch.empty(self.total, dtype=torch.float32, device=self.m.device)
+            v = torch.empty_like(m)
+            dist.all_gather_into_tensor(m, self.m, group=self.group)
+            dist.all_gather_into_tensor(v, self.v, group=self.group)
+        self._state_cache = (self.step_count, m, v)
+        return m, v
 
     def moments(self, p):
+        """fp32 (m, v) of parameter ``p`` from the last ``gather_state()`` (which must belong to the current step when the
+        group has more than one rank: this call itself never communicates, so rank 0 may call it alone)."""
+        if self._state_cache is None or self._state_cache[0] != self.step_count:
+            if self.world > 1:
+                raise RuntimeError("FusedDPAdamW.moments: call gather_state() on every rank after the last step first")
+            self.gather_state()
+        _, m, v = self._state_cache
         i = [id(q) for q in self.params].index(id(p))
-        m, v = self.gather_moments()
         o = self.offsets[i]
         return m[o:o + p.numel()].view_as(p), v[o:o + p.numel()].view_as(p)
+
+    def set_moments(self, p, m, v) -> None:
+        """Restore the moments of one parameter: the part of it that falls into this rank's shard is written."""
+        i = [id(q) for q in self.params].index(id(p))
+        o = self.offsets[i]
+        lo, hi = max(o, self.lo), min(o + p.numel(), self.hi)
+        if hi > lo:
+            dev = self.m.device
+            self.m[lo - self.lo:hi - self.lo].copy_(m.reshape(-1)[lo - o:hi - o].to(dev, torch.float32))
+            self.v[lo - self.lo:hi - self.lo].copy_(v.reshape(-1)[lo - o:hi - o].to(dev, torch.float32))
+        self._state_cache = None
+
+    def load_state(self, m_full: torch.Tensor, v_full: torch.Tensor, step: int) -> None:
+        """Restore from full-length moment vectors (as returned by ``gather_state``) and the bias-correction step."""
+        dev = self.m.device
+        self.m.copy_(m_full[self.lo:self.hi].to(dev, torch.float32))
+        self.v.copy_(v_full[self.lo:self.hi].to(dev, torch.float32))
+        self.step_count = int(step)
+        self._state_cache = None
 
 
 def emulate_ranks(param_sets: List[Sequence[torch.nn.Parameter]], **kw) -> List[FusedDPAdamW]:

@@ -195,13 +195,22 @@ class TrainRun:
 
     ``step_fn(batch, lr) -> (loss, grad_norm)`` runs one optimizer step; ``named_trainables()`` returns
     {name: tensor} for checkpoints; ``optimizer_state()`` / ``load_optimizer_state(sd)`` expose the moments;
-    ``sample_fn(progress, leaf) -> [png paths]`` is optional."""
+    ``sample_fn(progress, leaf) -> [png paths]`` is optional.
+
+    Multi-rank runs: sampling, backups and saves happen on the main rank only, between steps. ``pre_save_fn`` (optional) is
+    called by EVERY rank right before such a branch (gather sharded optimizer state there: collectives inside the
+    main-only branch would never be joined); ``barrier_fn`` (optional) is called by every rank right after it, so that the
+    other ranks do not enqueue the next step's device-side waits while rank 0 is still writing files; ``agree_fn(bits) ->
+    bits`` (optional) replaces this rank's cadence decision by the main rank's (time-based units differ between ranks).
+    ``loss_sync_every``: the loss is read back (a host sync) only every that many steps; 1 keeps a full loss history."""
 
     def __init__(self, cfg: TrainConfig, loader, step_fn: Callable, named_trainables: Callable[[], Dict[str, torch.Tensor]],
                  optimizer_state: Callable[[], Dict[str, torch.Tensor]], load_trainables: Callable, load_optimizer_state: Callable,
                  sample_fn: Optional[Callable] = None, ema: Optional[EMA] = None, board: Optional[BoardWriter] = None,
                  timestamp: Optional[str] = None, prefix: str = "", backup_after: int = 0, backup_after_unit: str = "NEVER",
-                 display: bool = True, stream=None, is_main: bool = True):
+                 display: bool = True, stream=None, is_main: bool = True, pre_save_fn: Optional[Callable] = None,
+                 barrier_fn: Optional[Callable] = None, agree_fn: Optional[Callable] = None, loss_sync_every: int = 1,
+                 status_check_fn: Optional[Callable] = None):
         self.cfg, self.loader, self.step_fn = cfg, loader, step_fn
         self.named_trainables, self.optimizer_state = named_trainables, optimizer_state
         self.load_trainables, self.load_optimizer_state = load_trainables, load_optimizer_state
@@ -215,6 +224,35 @@ class TrainRun:
         self.stream = stream
         self.losses: List[float] = []
         self.saved: List[str] = []
+        self.pre_save_fn, self.barrier_fn, self.agree_fn = pre_save_fn, barrier_fn, agree_fn
+        self.loss_sync_every = max(1, int(loss_sync_every))
+        self.status_check_fn = status_check_fn
+
+    def _decide(self, p: TrainProgress) -> ActionDecisions:
+        d = self.cadence.decide(p)
+        if self.agree_fn is not None:
+            bits = self.agree_fn((int(d.sample) << 2) | (int(d.backup) << 1) | int(d.save))
+            d = ActionDecisions(bool(bits & 4), bool(bits & 2), bool(bits & 1))
+        return d
+
+    def _act(self, d: ActionDecisions) -> None:
+        """Cadence actions of one decision point (every rank calls this; files are written by the main rank)."""
+        if not (d.sample or d.backup or d.save):
+            return
+        if self.status_check_fn is not None:
+            self.status_check_fn()                       # a step whose device waits ran out must not be saved
+        if (d.backup or d.save) and self.pre_save_fn is not None:
+            self.pre_save_fn()
+        p = self.progress
+        if self.is_main:
+            if d.sample and self.sample_fn:
+                self.sample_fn(p, training_sample_leaf(self.prefix, self.timestamp, p))
+            if d.backup:
+                self._backup()
+            if d.save:
+                self._save()
+        if self.barrier_fn is not None:
+            self.barrier_fn()
 
     def resume_if_requested(self) -> bool:
         if not self.cfg.continue_last_backup:
@@ -259,26 +297,25 @@ class TrainRun:
                 p.next_step(cfg.batch_size)
                 if self.ema is not None and p.global_step % max(1, cfg.ema_update_step_interval) == 0:
                     self.ema.update(p.global_step)
-                loss_f = float(loss)
-                self.losses.append(loss_f)
-                if disp:
-                    disp.update(p.global_step, p.epoch + 1, loss_f, float(gnorm))
-                if self.board and self.is_main:
-                    self.board.log_train_step(p.global_step, loss_f, float(gnorm), lr, time.monotonic() - t0)
-                d = self.cadence.decide(p)
-                if self.is_main:
-                    if d.sample and self.sample_fn:
-                        self.sample_fn(p, training_sample_leaf(self.prefix, self.timestamp, p))
-                    if d.backup:
-                        self._backup()
-                    if d.save:
-                        self._save()
+                if p.global_step % self.loss_sync_every == 0 or p.global_step >= total:
+                    loss_f = float(loss)                 # the only host sync of the step
+                    self.losses.append(loss_f)
+                    if disp:
+                        disp.update(p.global_step, p.epoch + 1, loss_f, float(gnorm))
+                    if self.board and self.is_main:
+                        self.board.log_train_step(p.global_step, loss_f, float(gnorm), lr, time.monotonic() - t0)
+                self._act(self._decide(p))
             else:
                 p.next_epoch()
+                self._act(self._decide(p))               # EPOCH-unit cadences fire here (epoch_step == 0)
                 continue
             break
         if disp:
             disp.finish()
+        if self.status_check_fn is not None:
+            self.status_check_fn()
+        if self.pre_save_fn is not None:
+            self.pre_save_fn()
         if self.is_main:
             self._backup()
             final = cfg.output_model_destination
@@ -287,4 +324,6 @@ class TrainRun:
                 os.makedirs(os.path.dirname(dst) or ".", exist_ok=True)
                 save_safetensors(dst, self.named_trainables(), {"global_step": str(p.global_step)})
                 self.saved.append(dst)
+        if self.barrier_fn is not None:
+            self.barrier_fn()
         return p

@@ -24,6 +24,14 @@ class StepConfig:
     timestep_shift: float = 1.0
     guidance: float = 1.0
     seed: int = 0
+    rank: int = 0                 # data-parallel rank and world size: every rank draws its own sigmas and noise
+    world: int = 1                # (seed * world + rank); set rank_identical_draws for the DP-N == batch-N parity tests
+    rank_identical_draws: bool = False
+
+    def stream_seed(self) -> int:
+        if self.rank_identical_draws or self.world <= 1:
+            return self.seed
+        return self.seed * self.world + self.rank
 
 
 class FlowMatchTrainer:
@@ -42,7 +50,8 @@ class FlowMatchTrainer:
         self.dp = dp
         self.cfg = cfg or StepConfig()
         self.step_index = 0
-        self._gen = torch.Generator().manual_seed(self.cfg.seed)
+        self._seed = self.cfg.stream_seed()
+        self._gen = torch.Generator().manual_seed(self._seed)
 
     def zero_grad(self):
         if self.dp is not None:
@@ -59,7 +68,7 @@ class FlowMatchTrainer:
         if sigma is None:
             sigma = sample_sigmas(B, self._gen, self.cfg.timestep_kind, self.cfg.timestep_shift).to(dev)
         if noise is None:
-            noise = ops.randn(tuple(x0.shape), seed=self.cfg.seed * 7919 + self.step_index, device=dev)
+            noise = ops.randn(tuple(x0.shape), seed=self._seed * 7919 + self.step_index, device=dev)
         xt, target = ops.flow_match(x0.float(), noise.float(), sigma.float())
         dt = next(self.model.parameters()).dtype
         guidance = torch.full((B,), self.cfg.guidance, device=dev) if self.model.cfg.guidance_embed else None
@@ -74,7 +83,7 @@ class FlowMatchTrainer:
         if sigma is None:
             sigma = sample_sigmas(B, self._gen, self.cfg.timestep_kind, self.cfg.timestep_shift).to(dev)
         if noise is None:
-            noise = ops.randn(tuple(x0.shape), seed=self.cfg.seed * 7919 + self.step_index, device=dev)
+            noise = ops.randn(tuple(x0.shape), seed=self._seed * 7919 + self.step_index, device=dev)
         inputs = [x0.float(), txt, y, sigma.float(), noise.float()]
         key = (tuple(x0.shape), tuple(txt.shape), tuple(y.shape), hw)
         if self._graphed is None or self._graph_key != key:

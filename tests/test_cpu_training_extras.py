@@ -415,3 +415,37 @@ def test_lora_key_schemes_of_the_other_families(tmp_path):
     vs = L.inject_ltx2_lora(vm, rank=4)
     assert len(vs) == 10 * len(vm.transformer_blocks)
     assert vs[0].key == "diffusion_model.transformer_blocks.0.attn1.to_q" and vs[9].key == "diffusion_model.transformer_blocks.0.ff.net.2"
+
+
+def test_epoch_unit_cadence_fires_at_epoch_boundaries(tmp_path):
+    """save_every = 1 EPOCH over two short epochs writes one file per finished epoch (the decision is taken right after
+    the epoch counter advances, where epoch_step == 0), and the hooks around rank-0-only actions are called."""
+    import torch
+    from mojodiffusion_b200.io.config import TrainConfig
+    from mojodiffusion_b200.training.loop import TrainRun
+
+    class Loader:
+        def steps_per_epoch(self):
+            return 3
+
+        def epoch(self, epoch, skip=0):
+            for i in range(skip, 3):
+                yield i
+
+    cfg = TrainConfig()
+    cfg.workspace_dir = str(tmp_path)
+    cfg.save_every, cfg.save_every_unit = 1, "EPOCH"
+    cfg.sample_after_unit, cfg.sample_every, cfg.sample_after = "NEVER", 0, 0
+    cfg.output_model_destination = ""
+    w = {"a": torch.zeros(2)}
+    calls = {"pre": 0, "bar": 0}
+    run = TrainRun(cfg, Loader(), lambda b, lr: (torch.tensor(1.0), torch.tensor(0.5)), lambda: w, lambda: {"m": torch.zeros(2)},
+                   lambda sd: None, lambda sd: None, display=False,
+                   pre_save_fn=lambda: calls.__setitem__("pre", calls["pre"] + 1),
+                   barrier_fn=lambda: calls.__setitem__("bar", calls["bar"] + 1), loss_sync_every=2)
+    p = run.run(max_steps=6)
+    assert p.global_step == 6 and p.epoch == 2
+    names = sorted(os.path.basename(s) for s in run.saved)
+    assert len(names) == 2 and names[0].endswith("-save-3-1-0.safetensors") and names[1].endswith("-save-6-2-0.safetensors"), names
+    assert calls["pre"] == 3 and calls["bar"] == 3          # two epoch saves + the final backup
+    assert len(run.losses) == 3                              # read back every second step only

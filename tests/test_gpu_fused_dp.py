@@ -127,3 +127,93 @@ def test_real_ranks_match_nccl_baseline(tmp_path):
     world = min(torch.cuda.device_count(), 4)
     mp.spawn(_mp_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert (tmp_path / "ok").exists()
+
+
+def _emulated(world, shapes, base, **kw):
+    from mojodiffusion_b200.parallel.fused_dp import emulate_ranks
+    sets = [[torch.nn.Parameter(b.clone().to("cuda")) for b in base] for _ in range(world)]
+    return sets, emulate_ranks(sets, **kw)
+
+
+def _load_grads(ranks, sets, grads_t):
+    for r, rk in enumerate(ranks):
+        rk.zero_grad()
+        for p, gg in zip(sets[r], grads_t[r]):
+            p.grad.copy_(gg.to("cuda"))
+
+
+def test_optimizer_state_round_trip_gives_identical_next_step():
+    """Save (full moments + step), load into fresh ranks, take one more step: parameters are bit-identical to the run that
+    never stopped. Also checks set_moments (per-parameter restore, as the LoRA state sidecar uses it) against load_state."""
+    from mojodiffusion_b200.ops import native
+    from mojodiffusion_b200.parallel.fused_dp import emulated_step
+    world = 2
+    shapes = [(16, 3072), (3072, 16), (7,), (1000, 33)]
+    g = torch.Generator().manual_seed(3)
+    base = [torch.randn(*s, generator=g).bfloat16() for s in shapes]
+    grads = [[[torch.randn(*s, generator=g).bfloat16() for s in shapes] for _ in range(world)] for _ in range(3)]
+    kw = dict(lr=1e-2, weight_decay=0.01, max_grad_norm=1.0)
+    sets_a, ranks_a = _emulated(world, shapes, base, **kw)
+    for t in range(2):
+        _load_grads(ranks_a, sets_a, grads[t])
+        emulated_step(ranks_a)
+    torch.cuda.synchronize()
+    # what gather_state() returns on real ranks: the shards in rank order
+    m_full = torch.cat([r.m for r in ranks_a]).clone()
+    v_full = torch.cat([r.v for r in ranks_a]).clone()
+    weights = [p.detach().clone() for p in sets_a[0]]
+    step = ranks_a[0].step_count
+    # resumed run B: load_state; resumed run C: set_moments per parameter
+    sets_b, ranks_b = _emulated(world, shapes, weights, **kw)
+    sets_c, ranks_c = _emulated(world, shapes, weights, **kw)
+    for r in ranks_b:
+        r.load_state(m_full, v_full, step)
+    for r, ps in zip(ranks_c, sets_c):
+        for p, o in zip(ps, r.offsets):
+            r.set_moments(p, m_full[o:o + p.numel()].view_as(p), v_full[o:o + p.numel()].view_as(p))
+        r.step_count = step
+    for sets, ranks in ((sets_a, ranks_a), (sets_b, ranks_b), (sets_c, ranks_c)):
+        _load_grads(ranks, sets, grads[2])
+        emulated_step(ranks)
+    torch.cuda.synchronize()
+    native.check_status()
+    for pa, pb, pc in zip(sets_a[0], sets_b[1], sets_c[0]):
+        assert torch.equal(pa.detach(), pb.detach()) and torch.equal(pa.detach(), pc.detach())
+    with pytest.raises(RuntimeError):
+        ranks_a[0].moments(sets_a[0][0])          # world > 1 and no gather_state() for this step: refuses instead of communicating
+
+
+def test_timed_out_reduce_leaves_parameters_untouched():
+    """A reduce wait that runs out (rank 1 never announces its gradients: a flag nothing sets) must not be followed by an
+    optimizer update on stale sums: parameters and moments stay as they were, the done flag is still published, and the
+    host gets TIMEOUT from its next status check. The wait limit is lowered to 5 ms for the test and restored after."""
+    from mojodiffusion_b200.ops import native
+    world = 2
+    shapes = [(64, 512), (33,)]
+    g = torch.Generator().manual_seed(5)
+    base = [torch.randn(*s, generator=g).bfloat16() for s in shapes]
+    sets, ranks = _emulated(world, shapes, base, lr=1e-1, weight_decay=0.0, max_grad_norm=0.0)
+    for r, rk in enumerate(ranks):
+        rk.zero_grad()
+        for p in sets[r]:
+            p.grad.fill_(1.0)
+    native.check_status(ranks[0].red)
+    before = ranks[0].flat_params.clone()
+    torch.ops.mdb200.set_wait_limit_ns(5_000_000)
+    try:
+        r0 = ranks[0]
+        r0.phase_ready()            # rank 1 never calls phase_ready: its READY flag stays at the old epoch
+        r0.phase_reduce()           # -> wait runs out, `red` is not written
+        r0.phase_publish()          # -> publishes NaN instead of a partial norm
+        r0.phase_update()           # -> skips the update (own status not OK), still publishes DONE
+        torch.cuda.synchronize()
+        assert torch.equal(r0.flat_params, before), "parameters changed after a timed-out reduce"
+        assert float(r0.m.abs().max()) == 0.0 and float(r0.v.abs().max()) == 0.0
+        assert int(ranks[1].flags[2 * 8 + 0]) == r0.epoch, "done flag was not published to the peer"
+        assert torch.isnan(ranks[1].scalars[0]), "peer should see NaN as this rank's partial norm"
+        with pytest.raises(RuntimeError) as e:
+            r0.check()
+        assert "TIMEOUT" in str(e.value) and "where=201" in str(e.value)
+    finally:
+        torch.ops.mdb200.set_wait_limit_ns(1_000_000_000)
+    native.check_status(ranks[0].red)
