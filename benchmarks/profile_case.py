@@ -71,7 +71,7 @@ def main():
         for bn in (256, 512):
             for _ in range(2):
                 _gemm([x], [w], bn=bn)
-            prof = torch.zeros(148, 8, dtype=torch.int64, device=dev)
+            prof = torch.zeros(torch.cuda.get_device_properties(0).multi_processor_count, 8, dtype=torch.int64, device=dev)
             flush.zero_()
             _gemm([x], [w], bn=bn, prof=prof)
             torch.cuda.synchronize()

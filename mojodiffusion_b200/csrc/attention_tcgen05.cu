@@ -333,37 +333,51 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
       tc_fence_after();
       const float inv_l = 1.f / l_run;
       const int tok = q0 + t * BQ + row_in_tile;
-      __nv_bfloat16* obase = p.o;
-      long long otok = tok;
-      if (p.route_rows_a > 0 && tok < p.Sq) {
-        if (tok < p.route_split) {
-          const int owner = tok / p.route_rows_a;
-          obase = reinterpret_cast<__nv_bfloat16*>(p.o_route_a[owner]);
-          otok = tok - owner * p.route_rows_a;
-        } else {
-          const int u = tok - p.route_split;
-          const int owner = u / p.route_rows_b;
-          obase = reinterpret_cast<__nv_bfloat16*>(p.o_route_b[owner]);
-          otok = u - owner * p.route_rows_b;
-        }
-      }
-      __nv_bfloat16* orow = obase + batch * p.o_strides[0] + otok * p.o_strides[1] + head * p.o_strides[2];
+      // The normalised rows go through shared memory (this tile's Q buffer: every S = Q K^T has completed by now, 8 KB per
+      // warp) so that the global stores are whole rows: DH / 8 lanes x 16 bytes per row instead of one 16-byte piece of 32
+      // different rows per instruction. That matters most when the rows are routed into a peer's memory over NVLink.
+      constexpr int CH = DH / 8;                       // 16-byte chunks per output row
+      uint8_t* stage = sQ + t * TILE_BYTES + quad * (32 * DH * 2);
+      uint4* my_row = reinterpret_cast<uint4*>(stage + lane * (DH * 2));
 #pragma unroll
       for (int c = 0; c < DH / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(o_addr + c * 32, r);
         tmem_wait_ld();
-        if (tok < p.Sq) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(r[i + 0]) * inv_l, __uint_as_float(r[i + 1]) * inv_l);
-            w.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l);
-            w.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l);
-            w.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+        for (int i = 0; i < 32; i += 8) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(r[i + 0]) * inv_l, __uint_as_float(r[i + 1]) * inv_l);
+          w.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l);
+          w.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l);
+          w.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l);
+          my_row[(c * 4 + (i >> 3)) ^ (lane & (CH - 1))] = w;
+        }
+      }
+      __syncwarp();
+      const int chunk = lane % CH;
+#pragma unroll 4
+      for (int i = 0; i < CH; ++i) {
+        const int rl = i * (32 / CH) + lane / CH;          // row of this warp copied by this lane in this round
+        const int tk = q0 + t * BQ + quad * 32 + rl;
+        if (tk >= p.Sq) continue;
+        __nv_bfloat16* obase = p.o;
+        long long otok = tk;
+        if (p.route_rows_a > 0) {
+          if (tk < p.route_split) {
+            const int owner = tk / p.route_rows_a;
+            obase = reinterpret_cast<__nv_bfloat16*>(p.o_route_a[owner]);
+            otok = tk - owner * p.route_rows_a;
+          } else {
+            const int u = tk - p.route_split;
+            const int owner = u / p.route_rows_b;
+            obase = reinterpret_cast<__nv_bfloat16*>(p.o_route_b[owner]);
+            otok = u - owner * p.route_rows_b;
           }
         }
+        __nv_bfloat16* orow = obase + batch * p.o_strides[0] + otok * p.o_strides[1] + head * p.o_strides[2];
+        *reinterpret_cast<uint4*>(orow + chunk * 8) =
+            reinterpret_cast<const uint4*>(stage + rl * (DH * 2))[chunk ^ (rl & (CH - 1))];
       }
       if (p.lse != nullptr && tok < p.Sq)
         p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq + tok] =

@@ -766,7 +766,7 @@ void set_wait_limit_ns(int64_t ns) {
 
 // number of kernel launches issued through this library since load
 int64_t launch_count() { return g_launches.load(); }
-int64_t gemm_pair_capacity() { return mdb_gemm_pair_capacity(148); }
+int64_t gemm_pair_capacity() { return mdb_gemm_pair_capacity(at::cuda::getCurrentDeviceProperties()->multiProcessorCount); }
 
 }  // namespace
 

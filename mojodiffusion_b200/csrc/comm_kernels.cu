@@ -266,7 +266,7 @@ peer_gather_kernel(MdbPeerTable src, uint4* __restrict__ dst, long long chunk_ve
 
 static inline int clamp_grid(long long n, int threads) {
   long long b = (n + threads - 1) / threads;
-  const long long cap = 148ll * 4;
+  const long long cap = static_cast<long long>(device_sm_count()) * 4;
   return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
@@ -339,9 +339,10 @@ extern "C" int mdb_rs_finalize(const MdbPeerTable* flags, const int* my_flags, i
                                int* status, cudaStream_t st) {
   if (D % 8 || rows < 0 || slot < 0 || slot >= MDB_FLAG_SLOTS || epoch <= 0 || (out == nullptr) == (accum == nullptr)) return -1;
   if (rows == 0) return 0;
-  // every block must be resident at once (each waits for the peers): one wave of 148 SMs x 8 blocks at most
+  // every block must be resident at once (each waits for the peers): one wave of 4 blocks per SM at most
   const long long want = (rows * (D / 8) + 255) / 256;
-  const int grid = static_cast<int>(want < 148 * 4 ? want : 148 * 4);
+  const int cap = device_sm_count() * 4;
+  const int grid = static_cast<int>(want < cap ? want : cap);
   rs_finalize_kernel<<<grid, 256, 0, st>>>(*flags, my_flags, slot, epoch, rank, world,
                                            reinterpret_cast<const __nv_bfloat16*>(stage), rows, D,
                                            reinterpret_cast<const __nv_bfloat16*>(bias),

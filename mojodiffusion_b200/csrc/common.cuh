@@ -35,6 +35,19 @@ static __device__ unsigned long long g_wait_limit_ns = 1000000000ull;
     return static_cast<int>(cudaMemcpyToSymbol(::mdb::g_wait_limit_ns, &ns, sizeof(ns)));         \
   }
 
+// number of SMs of the current device (queried once per device; grids of the grid-stride kernels are sized from it)
+inline int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -136,7 +136,7 @@ __global__ void avgpool2x_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloa
 
 static inline int grid_for(long long n, int threads) {
   long long b = (n + threads - 1) / threads;
-  const long long cap = 148ll * 16;
+  const long long cap = static_cast<long long>(mdb::device_sm_count()) * 16;
   return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
 }
 

@@ -1113,7 +1113,7 @@ static int launch_pair_variant(const GemmMaps& maps, const GemmParams& p, int nu
 
 }  // namespace mdb
 
-extern "C" int mdb_gemm_pair_capacity(int num_sms) { return mdb::pair_capacity(num_sms > 0 ? num_sms : 148); }
+extern "C" int mdb_gemm_pair_capacity(int num_sms) { return mdb::pair_capacity(num_sms > 0 ? num_sms : mdb::device_sm_count()); }
 
 // MDB200_GEMM_PAIR=0 keeps every automatically tiled GEMM on the one-CTA kernel (A/B measurements); default: choose.
 static int pair_mode() {
@@ -1131,7 +1131,7 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   const int eb = a->kind == 1 ? 1 : 2;
   const int k_elems = BK_BYTES / eb;
   const bool paired = a->pair_offset > 0;
-  const int sms = a->num_sms > 0 ? a->num_sms : 148;
+  const int sms = a->num_sms > 0 ? a->num_sms : device_sm_count();
   int bn = a->bn;
   // bn == 512 asks for the CTA-pair kernel (256 x 256 tile over two SMs); it shares the tensor maps of the 128 x 256 tile
   const bool pair_ok = a->kind == 0 && a->conv_taps <= 0 && a->gather_world <= 1 && a->split_k <= 1;

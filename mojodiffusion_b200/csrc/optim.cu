@@ -168,7 +168,8 @@ extern "C" int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks,
   h.bc1 = 1.f - powf(beta1, (float)step);
   h.bc2_sqrt = sqrtf(1.f - powf(beta2, (float)step));
   h.grad_scale = grad_scale; h.norm_sq = norm_sq; h.max_norm = max_norm; h.seed = seed; h.stochastic = stochastic;
-  const int grid = num_chunks < 148 * 8 ? num_chunks : 148 * 8;
+  const int cap = device_sm_count() * 8;
+  const int grid = num_chunks < cap ? num_chunks : cap;
   const int2* ch = reinterpret_cast<const int2*>(chunks);
 #define MDB_AD(TP, TG, TM) adamw_multi_kernel<TP, TG, TM><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, h)
   if (p_bf16) {
@@ -185,7 +186,8 @@ extern "C" int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks,
 extern "C" int mdb_sumsq_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems,
                                int g_bf16, float* out, cudaStream_t st) {
   if (num_chunks <= 0) return 0;
-  const int grid = num_chunks < 148 * 8 ? num_chunks : 148 * 8;
+  const int cap = device_sm_count() * 8;
+  const int grid = num_chunks < cap ? num_chunks : cap;
   const int2* ch = reinterpret_cast<const int2*>(chunks);
   if (g_bf16)
     sumsq_multi_kernel<bf16><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, out);
@@ -197,7 +199,8 @@ extern "C" int mdb_sumsq_multi(const MdbTensorEntry* tensors, const int* chunks,
 extern "C" int mdb_ema_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems,
                              int p_bf16, float decay, cudaStream_t st) {
   if (num_chunks <= 0) return 0;
-  const int grid = num_chunks < 148 * 8 ? num_chunks : 148 * 8;
+  const int cap = device_sm_count() * 8;
+  const int grid = num_chunks < cap ? num_chunks : cap;
   const int2* ch = reinterpret_cast<const int2*>(chunks);
   if (p_bf16)
     ema_multi_kernel<bf16><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, decay);
@@ -296,7 +299,8 @@ extern "C" int mdb_adamw8bit(void* p, const void* g, void* qm, void* qv, float* 
   using namespace mdb;
   if (n <= 0) return 0;
   const long long blocks = (n + 255) / 256;
-  const int grid = blocks < 148 * 16 ? static_cast<int>(blocks) : 148 * 16;
+  const long long cap16 = static_cast<long long>(device_sm_count()) * 16;
+  const int grid = static_cast<int>(blocks < cap16 ? blocks : cap16);
   const float bc1 = 1.f - powf(b1, static_cast<float>(step));
   const float bc2s = sqrtf(1.f - powf(b2, static_cast<float>(step)));
   const int first = step <= 1;

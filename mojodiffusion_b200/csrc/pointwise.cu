@@ -355,7 +355,7 @@ __global__ void fp8_dequant_kernel(const __nv_fp8_storage_t* __restrict__ q, con
 
 static inline int grid_for(long long n, int threads) {
   long long b = (n + threads - 1) / threads;
-  const long long cap = 148ll * 16;
+  const long long cap = static_cast<long long>(mdb::device_sm_count()) * 16;
   return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
 }
 

@@ -43,7 +43,15 @@ def _gemm(As, Bs, bias=None, residual=None, gate=None, rows_per_group=1, act=0, 
                        list(route_cfg), list(gather_ptrs), list(gather_cfg), gather_dst, gather_ready, split_k)
 
 
-_NUM_SMS = 148
+_sm_count = {}
+
+
+def _num_sms(device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _sm_count.get(idx)
+    if n is None:
+        n = _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
 
 
 def _gemm_skinny(A, B, a_mn=False, b_mn=False, alpha=1.0):
@@ -54,7 +62,7 @@ def _gemm_skinny(A, B, a_mn=False, b_mn=False, alpha=1.0):
     K = A.shape[0] if a_mn else A.shape[1]
     tiles = ((M + 127) // 128) * ((N + 63) // 64)
     kblocks = (K + 63) // 64
-    split = min(_NUM_SMS // max(tiles, 1), kblocks // 4, 16)
+    split = min(_num_sms(A.device) // max(tiles, 1), kblocks // 4, 16)
     if split <= 1:
         return _gemm([A], [B], a_mn=a_mn, b_mn=b_mn, alpha=alpha)
     out = torch.zeros(M, N, dtype=torch.float32, device=A.device)

@@ -25,11 +25,18 @@ def _lib():
     return fn
 
 
-def _call(fn, x, w, b, groups, eps, act):
+def _call(fn, x, w, b, groups, eps, act, check_free=True):
     y = torch.empty_like(x)                       # the caller owns inputs and outputs; the call allocates nothing
     N, H, W, C = x.shape
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = fn(x.data_ptr(), y.data_ptr(), w.data_ptr() if w is not None else None, b.data_ptr() if b is not None else None,
             N, H * W, C, groups, eps, act, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    # the driver's count of free device memory is the same before and after: nothing was allocated (or freed) by the call,
+    # neither through a CUDA allocation call nor through a library pool
+    if check_free:
+        assert torch.cuda.mem_get_info()[0] == free_before, "the static-workspace entry point changed the amount of free device memory"
     return rc, y
 
 
@@ -40,6 +47,10 @@ def test_static_workspace_group_norm_matches_regular_op_twice():
     G, eps = 32, 1e-6
     w = torch.randn(256, device=dev).bfloat16()
     b = torch.randn(256, device=dev).bfloat16()
+    # One unchecked call first: the driver loads a kernel's code into device memory the first time the kernel is launched
+    # (lazy module loading), which is not an allocation made by the entry point but would show up in the free-memory count.
+    _call(fn, torch.zeros(1, 4, 4, 64, device=dev, dtype=torch.bfloat16), w[:64], b[:64], G, eps, 2, check_free=False)
+    _call(fn, torch.zeros(1, 4, 4, 64, device=dev, dtype=torch.bfloat16), None, None, G, eps, 0, check_free=False)
     # two calls in a row with different shapes and data: the second must not see anything the first left behind
     for (N, H, W, C), act, ww, bb in (((3, 24, 40, 256), 2, w, b), ((2, 16, 16, 128), 0, None, None)):
         x = (torch.randn(N, H, W, C, device=dev) * 2 + 0.5).bfloat16()
