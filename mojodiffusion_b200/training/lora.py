@@ -296,3 +296,17 @@ def merge_lora_into_weights(model: nn.Module, multiplier: float = 1.0) -> None:
                 delta = (s.up.float() @ s.down.float()) * (s.scale * multiplier)
                 m.weight[s.row0:s.row1] += delta.to(m.weight.dtype)
             m.slots = nn.ModuleList()
+
+
+def sdxl_kohya_name(module_path: str) -> str:
+    """LDM module path of a UNet linear -> Kohya SDXL key prefix (``lora_unet_`` + the path with dots as underscores)."""
+    return "lora_unet_" + module_path.replace(".", "_")
+
+
+def inject_sdxl_lora(model, rank: int = 16, alpha: float = 16.0, seed: int = 0) -> List[LoRASlot]:
+    """SDXL UNet adapters on every linear of the SpatialTransformers (attn1 / attn2 q, k, v, out and the GEGLU feed-forward),
+    the surface the reference trains (serenitymojo/models/sdxl/sdxl_unet_stack_lora.mojo; real-dims step
+    serenitymojo/models/sdxl/sdxl_real_train.mojo:289,462), saved under Kohya's ``lora_unet_*`` names
+    (serenitymojo/lora.mojo:61-75 ``FMT_KOHYA_SDXL``)."""
+    names = {n: sdxl_kohya_name(n) for n in model.lora_target_names()}
+    return inject_lora_by_name(model, names, rank, alpha)
