@@ -17,7 +17,7 @@ from mojodiffusion_b200.ops import native  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "gemm_trace", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "gemm_trace", "attention_trace", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
     ap.add_argument("--shape", default="")
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
@@ -82,6 +82,39 @@ def main():
                 col = pr[:, i][pr[:, i] > 0]
                 if col.numel():
                     print(f"  {nm:24s} mean {col.mean():12.0f}  max {col.max():12.0f}  (n={col.numel()})")
+        native.check_status()
+        print("ok")
+        return
+    if a.op == "attention_trace":
+        # per-kv-tile time line of CTA (0,0,0): who waits for whom (MDB200_ATTN_ISSUE selects how the control warps issue)
+        B, S, H, Dh = dims or [1, 4608, 24, 128]
+        q, k, v = [torch.randn(B, S, H, Dh, device=dev, dtype=torch.bfloat16) for _ in range(3)]
+        n_kv = (S + 127) // 128
+        T = 4 * n_kv + 8
+        for _ in range(2):
+            O.attention(q, k, v)
+        tr = torch.zeros(4, T, dtype=torch.int64, device=dev)
+        torch.ops.mdb200.attention_set_trace(tr)
+        flush.zero_()
+        O.attention(q, k, v)
+        torch.cuda.synchronize()
+        torch.ops.mdb200.attention_set_trace(None)
+        tr = tr.cpu()
+        t0 = int(tr[2, 0])
+        seen, issued = tr[0, :2 * n_kv] - t0, tr[1, :2 * n_kv] - t0
+        wg = [(tr[2 + t, :4 * n_kv] - t0).view(n_kv, 4) for t in range(2)]
+        print(f"attention B={B} S={S} H={H} Dh={Dh}: {n_kv} kv tiles; issue mode {os.environ.get('MDB200_ATTN_ISSUE', 'default')}")
+        print("  kv | MMA: P0 seen, issued, P1 seen, issued | WG0: S seen, loaded, max, P out | WG1: same")
+        for j in list(range(0, 6)) + list(range(n_kv - 3, n_kv)):
+            print(f"  {j:3d} | {int(seen[2*j]):7d} {int(issued[2*j]):7d} {int(seen[2*j+1]):7d} {int(issued[2*j+1]):7d} | "
+                  + " ".join(f"{int(x):7d}" for x in wg[0][j]) + " | " + " ".join(f"{int(x):7d}" for x in wg[1][j]))
+        mid = slice(4, n_kv - 2)
+        per = (wg[0][mid, 0][1:] - wg[0][mid, 0][:-1]).double()
+        print(f"  steady state: period per kv tile {per.mean():.0f} cycles (ideal 2048); WG0 softmax span (S seen -> P out) "
+              f"{(wg[0][mid, 3] - wg[0][mid, 0]).double().mean():.0f}, of which load {(wg[0][mid, 1] - wg[0][mid, 0]).double().mean():.0f}, "
+              f"max {(wg[0][mid, 2] - wg[0][mid, 1]).double().mean():.0f}, exp+store {(wg[0][mid, 3] - wg[0][mid, 2]).double().mean():.0f}; "
+              f"WG0 wait for S (P out -> next S seen) {(wg[0][mid, 0][1:] - wg[0][mid, 3][:-1]).double().mean():.0f}; "
+              f"MMA issue time per (kv, q tile) {(issued[8:2*n_kv-4] - seen[8:2*n_kv-4]).double().mean():.0f}")
         native.check_status()
         print("ok")
         return

@@ -1,16 +1,19 @@
 // Flash-style attention forward for sm_100a on the 5th-generation tensor cores.
 //
-// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that ping-pong: while one
-// softmax warpgroup works on its S tile, the tensor core runs the other tile's P*V and next Q*K^T.
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that take turns: while all eight
+// softmax warps work on one tile's S, the tensor core runs the other tile's P*V and next Q*K^T.
 //   * Q (2 x 128 x Dh), K and V (128 x Dh, double buffered) arrive by TMA straight from the caller's
 //     [batch, seq, head, Dh] strides (4-D tensor maps, 128-byte swizzle): no head transpose pass exists.
 //   * S = Q K^T  : tcgen05.mma SS-form, fp32 accumulator in TMEM (128 columns per tile).
-//   * softmax    : one thread per query row (no shuffles), exp2 with the scale folded in, P written back
-//                  into TMEM as packed bf16 over the S columns it came from.
+//   * softmax    : two threads per query row (64 key columns each, no shuffles; the row maximum is exchanged through
+//                  shared memory), exp2 with the scale folded in, P written back into TMEM as packed bf16 over the S
+//                  columns it came from. A per-kv-tile time line (mdb_attention_set_trace) showed the kernel bound by the
+//                  softmax chain, not by the tensor core; one thread per row with one warpgroup per tile measured the
+//                  same throughput with twice the registers.
 //   * O += P V   : tcgen05.mma TS-form (A = P from TMEM, B = V MN-major from shared memory) accumulating in a
 //                  second TMEM region across all key tiles. The running maximum used for the exponent is only
 //                  raised when a row's true maximum exceeds it by more than 2^8 ("lazy rescale"): then, and
-//                  only then, the warp scales its 32 rows of O in TMEM. P stays below 256, exact in fp32 sums.
+//                  only then, the warp scales its rows of O in TMEM. P stays below 256, exact in fp32 sums.
 //   * 512 TMEM columns: S0 S1 O0 O1.
 // Keys beyond Skv or beyond kv_len[b] are masked; ragged Sq / Skv tiles are zero filled by TMA.
 //
@@ -35,6 +38,15 @@ constexpr int CTRL_REGS = MDB_ATT_CTRL_REGS, SOFTMAX_REGS = MDB_ATT_SOFTMAX_REGS
 constexpr int BQ = 128;   // rows per q tile
 constexpr int BKV = 128;  // keys per kv tile
 
+#ifndef MDB_ATTN_ISSUE_DEFAULT
+#define MDB_ATTN_ISSUE_DEFAULT 1
+#endif
+#ifndef MDB_ATTN_POLY_DEFAULT
+#define MDB_ATTN_POLY_DEFAULT 2
+#endif
+static long long* g_attn_trace = nullptr;
+static int g_attn_trace_len = 0;
+
 struct alignas(64) AttnMaps {
   CUtensorMap q, k, v;
 };
@@ -46,12 +58,14 @@ struct AttnParams {
   int B, H, Sq, Skv;
   long long o_strides[3];
   float scale_log2;
-  int exp_poly;   // MDB200_ATTN_EXP_POLY=1: every other exponential through a polynomial on the FMA pipe. Off by default:
-                  // measured 0.41 ms against 0.27 ms at S=4608 (the softmax warps are issue bound, not SFU bound).
+  int exp_poly;   // MDB200_ATTN_EXP_POLY=N (1, 2, 4): one exponential in 2N runs as a polynomial on the FMA pipe; 0: none.
+                  // Measured at S=4608, H=24: 0.374 ms (0), 0.374 (1), 0.361 (2, the default), 0.419 (4).
   int* status;
   void* o_route_a[8];
   void* o_route_b[8];
   int route_rows_a, route_split, route_rows_b;
+  long long* trace;   // optional time line of CTA (0,0,0): [4 roles][trace_len] clock64 values (see mdb_attention_set_trace)
+  int trace_len;
 };
 
 template <int REGS> __device__ __forceinline__ void setmaxnreg_inc() {
@@ -61,7 +75,23 @@ template <int REGS> __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
 }
 
-template <int DH>
+// How the two control warps run their loops. MODE 0: one lane runs the whole role inside a branch. MODE 1: the whole warp
+// runs the loop, every lane polls the barriers, elect.sync picks the issuing lane. MODE 2: the whole warp runs the loop,
+// lane 0 polls and broadcasts the outcome, elect.sync picks the issuing lane (a convergent warp issues TMA / tcgen05
+// instructions cheaper, and one polling lane keeps the traffic on barriers the softmax warps arrive on low).
+template <int MODE> __device__ __forceinline__ bool ctl_wait(uint64_t* bar, uint32_t par, int* abort_flag, int lane) {
+  if (MODE == 0) return mbar_wait(bar, par, abort_flag);
+  if (MODE == 1) return __all_sync(0xffffffffu, mbar_wait(bar, par, abort_flag));
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, par, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+template <int MODE> __device__ __forceinline__ bool ctl_issuer() { return MODE == 0 ? true : elect_one() != 0; }
+template <int MODE> __device__ __forceinline__ void ctl_rejoin() {
+  if (MODE != 0) __syncwarp();
+}
+
+template <int DH, int MODE, int POLY_EVERY>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
   constexpr int DBOX = DH / 64;               // 64-element (128 B) boxes along the head dim
@@ -72,6 +102,8 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
   __shared__ uint64_t s_full[2], p_full[2], o_full[2];
+  __shared__ uint64_t x_bar[2][4];          // max / sum exchange between the two threads of a row, per q tile and quadrant
+  __shared__ float x_val[2][2][BQ];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
@@ -99,7 +131,8 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 128);
+      mbar_init(&p_full[s], 256);
+      for (int qd = 0; qd < 4; ++qd) mbar_init(&x_bar[s][qd], 64);
       mbar_init(&o_full[s], 1);
     }
     abort_s = 0;
@@ -121,36 +154,46 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
 
   if (warp < 4) {
     setmaxnreg_dec<CTRL_REGS>();
-    if (warp == 0 && lane == 0) {
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    if (warp == 0 && (MODE != 0 || lane == 0)) {
       // ----------------------------- TMA producer -----------------------------
-      mbar_expect_tx(&q_full, 2 * TILE_BYTES);
-      for (int t = 0; t < 2; ++t)
-        for (int d = 0; d < DBOX; ++d)
-          tma_load_4d(sQ + t * TILE_BYTES + d * BOX_BYTES, &maps.q, &q_full, d * 64, q0 + t * BQ, head, batch);
+      if (ctl_issuer<MODE>()) {
+        mbar_expect_tx(&q_full, 2 * TILE_BYTES);
+        for (int t = 0; t < 2; ++t)
+          for (int d = 0; d < DBOX; ++d)
+            tma_load_4d(sQ + t * TILE_BYTES + d * BOX_BYTES, &maps.q, &q_full, d * 64, q0 + t * BQ, head, batch);
+      }
+      ctl_rejoin<MODE>();
       bool ok = true;
       uint64_t* last_bar = &q_full;
       uint32_t last_par = 0;
       for (int j = 0; ok && j < n_kv; ++j) {
         const int st = j & 1;
         const uint32_t par = (j >> 1) & 1;
-        if (!mbar_wait(&k_empty[st], par ^ 1u, &abort_s)) {
-          report_status(p.status, STATUS_TIMEOUT, 11, j);
+        if (!ctl_wait<MODE>(&k_empty[st], par ^ 1u, &abort_s, lane)) {
+          if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 11, j);
           ok = false;
           break;
         }
-        mbar_expect_tx(&k_full[st], TILE_BYTES);
-        for (int d = 0; d < DBOX; ++d)
-          tma_load_4d(sK + st * TILE_BYTES + d * BOX_BYTES, &maps.k, &k_full[st], d * 64, j * BKV, head, batch);
+        if (ctl_issuer<MODE>()) {
+          mbar_expect_tx(&k_full[st], TILE_BYTES);
+          for (int d = 0; d < DBOX; ++d)
+            tma_load_4d(sK + st * TILE_BYTES + d * BOX_BYTES, &maps.k, &k_full[st], d * 64, j * BKV, head, batch);
+        }
+        ctl_rejoin<MODE>();
         last_bar = &k_full[st];
         last_par = par;
-        if (!mbar_wait(&v_empty[st], par ^ 1u, &abort_s)) {
-          report_status(p.status, STATUS_TIMEOUT, 12, j);
+        if (!ctl_wait<MODE>(&v_empty[st], par ^ 1u, &abort_s, lane)) {
+          if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 12, j);
           ok = false;
           break;
         }
-        mbar_expect_tx(&v_full[st], TILE_BYTES);
-        for (int d = 0; d < DBOX; ++d)
-          tma_load_4d(sV + st * TILE_BYTES + d * BOX_BYTES, &maps.v, &v_full[st], d * 64, j * BKV, head, batch);
+        if (ctl_issuer<MODE>()) {
+          mbar_expect_tx(&v_full[st], TILE_BYTES);
+          for (int d = 0; d < DBOX; ++d)
+            tma_load_4d(sV + st * TILE_BYTES + d * BOX_BYTES, &maps.v, &v_full[st], d * 64, j * BKV, head, batch);
+        }
+        ctl_rejoin<MODE>();
         last_bar = &v_full[st];
         last_par = par;
       }
@@ -159,39 +202,45 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
         while (!mbar_try_wait(last_bar, last_par) && globaltimer_ns() - t0 < 5000000ull) {
         }
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1 && (MODE != 0 || lane == 0)) {
       // ----------------------------- UMMA issuer ------------------------------
+      // (Two issuing warps, one per q tile, were measured slower: the issuers block on the tensor pipe's short queue, so
+      // issue time is execution time, and two of them only contend.) Descriptors are built once; each MMA adds a constant
+      // to the address field.
       constexpr uint32_t idesc_s = make_idesc(1, UMMA_BF16, UMMA_BF16, 0, 0, BQ, BKV);
       constexpr uint32_t idesc_pv = make_idesc(1, UMMA_BF16, UMMA_BF16, 0, 1, BQ, DH);
-      const uint32_t s_cols[2] = {S_COL0, S_COL1};
-      const uint32_t o_cols[2] = {O_COL0, O_COL1};
+      const uint32_t s_tmem[2] = {tmem_base + S_COL0, tmem_base + S_COL1};
+      const uint32_t o_tmem[2] = {tmem_base + O_COL0, tmem_base + O_COL1};
+      const uint64_t q_desc[2] = {make_desc_kmajor_sw128(smem_u32(sQ)), make_desc_kmajor_sw128(smem_u32(sQ + TILE_BYTES))};
+      const uint64_t k_desc[2] = {make_desc_kmajor_sw128(smem_u32(sK)), make_desc_kmajor_sw128(smem_u32(sK + TILE_BYTES))};
+      const uint64_t v_desc[2] = {make_desc_mnmajor_sw128(smem_u32(sV), BOX_BYTES),
+                                  make_desc_mnmajor_sw128(smem_u32(sV + TILE_BYTES), BOX_BYTES)};
+      // both helpers run in the issuing lane only
       auto issue_s = [&](int t, int st) {
-        const uint32_t qa = smem_u32(sQ + t * TILE_BYTES);
-        const uint32_t ka = smem_u32(sK + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-          const uint32_t off = (kk / 4) * BOX_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + s_cols[t], make_desc_kmajor_sw128(qa + off), make_desc_kmajor_sw128(ka + off),
-                      idesc_s, kk != 0 ? 1u : 0u);
+          const uint32_t off = static_cast<uint32_t>((kk / 4) * BOX_BYTES + (kk % 4) * 32) >> 4;
+          umma_f16_ss(s_tmem[t], q_desc[t] + off, k_desc[st] + off, idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[t]);
       };
       auto issue_pv = [&](int t, int st, bool first) {
-        const uint32_t va = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          umma_f16_ts(tmem_base + o_cols[t], tmem_base + s_cols[t] + kk * 8,
-                      make_desc_mnmajor_sw128(va + kk * 2048, BOX_BYTES), idesc_pv, (first && kk == 0) ? 0u : 1u);
-        }
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          umma_f16_ts(o_tmem[t], s_tmem[t] + kk * 8, v_desc[st] + static_cast<uint32_t>((kk * 2048) >> 4), idesc_pv,
+                      (first && kk == 0) ? 0u : 1u);
         umma_commit(&o_full[t]);
       };
-      bool ok = mbar_wait(&q_full, 0, &abort_s) && mbar_wait(&k_full[0], 0, &abort_s);
-      if (!ok) report_status(p.status, STATUS_TIMEOUT, 21, 0);
+      bool ok = ctl_wait<MODE>(&q_full, 0, &abort_s, lane) && ctl_wait<MODE>(&k_full[0], 0, &abort_s, lane);
+      if (!ok && lane == 0) report_status(p.status, STATUS_TIMEOUT, 21, 0);
       if (ok) {
         tc_fence_after();
-        issue_s(0, 0);
-        issue_s(1, 0);
-        umma_commit(&k_empty[0]);
+        if (ctl_issuer<MODE>()) {
+          issue_s(0, 0);
+          issue_s(1, 0);
+          umma_commit(&k_empty[0]);
+        }
+        ctl_rejoin<MODE>();
       }
       for (int j = 0; ok && j < n_kv; ++j) {
         const int st = j & 1;
@@ -199,148 +248,189 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
         const bool more = (j + 1 < n_kv);
         const int st_n = (j + 1) & 1;
         const uint32_t par_n = ((j + 1) >> 1) & 1;
-        if (!mbar_wait(&v_full[st], par, &abort_s) || (more && !mbar_wait(&k_full[st_n], par_n, &abort_s))) {
-          report_status(p.status, STATUS_TIMEOUT, 22, j);
+        if (!ctl_wait<MODE>(&v_full[st], par, &abort_s, lane) || (more && !ctl_wait<MODE>(&k_full[st_n], par_n, &abort_s, lane))) {
+          if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 22, j);
           ok = false;
           break;
         }
         for (int t = 0; t < 2; ++t) {
-          if (!mbar_wait(&p_full[t], j & 1, &abort_s)) {
-            report_status(p.status, STATUS_TIMEOUT, 23 + t, j);
+          if (!ctl_wait<MODE>(&p_full[t], j & 1, &abort_s, lane)) {
+            if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 23 + t, j);
             ok = false;
             break;
           }
+          if (tracing && lane == 0 && (j * 2 + t) < p.trace_len) p.trace[0 * p.trace_len + j * 2 + t] = clock64();
           tc_fence_after();
-          issue_pv(t, st, j == 0);
-          if (more) issue_s(t, st_n);
+          if (ctl_issuer<MODE>()) {
+            issue_pv(t, st, j == 0);
+            if (more) issue_s(t, st_n);
+            if (t == 1) {
+              umma_commit(&v_empty[st]);
+              if (more) umma_commit(&k_empty[st_n]);
+            }
+          }
+          ctl_rejoin<MODE>();
+          if (tracing && lane == 0 && (j * 2 + t) < p.trace_len) p.trace[1 * p.trace_len + j * 2 + t] = clock64();
         }
         if (!ok) break;
-        umma_commit(&v_empty[st]);
-        if (more) umma_commit(&k_empty[st_n]);
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------- softmax warpgroups ---------------------------
+    // ------------------------------- softmax warps: two threads per query row ---------------
+    // Warps 4-7 own key columns 0..63 of every S tile (and output columns 0..Dh/2-1), warps 8-11 the other half; the two
+    // threads of a row sit in warps with the same TMEM lane quadrant. Both q tiles are processed by the same threads in
+    // turn, so tile 0's P V and next Q K^T run on the tensor core while all eight warps do tile 1's softmax and vice
+    // versa: the exponentials of one tile are spread over all four special-function units with two warps each. Per kv
+    // tile the two halves exchange their row maxima through shared memory (an mbarrier of 64 arrivals per tile and
+    // quadrant, bounded wait), so both use the same exponent reference and take the same rescale decisions; the row sums
+    // stay partial and are added once at the end.
     setmaxnreg_inc<SOFTMAX_REGS>();
-    const int t = (warp - 4) >> 2;        // q tile of this warpgroup
-    const int quad = warp & 3;            // TMEM lane quadrant
+    const int half = (warp - 4) >> 2;
+    const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
-    const uint32_t o_addr = tmem_base + lane_addr + (t ? O_COL1 : O_COL0);
     const float sl2 = p.scale_log2;
-
-    float m_used = -INFINITY, l_run = 0.f;
+    constexpr int OH = DH / 2;                 // output columns per thread
+    float m_used[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     bool ok = true;
 
-    for (int j = 0; j < n_kv; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, &abort_s));
+    // max / sum exchange between the two threads of a row
+    auto exchange = [&](int t, float mine, uint32_t parity, float& other) -> bool {
+      x_val[t][half][row_in_tile] = mine;
+      mbar_arrive(&x_bar[t][quad]);
+      const bool got = mbar_wait(&x_bar[t][quad], parity, &abort_s);
+      other = x_val[t][half ^ 1][row_in_tile];
+      return got;
+    };
+
+    for (int j = 0; ok && j < n_kv; ++j) {
+      const int kv0 = j * BKV + half * 64;
+      const bool tail = j * BKV + BKV > kv_valid;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const uint32_t s_tile = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
+        const uint32_t o_addr = tmem_base + lane_addr + (t ? O_COL1 : O_COL0) + half * OH;
+        ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, &abort_s));
+        if (!ok) {
+          if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 31 + t, j);
+          break;
+        }
+        tc_fence_after();
+        const bool tr = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 4 && lane == 0 &&
+                        4 * j + 3 < p.trace_len;
+        if (tr) p.trace[(2 + t) * p.trace_len + 4 * j] = clock64();
+        uint32_t s0[32], s1[32];
+        tmem_ld_32x32b_x32(s_tile + half * 64, s0);
+        tmem_ld_32x32b_x32(s_tile + half * 64 + 32, s1);
+        tmem_wait_ld();
+        if (tr) p.trace[(2 + t) * p.trace_len + 4 * j + 1] = clock64();
+        if (tail) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (kv0 + i >= kv_valid) s0[i] = 0xff800000u;        // -inf
+            if (kv0 + 32 + i >= kv_valid) s1[i] = 0xff800000u;
+          }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(s0[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(s1[i]));
+          mx3 = fmaxf(mx3, __uint_as_float(s1[i + 1]));
+        }
+        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+        float other;
+        ok = __all_sync(0xffffffffu, exchange(t, mx, j & 1, other));
+        if (!ok) {
+          if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 37 + t, j);
+          break;
+        }
+        mx = fmaxf(mx, other);                     // the row's maximum over all 128 keys of the tile, same in both halves
+        if (tr) p.trace[(2 + t) * p.trace_len + 4 * j + 2] = clock64();
+        if (j == 0) {
+          m_used[t] = mx;
+        } else {
+          // lazy rescale: raise the exponent reference only when a row outgrew it by more than 2^8
+          const bool need = mx > m_used[t] + 8.0f;
+          if (__any_sync(0xffffffffu, need)) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (j - 1) & 1, &abort_s));
+            if (!ok) {
+              if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 33 + t, j);
+              break;
+            }
+            tc_fence_after();
+            const float alpha = need ? exp2f(m_used[t] - mx) : 1.0f;
+            if (need) m_used[t] = mx;
+            l_run[t] *= alpha;
+#pragma unroll
+            for (int c = 0; c < OH / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(o_addr + c * 32, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32b_x32(o_addr + c * 32, r);
+            }
+            tmem_wait_st();
+          }
+        }
+        const float mref = m_used[t];
+        float sum0 = 0.f, sum1 = 0.f;
+        auto emit = [&](const uint32_t (&sv)[32], int c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            // every POLY_EVERY-th exponential runs as a polynomial on the FMA pipe: the special-function unit (16 results
+            // per clock per SM) is what bounds this loop, the FMA pipe has room
+            const float xa = fmaf(__uint_as_float(sv[i]), sl2, -mref);
+            const float xb = fmaf(__uint_as_float(sv[i + 1]), sl2, -mref);
+            const float a = exp2f(xa);
+            const float b = (POLY_EVERY > 0 && ((i >> 1) % POLY_EVERY) == POLY_EVERY - 1) ? ex2_poly(xb) : exp2f(xb);
+            sum0 += a;
+            sum1 += b;
+            pk[i >> 1] = pack_bf16x2(a, b);
+          }
+          // P (bf16) of this half: 32 TMEM columns at half * 32 of the tile's S region; both halves have loaded their S
+          // values before the exchange above, so nothing still needed is overwritten
+          tmem_st_32x32b_x16(s_tile + half * 32 + c * 16, pk);
+        };
+        emit(s0, 0);
+        emit(s1, 1);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_full[t]);
+        if (tr) p.trace[(2 + t) * p.trace_len + 4 * j + 3] = clock64();
+        l_run[t] += sum0 + sum1;
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      if (!ok) break;
+      const uint32_t o_addr = tmem_base + lane_addr + (t ? O_COL1 : O_COL0) + half * OH;
+      ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (n_kv - 1) & 1, &abort_s));
       if (!ok) {
-        if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 31 + t, j);
+        if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 35 + t, n_kv);
         break;
       }
       tc_fence_after();
-      const int kv0 = j * BKV;
-      const bool tail = kv0 + BKV > kv_valid;
-      // the whole S row in registers: four loads in flight, one wait
-      uint32_t s0[32], s1[32], s2[32], s3[32];
-      tmem_ld_32x32b_x32(s_addr + 0, s0);
-      tmem_ld_32x32b_x32(s_addr + 32, s1);
-      tmem_ld_32x32b_x32(s_addr + 64, s2);
-      tmem_ld_32x32b_x32(s_addr + 96, s3);
-      tmem_wait_ld();
-      if (tail) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (kv0 + i >= kv_valid) s0[i] = 0xff800000u;        // -inf
-          if (kv0 + 32 + i >= kv_valid) s1[i] = 0xff800000u;
-          if (kv0 + 64 + i >= kv_valid) s2[i] = 0xff800000u;
-          if (kv0 + 96 + i >= kv_valid) s3[i] = 0xff800000u;
-        }
+      float l_other;
+      ok = __all_sync(0xffffffffu, exchange(t, l_run[t], n_kv & 1, l_other));
+      if (!ok) {
+        if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 39 + t, n_kv);
+        break;
       }
-      float mx = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        mx = fmaxf(mx, fmaxf(fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])),
-                             fmaxf(__uint_as_float(s2[i]), __uint_as_float(s3[i]))));
-      }
-      mx *= sl2;
-      if (j == 0) {
-        m_used = mx;
-      } else {
-        // lazy rescale: raise the exponent reference only when a row outgrew it by more than 2^8
-        const bool need = mx > m_used + 8.0f;
-        if (__any_sync(0xffffffffu, need)) {
-          ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (j - 1) & 1, &abort_s));
-          if (!ok) {
-            if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 33 + t, j);
-            break;
-          }
-          tc_fence_after();
-          const float alpha = need ? exp2f(m_used - mx) : 1.0f;
-          if (need) m_used = mx;
-          l_run *= alpha;
-#pragma unroll
-          for (int c = 0; c < DH / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(o_addr + c * 32, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(o_addr + c * 32, r);
-          }
-          tmem_wait_st();
-        }
-      }
-      float rowsum = 0.f;
-      const bool poly = p.exp_poly != 0;
-      auto emit = [&](const uint32_t (&sv)[32], int c) {
-        uint32_t pk[16];
-        if (poly) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float a = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -m_used));
-            const float b = ex2_poly(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_used));   // every other one off the SFU
-            rowsum += a + b;
-            pk[i >> 1] = pack_bf16x2(a, b);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float a = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -m_used));
-            const float b = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_used));
-            rowsum += a + b;
-            pk[i >> 1] = pack_bf16x2(a, b);
-          }
-        }
-        tmem_st_32x32b_x16(s_addr + c * 16, pk);
-      };
-      emit(s0, 0);
-      emit(s1, 1);
-      emit(s2, 2);
-      emit(s3, 3);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&p_full[t]);
-      l_run += rowsum;
-    }
-    if (ok) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (n_kv - 1) & 1, &abort_s));
-      if (!ok && lane == 0) report_status(p.status, STATUS_TIMEOUT, 35 + t, n_kv);
-    }
-    if (ok) {
-      tc_fence_after();
-      const float inv_l = 1.f / l_run;
-      const int tok = q0 + t * BQ + row_in_tile;
-      // The normalised rows go through shared memory (this tile's Q buffer: every S = Q K^T has completed by now, 8 KB per
-      // warp) so that the global stores are whole rows: DH / 8 lanes x 16 bytes per row instead of one 16-byte piece of 32
-      // different rows per instruction. That matters most when the rows are routed into a peer's memory over NVLink.
+      const float l_tot = l_run[t] + l_other;
+      const float inv_l = 1.f / l_tot;
+      // The normalised rows go through shared memory (this tile's Q buffer: every S = Q K^T has completed by now, 32 rows
+      // per quadrant) so that the global stores are whole rows: DH / 8 lanes x 16 bytes per row instead of one 16-byte
+      // piece of 32 different rows per instruction. That matters most when the rows are routed into a peer's memory.
       constexpr int CH = DH / 8;                       // 16-byte chunks per output row
       uint8_t* stage = sQ + t * TILE_BYTES + quad * (32 * DH * 2);
       uint4* my_row = reinterpret_cast<uint4*>(stage + lane * (DH * 2));
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = 0; c < OH / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(o_addr + c * 32, r);
         tmem_wait_ld();
@@ -351,14 +441,21 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
           w.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l);
           w.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l);
           w.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l);
-          my_row[(c * 4 + (i >> 3)) ^ (lane & (CH - 1))] = w;
+          my_row[(half * (CH / 2) + c * 4 + (i >> 3)) ^ (lane & (CH - 1))] = w;
         }
       }
-      __syncwarp();
+      // both halves of the quadrant's 32 rows are staged (a rendezvous only: the exchange slots are not written again, the
+      // partner may still be reading the row sum left there)
+      mbar_arrive(&x_bar[t][quad]);
+      ok = __all_sync(0xffffffffu, mbar_wait(&x_bar[t][quad], (n_kv + 1) & 1, &abort_s));
+      if (!ok) {
+        if (lane == 0) report_status(p.status, STATUS_TIMEOUT, 41 + t, n_kv);
+        break;
+      }
       const int chunk = lane % CH;
 #pragma unroll 4
-      for (int i = 0; i < CH; ++i) {
-        const int rl = i * (32 / CH) + lane / CH;          // row of this warp copied by this lane in this round
+      for (int i = 0; i < CH / 2; ++i) {
+        const int rl = half * 16 + i * (32 / CH) + lane / CH;          // this warp copies 16 of the quadrant's 32 rows
         const int tk = q0 + t * BQ + quad * 32 + rl;
         if (tk >= p.Sq) continue;
         __nv_bfloat16* obase = p.o;
@@ -379,9 +476,9 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
         *reinterpret_cast<uint4*>(orow + chunk * 8) =
             reinterpret_cast<const uint4*>(stage + rl * (DH * 2))[chunk ^ (rl & (CH - 1))];
       }
-      if (p.lse != nullptr && tok < p.Sq)
-        p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq + tok] =
-            (m_used + log2f(l_run)) * 0.6931471805599453f;
+      const int tok = q0 + t * BQ + row_in_tile;
+      if (half == 0 && p.lse != nullptr && tok < p.Sq)
+        p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq + tok] = (m_used[t] + log2f(l_tot)) * 0.6931471805599453f;
     }
   }
 
@@ -393,10 +490,10 @@ attention_fwd_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) 
   }
 }
 
-template <int DH>
+template <int DH, int MODE, int POLY_EVERY>
 static int launch_attn(const AttnMaps& maps, const AttnParams& p, cudaStream_t st) {
   constexpr int SMEM = 6 * BQ * DH * 2 + 1024;
-  auto kern = attention_fwd_kernel<DH>;
+  auto kern = attention_fwd_kernel<DH, MODE, POLY_EVERY>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -447,7 +544,7 @@ extern "C" int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st) {
     static int mode = -1;
     if (mode < 0) {
       const char* e = getenv("MDB200_ATTN_EXP_POLY");
-      mode = (e != nullptr && e[0] == '1') ? 1 : 0;
+      mode = (e != nullptr && e[0] >= '0' && e[0] <= '4') ? e[0] - '0' : MDB_ATTN_POLY_DEFAULT;
     }
     p.exp_poly = mode;
   }
@@ -459,8 +556,37 @@ extern "C" int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st) {
   p.route_rows_a = a->route_rows_a;
   p.route_split = a->route_rows_a > 0 ? (a->o_route_b[0] ? a->route_split : a->Sq) : 0;
   p.route_rows_b = a->route_rows_b > 0 ? a->route_rows_b : 1;
-  if (a->Dh == 128) return launch_attn<128>(maps, p, st);
-  return launch_attn<64>(maps, p, st);
+  p.trace = g_attn_trace;
+  p.trace_len = g_attn_trace_len;
+  static int issue_mode = -1;
+  if (issue_mode < 0) {
+    const char* e = getenv("MDB200_ATTN_ISSUE");     // 0 / 1 / 2: see ctl_wait; measurement switch
+    issue_mode = (e != nullptr && e[0] >= '0' && e[0] <= '1') ? e[0] - '0' : MDB_ATTN_ISSUE_DEFAULT;
+  }
+  // p.exp_poly: 0 = every exponential on the special-function unit; N = one exponential in 2N as a polynomial on the FMA pipe
+  // (MDB200_ATTN_EXP_POLY, default MDB_ATTN_POLY_DEFAULT)
+#define MDB_ATTN_GO(DH_, MODE_)                                                     \
+  do {                                                                              \
+    if (p.exp_poly == 1) return launch_attn<DH_, MODE_, 1>(maps, p, st);            \
+    if (p.exp_poly == 2) return launch_attn<DH_, MODE_, 2>(maps, p, st);            \
+    if (p.exp_poly == 4) return launch_attn<DH_, MODE_, 4>(maps, p, st);            \
+    return launch_attn<DH_, MODE_, 0>(maps, p, st);                                 \
+  } while (0)
+  if (a->Dh == 128) {
+    if (issue_mode == 0) MDB_ATTN_GO(128, 0);
+    MDB_ATTN_GO(128, 1);
+  }
+  if (issue_mode == 0) MDB_ATTN_GO(64, 0);
+  MDB_ATTN_GO(64, 1);
+#undef MDB_ATTN_GO
+}
+
+// Debugging aid: the next forward launches write a clock64 time line of CTA (0, 0, 0) into `trace` (device memory,
+// [4][len] int64: 0 = MMA issuer saw P ready per (kv tile, q tile); 1 = MMA issuer done issuing; 2 / 3 = softmax warpgroup
+// 0 / 1: S seen, S loaded, maximum done, P published per kv tile). NULL switches it off.
+extern "C" void mdb_attention_set_trace(long long* trace, int len) {
+  mdb::g_attn_trace = trace;
+  mdb::g_attn_trace_len = len;
 }
 
 MDB_DEFINE_WAIT_LIMIT_SETTER(mdb_set_wait_limit_attn_fwd)

@@ -755,6 +755,15 @@ std::vector<int64_t> read_status(const Tensor& like, bool reset) {
   return {h[0], h[1], h[2], h[3]};
 }
 
+void attention_set_trace(const optional<Tensor>& trace) {
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() % 4 == 0, "attention_set_trace: int64 [4, len]");
+    mdb_attention_set_trace(reinterpret_cast<long long*>(trace->data_ptr()), (int)(trace->numel() / 4));
+  } else {
+    mdb_attention_set_trace(nullptr, 0);
+  }
+}
+
 // limit of every bounded device-side wait on the current device, in nanoseconds (default 1e9)
 void set_wait_limit_ns(int64_t ns) {
   TORCH_CHECK(ns > 0, "set_wait_limit_ns: positive nanoseconds");
@@ -811,4 +820,5 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("dp_adamw_shard", &dp_adamw_shard);
   m.def("read_status", &read_status);
   m.def("set_wait_limit_ns", &set_wait_limit_ns);
+  m.def("attention_set_trace", &attention_set_trace);
 }

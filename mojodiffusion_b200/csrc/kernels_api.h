@@ -136,6 +136,8 @@ typedef struct MdbAttnArgs {
   int route_rows_a, route_split, route_rows_b;
 } MdbAttnArgs;
 int mdb_attention_fwd(const MdbAttnArgs* a, cudaStream_t st);
+// debugging aid: per-kv-tile clock64 time line of CTA (0,0,0) of the following forward launches ([4][len] int64; NULL: off)
+void mdb_attention_set_trace(long long* trace, int len);
 
 // ---- shader_filters.cu: RGBA fp32 image filters (op codes and parameter layout documented at the definition)
 int mdb_image_filter(int op, const float* in, float* out, float* tmp, int H, int W, const float* params, int nparams,
