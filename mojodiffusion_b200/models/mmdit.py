@@ -15,6 +15,8 @@ Two execution styles share the same modules:
 """
 from __future__ import annotations
 
+import contextlib
+
 import zlib
 from dataclasses import dataclass
 from typing import Optional, Tuple
@@ -24,6 +26,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from ..utils.tracing import nvtx_enabled, nvtx_range
 from ..ops import native
 from .layers import Linear, MLPEmbedder, timestep_embedding
 
@@ -230,6 +233,9 @@ class LastLayer(nn.Module):
         return self.linear(ops.norm_modulate(x, scale=scale, shift=shift, eps=1e-6))
 
 
+_NULL = contextlib.nullcontext()
+
+
 class MMDiT(nn.Module):
     """FLUX-style double + single stream diffusion transformer predicting the rectified-flow velocity."""
 
@@ -313,17 +319,20 @@ class MMDiT(nn.Module):
             for i in range(len(self.single_blocks)):
                 x = st.step(nd + i, lambda b, h, v: b(h, v, cos, sin, sp), x, vec_silu)
             return self.final_layer(x[:, S_txt:], vec_silu)
-        for blk in self.double_blocks:
-            if ckpt:
-                img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, vec_silu, cos, sin, use_reentrant=False, preserve_rng_state=False)
-            else:
-                img, txt = blk(img, txt, vec_silu, cos, sin, sp)
+        trace = nvtx_enabled()
+        for i, blk in enumerate(self.double_blocks):
+            with nvtx_range(f"block/double/{i}") if trace else _NULL:
+                if ckpt:
+                    img, txt = torch.utils.checkpoint.checkpoint(blk, img, txt, vec_silu, cos, sin, use_reentrant=False, preserve_rng_state=False)
+                else:
+                    img, txt = blk(img, txt, vec_silu, cos, sin, sp)
         x = torch.cat((txt, img), dim=1)
-        for blk in self.single_blocks:
-            if ckpt:
-                x = torch.utils.checkpoint.checkpoint(blk, x, vec_silu, cos, sin, use_reentrant=False, preserve_rng_state=False)
-            else:
-                x = blk(x, vec_silu, cos, sin, sp)
+        for i, blk in enumerate(self.single_blocks):
+            with nvtx_range(f"block/single/{i}") if trace else _NULL:
+                if ckpt:
+                    x = torch.utils.checkpoint.checkpoint(blk, x, vec_silu, cos, sin, use_reentrant=False, preserve_rng_state=False)
+                else:
+                    x = blk(x, vec_silu, cos, sin, sp)
         x = x[:, S_txt:]
         return self.final_layer(x, vec_silu)
 

@@ -86,7 +86,9 @@ def _views(slab: torch.Tensor, members: Sequence[Member]) -> Dict[str, torch.Ten
 
 
 class BlockSwapLoader:
-    def __init__(self, store: PinnedBlockStore, device, slot_count: Optional[int] = None):
+    def __init__(self, store: PinnedBlockStore, device, slot_count: Optional[int] = None, copy_stream_priority: int = 0):
+        """``copy_stream_priority``: CUDA priority of the copy stream (0 default, -1 high). The race tests run every streamed
+        workload under both and require bit-identical results: an ordering that only holds by scheduling luck shows up."""
         self.store, self.plan = store, store.plan
         self.device = torch.device(device)
         self.cuda = self.device.type == "cuda"
@@ -100,7 +102,7 @@ class BlockSwapLoader:
         self._clock = 0
         self.resident: Dict[int, torch.Tensor] = {}
         if self.cuda:
-            self.copy_stream = torch.cuda.Stream(self.device)
+            self.copy_stream = torch.cuda.Stream(self.device, priority=copy_stream_priority)
             self.ready = [torch.cuda.Event() for _ in range(n_slots)]
             self.free = [torch.cuda.Event() for _ in range(n_slots)]
             self._free_recorded = [False] * n_slots

@@ -28,6 +28,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..ops import native
+from ..utils.tracing import nvtx_range
 from ..ops.functional import _flat2d, _gemm
 from .symm import SymmetricBuffer
 
@@ -122,7 +123,8 @@ class FSDPContext:
     @torch.no_grad()
     def step(self, lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, grad_scale: Optional[float] = None):
         """AdamW on every local master shard (one launch), bf16 shards refreshed for the next all-gather."""
-        self.barrier(SLOT_BWD_DONE)                       # every rank's dW tiles have been added into my shards
+        with nvtx_range("collective/fsdp/grad_barrier"):
+            self.barrier(SLOT_BWD_DONE)                       # every rank's dW tiles have been added into my shards
         self.step_count += 1
         scale = (1.0 / self.world) if grad_scale is None else grad_scale
         from ..training.optim import CHUNK

@@ -15,6 +15,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import native
+from ..utils.tracing import nvtx_range
 from .symm import SymmetricBuffer, emulated_group
 
 SLOT_READY, SLOT_NORM, SLOT_DONE = 0, 1, 2
@@ -119,11 +120,12 @@ class FusedDPAdamW:
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0, lr: Optional[float] = None):
         assert grad_scale == 1.0, "the 1/world scale is applied inside the fused kernels"
-        self.phase_ready()
-        self.phase_reduce()
-        self.phase_publish()
-        self.phase_update(lr)
-        self.phase_finish()
+        with nvtx_range("collective/dp/reduce_scatter_adamw_all_gather"):
+            self.phase_ready()
+            self.phase_reduce()
+            self.phase_publish()
+            self.phase_update(lr)
+            self.phase_finish()
         if self.step_count % self.check_every == 0:
             self.check()
 

@@ -24,6 +24,7 @@ import torch.distributed as dist
 from .. import ops
 from ..ops import native
 from ..ops.functional import _flat2d, _gemm
+from ..utils.tracing import nvtx_range
 from .symm import SymmetricBuffer
 
 SLOT_QKV, SLOT_ATTN = 4, 5
@@ -85,8 +86,9 @@ class UlyssesContext:
         base = 0 if part == "txt" else self.S_txt
         x2 = _flat2d(x)
         if self.mode == "fused":
-            _gemm([x2], [weight], bias=bias, route_ptrs=self.symm.ptrs_at(self.off_qkv),
-                  route_cfg=[self.Dl, self.D, base + self.rank * Sp, Sp, self.S, 3 * self.Dl])
+            with nvtx_range("collective/ulysses/qkv_scatter_gemm"):
+                _gemm([x2], [weight], bias=bias, route_ptrs=self.symm.ptrs_at(self.off_qkv),
+                      route_cfg=[self.Dl, self.D, base + self.rank * Sp, Sp, self.S, 3 * self.Dl])
         else:
             self._local_qkv[part] = ops.linear(x2, weight, bias).view(self.B, Sp, 3, self.world, self.Dl)
 
@@ -125,8 +127,9 @@ class UlyssesContext:
             base = self.symm.ptrs_at(self.off_att)
             ra = [p + col for p in base]
             rb = [p + self.St * self.D * 2 + col for p in base]
-            native.ops().attention_fwd(q, k, v, scale, None, False, None, ra, rb,
-                                       [self.St, self.S_txt, self.Si, self.Sl * self.D, self.D, Dh])
+            with nvtx_range("collective/ulysses/attention_row_scatter"):
+                native.ops().attention_fwd(q, k, v, scale, None, False, None, ra, rb,
+                                           [self.St, self.S_txt, self.Si, self.Sl * self.D, self.D, Dh])
             native.ops().flag_signal(self.symm.ptrs_at(0), SLOT_ATTN, self.rank, 0, self.flags, self.counters)
         else:
             o = ops.attention(q, k, v, scale).reshape(self.B, self.S, Dl)

@@ -22,6 +22,7 @@ import torch
 from ..io.png import encode_png, load_png, tensor_to_uint8
 from ..io.safetensors_io import load_safetensors
 from ..sampling import flow_match as fm
+from ..utils.tracing import nvtx_range
 from .backend import GenBackend, JobParams, StepResult, reject_unsupported_common
 
 _CONFIGS = {"flux": "flux1_dev_config", "tiny": "tiny_mmdit_config"}
@@ -72,25 +73,29 @@ class FluxBackend(GenBackend):
             return StepResult("cancelled")
         t0 = time.perf_counter()
         if self.phase == "encode":
-            self._encode(p)
+            with nvtx_range("stage/encode"):
+                self._encode(p)
             self.stage_s["encode"] = time.perf_counter() - t0
             self.phase = "load"
             return StepResult("progress", 0, p.steps, "load")         # announce what the NEXT tick does
         if self.phase == "load":
-            self._load(p)
-            self._prepare_latents(p)
+            with nvtx_range("stage/load"):
+                self._load(p)
+                self._prepare_latents(p)
             self.stage_s["load"] = time.perf_counter() - t0
             self.phase = "denoise"
             return StepResult("progress", 0, p.steps, "denoise")
         if self.phase == "denoise":
-            self._denoise_step()
+            with nvtx_range(f"stage/denoise/{self.i}"):
+                self._denoise_step()
             self.stage_s["denoise"] = self.stage_s.get("denoise", 0.0) + time.perf_counter() - t0
             self.i += 1
             if self.i >= self.n_steps:
                 self.phase = "decode"
                 return StepResult("progress", p.steps, p.steps, "decode")
             return StepResult("progress", self.i + (p.steps - self.n_steps), p.steps, "denoise")
-        path = self._decode_and_save(p)
+        with nvtx_range("stage/decode"):
+            path = self._decode_and_save(p)
         self.stage_s["decode"] = time.perf_counter() - t0
         self._write_sidecar(p, path)
         self.p = None

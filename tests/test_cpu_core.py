@@ -225,3 +225,34 @@ def test_euler_sampler_integrates_linear_field():
     out2 = fm.euler_flow_sample(lambda xb, s: v, x.clone(), fm.shifted_sigmas(7, 2.0), uncond_fn=lambda xb, s: 0 * v,
                                 cfg_scale=3.0, cfg_mode=fm.CFG_TEXTBOOK)
     assert torch.allclose(out2, x - 3.0 * v, atol=1e-5)
+
+
+def test_tracing_ranges_and_per_rank_metrics(tmp_path):
+    """NVTX ranges are off by default, name stage / block / collective when on; per-rank JSONL files aggregate on rank 0."""
+    import torch
+    from mojodiffusion_b200.models.mmdit import MMDiT, tiny_mmdit_config
+    from mojodiffusion_b200.utils import tracing
+    cfg = tiny_mmdit_config()
+    model = MMDiT(cfg, torch.float32, "cpu").init_weights(0).eval()
+    x, txt, y = torch.randn(1, 16, cfg.in_channels), torch.randn(1, 8, cfg.context_dim), torch.randn(1, cfg.vec_dim)
+    log = []
+    tracing.set_range_log(log)
+    try:
+        with torch.no_grad():
+            model(x, txt, torch.tensor([0.5]), y, torch.tensor([3.5]), hw=(4, 4))
+        assert log == []                                          # disabled: nothing recorded
+        tracing.enable_nvtx(True)
+        with torch.no_grad(), tracing.nvtx_range("stage/denoise/0"):
+            model(x, txt, torch.tensor([0.5]), y, torch.tensor([3.5]), hw=(4, 4))
+        assert log[0] == "stage/denoise/0" and "block/double/0" in log and f"block/single/{cfg.depth_single - 1}" in log
+    finally:
+        tracing.enable_nvtx(False)
+        tracing.set_range_log(None)
+    for r in range(2):
+        m = tracing.MetricsLog(str(tmp_path), r)
+        for s in range(3):
+            m.log(s, loss=1.0 / (s + 1) + r, ms_per_step=10.0 + r)
+        m.close()
+    agg = tracing.aggregate(str(tmp_path))
+    assert sorted(agg) == [0, 1, 2] and agg[0]["ms_per_step"] == {"min": 10.0, "max": 11.0, "mean": 10.5, "ranks": 2}
+    assert abs(agg[2]["loss"]["mean"] - (1 / 3 + 0.5)) < 1e-9

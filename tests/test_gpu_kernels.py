@@ -460,3 +460,36 @@ def test_bounded_wait_runs_out_and_reports_status():
     native.check_status(flags)                                             # the status word was reset by the read
     x, w = _rand(256, 128, seed=61), _rand(192, 128, scale=0.1, seed=62)
     _check(O.linear(x, w), ref.linear(x, w, out_dtype=torch.float32), name="gemm after a timed-out wait")
+
+
+def _poisoned(rows, cols, pad_r, pad_c, dtype=torch.bfloat16):
+    buf = torch.full((rows + 2 * pad_r, cols + 2 * pad_c), float("nan"), dtype=dtype, device=DEV)
+    return buf, buf[pad_r:pad_r + rows, pad_c:pad_c + cols]
+
+
+@pytest.mark.parametrize("M,N,K", [(200, 264, 72), (333, 1000, 520), (512, 768, 256), (130, 8, 64)])
+def test_gemm_writes_exactly_its_output_region(M, N, K):
+    """Race / overrun substitute for a memory checker: the output lives inside a NaN-filled buffer with guard rows and
+    columns; afterwards no NaN survives inside and every guard element is still NaN (nothing outside the tile was touched,
+    ragged edges included, for the direct and the shared-memory-staged epilogue)."""
+    x, w = _rand(M, K, seed=71), _rand(N, K, scale=1 / math.sqrt(K), seed=72)
+    buf, view = _poisoned(M, N, 3, 8)
+    from mojodiffusion_b200.ops.functional import _gemm
+    for bn in (0, 256, 512, 128, 64):
+        buf.fill_(float("nan"))
+        _gemm([x], [w], out=view, bn=bn)
+        _check(view, ref.linear(x, w, out_dtype=torch.float32), name=f"poison gemm bn={bn}")
+        guard = buf.clone()
+        guard[3:3 + M, 8:8 + N] = float("nan")
+        assert torch.isnan(guard).all(), f"bn={bn}: the kernel wrote outside its output"
+
+
+def test_attention_writes_exactly_its_output_region():
+    B, Sq, Skv, H, Dh = 1, 300, 200, 2, 128
+    q, k, v = _rand(B, Sq, H, Dh, seed=73), _rand(B, Skv, H, Dh, seed=74), _rand(B, Skv, H, Dh, seed=75)
+    buf = torch.full((B, Sq + 6, H, Dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = buf[:, 3:3 + Sq]
+    torch.ops.mdb200.attention_fwd(q, k, v, 1 / math.sqrt(Dh), None, False, out, [], [], [])
+    want = ref.attention(q, k, v, 1 / math.sqrt(Dh))
+    _check(out, want, cos=0.999, name="poison attention")
+    assert torch.isnan(buf[:, :3]).all() and torch.isnan(buf[:, 3 + Sq:]).all()

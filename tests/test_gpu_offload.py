@@ -78,3 +78,36 @@ def test_streamed_inference_and_lora_training_match_resident():
     torch.cuda.synchronize()
     native.check_status()
     assert loader.tel.await_calls >= 3 * (cfg.depth_double + cfg.depth_single)
+
+
+def test_streaming_is_bit_identical_under_permuted_stream_priorities():
+    """Race-detection substitute: the same streamed forward with the copy stream at default and at high priority, twice
+    each, after the slots were filled with a poison pattern. Every result must be bit-identical to the resident model: a
+    consumer that reads a slot before its copy landed (or a copy that overwrites a slot still in use) would differ."""
+    m, cfg = _model()
+    img, txt, t, y = _inputs(cfg)
+    g = torch.ones(1, device=DEV) if cfg.guidance_embed else None
+    with torch.no_grad():
+        ref = m(img, txt, t, y, g)
+    plan = flux_plan(cfg.depth_double, cfg.depth_single)
+    blocks = list(m.double_blocks) + list(m.single_blocks)
+    tensors = {s.prefix + n: p.detach().clone() for s, b in zip(plan.blocks, blocks) for n, p in b.named_parameters()}
+    for prio in (0, -1, 0, -1):
+        loader = BlockSwapLoader(PinnedBlockStore(plan, tensors), DEV, copy_stream_priority=prio)
+        for s in loader.slots:
+            s.fill_(0xFF)                                    # bf16 0xFFFF = NaN: any read of an unfilled slot poisons the output
+        torch.cuda.synchronize()
+        outs = []
+        for rep in range(2):
+            with torch.no_grad():
+                # every block's weights reach it only through the loader's slots
+                from mojodiffusion_b200.offload.streamed import StreamedStack
+                m.streamer = StreamedStack(blocks, loader)
+                try:
+                    outs.append(m(img, txt, t, y, g))
+                finally:
+                    m.streamer = None
+        torch.cuda.synchronize()
+        for o in outs:
+            assert torch.isfinite(o.float()).all() and torch.equal(o, ref), f"priority {prio}"
+    native.check_status()
