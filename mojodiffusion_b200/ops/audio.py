@@ -103,3 +103,76 @@ def log_mel(x: torch.Tensor, n_fft: int, hop: int, n_mels: int, sample_rate: int
     mag, _ = stft(x, n_fft, hop)
     fb = mel_filterbank(n_mels, n_fft, sample_rate).to(x.device)
     return torch.log(torch.clamp(fb @ mag, min=eps))
+
+
+# ---- anti-aliased activation and resampling (BigVGAN-v2 / torchaudio semantics) ---------------------------------------
+def kaiser_sinc_filter1d(cutoff: float, half_width: float, kernel_size: int) -> torch.Tensor:
+    """Kaiser-windowed sinc low-pass FIR [kernel_size], normalised to unit DC gain (the ratio-2 filters of the
+    anti-aliased activation use cutoff 0.5 / ratio, half width 0.6 / ratio, 12 taps)."""
+    even = kernel_size % 2 == 0
+    half = kernel_size // 2
+    delta_f = 4 * half_width
+    A_ = 2.285 * (half - 1) * math.pi * delta_f + 7.95
+    beta = 0.1102 * (A_ - 8.7) if A_ > 50.0 else (0.5842 * (A_ - 21) ** 0.4 + 0.07886 * (A_ - 21.0) if A_ >= 21.0 else 0.0)
+    window = torch.kaiser_window(kernel_size, beta=beta, periodic=False, dtype=torch.float64)
+    t = (torch.arange(-half, half, dtype=torch.float64) + 0.5) if even else (torch.arange(kernel_size, dtype=torch.float64) - half)
+    if cutoff == 0:
+        return torch.zeros(kernel_size)
+    f = 2 * cutoff * window * torch.sinc(2 * cutoff * t)
+    return (f / f.sum()).float()
+
+
+def activation1d(x: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, up_filter: Optional[torch.Tensor] = None,
+                 down_filter: Optional[torch.Tensor] = None, ratio: int = 2, log_scale: bool = True) -> torch.Tensor:
+    """Anti-aliased SnakeBeta: upsample by ``ratio`` with a kaiser-sinc FIR (replicate pad 5, zero insert, 12-tap filter,
+    gain ``ratio``, trim 15 / 15), apply the activation at the higher rate, low-pass and decimate back (replicate pad
+    5 / 6, stride ``ratio``). Length is preserved. x [B, C, L]; alpha / beta [C]
+    (serenitymojo/ops/activation1d.mojo:1-70)."""
+    B, Cc, Lx = x.shape
+    K = 12
+    if up_filter is None:
+        up_filter = kaiser_sinc_filter1d(0.5 / ratio, 0.6 / ratio, K)
+    if down_filter is None:
+        down_filter = kaiser_sinc_filter1d(0.5 / ratio, 0.6 / ratio, K)
+    uf = up_filter.to(x.device, torch.float32).view(1, 1, K)
+    df = down_filter.to(x.device, torch.float32).view(1, 1, K)
+    xf = x.float().reshape(B * Cc, 1, Lx)
+    pad = K // ratio - 1                                            # 5
+    y = zero_insert1d(replicate_pad1d(xf, pad, pad), ratio)
+    side = K - 1
+    y = TF.conv1d(TF.pad(y, (side, side)), uf) * float(ratio)
+    left = pad * ratio + (K - ratio) // 2                           # 15
+    right = pad * ratio + (K - ratio + 1) // 2                      # 15
+    y = y[..., left:y.shape[-1] - right]
+    y = snake(y.reshape(B, Cc, -1), alpha, beta, log_scale).float().reshape(B * Cc, 1, -1)
+    pl, pr = K // 2 - ratio // 2, K // 2 - ratio // 2 + (K % 2 == 0)  # 5, 6
+    out = TF.conv1d(replicate_pad1d(y, pl, pr), df, stride=ratio)
+    return out.reshape(B, Cc, -1).to(x.dtype)
+
+
+def resample_hann(x: torch.Tensor, orig_freq: int, new_freq: int, rolloff: float = 0.99, lowpass_filter_width: int = 6) -> torch.Tensor:
+    """Band-limited resampling as one strided convolution with a Hann-windowed sinc kernel bank (one phase per output sample
+    of a period): the rule of torchaudio's ``sinc_interp_hann``. x [B, C, L] -> [B, C, ceil(L * new / orig)]
+    (serenitymojo/ops/resample.mojo:1-40)."""
+    g = math.gcd(int(orig_freq), int(new_freq))
+    orig, new = int(orig_freq) // g, int(new_freq) // g
+    if orig == new:
+        return x
+    base = min(orig, new) * rolloff
+    width = int(math.ceil(lowpass_filter_width * orig / base))
+    idx = torch.arange(-width, width + orig, dtype=torch.float64)[None, None] / orig
+    t = (torch.arange(0, -new, -1, dtype=torch.float64)[:, None, None] / new + idx) * base
+    t = t.clamp(-lowpass_filter_width, lowpass_filter_width)
+    window = torch.cos(t * math.pi / lowpass_filter_width / 2) ** 2
+    t = t * math.pi
+    kern = torch.where(t == 0, torch.ones_like(t), torch.sin(t) / t) * window * (base / orig)       # [new, 1, K]
+    B, Cc, Lx = x.shape
+    xf = TF.pad(x.float().reshape(B * Cc, 1, Lx), (width, width + orig))
+    y = TF.conv1d(xf, kern.float().to(x.device), stride=orig)                                      # [B*C, new, L/orig]
+    y = y.transpose(1, 2).reshape(B, Cc, -1)
+    return y[..., :int(math.ceil(new * Lx / orig))].to(x.dtype)
+
+
+def sinc_upsample(x: torch.Tensor, ratio: int) -> torch.Tensor:
+    """Integer-ratio band-limited upsampling (the skip path of the bandwidth-extension vocoder)."""
+    return resample_hann(x, 1, ratio)
