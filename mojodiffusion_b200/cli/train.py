@@ -72,7 +72,15 @@ def main(argv=None) -> int:
     if not cache_dir or not os.path.isdir(cache_dir):
         print(f"error: no latent cache directory (cache_dir / dataset_cache_dir / dataset_path): '{cache_dir}'", file=sys.stderr)
         return 2
-    cache = LatentCache(cache_dir)
+    controlnet = cfg.training_method.upper() == "CONTROLNET"
+    if controlnet and m.family != "zimage":
+        print(f"error: training_method CONTROLNET is defined for the Z-Image family, not '{m.family}'", file=sys.stderr)
+        return 2
+    try:
+        cache = LatentCache(cache_dir, require_control=controlnet)
+    except Exception as e:                                  # a ControlNet run needs control_latent in every sample
+        print(f"error: latent cache: {e}", file=sys.stderr)
+        return 2
     pf = preflight(cfg, m, cache, tiny)
     prompts = None
     pfile = cfg.validation_prompts_file or cfg.sample_definition_file_name
@@ -142,11 +150,31 @@ def main(argv=None) -> int:
             from ..parallel.dp import DataParallelGrads, broadcast_parameters
             broadcast_parameters(params)
             dp = DataParallelGrads(params)
+    elif method == "CONTROLNET":
+        # frozen base + trainable control branch (copy-from-base blocks, zero projections); its own optimizer group
+        from ..models.zimage_controlnet import ControlledZImage, ZImageControlNet, load_controlnet
+        from ..training.full_finetune import prepare_full_finetune
+        slots = []
+        n_ctrl = cfg.controlnet_layers or max(1, model.cfg.depth // 5)
+        net = ZImageControlNet(model.cfg, n_ctrl, dtype=next(model.parameters()).dtype, device=dev).init_from_base(model)
+        ck = str(cfg.extra.get("controlnet_checkpoint", ""))
+        if ck:
+            load_controlnet(net, ck)
+        model = ControlledZImage(model, net, cfg.controlnet_scale)
+        inventory, opt = prepare_full_finetune(net, cfg.learning_rate, betas=(ocfg.beta1, ocfg.beta2), eps=ocfg.eps,
+                                               weight_decay=ocfg.weight_decay, max_grad_norm=cfg.max_grad_norm)
+        params = [p for _, p in inventory]
+        if world > 1:
+            from ..parallel.dp import DataParallelGrads, broadcast_parameters
+            broadcast_parameters(params)
+            dp = DataParallelGrads(params)
     else:
-        print(f"error: training_method '{cfg.training_method}' is not LORA or FINE_TUNE", file=sys.stderr)
+        print(f"error: training_method '{cfg.training_method}' is not LORA, FINE_TUNE or CONTROLNET", file=sys.stderr)
         return 2
-    if cfg.gradient_checkpointing.upper() != "OFF" and hasattr(model, "gradient_checkpointing"):
-        model.gradient_checkpointing = True
+    if cfg.gradient_checkpointing.upper() != "OFF":
+        for mod in (model, getattr(model, "base", None)):
+            if mod is not None and hasattr(mod, "gradient_checkpointing"):
+                mod.gradient_checkpointing = True
     model.train()
     trainer = FamilyTrainer(adapter, model, params, opt, cfg, dp, StepConfig(seed=cfg.seed, rank=rank, world=world,
                                                                               guidance=float(cfg.extra.get("train_guidance", 1.0))))

@@ -163,7 +163,24 @@ class SingleStreamDiT(nn.Module):
         ids[n_cap:, 2] = torch.arange(w, device=device, dtype=torch.float32)[None, :].expand(h, w).reshape(-1)
         return ids
 
-    def forward(self, img, cap, t, hw: Optional[Tuple[int, int]] = None, cap_len: Optional[torch.Tensor] = None):
+    def forward(self, img, cap, t, hw: Optional[Tuple[int, int]] = None, cap_len: Optional[torch.Tensor] = None,
+                control=None, control_scale: float = 1.0):
+        """``control`` = (ZImageControlNet, control tokens [B, S_img, control_in]): the control branch's per-layer hints are
+        added after the main layers it names (serenitymojo/models/zimage/controlnet_block.mojo:20-24)."""
+        st = self.embed(img, cap, t, hw, cap_len)
+        hints = None
+        if control is not None:
+            net, ctrl = control
+            hints = net(self, st, ctrl, control_scale)
+        return self.run_layers(st, hints)
+
+    def _run(self, blk, *a):
+        if self.gradient_checkpointing and torch.is_grad_enabled():
+            return torch.utils.checkpoint.checkpoint(blk, *a, use_reentrant=False, preserve_rng_state=False)
+        return blk(*a)
+
+    def embed(self, img, cap, t, hw=None, cap_len=None) -> dict:
+        """Everything before the main layers: embeddings, both refiners and the unified (image-first) sequence."""
         cfg = self.cfg
         B, S_img, _ = img.shape
         S_cap = cap.shape[1]
@@ -179,25 +196,24 @@ class SingleStreamDiT(nn.Module):
         if cap_len is not None:                                             # padded captions -> learned pad token
             pad = torch.arange(S_cap, device=img.device)[None, :] >= cap_len[:, None]
             y = torch.where(pad[..., None], self.cap_pad_token.to(y.dtype)[None], y)
-        ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
-
-        def run(blk, *a):
-            if ckpt:
-                return torch.utils.checkpoint.checkpoint(blk, *a, use_reentrant=False, preserve_rng_state=False)
-            return blk(*a)
-
         for blk in self.context_refiner:
-            y = run(blk, y, cos[:S_cap], sin[:S_cap])
+            y = self._run(blk, y, cos[:S_cap], sin[:S_cap])
         for blk in self.noise_refiner:
-            x = run(blk, x, cos[S_cap:], sin[S_cap:], c)
+            x = self._run(blk, x, cos[S_cap:], sin[S_cap:], c)
         # image tokens first so a caption padding mask is a pure key-length mask
         h = torch.cat((x, y), dim=1)
         cos_j = torch.cat((cos[S_cap:], cos[:S_cap]), 0).contiguous()
         sin_j = torch.cat((sin[S_cap:], sin[:S_cap]), 0).contiguous()
         kv_len = (S_img + cap_len).to(torch.int32) if cap_len is not None else None
-        for blk in self.layers:
-            h = run(blk, h, cos_j, sin_j, c, kv_len)
-        return self.all_final_layer["2-1"](h[:, :S_img], c)
+        return dict(h=h, cap=y, c=c, cos=cos_j, sin=sin_j, cos_img=cos[S_cap:], sin_img=sin[S_cap:], kv_len=kv_len, S_img=S_img, dt=dt)
+
+    def run_layers(self, st: dict, hints=None):
+        h = st["h"]
+        for i, blk in enumerate(self.layers):
+            h = self._run(blk, h, st["cos"], st["sin"], st["c"], st["kv_len"])
+            if hints is not None and i in hints:
+                h = h + hints[i]
+        return self.all_final_layer["2-1"](h[:, :st["S_img"]], st["c"])
 
     def init_weights(self, seed: int = 0, std: float = 0.02):
         return init_module_weights(self, seed, std)

@@ -29,6 +29,7 @@ class Cond:
     hw: Optional[Tuple[int, int]] = None    # token grid (rows, cols) of packed image latents
     grid: Optional[Tuple[int, int, int]] = None   # (frames, rows, cols) of video latents
     guidance: float = 1.0
+    control: Optional[torch.Tensor] = None  # packed, normalised control latent (ControlNet training / sampling)
 
 
 class FamilyAdapter:
@@ -96,6 +97,8 @@ class FamilyAdapter:
         if f == "qwenimage":
             return model(x, c.txt, sigma, c.hw, c.txt_len)
         if f == "zimage":
+            if c.control is not None:
+                return -model(x, c.txt, 1.0 - sigma, c.hw, c.txt_len, control=c.control.to(x.dtype))
             return -model(x, c.txt, 1.0 - sigma, c.hw, c.txt_len)     # the model's clock runs from noise (0) to image (1)
         if f == "sd3":
             return model(x, c.txt, sigma, c.pooled)

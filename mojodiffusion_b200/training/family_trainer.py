@@ -53,7 +53,7 @@ class FamilyTrainer:
 
     def loss_and_backward(self, batch: Dict[str, torch.Tensor], loss_scale: float = 1.0) -> torch.Tensor:
         """batch: ``latent`` [B,C,h,w] (VAE space, unscaled), ``text_embedding`` [B,T,D], ``text_mask`` [B,T], optional
-        ``pooled`` [B,P], ``latent_mask``. Returns the detached loss."""
+        ``pooled`` [B,P], ``latent_mask``, ``control_latent`` [B,C,h,w] (ControlNet). Returns the detached loss."""
         m, c = self.a.m, self.cfg
         dev = next(self.model.parameters()).device
         dt = next(self.model.parameters()).dtype
@@ -66,6 +66,10 @@ class FamilyTrainer:
         pooled = batch.get("pooled")
         cond = self.a.conditioning(cond, text, batch.get("text_mask"), pooled.to(dev, dt) if pooled is not None else None,
                                    self.model.cfg, guidance=self.sc.guidance)
+        ctrl = batch.get("control_latent")
+        if ctrl is not None:                          # the control image enters as a VAE latent with the training normalisation
+            cl = (ctrl.to(dev, torch.float32) - m.latent.shift) * m.latent.scale
+            cond.control, _ = self.a.to_model_space(cl)
         B = x0.shape[0]
         noise = ops.randn(tuple(x0.shape), seed=self._seed * 7919 + self.step_index, device=dev).float()
         mask = batch.get("latent_mask")
