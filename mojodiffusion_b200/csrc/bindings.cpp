@@ -347,6 +347,17 @@ std::tuple<Tensor, Tensor, Tensor> attention_bwd(const Tensor& q, const Tensor& 
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t B = q.size(0), Sq = q.size(1), H = q.size(2), Dh = q.size(3), Skv = k.size(1);
   TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == B * H * Sq, "attention_bwd: lse");
+  for (const Tensor* t : {&k, &v, &o, &dout})
+    TORCH_CHECK(t->is_cuda() && t->device() == q.device() && t->dim() == 4 && t->scalar_type() == at::kBFloat16,
+                "attention_bwd: k, v, o and dout must be [B,S,H,Dh] bf16 on q's device");
+  TORCH_CHECK(lse.is_cuda() && lse.device() == q.device(), "attention_bwd: lse must be on q's device");
+  TORCH_CHECK(k.size(0) == B && v.size(0) == B && k.size(2) == H && v.size(2) == H && k.size(3) == Dh && v.size(3) == Dh &&
+                  v.size(1) == Skv, "attention_bwd: k / v shapes must be [B,Skv,H,Dh]");
+  TORCH_CHECK(o.sizes() == q.sizes() && dout.sizes() == q.sizes(), "attention_bwd: o and dout must have q's shape");
+  TORCH_CHECK(Dh == 64 || Dh == 128, "attention_bwd: head dim 64 or 128");
+  if (kv_len.has_value() && kv_len->defined())
+    TORCH_CHECK(kv_len->is_cuda() && kv_len->scalar_type() == at::kInt && kv_len->is_contiguous() && kv_len->numel() == B,
+                "attention_bwd: kv_len must be [B] int32 on the device");
   // outs: empty, or {dq, dk, dv} views to write into (e.g. the three column ranges of one packed gradient buffer)
   TORCH_CHECK(outs.empty() || outs.size() == 3, "attention_bwd: outs must be {dq, dk, dv}");
   Tensor dq = outs.empty() ? at::empty({B, Sq, H, Dh}, q.options()) : outs[0];

@@ -458,6 +458,52 @@ __device__ __forceinline__ float ex2_poly(float x) {
   pz = fmaf(pz, f, 1.0f);
   return __int_as_float(__float_as_int(pz) + (__float_as_int(y) << 23));
 }
+// Packed fp32 pairs (one issue slot for two lanes of work on sm_100): fma / add on 64-bit register pairs, and the
+// three-input maximum. The softmax loops of the attention kernels are bound by issue slots, not by data.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2_rm(float2 a, float2 b) {     // rounded toward minus infinity
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rm.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float d;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(d) : "f"(x));
+  return d;
+}
+// ex2_poly on a pair: the floor / fraction split and the polynomial run as packed operations.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 y = fadd2_rm(x, make_float2(12582912.f, 12582912.f));
+  const float2 fl = fadd2(y, make_float2(-12582912.f, -12582912.f));          // exact
+  const float2 f = ffma2(fl, make_float2(-1.f, -1.f), x);
+  float2 pz = ffma2(make_float2(0.07706727f, 0.07706727f), f, make_float2(0.22764474f, 0.22764474f));
+  pz = ffma2(pz, f, make_float2(0.6951168f, 0.6951168f));
+  pz = ffma2(pz, f, make_float2(1.0f, 1.0f));
+  return make_float2(__int_as_float(__float_as_int(pz.x) + (__float_as_int(y.x) << 23)),
+                     __int_as_float(__float_as_int(pz.y) + (__float_as_int(y.y) << 23)));
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

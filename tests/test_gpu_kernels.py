@@ -202,6 +202,25 @@ def test_attention_strided_and_masked():
     _check(out, ref.attention(q, k, v, kv_len=kv_len).float(), cos=0.999, rel=3e-2, name="kv_len mask")
 
 
+def test_attention_late_large_maximum_is_exact():
+    """The exponent reference of a key tile is the row maximum of the EARLIER tiles; rows whose scores jump far above it
+    (here by more than 60 nats, several such keys of different height in one tile) take the redo path."""
+    B, S, H, Dh = 1, 1024, 2, 128
+    q, k, v = _rand(B, S, H, Dh, seed=50), _rand(B, S, H, Dh, seed=51), _rand(B, S, H, Dh, seed=52)
+    qn = q.float() / q.float().norm(dim=-1, keepdim=True)
+    k = k.clone()
+    for key, row, gain in ((700, 5, 9000.0), (710, 5, 8900.0), (705, 300, 12000.0), (900, 640, 20000.0), (130, 64, 7000.0)):
+        k[0, key] = (qn[0, row] * gain / math.sqrt(Dh)).to(torch.bfloat16)      # logit of (row, key) ~ gain / Dh * |q|
+    out, lse = torch.ops.mdb200.attention_fwd(q, k, v, 1 / math.sqrt(Dh), None, True, None, [], [], [])
+    assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    want, lse_ref = ref.attention(q, k, v, return_lse=True)
+    _check(out, want.float(), cos=0.999, rel=3e-2, name="late maximum")
+    _check(lse, lse_ref, cos=0.9999, rel=1e-2, name="late maximum lse")
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) / math.sqrt(Dh)
+    first = s[..., :128].amax(-1)
+    assert float((s.amax(-1) - first).max()) > 60.0                            # the case really occurs in this input
+
+
 def test_attention_lse_and_backward():
     B, S, H, Dh = 1, 384, 2, 128
     q, k, v = [_rand(B, S, H, Dh, seed=40 + i).requires_grad_(True) for i in range(3)]
@@ -215,6 +234,58 @@ def test_attention_lse_and_backward():
     _, lse = torch.ops.mdb200.attention_fwd(q.detach(), k.detach(), v.detach(), 1 / math.sqrt(Dh), None, True, None, [], [], [])
     _, lse_ref = ref.attention(q.detach(), k.detach(), v.detach(), return_lse=True)
     _check(lse, lse_ref, cos=0.9999, rel=1e-2, name="lse")
+
+
+def _sinusoid(B, S, H, Dh, phase):
+    """Deterministic fill that repeats over no axis: a gradient written to the wrong head, row or column changes the
+    result (a random fill with equal statistics per head can hide a head mix-up behind a good cosine)."""
+    b = torch.arange(B, device=DEV, dtype=torch.float32).view(B, 1, 1, 1)
+    s = torch.arange(S, device=DEV, dtype=torch.float32).view(1, S, 1, 1)
+    h = torch.arange(H, device=DEV, dtype=torch.float32).view(1, 1, H, 1)
+    d = torch.arange(Dh, device=DEV, dtype=torch.float32).view(1, 1, 1, Dh)
+    x = torch.sin(0.37 * s + 1.3 * h + 0.11 * d + 0.7 * b + phase) + 0.5 * torch.cos(0.013 * s * (h + 1) - 0.29 * d + phase)
+    return (0.7 * x).to(torch.bfloat16)
+
+
+ATT_BWD_CASES = [  # B, Sq, Skv, H, Dh, masked
+    (1, 1248, 1248, 24, 128, False), (1, 1536, 1536, 30, 128, False), (1, 4608, 4608, 32, 128, False),
+    (1, 1536, 1536, 30, 64, False), (2, 1248, 640, 24, 128, False), (1, 640, 1536, 32, 64, False),
+    (2, 1536, 1536, 30, 128, True), (2, 1000, 520, 3, 64, True),
+]
+
+
+@pytest.mark.parametrize("B,Sq,Skv,H,Dh,masked", ATT_BWD_CASES)
+def test_attention_backward_matrix(B, Sq, Skv, H, Dh, masked):
+    """Head counts 24 / 30 / 32 (30 is not a power of two and once produced all-zero dq / dk in the reference), ragged and
+    rectangular sequence lengths, key-length masks, both head sizes; gradients against fp32 autograd, per head."""
+    q, k, v = _sinusoid(B, Sq, H, Dh, 0.0), _sinusoid(B, Skv, H, Dh, 1.0), _sinusoid(B, Skv, H, Dh, 2.0)
+    dout = _sinusoid(B, Sq, H, Dh, 3.0)
+    kv_len = torch.tensor([max(1, Skv // 3), Skv][:B], dtype=torch.int32, device=DEV) if masked else None
+    scale = 1 / math.sqrt(Dh)
+    o, lse = torch.ops.mdb200.attention_fwd(q, k, v, scale, kv_len, True, None, [], [], [])
+    dq, dk, dv = torch.ops.mdb200.attention_bwd(q, k, v, o, lse, dout, scale, kv_len, [])
+    qr, kr, vr = [t.float().requires_grad_(True) for t in (q, k, v)]
+    ref.attention(qr, kr, vr, kv_len=kv_len).backward(dout.float())
+    for name, got, want in (("dq", dq, qr.grad), ("dk", dk, kr.grad), ("dv", dv, vr.grad)):
+        assert torch.isfinite(got).all(), name
+        if masked:                                         # keys past kv_len receive exactly no gradient
+            if name in ("dk", "dv"):
+                assert float(got[0, int(kv_len[0]):].float().abs().max()) == 0.0, name
+        g, w = got.float(), want.float()
+        per_head = torch.nn.functional.cosine_similarity(g.permute(2, 0, 1, 3).reshape(H, -1), w.permute(2, 0, 1, 3).reshape(H, -1), dim=1)
+        assert float(per_head.min()) > 0.99, f"{name}: worst head cosine {float(per_head.min()):.5f} (head {int(per_head.argmin())})"
+        assert float(g.abs().amax(dim=(0, 1, 3)).min()) > 0, f"{name}: a head received no gradient"
+        _check(got, want, cos=0.995, rel=8e-2, name=f"{name} {B},{Sq},{Skv},{H},{Dh}")
+
+
+def test_attention_backward_rejects_bad_arguments():
+    q, k, v = _rand(1, 256, 2, 128, seed=1), _rand(1, 256, 2, 128, seed=2), _rand(1, 256, 2, 128, seed=3)
+    o, lse = torch.ops.mdb200.attention_fwd(q, k, v, 0.1, None, True, None, [], [], [])
+    for bad in (dict(k=k[:, :, :1]), dict(v=v.float()), dict(o=o[:, :128]), dict(dout=o.cpu()), dict(kv_len=torch.zeros(1, dtype=torch.int64, device=DEV))):
+        a = dict(q=q, k=k, v=v, o=o, lse=lse, dout=o, kv_len=None)
+        a.update(bad)
+        with pytest.raises(RuntimeError):
+            torch.ops.mdb200.attention_bwd(a["q"], a["k"], a["v"], a["o"], a["lse"], a["dout"], 0.1, a["kv_len"], [])
 
 
 @pytest.mark.parametrize("rows,D", [(7, 64), (300, 256), (4608, 3072), (33, 4096), (5, 12288)])
