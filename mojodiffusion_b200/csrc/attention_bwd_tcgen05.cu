@@ -83,7 +83,7 @@ attention_bwd_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
   __shared__ uint64_t r_full, c_full[CST], c_empty[CST], xy_full[2], pds_full[2], lv_full[2], acc_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
-  __shared__ float s_lse2[2][CB], s_delta[2][CB];
+  __shared__ __align__(8) float s_lse2[2][CB], s_delta[2][CB];      // NEGATED lse * log2(e) and delta per staged query
 
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -280,8 +280,8 @@ attention_bwd_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         if (mt < CB) {
           if (i >= 2) lv_ok = mbar_wait(&pds_full[buf], ((i - 2) >> 1) & 1, &abort_s);
           const int q = i * CB + mt;
-          s_lse2[buf][mt] = q < p.Sq ? p.lse[lse_base + q] * LOG2E : INFINITY;
-          s_delta[buf][mt] = q < p.Sq ? p.delta[lse_base + q] : 0.f;
+          s_lse2[buf][mt] = q < p.Sq ? -p.lse[lse_base + q] * LOG2E : -INFINITY;
+          s_delta[buf][mt] = q < p.Sq ? -p.delta[lse_base + q] : 0.f;
           mbar_arrive(&lv_full[buf]);
         }
         lv_ok = mbar_wait(&lv_full[buf], (i >> 1) & 1, &abort_s) && lv_ok;
@@ -306,31 +306,50 @@ attention_bwd_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         tmem_ld_32x32b_x32(ya + c * 32, yr);
         tmem_wait_ld();
         uint32_t pk[16], dk[16];
+        // Four columns per step as packed pairs: exponent = x * scale - lse2 and (dP - delta) are one packed operation
+        // each; with exp_poly the odd columns' exponentials run as a packed polynomial on the FMA pipe.
+        const float2 sl2_2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2 my_nl2 = make_float2(-my_lse2, -my_lse2), my_ndl = make_float2(-my_delta, -my_delta);
+        const bool tail = !KV_MODE && (i * CB + CB > kv_valid);
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;
-            float l2, dl;
-            bool valid;
-            if (KV_MODE) {
-              l2 = s_lse2[buf][col];
-              dl = s_delta[buf][col];
-              valid = row_key_valid;
-            } else {
-              l2 = my_lse2;
-              dl = my_delta;
-              valid = (i * CB + col) < kv_valid;
-            }
-            const float ex = fmaf(__uint_as_float(xr[e + u]), p.scale_log2, -l2);
-            float pe = (u && p.exp_poly) ? ex2_poly(ex) : exp2f(ex);   // every other exponential off the special-function unit
-            if (!valid) pe = 0.f;
-            pv[u] = pe;
-            dv[u] = pe * (__uint_as_float(yr[e + u]) - dl);
+        for (int e = 0; e < 32; e += 4) {
+          const int col = c * 32 + e;
+          float2 nl01, nl23, nd01, nd23;
+          if (KV_MODE) {
+            nl01 = *reinterpret_cast<const float2*>(&s_lse2[buf][col]);
+            nl23 = *reinterpret_cast<const float2*>(&s_lse2[buf][col + 2]);
+            nd01 = *reinterpret_cast<const float2*>(&s_delta[buf][col]);
+            nd23 = *reinterpret_cast<const float2*>(&s_delta[buf][col + 2]);
+          } else {
+            nl01 = nl23 = my_nl2;
+            nd01 = nd23 = my_ndl;
           }
-          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
+          const float2 x01 = ffma2(make_float2(__uint_as_float(xr[e]), __uint_as_float(xr[e + 1])), sl2_2, nl01);
+          const float2 x23 = ffma2(make_float2(__uint_as_float(xr[e + 2]), __uint_as_float(xr[e + 3])), sl2_2, nl23);
+          float2 p01, p23;
+          if (p.exp_poly) {
+            const float2 b = ex2_poly2(make_float2(x01.y, x23.y));
+            p01 = make_float2(ex2_approx(x01.x), b.x);
+            p23 = make_float2(ex2_approx(x23.x), b.y);
+          } else {
+            p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
+            p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
+          }
+          if (KV_MODE) {
+            if (!row_key_valid) p01 = p23 = make_float2(0.f, 0.f);
+          } else if (tail) {
+            const int k0 = i * CB + col;
+            if (k0 >= kv_valid) p01.x = 0.f;
+            if (k0 + 1 >= kv_valid) p01.y = 0.f;
+            if (k0 + 2 >= kv_valid) p23.x = 0.f;
+            if (k0 + 3 >= kv_valid) p23.y = 0.f;
+          }
+          const float2 d01 = fmul2(p01, fadd2(make_float2(__uint_as_float(yr[e]), __uint_as_float(yr[e + 1])), nd01));
+          const float2 d23 = fmul2(p23, fadd2(make_float2(__uint_as_float(yr[e + 2]), __uint_as_float(yr[e + 3])), nd23));
+          pk[e >> 1] = pack_bf16x2(p01.x, p01.y);
+          pk[(e >> 1) + 1] = pack_bf16x2(p23.x, p23.y);
+          dk[e >> 1] = pack_bf16x2(d01.x, d01.y);
+          dk[(e >> 1) + 1] = pack_bf16x2(d23.x, d23.y);
         }
         if (KV_MODE) tmem_st_32x32b_x16(xa + c * 16, pk);
         tmem_st_32x32b_x16(ya + c * 16, dk);
