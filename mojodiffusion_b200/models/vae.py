@@ -283,3 +283,108 @@ class AutoencoderKL(nn.Module):
 
     def init_weights(self, seed: int = 0, std: float = 0.05):
         return init_module_weights(self, seed, std)
+
+
+# ---- diffusers key layout, Z-Image and FLUX.2 / Klein variants ---------------------------------------------------------
+def zimage_vae_config():
+    """The Z-Image VAE is the 16-channel FLUX autoencoder (scale 0.3611, shift 0.1159, no post-quant convolution) stored
+    under diffusers names (serenitymojo/models/vae/zimage_decoder.mojo:1-27)."""
+    return VAEConfig(name="zimage-vae")
+
+
+def klein_vae_config():
+    return VAEConfig(z_channels=32, scale_factor=1.0, shift_factor=0.0, name="flux2-klein-vae")
+
+
+_ATTN_LEAF = {"group_norm": "norm", "to_q": "q", "to_k": "k", "to_v": "v", "to_out.0": "proj_out", "query": "q", "key": "k", "value": "v",
+              "proj_attn": "proj_out"}
+
+
+def remap_diffusers_vae_keys(sd, n_levels: int = 4):
+    """diffusers AutoencoderKL names -> the LDM names of this module. Decoder ``up_blocks.{g}`` run from the deepest level,
+    LDM ``up.{n-1-g}`` stores them by resolution; ``resnets.{j}`` -> ``block.{j}``, ``upsamplers.0.conv`` ->
+    ``upsample.conv``, ``downsamplers.0.conv`` -> ``downsample.conv``, ``conv_shortcut`` -> ``nin_shortcut``,
+    ``mid_block.resnets.{0,1}`` -> ``mid.block_{1,2}``, ``mid_block.attentions.0.{group_norm,to_q,to_k,to_v,to_out.0}`` ->
+    ``mid.attn_1.{norm,q,k,v,proj_out}`` with linear weights [C, C] reshaped to 1x1 convolutions, ``conv_norm_out`` ->
+    ``norm_out``. Other keys (``quant_conv``, ``post_quant_conv``, ``bn.*``) pass through."""
+    import re
+    out = {}
+    for k, v in sd.items():
+        n = k
+        m = re.match(r"(encoder|decoder)\.(.*)", k)
+        if m:
+            side, rest = m.group(1), m.group(2)
+            rest = rest.replace("conv_norm_out.", "norm_out.").replace("conv_shortcut.", "nin_shortcut.")
+            mm = re.match(r"up_blocks\.(\d+)\.resnets\.(\d+)\.(.*)", rest)
+            if mm:
+                rest = f"up.{n_levels - 1 - int(mm.group(1))}.block.{mm.group(2)}.{mm.group(3)}"
+            elif (mm := re.match(r"up_blocks\.(\d+)\.upsamplers\.0\.(.*)", rest)):
+                rest = f"up.{n_levels - 1 - int(mm.group(1))}.upsample.{mm.group(2)}"
+            elif (mm := re.match(r"down_blocks\.(\d+)\.resnets\.(\d+)\.(.*)", rest)):
+                rest = f"down.{mm.group(1)}.block.{mm.group(2)}.{mm.group(3)}"
+            elif (mm := re.match(r"down_blocks\.(\d+)\.downsamplers\.0\.(.*)", rest)):
+                rest = f"down.{mm.group(1)}.downsample.{mm.group(2)}"
+            elif (mm := re.match(r"mid_block\.resnets\.(\d)\.(.*)", rest)):
+                rest = f"mid.block_{int(mm.group(1)) + 1}.{mm.group(2)}"
+            elif (mm := re.match(r"mid_block\.attentions\.0\.(.*)\.(weight|bias)", rest)):
+                leaf = _ATTN_LEAF.get(mm.group(1), mm.group(1))
+                rest = f"mid.attn_1.{leaf}.{mm.group(2)}"
+                if mm.group(2) == "weight" and v.dim() == 2:
+                    v = v[:, :, None, None]
+            n = f"{side}.{rest}"
+        out[n] = v
+    return out
+
+
+class KleinVAE(AutoencoderKL):
+    """FLUX.2 / Klein autoencoder: 32 latent channels at 1/8 resolution, exchanged with the transformer as 128 packed
+    channels at 1/16 (2 x 2 pixel-unshuffle, packed channel = (c * 2 + dy) * 2 + dx) normalised by a BatchNorm's running
+    statistics (eps 1e-4, no affine part). decode: inverse BatchNorm -> unpack -> post_quant_conv -> decoder; encode:
+    encoder -> quant_conv -> posterior mean -> pack -> BatchNorm
+    (serenitymojo/models/vae/klein_decoder.mojo:36-96,207-256, klein_encoder.mojo:13-27)."""
+
+    BN_EPS = 1e-4
+
+    def __init__(self, cfg: Optional[VAEConfig] = None, dtype=torch.float32, device=None, with_encoder: bool = True):
+        cfg = cfg or klein_vae_config()
+        super().__init__(cfg, dtype, device, with_encoder)
+        z = cfg.z_channels
+        self.post_quant_conv = Conv2d(z, z, 1, dtype=dtype, device=device)
+        if with_encoder:
+            self.quant_conv = Conv2d(2 * z, 2 * z, 1, dtype=dtype, device=device)
+        bn = nn.Module()
+        bn.register_buffer("running_mean", torch.zeros(4 * z, dtype=torch.float32, device=device))
+        bn.register_buffer("running_var", torch.ones(4 * z, dtype=torch.float32, device=device))
+        self.bn = bn
+
+    @property
+    def spatial_factor(self) -> int:
+        return 2 ** (len(self.cfg.ch_mult) - 1) * 2
+
+    @staticmethod
+    def pack(z):
+        B, Cc, H, W = z.shape
+        return z.reshape(B, Cc, H // 2, 2, W // 2, 2).permute(0, 1, 3, 5, 2, 4).reshape(B, Cc * 4, H // 2, W // 2)
+
+    @staticmethod
+    def unpack(zp):
+        B, Cp, H, W = zp.shape
+        return zp.reshape(B, Cp // 4, 2, 2, H, W).permute(0, 1, 4, 2, 5, 3).reshape(B, Cp // 4, H * 2, W * 2)
+
+    def decode(self, zp):
+        dt = self.decoder.conv_in.weight.dtype
+        std = torch.sqrt(self.bn.running_var.float() + self.BN_EPS).view(1, -1, 1, 1)
+        z = self.unpack(zp.float() * std + self.bn.running_mean.float().view(1, -1, 1, 1))
+        h = self.post_quant_conv(z.permute(0, 2, 3, 1).to(dt))
+        return self.decoder(h).permute(0, 3, 1, 2)
+
+    def encode(self, img, sample: bool = False, generator=None):
+        dt = self.decoder.conv_in.weight.dtype
+        mom = self.quant_conv(self.encoder(img.permute(0, 2, 3, 1).to(dt))).float()
+        mean, logvar = mom.chunk(2, dim=-1)
+        z = mean
+        if sample:
+            z = mean + torch.exp(0.5 * logvar.clamp(-30.0, 20.0)) * torch.randn(mean.shape, generator=generator, device=mean.device)
+        zp = self.pack(z.permute(0, 3, 1, 2))
+        inv = torch.rsqrt(self.bn.running_var.float() + self.BN_EPS).view(1, -1, 1, 1)
+        return (zp - self.bn.running_mean.float().view(1, -1, 1, 1)) * inv
