@@ -240,11 +240,15 @@ class GenericBackend(GenBackend):
             from ..models.video_vae import VideoVAE, ltx2_vae_config, tiny_video_vae_config
             vcfg = dataclasses.replace(tiny_video_vae_config(), latent_channels=self.cfg.in_channels) if self.tiny else ltx2_vae_config()
             vae = VideoVAE(vcfg, self.dtype, self.device)
-        else:
+        elif self.tiny or self.kind not in ("klein", "qwenimage", "zimage"):
             vae = AutoencoderKL(self._vae_config(), self.dtype, self.device, with_encoder=False)
+        else:                                   # families whose autoencoder is not the plain LDM one
+            from ..models.vae_factory import build_family_vae
+            vae = build_family_vae(self.kind, self.dtype, self.device, False)
         vpath = os.path.join(root, p.vae) if (root and p.vae) else ""
         if vpath and os.path.isfile(vpath):
-            vae.load_state_dict(load_safetensors(vpath, device=str(self.device), dtype=self.dtype), strict=False)
+            from ..models.vae_factory import load_vae_weights
+            load_vae_weights(vae, vpath, self.device, self.dtype)
         else:
             vae.init_weights(seed=1)
         self.model, self.vae = model.eval(), vae.eval()
@@ -274,8 +278,8 @@ class GenericBackend(GenBackend):
             self.sigmas = fm.ltx2_linear_quadratic_sigmas(p.steps)
             self.x = noise.float().to(dev)
             return
-        f = self.vae.spatial_factor
-        C = self.vae.cfg.z_channels
+        from ..models.vae_factory import latent_geometry
+        C, f = latent_geometry(self.vae)
         h, w = p.height // f, p.width // f
         noise = torch.randn(1, C, h, w, generator=g)
         if self.kind == "sdxl":
@@ -358,7 +362,8 @@ class GenericBackend(GenBackend):
         if self.kind == "ltx2":
             return self._decode_video(p)
         z = self.x if self.kind in ("sdxl", "sd3") else unpack_latents(self.x, self.hw[0], self.hw[1])
-        img = self.vae.tiled_decode(z) if max(z.shape[-2:]) > 96 else self.vae.decode(z)
+        from ..models.vae_factory import decode_latent
+        img = decode_latent(self.vae, z)
         arr = tensor_to_uint8(img[0].float().permute(1, 2, 0).cpu()).numpy()
         os.makedirs(p.out_dir or ".", exist_ok=True)
         path = p.output_path()

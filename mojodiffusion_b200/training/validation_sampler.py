@@ -74,12 +74,13 @@ class ValidationSampler:
             if self.tiny:
                 zc = self.model.cfg.in_channels // (self.m.latent.patch ** 2) if self.m.latent.packed else self.model.cfg.in_channels
                 vcfg = dataclasses.replace(V.tiny_vae_config(), z_channels=zc)
-            else:
-                vcfg = getattr(V, self.m.vae_config_fn)()
-            vae = V.AutoencoderKL(vcfg, self.dtype, self.device, with_encoder=False)
+                vae = V.AutoencoderKL(vcfg, self.dtype, self.device, with_encoder=False)
+            else:                                  # the family's own autoencoder (Klein: packed + BatchNorm; Qwen-Image: 3-D)
+                from ..models.vae_factory import build_family_vae
+                vae = build_family_vae(self.m.family, self.dtype, self.device, False, self.m.vae_config_fn)
         if self.vae_path and os.path.isfile(self.vae_path):
-            vae.load_state_dict(load_safetensors(self.vae_path, device=str(self.device), dtype=self.dtype), strict=False)
-            self.vae_weights = "checkpoint"
+            from ..models.vae_factory import load_vae_weights
+            self.vae_weights = load_vae_weights(vae, self.vae_path, self.device, self.dtype)
         else:
             vae.init_weights(seed=1)
             self.vae_weights = "random-init"
@@ -174,7 +175,8 @@ class ValidationSampler:
             arr = tensor_to_uint8(vid[0]).numpy()
         else:
             zz = z.to(self.device, self.dtype)
-            img = vae.tiled_decode(zz) if max(zz.shape[-2:]) > 96 else vae.decode(zz)
+            from ..models.vae_factory import decode_latent
+            img = decode_latent(vae, zz)
             arr = tensor_to_uint8(img[0].float().permute(1, 2, 0).cpu()).numpy()
         tmp = out_png + ".tmp"
         with open(tmp, "wb") as fh:

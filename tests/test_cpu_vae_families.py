@@ -125,3 +125,32 @@ def test_wan_diffusers_key_remap_and_full_size_structure():
     assert "decoder.upsamples.4.shortcut.weight" in mapped and "decoder.upsamples.3.time_conv.weight" in mapped
     w22 = W.wan22_vae_config()
     assert (w22.z_dim, w22.spatial_factor, w22.temporal_factor, len(w22.mean)) == (48, 16, 4, 48)
+
+
+def test_vae_factory_geometry_and_checkpoint_spellings(tmp_path):
+    from mojodiffusion_b200.io.safetensors_io import save_safetensors
+    from mojodiffusion_b200.models import vae_factory as F
+    cfg = V.VAEConfig(z_channels=4, ch=32, ch_mult=(1, 2), num_res_blocks=1, scale_factor=1.0, shift_factor=0.0)
+    klein = V.KleinVAE(cfg, dtype=torch.float32, with_encoder=False)
+    assert F.latent_geometry(klein) == (4, 2)
+    with torch.no_grad():
+        klein.init_weights(0)
+        z = torch.randn(1, 4, 4, 4)
+        assert F.decode_latent(klein, z).shape == (1, 3, 8, 8)                      # unpacked latent in, packed inside
+    wan = W.WanVAE(W.tiny_wan_vae_config("wan21"), with_encoder=False).init_weights(0)
+    assert F.latent_geometry(wan) == (4, 4) and F.decode_latent(wan, torch.randn(1, 4, 4, 4)).shape == (1, 3, 16, 16)
+    ldm = V.AutoencoderKL(V.tiny_vae_config(), dtype=torch.float32, with_encoder=False)
+    with torch.no_grad():
+        ldm.init_weights(2)
+    sd = {k: v.clone() for k, v in ldm.state_dict().items()}
+    spelled = {}
+    for k, v in sd.items():                                                        # a few tensors under diffusers names
+        k2 = k.replace("decoder.up.1.block.0.", "decoder.up_blocks.0.resnets.0.").replace("decoder.mid.block_1.", "decoder.mid_block.resnets.0.")
+        spelled[k2.replace("decoder.norm_out.", "decoder.conv_norm_out.")] = v
+    path = str(tmp_path / "vae.safetensors")
+    save_safetensors(path, spelled)
+    fresh = V.AutoencoderKL(V.tiny_vae_config(), dtype=torch.float32, with_encoder=False)
+    assert F.load_vae_weights(fresh, path) == "checkpoint"
+    assert torch.equal(fresh.decoder.up[1].block[0].conv1.weight, ldm.decoder.up[1].block[0].conv1.weight)
+    assert torch.equal(fresh.decoder.norm_out.weight, ldm.decoder.norm_out.weight)
+    assert type(F.build_family_vae("qwenimage", torch.float32, None)).__name__ == "WanVAE"
