@@ -183,8 +183,12 @@ Tensor gemm(std::vector<Tensor> As, std::vector<Tensor> Bs, const optional<Tenso
     g.reduce_rows_per_owner = (int)route_cfg[0];
     g.ld_out = (int)route_cfg[1];
   } else if (!route_ptrs.empty()) {
-    // route_cfg = {owner_cols, part_cols, row_offset, rows_per_batch, batch_rows, ld_out}
-    TORCH_CHECK(route_ptrs.size() <= MDB_GEMM_MAX_PEERS && route_cfg.size() == 6, "gemm: route arguments");
+    // route_cfg = {owner_cols, part_cols, row_offset, rows_per_batch, batch_rows, ld_out[, split, row_offset_b]}
+    TORCH_CHECK(route_ptrs.size() <= MDB_GEMM_MAX_PEERS && (route_cfg.size() == 6 || route_cfg.size() == 8), "gemm: route arguments");
+    if (route_cfg.size() == 8) {
+      g.route_split = (int)route_cfg[6];
+      g.route_row_offset_b = (int)route_cfg[7];
+    }
     for (size_t i = 0; i < route_ptrs.size(); ++i) g.route_out[i] = reinterpret_cast<void*>(route_ptrs[i]);
     g.route_owner_cols = (int)route_cfg[0];
     g.route_part_cols = (int)route_cfg[1];

@@ -51,8 +51,12 @@ typedef struct MdbGemmArgs {
   // row r is stored into route_out[owner] (that rank's buffer, leading dimension ld_out) at row
   // (r / route_rows_per_batch) * route_batch_rows + route_row_offset + r % route_rows_per_batch and column
   // part * route_owner_cols. This is the Ulysses head-scatter done by the projection's own epilogue.
+  // Two row ranges per batch entry (route_split > 0): rows with r % route_rows_per_batch >= route_split go to
+  // route_row_offset_b + (r % route_rows_per_batch - route_split) instead, so one GEMM over [text rows | image rows] of
+  // every sample scatters both streams without slicing its input.
   void* route_out[MDB_GEMM_MAX_PEERS];
   int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
+  int route_split, route_row_offset_b;
   // All-gather fused GEMM (gather_world > 1): the operand selected by gather_operand (0 = A, 1 = B) is read from
   // the local buffer gather_dst = [gather_world chunks of gather_chunk_rows rows]; chunk r is fetched inside the
   // kernel from gather_src[r] (rank r's shard in peer memory, gather_chunk_bytes bytes); chunk gather_rank must

@@ -63,6 +63,7 @@ struct GemmParams {
   // peer-routed output (sequence-parallel all-to-all in the epilogue): see MdbGemmArgs
   void* route_out[MDB_GEMM_MAX_PEERS];
   int route_owner_cols, route_part_cols, route_row_offset, route_rows_per_batch, route_batch_rows;
+  int route_split, route_row_offset_b;
   // all-gather fused into the GEMM (gather_world > 1): operand A (gather_operand 0) or B (1) lives in a local
   // buffer of `gather_world` equal row chunks; chunk r is rank r's shard. Warp 6 of every CTA copies its slice of
   // each remote chunk from the owner's memory (peer loads) and bumps ready[chunk]; the TMA producer waits for
@@ -145,7 +146,9 @@ __device__ __forceinline__ void* out_slab_ptr(const GemmParams& p, int row, int 
   const int owner = within / p.route_owner_cols;
   const int lcol = part * p.route_owner_cols + (within - owner * p.route_owner_cols);
   const int b = row / p.route_rows_per_batch;
-  const size_t orow = static_cast<size_t>(b) * p.route_batch_rows + p.route_row_offset + (row - b * p.route_rows_per_batch);
+  const int rin = row - b * p.route_rows_per_batch;
+  const int off = (p.route_split > 0 && rin >= p.route_split) ? p.route_row_offset_b + (rin - p.route_split) : p.route_row_offset + rin;
+  const size_t orow = static_cast<size_t>(b) * p.route_batch_rows + off;
   return reinterpret_cast<char*>(p.route_out[owner]) + (orow * p.ld_out + lcol) * esz;
 }
 
@@ -1276,6 +1279,8 @@ extern "C" int mdb_gemm_launch(const MdbGemmArgs* a, cudaStream_t stream) {
   p.route_row_offset = a->route_row_offset;
   p.route_rows_per_batch = a->route_rows_per_batch > 0 ? a->route_rows_per_batch : a->M;
   p.route_batch_rows = a->route_batch_rows;
+  p.route_split = a->route_split;
+  p.route_row_offset_b = a->route_row_offset_b;
   if (a->route_owner_cols > 0 && ((a->route_owner_cols % 32) || (p.route_part_cols % a->route_owner_cols))) return -5;
 
 #define MDB_LAUNCH(BN_, ST_, AMN_, BMN_, KIND_) return launch_variant<BN_, ST_, AMN_, BMN_, KIND_>(maps, p, sms, stream)

@@ -191,8 +191,7 @@ class SingleStreamBlock(nn.Module):
         if sp is not None:
             w1, b1, w2 = self.linear1.weight, self.linear1.bias, self.linear2.weight
             bq = b1[:3 * D] if b1 is not None else None
-            sp.scatter_qkv(xn[:, :sp.St], w1[:3 * D], bq, "txt")
-            sp.scatter_qkv(xn[:, sp.St:], w1[:3 * D], bq, "img")
+            sp.scatter_qkv_joint(xn, w1[:3 * D], bq)
             mlp = ops.linear(xn, w1[3 * D:], b1[3 * D:] if b1 is not None else None, act="gelu_tanh")
             sp.finish_scatter()
             sp.attention(wq, wk, wq, wk, cos, sin)

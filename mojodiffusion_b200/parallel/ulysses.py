@@ -92,6 +92,19 @@ class UlyssesContext:
         else:
             self._local_qkv[part] = ops.linear(x2, weight, bias).view(self.B, Sp, 3, self.world, self.Dl)
 
+    def scatter_qkv_joint(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> None:
+        """x: this rank's [B, St + Si, D] rows with the text rows of every sample first (the single-stream layout). One GEMM
+        scatters both streams: its epilogue sends rows below ``St`` to the text range and the others to the image range of
+        the gathered buffer, so the input is not sliced (a slice of a batch > 1 is not contiguous and would be copied)."""
+        if self.mode != "fused":
+            self.scatter_qkv(x[:, :self.St], weight, bias, "txt")
+            self.scatter_qkv(x[:, self.St:], weight, bias, "img")
+            return
+        with nvtx_range("collective/ulysses/qkv_scatter_gemm"):
+            _gemm([_flat2d(x)], [weight], bias=bias, route_ptrs=self.symm.ptrs_at(self.off_qkv),
+                  route_cfg=[self.Dl, self.D, self.rank * self.St, self.Sl, self.S, 3 * self.Dl,
+                             self.St, self.S_txt + self.rank * self.Si])
+
     def finish_scatter(self) -> None:
         """Publish "my projections have landed everywhere" (fused) / run the all-to-all (nccl)."""
         if self.mode == "fused":

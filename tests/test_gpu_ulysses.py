@@ -60,3 +60,55 @@ def test_sp_matches_single_gpu(tmp_path):
     world = 2 if torch.cuda.device_count() < 4 else 4
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert (tmp_path / "ok").exists()
+
+
+@pytest.mark.parametrize("joint", [False, True])
+def test_eight_emulated_ranks_real_head_count(joint):
+    """24 heads x 128 over 8 ranks (3 heads each) and batch 2 on ONE GPU: the ranks' buffers are ordinary allocations of
+    this device and the phases run rank by rank (every signal is issued before any wait is launched, so no launch ever
+    waits for a later one). Checks the routed QKV epilogue (separate streams, and the two-range form over
+    [text rows | image rows]), the routed attention epilogue and the epoch flags against a plain composition."""
+    from mojodiffusion_b200 import ops
+    from mojodiffusion_b200.ops import native
+    from mojodiffusion_b200.parallel.symm import emulated_group
+    from mojodiffusion_b200.parallel.ulysses import UlyssesContext
+    native.load(True)
+    dev = torch.device("cuda", 0)
+    N, H, Dh, B, S_txt, S_img = 8, 24, 128, 2, 64, 512
+    D = H * Dh
+    g = torch.Generator().manual_seed(11)
+    xt = (torch.randn(B, S_txt, D, generator=g) * 0.5).to(dev).bfloat16()
+    xi = (torch.randn(B, S_img, D, generator=g) * 0.5).to(dev).bfloat16()
+    W = (torch.randn(3 * D, D, generator=g) * 0.02).to(dev).bfloat16()
+    bias = (torch.randn(3 * D, generator=g) * 0.1).to(dev).bfloat16()
+    wq = (1.0 + 0.1 * torch.randn(Dh, generator=g)).to(dev).bfloat16()
+    wk = (1.0 + 0.1 * torch.randn(Dh, generator=g)).to(dev).bfloat16()
+    S = S_txt + S_img
+    ids = torch.zeros(S, 3, device=dev)
+    ids[:, 0] = torch.arange(S, device=dev)
+    cos, sin = ops.rope_table(ids, (16, 56, 56), 10000.0)
+    bufs = emulated_group(N, UlyssesContext.symm_bytes(B, S_txt, S_img, H, Dh, N), dev)
+    sps = [UlyssesContext(B, S_txt, S_img, H, Dh, mode="fused", symm=bufs[r], device=dev) for r in range(N)]
+    with torch.no_grad():
+        for rep in range(2):                                   # twice: epochs advance, buffers are reused
+            for sp in sps:
+                if joint:
+                    sp.scatter_qkv_joint(torch.cat((sp.shard(xt, "txt"), sp.shard(xi, "img")), dim=1), W, bias)
+                else:
+                    sp.scatter_qkv(sp.shard(xt, "txt"), W, bias, "txt")
+                    sp.scatter_qkv(sp.shard(xi, "img"), W, bias, "img")
+                sp.finish_scatter()
+            for sp in sps:
+                sp.attention(wq, wk, wq, wk, cos, sin)
+            outs = [sp.finish_attention().clone() for sp in sps]
+        torch.cuda.synchronize()
+        native.check_status()
+        # plain composition on the whole sequence
+        qkv = ops.linear(torch.cat((xt, xi), dim=1), W, bias)                              # [B, S, 3D] as (q|k|v) x (head, Dh)
+        ops.qk_norm_rope(qkv, H, Dh, wq, wk, cos, sin)
+        q, k, v = [qkv[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3)]
+        want = ops.attention(q, k, v).reshape(B, S, D)
+    for r, sp in enumerate(sps):
+        ref = torch.cat((want[:, r * sp.St:(r + 1) * sp.St], want[:, S_txt + r * sp.Si:S_txt + (r + 1) * sp.Si]), dim=1)
+        err = float((outs[r].float() - ref.float()).abs().max())
+        assert err <= 2e-2 * float(ref.float().abs().max()) + 1e-3, f"rank {r}: {err}"
