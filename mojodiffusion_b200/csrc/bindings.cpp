@@ -606,6 +606,27 @@ Tensor fp8_dequant(const Tensor& q, const optional<Tensor>& row_scale, double te
   return y;
 }
 
+Tensor mx_dequant(const Tensor& q, const Tensor& scales, bool fp4) {
+  TORCH_CHECK(q.is_cuda() && q.is_contiguous() && q.scalar_type() == at::kByte && scales.is_cuda() && scales.is_contiguous() &&
+                  scales.scalar_type() == at::kByte && scales.device() == q.device(), "mx_dequant: uint8 device tensors");
+  const int64_t per = fp4 ? 16 : 32, nb = scales.numel();
+  TORCH_CHECK(q.numel() == nb * per, "mx_dequant: ", per, " bytes per 32-element block and one scale byte per block");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor y = at::empty({nb * 32}, q.options().dtype(at::kBFloat16));
+  check_rc(mdb_mx_dequant(q.data_ptr(), scales.data_ptr(), y.data_ptr(), nb, fp4 ? 1 : 0, cur_stream()), "mx_dequant");
+  return y;
+}
+std::tuple<Tensor, Tensor> mx_quant(const Tensor& x, bool fp4) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16 && x.numel() % 32 == 0,
+              "mx_quant: contiguous bf16 with a multiple of 32 elements");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t nb = x.numel() / 32;
+  Tensor q = at::empty({nb * (fp4 ? 16 : 32)}, x.options().dtype(at::kByte));
+  Tensor sc = at::empty({nb}, x.options().dtype(at::kByte));
+  check_rc(mdb_mx_quant(x.data_ptr(), q.data_ptr(), sc.data_ptr(), nb, fp4 ? 1 : 0, cur_stream()), "mx_quant");
+  return {q, sc};
+}
+
 // ------------------------------------------------------------------------------------------
 // optimizer (tables are int64 device tensors laid out as MdbTensorEntry / int2)
 // ------------------------------------------------------------------------------------------
@@ -821,6 +842,8 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("randn", &randn);
   m.def("fp8_quant_rows", &fp8_quant_rows);
   m.def("fp8_dequant", &fp8_dequant);
+  m.def("mx_dequant", &mx_dequant);
+  m.def("mx_quant", &mx_quant);
   m.def("adamw_multi", &adamw_multi);
   m.def("sumsq_multi", &sumsq_multi);
   m.def("ema_multi", &ema_multi);

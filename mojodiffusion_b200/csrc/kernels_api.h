@@ -64,6 +64,9 @@ int mdb_mse_loss(const void* pred, const float* target, void* grad, float* loss_
 int mdb_randn(float* out_f32, void* out_bf16, long long n, unsigned long long seed, unsigned long long offset,
               cudaStream_t st);
 int mdb_fp8_quant_rows(const void* x, void* q, float* scale, long long rows, int D, int ldx, int ldq, cudaStream_t st);
+// MX formats: 32-element blocks with one E8M0 scale byte; fp4 != 0: E2M1 nibbles (16 bytes per block), else E4M3 bytes
+int mdb_mx_dequant(const void* q, const void* scales, void* y, long long n_blocks, int fp4, cudaStream_t st);
+int mdb_mx_quant(const void* x, void* q, void* scales, long long n_blocks, int fp4, cudaStream_t st);
 int mdb_fp8_dequant(const void* q, const float* row_scale, float tensor_scale, void* y, long long rows, int D,
                     cudaStream_t st);
 

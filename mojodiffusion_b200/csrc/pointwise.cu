@@ -430,6 +430,120 @@ extern "C" int mdb_randn(float* out_f32, void* out_bf16, long long n, unsigned l
   randn_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, st>>>(out_f32, (bf16*)out_bf16, n, seed, offset);
   return (int)cudaGetLastError();
 }
+// ---- microscaling (MX) formats: 32-element blocks sharing one E8M0 scale 2^(byte - 127) -------------------------------
+// MXFP4: E2M1 elements, two per byte, low nibble first (the layout of the gpt-oss checkpoints: blocks [.., G, 16] bytes,
+// scales [.., G] bytes; serenitymojo/ops/mxfp4.mojo:88-135). MXFP8: E4M3 elements. Quantisers choose the block exponent
+// floor(log2(absmax)) - emax of the element type (2 for E2M1, 8 for E4M3), clamp to the E8M0 range and round the scaled
+// elements to nearest-even on the element grid with saturation.
+__device__ __forceinline__ float e8m0_to_float(uint32_t b) {
+  // 2^(b - 127); byte 0 is 2^-127 (a subnormal float), byte 255 (NaN in the format) is not produced by the quantisers
+  return b == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(b << 23);
+}
+__device__ __forceinline__ uint32_t block_exponent_byte(float amax, int emax) {
+  if (!(amax > 0.f)) return 0u;
+  int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127;   // floor(log2(amax)) for normal floats
+  e = e - emax + 127;
+  return static_cast<uint32_t>(min(max(e, 0), 254));
+}
+__device__ __forceinline__ float e2m1_decode(uint32_t n) {
+  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  const float v = mag[n & 7u];
+  return (n & 8u) ? -v : v;
+}
+__device__ __forceinline__ uint32_t e2m1_encode(float x) {
+  const float a = fabsf(x);
+  // round to nearest, ties to the even mantissa, on {0, .5, 1, 1.5, 2, 3, 4, 6}; saturate at 6
+  uint32_t m;
+  if (a <= 0.25f) m = 0;
+  else if (a < 0.75f) m = 1;
+  else if (a <= 1.25f) m = 2;
+  else if (a < 1.75f) m = 3;
+  else if (a <= 2.5f) m = 4;
+  else if (a < 3.5f) m = 5;
+  else if (a <= 5.0f) m = 6;
+  else m = 7;
+  return m | ((__float_as_uint(x) >> 28) & 8u);
+}
+// one thread per block: 16 bytes in, 32 bf16 out
+__global__ void mxfp4_dequant_kernel(const uint4* __restrict__ blocks, const uint8_t* __restrict__ scales,
+                                     __nv_bfloat16* __restrict__ y, long long n_blocks) {
+  for (long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x; b < n_blocks; b += (long long)gridDim.x * blockDim.x) {
+    const float sc = e8m0_to_float(scales[b]);
+    const uint4 u = blocks[b];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    uint4* out = reinterpret_cast<uint4*>(y + b * 32);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = e2m1_decode((w[q] >> (4 * j)) & 0xfu) * sc;
+      uint4 o;
+      o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]); o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+      out[q] = o;
+    }
+  }
+}
+template <bool FP4>
+__global__ void mx_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ scales,
+                                long long n_blocks) {
+  for (long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x; b < n_blocks; b += (long long)gridDim.x * blockDim.x) {
+    float v[32];
+    const uint4* in = reinterpret_cast<const uint4*>(x + b * 32);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float t[8];
+      unpack8(in[i], t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i * 8 + j] = t[j];
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const uint32_t eb = block_exponent_byte(amax, FP4 ? 2 : 8);
+    scales[b] = static_cast<uint8_t>(eb);
+    const float inv = 1.0f / e8m0_to_float(eb);
+    if (FP4) {
+      uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int i = 0; i < 32; ++i) w[i >> 3] |= e2m1_encode(v[i] * inv) << (4 * (i & 7));
+      reinterpret_cast<uint4*>(q)[b] = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        w[i >> 2] |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3)) << ((i & 3) * 8);
+      uint4* out = reinterpret_cast<uint4*>(q + b * 32);
+      out[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      out[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  }
+}
+__global__ void mxfp8_dequant_kernel(const uint4* __restrict__ q, const uint8_t* __restrict__ scales, __nv_bfloat16* __restrict__ y,
+                                     long long n_blocks) {
+  for (long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x; b < n_blocks; b += (long long)gridDim.x * blockDim.x) {
+    const float sc = e8m0_to_float(scales[b]);
+    uint4* out = reinterpret_cast<uint4*>(y + b * 32);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 u = q[b * 2 + h];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((w[j >> 2] >> ((j & 3) * 8)) & 0xffu), __NV_E4M3);
+        v[j] = __half2float(*reinterpret_cast<const __half*>(&hr)) * sc;
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        uint4 o;
+        o.x = pack_bf16x2(v[k * 8 + 0], v[k * 8 + 1]); o.y = pack_bf16x2(v[k * 8 + 2], v[k * 8 + 3]);
+        o.z = pack_bf16x2(v[k * 8 + 4], v[k * 8 + 5]); o.w = pack_bf16x2(v[k * 8 + 6], v[k * 8 + 7]);
+        out[h * 2 + k] = o;
+      }
+    }
+  }
+}
+
 extern "C" int mdb_fp8_quant_rows(const void* x, void* q, float* scale, long long rows, int D, int ldx, int ldq,
                                   cudaStream_t st) {
   if (D % 8 || ldx % 8 || ldq % 8) return -1;
@@ -445,5 +559,17 @@ extern "C" int mdb_fp8_dequant(const void* q, const float* row_scale, float tens
   if (rows == 0) return 0;
   fp8_dequant_kernel<<<grid_for(rows * (D / 8), 256), 256, 0, st>>>((const __nv_fp8_storage_t*)q, row_scale,
                                                                     tensor_scale, (bf16*)y, rows, D);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_mx_dequant(const void* q, const void* scales, void* y, long long n_blocks, int fp4, cudaStream_t st) {
+  if (n_blocks == 0) return 0;
+  if (fp4) mxfp4_dequant_kernel<<<grid_for(n_blocks, 256), 256, 0, st>>>((const uint4*)q, (const uint8_t*)scales, (bf16*)y, n_blocks);
+  else mxfp8_dequant_kernel<<<grid_for(n_blocks, 256), 256, 0, st>>>((const uint4*)q, (const uint8_t*)scales, (bf16*)y, n_blocks);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_mx_quant(const void* x, void* q, void* scales, long long n_blocks, int fp4, cudaStream_t st) {
+  if (n_blocks == 0) return 0;
+  if (fp4) mx_quant_kernel<true><<<grid_for(n_blocks, 256), 256, 0, st>>>((const bf16*)x, (uint8_t*)q, (uint8_t*)scales, n_blocks);
+  else mx_quant_kernel<false><<<grid_for(n_blocks, 256), 256, 0, st>>>((const bf16*)x, (uint8_t*)q, (uint8_t*)scales, n_blocks);
   return (int)cudaGetLastError();
 }

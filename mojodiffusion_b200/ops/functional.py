@@ -18,7 +18,7 @@ from .reference import act_code
 
 __all__ = [
     "linear", "linear_glu", "lora_linear", "attention", "norm_modulate", "qk_norm_rope", "rope_table", "activation",
-    "glu", "gate_residual", "cfg_euler", "flow_match", "mse_loss", "randn", "fp8_quant_rows", "fp8_dequant",
+    "glu", "gate_residual", "cfg_euler", "flow_match", "mse_loss", "randn", "fp8_quant_rows", "fp8_dequant", "mx_quant", "mx_dequant",
     "fp8_linear", "qkv_attention", "split_cols",
 ]
 
@@ -668,6 +668,25 @@ def fp8_quant_rows(x):
     if not native.use_native(x):
         return ref.fp8_quant_rows(x)
     return _ops().fp8_quant_rows(_flat2d(x))
+
+
+def mx_dequant(q, scales, fp4: bool = True, shape=None):
+    """MXFP4 (E2M1 pairs per byte) or MXFP8 (E4M3 bytes) blocks of 32 with E8M0 scale bytes -> bf16. ``shape`` reshapes
+    the flat result (gpt-oss expert weights: blocks [.., G, 16] + scales [.., G] -> [.., G * 32])."""
+    if not native.use_native(q):
+        y = ref.mx_dequant(q, scales, fp4)
+    else:
+        y = _ops().mx_dequant(q.contiguous().reshape(-1), scales.contiguous().reshape(-1), bool(fp4))
+    if shape is None and fp4 and q.dim() >= 2 and q.shape[-1] == 16:
+        shape = tuple(q.shape[:-2]) + (q.shape[-2] * 32,)
+    return y.reshape(shape) if shape is not None else y
+
+
+def mx_quant(x, fp4: bool = True):
+    """bf16 -> (packed bytes, E8M0 scale bytes) over consecutive blocks of 32 elements."""
+    if not native.use_native(x):
+        return ref.mx_quant(x, fp4)
+    return _ops().mx_quant(x.contiguous().to(torch.bfloat16), bool(fp4))
 
 
 def fp8_dequant(q, row_scale=None, tensor_scale: float = 1.0):

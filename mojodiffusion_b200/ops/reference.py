@@ -282,6 +282,53 @@ def fp8_dequant(q: torch.Tensor, row_scale=None, tensor_scale: float = 1.0):
     return y.to(torch.bfloat16)
 
 
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def _e8m0(scales: torch.Tensor) -> torch.Tensor:
+    e = scales.to(torch.int32) - 127
+    return torch.ldexp(torch.ones(e.shape, dtype=torch.float32, device=scales.device), e)
+
+
+def mx_dequant(q: torch.Tensor, scales: torch.Tensor, fp4: bool = True) -> torch.Tensor:
+    """MX block formats -> bf16 [n_blocks * 32]: ``scales`` uint8 E8M0 (2^(b - 127)) per 32 elements; fp4: ``q`` uint8 with
+    two E2M1 values per byte, low nibble first (16 bytes per block); else ``q`` holds E4M3 bytes."""
+    sc = _e8m0(scales.reshape(-1))
+    if fp4:
+        b = q.reshape(-1, 16).to(torch.int32)
+        nib = torch.stack((b & 0xF, (b >> 4) & 0xF), dim=-1).reshape(-1, 32)
+        lut = torch.tensor(_E2M1, dtype=torch.float32, device=q.device)
+        v = lut[nib & 7] * torch.where((nib & 8) != 0, -1.0, 1.0)
+    else:
+        v = q.reshape(-1, 32).view(torch.float8_e4m3fn).float()
+    return (v * sc[:, None]).reshape(-1).to(torch.bfloat16)
+
+
+def mx_quant(x: torch.Tensor, fp4: bool = True):
+    """bf16 -> (packed uint8, E8M0 scale bytes). Block exponent = floor(log2(absmax)) - emax (2 for E2M1, 8 for E4M3),
+    elements rounded to nearest-even on the element grid with saturation."""
+    v = x.float().reshape(-1, 32)
+    amax = v.abs().amax(dim=1)
+    e = torch.floor(torch.log2(amax.clamp_min(1e-45))).to(torch.int32) - (2 if fp4 else 8) + 127
+    e = torch.where(amax > 0, e.clamp(0, 254), torch.zeros_like(e))
+    sc = torch.ldexp(torch.ones(e.shape, dtype=torch.float32, device=x.device), e - 127)
+    sc = torch.where(e == 0, torch.full_like(sc, 2.0 ** -127), sc)
+    y = v / sc[:, None]
+    if fp4:
+        a = y.abs()
+        bounds = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device=x.device)
+        # ties go to the even code: codes 0, 2, 4, 6 own their upper boundary, odd codes do not
+        m = torch.zeros_like(a, dtype=torch.int32)
+        for i, bnd in enumerate(bounds.tolist()):
+            m = m + ((a > bnd) if i % 2 == 0 else (a >= bnd)).to(torch.int32)
+        nib = m | ((y < 0) | ((y == 0) & torch.signbit(y))).to(torch.int32) * 8
+        nib = nib.reshape(-1, 16, 2)
+        q = (nib[..., 0] | (nib[..., 1] << 4)).to(torch.uint8).reshape(-1)
+    else:
+        q = y.clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).reshape(-1)
+    return q, e.to(torch.uint8)
+
+
 def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
     """torch.optim.AdamW order, fp32 math; returns new (p, m, v)."""
     g = g.float() * grad_scale

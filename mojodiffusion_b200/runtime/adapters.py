@@ -48,6 +48,8 @@ class FamilyAdapter:
         if L.packed:
             h, w = latent.shape[-2] // L.patch, latent.shape[-1] // L.patch
             return pack_latents(latent, L.patch), Cond(txt=None, hw=(h, w))
+        if self.family == "ernie":                              # one token per latent cell, channels as features
+            return latent.flatten(2).transpose(1, 2), Cond(txt=None, hw=(latent.shape[-2], latent.shape[-1]))
         return latent, Cond(txt=None)
 
     def to_latent(self, x: torch.Tensor, cond: Cond) -> torch.Tensor:
@@ -56,6 +58,8 @@ class FamilyAdapter:
             return x.reshape(x.shape[0], Fr, h, w, -1).permute(0, 4, 1, 2, 3)
         if self.m.latent.packed:
             return unpack_latents(x, cond.hw[0], cond.hw[1], self.m.latent.patch)
+        if self.family == "ernie":
+            return x.transpose(1, 2).reshape(x.shape[0], -1, cond.hw[0], cond.hw[1])
         return x
 
     def conditioning(self, cond: Cond, text: torch.Tensor, mask: Optional[torch.Tensor], pooled: Optional[torch.Tensor],
@@ -63,7 +67,7 @@ class FamilyAdapter:
         cond.txt = text
         cond.guidance = guidance
         T = self.m.text
-        if T.key_mask or self.family == "zimage":
+        if T.key_mask or self.family in ("zimage", "anima"):
             if mask is not None:
                 cond.txt_len = mask.to(torch.float32).sum(-1).round().to(torch.int32).clamp(min=1).to(text.device)
         P = self.pooled_dim(model_cfg)
@@ -106,6 +110,10 @@ class FamilyAdapter:
             return model(x, sigma, c.txt, c.pooled)
         if f == "ltx2":
             return model(x, c.txt, sigma, c.grid)
+        if f == "ernie":
+            return model(x, c.txt, sigma, c.hw, c.txt_len)
+        if f == "anima":
+            return model(x, c.txt, sigma, c.txt_len)
         raise NotImplementedError(f"no adapter for family '{f}'")
 
     # ---- adapters --------------------------------------------------------------------------------------------------

@@ -195,6 +195,18 @@ register(ModelManifest(
     LatentSpec(48, 16, 2, True, temporal_factor=4), TextSpec(512, 4096, 0, ("umt5",)),
     ScheduleSpec("shifted", 40, 5.0, shift=5.0), None, "", "wan22_plan", 5.0, ((1280, 704),)),
     "wan22", "wan2.2")
+register(ModelManifest(
+    "ernie-image", "ernie", _M + "ernie", "ErnieImage", "ernie_config", "tiny_ernie_config",
+    LatentSpec(128, 16, 1, False), TextSpec(256, 3072, 0, ("mistral3b",), key_mask=True),
+    ScheduleSpec("shifted", 50, 4.0, shift=3.0), LoraSpec("inject_ernie_lora", "peft"),
+    "klein_vae_config", "", 8.0, ((1024, 1024),), notes="latents are the packed 128-channel FLUX.2 VAE latents at 1/16"),
+    "ernie", "ernie-image-8b")
+register(ModelManifest(
+    "anima", "anima", _M + "anima", "Anima", "anima_config", "tiny_anima_config",
+    LatentSpec(16, 8, 1, False), TextSpec(256, 1024, 0, ("qwen3", "t5_adapter")),
+    ScheduleSpec("shifted", 30, 4.0, shift=3.0), LoraSpec("inject_anima_lora", "peft"),
+    "flux_vae_config", "", 2.0, ((1024, 1024),), notes="2 x 2 patches and the mask channel are added inside the model"),
+    "anima-minitraindit")
 
 
 # ---- execution config / shape profile / guard ------------------------------------------------------------------

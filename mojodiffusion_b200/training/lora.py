@@ -185,6 +185,22 @@ def inject_ltx2_lora(model, rank: int = 16, alpha: float = 16.0, cross_attention
     return _finish(model, slots)
 
 
+def inject_ernie_lora(model, rank: int = 16, alpha: float = 16.0, seed: int = 0) -> List[LoRASlot]:
+    """ERNIE-Image adapters on the attention and gated-MLP projections of every layer, under ``transformer.<module path>``."""
+    from ..models.ernie import ernie_lora_targets
+    _freeze(model)
+    mods = dict(model.named_modules())
+    return _finish(model, [mods[n].add_lora("transformer." + n, rank, alpha, None, seed) for n in ernie_lora_targets(len(model.layers))])
+
+
+def inject_anima_lora(model, rank: int = 16, alpha: float = 16.0, seed: int = 0) -> List[LoRASlot]:
+    """Anima adapters on self- / cross-attention and MLP projections, keys = the checkpoint's module paths (``net.blocks.…``)."""
+    from ..models.anima import anima_lora_targets
+    _freeze(model)
+    mods = dict(model.named_modules())
+    return _finish(model, [mods[n].add_lora("diffusion_model." + n, rank, alpha, None, seed) for n in anima_lora_targets(len(model.net.blocks))])
+
+
 def inject_lora_by_name(model: nn.Module, name_to_key: Dict[str, str], rank: int, alpha: float) -> List[LoRASlot]:
     """Generic injection: ``name_to_key`` maps a module path of a :class:`Linear` to its checkpoint prefix."""
     for p in model.parameters():

@@ -1,0 +1,91 @@
+"""ERNIE-Image and Anima single-stream families: forward contracts, checkpoint key names, masks, adapters, schedules, and a
+few optimisation steps through the shared family trainer."""
+import torch
+
+from mojodiffusion_b200.models import anima as A
+from mojodiffusion_b200.models import ernie as E
+from mojodiffusion_b200.runtime import default_manifest_by_id
+from mojodiffusion_b200.runtime.adapters import adapter_for, schedule_for
+
+
+def test_ernie_forward_mask_and_keys():
+    cfg = E.tiny_ernie_config()
+    m = E.ErnieImage(cfg, dtype=torch.float32)
+    g = torch.Generator().manual_seed(0)
+    with torch.no_grad():
+        m.init_weights(0)
+        img, txt = torch.randn(2, 16, cfg.in_channels, generator=g), torch.randn(2, 6, cfg.text_dim, generator=g)
+        s = torch.tensor([0.3, 0.9])
+        out = m(img, txt, s, (4, 4))
+        assert out.shape == img.shape and torch.isfinite(out).all()
+        masked = m(img, txt, s, (4, 4), text_len=torch.tensor([3, 6]))
+        assert (masked - out)[0].abs().max() > 1e-6 and torch.equal(masked[1], out[1])      # only the padded sample changes
+        txt2 = txt.clone()
+        txt2[0, 3:] = 7.0                                                                  # padded text keys are ignored
+        assert torch.allclose(m(img, txt2, s, (4, 4), text_len=torch.tensor([3, 6]))[0], masked[0], atol=1e-5)
+    keys = set(m.state_dict())
+    for k in ("x_embedder.proj.weight", "time_embedding.linear_2.bias", "text_proj.weight", "adaLN_modulation.1.weight",
+              "layers.1.adaLN_sa_ln.weight", "layers.0.self_attention.to_out.0.weight", "layers.0.self_attention.norm_k.weight",
+              "layers.0.mlp.gate_proj.weight", "layers.1.mlp.linear_fc2.weight", "final_norm.linear.weight", "final_linear.bias"):
+        assert k in keys, k
+    assert "text_proj.bias" not in keys and m.adaLN_modulation["1"].weight.shape[0] == 6 * cfg.hidden
+    sig = E.ernie_sigmas(50, 3.0)
+    assert len(sig) == 51 and sig[0] == 1.0 and sig[-1] == 0.0 and abs(sig[25] - 3 * 0.5 / (1 + 2 * 0.5)) < 1e-6
+    full = E.ernie_config()
+    assert (full.hidden, full.heads, full.depth, full.ffn_hidden, full.theta, full.axes_dim) == (4096, 32, 36, 12288, 256.0, (32, 48, 48))
+
+
+def test_anima_forward_patch_layout_and_keys():
+    cfg = A.tiny_anima_config()
+    m = A.Anima(cfg, dtype=torch.float32)
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        m.init_weights(0)
+        z, ctx = torch.randn(2, 4, 1, 8, 8, generator=g), torch.randn(2, 5, cfg.context_dim, generator=g)
+        s = torch.tensor([0.2, 0.7])
+        out = m(z, ctx, s)
+        assert out.shape == z.shape and torch.isfinite(out).all()
+        assert m(z[:, :, 0], ctx, s).shape == (2, 4, 8, 8)                                  # images may come 4-D
+        tok, grid = m.patchify(z)
+        assert tok.shape == (2, 16, cfg.patch_in) and grid == (1, 4, 4)
+        # token (row 1, col 2) holds channel c at in-patch (dy, dx) in slot (c * 2 + dy) * 2 + dx; the mask channel is zero
+        c, dy, dx = 3, 1, 0
+        assert tok[1, 1 * 4 + 2, (c * 2 + dy) * 2 + dx] == z[1, c, 0, 2 * 1 + dy, 2 * 2 + dx]
+        assert float(tok[..., 4 * 4:].abs().max()) == 0.0
+        y = torch.arange(2 * 16 * cfg.patch_out, dtype=torch.float32).reshape(2, 16, cfg.patch_out)
+        img = m.unpatchify(y, grid)
+        assert img[1, c, 0, 2 * 1 + dy, 2 * 2 + dx] == y[1, 1 * 4 + 2, (dy * 2 + dx) * 4 + c]      # output slots are (dy, dx, c)
+        short = m(z, ctx, s, ctx_len=torch.tensor([2, 5]))
+        assert (short - out)[0].abs().max() > 1e-6 and torch.equal(short[1], out[1])
+    keys = set(m.state_dict())
+    for k in ("net.x_embedder.proj.1.weight", "net.t_embedder.1.linear_2.weight", "net.t_embedding_norm.weight",
+              "net.blocks.0.self_attn.q_norm.weight", "net.blocks.1.cross_attn.k_proj.weight", "net.blocks.0.mlp.layer2.weight",
+              "net.blocks.0.adaln_modulation_cross_attn.2.weight", "net.final_layer.adaln_modulation.1.weight", "net.final_layer.linear.weight"):
+        assert k in keys, k
+    assert not any(k.endswith(".bias") for k in keys)
+    assert m.net.blocks[0].cross_attn.k_proj.weight.shape == (cfg.hidden, cfg.context_dim)
+    assert A.anima_config().patch_in == 68 and A.anima_config().patch_out == 64
+
+
+def test_both_families_train_through_the_family_trainer():
+    from mojodiffusion_b200.io.config import TrainConfig
+    from mojodiffusion_b200.training.family_trainer import FamilyTrainer
+    from mojodiffusion_b200.training.optim import FusedAdamW
+    for mid, C, D in (("ernie-image", 16, 96), ("anima", 4, 96)):
+        man = default_manifest_by_id(mid)
+        model = man.build(tiny=True, dtype=torch.float32)
+        with torch.no_grad():
+            model.init_weights(0)
+        ad = adapter_for(man)
+        slots = ad.inject_lora(model, rank=4, alpha=4.0)
+        params = [p for s in slots for p in (s.down, s.up)]
+        cfg = TrainConfig()
+        cfg.learning_rate, cfg.seed = 2e-3, 5
+        tr = FamilyTrainer(ad, model, params, FusedAdamW(params, lr=2e-3), cfg)
+        g = torch.Generator().manual_seed(2)
+        batch = {"latent": torch.randn(2, C, 8, 8, generator=g), "text_embedding": torch.randn(2, 6, D, generator=g), "text_mask": torch.ones(2, 6)}
+        losses = [float(tr.step(batch)) for _ in range(6)]
+        assert all(l == l for l in losses) and all(float(s.up.abs().sum()) > 0 for s in slots)
+        assert slots[0].key.startswith("transformer.layers.0." if mid == "ernie-image" else "diffusion_model.net.blocks.0.")
+        sig = schedule_for(man, man.schedule.steps, 1024)
+        assert len(sig) == man.schedule.steps + 1 and sig[0] == 1.0 and sig[-1] == 0.0

@@ -137,3 +137,30 @@ def test_audio_ops_and_vocoder():
     import dataclasses
     v2 = Vocoder(dataclasses.replace(tiny_vocoder_config(), istft_head=True))
     assert v2(torch.randn(1, 16, 10)).dim() == 2
+
+
+def test_mx_block_formats_reference():
+    """MXFP4 / MXFP8: known encodings decode to their values, quantise -> dequantise -> quantise is stable, the error stays
+    inside the format's bound, and the gpt-oss tensor layout ([.., G, 16] blocks + [.., G] scales) reshapes to [.., G * 32]."""
+    import torch
+    from mojodiffusion_b200 import ops as O
+    blocks = torch.zeros(1, 16, dtype=torch.uint8)
+    blocks[0, 0] = 0x21            # low nibble 1 -> 0.5, high nibble 2 -> 1.0
+    blocks[0, 1] = 0xF7            # low nibble 7 -> 6.0, high nibble 15 -> -6.0
+    y = O.mx_dequant(blocks, torch.tensor([128], dtype=torch.uint8)).float()       # scale 2^1
+    assert y[:4].tolist() == [1.0, 2.0, 12.0, -12.0] and float(y[4:].abs().max()) == 0.0
+    g = torch.Generator().manual_seed(0)
+    x = (torch.randn(64, 64, generator=g) * torch.logspace(-3, 3, 64)[:, None]).bfloat16()
+    for fp4, bound in ((True, 0.26), (False, 0.13)):
+        q, s = O.mx_quant(x, fp4)
+        assert q.dtype == torch.uint8 and s.numel() == x.numel() // 32 and q.numel() == x.numel() // (2 if fp4 else 1)
+        back = O.mx_dequant(q, s, fp4).reshape(x.shape)
+        blk = x.float().reshape(-1, 32)
+        err = (back.float().reshape(-1, 32) - blk).abs().amax(dim=1) / blk.abs().amax(dim=1)
+        assert float(err.max()) < bound
+        q2, s2 = O.mx_quant(back, fp4)
+        assert torch.equal(q2, q) and torch.equal(s2, s)
+    z, sz = O.mx_quant(torch.zeros(64, dtype=torch.bfloat16), True)
+    assert int(sz.max()) == 0 and int(z.max()) == 0
+    w = O.mx_dequant(torch.randint(0, 256, (3, 5, 4, 16), dtype=torch.uint8, generator=g), torch.randint(110, 130, (3, 5, 4), dtype=torch.uint8, generator=g))
+    assert w.shape == (3, 5, 128) and w.dtype == torch.bfloat16

@@ -202,6 +202,25 @@ def test_attention_strided_and_masked():
     _check(out, ref.attention(q, k, v, kv_len=kv_len).float(), cos=0.999, rel=3e-2, name="kv_len mask")
 
 
+@pytest.mark.parametrize("fp4", [True, False])
+def test_mx_quant_dequant_kernels_match_reference_bit_for_bit(fp4):
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(4096, 96, generator=g) * torch.logspace(-6, 6, 4096)[:, None]).to(DEV).bfloat16()
+    x[7, :32] = 0
+    q, s = O.mx_quant(x, fp4)
+    qr, sr = ref.mx_quant(x, fp4)
+    assert torch.equal(s, sr)
+    assert torch.equal(q, qr)
+    y = O.mx_dequant(q, s, fp4)
+    assert torch.equal(y, ref.mx_dequant(q, s, fp4))
+    rnd = torch.randint(0, 256, (1000, 16 if fp4 else 32), dtype=torch.uint8, generator=g).to(DEV)
+    if not fp4:
+        rnd = torch.where((rnd & 0x7F) == 0x7F, torch.zeros_like(rnd), rnd)          # no NaN encodings
+    sc = torch.randint(1, 255, (1000,), dtype=torch.uint8, generator=g).to(DEV)
+    a, b = O.mx_dequant(rnd, sc, fp4).float(), ref.mx_dequant(rnd, sc, fp4).float()
+    assert torch.equal(torch.nan_to_num(a, posinf=9e38, neginf=-9e38), torch.nan_to_num(b, posinf=9e38, neginf=-9e38))
+
+
 def test_attention_late_large_maximum_is_exact():
     """The exponent reference of a key tile is the row maximum of the EARLIER tiles; rows whose scores jump far above it
     (here by more than 60 nats, several such keys of different height in one tile) take the redo path."""
