@@ -96,6 +96,8 @@ def _fsdp_worker(rank, world, port, out_dir):
             loss.backward()
             g1 += a.grad / world
             g2 += b.grad / world
+        if t == 0:
+            first_grads = (g1.clone(), g2.clone())
         for W, gg, m, v in ((W1, g1, m1, v1), (W2, g2, m2, v2)):
             W.mul_(1 - lr * 0.01)
             m.mul_(0.9).add_(gg, alpha=0.1)
@@ -114,6 +116,19 @@ def _fsdp_worker(rank, world, port, out_dir):
             out = l2(h)
             loss = (out.float() - ts[rank].to(dev)).pow(2).mean()
             loss.backward()
+            if t == 0:
+                # the reduce-scattered fp32 gradient shard itself, before Adam normalises every element's step: the sum over
+                # ranks of this rank's rows against the fp32 reference (bf16 operands on both sides, fp32 accumulation)
+                from mojodiffusion_b200.parallel.fsdp import SLOT_BWD_DONE
+                ctx.barrier(SLOT_BWD_DONE)
+                torch.cuda.synchronize()
+                for lay, gref in ((l1, first_grads[0]), (l2, first_grads[1])):
+                    rl = lay.rows_local
+                    got_g = lay.g_shard.float() / world
+                    want_g = gref[rank * rl:(rank + 1) * rl]
+                    cg = float(torch.dot(got_g.flatten(), want_g.flatten()) / (got_g.norm() * want_g.norm() + 1e-30))
+                    assert cg >= 0.999, f"rank {rank} mode {mode}: gradient shard cosine {cg}"
+                    assert abs(float(got_g.norm() / want_g.norm()) - 1.0) < 0.02
             ctx.step(lr=lr, weight_decay=0.01)
         torch.cuda.synchronize()
         native.check_status()
