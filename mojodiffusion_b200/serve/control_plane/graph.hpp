@@ -904,6 +904,92 @@ inline const std::map<std::string, Kind>& Engine::registry() {
       c.emit("batch_size", one);
     });
     add({"ImageScale", "ImageScaleToTotalPixels", "ImageScaleBy"}, {"IMAGE"}, image_passthrough);
+    // Explicit resize: representable only when both target sides are given (no keep_proportion, no zero side, no size
+    // copied from another image); the sides become the request's width / height and are also INT outputs.
+    add({"ImageResizeKJ"}, {"IMAGE", "width", "height"}, [](Ctx& c) {
+      const Value* img = c.in("image", "IMAGE");
+      const Json& f = c.node.fields;
+      long long w = c.int_in("width", opt_int(f, "width", 512, 0, 8192)), h = c.int_in("height", opt_int(f, "height", 512, 0, 8192));
+      if (c.linked("get_image_size")) c.in_any("get_image_size", false);
+      if (c.pending) return;
+      if (c.linked("get_image_size"))
+        throw unsupported("workflow graph ImageResizeKJ get_image_size input copies the source image dims, which are not "
+                          "resolvable in the flat single-image model", c.node.id);
+      if (opt_bool(f, "keep_proportion", false))
+        throw unsupported("workflow graph ImageResizeKJ keep_proportion=true derives a dimension from the source image aspect, "
+                          "which is not resolvable in the flat single-image model; set explicit width and height instead", c.node.id);
+      if (w == 0 || h == 0)
+        throw unsupported("workflow graph ImageResizeKJ width/height of 0 keeps the source dimension, which is not resolvable "
+                          "in the flat single-image model; set explicit nonzero width and height", c.node.id);
+      if (w < 1 || w > 8192 || h < 1 || h > 8192) throw unsupported("workflow graph ImageResizeKJ width/height out of range", c.node.id);
+      c.out.set_if_missing("width", Json(w));
+      c.out.set_if_missing("height", Json(h));
+      Value v = text_value("IMAGE", img->text);
+      v.source = img->source;
+      c.emit("IMAGE", v);
+      Value wi = tagged("INT"), hi = tagged("INT");
+      wi.i = w; hi.i = h;
+      c.emit("width", wi);
+      c.emit("height", hi);
+    });
+    // Inpaint compositing after decode: the mask and its channel go to the request, the pasted image is what flows on.
+    add({"LanPaint_MaskBlend"}, {"IMAGE"}, [](Ctx& c) {
+      const Value* a = c.in("image1", "IMAGE");
+      const Value* b = c.in("image2", "IMAGE");
+      const Value* m = c.in("mask", "MASK");
+      if (c.pending) return;
+      c.out.set_if_missing("mask_image", Json(m->text));
+      c.out.set_if_missing("lanpaint_mask_channel", Json(m->source));
+      copy_field_if_missing(c.out, c.node.fields, "blend_overlap", "lanpaint_mask_blend_overlap");
+      c.emit("IMAGE", text_value("IMAGE", !b->text.empty() ? b->text : a->text));
+    });
+    // Image-to-video conditioning (Wan): size and length of the clip, the start image, conditioning passed through.
+    add({"WanImageToVideo"}, {"positive", "negative", "LATENT"}, [](Ctx& c) {
+      const Value* pos = c.in("positive", "CONDITIONING");
+      const Value* neg = c.linked("negative") ? c.in("negative", "CONDITIONING", false) : nullptr;
+      c.in("vae", "VAE");
+      const Value* img = c.in("image", "IMAGE");
+      if (c.linked("clip_vision_output")) c.in("clip_vision_output", "CLIP_VISION_OUTPUT", false);
+      if (c.pending) return;
+      const Json& f = c.node.fields;
+      long long w = opt_int(f, "width", 832, 16, 4096), h = opt_int(f, "height", 480, 16, 4096), n = opt_int(f, "length", 81, 1, 4096);
+      c.out.set_if_missing("width", Json(w));
+      c.out.set_if_missing("height", Json(h));
+      c.out.set_if_missing("num_frames", Json(n));
+      c.out.set_if_missing("frame_count", Json(n));
+      c.out.set_if_missing("video_conditioning_image", Json(img->text));
+      c.emit("positive", text_value("CONDITIONING", pos->text));
+      c.emit("negative", text_value("CONDITIONING", neg ? neg->text : ""));
+      c.emit("LATENT", latent(w, h, 1, img->text));
+    });
+    // One-node LTX video sampler: prompt, size, clip length and rate in its widgets; emits latent, video and audio handles.
+    add({"LTXVSampler"}, {"LATENT", "VIDEO", "AUDIO"}, [](Ctx& c) {
+      const bool by_name = c.linked("ltxv_model");
+      if (!by_name && !c.linked("model")) throw unsupported("workflow graph LTXVSampler missing ltxv_model input", c.node.id);
+      const Value* m = c.in(by_name ? "ltxv_model" : "model", "MODEL");
+      if (c.linked("audio")) c.in("audio", "AUDIO", false);
+      if (c.pending) return;
+      const Json& f = c.node.fields;
+      if (!m->text.empty()) c.out.set_if_missing("model", Json(m->text));
+      if (!fstr(f, "prompt").empty()) c.out.set_if_missing("prompt", Json(fstr(f, "prompt")));
+      if (!fstr(f, "negative_prompt").empty()) c.out.set_if_missing("negative", Json(fstr(f, "negative_prompt")));
+      long long w = opt_int(f, "width", 768, 16, 4096), h = opt_int(f, "height", 512, 16, 4096), n = opt_int(f, "num_frames", 97, 1, 4096);
+      long long fps = opt_int(f, "frame_rate", 24, 1, 240);
+      c.out.set_if_missing("width", Json(w));
+      c.out.set_if_missing("height", Json(h));
+      c.out.set_if_missing("num_frames", Json(n));
+      c.out.set_if_missing("frame_count", Json(n));
+      c.out.set_if_missing("steps", Json(opt_int(f, "steps", 25, 1, 1000)));
+      c.out.set_if_missing("seed", Json(opt_int(f, "seed", 0, 0, 4294967295LL)));
+      c.out.set_if_missing("cfg", Json(opt_float(f, "cfg", 3.0, 0.0, 100.0)));
+      c.out.set_if_missing("fps", Json(fps));
+      c.out.set_if_missing("frame_rate", Json(fps));
+      copy_field_if_missing(c.out, f, "mode", "video_mode");
+      for (const char* k : {"stg_scale", "audio_start_time", "audio_duration"}) copy_field_if_missing(c.out, f, k, k);
+      c.emit("LATENT", latent(w, h, 1));
+      c.emit("VIDEO", text_value("VIDEO", ""));
+      c.emit("AUDIO", text_value("AUDIO", ""));
+    });
     add({"ImagePadForOutpaint"}, {"IMAGE", "MASK"}, [](Ctx& c) {
       const Value* img = c.in("image", "IMAGE");
       if (c.pending) return;

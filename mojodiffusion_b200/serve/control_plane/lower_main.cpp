@@ -1,5 +1,6 @@
 // mdb-lower: reads one generation request (JSON) from stdin or a file, lowers its workflow graph and prints the flat
 // request. Exit code 0 on success; on a lowering error prints {"error": ..., "status": 501|422} and exits 3.
+// ``mdb-lower --node-types`` prints the node type ids the graph executor accepts (a JSON array) and exits.
 #include <fstream>
 #include <iostream>
 #include <sstream>
@@ -8,6 +9,12 @@
 
 int main(int argc, char** argv) {
   std::stringstream ss;
+  if (argc > 1 && std::string(argv[1]) == "--node-types") {
+    mdb::Json arr = mdb::Json::array();
+    for (auto& kv : mdb::graph::Engine::registry()) arr.push(mdb::Json(kv.first));
+    std::cout << arr.dump() << "\n";
+    return 0;
+  }
   if (argc > 1) {
     std::ifstream f(argv[1]);
     if (!f) { std::cerr << "cannot open " << argv[1] << "\n"; return 2; }

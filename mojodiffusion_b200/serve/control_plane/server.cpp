@@ -65,6 +65,11 @@ static std::string now_http_date() {
   strftime(buf, sizeof buf, "%a, %d %b %Y %H:%M:%S GMT", &g);
   return buf;
 }
+// true when ``path`` is ``root`` itself or lies under it (the prefix must end at a path separator)
+static bool inside_root(const std::string& path, const std::string& root) {
+  if (root.empty() || path.compare(0, root.size(), root) != 0 || path.find("..") != std::string::npos) return false;
+  return path.size() == root.size() || path[root.size()] == '/' || root.back() == '/';
+}
 static bool safe_relative(const std::string& p) {
   if (p.empty() || p[0] == '/') return false;
   return p.find("..") == std::string::npos && p.find('\0') == std::string::npos;
@@ -129,6 +134,9 @@ struct Job {
   Json request;                // lowered request as submitted (for manifests)
   std::vector<std::string> events;   // JSON frames, in order; never shrinks
   bool cancel_requested = false;
+  double hires_scale = 0.0, hires_denoise = 0.35;   // control-plane only: a second img2img pass under the same job id
+  int pass = 1;
+  std::string hires_src, kind_override;
   bool terminal() const { return state == "done" || state == "failed" || state == "cancelled"; }
   Json summary() const {
     Json j = Json::object();
@@ -290,6 +298,7 @@ static void driver_thread(App* ap) {
     };
     const Family* fam = family_of(job->model);
     if (!fam) { fail("no worker kind for model '" + job->model + "'"); continue; }
+    job->pass = 1;
     std::string kind = fam->kind;
     if (worker.alive() && kind != app.resident_kind) {
       worker.kill_and_reap();                                            // model swap: exit is what frees device memory
@@ -325,7 +334,34 @@ static void driver_thread(App* ap) {
         job->step = ev.step; job->total = ev.total; job->phase = ev.phase;
         app.publish_locked(*job, ws_frame_for(*job, ev));
       } else if (ev.terminal()) {
+        if (ev.kind == wire::Event::Done && job->hires_scale > 1.0 && job->pass == 1 && !job->cancel_requested) {
+          // Hires two-pass: the base image becomes the init image of an img2img pass at the scaled size (the worker
+          // resamples it; snapped to 512 or 1024 like the encoder grids it supports), under the same job id. Only the
+          // second pass publishes the terminal event. The base file is moved under a name the gallery does not list.
+          std::string base = ev.output_path;
+          size_t slash = base.find_last_of('/');
+          std::string src = (slash == std::string::npos ? std::string("") : base.substr(0, slash + 1)) + "hires_src_" + (slash == std::string::npos ? base : base.substr(slash + 1));
+          if (rename(base.c_str(), src.c_str()) != 0) src = base;
+          long long side = std::max(job->params.get("width").as_int(), job->params.get("height").as_int());
+          long long target = static_cast<long long>(side * job->hires_scale + 0.5) >= 768 ? 1024 : 512;
+          Json p2 = job->params;
+          p2.set("init_image", Json(src)); p2.set("creativity", Json(job->hires_denoise));
+          p2.set("width", Json(static_cast<int64_t>(target))); p2.set("height", Json(static_cast<int64_t>(target)));
+          job->pass = 2; job->hires_src = src; job->phase = "hires";
+          wire::Event pe; pe.kind = wire::Event::Progress; pe.step = 0; pe.total = job->total; pe.phase = "hires";
+          app.publish_locked(*job, ws_frame_for(*job, pe));
+          std::string e2;
+          if (!worker.send_line(wire::start_line(p2), &e2)) {
+            wire::Event fe; fe.kind = wire::Event::Failed; fe.error = "hires pass-2 send_start failed: " + e2;
+            finish_job(app, *job, fe);
+            app.in_flight.clear();
+            worker.kill_and_reap();
+            break;
+          }
+          continue;
+        }
         finish_job(app, *job, ev);
+        if (!job->hires_src.empty() && job->hires_src != job->output_path) remove(job->hires_src.c_str());
         app.in_flight.clear();
         break;
       }
@@ -421,6 +457,13 @@ static bool prepare(const std::string& body, Json* lowered, Json* params, int* s
   std::string err;
   if (!wire::params_from_request(req, params, &err)) { *status = 400; *report = Json::object(); report->set("error", Json(err)); return false; }
   std::string adm = admission_error(*params);
+  if (adm.empty() && req.present("hires_scale")) {
+    double hs = req.get("hires_scale").is_number() ? req.get("hires_scale").as_double() : -1.0;
+    double hd = req.present("hires_denoise") ? (req.get("hires_denoise").is_number() ? req.get("hires_denoise").as_double() : -1.0) : 0.35;
+    if (hs < 1.0 || hs > 4.0) adm = "hires_scale out of range [1, 4]";
+    else if (hd <= 0.0 || hd > 1.0) adm = "hires_denoise out of range (0, 1]";
+    else if (hs > 1.0 && std::string(family_of(params->str("model"))->kind) == "ltx2") adm = "hires two-pass applies to image models";
+  }
   if (!adm.empty()) {
     *status = 400;
     Json r = Json::object();
@@ -465,6 +508,8 @@ static std::vector<std::string> enqueue(App& app, const Json& lowered, Json para
     j->total = p.get("steps").as_int();
     j->image_index = i;
     j->image_count = images;
+    if (lowered.get("hires_scale").is_number()) j->hires_scale = lowered.get("hires_scale").as_double();
+    if (lowered.get("hires_denoise").is_number()) j->hires_denoise = lowered.get("hires_denoise").as_double();
     app.jobs.push_back(j);
     ids.push_back(j->id);
   }
@@ -472,6 +517,68 @@ static std::vector<std::string> enqueue(App& app, const Json& lowered, Json para
   app.cv.notify_all();
   return ids;
 }
+
+// ---- checkpoint scan: architecture from the safetensors header (first MiB of key names) or from the file name ----------
+static std::string header_text(const std::string& path, size_t cap = 1 << 20) {
+  std::ifstream f(path, std::ios::binary);
+  unsigned char len8[8];
+  if (!f || !f.read(reinterpret_cast<char*>(len8), 8)) return "";
+  unsigned long long n = 0;
+  for (int i = 0; i < 8; ++i) n |= static_cast<unsigned long long>(len8[i]) << (8 * i);
+  if (n == 0 || n > (1ull << 33)) return "";
+  std::string s(static_cast<size_t>(std::min<unsigned long long>(n, cap)), '\0');
+  f.read(&s[0], static_cast<std::streamsize>(s.size()));
+  s.resize(static_cast<size_t>(f.gcount()));
+  return s;
+}
+static bool has(const std::string& h, const char* needle) { return h.find(needle) != std::string::npos; }
+// substring probes over tensor names, most specific first
+static std::string detect_arch(const std::string& h) {
+  if (h.empty()) return "unknown";
+  if (has(h, "\"noise_refiner.")) return "zimage";
+  if (has(h, "\"double_stream_modulation_img")) return "flux-2/klein";
+  if (has(h, "\"distilled_guidance_layer")) return "chroma";
+  if (has(h, "\"double_blocks.")) return "flux";
+  if (has(h, "\"audio_vae.") || has(h, "audio_to_video_attn")) return "ltx2";
+  if (has(h, "\"embed_image_indicator.weight\"") || has(h, "\"llm_cond_proj.weight\"")) return "ideogram4";
+  if (has(h, "\"model.diffusion_model.joint_blocks") || has(h, "\"joint_blocks.")) return "sd3";
+  if (has(h, "\"model.diffusion_model.input_blocks") || has(h, "\"input_blocks.0.")) return "sdxl";
+  if (has(h, "\"txt_norm.")) return "qwen-image";
+  if (has(h, "\"time_projection.")) return "wan";
+  if (has(h, "\"adaLN_sa_ln") || has(h, ".adaLN_sa_ln.")) return "ernie-image";
+  if (has(h, "\"net.blocks.0.adaln_modulation_self_attn")) return "anima";
+  if (has(h, "scale_shift_table") && has(h, "transformer_blocks.0.attn1.")) return "ltx2";
+  if (has(h, "\"decoder.up.") || has(h, "\"decoder.up_blocks.") || has(h, "\"decoder.upsamples.")) return "vae";
+  return "unknown";
+}
+static std::string detect_arch_from_name(const std::string& name) {
+  std::string lo = mdb::graph::lower(name);
+  auto any = [&](std::initializer_list<const char*> ns) { for (auto* n : ns) if (lo.find(n) != std::string::npos) return true; return false; };
+  if (any({"wan2.2", "wan 2.2", "wan-2.2", "wan_2_2", "wan22"})) return "wan2.2";
+  if (any({"zimage_l2p", "z-image-l2p", "z_image_l2p", "l2p"})) return "zimage-l2p";
+  if (any({"hidream", "hi-dream", "hi_dream"})) return "hidream";
+  if (any({"sensenova", "sense_nova", "sense-nova"})) return "sensenova";
+  if (any({"qwen"})) return "qwen-image";
+  if (any({"sd3", "sd35"})) return "sd3";
+  if (any({"sdxl", "stable-diffusion-xl", "animagine"})) return "sdxl";
+  if (any({"flux2", "flux-2", "flux_2"})) return "flux-2";
+  if (any({"flux1", "flux-1", "flux_1", "flux-dev"})) return "flux";
+  if (any({"ltx"})) return "ltx2";
+  return "unknown";
+}
+static std::string detect_lora_target_arch(const std::string& h) {
+  if (has(h, "\"noise_refiner.") || has(h, "\"context_refiner.")) return "zimage";
+  if (has(h, "\"layers.") && has(h, ".lora_")) return "zimage";
+  if (has(h, "zimage") || has(h, "z_image")) return "zimage";
+  if (has(h, "\"lora_unet_") || has(h, "\"lora_te1") || has(h, "\"lora_te2")) return "sdxl";
+  if (has(h, "\"lora_transformer_distilled_guidance_layer")) return "chroma";
+  if (has(h, "\"lora_transformer_single_transformer_blocks") || has(h, "\"lora_transformer_transformer_blocks") || has(h, "\"lora_transformer")) return "flux";
+  if (has(h, "qwen")) return "qwen-image";
+  if (has(h, "ideogram")) return "ideogram4";
+  if (has(h, "ltx") || has(h, "diffusion_model.transformer_blocks")) return "ltx2";
+  return "unknown";
+}
+static bool looks_like_lora(const std::string& h) { return has(h, ".lora_down.") || has(h, ".lora_A.") || has(h, ".lora_up.") || has(h, ".lora_B."); }
 
 static void list_models(const App& app, Json& out) {
   Json arr = Json::array();
@@ -489,6 +596,13 @@ static void list_models(const App& app, Json& out) {
         m.set("name", Json(n)); m.set("path", Json(full)); m.set("bytes", Json(static_cast<int64_t>(dir ? 0 : st.st_size)));
         const Family* f = family_of(n);
         m.set("kind", Json(f ? f->kind : "unknown")); m.set("admitted", Json(f ? f->admitted : false));
+        // architecture: the file name decides when it is recognisable, else the tensor names of the header
+        std::string arch = detect_arch_from_name(n), source = "name", header;
+        if (!dir) header = header_text(full);
+        bool lora = !dir && looks_like_lora(header);
+        if (lora) { m.set("lora", Json(true)); std::string t = detect_lora_target_arch(header); if (arch == "unknown") { arch = t; source = "header"; } }
+        else if (arch == "unknown") { arch = detect_arch(header); source = arch == "unknown" ? "none" : "header"; }
+        m.set("arch", Json(arch)); m.set("arch_source", Json(source));
         arr.push(m);
       }
       closedir(d);
@@ -719,7 +833,7 @@ static void handle(App& app, const http::Request& rq, http::Response& rs) {
   if (p == "/v1/gallery" && m == "GET") { Json o = Json::object(); o.set("items", gallery_items(app)); return reply(rs, 200, o); }
   if (p == "/v1/gallery/read" && m == "GET") {
     std::string path = rq.param("path");
-    if (path.compare(0, app.out_dir.size(), app.out_dir) != 0 || path.find("..") != std::string::npos) return reply_error(rs, 400, "path outside the gallery root");
+    if (!inside_root(path, app.out_dir)) return reply_error(rs, 400, "path outside the gallery root");
     PngInfo png = read_png_info(path);
     if (!png.ok) return reply_error(rs, 404, "not a PNG: " + path);
     Json o = Json::object(), text = Json::object();
@@ -802,7 +916,96 @@ static void handle(App& app, const http::Request& rq, http::Response& rs) {
                       : rel.size() > 5 && rel.compare(rel.size() - 5, 5, ".json") == 0 ? "application/json" : "application/octet-stream";
     return;
   }
-  if (p == "/v1/video" || p == "/v1/video/probe" || p == "/v1/llms" || p == "/v1/magic_prompt")
+  // ---- video: the LTX-2 worker writes a PNG sequence (<job>.frames/NNNN.png) and a sidecar; no container encoder exists
+  //      in this build, so "mp4" stays empty and the result names the frame directory instead
+  //      (serenitymojo/serve/video_api.mojo:146-477)
+  if (p == "/v1/video" && m == "GET") {
+    Json o = Json::object();
+    o.set("schema", Json("serenity.video_status.v1")); o.set("endpoint", Json("/v1/video"));
+    o.set("accepted", Json(true)); o.set("backend", Json("ltx2")); o.set("container", Json("png-sequence"));
+    o.set("mp4", Json("")); o.set("audio", Json(false));
+    o.set("ffprobe", Json(system("command -v ffprobe >/dev/null 2>&1") == 0));
+    Json t = Json::object();
+    t.set("target_width", Json(768)); t.set("target_height", Json(512)); t.set("target_frame_count", Json(121)); t.set("target_fps", Json(24));
+    o.set("ltx2", t);
+    { std::lock_guard<std::mutex> lk(app.mu); o.set("resident", Json(app.resident_kind)); }
+    return reply(rs, 200, o);
+  }
+  if (p == "/v1/video" && m == "POST") {
+    Json body;
+    if (!Json::try_parse(rq.body, &body) || !body.is_object()) return reply_error(rs, 400, "invalid request body", "serenity.video_error.v1");
+    if (body.str("model").empty()) body.set("model", Json("ltx2"));
+    const Family* vf = family_of(body.str("model"));
+    if (!vf || std::string(vf->kind) != "ltx2") return reply_error(rs, 400, "/v1/video needs a video model (family ltx2), got '" + body.str("model") + "'", "serenity.video_error.v1");
+    body.set_if_missing("width", Json(768)); body.set_if_missing("height", Json(512));
+    body.set_if_missing("frames", Json(121)); body.set_if_missing("fps", Json(24));
+    long long frames = body.get("frames").as_int(), fps = body.get("fps").as_int();
+    if (frames < 1 || frames > 1025 || (frames - 1) % 8 != 0) return reply_error(rs, 400, "frames must be 8k + 1 within [1, 1025]", "serenity.video_error.v1");
+    if (fps < 1 || fps > 120) return reply_error(rs, 400, "fps out of range [1, 120]", "serenity.video_error.v1");
+    body.set("images", Json(1));
+    Json lowered, params, report;
+    int status = 200;
+    if (!prepare(body.dump(), &lowered, &params, &status, &report)) return reply(rs, status, report);
+    auto ids = enqueue(app, lowered, params);
+    Json o = Json::object();
+    o.set("schema", Json("serenity.video_job.v1")); o.set("job_id", Json(ids.front())); o.set("state", Json("queued"));
+    o.set("frames", Json(frames)); o.set("fps", Json(fps)); o.set("container", Json("png-sequence"));
+    o.set("result", Json("/v1/video/result?job=" + ids.front()));
+    return reply(rs, 200, o);
+  }
+  if (p == "/v1/video/result" && m == "GET") {
+    std::string id = rq.param("job");
+    std::shared_ptr<Job> j;
+    { std::lock_guard<std::mutex> lk(app.mu); j = app.find(id); }
+    if (!j) return reply_error(rs, 404, "no such job: " + id, "serenity.video_error.v1");
+    Json o = Json::object();
+    std::lock_guard<std::mutex> lk(app.mu);
+    o.set("schema", Json("serenity.video_result.v1")); o.set("job_id", Json(j->id)); o.set("state", Json(j->state));
+    o.set("ready", Json(j->state == "done")); o.set("error", Json(j->error)); o.set("mp4", Json("")); o.set("audio", Json(false));
+    o.set("container", Json("png-sequence"));
+    long long count = 0, w = 0, h = 0;
+    std::string fdir;
+    if (j->state == "done" && j->output_path.size() > 4) {
+      fdir = j->output_path.substr(0, j->output_path.size() - 4) + ".frames";
+      if (DIR* d = opendir(fdir.c_str())) {
+        while (dirent* e = readdir(d)) { std::string n = e->d_name; if (n.size() > 4 && n.compare(n.size() - 4, 4, ".png") == 0) ++count; }
+        closedir(d);
+      }
+      PngInfo png = read_png_info(j->output_path);
+      w = png.width; h = png.height;
+    }
+    Json gp;
+    double fps = 24.0;
+    if (Json::try_parse(j->params.str("params_json"), &gp) && gp.get("fps").is_number()) fps = gp.get("fps").as_double();
+    o.set("first_frame", Json(j->output_path)); o.set("frames_dir", Json(count > 0 ? fdir : std::string("")));
+    o.set("frame_count", Json(static_cast<int64_t>(count))); o.set("width", Json(static_cast<int64_t>(w))); o.set("height", Json(static_cast<int64_t>(h)));
+    o.set("fps", Json(fps)); o.set("duration", Json(fps > 0 ? count / fps : 0.0));
+    return reply(rs, 200, o);
+  }
+  if (p == "/v1/video/probe" && m == "POST") {
+    Json body;
+    if (!Json::try_parse(rq.body, &body) || body.str("path").empty()) return reply_error(rs, 400, "probe needs a path", "serenity.video_error.v1");
+    std::string path = body.str("path");
+    if (!inside_root(path, app.out_dir)) return reply_error(rs, 400, "path outside the gallery root", "serenity.video_error.v1");
+    struct stat st;
+    if (stat(path.c_str(), &st) != 0) return reply_error(rs, 404, "no such file: " + path, "serenity.video_error.v1");
+    if (S_ISDIR(st.st_mode)) {                      // a frame directory: count and measure the frames
+      long long count = 0;
+      std::string first;
+      if (DIR* d = opendir(path.c_str())) {
+        while (dirent* e = readdir(d)) { std::string n = e->d_name; if (n.size() > 4 && n.compare(n.size() - 4, 4, ".png") == 0) { ++count; if (first.empty() || n < first) first = n; } }
+        closedir(d);
+      }
+      PngInfo png = first.empty() ? PngInfo() : read_png_info(path + "/" + first);
+      Json o = Json::object();
+      o.set("schema", Json("serenity.video_probe.v1")); o.set("container", Json("png-sequence")); o.set("frame_count", Json(static_cast<int64_t>(count)));
+      o.set("width", Json(static_cast<int64_t>(png.width))); o.set("height", Json(static_cast<int64_t>(png.height))); o.set("audio", Json(false));
+      return reply(rs, 200, o);
+    }
+    if (system("command -v ffprobe >/dev/null 2>&1") != 0) return reply_error(rs, 501, "ffprobe is not available on PATH", "serenity.video_error.v1");
+    return reply_error(rs, 501, "container probing is not built: only PNG frame directories are produced here", "serenity.video_error.v1");
+  }
+  if (p == "/v1/llms" || p == "/v1/magic_prompt")
     return reply_error(rs, 501, "not available in this build: " + p);
   if (p == "/" || p == "/index.html") {
     rs.content_type = "text/html";

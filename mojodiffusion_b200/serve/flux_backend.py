@@ -194,9 +194,8 @@ class FluxBackend(GenBackend):
         x = noise
         self.init_latent = self.mask = None
         if p.init_image:
-            img, _ = load_png(p.init_image)
-            t = torch.from_numpy(np.ascontiguousarray(img[..., :3])).float().permute(2, 0, 1)[None] / 127.5 - 1.0
-            t = torch.nn.functional.interpolate(t, size=(p.height, p.width), mode="bilinear", align_corners=False)
+            from .image_io import load_image_rgb, load_mask, resize_lanczos
+            t = resize_lanczos(load_image_rgb(p.init_image), p.height, p.width).clamp(-1.0, 1.0)
             with torch.no_grad():
                 z0 = self.vae.encode(t.to(self.device), sample=False).float().cpu()
             start = min(p.steps - 1, int(round(p.steps * (1.0 - max(0.0, min(1.0, p.creativity))))))
@@ -204,9 +203,7 @@ class FluxBackend(GenBackend):
             x = (1.0 - s0) * z0 + s0 * noise
             self.init_latent = z0
             if p.mask_image:
-                m, _ = load_png(p.mask_image)
-                mt = torch.from_numpy(np.ascontiguousarray(m[..., 0] if m.ndim == 3 else m)).float()[None, None] / 255.0
-                self.mask = torch.nn.functional.interpolate(mt, size=(h, w), mode="bilinear", align_corners=False)
+                self.mask = resize_lanczos(load_mask(p.mask_image), h, w).clamp(0.0, 1.0)
         self.noise = noise
         self.sigmas = sigmas
         self.start, self.n_steps = start, p.steps - start

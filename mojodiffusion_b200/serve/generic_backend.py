@@ -198,10 +198,35 @@ class GenericBackend(GenBackend):
     def _encode(self, p: JobParams) -> None:
         self.cfg = cfg = self._model_config()
         T, D, P = self._text_shape(cfg)
-        self.txt, self.pooled, self.text_kind = self._read_caps(p.sample_caps_pos, p.prompt, T, D, P)
         self.use_cfg = p.cfg > 1.0
+        if self._encode_in_child(p, D, P):
+            return
+        self.txt, self.pooled, self.text_kind = self._read_caps(p.sample_caps_pos, p.prompt, T, D, P)
         if self.use_cfg:
             self.txt_neg, self.pooled_neg, _ = self._read_caps(p.sample_caps_neg, p.negative, self.txt.shape[1], D, P)
+
+    def _encode_in_child(self, p: JobParams, D: int, P: int) -> bool:
+        """Real text encoders in a child process that exits afterwards (``MDB_ENCODERS_DIR=<dir>``; with the tiny
+        architectures ``MDB_ENCODE_SUBPROCESS=1`` runs tiny random-weight encoders through the same protocol). Pre-encoded
+        caption files still win. Returns False when this path is not configured for the family."""
+        from .encode_subprocess import FAMILY_ENCODERS, encode_in_child
+        enc_dir = os.environ.get("MDB_ENCODERS_DIR", "")
+        tiny_child = self.tiny and os.environ.get("MDB_ENCODE_SUBPROCESS", "") == "1"
+        if self.kind not in FAMILY_ENCODERS or not (enc_dir or tiny_child) or (p.sample_caps_pos and os.path.isfile(p.sample_caps_pos)):
+            return False
+        res = encode_in_child(self.kind, p.prompt, p.negative if self.use_cfg else None, enc_dir, tiny_child,
+                              device="cpu" if self.device.type == "cpu" else "")
+
+        def fit(t, width):                      # tiny encoders are narrower than the tiny backbones' text inputs
+            return t if t.shape[-1] == width else torch.nn.functional.pad(t, (0, width - t.shape[-1])) if t.shape[-1] < width else t[..., :width]
+        self.txt, self.pooled = fit(res["text_embedding"].float(), D), fit(res["pooled"].float(), max(P, 1))
+        if self.use_cfg:
+            self.txt_neg, self.pooled_neg = fit(res["neg_text_embedding"].float(), D), fit(res["neg_pooled"].float(), max(P, 1))
+            n = min(self.txt.shape[1], self.txt_neg.shape[1])
+            self.txt, self.txt_neg = self.txt[:, :n], self.txt_neg[:, :n]
+        self.text_kind = "encoder-subprocess"
+        self.encoder_pid = int(res["child_pid"][0])
+        return True
 
     def _load(self, p: JobParams) -> None:
         from ..models.vae import AutoencoderKL
@@ -395,7 +420,8 @@ class GenericBackend(GenBackend):
     def _write_sidecar(self, p: JobParams, path: str) -> None:
         peak = torch.cuda.max_memory_allocated() if self.device.type == "cuda" else 0
         side = {"schema": f"serenity.{self.kind}.daemon_result.v1", "job_id": p.job_id, "model": p.model,
-                "weights": self.weights_kind, "text": self.text_kind, "cfg": p.cfg if self.use_cfg else 1.0,
+                "weights": self.weights_kind, "text": self.text_kind, "encoder_pid": getattr(self, "encoder_pid", 0),
+                "cfg": p.cfg if self.use_cfg else 1.0,
                 "stage_seconds": {k: round(v, 4) for k, v in self.stage_s.items()}, "peak_device_bytes": int(peak),
                 "steps_run": p.steps, "sampler": "euler", "device": str(self.device)}
         if self.kind == "ltx2":

@@ -192,10 +192,10 @@ def test_wire_contract():
 
 # ---- live server ---------------------------------------------------------------------------------------------------
 class Server:
-    def __init__(self, bins, out_dir, extra_env=None):
+    def __init__(self, bins, out_dir, extra_env=None, extra_args=()):
         env = dict(os.environ, PYTHONPATH=REPO + os.pathsep + os.environ.get("PYTHONPATH", ""), **(extra_env or {}))
         worker = f"{sys.executable} -m mojodiffusion_b200.serve.worker --kind {{kind}}"
-        self.proc = subprocess.Popen([bins[0], "--worker", worker, "--out-dir", out_dir, "--port", "0", "--settle-ms", "50"],
+        self.proc = subprocess.Popen([bins[0], "--worker", worker, "--out-dir", out_dir, "--port", "0", "--settle-ms", "50", *extra_args],
                                      stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=env)
         self.port = json.loads(self.proc.stdout.readline())["listening"]
         self.out_dir = out_dir
@@ -429,5 +429,155 @@ def test_other_families_serve_through_the_worker(bins, tmp_path, model, backend,
         assert s.call("GET", "/v1/health")[1]["backend"] == backend
         if backend == "ltx2":                       # video: frames beside the poster image
             assert side["frames"] == 9 and len(os.listdir(side["frames_dir"])) == 9
+    finally:
+        s.close()
+
+
+# ---- hires two-pass, video routes, checkpoint scan, node type allowlist ---------------------------------------------
+def test_hires_two_pass_runs_under_one_job(server):
+    st, r = server.call("POST", "/v1/generate", {"model": "stub", "prompt": "x", "steps": 3, "width": 256, "height": 256, "seed": 1,
+                                                 "hires_scale": 2.0, "hires_denoise": 0.4})
+    assert st == 200
+    ev = server.ws_events(r["job_id"])
+    assert [e["ev"] for e in ev].count("done") == 1 and ev[-1]["ev"] == "done"           # one terminal event for both passes
+    assert any(e.get("phase") == "hires" for e in ev)
+    assert [e["step"] for e in ev if e.get("ev") == "progress" and e.get("phase") != "hires"] == [1, 2, 3, 1, 2, 3]
+    img, text = load_png(ev[-1]["output_path"])
+    assert img.shape == (512, 512, 3)                                                    # 256 * 2 = 512 < 768 -> refine at 512
+    assert int(img[100, 100, 2]) == int(0.4 * 255.0)                                     # the refine pass ran img2img at the hires creativity
+    assert not [f for f in os.listdir(server.out_dir) if f.startswith("hires_src_")]      # the upscale source is removed
+    st, g = server.call("GET", "/v1/gallery")
+    assert [it["id"] for it in g["items"]] == [r["job_id"]]
+    st, r2 = server.call("POST", "/v1/generate", {"model": "stub", "prompt": "x", "steps": 2, "width": 512, "height": 384, "hires_scale": 1.5})
+    assert load_png(server.wait(r2["job_id"])["output_path"])[0].shape == (1024, 1024, 3)  # 768 -> refine at 1024
+    for bad in ({"hires_scale": 9}, {"hires_scale": 0.5}, {"hires_scale": 2, "hires_denoise": 0}):
+        st, e = server.call("POST", "/v1/generate", {"model": "stub", "prompt": "x", **bad})
+        assert st == 400 and "hires" in e["error"]
+
+
+def test_video_routes_over_the_ltx_worker(bins, tmp_path):
+    s = Server(bins, str(tmp_path / "out"), {"MDB_ARCH": "tiny"})
+    try:
+        st, v = s.call("GET", "/v1/video")
+        assert st == 200 and v["schema"] == "serenity.video_status.v1" and v["container"] == "png-sequence" and v["mp4"] == ""
+        st, e = s.call("POST", "/v1/video", {"model": "flux1-tiny", "prompt": "x"})
+        assert st == 400 and "video model" in e["error"]
+        st, e = s.call("POST", "/v1/video", {"model": "ltx-2-tiny", "prompt": "x", "frames": 10})
+        assert st == 400 and "8k + 1" in e["error"]
+        st, r = s.call("POST", "/v1/video", {"model": "ltx-2-tiny", "prompt": "a wave", "frames": 9, "fps": 12, "width": 64, "height": 64, "steps": 2, "seed": 4})
+        assert st == 200 and r["schema"] == "serenity.video_job.v1" and r["container"] == "png-sequence", r
+        st, pending = s.call("GET", "/v1/video/result?job=" + r["job_id"])
+        assert st == 200 and pending["schema"] == "serenity.video_result.v1"
+        j = s.wait(r["job_id"], timeout=240)
+        assert j["state"] == "done", j
+        st, res = s.call("GET", "/v1/video/result?job=" + r["job_id"])
+        assert res["ready"] is True and res["frame_count"] >= 1 and res["fps"] == 12 and res["mp4"] == "" and res["audio"] is False
+        assert res["frames_dir"].endswith(".frames") and abs(res["duration"] - res["frame_count"] / 12) < 1e-9
+        assert len([f for f in os.listdir(res["frames_dir"]) if f.endswith(".png")]) == res["frame_count"]
+        st, pr = s.call("POST", "/v1/video/probe", {"path": res["frames_dir"]})
+        assert st == 200 and pr["frame_count"] == res["frame_count"] and pr["width"] == res["width"] > 0
+        st, e = s.call("POST", "/v1/video/probe", {"path": "/etc"})
+        assert st == 400
+        st, e = s.call("GET", "/v1/video/result?job=job-9999")
+        assert st == 404
+    finally:
+        s.close()
+
+
+def _fake_safetensors(path, keys):
+    header = json.dumps({k: {"dtype": "BF16", "shape": [1], "data_offsets": [0, 2]} for k in keys}).encode()
+    with open(path, "wb") as fh:
+        fh.write(struct.pack("<Q", len(header)) + header + b"\0\0")
+
+
+def test_models_route_detects_architecture_from_headers(bins, tmp_path):
+    md = tmp_path / "models"
+    md.mkdir()
+    cases = {"a.safetensors": (["double_blocks.0.img_attn.qkv.weight", "single_blocks.0.linear1.weight"], "flux", "header"),
+             "b.safetensors": (["noise_refiner.0.attention.to_q.weight", "layers.0.attention.to_q.weight"], "zimage", "header"),
+             "c.safetensors": (["double_stream_modulation_img.lin.weight", "double_blocks.0.img_attn.qkv.weight"], "flux-2/klein", "header"),
+             "d.safetensors": (["model.diffusion_model.input_blocks.0.0.weight"], "sdxl", "header"),
+             "e.safetensors": (["txt_norm.weight", "transformer_blocks.0.attn.add_q_proj.weight"], "qwen-image", "header"),
+             "f.safetensors": (["distilled_guidance_layer.in_proj.weight", "double_blocks.0.img_attn.qkv.weight"], "chroma", "header"),
+             "my_sdxl_finetune.safetensors": (["whatever.weight"], "sdxl", "name"),
+             "g.safetensors": (["layers.0.adaLN_sa_ln.weight", "text_proj.weight"], "ernie-image", "header"),
+             "h.safetensors": (["something.else"], "unknown", "none"),
+             "style.safetensors": (["lora_unet_down_blocks_0.lora_down.weight", "lora_unet_down_blocks_0.lora_up.weight"], "sdxl", "header")}
+    for name, (keys, _, _) in cases.items():
+        _fake_safetensors(str(md / name), keys)
+    (md / "broken.safetensors").write_bytes(b"\x01")
+    s = Server(bins, str(tmp_path / "out"), extra_args=("--models-dir", str(md)))
+    try:
+        st, r = s.call("GET", "/v1/models")
+        got = {m["name"]: m for m in r["models"]}
+        for name, (_, arch, source) in cases.items():
+            assert got[name]["arch"] == arch and got[name]["arch_source"] == source, (name, got[name])
+        assert got["style.safetensors"].get("lora") is True and got["broken.safetensors"]["arch"] == "unknown"
+        st, e = s.call("GET", "/v1/gallery/read?path=" + urllib.request.quote(s.out_dir + "X/evil.png"))
+        assert st == 400 and "outside" in e["error"]                  # a sibling directory sharing the prefix is outside the root
+    finally:
+        s.close()
+
+
+REFERENCE_NODE_TYPES = """BOOLConstant BasicGuider BasicScheduler BetaSamplingScheduler CFGGuider CLIPLoader CLIPTextEncode CLIPTextEncodeFlux
+CLIPVisionEncode CLIPVisionLoader CheckpointLoaderSimple ConditioningSetMask ConditioningZeroOut DiffusionModelLoader DualCLIPLoader
+EmptyFlux2LatentImage EmptyHunyuanLatentVideo EmptyLatentImage EmptySD3LatentImage ExponentialScheduler FloatConstant GetNode INTConstant
+KSampler KSamplerAdvanced KSamplerSelect KarrasScheduler LTXVLoader LaplaceScheduler LoadImage LoraLoader LoraLoaderModelOnly
+PolyexponentialScheduler PreviewImage PrimitiveBoolean PrimitiveFloat PrimitiveInt PrimitiveNode PrimitiveString PrimitiveStringMultiline
+RandomNoise Reroute SDTurboScheduler SamplerCustom SamplerCustomAdvanced SamplerDPMAdaptative SamplerDPMPP_2M_SDE SamplerDPMPP_2S_Ancestral
+SamplerDPMPP_3M_SDE SamplerDPMPP_SDE SamplerER_SDE SamplerEuler SamplerEulerAncestral SamplerEulerAncestralCFGPP SamplerLMS SamplerSASolver
+SamplerSEEDS2 SaveImage SeedNode SetNode StringConstant StringConstantMultiline TripleCLIPLoader UNETLoader VAEDecode VAEEncode VAELoader
+VPScheduler ZImageLoraModelOnly ImageResizeKJ LTXVSampler LanPaint_MaskBlend WanImageToVideo""".split()
+
+
+def test_every_listed_node_type_is_registered_and_others_answer_501_with_their_id(bins):
+    r = subprocess.run([bins[1], "--node-types"], capture_output=True, text=True)
+    assert r.returncode == 0
+    types = set(json.loads(r.stdout))
+    assert len(types) >= 100, len(types)
+    missing = [t for t in REFERENCE_NODE_TYPES if t not in types]
+    assert not missing, missing
+    # the one-node LTX sampler and the explicit resize lower into flat parameters
+    wf = {"nodes": [{"id": 1, "type_id": "LTXVLoader", "fields": {"ckpt_name": "ltx-2.safetensors"}},
+                    {"id": 2, "type_id": "LTXVSampler", "fields": {"prompt": "a tide", "width": 768, "height": 512, "num_frames": 41, "frame_rate": 12, "steps": 8}}],
+          "edges": [{"from": {"node": 1, "port": "MODEL"}, "to": {"node": 2, "port": "ltxv_model"}}]}
+    r = subprocess.run([bins[1]], input=json.dumps({"workflow": wf}), capture_output=True, text=True)
+    low = json.loads(r.stdout)
+    assert r.returncode == 0, r.stdout
+    assert (low["model"], low["prompt"], low["num_frames"], low["fps"], low["steps"], low["width"]) == ("ltx-2.safetensors", "a tide", 41, 12, 8, 768)
+    wf = {"nodes": [{"id": 1, "type_id": "LoadImage", "fields": {"image": "in.png"}},
+                    {"id": 2, "type_id": "ImageResizeKJ", "fields": {"width": 640, "height": 0}}],
+          "edges": [{"from": {"node": 1, "port": "IMAGE"}, "to": {"node": 2, "port": "image"}}]}
+    r = subprocess.run([bins[1]], input=json.dumps({"model": "stub", "workflow": wf}), capture_output=True, text=True)
+    e = json.loads(r.stdout)
+    assert r.returncode == 3 and e["status"] == 501 and "keeps the source dimension" in e["error"]
+    req = {"model": "stub", "prompt": "x", "workflow": {"nodes": [{"id": 7, "type_id": "TotallyMadeUpNode", "fields": {}}], "edges": []}}
+    r = subprocess.run([bins[1]], input=json.dumps(req), capture_output=True, text=True)
+    e = json.loads(r.stdout)
+    assert r.returncode == 3 and e["status"] == 501 and e["type_id"] == "TotallyMadeUpNode" and e["node_id"] == 7
+
+
+def test_encode_phase_runs_text_encoders_in_a_child_process(bins, tmp_path):
+    """With MDB_ENCODE_SUBPROCESS=1 the ENCODE phase of the worker spawns a child that tokenises, runs the family's (tiny,
+    random-weight) encoders, writes a caption file and exits; the worker's sidecar names the child's pid."""
+    s = Server(bins, str(tmp_path / "out"), {"MDB_ARCH": "tiny", "MDB_ENCODE_SUBPROCESS": "1"})
+    try:
+        st, r = s.call("POST", "/v1/generate", {"model": "z-image-tiny", "prompt": "a red cube", "negative": "blurry", "steps": 2, "cfg": 3.0,
+                                                 "width": 64, "height": 64, "seed": 9})
+        assert st == 200, r
+        j = s.wait(r["job_id"], timeout=240)
+        assert j["state"] == "done", j
+        side = json.load(open(j["output_path"] + ".worker_result.json"))
+        assert side["text"] == "encoder-subprocess" and side["encoder_pid"] > 0
+        try:
+            os.kill(side["encoder_pid"], 0)
+            alive = True
+        except OSError:
+            alive = False
+        assert not alive                                  # the encoder process is gone: its memory went with it
+        st, r2 = s.call("POST", "/v1/generate", {"model": "z-image-tiny", "prompt": "a blue sphere", "steps": 2, "width": 64, "height": 64, "seed": 9})
+        j2 = s.wait(r2["job_id"], timeout=240)
+        a, b = load_png(j["output_path"])[0], load_png(j2["output_path"])[0]
+        assert a.shape == b.shape and (a != b).any()      # the prompt reaches the image through the encoders
     finally:
         s.close()
