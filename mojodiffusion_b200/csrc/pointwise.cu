@@ -435,6 +435,15 @@ extern "C" int mdb_randn(float* out_f32, void* out_bf16, long long n, unsigned l
 // scales [.., G] bytes; serenitymojo/ops/mxfp4.mojo:88-135). MXFP8: E4M3 elements. Quantisers choose the block exponent
 // floor(log2(absmax)) - emax of the element type (2 for E2M1, 8 for E4M3), clamp to the E8M0 range and round the scaled
 // elements to nearest-even on the element grid with saturation.
+// multiply without flush-to-zero (this file is built with fast math; the extreme block exponents of the MX formats live
+// in the subnormal range of fp32)
+__device__ __forceinline__ float mul_exact(float a, float b) {
+  float d;
+  asm("mul.rn.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+// 2^e for -126 <= e <= 127
+__device__ __forceinline__ float pow2i(int e) { return __uint_as_float(static_cast<uint32_t>(e + 127) << 23); }
 __device__ __forceinline__ float e8m0_to_float(uint32_t b) {
   // 2^(b - 127); byte 0 is 2^-127 (a subnormal float), byte 255 (NaN in the format) is not produced by the quantisers
   return b == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(b << 23);
@@ -476,7 +485,7 @@ __global__ void mxfp4_dequant_kernel(const uint4* __restrict__ blocks, const uin
     for (int q = 0; q < 4; ++q) {
       float v[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = e2m1_decode((w[q] >> (4 * j)) & 0xfu) * sc;
+      for (int j = 0; j < 8; ++j) v[j] = mul_exact(e2m1_decode((w[q] >> (4 * j)) & 0xfu), sc);
       uint4 o;
       o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]); o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
       out[q] = o;
@@ -501,17 +510,19 @@ __global__ void mx_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __
     for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
     const uint32_t eb = block_exponent_byte(amax, FP4 ? 2 : 8);
     scales[b] = static_cast<uint8_t>(eb);
-    const float inv = 1.0f / e8m0_to_float(eb);
+    // 1 / scale = 2^(127 - eb), applied as two normal powers of two so that neither factor leaves the fp32 range
+    const int ie = 127 - static_cast<int>(eb);
+    const float ia = pow2i(ie / 2), ib = pow2i(ie - ie / 2);
     if (FP4) {
       uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
-      for (int i = 0; i < 32; ++i) w[i >> 3] |= e2m1_encode(v[i] * inv) << (4 * (i & 7));
+      for (int i = 0; i < 32; ++i) w[i >> 3] |= e2m1_encode(mul_exact(mul_exact(v[i], ia), ib)) << (4 * (i & 7));
       reinterpret_cast<uint4*>(q)[b] = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
       uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        w[i >> 2] |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3)) << ((i & 3) * 8);
+        w[i >> 2] |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(mul_exact(mul_exact(v[i], ia), ib), __NV_SATFINITE, __NV_E4M3)) << ((i & 3) * 8);
       uint4* out = reinterpret_cast<uint4*>(q + b * 32);
       out[0] = make_uint4(w[0], w[1], w[2], w[3]);
       out[1] = make_uint4(w[4], w[5], w[6], w[7]);
@@ -531,7 +542,7 @@ __global__ void mxfp8_dequant_kernel(const uint4* __restrict__ q, const uint8_t*
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((w[j >> 2] >> ((j & 3) * 8)) & 0xffu), __NV_E4M3);
-        v[j] = __half2float(*reinterpret_cast<const __half*>(&hr)) * sc;
+        v[j] = mul_exact(__half2float(*reinterpret_cast<const __half*>(&hr)), sc);
       }
 #pragma unroll
       for (int k = 0; k < 2; ++k) {

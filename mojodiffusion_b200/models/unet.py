@@ -32,11 +32,26 @@ class UNetConfig:
     context_dim: int = 2048
     adm_in_channels: int = 2816
     head_dim: int = 64
+    num_heads: int = 0                       # > 0: fixed head COUNT per attention (SD1.5: 8), head_dim = channels / num_heads
+    mid_transformer_depth: int = -1          # -1: that of the deepest level
     name: str = "sdxl-unet"
 
 
 def sdxl_config() -> UNetConfig:
     return UNetConfig()
+
+
+def sd15_config() -> UNetConfig:
+    """Stable Diffusion 1.5: four levels (1, 2, 4, 4), one transformer block at the first three levels and in the middle,
+    eight heads per attention (head sizes 40 / 80 / 160), CLIP-L context, no class / size embedding
+    (serenitymojo/sampling/sd15_euler.mojo, the SD1.5 contract of serenitymojo/models/dit/sdxl_unet.mojo)."""
+    return UNetConfig(channel_mult=(1, 2, 4, 4), transformer_depth=(1, 1, 1, 0), context_dim=768, adm_in_channels=0, head_dim=0, num_heads=8,
+                      mid_transformer_depth=1, name="sd15-unet")
+
+
+def tiny_sd15_config() -> UNetConfig:
+    return UNetConfig(model_channels=64, channel_mult=(1, 2, 2), num_res_blocks=1, transformer_depth=(1, 1, 0), context_dim=48,
+                      adm_in_channels=0, head_dim=0, num_heads=4, mid_transformer_depth=1, name="tiny-sd15-unet")
 
 
 def tiny_unet_config() -> UNetConfig:
@@ -76,7 +91,9 @@ class CrossAttention(nn.Module):
         kv = packed_projection(context, (self.to_k, self.to_v))
         k = kv[..., :D].unflatten(-1, (self.heads, self.head_dim))
         v = kv[..., D:].unflatten(-1, (self.heads, self.head_dim))
-        return self.to_out[0](ops.attention(q, k, v).reshape(B, S, D), residual=residual)
+        # head sizes the tcgen05 kernel has no tile shape for (SD1.5: 40 / 80 / 160) go through the library attention
+        att = ops.attention if self.head_dim in (64, 128, 256) else ops.reference.attention
+        return self.to_out[0](att(q, k, v).reshape(B, S, D), residual=residual)
 
 
 class GEGLUFF(nn.Module):
@@ -115,6 +132,8 @@ class BasicTransformerBlock(nn.Module):
 class SpatialTransformer(nn.Module):
     def __init__(self, ch, depth, ctx_dim, head_dim, dtype, device):
         super().__init__()
+        if head_dim < 0:                         # a negative value is a head count
+            head_dim = ch // (-head_dim)
         self.norm = GroupNorm(ch, 32, 1e-6, dtype, device)
         self.proj_in = Linear(ch, ch, True, dtype, device)
         self.transformer_blocks = nn.ModuleList([BasicTransformerBlock(ch, ctx_dim, head_dim, dtype, device) for _ in range(depth)])
@@ -165,9 +184,12 @@ class UNet(nn.Module):
         self.cfg = cfg
         mc = cfg.model_channels
         ted = 4 * mc
+        hd = -cfg.num_heads if cfg.num_heads > 0 else cfg.head_dim
+        mid_depth = cfg.transformer_depth[-1] if cfg.mid_transformer_depth < 0 else cfg.mid_transformer_depth
         self.time_embed = nn.ModuleDict({"0": Linear(mc, ted, True, dtype, device), "2": Linear(ted, ted, True, dtype, device)})
-        le = nn.ModuleDict({"0": Linear(cfg.adm_in_channels, ted, True, dtype, device), "2": Linear(ted, ted, True, dtype, device)})
-        self.label_emb = nn.ModuleList([le])
+        if cfg.adm_in_channels > 0:
+            le = nn.ModuleDict({"0": Linear(cfg.adm_in_channels, ted, True, dtype, device), "2": Linear(ted, ted, True, dtype, device)})
+            self.label_emb = nn.ModuleList([le])
         self.input_blocks = nn.ModuleList([nn.ModuleList([Conv2d(cfg.in_channels, mc, 3, dtype=dtype, device=device)])])
         chans = [mc]
         ch = mc
@@ -177,14 +199,14 @@ class UNet(nn.Module):
                 layers = [ResBlock(ch, mult * mc, ted, dtype, device)]
                 ch = mult * mc
                 if cfg.transformer_depth[lvl] > 0:
-                    layers.append(SpatialTransformer(ch, cfg.transformer_depth[lvl], cfg.context_dim, cfg.head_dim, dtype, device))
+                    layers.append(SpatialTransformer(ch, cfg.transformer_depth[lvl], cfg.context_dim, hd, dtype, device))
                 self.input_blocks.append(nn.ModuleList(layers))
                 chans.append(ch)
             if lvl != nl - 1:
                 self.input_blocks.append(nn.ModuleList([Downsample(ch, dtype, device)]))
                 chans.append(ch)
         self.middle_block = nn.ModuleList([ResBlock(ch, ch, ted, dtype, device),
-                                           SpatialTransformer(ch, cfg.transformer_depth[-1], cfg.context_dim, cfg.head_dim, dtype, device),
+                                           SpatialTransformer(ch, mid_depth, cfg.context_dim, hd, dtype, device),
                                            ResBlock(ch, ch, ted, dtype, device)])
         self.output_blocks = nn.ModuleList()
         for lvl in reversed(range(nl)):
@@ -194,19 +216,20 @@ class UNet(nn.Module):
                 layers = [ResBlock(ch + ich, mult * mc, ted, dtype, device)]
                 ch = mult * mc
                 if cfg.transformer_depth[lvl] > 0:
-                    layers.append(SpatialTransformer(ch, cfg.transformer_depth[lvl], cfg.context_dim, cfg.head_dim, dtype, device))
+                    layers.append(SpatialTransformer(ch, cfg.transformer_depth[lvl], cfg.context_dim, hd, dtype, device))
                 if lvl and i == cfg.num_res_blocks:
                     layers.append(Upsample(ch, dtype, device))
                 self.output_blocks.append(nn.ModuleList(layers))
         self.out = nn.ModuleDict({"0": GroupNorm(ch, 32, 1e-5, dtype, device), "2": Conv2d(ch, cfg.out_channels, 3, dtype=dtype, device=device)})
 
-    def forward(self, x, timesteps, context, y):
+    def forward(self, x, timesteps, context, y=None):
         cfg = self.cfg
         dt = self.time_embed["0"].weight.dtype
         t_emb = timestep_embedding(timesteps, cfg.model_channels, time_factor=1.0).to(dt)
         emb = self.time_embed["2"](self.time_embed["0"](t_emb, act="silu"))
-        le = self.label_emb[0]
-        emb = emb + le["2"](le["0"](y.to(dt), act="silu"))
+        if cfg.adm_in_channels > 0:
+            le = self.label_emb[0]
+            emb = emb + le["2"](le["0"](y.to(dt), act="silu"))
         emb_silu = ops.activation(emb, "silu")
         h = x.permute(0, 2, 3, 1).to(dt).contiguous()
         context = context.to(dt)

@@ -185,6 +185,13 @@ register(ModelManifest(
     "sdxl_vae_config", "sdxl_plan", 2.6, ((1024, 1024), (832, 1216), (1216, 832))),
     "sdxl-base", "sd_xl")
 register(ModelManifest(
+    "sd15", "sdxl", _M + "unet", "UNet", "sd15_config", "tiny_sd15_config",
+    LatentSpec(4, 8, 1, False, scale=0.18215), TextSpec(77, 768, 0, ("clip_l",)),
+    ScheduleSpec("sdxl_ddpm", 30, 7.5, cfg_rule="textbook", prediction="epsilon"), LoraSpec("inject_sdxl_lora", "onetrainer"),
+    "sdxl_vae_config", "sdxl_plan", 0.86, ((512, 512), (512, 768), (768, 512)),
+    notes="the SDXL worker family with the SD1.5 UNet shape (no size / pooled conditioning)"),
+    "sd-v1-5", "v1-5", "stable-diffusion-v1-5")
+register(ModelManifest(
     "ltx2", "ltx2", _M + "video_dit", "VideoDiT", "ltx2_config", "tiny_video_dit_config",
     LatentSpec(128, 32, 1, True, temporal_factor=8), TextSpec(256, 4096, 0, ("gemma",)),
     ScheduleSpec("ltx2_linear_quadratic", 40, 3.0), LoraSpec("inject_ltx2_lora", "peft"),

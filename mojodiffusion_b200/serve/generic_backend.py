@@ -46,8 +46,8 @@ from ..utils.tracing import nvtx_range
 from .backend import GenBackend, JobParams, StepResult, UnsupportedParam, reject_unsupported_common
 from .flux_backend import prompt_embedding
 
-KINDS = ("zimage", "qwenimage", "sdxl", "ltx2", "sd3", "klein", "chroma")
-_REFUSED = {"sd15": "the SD 1.5 UNet variant is not wired"}
+KINDS = ("zimage", "qwenimage", "sdxl", "sd15", "ltx2", "sd3", "klein", "chroma")
+_REFUSED: dict = {}
 
 
 def _size_ids(values, dim: int = 256) -> torch.Tensor:
@@ -70,6 +70,9 @@ class GenericBackend(GenBackend):
         else:
             self._refusal = ""
         self.kind = self.name = kind
+        self.variant = kind
+        if kind == "sd15":                    # the SDXL loop (eps prediction over the DDPM grid) around the SD1.5 UNet shape
+            self.kind = "sdxl"
         self.tiny = os.environ.get("MDB_ARCH", "") == "tiny"
         self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
         self.dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
@@ -160,6 +163,8 @@ class GenericBackend(GenBackend):
             from ..models import chroma as M
             return M.tiny_chroma_config() if self.tiny else M.chroma_config()
         from ..models import unet as M
+        if self.variant == "sd15":
+            return M.tiny_sd15_config() if self.tiny else M.sd15_config()
         return M.tiny_unet_config() if self.tiny else M.sdxl_config()
 
     def _vae_config(self):
@@ -184,6 +189,8 @@ class GenericBackend(GenBackend):
             return (32 if self.tiny else 512), cfg.context_dim, 0
         if self.kind == "sd3":
             return (24 if self.tiny else 333), cfg.context_dim, cfg.pooled_dim
+        if cfg.adm_in_channels == 0:            # SD1.5: no pooled / size conditioning
+            return 77, cfg.context_dim, 0
         return 77, cfg.context_dim, cfg.adm_in_channels - 6 * 256 if not self.tiny else cfg.adm_in_channels
 
     # ---- phases -------------------------------------------------------------------------------------------------
@@ -311,7 +318,9 @@ class GenericBackend(GenBackend):
             from ..sampling.ddpm import SDXLEulerScheduler
             self.sched = SDXLEulerScheduler(p.steps)
             self.x = (noise * self.sched.init_noise_sigma).float().to(dev)
-            if self.tiny:
+            if self.cfg.adm_in_channels == 0:
+                self.y = self.y_neg = None
+            elif self.tiny:
                 self.y = self.pooled.to(dev, dt)
                 self.y_neg = self.pooled_neg.to(dev, dt) if self.use_cfg else None
             else:
@@ -419,7 +428,7 @@ class GenericBackend(GenBackend):
 
     def _write_sidecar(self, p: JobParams, path: str) -> None:
         peak = torch.cuda.max_memory_allocated() if self.device.type == "cuda" else 0
-        side = {"schema": f"serenity.{self.kind}.daemon_result.v1", "job_id": p.job_id, "model": p.model,
+        side = {"schema": f"serenity.{self.variant}.daemon_result.v1", "job_id": p.job_id, "model": p.model,
                 "weights": self.weights_kind, "text": self.text_kind, "encoder_pid": getattr(self, "encoder_pid", 0),
                 "cfg": p.cfg if self.use_cfg else 1.0,
                 "stage_seconds": {k: round(v, 4) for k, v in self.stage_s.items()}, "peak_device_bytes": int(peak),

@@ -409,7 +409,7 @@ def test_model_swap_restarts_worker_with_flux_kind(bins, tmp_path):
 
 @pytest.mark.parametrize("model,backend,cfg", [("z-image-tiny", "zimage", 4.0), ("qwen-image-tiny", "qwenimage", 1.0),
                                                ("sd_xl_tiny", "sdxl", 5.0), ("ltx-2-tiny", "ltx2", 3.0),
-                                               ("sd3.5_tiny", "sd3", 4.5),
+                                               ("sd3.5_tiny", "sd3", 4.5), ("sd15-tiny", "sd15", 6.0),
                                                ("flux2-klein-tiny", "klein", 4.0), ("chroma-tiny", "chroma", 4.0)])
 def test_other_families_serve_through_the_worker(bins, tmp_path, model, backend, cfg):
     """Z-Image, Qwen-Image and SDXL jobs run their own phase machines in the worker (tiny architectures, random weights),
