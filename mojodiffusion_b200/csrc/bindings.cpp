@@ -606,6 +606,38 @@ Tensor fp8_dequant(const Tensor& q, const optional<Tensor>& row_scale, double te
   return y;
 }
 
+// rows -> (E4M3 bytes [rows, K], scale chunks padded to ``pad_rows`` rows per tile row)
+std::tuple<Tensor, Tensor> mxfp8_quant_rows(const Tensor& x, int64_t pad_rows) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kBFloat16 && x.size(1) % 128 == 0,
+              "mxfp8_quant_rows: bf16 [rows, K] with contiguous K, K a multiple of 128");
+  TORCH_CHECK(pad_rows == 128 || pad_rows == 256, "mxfp8_quant_rows: pad_rows 128 (A operand) or 256 (B operand)");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0), K = x.size(1);
+  const int64_t padded = (rows + pad_rows - 1) / pad_rows * pad_rows;
+  Tensor q = at::empty({rows, K}, x.options().dtype(at::kByte));
+  Tensor sf = at::full({padded / 128, K / 128, 512}, 127, x.options().dtype(at::kByte));
+  check_rc(mdb_mxfp8_quant_rows(x.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, (int)K, x.stride(0), cur_stream()), "mxfp8_quant_rows");
+  return {q, sf};
+}
+Tensor gemm_mxfp8(const Tensor& a_q, const Tensor& sfa, const Tensor& b_q, const Tensor& sfb, const optional<Tensor>& bias) {
+  TORCH_CHECK(a_q.is_cuda() && a_q.dim() == 2 && a_q.is_contiguous() && a_q.scalar_type() == at::kByte, "gemm_mxfp8: a_q uint8 [M, K]");
+  TORCH_CHECK(b_q.is_cuda() && b_q.dim() == 2 && b_q.is_contiguous() && b_q.scalar_type() == at::kByte && b_q.size(1) == a_q.size(1) &&
+                  b_q.device() == a_q.device(), "gemm_mxfp8: b_q uint8 [N, K]");
+  const int64_t M = a_q.size(0), N = b_q.size(0), K = a_q.size(1);
+  TORCH_CHECK(K % 128 == 0 && N % 8 == 0, "gemm_mxfp8: K a multiple of 128, N a multiple of 8");
+  TORCH_CHECK(sfa.is_cuda() && sfa.is_contiguous() && sfa.scalar_type() == at::kByte && sfa.numel() == (M + 127) / 128 * (K / 128) * 512,
+              "gemm_mxfp8: sfa must hold ceil(M/128) x K/128 chunks of 512 bytes");
+  TORCH_CHECK(sfb.is_cuda() && sfb.is_contiguous() && sfb.scalar_type() == at::kByte && sfb.numel() == (N + 255) / 256 * 2 * (K / 128) * 512,
+              "gemm_mxfp8: sfb must hold 2 * ceil(N/256) x K/128 chunks of 512 bytes");
+  if (bias.has_value() && bias->defined())
+    TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == N, "gemm_mxfp8: bias bf16 [N]");
+  c10::cuda::CUDAGuard guard(a_q.device());
+  Tensor out = at::empty({M, N}, a_q.options().dtype(at::kBFloat16));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  check_rc(mdb_gemm_mxfp8(a_q.data_ptr(), sfa.data_ptr(), b_q.data_ptr(), sfb.data_ptr(), out.data_ptr(), opt_ptr(bias), (int)M, (int)N,
+                          (int)K, (int)N, status_ptr(a_q), cur_stream()), "gemm_mxfp8");
+  return out;
+}
 Tensor mx_dequant(const Tensor& q, const Tensor& scales, bool fp4) {
   TORCH_CHECK(q.is_cuda() && q.is_contiguous() && q.scalar_type() == at::kByte && scales.is_cuda() && scales.is_contiguous() &&
                   scales.scalar_type() == at::kByte && scales.device() == q.device(), "mx_dequant: uint8 device tensors");
@@ -805,7 +837,7 @@ void set_wait_limit_ns(int64_t ns) {
   TORCH_CHECK(ns > 0, "set_wait_limit_ns: positive nanoseconds");
   const unsigned long long v = static_cast<unsigned long long>(ns);
   const int rc = mdb_set_wait_limit_gemm(v) | mdb_set_wait_limit_attn_fwd(v) | mdb_set_wait_limit_attn_bwd(v) |
-                 mdb_set_wait_limit_comm(v);
+                 mdb_set_wait_limit_comm(v) | mdb_set_wait_limit_mxfp8(v);
   TORCH_CHECK(rc == 0, "set_wait_limit_ns failed: ", rc);
 }
 
@@ -843,6 +875,8 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("fp8_quant_rows", &fp8_quant_rows);
   m.def("fp8_dequant", &fp8_dequant);
   m.def("mx_dequant", &mx_dequant);
+  m.def("mxfp8_quant_rows", &mxfp8_quant_rows);
+  m.def("gemm_mxfp8", &gemm_mxfp8);
   m.def("mx_quant", &mx_quant);
   m.def("adamw_multi", &adamw_multi);
   m.def("sumsq_multi", &sumsq_multi);

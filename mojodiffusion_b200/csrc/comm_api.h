@@ -52,6 +52,7 @@ int mdb_set_wait_limit_gemm(unsigned long long ns);
 int mdb_set_wait_limit_attn_fwd(unsigned long long ns);
 int mdb_set_wait_limit_attn_bwd(unsigned long long ns);
 int mdb_set_wait_limit_comm(unsigned long long ns);
+int mdb_set_wait_limit_mxfp8(unsigned long long ns);
 
 #ifdef __cplusplus
 }

@@ -64,6 +64,11 @@ int mdb_mse_loss(const void* pred, const float* target, void* grad, float* loss_
 int mdb_randn(float* out_f32, void* out_bf16, long long n, unsigned long long seed, unsigned long long offset,
               cudaStream_t st);
 int mdb_fp8_quant_rows(const void* x, void* q, float* scale, long long rows, int D, int ldx, int ldq, cudaStream_t st);
+// MXFP8 GEMM operands: E4M3 bytes [rows, K] plus scale chunks [ceil(rows/128)][K/128][512] in the tensor core's layout
+// (byte (row % 32) * 16 + (row % 128 / 32) * 4 + k32 % 4); scale buffers are padded to whole tiles and preset to 127
+int mdb_mxfp8_quant_rows(const void* x, void* q, void* sf, long long rows, int K, long long ldx, cudaStream_t st);
+int mdb_gemm_mxfp8(const void* a_q, const void* sfa, const void* b_q, const void* sfb, void* out, const void* bias, int M, int N,
+                   int K, int ld_out, int* status, cudaStream_t st);
 // MX formats: 32-element blocks with one E8M0 scale byte; fp4 != 0: E2M1 nibbles (16 bytes per block), else E4M3 bytes
 int mdb_mx_dequant(const void* q, const void* scales, void* y, long long n_blocks, int fp4, cudaStream_t st);
 int mdb_mx_quant(const void* x, void* q, void* scales, long long n_blocks, int fp4, cudaStream_t st);

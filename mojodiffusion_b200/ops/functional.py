@@ -18,7 +18,7 @@ from .reference import act_code
 
 __all__ = [
     "linear", "linear_glu", "lora_linear", "attention", "norm_modulate", "qk_norm_rope", "rope_table", "activation",
-    "glu", "gate_residual", "cfg_euler", "flow_match", "mse_loss", "randn", "fp8_quant_rows", "fp8_dequant", "mx_quant", "mx_dequant",
+    "glu", "gate_residual", "cfg_euler", "flow_match", "mse_loss", "randn", "fp8_quant_rows", "fp8_dequant", "mx_quant", "mx_dequant", "mxfp8_quant_rows", "gemm_mxfp8", "MXFP8Weight",
     "fp8_linear", "qkv_attention", "split_cols",
 ]
 
@@ -687,6 +687,35 @@ def mx_quant(x, fp4: bool = True):
     if not native.use_native(x):
         return ref.mx_quant(x, fp4)
     return _ops().mx_quant(x.contiguous().to(torch.bfloat16), bool(fp4))
+
+
+def mxfp8_quant_rows(x, pad_rows: int = 128):
+    """bf16 [rows, K] -> (E4M3 bytes, scale chunks in the tensor core's layout). ``pad_rows`` 128 for the activation (A)
+    operand of ``gemm_mxfp8``, 256 for the weight (B) operand."""
+    if not native.use_native(x):
+        return ref.mxfp8_quant_rows(x, pad_rows)
+    return _ops().mxfp8_quant_rows(x.to(torch.bfloat16), int(pad_rows))
+
+
+def gemm_mxfp8(a_q, sfa, b_q, sfb, bias=None):
+    """[M, K] x [N, K]^T -> bf16 [M, N] with both operands in MXFP8 (hardware block scaling, fp32 accumulation)."""
+    if not native.use_native(a_q):
+        return ref.gemm_mxfp8(a_q, sfa, b_q, sfb, bias)
+    return _ops().gemm_mxfp8(a_q.contiguous(), sfa.contiguous(), b_q.contiguous(), sfb.contiguous(), bias)
+
+
+class MXFP8Weight:
+    """A linear weight [N, K] held in MXFP8 (quantised once); ``linear(x)`` quantises the activation rows on the fly."""
+
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        self.q, self.sf = mxfp8_quant_rows(weight.detach().to(torch.bfloat16).contiguous(), 256)
+        self.bias = bias.detach().to(torch.bfloat16).contiguous() if bias is not None else None
+        self.out_features, self.in_features = weight.shape
+
+    def linear(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, self.in_features).to(torch.bfloat16).contiguous()
+        aq, asf = mxfp8_quant_rows(x2, 128)
+        return gemm_mxfp8(aq, asf, self.q, self.sf, self.bias).reshape(*x.shape[:-1], self.out_features)
 
 
 def fp8_dequant(q, row_scale=None, tensor_scale: float = 1.0):

@@ -329,6 +329,41 @@ def mx_quant(x: torch.Tensor, fp4: bool = True):
     return q, e.to(torch.uint8)
 
 
+def mxfp8_quant_rows(x: torch.Tensor, pad_rows: int = 128):
+    """bf16 [rows, K] -> (E4M3 bytes [rows, K], scale chunks [ceil(rows / pad) * pad / 128, K / 128, 512]) in the layout the
+    block-scaled tensor-core instruction reads: byte (r % 32) * 16 + (r % 128 // 32) * 4 + (k32 % 4) of chunk
+    (r // 128, k32 // 4); unused bytes are 127 (scale 1)."""
+    rows, K = x.shape
+    q, e = mx_quant(x.contiguous(), fp4=False)
+    q = q.reshape(rows, K)
+    e = e.reshape(rows, K // 32)
+    padded = (rows + pad_rows - 1) // pad_rows * pad_rows
+    sf = torch.full((padded // 128, K // 128, 512), 127, dtype=torch.uint8, device=x.device)
+    r = torch.arange(rows, device=x.device)[:, None]
+    k = torch.arange(K // 32, device=x.device)[None, :]
+    sf[(r // 128).expand_as(e), (k // 4).expand_as(e), ((r % 32) * 16 + (r % 128 // 32) * 4 + (k % 4)).expand_as(e)] = e
+    return q, sf
+
+
+def mxfp8_scales_from_chunks(sf: torch.Tensor, rows: int, K: int) -> torch.Tensor:
+    """Inverse of the chunk layout: scale bytes [rows, K / 32]."""
+    r = torch.arange(rows, device=sf.device)[:, None]
+    k = torch.arange(K // 32, device=sf.device)[None, :]
+    return sf[(r // 128).expand(rows, K // 32), (k // 4).expand(rows, K // 32), ((r % 32) * 16 + (r % 128 // 32) * 4 + (k % 4)).expand(rows, K // 32)]
+
+
+def gemm_mxfp8(a_q, sfa, b_q, sfb, bias=None):
+    """fp32 product of the dequantised operands, rounded to bf16."""
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    a = mx_dequant(a_q.reshape(-1), mxfp8_scales_from_chunks(sfa, M, K).reshape(-1), fp4=False).float().reshape(M, K)
+    b = mx_dequant(b_q.reshape(-1), mxfp8_scales_from_chunks(sfb, N, K).reshape(-1), fp4=False).float().reshape(N, K)
+    y = a @ b.t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(torch.bfloat16)
+
+
 def adamw_step(p, g, m, v, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
     """torch.optim.AdamW order, fp32 math; returns new (p, m, v)."""
     g = g.float() * grad_scale

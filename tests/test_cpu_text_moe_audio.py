@@ -164,3 +164,29 @@ def test_mx_block_formats_reference():
     assert int(sz.max()) == 0 and int(z.max()) == 0
     w = O.mx_dequant(torch.randint(0, 256, (3, 5, 4, 16), dtype=torch.uint8, generator=g), torch.randint(110, 130, (3, 5, 4), dtype=torch.uint8, generator=g))
     assert w.shape == (3, 5, 128) and w.dtype == torch.bfloat16
+
+
+def test_mxfp8_operand_layout_and_reference_product():
+    """The scale chunks of the block-scaled GEMM: byte (r % 32) * 16 + (r % 128 // 32) * 4 + k32 % 4 of chunk
+    (r // 128, k32 // 4), padding bytes 127; the dequantised product stays within the format's error of the bf16 product."""
+    import torch
+    from mojodiffusion_b200 import ops as O
+    from mojodiffusion_b200.ops import reference as R
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(200, 256, generator=g).bfloat16()
+    w = (torch.randn(264, 256, generator=g) * 0.05).bfloat16()
+    xq, xs = O.mxfp8_quant_rows(x, 128)
+    wq, ws = O.mxfp8_quant_rows(w, 256)
+    assert xq.shape == (200, 256) and xs.shape == (2, 2, 512) and ws.shape == (4, 2, 512)
+    _, e = O.mx_quant(x, fp4=False)
+    e = e.reshape(200, 8)
+    r, k = 133, 5
+    assert xs[r // 128, k // 4, (r % 32) * 16 + (r % 128 // 32) * 4 + k % 4] == e[r, k]
+    assert torch.equal(R.mxfp8_scales_from_chunks(xs, 200, 256), e)
+    assert int(xs[1, 0, (200 % 32) * 16 + (200 % 128 // 32) * 4]) == 127          # rows past the end keep the neutral scale
+    y = O.gemm_mxfp8(xq, xs, wq, ws)
+    want = x.float() @ w.float().t()
+    cos = torch.nn.functional.cosine_similarity(y.float().flatten(), want.flatten(), dim=0)
+    assert y.shape == (200, 264) and float(cos) > 0.998
+    lin = O.MXFP8Weight(w, torch.zeros(264).bfloat16())
+    assert torch.equal(lin.linear(x.reshape(2, 100, 256)).reshape(200, 264), y)

@@ -221,6 +221,25 @@ def test_mx_quant_dequant_kernels_match_reference_bit_for_bit(fp4):
     assert torch.equal(torch.nan_to_num(a, posinf=9e38, neginf=-9e38), torch.nan_to_num(b, posinf=9e38, neginf=-9e38))
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 520, 384), (4608, 3072, 3072), (1000, 264, 1024), (64, 8, 256)])
+def test_gemm_mxfp8_block_scaled(M, N, K):
+    """Hardware block-scaled fp8 GEMM against the fp32 product of the dequantised operands (same quantised bytes and scale
+    bytes on both sides, so only the accumulation order differs), and the quantiser against its reference bit for bit."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x = (torch.randn(M, K, generator=g) * torch.logspace(-2, 2, M)[:, None]).to(DEV).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05 * torch.logspace(-1, 1, K)[None, :]).to(DEV).bfloat16()
+    bias = torch.randn(N, generator=g).to(DEV).bfloat16()
+    xq, xs = O.mxfp8_quant_rows(x, 128)
+    wq, ws = O.mxfp8_quant_rows(w, 256)
+    xq_r, xs_r = ref.mxfp8_quant_rows(x, 128)
+    assert torch.equal(xq, xq_r) and torch.equal(xs, xs_r)
+    y = O.gemm_mxfp8(xq, xs, wq, ws, bias)
+    want = ref.gemm_mxfp8(xq, xs, wq, ws, bias)
+    _check(y, want.float(), cos=0.99999, rel=1e-2, name=f"mxfp8 gemm {M}x{N}x{K}")
+    full = x.float() @ w.float().t() + bias.float()
+    _check(y, full, cos=0.998, rel=0.1, name="mxfp8 vs bf16 math")
+
+
 def test_attention_late_large_maximum_is_exact():
     """The exponent reference of a key tile is the row maximum of the EARLIER tiles; rows whose scores jump far above it
     (here by more than 60 nats, several such keys of different height in one tile) take the redo path."""
