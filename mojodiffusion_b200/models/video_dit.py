@@ -63,6 +63,35 @@ class FP8Linear(nn.Module):
         return y
 
 
+class MXFP8Linear(nn.Module):
+    """Linear with the weight held in MXFP8 (E4M3 + one E8M0 scale per 32 input features); activations are quantised the
+    same way per call and the tensor core applies both block scales (``ops.gemm_mxfp8``). Activation, residual and gate
+    run as the usual separate kernels after the GEMM."""
+
+    def __init__(self, lin: Linear):
+        super().__init__()
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+        w = ops.MXFP8Weight(lin.weight.detach(), lin.bias.detach() if lin.bias is not None else None)
+        self.register_buffer("weight", w.q)
+        self.register_buffer("weight_scale", w.sf)
+        self.bias = lin.bias
+        self.slots = nn.ModuleList()
+
+    def forward(self, x, act=None, residual=None, gate=None, rows_per_group: int = 1, out=None):
+        x2 = x.reshape(-1, self.in_features).to(torch.bfloat16).contiguous()
+        aq, asf = ops.mxfp8_quant_rows(x2, 128)
+        b = self.bias.to(torch.bfloat16) if self.bias is not None else None
+        y = ops.gemm_mxfp8(aq, asf, self.weight, self.weight_scale, b).reshape(*x.shape[:-1], self.out_features).to(x.dtype)
+        if act:
+            y = ops.activation(y, act)
+        if residual is not None:
+            y = ops.gate_residual(residual, y, gate, rows_per_group)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+
 class VideoAttention(nn.Module):
     def __init__(self, cfg: VideoDiTConfig, cross: bool, dtype, device):
         super().__init__()
@@ -170,16 +199,19 @@ class VideoDiT(nn.Module):
         x = torch.arange(w, device=device, dtype=torch.float32)[None, None, :].expand(frames, h, w)
         return torch.stack((t, y, x), -1).reshape(-1, 3)
 
-    def to_fp8(self, first: int = 0, last: Optional[int] = None) -> "VideoDiT":
-        """Replace the big linears of blocks [first, last) by fp8-resident weights (the reference serves blocks 4-46 so)."""
+    def to_fp8(self, first: int = 0, last: Optional[int] = None, block_scaled: bool = False) -> "VideoDiT":
+        """Replace the big linears of blocks [first, last) by fp8-resident weights (the reference serves blocks 4-46 so).
+        ``block_scaled``: MXFP8 (one scale per 32 input features, applied by the tensor core) instead of one scale per
+        output channel."""
+        FP8 = MXFP8Linear if block_scaled else FP8Linear
         last = len(self.transformer_blocks) if last is None else last
         for blk in self.transformer_blocks[first:last]:
             for att in (blk.attn1, blk.attn2):
                 for n in ("to_q", "to_k", "to_v"):
-                    setattr(att, n, FP8Linear(getattr(att, n)))
-                att.to_out[0] = FP8Linear(att.to_out[0])
-            blk.ff.net["0"].proj = FP8Linear(blk.ff.net["0"].proj)
-            blk.ff.net["2"] = FP8Linear(blk.ff.net["2"])
+                    setattr(att, n, FP8(getattr(att, n)))
+                att.to_out[0] = FP8(att.to_out[0])
+            blk.ff.net["0"].proj = FP8(blk.ff.net["0"].proj)
+            blk.ff.net["2"] = FP8(blk.ff.net["2"])
         return self
 
     def forward(self, x, context, t, grid: Tuple[int, int, int], ctx_len: Optional[torch.Tensor] = None):

@@ -125,8 +125,11 @@ def test_video_dit_bf16_and_fp8():
         ref = m(*[t.to(DEV) for t in inputs], grid=(2, 4, 8))
         q = copy.deepcopy(m).to_fp8()
         out = q(*[t.to(DEV) for t in inputs], grid=(2, 4, 8))
+        qb = copy.deepcopy(m).to_fp8(block_scaled=True)              # MXFP8 weights and activations, hardware block scaling
+        out_b = qb(*[t.to(DEV) for t in inputs], grid=(2, 4, 8))
     native.check_status(out)
     assert _cos(out, ref) > 0.99
+    assert _cos(out_b, ref) > 0.99 and type(qb.transformer_blocks[0].ff.net["2"]).__name__ == "MXFP8Linear"
 
 
 def test_unet_and_vae():
