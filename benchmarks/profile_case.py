@@ -15,12 +15,65 @@ import mojodiffusion_b200.ops as O  # noqa: E402
 from mojodiffusion_b200.ops import native  # noqa: E402
 
 
+def summarize(path, first_marker, last_marker):
+    """Device time per kernel group of one step out of an ncu launch list (serialised, cold-cache times: compare shares)."""
+    import collections
+    import csv
+    import re
+    rows = list(csv.reader(open(path, errors="ignore")))
+    hdr_i = next(i for i, r in enumerate(rows) if "Kernel Name" in r)
+    hdr = rows[hdr_i]
+    ki, mi, ui = hdr.index("Kernel Name"), hdr.index("Metric Value"), hdr.index("Metric Unit")
+    data = []
+    for r in rows[hdr_i + 1:]:
+        if len(r) <= mi:
+            continue
+        v = float(r[mi].replace(",", ""))
+        v = v / 1000 if r[ui] == "ns" else v * 1000 if r[ui] == "ms" else v
+        data.append((re.sub(r"\(.*", "", r[ki])[:110], v))
+    firsts = [i for i, (k, _) in enumerate(data) if first_marker in k]
+    lasts = [i for i, (k, _) in enumerate(data) if last_marker in k]
+    if not firsts or not lasts or lasts[-1] < firsts[-1] and len(firsts) < 2:
+        print(f"markers not found ({len(firsts)} x {first_marker}, {len(lasts)} x {last_marker}); capture more launches")
+        return 1
+    end = lasts[-1]
+    begin = max(i for i in firsts if i < end)
+    step = data[begin:end + 1]
+    tot = sum(v for _, v in step)
+    groups = collections.OrderedDict((g, [0, 0.0]) for g in ("base GEMMs, CTA-pair 256x256 tiles", "GEMMs, one-CTA 128-wide tiles",
+                                                              "skinny (LoRA) GEMMs, 64-wide tiles", "attention backward", "attention forward",
+                                                              "own norm / rope / pointwise / optimizer kernels", "torch copy / cat / fill / elementwise"))
+    agg = collections.defaultdict(lambda: [0, 0.0])
+    for k, v in step:
+        agg[k][0] += 1
+        agg[k][1] += v
+        g = ("base GEMMs, CTA-pair 256x256 tiles" if "pair_kernel" in k else "skinny (LoRA) GEMMs, 64-wide tiles" if "gemm_tcgen05_kernel<64" in k
+             else "GEMMs, one-CTA 128-wide tiles" if "gemm_tcgen05_kernel" in k else "attention backward" if ("attention_bwd" in k or "attn_delta" in k)
+             else "attention forward" if "attention_fwd" in k else "own norm / rope / pointwise / optimizer kernels" if "mdb::" in k
+             else "torch copy / cat / fill / elementwise")
+        groups[g][0] += 1
+        groups[g][1] += v
+    print(f"one step = launches {begin}..{end}: {len(step)} launches, {tot / 1000:.1f} ms of device time (serialised)")
+    for g, (n, v) in groups.items():
+        print(f"  {v / 1000:8.2f} ms {100 * v / tot:5.1f} %  n={n:5d}  {g}")
+    print("  top kernels:")
+    for k, (n, v) in sorted(agg.items(), key=lambda t: -t[1][1])[:16]:
+        print(f"  {v / 1000:8.2f} ms {100 * v / tot:5.1f} %  n={n:5d}  {k}")
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "gemm_trace", "attention_trace", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
     ap.add_argument("--shape", default="")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--summarize", default="", help="no GPU work: read an `ncu --metrics gpu__time_duration.sum --csv` launch list and "
+                    "print time per kernel group and per kernel, for the launches between --first-marker and --last-marker")
+    ap.add_argument("--first-marker", default="flow_match_kernel")
+    ap.add_argument("--last-marker", default="adamw")
     a = ap.parse_args()
+    if a.summarize:
+        return summarize(a.summarize, a.first_marker, a.last_marker)
     dev = "cuda"
     native.load(True)
     dims = [int(x) for x in a.shape.split(",")] if a.shape else []

@@ -248,6 +248,29 @@ Tensor group_norm_nhwc(const Tensor& x, const optional<Tensor>& w, const optiona
            "group_norm");
   return y;
 }
+// -> {dx, dw (fp32 [C] or empty), db}
+std::tuple<Tensor, Tensor, Tensor> group_norm_nhwc_bwd(const Tensor& x, const Tensor& dy, const optional<Tensor>& w, const optional<Tensor>& b,
+                                                       int64_t groups, double eps, int64_t act, bool need_wgrad) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "group_norm_nhwc_bwd: x");
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && dy.scalar_type() == at::kBFloat16 && dy.sizes() == x.sizes() && dy.device() == x.device(),
+              "group_norm_nhwc_bwd: dy must match x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t C = x.size(3);
+  Tensor dx = at::empty_like(x);
+  Tensor scratch = at::empty({x.size(0) * groups, 4}, x.options().dtype(at::kFloat));
+  Tensor dw, db;
+  if (need_wgrad) {
+    dw = at::zeros({C}, x.options().dtype(at::kFloat));
+    db = at::zeros({C}, x.options().dtype(at::kFloat));
+  }
+  float* st = scratch.data_ptr<float>();
+  g_launches.fetch_add(3, std::memory_order_relaxed);
+  check_rc(mdb_group_norm_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), st, st + 2 * x.size(0) * groups, opt_ptr(w), opt_ptr(b),
+                              need_wgrad ? dw.data_ptr<float>() : nullptr, need_wgrad ? db.data_ptr<float>() : nullptr, (int)x.size(0),
+                              (int)(x.size(1) * x.size(2)), (int)C, (int)groups, (float)eps, (int)act, cur_stream()),
+           "group_norm_bwd");
+  return {dx, need_wgrad ? dw : Tensor(), need_wgrad ? db : Tensor()};
+}
 Tensor image_filter(int64_t op, const Tensor& img, const std::vector<double>& params, const optional<Tensor>& aux) {
   TORCH_CHECK(img.is_cuda() && img.dim() == 3 && img.size(2) == 4 && img.is_contiguous() && img.scalar_type() == at::kFloat,
               "image_filter: fp32 contiguous [H, W, 4] expected");
@@ -853,6 +876,7 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("gemm", &gemm);
   m.def("conv2d_nhwc", &conv2d_nhwc);
   m.def("group_norm_nhwc", &group_norm_nhwc);
+  m.def("group_norm_nhwc_bwd", &group_norm_nhwc_bwd);
   m.def("image_filter", &image_filter);
   m.def("upsample2x_nhwc", &upsample2x_nhwc);
   m.def("avgpool2x_nhwc", &avgpool2x_nhwc);

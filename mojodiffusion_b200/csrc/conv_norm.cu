@@ -101,6 +101,89 @@ __global__ void group_norm_apply_kernel(const __nv_bfloat16* __restrict__ x, __n
   }
 }
 
+// ---- GroupNorm backward -------------------------------------------------------------------------------------------------
+// With xh = (x - mean) * rstd, z = xh * w + b, y = act(z) and g = dy * act'(z) * w:
+//   dx = rstd * (g - mean_group(g) - xh * mean_group(g * xh)),   dw[c] = sum dy act'(z) xh,   db[c] = sum dy act'(z)
+// (serenitymojo/ops/norm_backward.mojo:951,1080). Pass 1 (one block per sample and group) forms the two group means and,
+// when asked, adds the per-channel sums into fp32 dw / db; pass 2 is elementwise.
+__device__ __forceinline__ float gn_dact(float z, int act) {
+  if (act != 2) return 1.f;
+  const float sg = 1.f / (1.f + __expf(-z));
+  return sg * (1.f + z * (1.f - sg));
+}
+__global__ void __launch_bounds__(256)
+group_norm_bwd_sums_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ stats,
+                           const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b, float* __restrict__ sums,
+                           float* __restrict__ dw, float* __restrict__ db, int HW, int C, int G, int act) {
+  const int n = blockIdx.x / G, g = blockIdx.x % G;
+  const int cpg = C / G;
+  const size_t base = static_cast<size_t>(n) * HW * C + g * cpg;
+  const float mean = stats[2 * blockIdx.x], rstd = stats[2 * blockIdx.x + 1];
+  float s1 = 0.f, s2 = 0.f;
+  // each thread keeps to one channel of the group while it walks the pixels, so its dw / db partials are per channel;
+  // blockDim / cpg pixel lanes per channel, the threads beyond lanes * cpg idle
+  const int lanes = blockDim.x / cpg;
+  if (static_cast<int>(threadIdx.x) < lanes * cpg) {
+    const int c = threadIdx.x % cpg, pl = threadIdx.x / cpg;
+    const float wc = w ? __bfloat162float(w[g * cpg + c]) : 1.f, bc = b ? __bfloat162float(b[g * cpg + c]) : 0.f;
+    float a1 = 0.f, a2 = 0.f;
+    for (int p = pl; p < HW; p += lanes) {
+      const size_t off = base + static_cast<size_t>(p) * C + c;
+      const float xh = (__bfloat162float(x[off]) - mean) * rstd;
+      const float dz = __bfloat162float(dy[off]) * gn_dact(xh * wc + bc, act);
+      a1 += dz;
+      a2 += dz * xh;
+    }
+    if (dw) atomicAdd(&dw[g * cpg + c], a2);
+    if (db) atomicAdd(&db[g * cpg + c], a1);
+    s1 = a1 * wc;
+    s2 = a2 * wc;
+  }
+  __shared__ float r1[8], r2[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  if ((threadIdx.x & 31) == 0) { r1[threadIdx.x >> 5] = s1; r2[threadIdx.x >> 5] = s2; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, c2 = 0.f;
+    for (int i = 0; i < 8; ++i) { a += r1[i]; c2 += r2[i]; }
+    const float cnt = static_cast<float>(HW) * cpg;
+    sums[2 * blockIdx.x] = a / cnt;
+    sums[2 * blockIdx.x + 1] = c2 / cnt;
+  }
+}
+__global__ void group_norm_bwd_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                            __nv_bfloat16* __restrict__ dx, const float* __restrict__ stats, const float* __restrict__ sums,
+                                            const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b, long long total_vec,
+                                            int HW, int C, int G, int act) {
+  const int cv = C >> 3, cpg = C / G;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_vec; i += (long long)gridDim.x * blockDim.x) {
+    const int c0 = static_cast<int>(i % cv) * 8;
+    const int n = static_cast<int>((i / cv) / HW);
+    const uint4 ux = *reinterpret_cast<const uint4*>(x + i * 8), ud = *reinterpret_cast<const uint4*>(dy + i * 8);
+    const uint32_t x4[4] = {ux.x, ux.y, ux.z, ux.w}, d4[4] = {ud.x, ud.y, ud.z, ud.w};
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float2 fx = unpack_bf16x2(x4[k >> 1]), fd = unpack_bf16x2(d4[k >> 1]);
+      const float xv = (k & 1) ? fx.y : fx.x, dv = (k & 1) ? fd.y : fd.x;
+      const int c = c0 + k, g = c / cpg;
+      const float mean = stats[2 * (n * G + g)], rstd = stats[2 * (n * G + g) + 1];
+      const float m1 = sums[2 * (n * G + g)], m2 = sums[2 * (n * G + g) + 1];
+      const float wc = w ? __bfloat162float(w[c]) : 1.f, bc = b ? __bfloat162float(b[c]) : 0.f;
+      const float xh = (xv - mean) * rstd;
+      const float gg = dv * gn_dact(xh * wc + bc, act) * wc;
+      v[k] = rstd * (gg - m1 - xh * m2);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]); o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(dx + i * 8) = o;
+  }
+}
+
 // nearest-neighbour 2x upsample, NHWC
 __global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int N, int H, int W, int cv) {
   const long long total = static_cast<long long>(N) * H * 2 * W * 2 * cv;
@@ -145,6 +228,19 @@ static inline int grid_for(long long n, int threads) {
 using namespace mdb;
 typedef __nv_bfloat16 bf16;
 
+// stats: [N * G, 2] scratch (mean, rstd), sums: [N * G, 2] scratch; dw / db: fp32 [C] accumulators (zeroed by the caller) or null
+extern "C" int mdb_group_norm_bwd(const void* x, const void* dy, void* dx, float* stats, float* sums, const void* w, const void* b,
+                                  float* dw, float* db, int N, int HW, int C, int G, float eps, int act, cudaStream_t st) {
+  if (C % G || C % 8 || (act != 0 && act != 2) || (C / G) > 256) return -1;
+  if (N == 0) return 0;
+  group_norm_stats_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, stats, HW, C, G, eps);
+  group_norm_bwd_sums_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, stats, (const bf16*)w, (const bf16*)b, sums, dw, db,
+                                                    HW, C, G, act);
+  const long long tv = static_cast<long long>(N) * HW * (C / 8);
+  group_norm_bwd_apply_kernel<<<grid_for(tv, 256), 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (bf16*)dx, stats, sums, (const bf16*)w,
+                                                                 (const bf16*)b, tv, HW, C, G, act);
+  return (int)cudaGetLastError();
+}
 extern "C" int mdb_group_norm(const void* x, void* y, float* stats, const void* w, const void* b, int N, int HW, int C,
                               int G, float eps, int act, cudaStream_t st) {
   if (C % 8 || C % G) return -1;

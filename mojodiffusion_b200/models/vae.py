@@ -132,6 +132,10 @@ class Downsample(nn.Module):
         self.conv = Conv2d(ch, ch, 3, stride=2, padding=0, dtype=dtype, device=device)
 
     def forward(self, x):
+        from ..ops import native
+        if native.use_native(x) and x.dtype == torch.bfloat16 and x.shape[1] % 2 == 0 and x.shape[2] % 2 == 0:
+            # far-side padded stride-2 convolution = the "same" convolution sampled at the odd positions (native kernel)
+            return C.conv2d_nhwc(x, self.conv.ohwi(), self.conv.bias, 2, 1, offset=1)
         x = torch.nn.functional.pad(x, (0, 0, 0, 1, 0, 1))          # NHWC: pad W and H on the far side
         return self.conv(x)
 

@@ -28,23 +28,149 @@ def conv2d_nhwc_reference(x, w_ohwi, bias=None, stride: int = 1, padding=1, act=
     return y.to(x.dtype)
 
 
-def conv2d_nhwc(x, w_ohwi, bias=None, stride: int = 1, padding=1, act=None, residual=None):
+def _native_conv_ok(x, w_ohwi, pad) -> bool:
+    KH, KW = w_ohwi.shape[1], w_ohwi.shape[2]
+    return native.use_native(x) and x.dtype == torch.bfloat16 and 2 * pad[0] == KH - 1 and 2 * pad[1] == KW - 1
+
+
+def _pad_channels(t, mult: int, dim: int = -1):
+    c = t.shape[dim]
+    extra = (-c) % mult
+    if extra == 0:
+        return t
+    shape = list(t.shape)
+    shape[dim] = extra
+    return torch.cat((t, t.new_zeros(shape)), dim=dim)
+
+
+def _conv_same_native(x, w_ohwi, bias, pad, act=None, residual=None):
+    """Stride-1 "same" convolution on the implicit-GEMM kernel for ANY channel counts: input channels are zero-padded to a
+    multiple of 64 (the 3- / 4-channel stems), output channels to a multiple of 8 (the 3- / 4-channel heads)."""
+    Cout, Cin = w_ohwi.shape[0], w_ohwi.shape[3]
+    xp, wp = _pad_channels(x, 64), _pad_channels(w_ohwi, 64)
+    if Cout % 8:
+        wp = _pad_channels(wp, 8, 0)
+        bias = _pad_channels(bias, 8, 0) if bias is not None else None
+        residual = _pad_channels(residual, 8) if residual is not None else None
+    y = native.ops().conv2d_nhwc(xp.contiguous(), wp.contiguous(), bias, pad[0], pad[1], act_code(act),
+                                 residual.contiguous() if residual is not None else None)
+    return y[..., :Cout] if Cout % 8 else y
+
+
+def _rotated(w_ohwi):
+    """Weights of the input-gradient convolution: spatially flipped, input / output channels exchanged ([Cin, KH, KW, Cout])."""
+    return w_ohwi.flip(1, 2).permute(3, 1, 2, 0).contiguous()
+
+
+def conv2d_weight_grad(x, dy, KH: int, KW: int, pad):
+    """dW [Cout, KH, KW, Cin] of a stride-1 "same" convolution as KH * KW GEMMs over the pixels. Both tensors are
+    zero-padded by the kernel radius and flattened to [pixels', C]; a tap is then a constant offset between the two
+    flat index spaces (the zero border makes every wrap-around term vanish), so each tap is one MN-major GEMM on two
+    contiguous slices, fp32 accumulation (serenitymojo/ops/conv2d_backward.mojo:73-182)."""
+    from .functional import _gemm
+    N, H, W, Cin = x.shape
+    Cout = dy.shape[-1]
+    ph, pw = pad
+    Wp = W + 2 * pw
+    xp = torch.nn.functional.pad(x, (0, 0, pw, pw, ph, ph)).reshape(-1, Cin)
+    dyp = torch.nn.functional.pad(dy, (0, 0, pw, pw, ph, ph)).reshape(-1, Cout)
+    P = xp.shape[0]
+    dw = torch.empty(Cout, KH, KW, Cin, dtype=torch.float32, device=x.device)
+    for kh in range(KH):
+        for kw in range(KW):
+            off = (kh - ph) * Wp + (kw - pw)                       # x index = dy index + off
+            a = dyp[max(0, -off):P - max(0, off)]
+            b = xp[max(0, off):P - max(0, -off)]
+            if native.use_native(x) and x.dtype == torch.bfloat16 and Cin % 8 == 0 and Cout % 8 == 0:
+                dw[:, kh, kw] = _gemm([a], [b], a_mn=True, b_mn=True, out_fp32=True)
+            else:
+                dw[:, kh, kw] = a.float().t() @ b.float()
+    return dw
+
+
+class _Conv2dFn(torch.autograd.Function):
+    """Convolution with native forward and native input gradient (the same kernel on the rotated weights; a stride-2
+    layer is the stride-1 result sampled at every second position, its gradient scattered back before the rotation).
+    Weight and bias gradients are computed only when asked for."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, stride, pad, offset):
+        y = _conv_same_native(x, w, bias, pad)
+        if stride > 1:
+            y = y[:, offset::stride, offset::stride].contiguous()
+        ctx.save_for_backward(x, w)
+        ctx.meta = (stride, pad, offset, bias is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        stride, pad, offset, has_bias = ctx.meta
+        dy = dy.contiguous()
+        if stride > 1:
+            full = dy.new_zeros(x.shape[0], x.shape[1], x.shape[2], dy.shape[-1])
+            full[:, offset::stride, offset::stride] = dy
+            dy = full
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = _conv_same_native(dy, _rotated(w), None, pad).to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            dw = conv2d_weight_grad(x, dy, w.shape[1], w.shape[2], pad).to(w.dtype)
+        if has_bias and ctx.needs_input_grad[2]:
+            db = dy.float().sum(dim=(0, 1, 2)).to(w.dtype)
+        return dx, dw, db, None, None, None
+
+
+def conv2d_nhwc(x, w_ohwi, bias=None, stride: int = 1, padding=1, act=None, residual=None, offset: int = 0):
+    """``stride`` 2 samples the stride-1 "same" result at ``offset::2`` (offset 0: symmetric padding as in the UNet
+    down-samplers; offset 1: the right / bottom padded stride-2 convolution of the LDM encoders)."""
     pad = (padding, padding) if isinstance(padding, int) else tuple(padding)
     KH, KW, Cin = w_ohwi.shape[1], w_ohwi.shape[2], w_ohwi.shape[3]
-    fast = (native.use_native(x) and not torch.is_grad_enabled() and x.dtype == torch.bfloat16 and stride == 1
-            and Cin % 64 == 0 and w_ohwi.shape[0] % 8 == 0 and 2 * pad[0] == KH - 1 and 2 * pad[1] == KW - 1)
-    if fast:
-        res = residual.contiguous() if residual is not None else None
-        return native.ops().conv2d_nhwc(x.contiguous(), w_ohwi.contiguous(), bias, pad[0], pad[1], act_code(act), res)
+    ok = _native_conv_ok(x, w_ohwi, pad)
+    if ok and torch.is_grad_enabled() and (x.requires_grad or w_ohwi.requires_grad or (bias is not None and bias.requires_grad)):
+        y = _Conv2dFn.apply(x, w_ohwi, bias, stride, pad, offset)
+        if act is not None:
+            from . import functional as Fn
+            y = Fn.activation(y, act)
+        return y + residual if residual is not None else y
+    if ok and stride == 1:
+        if Cin % 64 == 0 and w_ohwi.shape[0] % 8 == 0:
+            res = residual.contiguous() if residual is not None else None
+            return native.ops().conv2d_nhwc(x.contiguous(), w_ohwi.contiguous(), bias, pad[0], pad[1], act_code(act), res)
+        return _conv_same_native(x, w_ohwi, bias, pad, act, residual)
+    if ok and stride == 2:
+        y = _conv_same_native(x, w_ohwi, bias, pad, act)[:, offset::2, offset::2].contiguous()
+        return y + residual if residual is not None else y
+    if offset:
+        raise NotImplementedError("offset sampling is defined for the native path")
     return conv2d_nhwc_reference(x, w_ohwi, bias, stride, pad, act, residual)
+
+
+class _GroupNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, groups, eps, act):
+        ctx.save_for_backward(x, weight, bias)
+        ctx.meta = (groups, eps, act)
+        return native.ops().group_norm_nhwc(x.contiguous(), weight, bias, groups, eps, act)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, bias = ctx.saved_tensors
+        groups, eps, act = ctx.meta
+        need_w = weight is not None and (ctx.needs_input_grad[1] or ctx.needs_input_grad[2])
+        dx, dw, db = native.ops().group_norm_nhwc_bwd(x.contiguous(), dy.contiguous(), weight, bias, groups, eps, act, bool(need_w))
+        return (dx if ctx.needs_input_grad[0] else None, dw.to(weight.dtype) if need_w and ctx.needs_input_grad[1] else None,
+                db.to(weight.dtype) if need_w and bias is not None and ctx.needs_input_grad[2] else None, None, None, None)
 
 
 def group_norm_nhwc(x, weight=None, bias=None, groups: int = 32, eps: float = 1e-6, act=None):
     """GroupNorm over (H, W, C/G) per sample and group on an NHWC tensor, optional fused SiLU."""
     a = act_code(act)
-    if native.use_native(x) and not torch.is_grad_enabled() and x.dtype == torch.bfloat16 and a in (0, 2) \
-            and x.shape[-1] % 8 == 0:
-        return native.ops().group_norm_nhwc(x.contiguous(), weight, bias, groups, eps, a)
+    if native.use_native(x) and x.dtype == torch.bfloat16 and a in (0, 2) and x.shape[-1] % 8 == 0:
+        if torch.is_grad_enabled() and (x.requires_grad or (weight is not None and weight.requires_grad)):
+            return _GroupNormFn.apply(x, weight, bias, groups, eps, a)
+        if not torch.is_grad_enabled():
+            return native.ops().group_norm_nhwc(x.contiguous(), weight, bias, groups, eps, a)
     N, H, W, C = x.shape
     xf = x.float().reshape(N, H * W, groups, C // groups)
     mu = xf.mean(dim=(1, 3), keepdim=True)

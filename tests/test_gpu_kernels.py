@@ -602,3 +602,81 @@ def test_attention_writes_exactly_its_output_region():
     want = ref.attention(q, k, v, 1 / math.sqrt(Dh))
     _check(out, want, cos=0.999, name="poison attention")
     assert torch.isnan(buf[:, :3]).all() and torch.isnan(buf[:, 3 + Sq:]).all()
+
+
+# ---- convolution / GroupNorm in training -------------------------------------------------------------------------------
+@pytest.mark.parametrize("Cin,Cout,K,stride,offset", [(64, 128, 3, 1, 0), (4, 320, 3, 1, 0), (128, 3, 3, 1, 0), (320, 320, 3, 2, 0),
+                                                      (128, 128, 3, 2, 1), (192, 64, 1, 1, 0)])
+def test_conv2d_forward_and_gradients_native(Cin, Cout, K, stride, offset):
+    """Any channel count and the two stride-2 forms on the implicit-GEMM kernel; input, weight and bias gradients against
+    fp32 autograd of torch's convolution."""
+    from mojodiffusion_b200.ops import conv as C
+    g = torch.Generator().manual_seed(Cin + Cout)
+    N, H, W = 2, 24, 20
+    x = torch.randn(N, H, W, Cin, generator=g).to(DEV).bfloat16().requires_grad_(True)
+    w = (torch.randn(Cout, K, K, Cin, generator=g) * (1.0 / math.sqrt(K * K * Cin))).to(DEV).bfloat16().requires_grad_(True)
+    b = torch.randn(Cout, generator=g).to(DEV).bfloat16().requires_grad_(True)
+    pad = K // 2
+    y = C.conv2d_nhwc(x, w, b, stride, pad, offset=offset)
+    xr, wr, br = [t.detach().float().requires_grad_(True) for t in (x, w, b)]
+    xin = xr.permute(0, 3, 1, 2)
+    if stride == 2 and offset == 1:
+        yr = torch.nn.functional.conv2d(torch.nn.functional.pad(xin, (0, 1, 0, 1)), wr.permute(0, 3, 1, 2), br, stride=2, padding=0)
+    else:
+        yr = torch.nn.functional.conv2d(xin, wr.permute(0, 3, 1, 2), br, stride=stride, padding=pad)
+    yr = yr.permute(0, 2, 3, 1)
+    assert y.shape == yr.shape
+    _check(y, yr, cos=0.9995, rel=3e-2, name="conv fwd")
+    dy = torch.randn(y.shape, generator=g).to(DEV)
+    y.backward(dy.bfloat16())
+    yr.backward(dy.bfloat16().float())
+    _check(x.grad, xr.grad, cos=0.999, rel=4e-2, name="conv dx")
+    _check(w.grad, wr.grad, cos=0.999, rel=4e-2, name="conv dw")
+    _check(b.grad, br.grad, cos=0.999, rel=4e-2, name="conv db")
+    with torch.no_grad():
+        _check(C.conv2d_nhwc(x.detach(), w.detach(), b.detach(), stride, pad, offset=offset), yr.detach(), cos=0.9995, rel=3e-2, name="conv inference")
+
+
+@pytest.mark.parametrize("C_,G,act", [(320, 32, "silu"), (128, 32, None), (64, 8, "silu")])
+def test_group_norm_backward_kernel(C_, G, act):
+    from mojodiffusion_b200.ops import conv as C
+    g = torch.Generator().manual_seed(C_)
+    x = (torch.randn(2, 12, 10, C_, generator=g) * 2 + 0.5).to(DEV).bfloat16().requires_grad_(True)
+    w = (1 + 0.2 * torch.randn(C_, generator=g)).to(DEV).bfloat16().requires_grad_(True)
+    b = (0.2 * torch.randn(C_, generator=g)).to(DEV).bfloat16().requires_grad_(True)
+    y = C.group_norm_nhwc(x, w, b, G, 1e-5, act)
+    xr, wr, br = [t.detach().float().requires_grad_(True) for t in (x, w, b)]
+    yr = torch.nn.functional.group_norm(xr.permute(0, 3, 1, 2), G, wr, br, 1e-5)
+    yr = (torch.nn.functional.silu(yr) if act else yr).permute(0, 2, 3, 1)
+    _check(y, yr, cos=0.9995, rel=3e-2, name="gn fwd")
+    dy = torch.randn(y.shape, generator=g).to(DEV).bfloat16()
+    y.backward(dy)
+    yr.backward(dy.float())
+    _check(x.grad, xr.grad, cos=0.999, rel=4e-2, name="gn dx")
+    _check(w.grad, wr.grad, cos=0.999, rel=4e-2, name="gn dw")
+    _check(b.grad, br.grad, cos=0.999, rel=4e-2, name="gn db")
+
+
+def test_unet_lora_step_runs_without_library_convolutions(monkeypatch):
+    """A LoRA step of the (tiny) UNet: every convolution and GroupNorm, forward and backward, is one of this package's
+    kernels; torch's convolution is never entered."""
+    from mojodiffusion_b200.models.unet import UNet, tiny_unet_config
+    from mojodiffusion_b200.training import lora as L
+    calls = {"n": 0}
+    orig = torch.nn.functional.conv2d
+
+    def spy(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+    m = UNet(tiny_unet_config(), torch.bfloat16, DEV).init_weights(0)
+    slots = L.inject_sdxl_lora(m, rank=4, alpha=4.0)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(2, 4, 16, 16, generator=g).to(DEV)
+    ctx = torch.randn(2, 7, 64, generator=g).to(DEV)
+    y = torch.randn(2, 96, generator=g).to(DEV)
+    monkeypatch.setattr(torch.nn.functional, "conv2d", spy)
+    out = m(x, torch.tensor([10.0, 500.0], device=DEV), ctx, y)
+    out.float().square().mean().backward()
+    native.check_status(out)
+    assert calls["n"] == 0
+    assert all(s.up.grad is not None for s in slots) and any(float(s.down.grad.abs().sum()) > 0 or float(s.up.grad.abs().sum()) > 0 for s in slots)
