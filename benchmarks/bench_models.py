@@ -6,7 +6,7 @@ device-timed with CUDA events after warm-up; every step streams far more weight 
 the reference's per-model sampler smokes and trainer step reports (serenitymojo/docs/MODEL_RENDER_CAMPAIGN_2026-06-15.md,
 BEAT_FLAME_SCOREBOARD_2026-06-10.md), which time the same loops on its hardware.
 
-    python benchmarks/bench_models.py [--only ltx2,ltx2_fp8,qwen,zimage,zimage_train,klein,klein_train,sdxl,vae] [--tiny] [--json out.json]
+    python benchmarks/bench_models.py [--only ltx2,ltx2_fp8,ltx2_mxfp8,ltx2_vae,qwen,zimage,zimage_train,klein,klein_train,sdxl,sdxl_train,vae] [--tiny] [--json out.json]
 """
 import argparse
 import json
@@ -38,7 +38,7 @@ def nparams(m):
     return sum(p.numel() for p in m.parameters()) + sum(b.numel() for b in m.buffers())
 
 
-def bench_ltx2(dev, tiny, steps, warmup, fp8):
+def bench_ltx2(dev, tiny, steps, warmup, fp8, block_scaled=False):
     """LTX-2-shaped 48-layer video DiT, 6144 latent tokens (8 frames x 24 x 32), 256 context tokens, Euler update."""
     from mojodiffusion_b200.models.video_dit import VideoDiT, ltx2_config, tiny_video_dit_config
     cfg = tiny_video_dit_config() if tiny else ltx2_config()
@@ -46,7 +46,7 @@ def bench_ltx2(dev, tiny, steps, warmup, fp8):
     S = grid[0] * grid[1] * grid[2]
     m = VideoDiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
     if fp8:
-        m.to_fp8(0 if tiny else 4, None if tiny else 46)
+        m.to_fp8(0 if tiny else 4, None if tiny else 46, block_scaled=block_scaled)
     x = torch.randn(1, S, cfg.in_channels, device=dev)
     xb = x.to(torch.bfloat16)
     ctx = torch.randn(1, 16 if tiny else 256, cfg.context_dim, device=dev, dtype=torch.bfloat16)
@@ -58,7 +58,7 @@ def bench_ltx2(dev, tiny, steps, warmup, fp8):
             ops.cfg_euler(x, v, None, dt=-0.025, mode=0, x_bf16=xb)
 
     ms = timed(step, steps, warmup)
-    return {"model": cfg.name + (" fp8 blocks 4-46" if fp8 else " bf16"), "params_b": nparams(m) / 1e9, "tokens": S,
+    return {"model": cfg.name + ((" mxfp8 (block-scaled) blocks 4-46" if block_scaled else " fp8 blocks 4-46") if fp8 else " bf16"), "params_b": nparams(m) / 1e9, "tokens": S,
             "metric": "denoise it/s", "ms_per_step": ms, "value": 1000.0 / ms}
 
 
@@ -215,6 +215,65 @@ def bench_vae(dev, tiny, steps, warmup):
             "tokens": side * side, "metric": "images/s", "ms_per_step": ms, "value": 1000.0 / ms}
 
 
+def bench_ltx2_vae(dev, tiny, steps, warmup):
+    """LTX-2 video VAE decode of a 768 x 512, 121-frame clip (latent 128 x 16 x 16 x 24)."""
+    from mojodiffusion_b200.models.video_vae import VideoVAE, ltx2_vae_config, tiny_video_vae_config
+    cfg = tiny_video_vae_config() if tiny else ltx2_vae_config()
+    shape = (1, cfg.latent_channels, 2, 4, 4) if tiny else (1, cfg.latent_channels, 16, 16, 24)
+    m = VideoVAE(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    z = torch.randn(*shape, device=dev)
+    out = {}
+
+    def step():
+        with torch.no_grad():
+            out["v"] = m.decode(z)
+
+    ms = timed(step, steps, warmup)
+    v = out["v"]
+    return {"model": cfg.name + " decode", "params_b": nparams(m) / 1e9, "tokens": int(z.numel() // z.shape[1]), "frames": int(v.shape[2]),
+            "height": int(v.shape[3]), "width": int(v.shape[4]), "metric": "clips/s", "ms_per_step": ms, "value": 1000.0 / ms}
+
+
+def bench_sdxl_train(dev, tiny, steps, warmup):
+    """SDXL UNet LoRA (rank 16) train step at 1024^2 (128 x 128 latent, batch 1): eps target over the DDPM grid, forward +
+    backward on the package's convolution / GroupNorm / attention / GEMM kernels, fused AdamW on the adapters."""
+    from mojodiffusion_b200.models.unet import UNet, sdxl_config, tiny_unet_config
+    from mojodiffusion_b200.training import lora as L
+    from mojodiffusion_b200.training.optim import FusedAdamW
+    cfg = tiny_unet_config() if tiny else sdxl_config()
+    side = 16 if tiny else 128
+    m = UNet(cfg, torch.bfloat16, dev).init_weights(0)
+    slots = L.inject_sdxl_lora(m, rank=4 if tiny else 16, alpha=16.0)
+    params = L.lora_parameters(slots)
+    opt = FusedAdamW(params, lr=1e-4, max_grad_norm=1.0)
+    x0 = torch.randn(1, cfg.in_channels, side, side, device=dev)
+    ctx = torch.randn(1, 77, cfg.context_dim, device=dev, dtype=torch.bfloat16)
+    y = torch.randn(1, cfg.adm_in_channels, device=dev, dtype=torch.bfloat16)
+    ts = torch.full((1,), 500.0, device=dev)
+    calls = {"n": 0}
+    orig = torch.nn.functional.conv2d
+
+    def spy(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+    torch.nn.functional.conv2d = spy
+
+    def step():
+        noise = torch.randn_like(x0)
+        xt = (0.7 * x0 + 0.714 * noise).to(torch.bfloat16)
+        opt.zero_grad(set_to_none=True)
+        loss = (m(xt, ts, ctx, y).float() - noise).square().mean()
+        loss.backward()
+        opt.step()
+
+    try:
+        ms = timed(step, steps, warmup)
+    finally:
+        torch.nn.functional.conv2d = orig
+    return {"model": cfg.name + " LoRA r16 train", "params_b": nparams(m) / 1e9, "tokens": side * side, "metric": "samples/s",
+            "library_conv_calls": calls["n"], "ms_per_step": ms, "value": 1000.0 / ms}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="ltx2,ltx2_fp8,qwen,zimage,zimage_train,klein,klein_train,sdxl,vae")
@@ -235,6 +294,9 @@ def main():
         "klein_train": lambda: bench_klein(dev, args.tiny, args.steps, args.warmup, True),
         "sdxl": lambda: bench_sdxl(dev, args.tiny, args.steps, args.warmup),
         "vae": lambda: bench_vae(dev, args.tiny, args.steps, args.warmup),
+        "ltx2_mxfp8": lambda: bench_ltx2(dev, args.tiny, args.steps, args.warmup, True, True),
+        "ltx2_vae": lambda: bench_ltx2_vae(dev, args.tiny, args.steps, args.warmup),
+        "sdxl_train": lambda: bench_sdxl_train(dev, args.tiny, args.steps, args.warmup),
     }
     rows = []
     for name in args.only.split(","):

@@ -242,7 +242,8 @@ Tensor group_norm_nhwc(const Tensor& x, const optional<Tensor>& w, const optiona
   TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "group_norm_nhwc");
   c10::cuda::CUDAGuard guard(x.device());
   Tensor y = at::empty_like(x);
-  Tensor stats = at::empty({x.size(0) * groups, 2}, x.options().dtype(at::kFloat));
+  Tensor stats = at::empty({mdb_group_norm_scratch_floats((int)x.size(0), (int)(x.size(1) * x.size(2)), (int)x.size(3), (int)groups, -1)},
+                           x.options().dtype(at::kFloat));
   check_rc(mdb_group_norm(x.data_ptr(), y.data_ptr(), stats.data_ptr<float>(), opt_ptr(w), opt_ptr(b), (int)x.size(0),
                           (int)(x.size(1) * x.size(2)), (int)x.size(3), (int)groups, (float)eps, (int)act, cur_stream()),
            "group_norm");
@@ -257,7 +258,8 @@ std::tuple<Tensor, Tensor, Tensor> group_norm_nhwc_bwd(const Tensor& x, const Te
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t C = x.size(3);
   Tensor dx = at::empty_like(x);
-  Tensor scratch = at::empty({x.size(0) * groups, 4}, x.options().dtype(at::kFloat));
+  Tensor scratch = at::empty({mdb_group_norm_scratch_floats((int)x.size(0), (int)(x.size(1) * x.size(2)), (int)C, (int)groups, need_wgrad ? 1 : 0)},
+                             x.options().dtype(at::kFloat));
   Tensor dw, db;
   if (need_wgrad) {
     dw = at::zeros({C}, x.options().dtype(at::kFloat));
@@ -265,7 +267,7 @@ std::tuple<Tensor, Tensor, Tensor> group_norm_nhwc_bwd(const Tensor& x, const Te
   }
   float* st = scratch.data_ptr<float>();
   g_launches.fetch_add(3, std::memory_order_relaxed);
-  check_rc(mdb_group_norm_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), st, st + 2 * x.size(0) * groups, opt_ptr(w), opt_ptr(b),
+  check_rc(mdb_group_norm_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), st, opt_ptr(w), opt_ptr(b),
                               need_wgrad ? dw.data_ptr<float>() : nullptr, need_wgrad ? db.data_ptr<float>() : nullptr, (int)x.size(0),
                               (int)(x.size(1) * x.size(2)), (int)C, (int)groups, (float)eps, (int)act, cur_stream()),
            "group_norm_bwd");

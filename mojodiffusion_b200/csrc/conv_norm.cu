@@ -63,6 +63,75 @@ group_norm_stats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__
   }
 }
 
+// Statistics over many blocks: a block takes a range of pixels of one sample for ALL channels (each thread owns one
+// 8-channel vector and strides over the pixels: 128-bit coalesced loads). Its per-channel partials are reduced in a fixed
+// order (over the pixel lanes, then over the channels of a group) and written to part[n, chunk, g] = (sum, sum of squares);
+// a second kernel adds the chunks in order and turns them into (mean, rstd). No atomics: the result does not depend on
+// scheduling. One block per (sample, group), as the kernel above, leaves most of the device idle for a 1024 x 1024 x 128
+// image (32 blocks, and 4 channels per group defeat its vector path).
+__global__ void __launch_bounds__(256)
+group_norm_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ part, int HW, int C, int G, int ppb) {
+  extern __shared__ float gsm[];                 // [256][16] per-thread channel partials, then [C][2] channel sums
+  const int n = blockIdx.y, cv = C >> 3, cpg = C / G;
+  const int lanes = blockDim.x / cv;
+  float s[8], ss[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s[k] = ss[k] = 0.f;
+  if (static_cast<int>(threadIdx.x) < lanes * cv) {
+    const int v = threadIdx.x % cv, pl = threadIdx.x / cv;
+    const int p0 = blockIdx.x * ppb, p1 = min(p0 + ppb, HW);
+    const __nv_bfloat16* base = x + (static_cast<size_t>(n) * HW) * C + v * 8;
+    for (int p = p0 + pl; p < p1; p += lanes) {
+      const uint4 u = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(p) * C);
+      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16x2(w4[k]);
+        s[2 * k] += f.x; ss[2 * k] += f.x * f.x;
+        s[2 * k + 1] += f.y; ss[2 * k + 1] += f.y * f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { gsm[threadIdx.x * 16 + k] = s[k]; gsm[threadIdx.x * 16 + 8 + k] = ss[k]; }
+  __syncthreads();
+  float* csum = gsm + 256 * 16;                  // [C][2]
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int v = c >> 3, k = c & 7;
+    float a = 0.f, b = 0.f;
+    for (int pl = 0; pl < lanes; ++pl) { a += gsm[(pl * cv + v) * 16 + k]; b += gsm[(pl * cv + v) * 16 + 8 + k]; }
+    csum[2 * c] = a; csum[2 * c + 1] = b;
+  }
+  __syncthreads();
+  float* out = part + (static_cast<size_t>(n) * gridDim.x + blockIdx.x) * 2 * G;
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    float a = 0.f, b = 0.f;
+    for (int c = g * cpg; c < (g + 1) * cpg; ++c) { a += csum[2 * c]; b += csum[2 * c + 1]; }
+    out[2 * g] = a; out[2 * g + 1] = b;
+  }
+}
+// stats[n, g] = (mean, rstd) (or, with cnt <= 0, the raw sums) from the chunk partials, added in chunk order
+__global__ void group_norm_finalize_kernel(const float* __restrict__ part, float* __restrict__ stats, int N, int G, int chunks, int stride,
+                                           float cnt, float eps) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N * G) return;
+  const int n = i / G, g = i % G;
+  float a = 0.f, b = 0.f;
+  for (int c = 0; c < chunks; ++c) {
+    const float* p = part + (static_cast<size_t>(n) * chunks + c) * stride + 2 * g;
+    a += p[0]; b += p[1];
+  }
+  if (cnt > 0.f) {
+    const float mean = a / cnt;
+    const float var = fmaxf(b / cnt - mean * mean, 0.f);
+    stats[2 * i] = mean;
+    stats[2 * i + 1] = rsqrtf(var + eps);
+  } else {
+    stats[2 * i] = a;
+    stats[2 * i + 1] = b;
+  }
+}
+
 // y = act((x - mean) * rstd * w[c] + b[c]); act 0 none, 2 SiLU
 __global__ void group_norm_apply_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                         const float* __restrict__ stats, const __nv_bfloat16* __restrict__ w,
@@ -155,10 +224,84 @@ group_norm_bwd_sums_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
     sums[2 * blockIdx.x + 1] = c2 / cnt;
   }
 }
+// many-block form of the sums above (same decomposition and ordered reductions as group_norm_partial_kernel). part[n, chunk]
+// holds per group (sum g, sum g * xh) and, when weight gradients are wanted, per channel (sum dz * xh, sum dz) after the
+// 2 * G group values; group_norm_finalize_kernel / group_norm_wgrad_kernel add the chunks in order.
+__global__ void __launch_bounds__(256)
+group_norm_bwd_partial_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ stats,
+                              const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b, float* __restrict__ part,
+                              int wgrad, int HW, int C, int G, int act, int ppb) {
+  extern __shared__ float gsm[];                 // [256][16], then [C][2]
+  const int n = blockIdx.y, cv = C >> 3, cpg = C / G;
+  const int lanes = blockDim.x / cv;
+  float a1[8], a2[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a1[k] = a2[k] = 0.f;
+  if (static_cast<int>(threadIdx.x) < lanes * cv) {
+    const int v = threadIdx.x % cv, pl = threadIdx.x / cv;
+    const int p0 = blockIdx.x * ppb, p1 = min(p0 + ppb, HW);
+    float wc[8], bc[8], mean[8], rstd[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = v * 8 + k, g = c / cpg;
+      wc[k] = w ? __bfloat162float(w[c]) : 1.f;
+      bc[k] = b ? __bfloat162float(b[c]) : 0.f;
+      mean[k] = stats[2 * (n * G + g)];
+      rstd[k] = stats[2 * (n * G + g) + 1];
+    }
+    const size_t base = (static_cast<size_t>(n) * HW) * C + v * 8;
+    for (int p = p0 + pl; p < p1; p += lanes) {
+      const uint4 ux = *reinterpret_cast<const uint4*>(x + base + static_cast<size_t>(p) * C);
+      const uint4 ud = *reinterpret_cast<const uint4*>(dy + base + static_cast<size_t>(p) * C);
+      const uint32_t x4[4] = {ux.x, ux.y, ux.z, ux.w}, d4[4] = {ud.x, ud.y, ud.z, ud.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float2 fx = unpack_bf16x2(x4[k >> 1]), fd = unpack_bf16x2(d4[k >> 1]);
+        const float xh = (((k & 1) ? fx.y : fx.x) - mean[k]) * rstd[k];
+        const float dz = ((k & 1) ? fd.y : fd.x) * gn_dact(xh * wc[k] + bc[k], act);
+        a1[k] += dz;
+        a2[k] += dz * xh;
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { gsm[threadIdx.x * 16 + k] = a1[k]; gsm[threadIdx.x * 16 + 8 + k] = a2[k]; }
+  __syncthreads();
+  float* csum = gsm + 256 * 16;                  // [C][2] = (sum dz, sum dz * xh)
+  const int stride = 2 * G + (wgrad ? 2 * C : 0);
+  float* out = part + (static_cast<size_t>(n) * gridDim.x + blockIdx.x) * stride;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int v = c >> 3, k = c & 7;
+    float a = 0.f, bsum = 0.f;
+    for (int pl = 0; pl < lanes; ++pl) { a += gsm[(pl * cv + v) * 16 + k]; bsum += gsm[(pl * cv + v) * 16 + 8 + k]; }
+    csum[2 * c] = a; csum[2 * c + 1] = bsum;
+    if (wgrad) { out[2 * G + 2 * c] = bsum; out[2 * G + 2 * c + 1] = a; }
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    float a = 0.f, bsum = 0.f;
+    for (int c = g * cpg; c < (g + 1) * cpg; ++c) {
+      const float wc = w ? __bfloat162float(w[c]) : 1.f;
+      a += csum[2 * c] * wc; bsum += csum[2 * c + 1] * wc;
+    }
+    out[2 * g] = a; out[2 * g + 1] = bsum;
+  }
+}
+// dw[c] / db[c] += over samples and chunks, in order
+__global__ void group_norm_wgrad_kernel(const float* __restrict__ part, float* __restrict__ dw, float* __restrict__ db, int N, int C, int G,
+                                        int chunks) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int stride = 2 * G + 2 * C;
+  float a = 0.f, b = 0.f;
+  for (int i = 0; i < N * chunks; ++i) { a += part[static_cast<size_t>(i) * stride + 2 * G + 2 * c]; b += part[static_cast<size_t>(i) * stride + 2 * G + 2 * c + 1]; }
+  dw[c] += a;
+  db[c] += b;
+}
 __global__ void group_norm_bwd_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
                                             __nv_bfloat16* __restrict__ dx, const float* __restrict__ stats, const float* __restrict__ sums,
                                             const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b, long long total_vec,
-                                            int HW, int C, int G, int act) {
+                                            int HW, int C, int G, int act, float sum_scale) {
   const int cv = C >> 3, cpg = C / G;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_vec; i += (long long)gridDim.x * blockDim.x) {
     const int c0 = static_cast<int>(i % cv) * 8;
@@ -172,7 +315,7 @@ __global__ void group_norm_bwd_apply_kernel(const __nv_bfloat16* __restrict__ x,
       const float xv = (k & 1) ? fx.y : fx.x, dv = (k & 1) ? fd.y : fd.x;
       const int c = c0 + k, g = c / cpg;
       const float mean = stats[2 * (n * G + g)], rstd = stats[2 * (n * G + g) + 1];
-      const float m1 = sums[2 * (n * G + g)], m2 = sums[2 * (n * G + g) + 1];
+      const float m1 = sums[2 * (n * G + g)] * sum_scale, m2 = sums[2 * (n * G + g) + 1] * sum_scale;
       const float wc = w ? __bfloat162float(w[c]) : 1.f, bc = b ? __bfloat162float(b[c]) : 0.f;
       const float xh = (xv - mean) * rstd;
       const float gg = dv * gn_dact(xh * wc + bc, act) * wc;
@@ -228,24 +371,76 @@ static inline int grid_for(long long n, int threads) {
 using namespace mdb;
 typedef __nv_bfloat16 bf16;
 
+// How the many-block kernels split a sample: chunk count and pixels per chunk (0 chunks: use the block-per-group kernels)
+static void gn_chunks(int N, int HW, int C, int G, int* chunks, int* ppb) {
+  const int cv = C / 8, sms = mdb::device_sm_count();
+  *chunks = 0;
+  *ppb = 0;
+  if (cv > 256 || C > 2048 || N * G >= 4 * sms) return;
+  int ch = (4 * sms + N - 1) / N;                               // about four blocks per SM over all samples
+  int pp = (HW + ch - 1) / ch;
+  const int lanes = 256 / cv;
+  if (pp < 4 * lanes) pp = 4 * lanes;                           // at least a few pixels per thread
+  *ppb = pp;
+  *chunks = (HW + pp - 1) / pp;
+}
+// fp32 elements of scratch the forward (wgrad < 0) or the backward (wgrad 0 / 1) needs
+extern "C" long long mdb_group_norm_scratch_floats(int N, int HW, int C, int G, int wgrad) {
+  int chunks, ppb;
+  gn_chunks(N, HW, C, G, &chunks, &ppb);
+  const long long base = (wgrad < 0 ? 2ll : 4ll) * N * G;
+  const long long fwd = 2ll * G * N * chunks;
+  const long long bwd = (2ll * G + (wgrad > 0 ? 2ll * C : 0)) * N * chunks;
+  return base + (wgrad < 0 ? fwd : (fwd > bwd ? fwd : bwd));
+}
+// (mean, rstd) per (sample, group) into stats; ``part`` is scratch for the chunk partials
+static int launch_group_stats(const void* x, float* stats, float* part, int N, int HW, int C, int G, float eps, cudaStream_t st) {
+  int chunks, ppb;
+  gn_chunks(N, HW, C, G, &chunks, &ppb);
+  if (chunks == 0) {
+    group_norm_stats_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, stats, HW, C, G, eps);
+    return (int)cudaGetLastError();
+  }
+  const size_t smem = (256 * 16 + 2 * C) * sizeof(float);
+  group_norm_partial_kernel<<<dim3(chunks, N), 256, smem, st>>>((const bf16*)x, part, HW, C, G, ppb);
+  group_norm_finalize_kernel<<<(N * G + 255) / 256, 256, 0, st>>>(part, stats, N, G, chunks, 2 * G, static_cast<float>(HW) * (C / G), eps);
+  return (int)cudaGetLastError();
+}
+
 // stats: [N * G, 2] scratch (mean, rstd), sums: [N * G, 2] scratch; dw / db: fp32 [C] accumulators (zeroed by the caller) or null
-extern "C" int mdb_group_norm_bwd(const void* x, const void* dy, void* dx, float* stats, float* sums, const void* w, const void* b,
-                                  float* dw, float* db, int N, int HW, int C, int G, float eps, int act, cudaStream_t st) {
+extern "C" int mdb_group_norm_bwd(const void* x, const void* dy, void* dx, float* scratch, const void* w, const void* b, float* dw,
+                                  float* db, int N, int HW, int C, int G, float eps, int act, cudaStream_t st) {
   if (C % G || C % 8 || (act != 0 && act != 2) || (C / G) > 256) return -1;
   if (N == 0) return 0;
-  group_norm_stats_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, stats, HW, C, G, eps);
-  group_norm_bwd_sums_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, stats, (const bf16*)w, (const bf16*)b, sums, dw, db,
-                                                    HW, C, G, act);
+  float* stats = scratch;
+  float* sums = scratch + 2ll * N * G;
+  float* part = scratch + 4ll * N * G;
+  if (int rc = launch_group_stats(x, stats, part, N, HW, C, G, eps, st)) return rc;
+  int chunks, ppb;
+  gn_chunks(N, HW, C, G, &chunks, &ppb);
+  if (chunks == 0) {
+    group_norm_bwd_sums_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, stats, (const bf16*)w, (const bf16*)b, sums, dw, db,
+                                                      HW, C, G, act);
+  } else {
+    const int wgrad = dw != nullptr ? 1 : 0;
+    const size_t smem = (256 * 16 + 2 * C) * sizeof(float);
+    group_norm_bwd_partial_kernel<<<dim3(chunks, N), 256, smem, st>>>((const bf16*)x, (const bf16*)dy, stats, (const bf16*)w, (const bf16*)b,
+                                                                      part, wgrad, HW, C, G, act, ppb);
+    if (wgrad) group_norm_wgrad_kernel<<<(C + 255) / 256, 256, 0, st>>>(part, dw, db, N, C, G, chunks);
+    // raw group sums (cnt <= 0), chunks added in order
+    group_norm_finalize_kernel<<<(N * G + 255) / 256, 256, 0, st>>>(part, sums, N, G, chunks, 2 * G + (wgrad ? 2 * C : 0), -1.f, 0.f);
+  }
+  const float sum_scale = chunks == 0 ? 1.f : 1.f / (static_cast<float>(HW) * (C / G));
   const long long tv = static_cast<long long>(N) * HW * (C / 8);
   group_norm_bwd_apply_kernel<<<grid_for(tv, 256), 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (bf16*)dx, stats, sums, (const bf16*)w,
-                                                                 (const bf16*)b, tv, HW, C, G, act);
+                                                                 (const bf16*)b, tv, HW, C, G, act, sum_scale);
   return (int)cudaGetLastError();
 }
 extern "C" int mdb_group_norm(const void* x, void* y, float* stats, const void* w, const void* b, int N, int HW, int C,
                               int G, float eps, int act, cudaStream_t st) {
   if (C % 8 || C % G) return -1;
   if (N <= 0 || HW <= 0) return 0;
-  group_norm_stats_kernel<<<N * G, 256, 0, st>>>((const bf16*)x, stats, HW, C, G, eps);
+  if (int rc = launch_group_stats(x, stats, stats + 2ll * N * G, N, HW, C, G, eps, st)) return rc;
   const long long tv = static_cast<long long>(N) * HW * (C / 8);
   group_norm_apply_kernel<<<grid_for(tv, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, stats, (const bf16*)w,
                                                              (const bf16*)b, tv, HW, C, G, act);

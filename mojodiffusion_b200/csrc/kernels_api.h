@@ -76,8 +76,11 @@ int mdb_fp8_dequant(const void* q, const float* row_scale, float tensor_scale, v
                     cudaStream_t st);
 
 // ---- conv_norm.cu (NHWC)
-int mdb_group_norm_bwd(const void* x, const void* dy, void* dx, float* stats, float* sums, const void* w, const void* b,
-                       float* dw, float* db, int N, int HW, int C, int G, float eps, int act, cudaStream_t st);
+// scratch: mdb_group_norm_scratch_floats(N, HW, C, G, wgrad) fp32 values (wgrad < 0: forward; 0 / 1: backward without / with dw, db)
+long long mdb_group_norm_scratch_floats(int N, int HW, int C, int G, int wgrad);
+int mdb_group_norm_bwd(const void* x, const void* dy, void* dx, float* scratch, const void* w, const void* b, float* dw, float* db,
+                       int N, int HW, int C, int G, float eps, int act, cudaStream_t st);
+// stats: scratch of mdb_group_norm_scratch_floats(N, HW, C, G, -1) fp32 values; its first 2 * N * G hold (mean, rstd) afterwards
 int mdb_group_norm(const void* x, void* y, float* stats, const void* w, const void* b, int N, int HW, int C, int G,
                    float eps, int act, cudaStream_t st);
 int mdb_upsample2x(const void* x, void* y, int N, int H, int W, int C, cudaStream_t st);
