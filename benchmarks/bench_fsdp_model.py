@@ -31,6 +31,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--fuse-optimizer", action="store_true", help="AdamW of the sharded weights inside the reduce-scatter tail of backward")
     ap.add_argument("--depth", type=int, default=0, help="number of blocks (0: the architecture's own)")
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
@@ -54,7 +55,7 @@ def main():
     t0 = time.time()
     model = QwenImageDiT(cfg, torch.bfloat16, dev).init_weights(0)
     n_params = sum(p.numel() for p in model.parameters())
-    ctx = FSDPContext(mode=args.mode, device=dev)
+    ctx = FSDPContext(mode=args.mode, device=dev, fuse_optimizer=args.fuse_optimizer and args.mode == "fused")
     n_sharded = shard_model(model, ctx)
     torch.cuda.empty_cache()
     rest = [p for p in model.parameters() if p.numel() > 0]
@@ -77,6 +78,8 @@ def main():
             dp.zero_grad()
         else:
             opt.zero_grad(set_to_none=True)
+        if ctx.fused_active():
+            ctx.begin_step(lr=1e-5)
         xt, target = ops.flow_match(x0, eps, t)
         loss = ops.mse_loss(model(xt.to(torch.bfloat16), txt, t, hw), target)
         loss.backward()

@@ -796,6 +796,25 @@ Tensor rs_finalize(std::vector<int64_t> flag_ptrs, const Tensor& my_flags, int64
            "rs_finalize");
   return out;
 }
+void rs_adamw(std::vector<int64_t> flag_ptrs, const Tensor& my_flags, int64_t slot, int64_t epoch, int64_t rank, const Tensor& stage,
+              Tensor master, Tensor m, Tensor v, Tensor shadow, double lr, double beta1, double beta2, double eps, double wd, int64_t step,
+              double grad_scale) {
+  TORCH_CHECK(stage.is_cuda() && stage.dim() == 3 && stage.is_contiguous() && stage.scalar_type() == at::kBFloat16, "rs_adamw: stage bf16 [world, rows, D]");
+  TORCH_CHECK((int64_t)flag_ptrs.size() == stage.size(0), "rs_adamw: one staging slot per rank");
+  const int64_t n = stage.size(1) * stage.size(2);
+  for (const Tensor* t : {&master, &m, &v})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == n && t->device() == stage.device(),
+                "rs_adamw: master / m / v must be fp32 [rows, D] on the stage's device");
+  TORCH_CHECK(shadow.scalar_type() == at::kBFloat16 && shadow.is_contiguous() && shadow.numel() == n && shadow.device() == stage.device(),
+              "rs_adamw: shadow must be bf16 [rows, D]");
+  c10::cuda::CUDAGuard guard(stage.device());
+  MdbPeerTable f = peer_table(flag_ptrs);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  check_rc(mdb_rs_adamw(&f, my_flags.data_ptr<int>(), (int)slot, (int)epoch, (int)rank, (int)stage.size(0), stage.data_ptr(), n,
+                        master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), shadow.data_ptr(), (float)lr, (float)beta1,
+                        (float)beta2, (float)eps, (float)wd, (int)step, (float)grad_scale, status_ptr(stage), cur_stream()),
+           "rs_adamw");
+}
 void peer_gather(std::vector<int64_t> src_ptrs, Tensor dst, int64_t chunk_bytes, int64_t rank, bool copy_local) {
   c10::cuda::CUDAGuard guard(dst.device());
   MdbPeerTable s = peer_table(src_ptrs);
@@ -912,6 +931,7 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("flag_wait", &flag_wait);
   m.def("flag_barrier", &flag_barrier);
   m.def("rs_finalize", &rs_finalize);
+  m.def("rs_adamw", &rs_adamw);
   m.def("peer_gather", &peer_gather);
   m.def("dp_reduce_shard", &dp_reduce_shard);
   m.def("publish_scalar", &publish_scalar);

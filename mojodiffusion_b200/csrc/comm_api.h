@@ -27,6 +27,10 @@ int mdb_flag_barrier(const MdbPeerTable* flags, const int* my_flags, int slot, i
 // staged reduce-scatter tail: barrier on `slot` (explicit epoch > 0), then out = residual + gate * (sum of the `world`
 // bf16 slots of stage[world][rows][D] + bias). bias / residual / gate may be NULL. Exactly one of out (bf16 [rows, D]) and
 // accum (fp32 [rows, D], += the result: gradient accumulation) is given.
+// reduce-scatter tail + AdamW on the owner's shard in one launch (stage: bf16 [world][n]); see rs_adamw_kernel
+int mdb_rs_adamw(const MdbPeerTable* flags, const int* my_flags, int slot, int epoch, int rank, int world, const void* stage, long long n,
+                 float* master, float* m, float* v, void* shadow, float lr, float beta1, float beta2, float eps, float wd, int step,
+                 float grad_scale, int* status, cudaStream_t st);
 int mdb_rs_finalize(const MdbPeerTable* flags, const int* my_flags, int slot, int epoch, int rank, int world,
                     const void* stage, long long rows, int D, const void* bias, const void* residual, const void* gate,
                     int rows_per_group, long long gate_stride, void* out, float* accum, int* status, cudaStream_t st);

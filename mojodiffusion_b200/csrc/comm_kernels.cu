@@ -327,10 +327,71 @@ rs_finalize_kernel(MdbPeerTable flags, const int* my_flags, int slot, int epoch,
 
 using namespace mdb;
 
+// Reduce-scatter tail fused with the optimizer (fully-sharded training, one launch per layer inside backward): after the
+// same signal / wait as rs_finalize_kernel, every thread adds the N staged bf16 partial gradients of its elements in fp32
+// and applies AdamW to the fp32 master shard, its moments, and the bf16 shard the next all-gather reads. The gradient
+// shard is never stored. All ranks have finished the input-gradient GEMM that read the OLD shard before they signal, so
+// overwriting the bf16 shard here cannot race with a peer's gather of this layer.
+struct RsAdam { float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt, grad_scale; };
+__global__ void __launch_bounds__(256)
+rs_adamw_kernel(MdbPeerTable flags, const int* my_flags, int slot, int epoch, int rank, int world,
+                const __nv_bfloat16* __restrict__ stage, long long n, float* __restrict__ master, float* __restrict__ m,
+                float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, RsAdam h, int* status) {
+  if (world > 1) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(flags, slot, rank, world, epoch);
+    if (!block_wait_all(my_flags, slot, world, epoch, status, 140 + slot)) return;
+  }
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != STATUS_OK) return;      // see rs_finalize_kernel
+  const long long nv = n / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < world; ++s) add8_bf16(*reinterpret_cast<const uint4*>(stage + s * n + i * 8), g);
+    float4 p0 = *reinterpret_cast<const float4*>(master + i * 8), p1 = *reinterpret_cast<const float4*>(master + i * 8 + 4);
+    float4 m0 = *reinterpret_cast<const float4*>(m + i * 8), m1 = *reinterpret_cast<const float4*>(m + i * 8 + 4);
+    float4 v0 = *reinterpret_cast<const float4*>(v + i * 8), v1 = *reinterpret_cast<const float4*>(v + i * 8 + 4);
+    float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = g[j] * h.grad_scale;
+      pp[j] *= 1.f - h.lr * h.wd;
+      mm[j] = h.beta1 * mm[j] + (1.f - h.beta1) * gj;
+      vv[j] = h.beta2 * vv[j] + (1.f - h.beta2) * gj * gj;
+      pp[j] -= (h.lr / h.bc1) * mm[j] / (sqrtf(vv[j]) / h.bc2_sqrt + h.eps);
+    }
+    *reinterpret_cast<float4*>(master + i * 8) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+    *reinterpret_cast<float4*>(master + i * 8 + 4) = make_float4(pp[4], pp[5], pp[6], pp[7]);
+    *reinterpret_cast<float4*>(m + i * 8) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    *reinterpret_cast<float4*>(m + i * 8 + 4) = make_float4(mm[4], mm[5], mm[6], mm[7]);
+    *reinterpret_cast<float4*>(v + i * 8) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    *reinterpret_cast<float4*>(v + i * 8 + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    uint4 o;
+    o.x = pack_bf16x2(pp[0], pp[1]); o.y = pack_bf16x2(pp[2], pp[3]); o.z = pack_bf16x2(pp[4], pp[5]); o.w = pack_bf16x2(pp[6], pp[7]);
+    *reinterpret_cast<uint4*>(shadow + i * 8) = o;
+  }
+}
+
 extern "C" int mdb_flag_barrier(const MdbPeerTable* flags, const int* my_flags, int slot, int rank, int world, int value,
                                 int* counters, int* status, cudaStream_t st) {
   if (slot < 0 || slot >= MDB_FLAG_SLOTS || (value <= 0 && counters == nullptr)) return -1;
   flag_barrier_kernel<<<1, 32, 0, st>>>(*flags, my_flags, slot, rank, world, value, counters, status);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_rs_adamw(const MdbPeerTable* flags, const int* my_flags, int slot, int epoch, int rank, int world, const void* stage,
+                            long long n, float* master, float* m, float* v, void* shadow, float lr, float beta1, float beta2, float eps,
+                            float wd, int step, float grad_scale, int* status, cudaStream_t st) {
+  if ((n & 7) || n < 0 || slot < 0 || slot >= MDB_FLAG_SLOTS || epoch <= 0 || step < 1) return -1;
+  if (n == 0) return 0;
+  RsAdam h;
+  h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.wd = wd; h.grad_scale = grad_scale;
+  h.bc1 = 1.f - powf(beta1, static_cast<float>(step));
+  h.bc2_sqrt = sqrtf(1.f - powf(beta2, static_cast<float>(step)));
+  const long long want = (n / 8 + 255) / 256;
+  const int cap = device_sm_count() * 4;                       // every block waits for the peers: one resident wave
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  rs_adamw_kernel<<<grid, 256, 0, st>>>(*flags, my_flags, slot, epoch, rank, world, reinterpret_cast<const __nv_bfloat16*>(stage), n, master,
+                                        m, v, reinterpret_cast<__nv_bfloat16*>(shadow), h, status);
   return (int)cudaGetLastError();
 }
 extern "C" int mdb_rs_finalize(const MdbPeerTable* flags, const int* my_flags, int slot, int epoch, int rank, int world,

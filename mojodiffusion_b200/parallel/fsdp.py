@@ -40,8 +40,14 @@ class FSDPContext:
     """Owns the symmetric arena (weight shards + gradient shards of all layers), the transient gather buffer and the
     flags. Layers register themselves; ``finalize()`` allocates."""
 
-    def __init__(self, group=None, mode: str = "fused", device=None):
+    def __init__(self, group=None, mode: str = "fused", device=None, fuse_optimizer: bool = False):
+        """``fuse_optimizer``: the reduce-scatter tail of every layer's weight gradient also applies AdamW to the owner's
+        shard (one launch per layer inside backward, no stored gradient shard); call ``begin_step`` with the step's
+        hyper-parameters before backward, ``step`` afterwards only publishes the new shards. Each layer may be used once
+        per step in this mode, and there is no gradient accumulation or clipping across layers."""
         self.group, self.mode = group, mode
+        self.fuse_optimizer = fuse_optimizer
+        self.hyper = None
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -120,9 +126,29 @@ class FSDPContext:
         return W
 
     # ---- optimizer ---------------------------------------------------------------------------------------------
+    def begin_step(self, lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, grad_scale: Optional[float] = None):
+        """Fused-optimizer mode: fix this step's AdamW hyper-parameters before backward runs."""
+        self.step_count += 1
+        self.hyper = (float(lr), float(betas[0]), float(betas[1]), float(eps), float(weight_decay), self.step_count,
+                      (1.0 / self.world) if grad_scale is None else float(grad_scale))
+        for l in self.layers:
+            l._updated = False
+
+    def fused_active(self) -> bool:
+        return self.fuse_optimizer and self.world > 1 and self.symm is not None
+
     @torch.no_grad()
     def step(self, lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, grad_scale: Optional[float] = None):
         """AdamW on every local master shard (one launch), bf16 shards refreshed for the next all-gather."""
+        if self.fused_active():
+            if self.hyper is None or not all(getattr(l, "_updated", False) for l in self.layers):
+                raise RuntimeError("fuse_optimizer: call begin_step() before backward, and every layer must take part in it")
+            self.hyper = None
+            self.gathered_owner = None
+            self.barrier(SLOT_STEP_DONE)                      # every rank's updated shards are in place before the next gather
+            if self.step_count % getattr(self, "check_every", 16) == 0:
+                self.check()
+            return
         with nvtx_range("collective/fsdp/grad_barrier"):
             self.barrier(SLOT_BWD_DONE)                       # every rank's dW tiles have been added into my shards
         self.step_count += 1
@@ -190,8 +216,18 @@ class _FSDPLinearFn(torch.autograd.Function):
             rl, K = layer.rows_local, layer.in_features
             _gemm([dy], [x2], a_mn=True, b_mn=True, route_ptrs=c.symm.ptrs_at(off), route_cfg=[rl, K, c.rank])
             stage = c.arena[off:off + c.world * rl * K * 2].view(torch.bfloat16).view(c.world, rl, K)
-            native.ops().rs_finalize(c.symm.ptrs_at(0), c.flags, SLOT_RS, c.rs_calls, c.rank, stage, None, None, None, 1,
-                                     layer.g_shard)
+            if c.fuse_optimizer:
+                if c.hyper is None:
+                    raise RuntimeError("fuse_optimizer: begin_step() was not called before backward")
+                if getattr(layer, "_updated", False):
+                    raise RuntimeError("fuse_optimizer: a layer took part in backward twice in one step")
+                lr, b1, b2, eps_, wd, t_step, gs = c.hyper
+                native.ops().rs_adamw(c.symm.ptrs_at(0), c.flags, SLOT_RS, c.rs_calls, c.rank, stage, layer.master, layer.m, layer.v,
+                                      layer.w_shard, lr, b1, b2, eps_, wd, t_step, gs)
+                layer._updated = True
+            else:
+                native.ops().rs_finalize(c.symm.ptrs_at(0), c.flags, SLOT_RS, c.rs_calls, c.rank, stage, None, None, None, 1,
+                                         layer.g_shard)
         else:
             dw = _gemm([dy], [x2], a_mn=True, b_mn=True, out_fp32=True)
             if c.world > 1:

@@ -142,6 +142,29 @@ def _fsdp_worker(rank, world, port, out_dir):
             assert cos > 0.9, f"rank {rank} mode {mode}: update cosine {cos}"
             assert abs(float(du.norm() / dr.norm()) - 1.0) < 0.1
             assert float((got - W).abs().mean()) < 0.35 * float(dr.abs().mean())
+    # the optimizer inside the reduce-scatter tail: same three steps, no stored gradient shard, same result as the
+    # separate AdamW launch of the fused mode above (bf16 staged partials, fp32 sum and update in both)
+    ctx = FSDPContext(mode="fused", device=dev, fuse_optimizer=True)
+    f1 = FSDPLinear(ctx, D, F, bias=False, full_weight=w1)
+    f2 = FSDPLinear(ctx, F, D, bias=False, full_weight=w2)
+    ctx.finalize()
+    for t in range(steps):
+        ctx.begin_step(lr=lr, weight_decay=0.01)
+        out = f2(O.activation(f1(xs[rank].to(dev)), "gelu_tanh"))
+        (out.float() - ts[rank].to(dev)).pow(2).mean().backward()
+        ctx.step()
+    torch.cuda.synchronize()
+    native.check_status()
+    for lay, other, W in ((f1, l1, W1), (f2, l2, W2)):
+        got, sep = lay.full_master(), other.full_master()
+        w0 = (w1 if lay is f1 else w2).to(dev)
+        du, dr = (got - w0).flatten(), (sep - w0).flatten()
+        # Adam turns a last-bit difference of a near-zero gradient into a step of size lr, so the two runs are compared as
+        # update vectors: same direction, same length, small mean deviation
+        cosu = float(torch.dot(du, dr) / (du.norm() * dr.norm() + 1e-30))
+        assert cosu > 0.995 and abs(float(du.norm() / dr.norm()) - 1.0) < 0.01, f"rank {rank}: fused optimizer update cosine {cosu}"
+        assert float((du - dr).abs().mean()) < 0.03 * float(dr.abs().mean())
+        assert torch.equal(lay.w_shard.float(), lay.master.to(torch.bfloat16).float())
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:
