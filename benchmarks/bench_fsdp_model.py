@@ -106,7 +106,7 @@ def main():
     peak = torch.cuda.max_memory_allocated() / 2 ** 30
     if rank == 0:
         row = {"metric": "full-finetune samples/s", "value": world * 1000.0 / ms, "ms_per_step": ms, "n_gpus": world,
-               "mode": args.mode, "model": cfg.name, "depth": cfg.depth, "params_b": n_params / 1e9,
+               "mode": args.mode + ("+optimizer-in-backward" if ctx.fused_active() else ""), "model": cfg.name, "depth": cfg.depth, "params_b": n_params / 1e9,
                "sharded_linears": n_sharded, "tokens": hw[0] * hw[1] + S_txt, "batch_per_gpu": 1,
                "gradient_checkpointing": True, "peak_gib_rank0": peak, "init_s": t_init,
                "losses": [float(l) for l in losses], "steps": args.steps, "warmup": args.warmup}

@@ -141,8 +141,13 @@ class FSDPContext:
     def step(self, lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, grad_scale: Optional[float] = None):
         """AdamW on every local master shard (one launch), bf16 shards refreshed for the next all-gather."""
         if self.fused_active():
-            if self.hyper is None or not all(getattr(l, "_updated", False) for l in self.layers):
-                raise RuntimeError("fuse_optimizer: call begin_step() before backward, and every layer must take part in it")
+            if self.hyper is None:
+                raise RuntimeError("fuse_optimizer: call begin_step() before backward")
+            # layers that received no gradient this step (their output does not reach the loss) still decay: one AdamW
+            # launch over just those, with their zero gradient shards
+            idle = tuple(i for i, l in enumerate(self.layers) if not getattr(l, "_updated", False))
+            if idle:
+                self._adamw_over(idle, *self.hyper)
             self.hyper = None
             self.gathered_owner = None
             self.barrier(SLOT_STEP_DONE)                      # every rank's updated shards are in place before the next gather
@@ -171,6 +176,20 @@ class FSDPContext:
         self.barrier(SLOT_STEP_DONE)                      # new shards visible everywhere before the next gather
         if self.step_count % getattr(self, "check_every", 16) == 0:
             self.check()
+
+    def _adamw_over(self, idx, lr, b1, b2, eps, wd, t_step, scale):
+        from ..training.optim import CHUNK
+        cache = self.__dict__.setdefault("_idle_tables", {})
+        if idx not in cache:
+            rows, chunks = [], []
+            for j, i in enumerate(idx):
+                l = self.layers[i]
+                n = l.master.numel()
+                rows.append([l.master.data_ptr(), l.g_shard.data_ptr(), l.m.data_ptr(), l.v.data_ptr(), l.w_shard.data_ptr(), n])
+                chunks += [[j, c] for c in range((n + CHUNK - 1) // CHUNK)]
+            cache[idx] = (torch.tensor(rows, dtype=torch.int64).to(self.device), torch.tensor(chunks, dtype=torch.int32).to(self.device))
+        table, chunks = cache[idx]
+        native.ops().adamw_multi(table, chunks, CHUNK, False, False, False, lr, b1, b2, eps, wd, t_step, scale, None, 0.0, 0, False)
 
     def check(self) -> None:
         """Raise if a bounded wait of the fused kernels ran out on this device since the last check (the AdamW launch of
