@@ -269,7 +269,6 @@ def main():
         torch.cuda.empty_cache()
         slots = L.inject_flux_lora(model, rank=16, alpha=16.0)
         params = L.lora_parameters(slots)
-        model.gradient_checkpointing = True
         model.train()
         dp = None
         if lib_baseline:
@@ -296,52 +295,66 @@ def main():
             opt = FusedDPAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
         else:
             opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01, max_grad_norm=1.0)
-        tr = FlowMatchTrainer(model, params, opt, dp, use_cuda_graph=not args.no_train_graph and not lib_baseline)
         gt = torch.Generator().manual_seed(99 + rank)   # data parallel: every rank trains on its own samples
         x0 = torch.randn(B, S_img, cfg.in_channels, generator=gt).to(dev)
         txt = torch.randn(B, S_txt, cfg.context_dim, generator=gt).to(dev, torch.bfloat16)
         y = torch.randn(B, cfg.vec_dim, generator=gt).to(dev, torch.bfloat16)
-        want_graph = tr.use_cuda_graph
-        tr.use_cuda_graph = False
-        l0 = launches()
-        tr.step(x0, txt, y, hw=hw)                       # one eager step: also counts the kernels of a step
-        torch.cuda.synchronize()
-        train_launches_per_step = launches() - l0
-        if want_graph:
-            ok_graph = 1
-            tr.use_cuda_graph = True
+
+        def time_train(ckpt: bool):
+            model.gradient_checkpointing = ckpt
+            tr = FlowMatchTrainer(model, params, opt, dp, use_cuda_graph=not args.no_train_graph and not lib_baseline)
+            want_graph = tr.use_cuda_graph
+            tr.use_cuda_graph = False
+            l0 = launches()
+            tr.step(x0, txt, y, hw=hw)                       # one eager step: also counts the kernels of a step
+            torch.cuda.synchronize()
+            train_launches_per_step = launches() - l0
+            if want_graph:
+                ok_graph = 1
+                tr.use_cuda_graph = True
+                try:
+                    tr.step(x0, txt, y, hw=hw)               # warms up, captures forward + backward, replays once
+                    torch.cuda.synchronize()
+                except Exception as ex:                      # capture refused: report it and time the eager step instead
+                    ok_graph = 0
+                    sys.stderr.write(f"[bench] training graph capture failed, timing the eager step: {ex}\n")
+                if world > 1:
+                    flag = torch.tensor([ok_graph], device=dev)
+                    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                    ok_graph = int(flag.item())
+                if not ok_graph:
+                    tr.use_cuda_graph, tr._graphed = False, None
+            for i in range(2):
+                tr.step(x0, txt, y, hw=hw)
+            torch.cuda.synchronize()
+            pdist.barrier()
+            t0n = launches()
+            e0.record()
+            for i in range(tsteps):
+                loss = tr.step(x0, txt, y, hw=hw)
+            e1.record()
+            torch.cuda.synchronize()
+            pdist.barrier()
+            ms_t = pdist.max_over_ranks(e0.elapsed_time(e1) / tsteps)
+            native.check_status()
+            return {"metric": "lora_train_samples_per_s", "value": world * B * 1000.0 / ms_t, "unit": "samples/s",
+                     "ms_per_step": ms_t, "steps": tsteps, "warmup": 3, "loss": float(loss), "rank": 16,
+                     "gpu_launches": (train_launches_per_step * tsteps if tr._graphed is not None else launches() - t0n),
+                     "launches_per_step": train_launches_per_step, "gradient_checkpointing": ckpt, "cuda_graph": bool(tr._graphed is not None),
+                     "parallelism": f"dp{world}, NCCL all-reduce + torch AdamW" if (lib_baseline and world > 1) else (f"dp{world}, grad reduce-scatter + clip + AdamW + param all-gather fused in peer-memory "
+                                     f"kernels (multicast {'on' if getattr(opt, 'symm', None) is not None and opt.symm.mc_ptr else 'off'})")
+                     if world > 1 else "single"}
+
+        # the reference's trainer recomputes every block in backward (24 GB cards); with 180 GB the activations of all 57
+        # blocks stay resident, so the same step is also timed without recompute
+        train = time_train(True)
+        if not lib_baseline and args.model == "flux1-dev":
             try:
-                tr.step(x0, txt, y, hw=hw)               # warms up, captures forward + backward, replays once
-                torch.cuda.synchronize()
-            except Exception as ex:                      # capture refused: report it and time the eager step instead
-                ok_graph = 0
-                sys.stderr.write(f"[bench] training graph capture failed, timing the eager step: {ex}\n")
-            if world > 1:
-                flag = torch.tensor([ok_graph], device=dev)
-                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-                ok_graph = int(flag.item())
-            if not ok_graph:
-                tr.use_cuda_graph, tr._graphed = False, None
-        for i in range(2):
-            tr.step(x0, txt, y, hw=hw)
-        torch.cuda.synchronize()
-        pdist.barrier()
-        t0n = launches()
-        e0.record()
-        for i in range(tsteps):
-            loss = tr.step(x0, txt, y, hw=hw)
-        e1.record()
-        torch.cuda.synchronize()
-        pdist.barrier()
-        ms_t = pdist.max_over_ranks(e0.elapsed_time(e1) / tsteps)
-        native.check_status()
-        train = {"metric": "lora_train_samples_per_s", "value": world * B * 1000.0 / ms_t, "unit": "samples/s",
-                 "ms_per_step": ms_t, "steps": tsteps, "warmup": 3, "loss": float(loss), "rank": 16,
-                 "gpu_launches": (train_launches_per_step * tsteps if tr._graphed is not None else launches() - t0n),
-                 "launches_per_step": train_launches_per_step, "gradient_checkpointing": True, "cuda_graph": bool(tr._graphed is not None),
-                 "parallelism": f"dp{world}, NCCL all-reduce + torch AdamW" if (lib_baseline and world > 1) else (f"dp{world}, grad reduce-scatter + clip + AdamW + param all-gather fused in peer-memory "
-                                 f"kernels (multicast {'on' if getattr(opt, 'symm', None) is not None and opt.symm.mc_ptr else 'off'})")
-                 if world > 1 else "single"}
+                nr = time_train(False)
+                train["activations_resident"] = {k: nr[k] for k in ("value", "unit", "ms_per_step", "loss", "launches_per_step", "cuda_graph", "gradient_checkpointing")}
+                train["activations_resident"]["peak_gib"] = round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)
+            except torch.OutOfMemoryError as ex:
+                train["activations_resident"] = {"error": str(ex)[:200]}
 
     # ------------------------------------------------------------------ one sample over all GPUs (strong scaling)
     # Runs last and guarded: a failure here must not cost the numbers above.

@@ -64,7 +64,7 @@ def summarize(path, first_marker, last_marker):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "gemm_trace", "attention_trace", "attention", "attention_bwd", "norm", "gemm_fp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "gemm_trace", "attention_trace", "attention", "attention_bwd", "norm", "gemm_fp8", "gemm_mxfp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
     ap.add_argument("--shape", default="")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--summarize", default="", help="no GPU work: read an `ncu --metrics gpu__time_duration.sum --csv` launch list and "
@@ -268,7 +268,14 @@ def main():
         native.check_status()
         print("ok")
         return
-    if a.op in ("gemm", "gemm_fp8"):
+    if a.op == "gemm_mxfp8":
+        M, N, K = dims or [4608, 3072, 12288]
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        xq, xs = O.mxfp8_quant_rows(x, 128)
+        wq, ws = O.mxfp8_quant_rows(w, 256)
+        fn = lambda: O.gemm_mxfp8(xq, xs, wq, ws)
+    elif a.op in ("gemm", "gemm_fp8"):
         M, N, K = dims or [4608, 3072, 3072]
         x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02

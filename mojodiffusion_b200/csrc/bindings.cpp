@@ -566,6 +566,62 @@ Tensor gate_residual(const Tensor& x, const Tensor& y, const optional<Tensor>& g
            "gate_residual");
   return out;
 }
+// out[rows, cols] = act(x) (dy absent) or dy * act'(x), on row-strided 2-D views; act 0 without dy is a strided copy
+void act_strided(const Tensor& x, const optional<Tensor>& dy, Tensor out, int64_t act) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1 &&
+                  x.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 && x.sizes() == out.sizes() &&
+                  out.device() == x.device(),
+              "act_strided: bf16 [rows, cols] views with a contiguous last dimension");
+  const bool has_dy = dy.has_value() && dy->defined();
+  if (has_dy)
+    TORCH_CHECK(dy->dim() == 2 && dy->stride(1) == 1 && dy->sizes() == x.sizes() && dy->scalar_type() == at::kBFloat16 &&
+                    dy->device() == x.device(),
+                "act_strided: dy must match x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(mdb_act_strided(x.data_ptr(), x.stride(0), has_dy ? dy->data_ptr() : nullptr, has_dy ? dy->stride(0) : 0,
+                           out.data_ptr(), out.stride(0), x.size(0), (int)x.size(1), (int)act, cur_stream()),
+           "act_strided");
+}
+// gated linear unit on row-strided views: out[rows, F] = glu(x[rows, 2F]) (dy absent) or out[rows, 2F] = its gradient
+void glu_strided(const Tensor& x, const optional<Tensor>& dy, Tensor out, int64_t act, bool second) {
+  const bool has_dy = dy.has_value() && dy->defined();
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1 &&
+                  x.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 && x.size(1) % 16 == 0 &&
+                  out.size(0) == x.size(0) && out.size(1) == (has_dy ? x.size(1) : x.size(1) / 2) &&
+                  out.device() == x.device(),
+              "glu_strided: bf16 [rows, 2F] input view, [rows, F] (forward) or [rows, 2F] (gradient) output view");
+  const int64_t F = x.size(1) / 2;
+  if (has_dy)
+    TORCH_CHECK(dy->dim() == 2 && dy->stride(1) == 1 && dy->size(0) == x.size(0) && dy->size(1) == F &&
+                    dy->scalar_type() == at::kBFloat16 && dy->device() == x.device(),
+                "glu_strided: dy [rows, F]");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0,
+              "glu_strided: 16-byte aligned views");
+  if (has_dy) TORCH_CHECK(reinterpret_cast<uintptr_t>(dy->data_ptr()) % 16 == 0, "glu_strided: 16-byte aligned dy");
+  c10::cuda::CUDAGuard guard(x.device());
+  if (has_dy)
+    check_rc(mdb_glu_bwd(x.data_ptr(), dy->data_ptr(), out.data_ptr(), x.size(0), (int)F, (int)x.stride(0),
+                         (int)dy->stride(0), (int)out.stride(0), (int)act, second, cur_stream()),
+             "glu_strided (gradient)");
+  else
+    check_rc(mdb_glu_fwd(x.data_ptr(), out.data_ptr(), x.size(0), (int)F, (int)x.stride(0), (int)out.stride(0), (int)act,
+                         second, cur_stream()),
+             "glu_strided");
+}
+// dy = gate[group] * dout: the gradient of the gated branch of gate_residual
+Tensor gate_mul(const Tensor& y, const Tensor& gate, int64_t rows_per_group, bool tanh_gate) {
+  TORCH_CHECK(y.is_cuda() && y.is_contiguous() && y.scalar_type() == at::kBFloat16, "gate_mul: contiguous bf16");
+  c10::cuda::CUDAGuard guard(y.device());
+  const int64_t D = y.size(-1);
+  TORCH_CHECK(gate.dim() == 2 && gate.stride(1) == 1 && gate.size(1) == D && gate.scalar_type() == at::kBFloat16 &&
+                  gate.device() == y.device(),
+              "gate_mul: gate [groups, D] bf16");
+  Tensor out = at::empty_like(y);
+  check_rc(mdb_gate_residual(nullptr, y.data_ptr(), gate.data_ptr(), out.data_ptr(), y.numel() / D, (int)D,
+                             (int)gate.stride(0), (int)rows_per_group, tanh_gate, cur_stream()),
+           "gate_mul");
+  return out;
+}
 void cfg_euler(Tensor x, const Tensor& vc, const optional<Tensor>& vu, const optional<Tensor>& x_bf16, double dt,
                double s, int64_t mode) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous() && vc.is_contiguous() &&
@@ -913,6 +969,9 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("glu_fwd", &glu_fwd);
   m.def("glu_bwd", &glu_bwd);
   m.def("gate_residual", &gate_residual);
+  m.def("gate_mul", &gate_mul);
+  m.def("act_strided", &act_strided);
+  m.def("glu_strided", &glu_strided);
   m.def("cfg_euler", &cfg_euler);
   m.def("flow_match", &flow_match);
   m.def("mse_loss", &mse_loss);

@@ -53,6 +53,8 @@ int mdb_act_bwd(const void* x, const void* dy, void* dx, const void* bias, long 
 int mdb_glu_fwd(const void* x, void* y, long long rows, int F, int ldx, int ldy, int act, int second, cudaStream_t st);
 int mdb_glu_bwd(const void* x, const void* dy, void* dx, long long rows, int F, int ldx, int lddy, int lddx, int act,
                 int second, cudaStream_t st);
+int mdb_act_strided(const void* x, long long ldx, const void* dy, long long lddy, void* out, long long ldo,
+                    long long rows, int cols, int act, cudaStream_t st);
 int mdb_gate_residual(const void* x, const void* y, const void* gate, void* out, long long rows, int D,
                       int gate_stride, int rows_per_group, int tanh_gate, cudaStream_t st);
 int mdb_cfg_euler(float* x, const void* vc, const void* vu, void* x_bf16, long long n, float dt, float s, int mode,

@@ -105,6 +105,37 @@ __global__ void act_bwd_kernel(const uint4* __restrict__ x, const uint4* __restr
   }
 }
 
+// Column-range pointwise op on row-strided [rows, cols] views (cols % 8 == 0, leading dimensions in elements):
+//   dy == null: out = act(x)   (act 0 = a plain strided copy);   dy != null: out = dy * act'(x).
+// Lets a packed projection buffer be consumed and produced in place of slice / concatenate copies.
+__global__ void act_strided_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                   const __nv_bfloat16* __restrict__ dy, long long lddy, __nv_bfloat16* __restrict__ out,
+                                   long long ldo, long long rows, int cols, int act) {
+  const int cv = cols >> 3;
+  const long long n = rows * cv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cv;
+    const int c = static_cast<int>(i % cv) * 8;
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + r * ldx + c);
+    if (act == 0 && dy == nullptr) {
+      *reinterpret_cast<uint4*>(out + r * ldo + c) = xv;
+      continue;
+    }
+    float v[8];
+    unpack8(xv, v);
+    if (dy) {
+      float g[8];
+      unpack8(*reinterpret_cast<const uint4*>(dy + r * lddy + c), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = g[j] * act_grad(act, v[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = act_fwd(act, v[j]);
+    }
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = pack8(v);
+  }
+}
+
 // gated-linear-unit forward on a [rows, 2F] buffer (first half a, second half b):
 //   act_on_second = 0: y = act(a) * b (SwiGLU);  1: y = a * act(b) (GEGLU)
 __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long rows,
@@ -150,7 +181,8 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_b
   }
 }
 
-// out = x + gate[group] * y   (gate may be null: plain add). tanh_gate: gate -> tanh(gate)
+// out = x + gate[group] * y   (gate may be null: plain add; x may be null: out = gate * y, the gradient of y).
+// tanh_gate: gate -> tanh(gate)
 __global__ void gate_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ y,
                                      const __nv_bfloat16* __restrict__ gate, __nv_bfloat16* __restrict__ out,
                                      long long rows, int D, int gate_stride, int rows_per_group, int tanh_gate) {
@@ -160,7 +192,12 @@ __global__ void gate_residual_kernel(const __nv_bfloat16* __restrict__ x, const 
     const long long r = i / dv;
     const int c = static_cast<int>(i % dv) * 8;
     float a[8], b[8];
-    unpack8(*reinterpret_cast<const uint4*>(x + r * D + c), a);
+    if (x) {
+      unpack8(*reinterpret_cast<const uint4*>(x + r * D + c), a);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = 0.f;
+    }
     unpack8(*reinterpret_cast<const uint4*>(y + r * D + c), b);
     if (gate) {
       float g[8];
@@ -377,6 +414,15 @@ extern "C" int mdb_act_bwd(const void* x, const void* dy, void* dx, const void* 
   if (n == 0) return 0;
   act_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((const uint4*)x, (const uint4*)dy, (uint4*)dx,
                                                        (const uint4*)bias, n / 8, cols > 0 ? cols / 8 : 1, act);
+  return (int)cudaGetLastError();
+}
+extern "C" int mdb_act_strided(const void* x, long long ldx, const void* dy, long long lddy, void* out, long long ldo,
+                               long long rows, int cols, int act, cudaStream_t st) {
+  if (cols % 8 || ldx % 8 || ldo % 8 || (dy && lddy % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dy)) & 15) return -1;
+  if (rows == 0 || cols == 0) return 0;
+  act_strided_kernel<<<grid_for(rows * (cols / 8), 256), 256, 0, st>>>((const bf16*)x, ldx, (const bf16*)dy, lddy,
+                                                                       (bf16*)out, ldo, rows, cols, act);
   return (int)cudaGetLastError();
 }
 extern "C" int mdb_glu_fwd(const void* x, void* y, long long rows, int F, int ldx, int ldy, int act, int second,

@@ -136,10 +136,8 @@ class Flux2SingleBlock(nn.Module):
             mlp = ops.linear_glu(xn, w1[3 * D:], None, "silu", False)
             attn = ops.qkv_attention(qkv, H, Dh, wq, wk, cos, sin)
             return ops.linear(attn, w2[:, :D], None, residual=x, gate=gate, rows_per_group=S, extra=[(mlp, w2[:, D:])])
-        qkv_pre, gate_up = ops.split_cols(self.linear1(xn), 3 * D)
-        attn = ops.qkv_attention(qkv_pre, H, Dh, wq, wk, cos, sin)
-        mlp = ops.glu(gate_up, "silu", False)
-        return self.linear2(torch.cat((attn, mlp), dim=-1), residual=x, gate=gate, rows_per_group=S)
+        mid = ops.packed_attention_mlp(self.linear1(xn), H, Dh, wq, wk, cos, sin, act="silu", gated=False)
+        return self.linear2(mid, residual=x, gate=gate, rows_per_group=S)
 
 
 class _Mod(nn.Module):

@@ -204,10 +204,9 @@ class SingleStreamBlock(nn.Module):
             mlp = ops.linear(xn, w1[3 * D:], b1[3 * D:] if b1 is not None else None, act="gelu_tanh")
             ops.qk_norm_rope(qkv, H, Dh, wq, wk, cos, sin)
         else:
-            qkv_pre, mlp_pre = ops.split_cols(self.linear1(xn), 3 * D)
-            attn = ops.qkv_attention(qkv_pre, H, Dh, wq, wk, cos, sin)
-            mlp = ops.activation(mlp_pre, "gelu_tanh")
-            return self.linear2(torch.cat((attn, mlp), dim=-1), residual=x, gate=gate, rows_per_group=S)
+            # training path: attention and the activated MLP half land in one buffer, as one autograd node
+            mid = ops.packed_attention_mlp(self.linear1(xn), H, Dh, wq, wk, cos, sin, act="gelu_tanh")
+            return self.linear2(mid, residual=x, gate=gate, rows_per_group=S)
         q = qkv[..., 0:D].unflatten(-1, (H, Dh))
         k = qkv[..., D:2 * D].unflatten(-1, (H, Dh))
         v = qkv[..., 2 * D:3 * D].unflatten(-1, (H, Dh))

@@ -19,7 +19,7 @@ from .reference import act_code
 __all__ = [
     "linear", "linear_glu", "lora_linear", "attention", "norm_modulate", "qk_norm_rope", "rope_table", "activation",
     "glu", "gate_residual", "cfg_euler", "flow_match", "mse_loss", "randn", "fp8_quant_rows", "fp8_dequant", "mx_quant", "mx_dequant", "mxfp8_quant_rows", "gemm_mxfp8", "MXFP8Weight",
-    "fp8_linear", "qkv_attention", "split_cols",
+    "fp8_linear", "qkv_attention", "split_cols", "packed_attention_mlp",
 ]
 
 
@@ -100,7 +100,7 @@ class _LoraLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x2, w, bias, A, B, scale):
         t = _gemm_skinny(x2, A)                    # [M, r]
-        Bs = (B.float() * scale).to(B.dtype)       # [N, r]
+        Bs = B if scale == 1.0 else (B.float() * scale).to(B.dtype)       # [N, r]
         y = _gemm([x2, t], [w, Bs], bias=bias)
         ctx.save_for_backward(x2, w, A, B, t, Bs)
         ctx.scale = scale
@@ -362,6 +362,78 @@ def qkv_attention(qkv: torch.Tensor, H: int, Dh: int, wq, wk, cos, sin, split: i
     return attention(q, k, v, scale).reshape(B, S, D)
 
 
+class _PackedAttnMlpFn(torch.autograd.Function):
+    """[B, S, 3D + F] projection buffer (q | k | v | mlp) -> [B, S, D + F] (attention | act(mlp)) as ONE autograd node.
+
+    The attention output and the activated MLP half are written straight into the two column ranges of the result
+    (the input of the block's second projection), and the backward writes dq | dk | dv | dmlp into the column ranges
+    of one gradient buffer, so no slice copy, concatenation or zero fill surrounds the attention of a single-stream
+    block in a training step. The only copy is the q | k | v range into the buffer that is normalised in place (the
+    RMSNorm backward needs the projection as it was)."""
+
+    @staticmethod
+    def forward(ctx, h, wq, wk, cos, sin, H, Dh, act, interleaved, scale, eps, glu):
+        B, S, W = h.shape
+        D = H * Dh
+        F_ = (W - 3 * D) // 2 if glu is not None else W - 3 * D
+        o_ = _ops()
+        h2 = h.view(B * S, W)
+        post = torch.empty(B, S, 3 * D, dtype=h.dtype, device=h.device)
+        o_.act_strided(h2[:, :3 * D], None, post.view(B * S, 3 * D), 0)
+        o_.qk_norm_rope(post, wq, wk, cos, sin, H, Dh, 0, D, eps, interleaved, False, True, 0, 0)
+        q, k, v = (post[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3))
+        out = torch.empty(B, S, D + F_, dtype=h.dtype, device=h.device)
+        _, lse = o_.attention_fwd(q, k, v, scale, None, True, out[..., :D].unflatten(-1, (H, Dh)), [], [], [])
+        if glu is not None:
+            o_.glu_strided(h2[:, 3 * D:], None, out.view(B * S, D + F_)[:, D:], act, glu)
+        else:
+            o_.act_strided(h2[:, 3 * D:], None, out.view(B * S, D + F_)[:, D:], act)
+        ctx.save_for_backward(h, post, out, lse, wq, wk, cos, sin)
+        ctx.cfg = (H, Dh, act, interleaved, scale, eps, glu)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        h, post, out, lse, wq, wk, cos, sin = ctx.saved_tensors
+        H, Dh, act, interleaved, scale, eps, glu = ctx.cfg
+        B, S, W = h.shape
+        D = H * Dh
+        from . import attention_bwd
+        o_ = _ops()
+        if dout.stride(-1) != 1 or dout.stride(-2) % 8 or dout.data_ptr() % 16:
+            dout = dout.contiguous()
+        dh = torch.empty_like(h)
+        q, k, v = (post[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3))
+        outs = [dh[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3)]
+        attention_bwd.backward(q, k, v, out[..., :D].unflatten(-1, (H, Dh)), lse, dout[..., :D].unflatten(-1, (H, Dh)),
+                               scale, None, outs)
+        o_.qk_norm_rope_bwd(dh[..., :3 * D], h[..., :3 * D], wq, wk, cos, sin, H, Dh, 0, D, eps, interleaved, True, 0, 0)
+        x_mlp, d_mlp, g_mlp = h.view(B * S, W)[:, 3 * D:], dout.reshape(B * S, -1)[:, D:], dh.view(B * S, W)[:, 3 * D:]
+        if glu is not None:
+            o_.glu_strided(x_mlp, d_mlp, g_mlp, act, glu)
+        else:
+            o_.act_strided(x_mlp, d_mlp, g_mlp, act)
+        return (dh,) + (None,) * 11
+
+
+def packed_attention_mlp(h: torch.Tensor, H: int, Dh: int, wq, wk, cos, sin, act="gelu_tanh", interleaved: bool = True,
+                         scale: Optional[float] = None, eps: float = 1e-6, gated: Optional[bool] = None) -> torch.Tensor:
+    """The middle of a single-stream block: h [B, S, 3*H*Dh + F] holds (q | k | v | mlp) of one fused projection; returns
+    [B, S, H*Dh + F] = (attention(QK-RMSNorm + RoPE (q, k), v) | act(mlp)), the input of the block's output projection.
+    With ``gated`` set (False: act(a) * b, True: a * act(b)) the MLP range is 2F wide (a | b) and contributes F columns."""
+    B, S, W = h.shape
+    D = H * Dh
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(Dh)
+    if (native.use_native(h) and torch.is_grad_enabled() and h.requires_grad and h.dtype == torch.bfloat16
+            and h.is_contiguous() and (W - 3 * D) % 16 == 0 and W > 3 * D):
+        return _PackedAttnMlpFn.apply(h, wq, wk, cos, sin, H, Dh, act_code(act), interleaved, scale, eps,
+                                      None if gated is None else bool(gated))
+    qkv, mlp = split_cols(h, 3 * D)
+    attn = qkv_attention(qkv, H, Dh, wq, wk, cos, sin, interleaved=interleaved, scale=scale, eps=eps)
+    mlp = activation(mlp, act) if gated is None else glu(mlp, act, bool(gated))
+    return torch.cat((attn, mlp), dim=-1)
+
+
 class _SplitColsFn(torch.autograd.Function):
     """[.., a + b] -> contiguous ([.., a], [.., b]); the backward is one concatenation (no zero-filled buffers)."""
 
@@ -578,11 +650,10 @@ class _GateResFn(torch.autograd.Function):
             return dx, dout, None, None, None
         D = y.shape[-1]
         d2 = dout.reshape(-1, D)
-        g = torch.tanh(gate.float()) if tanh_gate else gate.float()
-        ge = ref._group_expand(g, d2.shape[0], rpg)
-        dy = (d2.float() * ge).to(dout.dtype).reshape(dout.shape)
+        dy = _ops().gate_mul(dout.contiguous(), gate, rpg, tanh_gate)
         dgate = None
         if ctx.needs_input_grad[2]:
+            g = torch.tanh(gate.float()) if tanh_gate else gate.float()
             prod = (d2.float() * y.reshape(-1, D).float())
             groups = gate.shape[0]
             if groups == 1:

@@ -526,6 +526,60 @@ def test_packed_qkv_attention_matches_composed_ops():
     assert a.is_contiguous() and torch.equal(h.grad[..., :3 * D], torch.full_like(a, 2)) and torch.equal(h.grad[..., 3 * D:], torch.full_like(b, 3))
 
 
+def test_packed_attention_mlp_matches_composed_ops_and_fp32_reference():
+    """The middle of a single-stream block as one node (strided column kernels, attention writing into the joint buffer):
+    forward and gradient equal the composed ops and agree with the fp32 math of the same expression."""
+    B, S, H, Dh, F_ = 2, 256, 4, 128, 1024
+    D = H * Dh
+    h0 = _rand(B, S, 3 * D + F_, seed=51)
+    wq, wk = (1.0 + 0.1 * _rand(Dh, seed=52 + i) for i in range(2))
+    pos = torch.stack([torch.zeros(S), torch.arange(S).float(), torch.arange(S).float() * 0.5], 1).to(DEV)
+    cos, sin = O.rope_table(pos, [16, 56, 56], 10000.0)
+    go = _rand(B, S, D + F_, seed=55)
+    outs, grads = [], []
+    for packed in (True, False):
+        h = h0.clone().requires_grad_(True)
+        if packed:
+            o = O.packed_attention_mlp(h, H, Dh, wq, wk, cos, sin, act="gelu_tanh")
+        else:
+            qkv, mlp = O.split_cols(h, 3 * D)
+            o = torch.cat((O.qkv_attention(qkv, H, Dh, wq, wk, cos, sin), O.activation(mlp, "gelu_tanh")), -1)
+        o.backward(go)
+        outs.append(o.detach())
+        grads.append(h.grad.detach())
+    assert torch.equal(outs[0], outs[1])
+    _check(grads[0], grads[1].float(), cos=0.99999, rel=1e-2, name="packed dh")
+    # fp32 oracle of the same expression on the reference ops
+    hf = h0.float().cpu().requires_grad_(True)
+    of = O.packed_attention_mlp(hf, H, Dh, wq.float().cpu(), wk.float().cpu(), cos.cpu(), sin.cpu(), act="gelu_tanh")
+    of.backward(go.float().cpu())
+    _check(outs[0], of.detach().to(DEV), cos=0.9999, rel=3e-2, name="packed forward vs fp32")
+    _check(grads[0], hf.grad.to(DEV), cos=0.999, rel=6e-2, name="packed dh vs fp32")
+    # gated (SwiGLU) MLP half: [q | k | v | gate | up] -> [attention | silu(gate) * up]
+    hg0 = _rand(B, S, 3 * D + 2 * F_, seed=62)
+    res = []
+    for packed in (True, False):
+        h = hg0.clone().requires_grad_(True)
+        if packed:
+            o = O.packed_attention_mlp(h, H, Dh, wq, wk, cos, sin, act="silu", gated=False)
+        else:
+            qkv, mlp = O.split_cols(h, 3 * D)
+            o = torch.cat((O.qkv_attention(qkv, H, Dh, wq, wk, cos, sin), O.glu(mlp, "silu", False)), -1)
+        o.backward(go)
+        res.append((o.detach(), h.grad.detach()))
+    assert torch.equal(res[0][0], res[1][0])
+    _check(res[0][1], res[1][1].float(), cos=0.99999, rel=1e-2, name="packed gated dh")
+    # strided copy / activation kernels against torch on odd row strides
+    x = _rand(96, 640, seed=60)
+    dst = torch.zeros(96, 512, dtype=torch.bfloat16, device=DEV)
+    torch.ops.mdb200.act_strided(x[:, 128:384], None, dst[:, 64:320], 0)
+    assert torch.equal(dst[:, 64:320], x[:, 128:384]) and float(dst[:, :64].abs().sum()) == 0 and float(dst[:, 320:].abs().sum()) == 0
+    # gate_mul = the gated branch's gradient
+    gate = _rand(2, 640, seed=61)
+    gm = torch.ops.mdb200.gate_mul(x, gate, 48, False)
+    _check(gm, x.float() * gate.float().repeat_interleave(48, 0), rel=1e-2, name="gate_mul")
+
+
 def test_adamw8bit_kernel_matches_blockwise_reference():
     """The one-kernel 8-bit AdamW (block-wise code-book moments) against the same optimizer stepped on the CPU with the
     tensor-op de-quantise / update / re-quantise sequence."""
