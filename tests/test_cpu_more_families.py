@@ -89,3 +89,42 @@ def test_both_families_train_through_the_family_trainer():
         assert slots[0].key.startswith("transformer.layers.0." if mid == "ernie-image" else "diffusion_model.net.blocks.0.")
         sig = schedule_for(man, man.schedule.steps, 1024)
         assert len(sig) == man.schedule.steps + 1 and sig[0] == 1.0 and sig[-1] == 0.0
+
+
+def test_asymflux2_velocity_oklab_and_sampler():
+    """AsymFLUX.2: the one-projection velocity equals the two-branch statement, Oklab round-trips, the gamut clamp and the
+    orthogonal guidance behave as defined, and the pixel-space sampler runs on a tiny transformer."""
+    import dataclasses
+    from mojodiffusion_b200.models import asymflux2 as A
+    from mojodiffusion_b200.models.flux2 import Flux2DiT, tiny_flux2_config
+    torch.manual_seed(0)
+    B, N, D, R = 2, 16, 768, 32
+    P = torch.linalg.qr(torch.randn(D, R))[0]
+    ua, xt = torch.randn(B, N, D), torch.randn(B, N, D)
+    cal = A.compute_calibration(0.7, 0.3)
+    assert abs(cal.k - 1.0 / (0.3 + 0.7 * 0.7)) < 1e-12 and abs(cal.cal_timestep - 0.7 * cal.k) < 1e-12
+    sub = lambda z: (z @ P) @ P.t()
+    sk = cal.s * cal.k
+    want = sk * sub(ua) + (1 - sk) / cal.sigma * sub(xt) + ((xt - sub(xt)) + cal.s * (ua - sub(ua))) / cal.sigma
+    assert (A.asymflow_velocity(ua, xt, cal, P) - want).abs().max() < 1e-4
+    tiny = A.compute_calibration(1e-7, 0.3)                          # sigma below the floor is clamped
+    assert torch.isfinite(A.asymflow_velocity(ua, xt, tiny, P)).all()
+    rgb = torch.rand(2, 3, 8, 8) * 2 - 1
+    assert (A.oklab_decode(A.oklab_encode(rgb)) - rgb).abs().max() < 1e-3
+    white = A.oklab_encode(torch.ones(1, 3, 1, 1))
+    assert abs(float(white[0, 0]) * A.OKLAB_STD + A.OKLAB_MEAN[0] - 1.0) < 1e-3       # L of white is 1
+    x = torch.randn(1, 3, 8, 8) * 3
+    v = A.clamp_denoised_oklab(x, torch.zeros_like(x), 0.5)
+    den = A.oklab_decode(x - v * 0.5)
+    assert den.min() >= -1 - 1e-4 and den.max() <= 1 + 1e-4
+    pos, neg, par = torch.randn(2, 3, 4, 4), torch.randn(2, 3, 4, 4), torch.randn(2, 3, 4, 4)
+    b = A.guidance_bias(pos, neg, 4.0, 1.0, par)
+    assert (b * par).mean((1, 2, 3)).abs().max() < 1e-5              # fully orthogonalised
+    assert torch.equal(A.guidance_bias(pos, neg, 4.0, 0.0, par), (pos - neg) * 3.0)
+    sig = A.sigma_schedule(4, A.dynamic_shift(1024, 1024))
+    assert abs(A.dynamic_shift(1024, 1024) - 17.0) < 1e-9 and abs(A.dynamic_shift(2048, 2048) - 34.0) < 1e-9
+    assert sig[0] == 1.0 and sig[-1] == 0.0 and all(a > b for a, b in zip(sig, sig[1:]))
+    cfg = dataclasses.replace(tiny_flux2_config(), in_channels=768)
+    m = A.AsymFlux2(Flux2DiT(cfg, torch.float32).init_weights(0), P, 0.3)
+    img = m.sample(torch.randn(1, 3, 32, 32), torch.randn(1, 8, cfg.context_dim), torch.randn(1, 8, cfg.context_dim), steps=3)
+    assert img.shape == (1, 3, 32, 32) and torch.isfinite(img).all() and img.abs().max() <= 1 + 1e-4
