@@ -150,7 +150,11 @@ class WanDiT(nn.Module):
         x = torch.arange(w, device=device, dtype=torch.float32)[None, None, :].expand(f, h, w)
         return torch.stack((t, y, x), -1).reshape(-1, 3)
 
-    def forward(self, z, text, timesteps, text_len: Optional[torch.Tensor] = None):
+    def _control_hints(self, x, ctx, e0, cos, sin, text_len, control):
+        raise NotImplementedError("this model takes no control input")
+
+    def forward(self, z, text, timesteps, text_len: Optional[torch.Tensor] = None, control: Optional[torch.Tensor] = None,
+                control_scale: float = 1.0):
         cfg = self.cfg
         B, C, F_, Hh, Ww = z.shape
         pt, ph, pw = cfg.patch
@@ -166,12 +170,15 @@ class WanDiT(nn.Module):
         tx = self.text_embedding
         ctx = tx["2"](tx["0"](text.to(dt), act="gelu_tanh"))
         ckpt = self.gradient_checkpointing and torch.is_grad_enabled()
-        for blk in self.blocks:
+        hints = self._control_hints(x, ctx, e0, cos, sin, text_len, control) if control is not None else {}
+        for i, blk in enumerate(self.blocks):
             if ckpt:
                 x = torch.utils.checkpoint.checkpoint(blk, x, ctx, e0, cos, sin, text_len, use_reentrant=False,
                                                       preserve_rng_state=False)
             else:
                 x = blk(x, ctx, e0, cos, sin, text_len)
+            if i in hints:
+                x = x + hints[i] * control_scale
         m = (self.head.modulation.float() + e[:, None].float()).to(x.dtype)                         # [B, 2, D]
         out = self.head.head(ops.norm_modulate(x, scale=m[:, 1], shift=m[:, 0], eps=1e-6))
         # token vector is (pt, ph, pw, channel): channel innermost
@@ -187,4 +194,77 @@ class WanDiT(nn.Module):
                     prm.copy_((torch.randn(prm.shape, generator=g) * std).to(prm.dtype))
                 if n.endswith("norm_q.weight") or n.endswith("norm_k.weight") or n.endswith("norm3.weight"):
                     prm.fill_(1.0)
+        return self
+
+
+# ---- Wan-VACE: ControlNet-style conditioning on the Wan stack ----------------------------------------------------------
+@dataclass
+class WanVaceConfig(WanConfig):
+    vace_in_dim: int = 96          # control latent + mask channels
+    vace_blocks: int = 8           # control block i feeds base layer 2 i
+
+
+def wan21_vace_14b_config() -> WanVaceConfig:
+    return WanVaceConfig(in_dim=16, out_dim=16, dim=5120, heads=40, ffn_dim=13824, depth=40, name="wan2.1-vace-14b")
+
+
+def tiny_wan_vace_config() -> WanVaceConfig:
+    return WanVaceConfig(in_dim=8, out_dim=8, dim=128, heads=2, ffn_dim=256, depth=4, text_dim=96, freq_dim=64,
+                         vace_in_dim=12, vace_blocks=2, name="tiny-wan-vace")
+
+
+class _VacePatch(nn.Module):
+    def __init__(self, cfg: WanVaceConfig, dtype, device):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(cfg.dim, cfg.vace_in_dim, *cfg.patch, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(cfg.dim, dtype=dtype, device=device))
+
+
+class WanVaceBlock(WanBlock):
+    """A Wan block of the control branch: block 0 mixes the control embedding into the base tokens through ``before_proj``,
+    every block emits its hint through ``after_proj`` (both zero-initialised, so an untrained branch changes nothing)."""
+
+    def __init__(self, cfg: WanVaceConfig, first: bool, dtype, device):
+        super().__init__(cfg, dtype, device)
+        self.before_proj = Linear(cfg.dim, cfg.dim, True, dtype, device) if first else None
+        self.after_proj = Linear(cfg.dim, cfg.dim, True, dtype, device)
+
+
+class WanVaceDiT(WanDiT):
+    """Wan DiT + VACE control branch. ``forward(z, text, t, control=[B, vace_in_dim, F, H, W], control_scale=s)``: the
+    control latent gets its own patch embedding, runs through ``vace_blocks`` Wan blocks (the running hidden state is
+    carried block to block) and hint i is added, times ``s``, after base layer 2 i
+    (serenitymojo/models/dit/wan_vace_dit.mojo:14-33,118-200)."""
+
+    def __init__(self, cfg: WanVaceConfig, dtype=torch.bfloat16, device=None):
+        super().__init__(cfg, dtype, device)
+        self.vace_patch_embedding = _VacePatch(cfg, dtype, device)
+        self.vace_blocks = nn.ModuleList([WanVaceBlock(cfg, i == 0, dtype, device) for i in range(cfg.vace_blocks)])
+
+    def vace_layer(self, i: int) -> int:
+        return 2 * i
+
+    def _control_hints(self, x, ctx, e0, cos, sin, text_len, control):
+        cfg = self.cfg
+        pt, ph, pw = cfg.patch
+        tok = patchify_3d(control, pt, ph, pw)
+        c = ops.linear(tok.to(x.dtype), self.vace_patch_embedding.weight.flatten(1), self.vace_patch_embedding.bias)
+        if c.shape[1] < x.shape[1]:                       # shorter control clip: zero tokens up to the base length
+            c = torch.nn.functional.pad(c, (0, 0, 0, x.shape[1] - c.shape[1]))
+        hints = {}
+        for i, blk in enumerate(self.vace_blocks):
+            if blk.before_proj is not None:
+                c = (blk.before_proj(c).float() + x.float()).to(x.dtype)
+            c = blk(c, ctx, e0, cos, sin, text_len)
+            hints[self.vace_layer(i)] = blk.after_proj(c)
+        return hints
+
+    def init_weights(self, seed: int = 0, std: float = 0.02):
+        super().init_weights(seed, std)
+        with torch.no_grad():
+            for blk in self.vace_blocks:
+                for lin in (blk.before_proj, blk.after_proj):
+                    if lin is not None:
+                        lin.weight.zero_()
+                        lin.bias.zero_()
         return self

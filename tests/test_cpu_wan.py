@@ -93,3 +93,31 @@ def test_wan_sizes_and_keys():
         assert k in sd, k
     n = sum(v.numel() for v in sd.values())
     assert 4.6e9 < n < 5.4e9, n
+
+
+def test_wan_vace_control_branch():
+    """Wan-VACE: an untrained (zero-initialised) control branch leaves the output unchanged, a trained one changes it in
+    proportion to ``control_scale``, hints land after base layers 0, 2, ..., and the checkpoint keys carry the control names."""
+    import torch
+    from mojodiffusion_b200.models.wan import WanVaceDiT, tiny_wan_vace_config, wan21_vace_14b_config
+    cfg = tiny_wan_vace_config()
+    m = WanVaceDiT(cfg, torch.float32).init_weights(0)
+    z, txt, t = torch.randn(1, 8, 2, 8, 8), torch.randn(1, 6, 96), torch.tensor([0.5])
+    c = torch.randn(1, cfg.vace_in_dim, 2, 8, 8)
+    with torch.no_grad():
+        base = m(z, txt, t)
+        assert torch.equal(m(z, txt, t, control=c), base)
+        for blk in m.vace_blocks:
+            blk.after_proj.weight.normal_(0, 0.05)
+        m.vace_blocks[0].before_proj.weight.normal_(0, 0.05)
+        full = m(z, txt, t, control=c)
+        assert (full - base).abs().max() > 1e-3
+        assert torch.equal(m(z, txt, t, control=c, control_scale=0.0), base)
+        short = m(z, txt, t, control=c[:, :, :1])                      # a shorter control clip is zero-padded in tokens
+        assert short.shape == base.shape and torch.isfinite(short).all()
+    keys = set(m.state_dict())
+    assert {"vace_patch_embedding.weight", "vace_blocks.0.before_proj.weight", "vace_blocks.1.after_proj.bias"} <= keys
+    assert "vace_blocks.1.before_proj.weight" not in keys
+    assert [m.vace_layer(i) for i in range(cfg.vace_blocks)] == [0, 2]
+    big = wan21_vace_14b_config()
+    assert (big.dim, big.depth, big.heads, big.head_dim, big.vace_in_dim, big.vace_blocks) == (5120, 40, 40, 128, 96, 8)
