@@ -290,72 +290,95 @@ norm_modulate_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 //   interleaved: pairs (2i, 2i+1) use angle i. half-split: pairs (i, i + Dh/2) use angle i.
 //   inverse=1 applies the transposed rotation and skips the norm (backward of the rotation).
 // ---------------------------------------------------------------------------------------------
-template <int DH>
+template <int DH, int HPW>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kernel(__nv_bfloat16* __restrict__ buf, const __nv_bfloat16* __restrict__ wq,
                     const __nv_bfloat16* __restrict__ wk, const float* __restrict__ cosv,
                     const float* __restrict__ sinv, long long tokens, int tokens_per_batch, int H, int row_stride,
                     int q_off, int k_off, float eps, int interleaved, int inverse, int do_norm, int rope_tokens_start,
                     long long batch_stride, int pos_offset) {
+  // One warp owns HPW consecutive heads of one token's q or k: all HPW row loads are issued before any arithmetic
+  // (the kernel is latency bound with a single 8-byte load per lane in flight), and the norm weights and the rotary
+  // row, which are the same for every head of a token, are read once per warp.
   constexpr int EPL = DH / 32;  // elements per lane
   const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  const long long total = tokens * H * 2;
+  const int groups = H / HPW;
+  const long long total = tokens * groups * 2;
   if (warp_global >= total) return;
   const int part = static_cast<int>(warp_global % 2);
-  const int head = static_cast<int>((warp_global / 2) % H);
-  const long long tok = warp_global / (2 * H);
+  const int head0 = static_cast<int>((warp_global / 2) % groups) * HPW;
+  const long long tok = warp_global / (2 * groups);
   const long long bidx = tok / tokens_per_batch;
   const int tin = static_cast<int>(tok % tokens_per_batch);
   __nv_bfloat16* p = buf + bidx * batch_stride + static_cast<long long>(tin) * row_stride + (part ? k_off : q_off) +
-                     head * DH;
+                     head0 * DH + lane * EPL;
   const __nv_bfloat16* w = part ? wk : wq;
   const int pos = tin + pos_offset;
-  float v[EPL];
-  // lane owns elements [lane*EPL, lane*EPL+EPL) for interleaved, and for half-split the pair
-  // partner (i + DH/2) lives in lane + 16: handled by a shuffle.
-  load_vec<EPL>(p + lane * EPL, v);
-  if (do_norm && !inverse) {
-    float ss = 0.f;
+  float v[HPW][EPL];
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) ss += v[j] * v[j];
-    ss = warp_sum(ss);
-    const float r = rsqrtf(ss / DH + eps);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      float wj = w ? __bfloat162float(w[lane * EPL + j]) : 1.f;
-      // round to bf16 after the norm like an unfused bf16 pipeline would
-      v[j] = __bfloat162float(__float2bfloat16_rn(v[j] * r * wj));
-    }
-  }
-  if (cosv != nullptr && pos >= rope_tokens_start) {
+  for (int h = 0; h < HPW; ++h) load_vec<EPL>(p + h * DH, v[h]);
+  const bool rope = cosv != nullptr && pos >= rope_tokens_start;
+  // lane owns elements [lane*EPL, lane*EPL+EPL) for interleaved; for half-split the pair partner (i + DH/2) lives in
+  // lane + 16 and comes by shuffle
+  const bool upper = lane >= 16;
+  float c[EPL], sn[EPL];
+  if (rope) {
     const float* cr = cosv + static_cast<size_t>(pos) * (DH / 2);
     const float* sr = sinv + static_cast<size_t>(pos) * (DH / 2);
     const float sgn = inverse ? -1.f : 1.f;
-    if (interleaved) {
 #pragma unroll
-      for (int j = 0; j < EPL; j += 2) {
-        const int pi = (lane * EPL + j) >> 1;
-        const float c = cr[pi], s = sr[pi] * sgn;
-        const float a = v[j], b = v[j + 1];
-        v[j] = a * c - b * s;
-        v[j + 1] = a * s + b * c;
-      }
-    } else {
-      // half-split: element e < DH/2 pairs with e + DH/2
-      const bool upper = lane >= 16;
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-        const int e = lane * EPL + j;
-        const int pi = upper ? e - DH / 2 : e;
-        const float c = cr[pi], s = sr[pi] * sgn;
-        // lower: a*c - b*s ; upper: b*c + a*s  (a = lower element, b = upper element)
-        v[j] = upper ? (v[j] * c + other * s) : (v[j] * c - other * s);
+    for (int j = 0; j < EPL; ++j) {
+      const int e = lane * EPL + j;
+      const int pi = interleaved ? (e >> 1) : (upper ? e - DH / 2 : e);
+      if (!interleaved || (j & 1) == 0) {   // an interleaved pair (j, j + 1) shares entry j
+        c[j] = cr[pi];
+        sn[j] = sr[pi] * sgn;
+      } else {
+        c[j] = 0.f;
+        sn[j] = 0.f;
       }
     }
   }
-  store_vec<EPL>(p + lane * EPL, v);
+  float wv[EPL];
+  if (do_norm && !inverse) {
+    if (w) load_vec<EPL>(w + lane * EPL, wv);
+    else {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) wv[j] = 1.f;
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < HPW; ++h) {
+    if (do_norm && !inverse) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) ss += v[h][j] * v[h][j];
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / DH + eps);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j)  // round to bf16 after the norm like an unfused bf16 pipeline would
+        v[h][j] = __bfloat162float(__float2bfloat16_rn(v[h][j] * r * wv[j]));
+    }
+    if (rope) {
+      if (interleaved) {
+#pragma unroll
+        for (int j = 0; j < EPL; j += 2) {
+          const float a = v[h][j], b = v[h][j + 1];
+          v[h][j] = a * c[j] - b * sn[j];
+          v[h][j + 1] = a * sn[j] + b * c[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[h][j], 16);
+          // lower: a*c - b*s ; upper: b*c + a*s  (a = lower element, b = upper element)
+          v[h][j] = upper ? (v[h][j] * c[j] + other * sn[j]) : (v[h][j] * c[j] - other * sn[j]);
+        }
+      }
+    }
+    store_vec<EPL>(p + h * DH, v[h]);
+  }
 }
 
 // Backward of the kernel above, in place on the gradient buffer (same packing as the forward buffer):
@@ -513,25 +536,27 @@ extern "C" int mdb_qk_norm_rope(void* buf, const void* wq, const void* wk, const
                                 long long batch_stride, int pos_offset, cudaStream_t st) {
   if (tokens <= 0) return 0;
   if ((row_stride % 8) || (q_off % 8) || (k_off % 8) || (batch_stride % 8)) return -1;
-  const long long warps = tokens * H * 2;
+  if ((reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk)) & 15) return -1;   // vector loads of the weights
+  const int hpw = (Dh == 256) ? ((H % 2 == 0) ? 2 : 1) : ((H % 4 == 0) ? 4 : (H % 2 == 0) ? 2 : 1);   // heads per warp
+  const long long warps = tokens * (H / hpw) * 2;
   const long long blocks = (warps * 32 + 255) / 256;
   auto B = reinterpret_cast<__nv_bfloat16*>(buf);
   auto WQ = reinterpret_cast<const __nv_bfloat16*>(wq);
   auto WK = reinterpret_cast<const __nv_bfloat16*>(wk);
-  if (Dh == 128)
-    qk_norm_rope_kernel<128><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
-        B, WQ, WK, cosv, sinv, tokens, tokens_per_batch, H, row_stride, q_off, k_off, eps, interleaved, inverse,
-        do_norm, rope_start, batch_stride, pos_offset);
-  else if (Dh == 64)
-    qk_norm_rope_kernel<64><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
-        B, WQ, WK, cosv, sinv, tokens, tokens_per_batch, H, row_stride, q_off, k_off, eps, interleaved, inverse,
-        do_norm, rope_start, batch_stride, pos_offset);
-  else if (Dh == 256)
-    qk_norm_rope_kernel<256><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
-        B, WQ, WK, cosv, sinv, tokens, tokens_per_batch, H, row_stride, q_off, k_off, eps, interleaved, inverse,
-        do_norm, rope_start, batch_stride, pos_offset);
-  else
+#define MDB_QKNR(DH_, HPW_)                                                                                          \
+  qk_norm_rope_kernel<DH_, HPW_><<<static_cast<unsigned>(blocks), 256, 0, st>>>(                                      \
+      B, WQ, WK, cosv, sinv, tokens, tokens_per_batch, H, row_stride, q_off, k_off, eps, interleaved, inverse, do_norm, \
+      rope_start, batch_stride, pos_offset)
+  if (Dh == 128) {
+    if (hpw == 4) MDB_QKNR(128, 4); else if (hpw == 2) MDB_QKNR(128, 2); else MDB_QKNR(128, 1);
+  } else if (Dh == 64) {
+    if (hpw == 4) MDB_QKNR(64, 4); else if (hpw == 2) MDB_QKNR(64, 2); else MDB_QKNR(64, 1);
+  } else if (Dh == 256) {
+    if (hpw == 2) MDB_QKNR(256, 2); else MDB_QKNR(256, 1);
+  } else {
     return -2;
+  }
+#undef MDB_QKNR
   return static_cast<int>(cudaGetLastError());
 }
 
