@@ -128,3 +128,83 @@ def test_asymflux2_velocity_oklab_and_sampler():
     m = A.AsymFlux2(Flux2DiT(cfg, torch.float32).init_weights(0), P, 0.3)
     img = m.sample(torch.randn(1, 3, 32, 32), torch.randn(1, 8, cfg.context_dim), torch.randn(1, 8, cfg.context_dim), steps=3)
     assert img.shape == (1, 3, 32, 32) and torch.isfinite(img).all() and img.abs().max() <= 1 + 1e-4
+
+
+def test_ideogram4_matches_plain_torch_statement():
+    """Ideogram-4: the model equals a plain-torch statement of the published forward (rotate-half rotary with full-width
+    interleaved three-axis tables, separate w1 / w3, masks from the indicator), and reference checkpoint keys load."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models.ideogram4 import (IND_IMAGE, IND_TEXT, Ideogram4DiT, mrope_table, remap_ideogram4_keys,
+                                                     scalar_embedding, tiny_ideogram4_config)
+    torch.manual_seed(0)
+    cfg = tiny_ideogram4_config()
+    m = Ideogram4DiT(cfg, torch.float32).init_weights(3)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    # a checkpoint in reference naming: w1 / w3 separate
+    ref_sd = {}
+    for k, v in m.state_dict().items():
+        if k.endswith("feed_forward.w13.weight"):
+            ref_sd[k.replace("w13", "w1")], ref_sd[k.replace("w13", "w3")] = v[:cfg.mlp_hidden].clone(), v[cfg.mlp_hidden:].clone()
+        else:
+            ref_sd[k] = v.clone()
+    m2 = Ideogram4DiT(cfg, torch.float32)
+    m2.load_state_dict(remap_ideogram4_keys(ref_sd))
+    L, D, H, Dh = 12, cfg.hidden, cfg.heads, cfg.head_dim
+    ind = torch.tensor([[3] * 4 + [2] * 6 + [0] * 2])
+    pos = torch.stack([torch.zeros(L), torch.arange(L).float() * 7.0, torch.arange(L).float() * 3.0], 1)
+    x, llm, t = torch.randn(1, L, cfg.in_channels), torch.randn(1, L, cfg.llm_dim), torch.tensor([0.4])
+    got = m2(x, llm, t, ind, pos)
+
+    sd = ref_sd
+    lin = lambda v, name, bias=True: F.linear(v, sd[name + ".weight"], sd.get(name + ".bias") if bias else None)
+    rms = lambda v, w, eps: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w
+    half = Dh // 2
+    # full-width tables, slot d -> axis by the interleave rule
+    inv = 1.0 / (cfg.theta ** (torch.arange(0, Dh, 2).float() / Dh))
+    fr = [pos[:, a:a + 1] * inv[None] for a in range(3)]
+    f = fr[0].clone()
+    for d in range(half):
+        if d % 3 == 1 and d < cfg.mrope_section[1] * 3:
+            f[:, d] = fr[1][:, d]
+        elif d % 3 == 2 and d < cfg.mrope_section[2] * 3:
+            f[:, d] = fr[2][:, d]
+    emb = torch.cat((f, f), -1).double()
+    cosf, sinf = emb.cos().float()[None, :, None], emb.sin().float()[None, :, None]
+    rot = lambda v: torch.cat((-v[..., half:], v[..., :half]), -1)
+    c0, s0 = mrope_table(pos, Dh, cfg.mrope_section, cfg.theta)
+    assert (c0 - cosf[0, :, 0, :half]).abs().max() < 1e-4 and (s0 - sinf[0, :, 0, :half]).abs().max() < 1e-4
+    far = torch.tensor([[65536.0, 65536.0, 65536.0]])                      # large positions: the angle is reduced in float64
+    cf, _ = mrope_table(far, Dh, cfg.mrope_section, cfg.theta)
+    inv32 = torch.exp(-(torch.arange(half).float() / half) * math.log(cfg.theta))
+    assert (cf[0] - (far[0, 0] * inv32).double().cos().float()).abs().max() < 1e-6
+    # conditioning
+    hh = D // 2
+    fq = torch.exp(-torch.arange(hh).float() * math.log(1e4) / (hh - 1))
+    a = t[:, None] * 1e4 * fq[None]
+    te = torch.cat((a.sin(), a.cos()), -1)
+    assert (te - scalar_embedding(t, D)).abs().max() < 1e-3
+    c = lin(F.silu(lin(te, "t_embedding.mlp_in")), "t_embedding.mlp_out")
+    ada = F.silu(lin(c, "adaln_proj"))[:, None]
+    im, tm = (ind == IND_IMAGE)[..., None].float(), (ind == IND_TEXT)[..., None].float()
+    h = lin(x * im, "input_proj") * im + lin(rms(llm * tm, sd["llm_cond_norm.weight"], 1e-6), "llm_cond_proj") * tm
+    h = h + sd["embed_image_indicator.weight"][(ind == IND_IMAGE).long()]
+    for i in range(cfg.depth):
+        p = f"layers.{i}."
+        mod = lin(ada, p + "adaln_modulation")
+        sc1, g1, sc2, g2 = 1 + mod[..., :D], torch.tanh(mod[..., D:2 * D]), 1 + mod[..., 2 * D:3 * D], torch.tanh(mod[..., 3 * D:])
+        qkv = lin(rms(h, sd[p + "attention_norm1.weight"], 1e-5) * sc1, p + "attention.qkv", False).reshape(1, L, 3, H, Dh)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        q, k = rms(q, sd[p + "attention.norm_q.weight"], 1e-5), rms(k, sd[p + "attention.norm_k.weight"], 1e-5)
+        q, k = q * cosf + rot(q) * sinf, k * cosf + rot(k) * sinf
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).reshape(1, L, D)
+        h = h + g1 * rms(lin(o, p + "attention.o", False), sd[p + "attention_norm2.weight"], 1e-5)
+        u = rms(h, sd[p + "ffn_norm1.weight"], 1e-5) * sc2
+        ff = lin(F.silu(lin(u, p + "feed_forward.w1", False)) * lin(u, p + "feed_forward.w3", False), p + "feed_forward.w2", False)
+        h = h + g2 * rms(ff, sd[p + "ffn_norm2.weight"], 1e-5)
+    fs = 1 + lin(F.silu(ada), "final_layer.adaln_modulation")
+    want = lin(F.layer_norm(h, (D,), eps=1e-6) * fs, "final_layer.linear")
+    assert (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
