@@ -208,3 +208,64 @@ def test_ideogram4_matches_plain_torch_statement():
     fs = 1 + lin(F.silu(ada), "final_layer.adaln_modulation")
     want = lin(F.layer_norm(h, (D,), eps=1e-6) * fs, "final_layer.linear")
     assert (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_hunyuan15_matches_plain_torch_statement():
+    """HunyuanVideo-1.5: equals a plain-torch statement with [video, text] row order, rotate-half rotary on the video rows
+    only and separate q / k / v projections; checkpoint key names are the published ones."""
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models.hunyuan15 import Hunyuan15DiT, tiny_hunyuan15_config
+    from mojodiffusion_b200.models.layers import timestep_embedding
+    torch.manual_seed(1)
+    cfg = tiny_hunyuan15_config()
+    m = Hunyuan15DiT(cfg, torch.float32).init_weights(5)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    for k in ("img_in.proj.weight", "time_in.mlp.0.weight", "double_blocks.1.img_attn_q_norm.weight", "double_blocks.0.txt_mlp.fc2.bias",
+              "double_blocks.0.img_mod.linear.weight", "final_layer.adaLN_modulation.1.bias", "final_layer.linear.weight"):
+        assert k in sd, k
+    B, Fr, Hh, Ww, St = 1, 2, 3, 4, 5
+    D, H, Dh = cfg.hidden, cfg.heads, cfg.head_dim
+    z, txt, t = torch.randn(B, cfg.in_channels, Fr, Hh, Ww), torch.randn(B, St, D), torch.tensor([0.3])
+    got = m(z, txt, t)
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd[n + ".bias"])
+    rms = lambda v, w: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
+    img = F.conv3d(z, sd["img_in.proj.weight"], sd["img_in.proj.bias"]).flatten(2).transpose(1, 2)
+    vec = lin(F.silu(lin(timestep_embedding(t, 256), "time_in.mlp.0")), "time_in.mlp.2")
+    vs = F.silu(vec)
+    half = Dh // 2
+    pos = torch.stack(torch.meshgrid(torch.arange(Fr), torch.arange(Hh), torch.arange(Ww), indexing="ij"), -1).reshape(-1, 3).float()
+    ang = []
+    for a, d in enumerate(cfg.axes_dim):
+        inv = cfg.theta ** (-torch.arange(0, d, 2).float() / d)
+        ang.append(pos[:, a:a + 1] * inv[None])
+    ang = torch.cat(ang, -1)                                      # [S_img, Dh/2]
+    cosf, sinf = torch.cat((ang.cos(), ang.cos()), -1)[None, :, None], torch.cat((ang.sin(), ang.sin()), -1)[None, :, None]
+    rot = lambda v: torch.cat((-v[..., half:], v[..., :half]), -1)
+    mod = lambda v, sc, sh: F.layer_norm(v, (D,), eps=cfg.eps) * (1 + sc[:, None]) + sh[:, None]
+    S_img = img.shape[1]
+    for i in range(cfg.depth):
+        p = f"double_blocks.{i}."
+        im = lin(vs, p + "img_mod.linear").chunk(6, -1)
+        tm = lin(vs, p + "txt_mod.linear").chunk(6, -1)
+        def qkv(x, s, rope):
+            q, k, v = (lin(x, p + f"{s}_attn_{c}").reshape(B, -1, H, Dh) for c in "qkv")
+            q, k = rms(q, sd[p + f"{s}_attn_q_norm.weight"]), rms(k, sd[p + f"{s}_attn_k_norm.weight"])
+            if rope:
+                q, k = q * cosf + rot(q) * sinf, k * cosf + rot(k) * sinf
+            return q, k, v
+        iq, ik, iv = qkv(mod(img, im[1], im[0]), "img", True)
+        tq, tk, tv = qkv(mod(txt, tm[1], tm[0]), "txt", False)
+        q, k, v = torch.cat((iq, tq), 1), torch.cat((ik, tk), 1), torch.cat((iv, tv), 1)
+        a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).reshape(B, -1, D)
+        img = img + im[2][:, None] * lin(a[:, :S_img], p + "img_attn_proj")
+        txt = txt + tm[2][:, None] * lin(a[:, S_img:], p + "txt_attn_proj")
+        img = img + im[5][:, None] * lin(F.gelu(lin(mod(img, im[4], im[3]), p + "img_mlp.fc1"), approximate="tanh"), p + "img_mlp.fc2")
+        txt = txt + tm[5][:, None] * lin(F.gelu(lin(mod(txt, tm[4], tm[3]), p + "txt_mlp.fc1"), approximate="tanh"), p + "txt_mlp.fc2")
+    fm = lin(vs, "final_layer.adaLN_modulation.1")
+    out = lin(mod(img, fm[:, D:], fm[:, :D]), "final_layer.linear")
+    want = out.reshape(B, Fr, Hh, Ww, cfg.out_channels).permute(0, 4, 1, 2, 3)
+    assert got.shape == want.shape and (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
