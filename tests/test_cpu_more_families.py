@@ -269,3 +269,78 @@ def test_hunyuan15_matches_plain_torch_statement():
     out = lin(mod(img, fm[:, D:], fm[:, :D]), "final_layer.linear")
     want = out.reshape(B, Fr, Hh, Ww, cfg.out_channels).permute(0, 4, 1, 2, 3)
     assert got.shape == want.shape and (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_kandinsky5_matches_plain_torch_statement():
+    """Kandinsky-5: equals a plain-torch statement (pair-rotation rotary, separate q / k / v, per-head softmax cross
+    attention, exact GELU) and carries the published checkpoint key names."""
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models.kandinsky5 import Kandinsky5DiT, tiny_kandinsky5_config
+    from mojodiffusion_b200.models.layers import timestep_embedding
+    torch.manual_seed(2)
+    cfg = tiny_kandinsky5_config()
+    m = Kandinsky5DiT(cfg, torch.float32).init_weights(7)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    for k in ("text_embeddings.norm.bias", "pooled_text_embeddings.in_layer.weight", "time_embeddings.out_layer.bias",
+              "visual_embeddings.in_layer.weight", "text_transformer_blocks.0.text_modulation.out_layer.weight",
+              "visual_transformer_blocks.1.cross_attention.key_norm.weight", "visual_transformer_blocks.0.feed_forward.in_layer.weight",
+              "out_layer.modulation.out_layer.bias", "out_layer.out_layer.weight"):
+        assert k in sd, k
+    assert "visual_transformer_blocks.0.feed_forward.in_layer.bias" not in sd
+    B, Fr, Hh, Ww, T = 1, 2, 4, 6, 5
+    D, H, Dh = cfg.model_dim, cfg.heads, cfg.head_dim
+    z, text, pooled, t = torch.randn(B, cfg.in_visual_dim, Fr, Hh, Ww), torch.randn(B, T, cfg.in_text_dim), torch.randn(B, cfg.in_text_dim2), torch.tensor([417.0])
+    got = m(z, text, pooled, t)
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, w: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
+    ln = lambda v, n: F.layer_norm(v, (v.shape[-1],), sd[n + ".weight"], sd[n + ".bias"], cfg.eps)
+    mod = lambda v, sc, sh: F.layer_norm(v, (D,), eps=cfg.eps) * (1 + sc[:, None]) + sh[:, None]
+
+    def table(pos, axes):
+        parts = [pos[:, a:a + 1] * torch.exp(-torch.log(torch.tensor(cfg.max_period)) * torch.arange(d // 2).float() / (d // 2))[None]
+                 for a, d in enumerate(axes)]
+        return torch.cat(parts, -1)
+
+    def rope(v, ang):                                   # v [B, S, H, Dh], pairs (2i, 2i + 1)
+        c, s = ang.cos()[None, :, None], ang.sin()[None, :, None]
+        a, b = v[..., 0::2], v[..., 1::2]
+        return torch.stack((a * c - b * s, a * s + b * c), -1).flatten(-2)
+
+    def attn(p, xq, xkv, ang):
+        q = rms(lin(xq, p + "to_query").reshape(B, -1, H, Dh), sd[p + "query_norm.weight"])
+        k = rms(lin(xkv, p + "to_key").reshape(B, -1, H, Dh), sd[p + "key_norm.weight"])
+        v = lin(xkv, p + "to_value").reshape(B, -1, H, Dh)
+        if ang is not None:
+            q, k = rope(q, ang), rope(k, ang)
+        w_ = torch.softmax(torch.einsum("bqhd,bkhd->bhqk", q, k) / Dh ** 0.5, -1)
+        return lin(torch.einsum("bhqk,bkhd->bqhd", w_, v).reshape(B, -1, D), p + "out_layer")
+
+    te = lin(F.silu(lin(timestep_embedding(t, D, cfg.max_period, time_factor=1.0), "time_embeddings.in_layer")), "time_embeddings.out_layer")
+    te = te + ln(lin(pooled, "pooled_text_embeddings.in_layer"), "pooled_text_embeddings.norm")
+    txt = ln(lin(text, "text_embeddings.in_layer"), "text_embeddings.norm")
+    tang = table(torch.arange(T).float()[:, None], [Dh])
+    for i in range(cfg.num_text_blocks):
+        p = f"text_transformer_blocks.{i}."
+        c6 = lin(F.silu(te), p + "text_modulation.out_layer").chunk(6, -1)
+        txt = txt + c6[2][:, None] * attn(p + "self_attention.", mod(txt, c6[1], c6[0]), mod(txt, c6[1], c6[0]), tang)
+        txt = txt + c6[5][:, None] * lin(F.gelu(lin(mod(txt, c6[4], c6[3]), p + "feed_forward.in_layer")), p + "feed_forward.out_layer")
+    f, h, w = Fr, Hh // 2, Ww // 2
+    tok = z.reshape(B, -1, f, 1, h, 2, w, 2).permute(0, 2, 4, 6, 1, 3, 5, 7).reshape(B, f * h * w, -1)
+    x = lin(tok, "visual_embeddings.in_layer")
+    ids = torch.stack(torch.meshgrid(torch.arange(f), torch.arange(h), torch.arange(w), indexing="ij"), -1).reshape(-1, 3).float()
+    vang = table(ids, cfg.axes_dim)
+    for i in range(cfg.num_visual_blocks):
+        p = f"visual_transformer_blocks.{i}."
+        c9 = lin(F.silu(te), p + "visual_modulation.out_layer").chunk(9, -1)
+        u = mod(x, c9[1], c9[0])
+        x = x + c9[2][:, None] * attn(p + "self_attention.", u, u, vang)
+        x = x + c9[5][:, None] * attn(p + "cross_attention.", mod(x, c9[4], c9[3]), txt, None)
+        x = x + c9[8][:, None] * lin(F.gelu(lin(mod(x, c9[7], c9[6]), p + "feed_forward.in_layer")), p + "feed_forward.out_layer")
+    om = lin(F.silu(te), "out_layer.modulation.out_layer")
+    out = lin(mod(x, om[:, D:], om[:, :D]), "out_layer.out_layer")
+    want = out.reshape(B, f, h, w, cfg.out_visual_dim, 1, 2, 2).permute(0, 4, 1, 5, 2, 6, 3, 7).reshape(B, cfg.out_visual_dim, Fr, Hh, Ww)
+    assert got.shape == want.shape and (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
