@@ -344,3 +344,71 @@ def test_kandinsky5_matches_plain_torch_statement():
     out = lin(mod(x, om[:, D:], om[:, :D]), "out_layer.out_layer")
     want = out.reshape(B, f, h, w, cfg.out_visual_dim, 1, 2, 2).permute(0, 4, 1, 5, 2, 6, 3, 7).reshape(B, cfg.out_visual_dim, Fr, Hh, Ww)
     assert got.shape == want.shape and (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_cosmos_predict25_matches_plain_torch_statement():
+    """Cosmos-Predict2.5: equals a plain-torch statement (adaLN-LoRA modulation, NTK per-axis rotary bases, channel-slowest
+    un-patchify, mask channels) and carries the published checkpoint key names; per-frame timesteps are accepted."""
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models.cosmos import CosmosDiT, tiny_cosmos_config
+    from mojodiffusion_b200.models.layers import timestep_embedding
+    torch.manual_seed(3)
+    cfg = tiny_cosmos_config()
+    m = CosmosDiT(cfg, torch.float32).init_weights(9)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    for k in ("x_embedder.proj.1.weight", "crossattn_proj.0.bias", "t_embedder.1.linear_2.weight", "t_embedding_norm.weight",
+              "blocks.0.adaln_modulation_self_attn.1.weight", "blocks.1.adaln_modulation_mlp.2.weight", "blocks.0.self_attn.q_norm.weight",
+              "blocks.0.cross_attn.k_proj.weight", "blocks.1.mlp.layer2.weight", "final_layer.adaln_modulation.2.weight", "final_layer.linear.weight"):
+        assert k in sd, k
+    assert not any(k.endswith(".bias") and "crossattn_proj" not in k for k in sd)
+    B, T, Hh, Ww, St = 1, 2, 4, 6, 5
+    D, H, Dh = cfg.model_channels, cfg.heads, cfg.head_dim
+    z, text, t = torch.randn(B, cfg.in_channels, T, Hh, Ww), torch.randn(B, St, cfg.text_in_dim), torch.tensor([[0.3, 0.7]])
+    mask = (torch.rand(B, 1, T, Hh, Ww) > 0.5).float()
+    got = m(z, text, t, cond_mask=mask)
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, w: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
+    tp, hp, wp = T, Hh // 2, Ww // 2
+    x_in = torch.cat((z, mask, torch.zeros(B, 1, T, Hh, Ww)), 1)
+    tok = x_in.reshape(B, -1, tp, 1, hp, 2, wp, 2).permute(0, 2, 4, 6, 1, 3, 5, 7).reshape(B, tp, hp * wp, -1)
+    x = lin(tok, "x_embedder.proj.1")                                            # [B, tp, hw, D]
+    txt = lin(text, "crossattn_proj.0")
+    sample = timestep_embedding(t.reshape(-1), D, 10000.0, time_factor=1.0).reshape(B, tp, 1, D)
+    lora = lin(F.silu(lin(sample, "t_embedder.1.linear_1")), "t_embedder.1.linear_2")
+    emb = rms(sample, sd["t_embedding_norm.weight"])
+    dims = (Dh - 2 * (Dh // 6 * 2), Dh // 6 * 2, Dh // 6 * 2)
+    ids = torch.stack(torch.meshgrid(torch.arange(tp), torch.arange(hp), torch.arange(wp), indexing="ij"), -1).reshape(-1, 3).float()
+    ang = torch.cat([ids[:, a:a + 1] * ((10000.0 * r ** (d / (d - 2))) ** (-torch.arange(0, d, 2).float() / d))[None]
+                     for a, (d, r) in enumerate(zip(dims, (1.0, 3.0, 3.0)))], -1)
+    cosf, sinf = torch.cat((ang.cos(), ang.cos()), -1)[None, :, None], torch.cat((ang.sin(), ang.sin()), -1)[None, :, None]
+    rot = lambda v: torch.cat((-v[..., Dh // 2:], v[..., :Dh // 2]), -1)
+
+    def attn(p, xq, xkv, rope):
+        q = rms(lin(xq, p + "q_proj").reshape(B, -1, H, Dh), sd[p + "q_norm.weight"])
+        k = rms(lin(xkv, p + "k_proj").reshape(B, -1, H, Dh), sd[p + "k_norm.weight"])
+        v = lin(xkv, p + "v_proj").reshape(B, -1, H, Dh)
+        if rope:
+            q, k = q * cosf + rot(q) * sinf, k * cosf + rot(k) * sinf
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
+        return lin(o.reshape(B, -1, D), p + "output_proj")
+
+    for i in range(cfg.depth):
+        p = f"blocks.{i}."
+        for sub in ("self_attn", "cross_attn", "mlp"):
+            sh, sc, g = (lin(lin(F.silu(emb), p + f"adaln_modulation_{sub}.1"), p + f"adaln_modulation_{sub}.2") + lora).chunk(3, -1)
+            u = F.layer_norm(x, (D,), eps=cfg.eps) * (1 + sc) + sh
+            if sub == "self_attn":
+                y = attn(p + "self_attn.", u.reshape(B, -1, D), u.reshape(B, -1, D), True)
+            elif sub == "cross_attn":
+                y = attn(p + "cross_attn.", u.reshape(B, -1, D), txt, False)
+            else:
+                y = lin(F.gelu(lin(u, p + "mlp.layer1")), p + "mlp.layer2").reshape(B, -1, D)
+            x = x + g * y.reshape(B, tp, hp * wp, D)
+    fm = lin(lin(F.silu(emb), "final_layer.adaln_modulation.1"), "final_layer.adaln_modulation.2") + lora[..., :2 * D]
+    out = lin(F.layer_norm(x, (D,), eps=cfg.eps) * (1 + fm[..., D:]) + fm[..., :D], "final_layer.linear")
+    want = out.reshape(B, tp, hp, wp, 2, 2, 1, cfg.out_channels).permute(0, 7, 1, 6, 2, 4, 3, 5).reshape(B, cfg.out_channels, T, Hh, Ww)
+    assert got.shape == want.shape and (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
