@@ -144,6 +144,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             out.reshape(-1, out.shape[-1]).copy_(y)
             return out
         return y.reshape(*lead, w.shape[0])
+    if (x.shape[-1] % 8 or w.shape[0] % 8) and not extra:
+        # rows of 16-byte multiples are a TMA rule: zero-pad the reduction and / or the output width (patch embedders
+        # and heads with odd channel counts; small matrices), then drop the padded output columns
+        kp, npad = (-x.shape[-1]) % 8, (-w.shape[0]) % 8
+        pad = torch.nn.functional.pad
+        y = linear(pad(x, (0, kp)), pad(w, (0, kp, 0, npad)), pad(bias, (0, npad)) if bias is not None else None, act,
+                   pad(residual, (0, npad)) if residual is not None else None,
+                   pad(gate, (0, npad)) if gate is not None else None, rows_per_group)
+        y = y[..., :w.shape[0]]
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y.contiguous() if npad else y
     x2 = _flat2d(x)
     need_grad = torch.is_grad_enabled() and (x.requires_grad or w.requires_grad or
                                              (bias is not None and bias.requires_grad))

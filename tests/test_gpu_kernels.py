@@ -734,3 +734,19 @@ def test_unet_lora_step_runs_without_library_convolutions(monkeypatch):
     native.check_status(out)
     assert calls["n"] == 0
     assert all(s.up.grad is not None for s in slots) and any(float(s.down.grad.abs().sum()) > 0 or float(s.up.grad.abs().sum()) > 0 for s in slots)
+
+
+def test_linear_pads_odd_reduction_and_output_widths():
+    """Patch embedders with 65 or 132 input values per token and heads with narrow outputs: rows that are not 16-byte
+    multiples are zero-padded on the way in and sliced on the way out, with and without autograd."""
+    for K, N in ((65, 128), (132, 64), (64, 12), (20, 4)):
+        x, w, b = _rand(96, K, seed=K), _rand(N, K, seed=K + 1) * 0.1, _rand(N, seed=K + 2)
+        y = O.linear(x, w, b, act="silu")
+        _check(y, torch.nn.functional.silu(x.float() @ w.float().t() + b.float()), name=f"linear K={K} N={N}")
+        assert y.shape == (96, N) and y.is_contiguous()
+        xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        O.linear(xg, wg, b).float().square().sum().backward()
+        xr, wr = x.float().requires_grad_(True), w.float().requires_grad_(True)
+        (xr @ wr.t() + b.float()).square().sum().backward()
+        _check(xg.grad, xr.grad, rel=5e-2, name="dx of padded linear")
+        _check(wg.grad, wr.grad, rel=5e-2, name="dw of padded linear")

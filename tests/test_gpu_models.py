@@ -262,3 +262,43 @@ def test_cuda_graph_train_step_matches_eager():
     (l0, w0), (l1, w1) = out
     assert all(abs(a - b) <= 2e-3 * abs(a) + 1e-4 for a, b in zip(l0, l1)), (l0, l1)
     assert _cos(w1, w0) > 0.9999
+
+
+def test_more_video_and_image_families_on_native_kernels():
+    """Ideogram-4, HunyuanVideo-1.5, Kandinsky-5, Cosmos-Predict2.5 and Wan-VACE (tiny configurations) in bf16 on the
+    sm_100a kernels against their fp32 CPU forward."""
+    from mojodiffusion_b200.models.cosmos import CosmosDiT, tiny_cosmos_config
+    from mojodiffusion_b200.models.hunyuan15 import Hunyuan15DiT, tiny_hunyuan15_config
+    from mojodiffusion_b200.models.ideogram4 import Ideogram4DiT, tiny_ideogram4_config
+    from mojodiffusion_b200.models.kandinsky5 import Kandinsky5DiT, tiny_kandinsky5_config
+    from mojodiffusion_b200.models.wan import WanVaceDiT, tiny_wan_vace_config
+    g = torch.Generator().manual_seed(11)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    ci = tiny_ideogram4_config()
+    L = 48
+    ind = torch.tensor([[3] * 16 + [2] * 24 + [0] * 8])
+    pos = torch.stack([torch.zeros(L), torch.arange(L).float() * 5, torch.arange(L).float()], 1)
+    _gpu_vs_cpu(lambda dt, dev: Ideogram4DiT(ci, dt, dev), (rn(1, L, ci.in_channels), rn(1, L, ci.llm_dim), torch.tensor([0.4]), ind, pos), cos_min=0.99)
+    ch = tiny_hunyuan15_config()
+    _gpu_vs_cpu(lambda dt, dev: Hunyuan15DiT(ch, dt, dev), (rn(1, ch.in_channels, 2, 4, 8), rn(1, 16, ch.hidden), torch.tensor([0.3])), cos_min=0.99)
+    ck = tiny_kandinsky5_config()
+    _gpu_vs_cpu(lambda dt, dev: Kandinsky5DiT(ck, dt, dev), (rn(1, ck.in_visual_dim, 2, 8, 8), rn(1, 16, ck.in_text_dim), rn(1, ck.in_text_dim2),
+                                                           torch.tensor([417.0])), cos_min=0.99)
+    cc = tiny_cosmos_config()
+    _gpu_vs_cpu(lambda dt, dev: CosmosDiT(cc, dt, dev), (rn(1, cc.in_channels, 2, 8, 8), rn(1, 16, cc.text_in_dim), torch.tensor([0.6])), cos_min=0.99)
+    cv = tiny_wan_vace_config()
+    m32 = WanVaceDiT(cv, torch.float32, "cpu").init_weights(0)
+    with torch.no_grad():                              # give the zero-initialised control projections weight so the branch acts
+        for blk in m32.vace_blocks:
+            for lin in (blk.before_proj, blk.after_proj):
+                if lin is not None:
+                    lin.weight.copy_(torch.randn(lin.weight.shape, generator=g) * 0.05)
+    mg = WanVaceDiT(cv, torch.bfloat16, DEV)
+    mg.load_state_dict({k: v.to(torch.bfloat16) for k, v in m32.state_dict().items()})
+    m32.load_state_dict({k: v.float() for k, v in mg.state_dict().items()})
+    z, txt, t, ctl = rn(1, cv.in_dim, 2, 8, 8), rn(1, 16, cv.text_dim), torch.tensor([0.5]), rn(1, cv.vace_in_dim, 2, 8, 8)
+    with torch.no_grad():
+        want, base = m32(z, txt, t, control=ctl), m32(z, txt, t)
+        got = mg(z.to(DEV), txt.to(DEV), t.to(DEV), control=ctl.to(DEV))
+    native.check_status()
+    assert (want - base).abs().max() > 1e-3 and _cos(got, want) >= 0.99
