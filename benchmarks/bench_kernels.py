@@ -94,6 +94,38 @@ def main():
     rows.append({"op": "layernorm_modulate", "shape": [rows_n, D], "ms": t, "gbs": by / t / 1e6,
                  "frac_of_measured_copy_bw": by / t / 1e6 / peak_bw})
     print(rows[-1], flush=True)
+    # QK-RMSNorm + RoPE in place on a packed [S, 3 * 24 * 128] projection buffer (q and k ranges: read + write)
+    S, H, Dh = 4608, 24, 128
+    qkv = torch.randn(1, S, 3 * H * Dh, device=dev, dtype=torch.bfloat16)
+    wq = torch.ones(Dh, device=dev, dtype=torch.bfloat16)
+    pos = torch.stack([torch.zeros(S), torch.arange(S).float(), torch.arange(S).float()], 1).to(dev)
+    cos, sin = O.rope_table(pos, [16, 56, 56], 10000.0)
+    t = timeit(lambda: O.qk_norm_rope(qkv, H, Dh, wq, wq, cos, sin), flush=flush)
+    by = 2.0 * S * 2 * H * Dh * 2
+    rows.append({"op": "qk_norm_rope", "shape": [S, H, Dh], "ms": t, "gbs": by / t / 1e6, "frac_of_measured_copy_bw": by / t / 1e6 / peak_bw})
+    print(rows[-1], flush=True)
+    # LoRA linear (rank 16): skinny down projection + the up projection as an extra K segment of the base GEMM, against the
+    # chain it replaces (base GEMM, down GEMM, up GEMM accumulated into the base output), both on this package's GEMM and
+    # on cuBLAS (addmm for the accumulation)
+    for M, N, K in [(4608, 9216, 3072), (4608, 3072, 15360)][: 1 if args.quick else 2]:
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        A = torch.randn(16, K, device=dev, dtype=torch.bfloat16) * 0.02
+        Bm = torch.randn(N, 16, device=dev, dtype=torch.bfloat16) * 0.02
+        from mojodiffusion_b200.ops.functional import _gemm
+        t_fused = timeit(lambda: O.lora_linear(x, w, None, A, Bm, 1.0), flush=flush)
+        t_base = timeit(lambda: O.linear(x, w), flush=flush)
+
+        def chain_ours():
+            y = _gemm([x], [w])
+            return _gemm([_gemm([x], [A])], [Bm], residual=y)
+
+        def chain_lib():
+            return torch.addmm(torch.matmul(x, w.t()), torch.matmul(x, A.t()), Bm.t())
+        t_chain, t_chain_lib = timeit(chain_ours, flush=flush), timeit(chain_lib, flush=flush)
+        rows.append({"op": "lora_linear_r16", "shape": [M, N, K], "fused_ms": t_fused, "base_gemm_ms": t_base,
+                     "adapter_cost_ms": t_fused - t_base, "chain_ours_ms": t_chain, "chain_cublas_ms": t_chain_lib})
+        print(rows[-1], flush=True)
     native.check_status()
     if args.json:
         json.dump(rows, open(args.json, "w"), indent=1)

@@ -225,7 +225,7 @@ def lora_linear(x, w, bias, A, B, scale: float, act=None, residual=None, gate=No
             out.copy_(y)
             return out
         return y
-    t = _gemm([x2], [A.contiguous()])
+    t = _gemm_skinny(x2, A.contiguous())          # few output tiles: the reduction is split over the idle SMs
     Bs = B if scale == 1.0 else (B.float() * scale).to(B.dtype)
     r2 = _flat2d(residual) if residual is not None else None
     o2 = out.reshape(-1, out.shape[-1]) if out is not None else None
