@@ -215,6 +215,36 @@ register(ModelManifest(
     "flux_vae_config", "", 2.0, ((1024, 1024),), notes="2 x 2 patches and the mask channel are added inside the model"),
     "anima-minitraindit")
 
+_NO_PIPELINE = "the backbone and its parity tests exist; no sampler adapter, serving backend or trainer adapter is wired"
+register(ModelManifest(
+    "ideogram-4", "ideogram4", _M + "ideogram4", "Ideogram4DiT", "Ideogram4Config", "tiny_ideogram4_config",
+    LatentSpec(128, 16, 1, True), TextSpec(512, 53248, 0, ("qwen3_vl_stacked",)),
+    ScheduleSpec("logit_normal", 30, 1.0), None, "klein_vae_config", "", 10.6, ((1024, 1024),), blocked=_NO_PIPELINE,
+    notes="text and image tokens share one sequence; an indicator per position selects the embedding path"),
+    "ideogram4")
+register(ModelManifest(
+    "hunyuan-video-1.5", "hunyuan15", _M + "hunyuan15", "Hunyuan15DiT", "Hunyuan15Config", "tiny_hunyuan15_config",
+    LatentSpec(32, 16, 1, False, temporal_factor=4), TextSpec(1000, 2048, 0, ("qwen25_vl", "byt5")),
+    ScheduleSpec("shifted", 50, 6.0, shift=7.0), None, "", "", 8.3, ((1280, 720),), blocked=_NO_PIPELINE,
+    notes="65 input channels: latent, condition latent and mask are concatenated by the caller; text arrives projected"),
+    "hunyuan15", "hunyuanvideo-1.5")
+register(ModelManifest(
+    "kandinsky-5-t2v-lite", "kandinsky5", _M + "kandinsky5", "Kandinsky5DiT", "Kandinsky5Config", "tiny_kandinsky5_config",
+    LatentSpec(16, 8, 2, False, temporal_factor=4), TextSpec(256, 3584, 768, ("qwen25_vl", "clip_l")),
+    ScheduleSpec("shifted", 50, 5.0, shift=5.0), None, "", "", 2.0, ((768, 512),), blocked=_NO_PIPELINE),
+    "kandinsky5", "kandinsky-5")
+register(ModelManifest(
+    "cosmos-predict2.5-2b", "cosmos", _M + "cosmos", "CosmosDiT", "CosmosConfig", "tiny_cosmos_config",
+    LatentSpec(16, 8, 2, False, temporal_factor=4), TextSpec(512, 100352, 0, ("cosmos_reason1",)),
+    ScheduleSpec("rectified_flow_unipc", 35, 7.0), None, "", "", 2.0, ((1280, 704),), blocked=_NO_PIPELINE),
+    "cosmos", "cosmos-predict25")
+register(ModelManifest(
+    "wan21-vace-14b", "wan_vace", _M + "wan", "WanVaceDiT", "wan21_vace_14b_config", "tiny_wan_vace_config",
+    LatentSpec(16, 8, 2, False, temporal_factor=4), TextSpec(512, 4096, 0, ("umt5",)),
+    ScheduleSpec("shifted", 50, 5.0, shift=5.0), None, "", "", 14.0, ((832, 480),), blocked=_NO_PIPELINE,
+    notes="control latent + mask (96 channels) enter through the VACE branch; hints feed every second base layer"),
+    "wan-vace", "vace")
+
 
 # ---- execution config / shape profile / guard ------------------------------------------------------------------
 @dataclass
