@@ -68,3 +68,38 @@ def moe_ffn(tokens: torch.Tensor, router_w: torch.Tensor, gate_w, up_w, down_w, 
     out = torch.zeros_like(tokens)
     token_of_slot = torch.arange(tokens.shape[0], device=tokens.device).repeat_interleave(k)
     return gated_scatter_add(eo, gating, token_of_slot, out)
+
+
+# ---- expert-choice routing (each expert picks its top-C tokens) ----------------------------------------------------------
+def expert_choice_route(affinity: torch.Tensor, capacity: int, route_scale: float = 1.0):
+    """affinity [B, E, S] (softmax over experts, transposed) -> (token index [E, B*C] into the flat [B*S] token list,
+    gate [E, B*C] fp32). Every (sample, expert) takes its ``capacity`` highest-affinity tokens (ties to the lower token
+    index); a token's gates are divided by their sum over all experts that picked it, then multiplied by ``route_scale``
+    (serenitymojo/models/dit/nucleus_moe.mojo:27-110)."""
+    B, E, S = affinity.shape
+    if not 1 <= capacity <= S:
+        raise ValueError("expert_choice_route: capacity must lie in [1, tokens per sample]")
+    a = affinity.float()
+    order = torch.sort(a, dim=2, descending=True, stable=True).indices[:, :, :capacity]        # [B, E, C]
+    w = torch.gather(a, 2, order)
+    idx = (order + (torch.arange(B, device=a.device) * S)[:, None, None]).permute(1, 0, 2).reshape(E, B * capacity)
+    w = w.permute(1, 0, 2).reshape(E, B * capacity)
+    tsum = torch.zeros(B * S, dtype=torch.float32, device=a.device).index_add_(0, idx.reshape(-1), w.reshape(-1))
+    gate = w / (tsum[idx] + 1e-12) * route_scale
+    return idx, gate
+
+
+def expert_choice_ffn(tokens: torch.Tensor, idx: torch.Tensor, gate: torch.Tensor, gate_up_w: torch.Tensor,
+                      down_w: torch.Tensor) -> torch.Tensor:
+    """tokens [T, D]; idx / gate [E, P] from ``expert_choice_route``; gate_up_w [E, D, 2I] (gate columns then up columns,
+    ``x @ W`` layout); down_w [E, I, D]. Returns sum over picks of gate * (silu(x Wg) * (x Wu)) Wd, accumulated per token
+    in fp32, in the dtype of ``tokens``. The experts run as two batched GEMMs over the gathered [E, P, D] rows."""
+    E, P = idx.shape
+    T, D = tokens.shape
+    x = tokens[idx.reshape(-1)].reshape(E, P, D)
+    gu = torch.bmm(x, gate_up_w.to(x.dtype))                                              # [E, P, 2I]
+    inner = gu.shape[-1] // 2
+    h = torch.nn.functional.silu(gu[..., :inner].float()).to(x.dtype) * gu[..., inner:]
+    y = torch.bmm(h, down_w.to(x.dtype)).float() * gate[..., None]                          # [E, P, D]
+    out = torch.zeros(T, D, dtype=torch.float32, device=tokens.device).index_add_(0, idx.reshape(-1), y.reshape(E * P, D))
+    return out.to(tokens.dtype)

@@ -244,6 +244,12 @@ register(ModelManifest(
     ScheduleSpec("shifted", 50, 5.0, shift=5.0), None, "", "", 14.0, ((832, 480),), blocked=_NO_PIPELINE,
     notes="control latent + mask (96 channels) enter through the VACE branch; hints feed every second base layer"),
     "wan-vace", "vace")
+register(ModelManifest(
+    "nucleus-image", "nucleus", _M + "nucleus", "NucleusDiT", "NucleusConfig", "tiny_nucleus_config",
+    LatentSpec(16, 8, 2, True), TextSpec(512, 4096, 0, ("qwen3_vl",)),
+    ScheduleSpec("shifted", 30, 4.0, shift=3.0), None, "flux_vae_config", "", 17.0, ((1024, 1024),), blocked=_NO_PIPELINE,
+    notes="29 of 32 blocks are expert-choice mixtures of 64 experts plus a shared expert"),
+    "nucleus")
 
 
 # ---- execution config / shape profile / guard ------------------------------------------------------------------

@@ -412,3 +412,117 @@ def test_cosmos_predict25_matches_plain_torch_statement():
     out = lin(F.layer_norm(x, (D,), eps=cfg.eps) * (1 + fm[..., D:]) + fm[..., :D], "final_layer.linear")
     want = out.reshape(B, tp, hp, wp, 2, 2, 1, cfg.out_channels).permute(0, 7, 1, 6, 2, 4, 3, 5).reshape(B, cfg.out_channels, T, Hh, Ww)
     assert got.shape == want.shape and (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_nucleus_moe_dit_matches_plain_torch_statement():
+    """Nucleus-Image: expert-choice routing equals a loop statement (greedy top-C per sample and expert, ties to the lower
+    token, per-token renormalisation times the route scale) and the whole model equals a plain-torch forward."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models.layers import timestep_embedding
+    from mojodiffusion_b200.models.nucleus import NucleusDiT, _signed, tiny_nucleus_config
+    from mojodiffusion_b200.ops import moe
+    torch.manual_seed(4)
+    # routing against loops, with a deliberate tie
+    aff = torch.softmax(torch.randn(2, 3, 7), 1)
+    aff[0, 1, 2] = aff[0, 1, 5]
+    idx, gate = moe.expert_choice_route(aff, 3, 2.5)
+    B, E, S, C = 2, 3, 7, 3
+    picks = {}
+    for b in range(B):
+        for e in range(E):
+            taken = []
+            for _ in range(C):
+                best = max((s for s in range(S) if s not in taken), key=lambda s: (float(aff[b, e, s]), -s))
+                taken.append(best)
+            picks[(b, e)] = taken
+    tsum = torch.zeros(B * S)
+    for (b, e), tk in picks.items():
+        for s in tk:
+            tsum[b * S + s] += aff[b, e, s]
+    for e in range(E):
+        for b in range(B):
+            for c, s in enumerate(picks[(b, e)]):
+                assert int(idx[e, b * C + c]) == b * S + s
+                assert abs(float(gate[e, b * C + c]) - float(aff[b, e, s] / (tsum[b * S + s] + 1e-12) * 2.5)) < 1e-6
+    assert [float(v) for v in _signed(5)] == [-3, -2, -1, 0, 1] and [float(v) for v in _signed(4)] == [-2, -1, 0, 1]
+
+    cfg = tiny_nucleus_config()
+    m = NucleusDiT(cfg, torch.float32).init_weights(11)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    f, h, w, St = 1, 4, 6, 5
+    D, H, KV, Dh = cfg.hidden, cfg.heads, cfg.kv_heads, cfg.head_dim
+    x_in, text, t = torch.randn(2, f * h * w, cfg.in_channels), torch.randn(2, St, cfg.joint_dim), torch.tensor([0.3, 0.8])
+    got = m(x_in, text, t, (f, h, w))
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, wt: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * wt
+    ln = lambda v: F.layer_norm(v, (D,), eps=cfg.eps)
+
+    def angles(pos):
+        return torch.cat([pos[:, a:a + 1] / (cfg.theta ** (torch.arange(d // 2).float() / (d // 2)))[None]
+                          for a, d in enumerate(cfg.axes_dim)], -1)
+    ipos = torch.stack(torch.meshgrid(torch.arange(f).float(), _signed(h), _signed(w), indexing="ij"), -1).reshape(-1, 3)
+    tpos = (max(h // 2, w // 2) + torch.arange(St)).float()[:, None].expand(St, 3)
+    iang, tang = angles(ipos), angles(tpos)
+
+    def rope(v, ang):
+        c, s = ang.cos()[None, :, None], ang.sin()[None, :, None]
+        a, b = v[..., 0::2], v[..., 1::2]
+        return torch.stack((a * c - b * s, a * s + b * c), -1).flatten(-2)
+
+    def swiglu_ffn(v, p0, p2):
+        gu = F.linear(v, sd[p0])
+        inner = gu.shape[-1] // 2
+        return F.linear(F.silu(gu[..., inner:]) * gu[..., :inner], sd[p2])
+
+    x = lin(x_in, "img_in")
+    enc = rms(text, sd["txt_norm.weight"])
+    temb = rms(lin(F.silu(lin(timestep_embedding(t, D), "time_text_embed.timestep_embedder.linear_1")),
+                   "time_text_embed.timestep_embedder.linear_2"), sd["time_text_embed.norm.weight"])
+    for i in range(cfg.depth):
+        p = f"transformer_blocks.{i}."
+        sc1, g1, sc2, g2 = lin(F.silu(temb), p + "img_mod.1").chunk(4, -1)
+        g1, g2 = torch.tanh(g1.clamp(-2, 2))[:, None], torch.tanh(g2.clamp(-2, 2))[:, None]
+        ctx = lin(enc, p + "encoder_proj")
+        u = ln(x) * (1 + sc1[:, None])
+        q = rope(rms(lin(u, p + "attn.to_q").unflatten(-1, (H, Dh)), sd[p + "attn.norm_q.weight"]), iang)
+        k = torch.cat((rope(rms(lin(u, p + "attn.to_k").unflatten(-1, (KV, Dh)), sd[p + "attn.norm_k.weight"]), iang),
+                       rope(rms(lin(ctx, p + "attn.add_k_proj").unflatten(-1, (KV, Dh)), sd[p + "attn.norm_added_k.weight"]), tang)), 1)
+        v = torch.cat((lin(u, p + "attn.to_v"), lin(ctx, p + "attn.add_v_proj")), 1).unflatten(-1, (KV, Dh))
+        k, v = k.repeat_interleave(H // KV, 2), v.repeat_interleave(H // KV, 2)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).flatten(-2)
+        x = x + g1 * lin(o, p + "attn.to_out.0")
+        un = ln(x)
+        u = un * (1 + sc2[:, None])
+        if i < cfg.dense_layers:
+            y = swiglu_ffn(u, p + "img_mlp.net.0.proj.weight", p + "img_mlp.net.2.weight")
+        else:
+            Bn, S = u.shape[:2]
+            C = max(1, math.ceil(cfg.capacity_factor(i) * S / cfg.num_experts))
+            scores = torch.softmax(F.linear(torch.cat((temb[:, None].expand(Bn, S, D), un), -1), sd[p + "img_mlp.gate.weight"]).float(), -1)
+            scores = scores.to(torch.bfloat16).float()
+            routed = torch.zeros(Bn * S, D)
+            flat = u.reshape(Bn * S, D)
+            top = torch.sort(scores.transpose(1, 2), dim=2, descending=True, stable=True).indices[:, :, :C]     # [B, E, C]
+            tsum = torch.zeros(Bn * S)
+            for b in range(Bn):
+                for e in range(cfg.num_experts):
+                    for s in top[b, e]:
+                        tsum[b * S + int(s)] += scores[b, int(s), e]
+            for b in range(Bn):
+                for e in range(cfg.num_experts):
+                    for s in top[b, e]:
+                        tk = b * S + int(s)
+                        gu = flat[tk] @ sd[p + "img_mlp.experts.gate_up_proj"][e]
+                        inner = gu.shape[-1] // 2
+                        eo = (F.silu(gu[:inner]) * gu[inner:]) @ sd[p + "img_mlp.experts.down_proj"][e]
+                        routed[tk] += eo * (scores[b, int(s), e] / (tsum[tk] + 1e-12) * cfg.route_scale)
+            y = swiglu_ffn(u, p + "img_mlp.shared_expert.net.0.proj.weight", p + "img_mlp.shared_expert.net.2.weight") + routed.reshape(Bn, S, D)
+        x = x + g2 * y
+    sc, sh = lin(F.silu(temb), "norm_out.linear").chunk(2, -1)
+    want = F.linear(ln(x) * (1 + sc[:, None]) + sh[:, None], sd["proj_out.weight"])
+    assert got.shape == want.shape and (got - want).abs().max() < 3e-4 * max(1.0, float(want.abs().max()))
