@@ -250,6 +250,12 @@ register(ModelManifest(
     ScheduleSpec("shifted", 30, 4.0, shift=3.0), None, "flux_vae_config", "", 17.0, ((1024, 1024),), blocked=_NO_PIPELINE,
     notes="29 of 32 blocks are expert-choice mixtures of 64 experts plus a shared expert"),
     "nucleus")
+register(ModelManifest(
+    "ace-step-1.5", "acestep", _M + "acestep", "AceStepDiT", "AceStepConfig", "tiny_acestep_config",
+    LatentSpec(64, 1, 2, False), TextSpec(512, 2048, 0, ("qwen3_embedding", "lyric", "timbre")),
+    ScheduleSpec("shifted", 8, 1.0, shift=3.0), None, "", "", 2.0, ((1, 1),), blocked=_NO_PIPELINE,
+    notes="audio: a 1-D token sequence of acoustic latents; the acoustic VAE and the condition encoder are not built"),
+    "acestep", "ace-step")
 
 
 # ---- execution config / shape profile / guard ------------------------------------------------------------------

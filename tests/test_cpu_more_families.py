@@ -526,3 +526,69 @@ def test_nucleus_moe_dit_matches_plain_torch_statement():
     sc, sh = lin(F.silu(temb), "norm_out.linear").chunk(2, -1)
     want = F.linear(ln(x) * (1 + sc[:, None]) + sh[:, None], sd["proj_out.weight"])
     assert got.shape == want.shape and (got - want).abs().max() < 3e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_acestep_audio_dit_matches_plain_torch_statement():
+    """ACE-Step: equals a plain-torch statement built on conv1d / conv_transpose1d, rotate-half rotary, grouped-query
+    attention and a +-window band mask on the even layers (sequence longer than the window), odd length padded and cropped."""
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models.acestep import AceStepDiT, tiny_acestep_config
+    from mojodiffusion_b200.models.layers import timestep_embedding
+    torch.manual_seed(5)
+    cfg = tiny_acestep_config()
+    m = AceStepDiT(cfg, torch.float32).init_weights(13)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() == 1 or "scale_shift_table" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    B, T, L = 2, 21, 5
+    D, H, KV, Dh = cfg.hidden, cfg.heads, cfg.kv_heads, cfg.head_dim
+    x_t, ctx, cond = torch.randn(B, T, cfg.acoustic_dim), torch.randn(B, T, cfg.in_channels - cfg.acoustic_dim), torch.randn(B, L, D)
+    t, r = torch.tensor([0.7, 0.2]), torch.tensor([0.5, 0.1])
+    got = m(x_t, ctx, cond, t, r)
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, wt: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * wt
+
+    def temb(tv, p):
+        e = lin(F.silu(lin(timestep_embedding(tv, 256), p + ".linear_1")), p + ".linear_2")
+        return e, lin(F.silu(e), p + ".time_proj").reshape(B, 6, D)
+    e1, p1 = temb(t, "decoder.time_embed")
+    e2, p2 = temb(t - r, "decoder.time_embed_r")
+    te, tp = e1 + e2, p1 + p2
+    xin = F.pad(torch.cat((ctx, x_t), -1), (0, 0, 0, 1))
+    x = F.conv1d(xin.transpose(1, 2), sd["decoder.proj_in.1.weight"], sd["decoder.proj_in.1.bias"], stride=2).transpose(1, 2)
+    S = x.shape[1]
+    assert S == 11 and S > cfg.sliding_window
+    enc = lin(cond, "decoder.condition_embedder")
+    ang = torch.arange(S).float()[:, None] / (cfg.theta ** (torch.arange(0, Dh, 2).float() / Dh))[None]
+    cosf, sinf = torch.cat((ang.cos(), ang.cos()), -1)[None, :, None], torch.cat((ang.sin(), ang.sin()), -1)[None, :, None]
+    rot = lambda v: torch.cat((-v[..., Dh // 2:], v[..., :Dh // 2]), -1)
+    idx = torch.arange(S)
+    band = (idx[:, None] - idx[None]).abs() <= cfg.sliding_window
+
+    def attn(p, xq, xkv, rope, mask):
+        q = rms(lin(xq, p + ".q_proj").unflatten(-1, (H, Dh)), sd[p + ".q_norm.weight"])
+        k = rms(lin(xkv, p + ".k_proj").unflatten(-1, (KV, Dh)), sd[p + ".k_norm.weight"])
+        v = lin(xkv, p + ".v_proj").unflatten(-1, (KV, Dh))
+        if rope:
+            q, k = q * cosf + rot(q) * sinf, k * cosf + rot(k) * sinf
+        k, v = k.repeat_interleave(H // KV, 2), v.repeat_interleave(H // KV, 2)
+        s = torch.einsum("bqhd,bkhd->bhqk", q, k) / Dh ** 0.5
+        if mask is not None:
+            s = s.masked_fill(~mask, float("-inf"))
+        return lin(torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v).flatten(-2), p + ".o_proj")
+
+    for i in range(cfg.depth):
+        p = f"decoder.layers.{i}."
+        mod = sd[p + "scale_shift_table"] + tp
+        sh1, sc1, g1, sh2, sc2, g2 = (mod[:, j:j + 1] for j in range(6))
+        u = rms(x, sd[p + "self_attn_norm.weight"]) * (1 + sc1) + sh1
+        x = x + g1 * attn(p + "self_attn", u, u, True, band if i % 2 == 0 else None)
+        x = x + attn(p + "cross_attn", rms(x, sd[p + "cross_attn_norm.weight"]), enc, False, None)
+        u = rms(x, sd[p + "mlp_norm.weight"]) * (1 + sc2) + sh2
+        x = x + g2 * lin(F.silu(lin(u, p + "mlp.gate_proj")) * lin(u, p + "mlp.up_proj"), p + "mlp.down_proj")
+    fm = sd["decoder.scale_shift_table"] + te[:, None]
+    xo = rms(x, sd["decoder.norm_out.weight"]) * (1 + fm[:, 1:2]) + fm[:, 0:1]
+    want = F.conv_transpose1d(xo.transpose(1, 2), sd["decoder.proj_out.1.weight"], sd["decoder.proj_out.1.bias"], stride=2).transpose(1, 2)[:, :T]
+    assert got.shape == want.shape == (B, T, cfg.acoustic_dim) and (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
