@@ -110,3 +110,51 @@ def test_registry_admission():
     assert j["schema"] == "serenity.samplers.v1" and "res_2s" in j["samplers"]
     k = registry.karras_sigmas(5, 0.03, 14.6)
     assert abs(k[0] - 14.6) < 1e-9 and abs(k[-2] - 0.03) < 1e-9 and k[-1] == 0.0
+
+
+def test_family_schedules():
+    """Ideogram-4, Cosmos, ACE-Step, Lens, Krea-2 and HiDream-O1 schedule tables against their closed forms and anchors."""
+    import math
+    import torch
+    from mojodiffusion_b200.sampling import family_schedules as S
+    # Ideogram-4: the median of the logit-normal sits at 1 - sigmoid(mean); the ends are clamped by the log-SNR window
+    mean = S.ideogram4_schedule_mean(1024, 1024)
+    assert abs(mean - (1.0 + 0.5 * math.log(4.0))) < 1e-12
+    assert abs(S.ideogram4_logitnormal(0.5, mean) - (1 - 1 / (1 + math.exp(-mean)))) < 1e-12
+    lv = S.ideogram4_levels(10, 1024, 1024)
+    assert len(lv) == 11 and all(a > b for a, b in zip(lv, lv[1:]))
+    assert abs(lv[0] - 1 / (1 + math.exp(-7.5))) < 1e-12 and abs(lv[-1] - 1 / (1 + math.exp(9.0))) < 1e-12
+    assert abs(S.ideogram4_logitnormal(0.975, 0.0) - (1 - 1 / (1 + math.exp(-1.959963984540054)))) < 1e-9
+    # Cosmos: first sigma 0.9998 at shift 5, 35 steps
+    cs = S.cosmos_rf_sigmas(35, 5.0)
+    assert len(cs) == 36 and cs[-1] == 0.0 and abs(cs[0] - 5 * 0.999 / (1 + 4 * 0.999)) < 1e-12 and abs(cs[0] - 0.9998) < 1e-4
+    assert S.cosmos_timesteps(cs)[0] == cs[0] * 1000 and len(S.cosmos_timesteps(cs)) == 35
+    # ACE-Step
+    a = S.acestep_sigmas(8, 3.0)
+    assert len(a) == 9 and a[0] == 1.0 and a[-1] == 0.0 and abs(a[4] - 3 * 0.5 / (1 + 2 * 0.5)) < 1e-12
+    x, v = torch.ones(3), torch.full((3,), 2.0)
+    assert torch.allclose(S.acestep_euler_step(x, v, 0.8, 0.5), x - v * 0.3)
+    # Lens: documented anchor mu(4096 tokens, 20 steps) = 2.1980220725551165
+    assert abs(S.lens_empirical_mu(S.lens_image_seq_len(1024, 1024), 20) - 2.1980220725551165) < 1e-12
+    ls = S.lens_sigmas(20, 4096)
+    assert len(ls) == 20 and ls[0] == 1.0 and all(p > q for p, q in zip(ls, ls[1:]))
+    e = math.exp(2.1980220725551165)
+    assert abs(ls[-1] - e * 0.05 / (e * 0.05 + 0.95)) < 1e-12
+    assert abs(S.lens_empirical_mu(5000, 7) - (0.00016927 * 5000 + 0.45666666)) < 1e-12
+    # Krea-2: the line through (256 tokens, 0.5) and (6400 tokens, 1.15)
+    assert abs(S.krea2_mu(256) - 0.5) < 1e-12 and abs(S.krea2_mu(6400) - 1.15) < 1e-12
+    kt = S.krea2_timesteps(S.krea2_packed_seq_len(1024, 1024), 4)
+    mu = S.krea2_mu(4096)
+    assert kt[0] == 1.0 and kt[-1] == 0.0 and abs(kt[2] - math.exp(mu) / (math.exp(mu) + 1.0)) < 1e-12
+    assert abs(S.krea2_timesteps(4096, 4, mu=1.15)[2] - math.exp(1.15) / (math.exp(1.15) + 1)) < 1e-12
+    assert torch.allclose(S.krea2_cfg(torch.tensor([2.0]), torch.tensor([1.0]), 3.0), torch.tensor([5.0]))
+    # HiDream-O1
+    d = S.HiDreamO1Scheduler.dev()
+    assert len(d.timesteps) == 28 and d.sigmas[0] == 0.999 and d.sigmas[-1] == 0.0 and d.flash
+    f = S.HiDreamO1Scheduler.full(5, 3.0)
+    assert abs(f.sigmas[0] - 1.0) < 1e-12 and abs(f.sigmas[4] - 3 * 0.001 / (1 + 2 * 0.001)) < 1e-12 and not f.flash
+    smp, mo, nz = torch.randn(4, 8), torch.randn(4, 8), torch.randn(4, 8) * 3
+    assert torch.allclose(f.step(mo, 1, smp), smp + (f.sigmas[2] - f.sigmas[1]) * mo)
+    out = d.step(mo, 0, smp, nz, s_noise=1.0, noise_clip_std=1.0)
+    clip = float(nz.std(unbiased=False))
+    assert torch.allclose(out, d.sigmas[1] * nz.clamp(-clip, clip) + (1 - d.sigmas[1]) * (smp - d.sigmas[0] * mo), atol=1e-6)
