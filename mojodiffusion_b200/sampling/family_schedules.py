@@ -162,3 +162,40 @@ class HiDreamO1Scheduler:
             clip = noise_clip_std * float(n.float().std(unbiased=False))
             n = n.clamp(-clip, clip)
         return nxt * s_noise * n + (1.0 - nxt) * denoised
+
+
+# ---- PiD / PixelDiT distilled super-resolution decoder ---------------------------------------------------------------------
+PID_STUDENT_TIMES = (0.999, 0.866, 0.634, 0.342, 0.0)      # the released 4-step student schedule
+PID_TIMESCALE = 1000.0
+
+
+def pid_distill_sample(model_fn, x: torch.Tensor, noise_fn, times=PID_STUDENT_TIMES) -> torch.Tensor:
+    """Few-step stochastic sampling of a distilled velocity model in pixel space: at every step the clean estimate
+    ``x - t v`` is re-noised to the next time with fresh noise, ``(1 - t') x0 + t' eps``; the result is clamped to [-1, 1].
+    ``model_fn(x, t * 1000)`` returns the velocity, ``noise_fn()`` a standard normal tensor of x's shape
+    (serenitymojo/sampling/pid_distill.mojo:1-199)."""
+    for t, t_next in zip(times[:-1], times[1:]):
+        x0 = x - t * model_fn(x, t * PID_TIMESCALE).to(x.dtype)
+        x = (1.0 - t_next) * x0 + t_next * noise_fn().to(x.dtype) if t_next > 0.0 else x0
+    return x.clamp(-1.0, 1.0)
+
+
+# ---- Lance T2V ---------------------------------------------------------------------------------------------------------------
+def lance_times(num_steps: int, shift: float) -> List[float]:
+    if num_steps <= 0 or shift <= 0:
+        raise ValueError("lance_times: num_steps and shift must be positive")
+    return shifted_sigmas(num_steps, shift)
+
+
+def lance_cfg_renorm(v_cond: torch.Tensor, v_uncond: torch.Tensor, scale: float, renorm_min: float = 0.0,
+                     renorm_max: float = 1.0) -> torch.Tensor:
+    """Textbook guidance followed by a global renormalisation: the guided velocity is scaled by
+    clamp(||v_cond|| / (||v_cfg|| + 1e-8), renorm_min, renorm_max), norms over the whole tensor, no host read-back
+    (serenitymojo/sampling/lance_t2v.mojo:41-352)."""
+    v = v_uncond + scale * (v_cond - v_uncond)
+    ratio = (v_cond.float().square().sum().sqrt() / (v.float().square().sum().sqrt() + 1e-8)).clamp(renorm_min, renorm_max)
+    return (v.float() * ratio).to(v.dtype)
+
+
+def lance_denoise_step(x: torch.Tensor, v: torch.Tensor, t_curr: float, t_next: float) -> torch.Tensor:
+    return x - (t_curr - t_next) * v

@@ -158,3 +158,45 @@ def test_family_schedules():
     out = d.step(mo, 0, smp, nz, s_noise=1.0, noise_clip_std=1.0)
     clip = float(nz.std(unbiased=False))
     assert torch.allclose(out, d.sigmas[1] * nz.clamp(-clip, clip) + (1 - d.sigmas[1]) * (smp - d.sigmas[0] * mo), atol=1e-6)
+
+
+def test_pid_lance_samplers_and_lance_kv_plan():
+    import dataclasses
+    import pytest
+    import torch
+    from mojodiffusion_b200.runtime import lance_kv_plan as K
+    from mojodiffusion_b200.sampling import family_schedules as S
+    # PiD: with the exact velocity of a straight path and zero fresh noise the sample lands on the data
+    x0, eps = torch.rand(1, 3, 4, 4) * 1.6 - 0.8, torch.randn(1, 3, 4, 4)
+    seen = []
+
+    def model(x, t):
+        seen.append(t)
+        return (x - x0) / (t / 1000.0)                 # v with x = x0 + t (eps' ) for whichever noise is in x
+    out = S.pid_distill_sample(model, 0.001 * x0 + 0.999 * eps, lambda: torch.zeros_like(x0))
+    assert seen == [999.0, 866.0, 634.0, 342.0] and torch.allclose(out, x0, atol=1e-5)
+    assert S.pid_distill_sample(lambda x, t: torch.zeros_like(x), torch.full((2,), 5.0), lambda: torch.zeros(2), times=(0.5, 0.0)).max() == 1.0
+    # Lance: schedule, renormalised guidance, Euler step
+    lt = S.lance_times(4, 3.0)
+    assert lt[0] == 1.0 and lt[-1] == 0.0 and abs(lt[2] - 3 * 0.5 / 2.0) < 1e-12
+    vc, vu = torch.tensor([3.0, 4.0]), torch.tensor([0.0, 0.0])
+    g = S.lance_cfg_renorm(vc, vu, 5.0)                # guided norm 25 -> ratio 0.2 -> back to norm 5
+    assert torch.allclose(g, vc, atol=1e-5)
+    assert torch.allclose(S.lance_cfg_renorm(vc, vu, 0.5, 0.0, 1.0), vc * 0.5)        # ratio 2 clamped to 1
+    assert torch.allclose(S.lance_denoise_step(torch.ones(2), torch.ones(2), 0.8, 0.5), torch.full((2,), 0.7))
+    # KV plan: 5 text tokens, 2 x 2 x 3 latent grid
+    gen = 12
+    total = 5 + 1 + gen + 1
+    inp = K.LanceInput(list(range(total)), [0] * total, [0] * total, [0] * total, 5, 6, gen, list(range(gen)))
+    plan = K.text_drop_plan(inp)
+    K.validate_plan(inp, plan, 4, (2, 2, 3))
+    c, u = K.layer_call(plan, K.BRANCH_COND, 3), K.layer_call(plan, K.BRANCH_TEXT_UNCOND, 3)
+    assert (c.source_query_start, c.packed_query_start, c.attention_kv_len, c.prefix_cache_write_len) == (5, 5, total, 5)
+    assert (u.source_query_start, u.packed_query_start, u.attention_kv_len, u.prefix_cache_write_len) == (5, 0, gen + 2, 0)
+    assert plan.total_kv_bytes(4, 8, 128) == 5 * 8 * 128 * 2 * 2 * 4
+    with pytest.raises(ValueError):
+        K.validate_plan(inp, plan, 4, (2, 2, 2))
+    with pytest.raises(ValueError):
+        K.validate_input(dataclasses.replace(inp, gen_start=5))
+    with pytest.raises(ValueError):
+        K.layer_call(plan, 2, 0)
