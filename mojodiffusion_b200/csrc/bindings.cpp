@@ -755,6 +755,29 @@ void adamw_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems,
                            (unsigned int)seed, stochastic, status_ptr(table), cur_stream()),
            "adamw_multi");
 }
+void lion_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, bool p_bf16, bool g_bf16, double lr,
+                double beta1, double beta2, double wd, double grad_scale) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() && table.size(-1) == 6, "lion: table [n,6] int64");
+  TORCH_CHECK(chunks.is_cuda() && chunks.scalar_type() == at::kInt && chunks.is_contiguous() && chunks.size(-1) == 2, "lion: chunks [c,2] int32");
+  c10::cuda::CUDAGuard guard(table.device());
+  check_rc(mdb_lion_multi((const MdbTensorEntry*)table.data_ptr(), chunks.data_ptr<int>(), (int)chunks.size(0), (int)chunk_elems,
+                          p_bf16, g_bf16, (float)lr, (float)beta1, (float)beta2, (float)wd, (float)grad_scale,
+                          status_ptr(table), cur_stream()),
+           "lion_multi");
+}
+// beta1h / beta2h: the debiased betas of this step; returns the per-tensor sums of g^2 / max(v, eps^2)
+Tensor stable_adamw_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, bool p_bf16, bool g_bf16, double lr,
+                          double beta1h, double beta2h, double eps, double wd, double grad_scale) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() && table.size(-1) == 6, "stable_adamw: table [n,6] int64");
+  TORCH_CHECK(chunks.is_cuda() && chunks.scalar_type() == at::kInt && chunks.is_contiguous() && chunks.size(-1) == 2, "stable_adamw: chunks [c,2] int32");
+  c10::cuda::CUDAGuard guard(table.device());
+  Tensor acc = at::zeros({table.size(0)}, table.options().dtype(at::kFloat));
+  check_rc(mdb_stable_adamw_multi((const MdbTensorEntry*)table.data_ptr(), chunks.data_ptr<int>(), (int)chunks.size(0),
+                                  (int)chunk_elems, p_bf16, g_bf16, (float)lr, (float)beta1h, (float)beta2h, (float)eps,
+                                  (float)wd, (float)grad_scale, acc.data_ptr<float>(), status_ptr(table), cur_stream()),
+           "stable_adamw_multi");
+  return acc;
+}
 Tensor sumsq_multi(const Tensor& table, const Tensor& chunks, int64_t chunk_elems, bool g_bf16) {
   c10::cuda::CUDAGuard guard(table.device());
   Tensor out = at::zeros({}, table.options().dtype(at::kFloat));
@@ -983,6 +1006,8 @@ TORCH_LIBRARY(mdb200, m) {
   m.def("gemm_mxfp8", &gemm_mxfp8);
   m.def("mx_quant", &mx_quant);
   m.def("adamw_multi", &adamw_multi);
+  m.def("lion_multi", &lion_multi);
+  m.def("stable_adamw_multi", &stable_adamw_multi);
   m.def("sumsq_multi", &sumsq_multi);
   m.def("ema_multi", &ema_multi);
   m.def("adamw8bit", &adamw8bit);

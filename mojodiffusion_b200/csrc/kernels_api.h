@@ -113,6 +113,11 @@ int mdb_group_norm_static_ws(const void* x, void* y, const void* w, const void* 
                              float eps, int act, cudaStream_t st);
 
 // ---- optim.cu
+int mdb_lion_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16, int g_bf16,
+                   float lr, float beta1, float beta2, float wd, float grad_scale, const int* status, cudaStream_t st);
+int mdb_stable_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
+                           int g_bf16, float lr, float beta1h, float beta2h, float eps, float wd, float grad_scale,
+                           float* rms_acc, const int* status, cudaStream_t st);
 int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
                     int g_bf16, int m_bf16, float lr, float beta1, float beta2, float eps, float wd, int step,
                     float grad_scale, const float* norm_sq, float max_norm, unsigned int seed, int stochastic,

@@ -183,6 +183,124 @@ extern "C" int mdb_adamw_multi(const MdbTensorEntry* tensors, const int* chunks,
   return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Lion and StableAdamW over the same tensor table (fp32 moments; fp32 or bf16 parameters and gradients)
+// ---------------------------------------------------------------------------------------------
+// Lion: update = sign(beta1 m + (1 - beta1) g); p = p (1 - lr wd) - lr update; m = beta2 m + (1 - beta2) g
+template <typename TP, typename TG>
+__global__ void __launch_bounds__(256)
+lion_multi_kernel(const MdbTensorEntry* __restrict__ tensors, const int2* __restrict__ chunks, int num_chunks,
+                  int chunk_elems, float lr, float beta1, float beta2, float wd, float gmul, const int* status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != STATUS_OK) return;
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ch = chunks[c];
+    const MdbTensorEntry t = tensors[ch.x];
+    const long long start = static_cast<long long>(ch.y) * chunk_elems;
+    const long long end = min(start + static_cast<long long>(chunk_elems), t.numel);
+    TP* p = reinterpret_cast<TP*>(t.param);
+    const TG* g = reinterpret_cast<const TG*>(t.grad);
+    float* m = reinterpret_cast<float*>(t.exp_avg);
+    for (long long i = start + threadIdx.x; i < end; i += blockDim.x) {
+      const float grad = ldf<TG>(g, i) * gmul;
+      const float mv = m[i];
+      const float cdir = beta1 * mv + (1.f - beta1) * grad;
+      const float upd = cdir > 0.f ? 1.f : (cdir < 0.f ? -1.f : 0.f);
+      stf<TP>(p, i, ldf<TP>(p, i) * (1.f - lr * wd) - lr * upd);
+      m[i] = beta2 * mv + (1.f - beta2) * grad;
+    }
+  }
+}
+
+// StableAdamW, pass 1: moments with the debiased betas, and per tensor the sum of g^2 / max(v, eps^2)
+template <typename TG>
+__global__ void __launch_bounds__(256)
+stable_adamw_moments_kernel(const MdbTensorEntry* __restrict__ tensors, const int2* __restrict__ chunks, int num_chunks,
+                            int chunk_elems, float beta1h, float beta2h, float eps, float gmul,
+                            float* __restrict__ rms_acc, const int* status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != STATUS_OK) return;
+  __shared__ float red[8];
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ch = chunks[c];
+    const MdbTensorEntry t = tensors[ch.x];
+    const long long start = static_cast<long long>(ch.y) * chunk_elems;
+    const long long end = min(start + static_cast<long long>(chunk_elems), t.numel);
+    const TG* g = reinterpret_cast<const TG*>(t.grad);
+    float* m = reinterpret_cast<float*>(t.exp_avg);
+    float* v = reinterpret_cast<float*>(t.exp_avg_sq);
+    float acc = 0.f;
+    for (long long i = start + threadIdx.x; i < end; i += blockDim.x) {
+      const float grad = ldf<TG>(g, i) * gmul;
+      m[i] = beta1h * m[i] + (1.f - beta1h) * grad;
+      const float vv = beta2h * v[i] + (1.f - beta2h) * grad * grad;
+      v[i] = vv;
+      acc += grad * grad / fmaxf(vv, eps * eps);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) red[w] = acc;
+    __syncthreads();
+    if (w == 0) {
+      float s = l < 8 ? red[l] : 0.f;
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (l == 0) atomicAdd(rms_acc + ch.x, s);
+    }
+    __syncthreads();
+  }
+}
+
+// StableAdamW, pass 2: eta = lr / max(1, sqrt(rms_acc / numel)); p = p (1 - eta wd) - eta m / (sqrt(v) + eps)
+template <typename TP>
+__global__ void __launch_bounds__(256)
+stable_adamw_update_kernel(const MdbTensorEntry* __restrict__ tensors, const int2* __restrict__ chunks, int num_chunks,
+                           int chunk_elems, float lr, float eps, float wd, const float* __restrict__ rms_acc,
+                           const int* status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != STATUS_OK) return;
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ch = chunks[c];
+    const MdbTensorEntry t = tensors[ch.x];
+    const long long start = static_cast<long long>(ch.y) * chunk_elems;
+    const long long end = min(start + static_cast<long long>(chunk_elems), t.numel);
+    TP* p = reinterpret_cast<TP*>(t.param);
+    const float* m = reinterpret_cast<const float*>(t.exp_avg);
+    const float* v = reinterpret_cast<const float*>(t.exp_avg_sq);
+    const float rms = sqrtf(rms_acc[ch.x] / static_cast<float>(t.numel));
+    const float eta = lr / fmaxf(1.f, rms);
+    for (long long i = start + threadIdx.x; i < end; i += blockDim.x)
+      stf<TP>(p, i, ldf<TP>(p, i) * (1.f - eta * wd) - eta * m[i] / (sqrtf(v[i]) + eps));
+  }
+}
+
+extern "C" int mdb_lion_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems, int p_bf16,
+                              int g_bf16, float lr, float beta1, float beta2, float wd, float grad_scale,
+                              const int* status, cudaStream_t st) {
+  if (num_chunks <= 0) return 0;
+  const int cap = device_sm_count() * 8;
+  const int grid = num_chunks < cap ? num_chunks : cap;
+  const int2* ch = reinterpret_cast<const int2*>(chunks);
+#define MDB_LION(TP, TG) lion_multi_kernel<TP, TG><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, lr, beta1, beta2, wd, grad_scale, status)
+  if (p_bf16) { if (g_bf16) MDB_LION(bf16, bf16); else MDB_LION(bf16, float); }
+  else        { if (g_bf16) MDB_LION(float, bf16); else MDB_LION(float, float); }
+#undef MDB_LION
+  return (int)cudaGetLastError();
+}
+
+// rms_acc: one zeroed float per tensor of the table
+extern "C" int mdb_stable_adamw_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems,
+                                      int p_bf16, int g_bf16, float lr, float beta1h, float beta2h, float eps, float wd,
+                                      float grad_scale, float* rms_acc, const int* status, cudaStream_t st) {
+  if (num_chunks <= 0) return 0;
+  const int cap = device_sm_count() * 8;
+  const int grid = num_chunks < cap ? num_chunks : cap;
+  const int2* ch = reinterpret_cast<const int2*>(chunks);
+  if (g_bf16) stable_adamw_moments_kernel<bf16><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, beta1h, beta2h, eps, grad_scale, rms_acc, status);
+  else stable_adamw_moments_kernel<float><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, beta1h, beta2h, eps, grad_scale, rms_acc, status);
+  if (p_bf16) stable_adamw_update_kernel<bf16><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, lr, eps, wd, rms_acc, status);
+  else stable_adamw_update_kernel<float><<<grid, 256, 0, st>>>(tensors, ch, num_chunks, chunk_elems, lr, eps, wd, rms_acc, status);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int mdb_sumsq_multi(const MdbTensorEntry* tensors, const int* chunks, int num_chunks, int chunk_elems,
                                int g_bf16, float* out, cudaStream_t st) {
   if (num_chunks <= 0) return 0;

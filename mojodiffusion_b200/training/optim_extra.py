@@ -12,6 +12,39 @@ import torch
 from .optim import FusedAdamW
 
 
+def _device_step(opt, kind: str, grad_scale: float, lr: float, b1: float, b2: float) -> bool:
+    """Lion / StableAdamW on the GPU: every tensor in one (Lion) or two (StableAdamW: moments + per-tensor update RMS,
+    then the clipped update) multi-tensor launches over the same device table the fused AdamW uses. Returns False when the
+    parameters are not on a GPU with the native extension (the torch statements below then run)."""
+    from ..ops import native
+    from .optim import CHUNK
+    ps = [p for p in opt.params if p.grad is not None]
+    if not ps or not ps[0].is_cuda or not native.use_native(ps[0]):
+        return False
+    p0, g0 = ps[0], ps[0].grad
+    if any(p.dtype != p0.dtype or p.grad.dtype != g0.dtype or not p.is_contiguous() or not p.grad.is_contiguous() for p in ps):
+        return False
+    if p0.dtype not in (torch.float32, torch.bfloat16) or g0.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    key = tuple((p.data_ptr(), p.grad.data_ptr()) for p in ps)
+    if getattr(opt, "_table_key", None) != key:
+        rows, chunks = [], []
+        for i, p in enumerate(ps):
+            v = opt.v[id(p)].data_ptr() if hasattr(opt, "v") else 0
+            rows.append([p.data_ptr(), p.grad.data_ptr(), opt.m[id(p)].data_ptr(), v, 0, p.numel()])
+            chunks += [[i, c] for c in range((p.numel() + CHUNK - 1) // CHUNK)]
+        opt._table = (torch.tensor(rows, dtype=torch.int64).to(p0.device), torch.tensor(chunks, dtype=torch.int32).to(p0.device))
+        opt._table_key = key
+    table, ch = opt._table
+    o = native.ops()
+    pb, gb = p0.dtype == torch.bfloat16, g0.dtype == torch.bfloat16
+    if kind == "lion":
+        o.lion_multi(table, ch, CHUNK, pb, gb, lr, b1, b2, opt.wd, grad_scale)
+    else:
+        opt.last_update_rms = o.stable_adamw_multi(table, ch, CHUNK, pb, gb, lr, b1, b2, opt.eps, opt.wd, grad_scale)
+    return True
+
+
 class _Base:
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float):
         self.params = [p for p in params]
@@ -37,6 +70,8 @@ class Lion(_Base):
         lr = self.lr if lr is None else lr
         self.step_count += 1
         b1, b2 = self.betas
+        if _device_step(self, "lion", grad_scale, lr, b1, b2):
+            return
         for p, g in self._grads(grad_scale):
             m = self.m[id(p)]
             upd = torch.sign(b1 * m + (1 - b1) * g)
@@ -79,6 +114,8 @@ class StableAdamW(_Base):
         b1, b2 = self.betas
         b1h = b1 * (1 - b1 ** (t - 1)) / (1 - b1 ** t)
         b2h = b2 * (1 - b2 ** (t - 1)) / (1 - b2 ** t)
+        if _device_step(self, "stable_adamw", grad_scale, lr, b1h, b2h):
+            return
         for p, g in self._grads(grad_scale):
             m, v = self.m[id(p)], self.v[id(p)]
             m.mul_(b1h).add_(g, alpha=1 - b1h)

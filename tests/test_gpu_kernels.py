@@ -750,3 +750,29 @@ def test_linear_pads_odd_reduction_and_output_widths():
         (xr @ wr.t() + b.float()).square().sum().backward()
         _check(xg.grad, xr.grad, rel=5e-2, name="dx of padded linear")
         _check(wg.grad, wr.grad, rel=5e-2, name="dw of padded linear")
+
+
+def test_lion_and_stable_adamw_device_kernels_match_the_torch_statements():
+    """Lion and StableAdamW: the multi-tensor device launches against the same optimizers' torch statements on the CPU,
+    several steps, fp32 and bf16 parameters, tensors of unequal size."""
+    from mojodiffusion_b200.training.optim_extra import Lion, StableAdamW
+    for cls, kw in ((Lion, dict(lr=1e-2, weight_decay=0.1)), (StableAdamW, dict(lr=1e-2, weight_decay=0.1))):
+        for dt in (torch.float32, torch.bfloat16):
+            g = torch.Generator().manual_seed(3)
+            shapes = [(300, 70), (5000,), (17,)]
+            cpu = [torch.nn.Parameter(torch.randn(s, generator=g).to(dt)) for s in shapes]
+            gpu = [torch.nn.Parameter(p.detach().clone().to(DEV)) for p in cpu]
+            oc, og = cls(cpu, **kw), cls(gpu, **kw)
+            for step in range(4):
+                for pc, pg in zip(cpu, gpu):
+                    gr = torch.randn(pc.shape, generator=g) * (1.0 + step)
+                    pc.grad, pg.grad = gr.to(dt), gr.to(dt).to(DEV)
+                oc.step(grad_scale=0.5)
+                og.step(grad_scale=0.5)
+            torch.cuda.synchronize()
+            native.check_status()
+            assert getattr(og, "_table", None) is not None, "the device path did not run"
+            for pc, pg in zip(cpu, gpu):
+                tol = 3e-2 if dt == torch.bfloat16 else 2e-5
+                assert (pc.detach().float() - pg.detach().float().cpu()).abs().max() < tol, (cls.__name__, dt)
+                assert (oc.m[id(pc)] - og.m[id(pg)].cpu()).abs().max() < 1e-4
