@@ -125,6 +125,87 @@ class StableAdamW(_Base):
             p.copy_((p.float() * (1 - eta * self.wd) - eta * m / (v.sqrt() + self.eps)).to(p.dtype))
 
 
+class Automagic3(_Base):
+    """Self-tuning optimizer: a magnitude-normalised update from a factored second moment, and ONE learning rate for the
+    whole parameter group that a per-element vote over the last ``history`` update signs raises or lowers every step.
+
+    Per tensor: for matrices row = b2 row + (1 - b2)(mean_cols(g^2) + eps), col likewise over rows, update =
+    rsqrt(row / mean(row)) x rsqrt(col) * g; for vectors v = b2 v + (1 - b2) g^2, update = rsqrt(v + eps) g. The update is
+    divided by max(RMS(update) / clip, 1) and clamped to +-clip. Vote: an element whose last H update signs all agree adds
+    +|update| ("step too small"), one whose signs alternate perfectly adds -|update| ("overshoot"); pooled over every
+    element of every tensor, lr *= exp(clamp(sum / sum|update|, -1, 1)), once per step, and not before a tensor's window is
+    full. The parameter step uses the learning rate from before the vote; weight decay is added to the update. bf16
+    parameters are written back with stochastic rounding (a uniform dither in the 16 dropped mantissa bits, then
+    truncation): at the small self-chosen rates round-to-nearest would leave most weights unchanged.
+    The scheduler's learning rate is ignored after the first step (serenitymojo/training/automagic3.mojo:1-500)."""
+
+    LR_MIN, LR_MAX = 1e-30, 1e3
+
+    def __init__(self, params, lr=1e-6, beta2=0.999, eps=1e-30, clip=1.0, weight_decay=0.0, history=8, seed=0):
+        super().__init__(params, lr)
+        self.beta2, self.eps, self.clip, self.wd = beta2, eps, clip, weight_decay
+        self.h = min(max(int(history), 2), 64)
+        self.state = {}
+        self.gen = {}
+        self.seed = seed
+
+    def _rng(self, device):
+        key = str(device)
+        if key not in self.gen:
+            self.gen[key] = torch.Generator(device=device).manual_seed(0x9E3779B97F4A7C15 % (2 ** 63) + self.seed)
+        return self.gen[key]
+
+    @torch.no_grad()
+    def step(self, grad_scale: float = 1.0, lr: Optional[float] = None):
+        self.step_count += 1
+        b2, H = self.beta2, self.h
+        num = den = 0.0
+        for p, g in self._grads(grad_scale):
+            g = torch.nan_to_num(g, nan=0.0, posinf=0.0, neginf=0.0)
+            st = self.state.setdefault(id(p), {"idx": 0, "fill": 0})
+            sq = g * g
+            if g.dim() >= 2:
+                if "row" not in st:
+                    st["row"] = torch.zeros(g.shape[:-1], dtype=torch.float32, device=g.device)
+                    st["col"] = torch.zeros(g.shape[:-2] + g.shape[-1:], dtype=torch.float32, device=g.device)
+                st["row"].mul_(b2).add_(sq.mean(-1) + self.eps, alpha=1 - b2)
+                st["col"].mul_(b2).add_(sq.mean(-2) + self.eps, alpha=1 - b2)
+                r = torch.rsqrt(st["row"] / st["row"].mean(-1, keepdim=True))
+                upd = r.unsqueeze(-1) * torch.rsqrt(st["col"]).unsqueeze(-2) * g
+            else:
+                if "v" not in st:
+                    st["v"] = torch.zeros_like(g)
+                st["v"].mul_(b2).add_(sq, alpha=1 - b2)
+                upd = torch.rsqrt(st["v"] + self.eps) * g
+            upd = upd / max(float(upd.square().mean().sqrt()) / self.clip, 1.0)
+            upd = upd.clamp(-self.clip, self.clip)
+            flat = upd.reshape(-1)
+            if "hist" not in st:
+                st["hist"] = torch.zeros(H, flat.numel(), dtype=torch.bool, device=g.device)
+            st["hist"][st["idx"]] = flat > 0
+            st["idx"] = (st["idx"] + 1) % H
+            st["fill"] = min(st["fill"] + 1, H)
+            if st["fill"] == H:
+                hist = torch.roll(st["hist"], -st["idx"], 0)                    # oldest plane first
+                s1 = hist.sum(0)
+                agree = (s1 == H) | (s1 == 0)
+                alternate = ((hist[1:] != hist[:-1]).sum(0) == H - 1) & ~agree
+                w = flat.abs().double()
+                num += float((w * agree).sum() - (w * alternate).sum())
+                den += float(w.sum())
+            if self.wd:
+                upd = upd + self.wd * p.float()
+            new = p.float() - self.lr * upd
+            if p.dtype == torch.bfloat16:
+                bits = new.contiguous().view(torch.int32)
+                dither = torch.randint(0, 1 << 16, bits.shape, dtype=torch.int32, device=bits.device, generator=self._rng(bits.device))
+                new = ((bits + dither) & ~0xFFFF).view(torch.float32)
+            p.copy_(new.to(p.dtype))
+        if den > 0.0:
+            signal = min(max(num / max(den, 1e-30), -1.0), 1.0)
+            self.lr = min(max(self.lr * math.exp(signal), self.LR_MIN), self.LR_MAX)
+
+
 class Adafactor(_Base):
     """Factored second moments for matrices (row / column statistics), relative step off, no first moment."""
 
@@ -349,6 +430,8 @@ def create_optimizer(name: str, params, lr: float, betas=(0.9, 0.999), eps=1e-8,
         return StableAdamW(params, lr, (betas[0], 0.99), eps, weight_decay)
     if n == "ADAFACTOR":
         return Adafactor(params, lr, weight_decay=weight_decay)
+    if n in ("AUTOMAGIC3", "AUTOMAGIC"):
+        return Automagic3(params, lr, weight_decay=weight_decay)
     if n == "PRODIGY":
         return Prodigy(params, lr if lr >= 0.1 else 1.0, betas, eps, weight_decay)
     if n in ("SCHEDULE_FREE_ADAMW", "ADAMW_SCHEDULEFREE"):

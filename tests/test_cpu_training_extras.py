@@ -449,3 +449,55 @@ def test_epoch_unit_cadence_fires_at_epoch_boundaries(tmp_path):
     assert len(names) == 2 and names[0].endswith("-save-3-1-0.safetensors") and names[1].endswith("-save-6-2-0.safetensors"), names
     assert calls["pre"] == 3 and calls["bar"] == 3          # two epoch saves + the final backup
     assert len(run.losses) == 3                              # read back every second step only
+
+
+def test_automagic3_update_vote_and_stochastic_rounding():
+    import math
+    import torch
+    from mojodiffusion_b200.training.optim_extra import Automagic3, create_optimizer
+    torch.manual_seed(0)
+    # factored update of one step against the loop statement
+    p = torch.nn.Parameter(torch.zeros(3, 4))
+    g = torch.randn(3, 4)
+    p.grad = g.clone()
+    opt = Automagic3([p], lr=1e-3, beta2=0.9, eps=1e-30, clip=1.0)
+    opt.step()
+    row = 0.1 * ((g * g).mean(1) + 1e-30)
+    col = 0.1 * ((g * g).mean(0) + 1e-30)
+    upd = torch.zeros(3, 4)
+    for i in range(3):
+        for j in range(4):
+            upd[i, j] = (row[i] / row.mean()) ** -0.5 * col[j] ** -0.5 * g[i, j]
+    upd = (upd / max(float(upd.square().mean().sqrt()) / 1.0, 1.0)).clamp(-1, 1)
+    assert torch.allclose(p.detach(), -1e-3 * upd, atol=1e-7)
+    # vote: abstains for H steps, then constant-sign gradients multiply the rate by e per step, alternating ones divide
+    q = torch.nn.Parameter(torch.zeros(6))
+    o2 = Automagic3([q], lr=1e-4, history=4)
+    rates = []
+    for _ in range(7):
+        q.grad = torch.ones(6)
+        o2.step()
+        rates.append(o2.lr)
+    assert rates[:3] == [1e-4] * 3 and all(abs(rates[i + 1] / rates[i] - math.e) < 1e-9 for i in range(3, 6))
+    o3 = Automagic3([torch.nn.Parameter(torch.zeros(6))], lr=1e-4, history=4)
+    r3 = []
+    for k in range(7):
+        o3.params[0].grad = torch.full((6,), 1.0 if k % 2 == 0 else -1.0)
+        o3.step()
+        r3.append(o3.lr)
+    assert r3[:3] == [1e-4] * 3 and abs(r3[4] / r3[3] - math.exp(-1)) < 1e-9
+    # mixed histories neither raise nor lower
+    o4 = Automagic3([torch.nn.Parameter(torch.zeros(2))], lr=1e-4, history=4)
+    for sgn in (1, 1, -1, -1, 1, 1):
+        o4.params[0].grad = torch.full((2,), float(sgn))
+        o4.step()
+    assert o4.lr == 1e-4
+    # bf16 weights keep moving at a step far below one bf16 ulp (unbiased stochastic rounding)
+    w = torch.nn.Parameter(torch.full((4096,), 0.1, dtype=torch.bfloat16))
+    o5 = Automagic3([w], lr=1e-5, history=64)
+    for _ in range(50):
+        w.grad = torch.ones(4096, dtype=torch.bfloat16)
+        o5.step()
+    moved = 0.1 - float(w.detach().float().mean())
+    assert 0.6 * 50e-5 < moved < 1.4 * 50e-5            # expected 50 steps x 1e-5 x |update| = 1
+    assert isinstance(create_optimizer("automagic3", [torch.nn.Parameter(torch.zeros(2))], 1e-6), Automagic3)
