@@ -10,7 +10,10 @@
 // Routes and behaviour follow serenity-server/crates/server/src/main.rs:1326-1532 (driver), :1974-2330 (generate),
 // :2335-2460 (progress socket), :3648-3690 (route table), jobs.rs, gallery.rs, result_manifest.rs, capabilities.rs.
 #include <dirent.h>
+#include <poll.h>
 #include <sys/stat.h>
+#include <sys/wait.h>
+#include <unistd.h>
 
 #include <atomic>
 #include <chrono>
@@ -152,6 +155,8 @@ struct Job {
 
 struct App {
   std::string out_dir, models_dir, worker_cmd;
+  std::string llm_dir;                                   // language models for /v1/llms and /v1/magic_prompt
+  std::string magic_cmd = "python -m mojodiffusion_b200.captioner.magic_prompt";
   int settle_ms = 800;
   std::mutex mu;
   std::condition_variable cv;
@@ -611,6 +616,80 @@ static void list_models(const App& app, Json& out) {
   out.set("models", arr);
 }
 
+// ---- prompt generator: language models on disk, one throw-away process per request --------------------------------------
+static bool ends_with(const std::string& s, const char* suf) { size_t n = strlen(suf); return s.size() >= n && s.compare(s.size() - n, n, suf) == 0; }
+static void scan_llms(const std::string& dir, bool deep, std::vector<Json>* out) {
+  std::vector<std::string> names;
+  if (DIR* d = opendir(dir.c_str())) {
+    while (dirent* e = readdir(d)) { std::string n = e->d_name; if (n != "." && n != "..") names.push_back(n); }
+    closedir(d);
+  } else return;
+  std::sort(names.begin(), names.end());
+  auto add = [&](const std::string& path, int64_t size) {
+    std::string base = path.substr(path.find_last_of('/') + 1);
+    size_t dot = base.find_last_of('.');
+    Json m = Json::object();
+    m.set("id", Json(path)); m.set("name", Json(dot == std::string::npos || !ends_with(base, ".gguf") ? base : base.substr(0, dot)));
+    m.set("path", Json(path)); m.set("size", Json(size));
+    out->push_back(m);
+  };
+  bool has_cfg = false; int64_t st_bytes = 0; bool has_st = false;
+  for (auto& n : names) { if (n == "config.json") has_cfg = true; if (ends_with(n, ".safetensors")) { has_st = true; st_bytes += file_size(dir + "/" + n); } }
+  if (has_cfg && has_st) { add(dir, st_bytes); return; }
+  for (auto& n : names) {
+    std::string full = dir + "/" + n;
+    struct stat st;
+    if (stat(full.c_str(), &st) != 0) continue;
+    if (S_ISDIR(st.st_mode)) { if (deep) scan_llms(full, false, out); }
+    else if (ends_with(n, ".gguf")) add(full, st.st_size);
+  }
+}
+// run argv, collect stdout and stderr (each at most 1 MiB), kill it after timeout_s; returns the exit status or -1
+static int run_capture(const std::vector<std::string>& argv, int timeout_s, std::string* out, std::string* err) {
+  int po[2], pe[2];
+  if (pipe(po) != 0) return -1;
+  if (pipe(pe) != 0) { close(po[0]); close(po[1]); return -1; }
+  pid_t pid = fork();
+  if (pid < 0) { close(po[0]); close(po[1]); close(pe[0]); close(pe[1]); return -1; }
+  if (pid == 0) {
+    dup2(po[1], 1); dup2(pe[1], 2);
+    close(po[0]); close(po[1]); close(pe[0]); close(pe[1]);
+    std::vector<char*> av;
+    for (auto& a : argv) av.push_back(const_cast<char*>(a.c_str()));
+    av.push_back(nullptr);
+    execvp(av[0], av.data());
+    _exit(127);
+  }
+  close(po[1]); close(pe[1]);
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(timeout_s);
+  pollfd fds[2] = {{po[0], POLLIN, 0}, {pe[0], POLLIN, 0}};
+  int open_fds = 2;
+  bool timed_out = false;
+  char buf[4096];
+  while (open_fds > 0) {
+    auto left = std::chrono::duration_cast<std::chrono::milliseconds>(deadline - std::chrono::steady_clock::now()).count();
+    if (left <= 0) { timed_out = true; break; }
+    int r = poll(fds, 2, static_cast<int>(std::min<long long>(left, 1000)));
+    if (r < 0) break;
+    for (int i = 0; i < 2; ++i) {
+      if (fds[i].fd < 0 || !(fds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
+      ssize_t n = read(fds[i].fd, buf, sizeof(buf));
+      if (n > 0) { std::string* dst = i == 0 ? out : err; if (dst->size() < (1u << 20)) dst->append(buf, static_cast<size_t>(n)); }
+      else { close(fds[i].fd); fds[i].fd = -1; --open_fds; }
+    }
+  }
+  for (auto& f : fds) if (f.fd >= 0) close(f.fd);
+  if (timed_out) kill(pid, SIGKILL);
+  int status = 0;
+  waitpid(pid, &status, 0);
+  if (timed_out) { *err += "timed out"; return -1; }
+  return WIFEXITED(status) ? WEXITSTATUS(status) : -1;
+}
+static std::string trim(const std::string& s) {
+  size_t a = s.find_first_not_of(" \t\r\n"), b = s.find_last_not_of(" \t\r\n");
+  return a == std::string::npos ? "" : s.substr(a, b - a + 1);
+}
+
 static Json gallery_items(App& app) {
   Json meta;
   std::string raw;
@@ -1005,8 +1084,39 @@ static void handle(App& app, const http::Request& rq, http::Response& rs) {
     if (system("command -v ffprobe >/dev/null 2>&1") != 0) return reply_error(rs, 501, "ffprobe is not available on PATH", "serenity.video_error.v1");
     return reply_error(rs, 501, "container probing is not built: only PNG frame directories are produced here", "serenity.video_error.v1");
   }
-  if (p == "/v1/llms" || p == "/v1/magic_prompt")
-    return reply_error(rs, 501, "not available in this build: " + p);
+  if (p == "/v1/llms") {
+    std::vector<Json> found;
+    if (!app.llm_dir.empty()) scan_llms(app.llm_dir, true, &found);
+    std::sort(found.begin(), found.end(), [](const Json& a, const Json& b) { return a.str("name") < b.str("name"); });
+    Json arr = Json::array();
+    for (auto& f : found) arr.push(f);
+    Json o = Json::object();
+    o.set("llms", arr);
+    return reply(rs, 200, o);
+  }
+  if (p == "/v1/magic_prompt") {
+    if (m != "POST") return reply_error(rs, 405, "POST {idea, aspect, model}");
+    Json b;
+    if (!Json::try_parse(rq.body, &b)) return reply_error(rs, 400, "bad json");
+    std::string idea = trim(b.str("idea")), aspect = b.str("aspect", "1:1"), model = b.str("model");
+    if (idea.empty()) return reply_error(rs, 400, "idea required");
+    bool stub = model.compare(0, 5, "stub:") == 0;
+    if (model.empty() || !file_exists(stub ? model.substr(5) : model))
+      return reply_error(rs, 400, "valid model path required");
+    // one throw-away process per request: the language model holds device memory only while it generates
+    std::vector<std::string> argv = split_cmd(app.magic_cmd, "");
+    argv.push_back(model); argv.push_back(aspect); argv.push_back(idea);
+    std::string out, err;
+    int rc = run_capture(argv, 600, &out, &err);
+    std::string caption = trim(out);
+    size_t nl = caption.find_last_of('\n');
+    if (nl != std::string::npos) caption = caption.substr(nl + 1);          // the last line is the caption
+    if (rc != 0) return reply_error(rs, 500, "magic_prompt failed: " + trim(err).substr(0, 2000));
+    if (caption.empty()) return reply_error(rs, 500, "empty caption");
+    Json o = Json::object();
+    o.set("caption", Json(caption));
+    return reply(rs, 200, o);
+  }
   if (p == "/" || p == "/index.html") {
     rs.content_type = "text/html";
     rs.body = "<!doctype html><title>mdb-server</title><h1>mdb-server</h1><p>POST /v1/generate, GET /v1/jobs, WS /v1/progress?job=ID</p>";
@@ -1028,11 +1138,13 @@ int main(int argc, char** argv) {
     else if (a == "--out-dir") app.out_dir = next();
     else if (a == "--port") port = atoi(next().c_str());
     else if (a == "--models-dir") app.models_dir = next();
+    else if (a == "--llm-dir") app.llm_dir = next();
+    else if (a == "--magic-cmd") app.magic_cmd = next();
     else if (a == "--settle-ms") app.settle_ms = atoi(next().c_str());
     else { std::cerr << "unknown argument " << a << "\n"; return 2; }
   }
   if (app.worker_cmd.empty() || app.out_dir.empty()) {
-    std::cerr << "usage: mdb-server --worker \"<cmd> [{kind}]\" --out-dir DIR [--port N] [--models-dir DIR] [--settle-ms N]\n";
+    std::cerr << "usage: mdb-server --worker \"<cmd> [{kind}]\" --out-dir DIR [--port N] [--models-dir DIR] [--llm-dir DIR] [--magic-cmd CMD] [--settle-ms N]\n";
     return 2;
   }
   while (app.out_dir.size() > 1 && app.out_dir.back() == '/') app.out_dir.pop_back();

@@ -581,3 +581,48 @@ def test_encode_phase_runs_text_encoders_in_a_child_process(bins, tmp_path):
         assert a.shape == b.shape and (a != b).any()      # the prompt reaches the image through the encoders
     finally:
         s.close()
+
+
+def test_llm_listing_and_magic_prompt_through_a_throw_away_process(bins, tmp_path):
+    """/v1/llms lists GGUF files and safetensors model directories (one level deep, sorted); /v1/magic_prompt runs the prompt
+    generator as a child process per request and returns its one-line caption; bad requests and a failing generator are
+    answered with 400 / 500 and the reason."""
+    llm = tmp_path / "llms"
+    (llm / "qwen3-4b").mkdir(parents=True)
+    (llm / "qwen3-4b" / "config.json").write_text("{}")
+    (llm / "qwen3-4b" / "model.safetensors").write_bytes(b"\0" * 32)
+    (llm / "sub").mkdir()
+    (llm / "sub" / "gemma.gguf").write_bytes(b"\0" * 8)
+    (llm / "alpha.gguf").write_bytes(b"\0" * 4)
+    (llm / "notes.txt").write_text("x")
+    reply = tmp_path / "reply.txt"
+    reply.write_text('Here you go:\n```json\n{"compositional_deconstruction":{"elements":[{"desc":"a fox","bbox":[10,20,300,400],"type":"obj"}],'
+                     '"background":"snow"},"aspect_ratio":"1:1","high_level_description":"A fox in snow"}\n```\n')
+    s = Server(bins, str(tmp_path / "out"), extra_args=("--llm-dir", str(llm), "--magic-cmd", f"{sys.executable} -m mojodiffusion_b200.captioner.magic_prompt"))
+    try:
+        st, v = s.call("GET", "/v1/llms")
+        assert st == 200 and [m["name"] for m in v["llms"]] == ["alpha", "gemma", "qwen3-4b"]
+        assert v["llms"][2]["path"].endswith("/qwen3-4b") and v["llms"][2]["size"] == 32 and v["llms"][0]["size"] == 4
+        st, v = s.call("POST", "/v1/magic_prompt", {"idea": "  a fox in snow ", "aspect": "1:1", "model": "stub:" + str(reply)})
+        assert st == 200, v
+        cap = json.loads(v["caption"])
+        assert "\n" not in v["caption"] and list(cap) == ["high_level_description", "compositional_deconstruction"]
+        assert cap["compositional_deconstruction"]["elements"][0] == {"type": "obj", "bbox": [10, 20, 300, 400], "desc": "a fox"}
+        assert s.call("POST", "/v1/magic_prompt", {"idea": " ", "model": "stub:" + str(reply)})[0] == 400
+        assert s.call("POST", "/v1/magic_prompt", {"idea": "x", "model": str(tmp_path / "missing")})[0] == 400
+        assert s.call("GET", "/v1/magic_prompt")[0] == 405
+        reply.write_text("no json in this reply")
+        st, v = s.call("POST", "/v1/magic_prompt", {"idea": "x", "model": "stub:" + str(reply)})
+        assert st == 500 and "no JSON caption" in v["error"]
+    finally:
+        s.close()
+
+
+def test_llm_listing_in_python_matches_the_route_rules(tmp_path):
+    from mojodiffusion_b200.captioner.magic_prompt import list_llms
+    (tmp_path / "m1").mkdir()
+    (tmp_path / "m1" / "config.json").write_text("{}")
+    (tmp_path / "m1" / "a.safetensors").write_bytes(b"1234")
+    (tmp_path / "z.gguf").write_bytes(b"12")
+    got = list_llms(str(tmp_path))
+    assert [(e["name"], e["size"]) for e in got] == [("m1", 4), ("z", 2)]
