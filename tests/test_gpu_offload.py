@@ -111,3 +111,67 @@ def test_streaming_is_bit_identical_under_permuted_stream_priorities():
         for o in outs:
             assert torch.isfinite(o.float()).all() and torch.equal(o, ref), f"priority {prio}"
     native.check_status()
+
+
+def test_vmm_slab_keeps_addresses_while_physical_memory_comes_and_goes():
+    """Blocks keep their device address across evict / reload; a byte budget evicts the least recently used idle block;
+    blocks in use are never evicted; a captured CUDA graph that reads a block sees the bytes loaded after a reload.
+    Unmapped ranges are never touched: views of them are refused on the host."""
+    import pytest
+    import torch
+    from mojodiffusion_b200.offload.vmm_slab import VmmSlab
+    MiB = 1 << 20
+    slab = VmmSlab([3 * MiB] * 4, budget_bytes=2 * 4 * MiB)
+    try:
+        assert slab.gran % (64 * 1024) == 0 and all(s % slab.gran == 0 and s >= 3 * MiB for s in slab.sizes)
+        free0 = torch.cuda.mem_get_info()[0]
+        addr = [slab.address(i) for i in range(4)]
+        a = slab.acquire(0)
+        assert a.numel() == 3 * MiB and a.data_ptr() == addr[0]
+        a.fill_(7)
+        slab.release(0)
+        assert slab.ensure_resident(1) is True and slab.ensure_resident(1) is False
+        slab.tensor(1).fill_(9)
+        torch.cuda.synchronize()
+        assert slab.resident_bytes == 2 * slab.sizes[0] and free0 - torch.cuda.mem_get_info()[0] >= 2 * slab.sizes[0] - MiB
+        assert slab.ensure_resident(2) is True                      # over budget: block 0 (least recently used) goes
+        assert not slab.is_resident(0) and slab.is_resident(1) and slab.is_resident(2) and slab.evictions == 1
+        with pytest.raises(RuntimeError):
+            slab.tensor(0)                                          # a view of an unmapped range is refused
+        assert [slab.address(i) for i in range(4)] == addr
+        assert int(slab.tensor(1)[12345]) == 9
+        # a block in use is never the victim
+        t2 = slab.acquire(2)
+        assert slab.ensure_resident(3) is True and slab.is_resident(2) and not slab.is_resident(1)
+        t3 = slab.acquire(3)
+        with pytest.raises(MemoryError):
+            slab.ensure_resident(0)
+        slab.release(3)
+        slab.release(2)
+        # CUDA graph over a fixed address: reload the block with other bytes, replay, see the new bytes
+        x = slab.tensor(2, torch.float32)
+        x.fill_(1.5)
+        out = torch.zeros(1, device="cuda")
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            out.copy_(x[:1024].sum().reshape(1))                    # warm-up outside capture
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out.copy_(x[:1024].sum().reshape(1))
+        g.replay()
+        torch.cuda.synchronize()
+        assert float(out) == 1.5 * 1024
+        del x, t2, t3
+        slab.evict(2)
+        assert slab.ensure_resident(2) is True and slab.address(2) == addr[2]
+        slab.tensor(2, torch.float32).fill_(2.0)
+        g.replay()
+        torch.cuda.synchronize()
+        assert float(out) == 2.0 * 1024
+        with pytest.raises(RuntimeError):
+            torch.ops.mdb200.vmm_slab_map(slab.handle, slab.offsets[2], slab.sizes[2])     # overlaps a mapped region
+    finally:
+        torch.cuda.synchronize()
+        slab.close()
