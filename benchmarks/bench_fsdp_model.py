@@ -32,6 +32,7 @@ def main():
     ap.add_argument("--mode", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--tiny", action="store_true")
     ap.add_argument("--fuse-optimizer", action="store_true", help="AdamW of the sharded weights inside the reduce-scatter tail of backward")
+    ap.add_argument("--offload-optimizer", action="store_true", help="fp32 masters and AdamW moments in pinned host memory, streamed per layer in step()")
     ap.add_argument("--depth", type=int, default=0, help="number of blocks (0: the architecture's own)")
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
@@ -55,9 +56,11 @@ def main():
     t0 = time.time()
     model = QwenImageDiT(cfg, torch.bfloat16, dev).init_weights(0)
     n_params = sum(p.numel() for p in model.parameters())
-    ctx = FSDPContext(mode=args.mode, device=dev, fuse_optimizer=args.fuse_optimizer and args.mode == "fused")
+    ctx = FSDPContext(mode=args.mode, device=dev, fuse_optimizer=args.fuse_optimizer and args.mode == "fused",
+                      offload_optimizer=args.offload_optimizer)
     n_sharded = shard_model(model, ctx)
     torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()       # the peak of the training steps, not of building the unsharded model
     rest = [p for p in model.parameters() if p.numel() > 0]
     for p in rest:
         p.requires_grad_(True)
@@ -106,7 +109,7 @@ def main():
     peak = torch.cuda.max_memory_allocated() / 2 ** 30
     if rank == 0:
         row = {"metric": "full-finetune samples/s", "value": world * 1000.0 / ms, "ms_per_step": ms, "n_gpus": world,
-               "mode": args.mode + ("+optimizer-in-backward" if ctx.fused_active() else ""), "model": cfg.name, "depth": cfg.depth, "params_b": n_params / 1e9,
+               "mode": args.mode + ("+optimizer-in-backward" if ctx.fused_active() else "") + ("+optimizer-state-on-host" if args.offload_optimizer else ""), "model": cfg.name, "depth": cfg.depth, "params_b": n_params / 1e9,
                "sharded_linears": n_sharded, "tokens": hw[0] * hw[1] + S_txt, "batch_per_gpu": 1,
                "gradient_checkpointing": True, "peak_gib_rank0": peak, "init_s": t_init,
                "losses": [float(l) for l in losses], "steps": args.steps, "warmup": args.warmup}

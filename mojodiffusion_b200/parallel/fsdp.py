@@ -40,13 +40,20 @@ class FSDPContext:
     """Owns the symmetric arena (weight shards + gradient shards of all layers), the transient gather buffer and the
     flags. Layers register themselves; ``finalize()`` allocates."""
 
-    def __init__(self, group=None, mode: str = "fused", device=None, fuse_optimizer: bool = False):
-        """``fuse_optimizer``: the reduce-scatter tail of every layer's weight gradient also applies AdamW to the owner's
+    def __init__(self, group=None, mode: str = "fused", device=None, fuse_optimizer: bool = False,
+                 offload_optimizer: bool = False):
+        """``offload_optimizer``: the fp32 master shards and both AdamW moments (12 of the 14 resident bytes per sharded
+        parameter) live in pinned host memory; ``step`` streams them through four device staging slots, layer by layer,
+        on two copy streams (one per direction) that run ahead of / behind the per-layer AdamW launches (not combinable with ``fuse_optimizer``).
+
+        ``fuse_optimizer``: the reduce-scatter tail of every layer's weight gradient also applies AdamW to the owner's
         shard (one launch per layer inside backward, no stored gradient shard); call ``begin_step`` with the step's
         hyper-parameters before backward, ``step`` afterwards only publishes the new shards. Each layer may be used once
         per step in this mode, and there is no gradient accumulation or clipping across layers."""
         self.group, self.mode = group, mode
         self.fuse_optimizer = fuse_optimizer
+        self.offload_optimizer = offload_optimizer
+        assert not (fuse_optimizer and offload_optimizer), "the fused optimizer updates device-resident state"
         self.hyper = None
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -92,6 +99,20 @@ class FSDPContext:
             l.w_shard.copy_(l.master.to(torch.bfloat16))
             l.g_shard.zero_()
         torch.cuda.synchronize(self.device)
+        if self.offload_optimizer:
+            biggest = max(l.rows_local * l.in_features for l in self.layers)
+            self._slots = [torch.empty(3, biggest, dtype=torch.float32, device=self.device) for _ in range(4)]
+            self._copy_stream = torch.cuda.Stream(self.device)       # host -> device
+            self._back_stream = torch.cuda.Stream(self.device)       # device -> host: both directions of the link run at once
+            for l in self.layers:                                  # [master | m | v] of a layer as one pinned block = one DMA each way
+                host = torch.empty(3, l.master.numel(), dtype=torch.float32).pin_memory()
+                host[0].copy_(l.master.reshape(-1))
+                host[1:].zero_()
+                l.host_state = host
+                l.master = host[0].view(l.rows_local, l.in_features)
+                l.m = host[1].view(l.rows_local, l.in_features)
+                l.v = host[2].view(l.rows_local, l.in_features)
+            torch.cuda.empty_cache()
         if self.world > 1:
             dist.barrier(self.group)
         return self
@@ -159,6 +180,15 @@ class FSDPContext:
         self.step_count += 1
         scale = (1.0 / self.world) if grad_scale is None else grad_scale
         from ..training.optim import CHUNK
+        if self.offload_optimizer:
+            self._offloaded_adamw(lr, betas, eps, weight_decay, scale)
+            for l in self.layers:
+                l.g_shard.zero_()
+            self.gathered_owner = None
+            self.barrier(SLOT_STEP_DONE)
+            if self.step_count % getattr(self, "check_every", 16) == 0:
+                self.check()
+            return
         if getattr(self, "_table", None) is None:
             rows, chunks = [], []
             for i, l in enumerate(self.layers):
@@ -176,6 +206,56 @@ class FSDPContext:
         self.barrier(SLOT_STEP_DONE)                      # new shards visible everywhere before the next gather
         if self.step_count % getattr(self, "check_every", 16) == 0:
             self.check()
+
+    def _offloaded_adamw(self, lr, betas, eps, wd, scale):
+        """Layer i's [master | m | v] block goes host -> slot i % 4 on one copy stream, AdamW runs on it in the compute
+        stream (gradient shard and bf16 weight shard stay on the device), and the block returns to the host on a second
+        copy stream while the next layers' blocks are already arriving in the other slots."""
+        from ..training.optim import CHUNK
+        cs, bs, main = self._copy_stream, self._back_stream, torch.cuda.current_stream(self.device)
+        NS = len(self._slots)
+        if getattr(self, "_off_tables", None) is None:
+            self._off_tables = []
+            for i, l in enumerate(self.layers):
+                n, slot = l.master.numel(), self._slots[i % NS]
+                row = [[slot[0].data_ptr(), l.g_shard.data_ptr(), slot[1].data_ptr(), slot[2].data_ptr(), l.w_shard.data_ptr(), n]]
+                self._off_tables.append((torch.tensor(row, dtype=torch.int64).to(self.device),
+                                         torch.tensor([[0, c] for c in range((n + CHUNK - 1) // CHUNK)], dtype=torch.int32).to(self.device)))
+        L = len(self.layers)
+        loaded = [torch.cuda.Event() for _ in range(L)]
+        updated = [torch.cuda.Event() for _ in range(L)]
+        stored = [torch.cuda.Event() for _ in range(L)]
+        cs.wait_stream(main)
+        bs.wait_stream(main)
+
+        def fetch(i):
+            n = self.layers[i].master.numel()
+            if i >= NS:
+                cs.wait_event(stored[i - NS])                     # the slot's previous block is back on the host
+            with torch.cuda.stream(cs):
+                self._slots[i % NS][:, :n].copy_(self.layers[i].host_state, non_blocking=True)
+                loaded[i].record(cs)
+
+        def write_back(i):
+            bs.wait_event(updated[i])
+            n = self.layers[i].master.numel()
+            with torch.cuda.stream(bs):
+                self.layers[i].host_state.copy_(self._slots[i % NS][:, :n], non_blocking=True)
+                stored[i].record(bs)
+        for i in range(min(NS - 1, L)):
+            fetch(i)
+        for i in range(L):
+            main.wait_event(loaded[i])
+            table, chunks = self._off_tables[i]
+            native.ops().adamw_multi(table, chunks, CHUNK, False, False, False, lr, betas[0], betas[1], eps, wd,
+                                     self.step_count, scale, None, 0.0, 0, False)
+            updated[i].record(main)
+            write_back(i)
+            if i + NS - 1 < L:
+                fetch(i + NS - 1)
+        main.wait_stream(cs)
+        main.wait_stream(bs)
+        bs.synchronize()                                          # host tensors are read by checkpointing right after step()
 
     def _adamw_over(self, idx, lr, b1, b2, eps, wd, t_step, scale):
         from ..training.optim import CHUNK
@@ -294,8 +374,9 @@ class FSDPLinear(nn.Module):
         """All-gather of the fp32 master shards (checkpointing)."""
         if self.ctx.world == 1:
             return self.master.clone()
-        parts = [torch.empty_like(self.master) for _ in range(self.ctx.world)]
-        dist.all_gather(parts, self.master, group=self.ctx.group)
+        mine = self.master.to(self.ctx.device)                  # a host-resident master (offloaded optimizer) travels by the device
+        parts = [torch.empty_like(mine) for _ in range(self.ctx.world)]
+        dist.all_gather(parts, mine, group=self.ctx.group)
         return torch.cat(parts, 0)
 
 

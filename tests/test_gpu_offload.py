@@ -175,3 +175,35 @@ def test_vmm_slab_keeps_addresses_while_physical_memory_comes_and_goes():
     finally:
         torch.cuda.synchronize()
         slab.close()
+
+
+def test_fsdp_optimizer_state_offload_matches_device_resident_state():
+    """Sharded linears with their fp32 masters and AdamW moments in pinned host memory, streamed through device staging slots
+    per step: after several training steps the master shards, the moments and the bf16 weight shards equal those of the
+    same run with device-resident state bit for bit (one process: the sharding degenerates to one shard per layer)."""
+    from mojodiffusion_b200.parallel.fsdp import FSDPContext, FSDPLinear
+
+    def run(offload):
+        ctx = FSDPContext(mode="fused", offload_optimizer=offload)
+        dims = [(256, 512), (512, 1024), (1024, 256), (256, 128)]
+        layers = [FSDPLinear(ctx, i, o, bias=False, seed=10 + k) for k, (i, o) in enumerate(dims)]
+        ctx.finalize()
+        g = torch.Generator().manual_seed(0)
+        for step in range(3):
+            x = torch.randn(64, 256, generator=g).to("cuda", torch.bfloat16)
+            h = x
+            for l in layers:
+                h = torch.tanh(l(h))
+            h.float().square().mean().backward()
+            ctx.step(lr=1e-2, weight_decay=0.1)
+        torch.cuda.synchronize()
+        ctx.check()
+        return ctx, layers
+
+    c0, l0 = run(False)
+    c1, l1 = run(True)
+    assert all(not l.master.is_cuda and l.master.is_pinned() and not l.m.is_cuda for l in l1)
+    for a, b in zip(l0, l1):
+        assert torch.equal(a.master.cpu(), b.master) and torch.equal(a.m.cpu(), b.m) and torch.equal(a.v.cpu(), b.v)
+        assert torch.equal(a.w_shard, b.w_shard)
+        assert float(b.m.abs().sum()) > 0 and torch.equal(b.full_master().cpu(), b.master)
