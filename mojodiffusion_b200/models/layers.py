@@ -40,6 +40,23 @@ class LoRASlot(nn.Module):
         return self.alpha / self.rank
 
 
+class _BlockUp(torch.autograd.Function):
+    """[N, R] matrix holding each adapter's scaled up-projection in its (row range, rank column range) block and zeros
+    elsewhere: one fill plus one multiply-into-place per adapter, and one multiply per adapter in backward."""
+
+    @staticmethod
+    def forward(ctx, n, r, places, *ups):
+        ctx.places = places
+        out = ups[0].new_zeros(n, r)
+        for (r0, r1, c0, c1, sc), u in zip(places, ups):
+            torch.mul(u, sc, out=out[r0:r1, c0:c1])
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return (None, None, None) + tuple(g[r0:r1, c0:c1] * sc for (r0, r1, c0, c1, sc) in ctx.places)
+
+
 class Linear(nn.Module):
     """``y = x W^T + b`` on the tcgen05 GEMM, with optional fused activation / gated residual and LoRA slots."""
 
@@ -75,29 +92,11 @@ class Linear(nn.Module):
             return s.down, s.up * (s.scale * self.lora_multiplier)
         down = torch.cat([s.down for s in slots], 0)
         R = down.shape[0]
-        up = self.weight.new_zeros(self.out_features, R)
-        cols = 0
-        pieces = []
+        places, c0 = [], 0
         for s in slots:
-            pieces.append((s, cols))
-            cols += s.rank
-        if torch.is_grad_enabled() and any(s.up.requires_grad for s in slots):
-            rows = []
-            # assemble differentiably: pad each up block to full width, then stack rows in order
-            cover = sorted(pieces, key=lambda t: t[0].row0)
-            cur = 0
-            for s, c0 in cover:
-                if s.row0 > cur:
-                    rows.append(self.weight.new_zeros(s.row0 - cur, R))
-                blk = torch.nn.functional.pad(s.up * (s.scale * self.lora_multiplier), (c0, R - c0 - s.rank))
-                rows.append(blk)
-                cur = s.row1
-            if cur < self.out_features:
-                rows.append(self.weight.new_zeros(self.out_features - cur, R))
-            up = torch.cat(rows, 0)
-        else:
-            for s, c0 in pieces:
-                up[s.row0:s.row1, c0:c0 + s.rank] = s.up * (s.scale * self.lora_multiplier)
+            places.append((s.row0, s.row1, c0, c0 + s.rank, s.scale * self.lora_multiplier))
+            c0 += s.rank
+        up = _BlockUp.apply(self.out_features, R, tuple(places), *[s.up for s in slots])
         return down, up
 
     # ---- forward ------------------------------------------------------------------------------
