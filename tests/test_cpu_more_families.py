@@ -592,3 +592,71 @@ def test_acestep_audio_dit_matches_plain_torch_statement():
     xo = rms(x, sd["decoder.norm_out.weight"]) * (1 + fm[:, 1:2]) + fm[:, 0:1]
     want = F.conv_transpose1d(xo.transpose(1, 2), sd["decoder.proj_out.1.weight"], sd["decoder.proj_out.1.bias"], stride=2).transpose(1, 2)[:, :T]
     assert got.shape == want.shape == (B, T, cfg.acoustic_dim) and (got - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_hidream_o1_spine_heads_mask_and_positions():
+    """HiDream-O1: the text prefix is causal and the image rows see every key, the timestep embedding replaces the reserved
+    token's embedding, positions follow the text-count / fix-point rule, and the forward equals a plain-torch statement of
+    one layer stack built from the checkpoint-named tensors."""
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models.hidream_o1 import HiDreamO1, build_mrope_positions, prefix_causal_mask, tiny_hidream_o1_config
+    from mojodiffusion_b200.models.ideogram4 import mrope_table
+    from mojodiffusion_b200.models.layers import timestep_embedding
+    torch.manual_seed(6)
+    cfg = tiny_hidream_o1_config()
+    c = cfg.spine
+    m = HiDreamO1(cfg, torch.float32).init_weights(17)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    for k in ("model.language_model.embed_tokens.weight", "model.language_model.layers.1.self_attn.k_norm.weight", "model.language_model.norm.weight",
+              "model.x_embedder.proj1.weight", "model.x_embedder.proj2.bias", "model.t_embedder1.mlp.2.weight", "model.final_layer2.linear.bias"):
+        assert k in sd, k
+    assert "model.x_embedder.proj1.bias" not in sd
+    ids = [1, 2, cfg.tms_token_id, 3, cfg.vision_start_token_id]
+    L, ph, pw = 6, 2, 3
+    pos = build_mrope_positions(ids + [cfg.image_token_id] * L, cfg.image_token_id, ph, pw, 10)
+    assert pos[:4].tolist() == [[i] * 3 for i in range(4)] and pos[4].tolist() == [10, 10, 10] and pos[9].tolist() == [10, 11, 12]
+    assert build_mrope_positions([1, 2, 3], cfg.image_token_id, 1, 1, 5).tolist() == [[0] * 3, [1] * 3, [2] * 3]
+    mk = prefix_causal_mask(4, 2)[0, 0]
+    assert mk.tolist() == [[0, -1e4, -1e4, -1e4], [0, 0, -1e4, -1e4], [0, 0, 0, 0], [0, 0, 0, 0]]
+    assert prefix_causal_mask(3, 0, torch.tensor([1, 0, 1]))[0, 0, :, 1].tolist() == [-1e4] * 3
+    patches = torch.randn(1, L, cfg.patch_dim)
+    S, ar = len(ids) + L, len(ids)
+    out = m(ids, patches, pos, ar, 0.4)
+    # causality of the prefix: changing the last text token leaves earlier text rows alone but moves the image rows
+    ids2 = list(ids)
+    ids2[-1] = 7
+    out2 = m(ids2, patches, pos, ar, 0.4)
+    assert torch.allclose(out[:, :ar - 1], out2[:, :ar - 1], atol=1e-6) and (out[:, ar:] - out2[:, ar:]).abs().max() > 1e-5
+    # the timestep reaches the output only through the reserved token's row and what attends to it
+    out3 = m(ids, patches, pos, ar, 0.9)
+    assert torch.allclose(out[:, :2], out3[:, :2], atol=1e-6) and (out[:, 2] - out3[:, 2]).abs().max() > 1e-6
+    # plain-torch statement
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, w: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + c.rms_norm_eps) * w
+    H, KV, Dh = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+    x = sd["model.language_model.embed_tokens.weight"][torch.tensor(ids)][None].clone()
+    x[0, 2] = lin(F.silu(lin(timestep_embedding(torch.tensor([0.4]), cfg.timestep_freq_dim), "model.t_embedder1.mlp.0")), "model.t_embedder1.mlp.2")[0]
+    x = torch.cat((x, lin(lin(patches, "model.x_embedder.proj1"), "model.x_embedder.proj2")), 1)
+    cs, sn = mrope_table(pos, Dh, cfg.mrope_section, c.rope_theta)
+    cosf, sinf = torch.cat((cs, cs), -1)[None, :, None], torch.cat((sn, sn), -1)[None, :, None]
+    rot = lambda v: torch.cat((-v[..., Dh // 2:], v[..., :Dh // 2]), -1)
+    i = torch.arange(S)
+    allow = (i[None] <= i[:, None]) | (i[:, None] >= ar)
+    for li in range(c.num_hidden_layers):
+        p = f"model.language_model.layers.{li}."
+        hN = rms(x, sd[p + "input_layernorm.weight"])
+        q = rms(lin(hN, p + "self_attn.q_proj").unflatten(-1, (H, Dh)), sd[p + "self_attn.q_norm.weight"])
+        k = rms(lin(hN, p + "self_attn.k_proj").unflatten(-1, (KV, Dh)), sd[p + "self_attn.k_norm.weight"])
+        v = lin(hN, p + "self_attn.v_proj").unflatten(-1, (KV, Dh))
+        q, k = q * cosf + rot(q) * sinf, k * cosf + rot(k) * sinf
+        k, v = k.repeat_interleave(H // KV, 2), v.repeat_interleave(H // KV, 2)
+        sc = torch.einsum("bqhd,bkhd->bhqk", q, k) / Dh ** 0.5 + torch.where(allow, 0.0, -1e4)
+        x = x + lin(torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1), v).flatten(-2), p + "self_attn.o_proj")
+        hN = rms(x, sd[p + "post_attention_layernorm.weight"])
+        x = x + lin(F.silu(lin(hN, p + "mlp.gate_proj")) * lin(hN, p + "mlp.up_proj"), p + "mlp.down_proj")
+    want = lin(rms(x, sd["model.language_model.norm.weight"]), "model.final_layer2.linear")
+    assert (out - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
