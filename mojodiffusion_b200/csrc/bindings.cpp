@@ -426,6 +426,8 @@ Tensor norm_modulate_fwd(const Tensor& x, const optional<Tensor>& weight, const 
                          const optional<Tensor>& scale, const optional<Tensor>& shift, int64_t rows_per_group,
                          double eps, bool rms) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "norm: x [rows,D] bf16");
+  for (const optional<Tensor>* t : {&weight, &bias, &scale, &shift})
+    TORCH_CHECK(!(t->has_value() && (*t)->defined()) || (*t)->scalar_type() == at::kBFloat16, "norm: weight / bias / scale / shift must be bf16");
   c10::cuda::CUDAGuard guard(x.device());
   Tensor out = at::empty({x.size(0), x.size(1)}, x.options());
   int mod_stride = 0;

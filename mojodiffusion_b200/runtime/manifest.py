@@ -256,6 +256,18 @@ register(ModelManifest(
     ScheduleSpec("shifted", 8, 1.0, shift=3.0), None, "", "", 2.0, ((1, 1),), blocked=_NO_PIPELINE,
     notes="audio: a 1-D token sequence of acoustic latents; the acoustic VAE and the condition encoder are not built"),
     "acestep", "ace-step")
+register(ModelManifest(
+    "krea-2", "krea2", _M + "krea2", "Krea2DiT", "Krea2Config", "tiny_krea2_config",
+    LatentSpec(16, 8, 2, True), TextSpec(512, 2560, 0, ("qwen3_vl_4b_12_layers",)),
+    ScheduleSpec("krea2_exp_shift", 20, 4.5), None, "qwen_image_vae_config", "", 13.0, ((1024, 1024),), blocked=_NO_PIPELINE,
+    notes="the text input is twelve stacked encoder layers per token; `models.krea2.krea2_sample` is the sampling loop"),
+    "krea2")
+register(ModelManifest(
+    "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
+    LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
+    ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,
+    notes="pixel space: 32 x 32 RGB patches and the prompt's token ids run through one language-model spine"),
+    "hidream_o1", "hidream")
 
 
 # ---- execution config / shape profile / guard ------------------------------------------------------------------

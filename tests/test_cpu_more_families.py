@@ -660,3 +660,102 @@ def test_hidream_o1_spine_heads_mask_and_positions():
         x = x + lin(F.silu(lin(hN, p + "mlp.gate_proj")) * lin(hN, p + "mlp.up_proj"), p + "mlp.down_proj")
     want = lin(rms(x, sd["model.language_model.norm.weight"]), "model.final_layer2.linear")
     assert (out - want).abs().max() < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_krea2_single_stream_dit_matches_plain_torch_statement():
+    """Krea-2: three-axis rotary table against the complex-rotation statement (float64), patchify round trip, and the
+    whole model (text fusion over layers then tokens, shared modulation vector + per-block offsets, grouped-query gated
+    attention, SwiGLU, last layer on the time vector) against a plain-torch forward written from the state dict."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import krea2 as K
+    torch.manual_seed(9)
+    cfg = K.tiny_krea2_config()
+    assert K.Krea2Config().rope_axes == (32, 48, 48) and K.swiglu_width(6144, 4) == 16384 and cfg.head_dim == 32
+
+    lat = torch.randn(2, cfg.channels, 6, 8)
+    tok = K.patchify(lat, 2)
+    assert tok.shape == (2, 12, cfg.channels * 4)
+    assert torch.equal(tok[1, 1 * 4 + 2].reshape(cfg.channels, 2, 2), lat[1, :, 2:4, 4:6])
+    assert torch.equal(K.unpatchify(tok, 3, 4, 2), lat)
+
+    pos = K.krea2_positions(3, 3, 4)
+    assert pos.shape == (15, 3) and float(pos[:3].abs().sum()) == 0 and pos[3 + 1 * 4 + 2].tolist() == [0.0, 1.0, 2.0]
+    big = torch.tensor([[4000.0, 37.0, 63.0]])
+    cos, sin = K.krea2_rope_table(big, (32, 48, 48), 1.0e3)
+    want = torch.cat([big[:, a:a + 1].double() / (1.0e3 ** (torch.arange(0, d, 2).double() / d)) for a, d in enumerate((32, 48, 48))], -1)
+    assert cos.shape == (1, 64) and (cos.double() - want.cos()).abs().max() < 1e-6 and (sin.double() - want.sin()).abs().max() < 1e-6
+
+    m = K.Krea2DiT(cfg, torch.float32).init_weights(5)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith(".scale") or n.endswith(".lin"):
+                p.add_(torch.randn_like(p) * 0.2)
+    sd = m.state_dict()
+    assert {"first.weight", "tmlp.0.bias", "tmlp.2.weight", "tproj.1.weight", "txtfusion.projector.weight", "txtmlp.0.scale",
+            "txtmlp.1.weight", "txtmlp.3.bias", "blocks.0.mod.lin", "blocks.1.attn.qknorm.knorm.scale", "blocks.0.attn.gate.weight",
+            "blocks.0.mlp.down.weight", "txtfusion.layerwise_blocks.1.attn.wq.weight", "txtfusion.refiner_blocks.0.postnorm.scale",
+            "last.norm.scale", "last.modulation.lin", "last.linear.bias"} <= set(sd)
+    B, Lt, gh, gw = 2, 5, 3, 4
+    img = torch.randn(B, gh * gw, cfg.patch_dim)
+    context = torch.randn(B, Lt, cfg.txtlayers, cfg.txtdim)
+    t = torch.tensor([0.25, 0.9])
+    pos = K.krea2_positions(Lt, gh, gw)
+    got = m(img, context, t, pos)
+    assert got.shape == (B, gh * gw, cfg.patch_dim)
+
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    norm = lambda v, n: F.rms_norm(v, (v.shape[-1],), weight=sd[n + ".scale"] + 1.0, eps=1e-5)
+    gelu = lambda v: F.gelu(v, approximate="tanh")
+
+    def attn(v, p, heads, kvheads, ang=None):
+        b, s, d = v.shape
+        dh = d // heads
+        q = norm(lin(v, p + ".wq").reshape(b, s, heads, dh), p + ".qknorm.qnorm").transpose(1, 2)
+        k = norm(lin(v, p + ".wk").reshape(b, s, kvheads, dh), p + ".qknorm.knorm").transpose(1, 2)
+        vv = lin(v, p + ".wv").reshape(b, s, kvheads, dh).transpose(1, 2)
+        if ang is not None:
+            rot = torch.polar(torch.ones_like(ang), ang)[None, None]                  # [1, 1, S, dh / 2] complex
+            q = torch.view_as_real(torch.view_as_complex(q.reshape(b, heads, s, dh // 2, 2).contiguous()) * rot).flatten(-2)
+            k = torch.view_as_real(torch.view_as_complex(k.reshape(b, kvheads, s, dh // 2, 2).contiguous()) * rot).flatten(-2)
+        o = F.scaled_dot_product_attention(q, k, vv, enable_gqa=kvheads != heads).transpose(1, 2).reshape(b, s, d)
+        return lin(o * torch.sigmoid(lin(v, p + ".gate")), p + ".wo")
+
+    swiglu = lambda v, p: lin(F.silu(lin(v, p + ".gate")) * lin(v, p + ".up"), p + ".down")
+
+    def fusion_block(v, p):
+        v = v + attn(norm(v, p + ".prenorm"), p + ".attn", cfg.txtheads, cfg.txtkvheads)
+        return v + swiglu(norm(v, p + ".postnorm"), p + ".mlp")
+
+    half = cfg.tdim // 2
+    args = (t * 1000.0)[:, None] * torch.exp(-math.log(1.0e4) * torch.arange(half).float() / half)[None]
+    tv = lin(gelu(lin(torch.cat((args.cos(), args.sin()), -1), "tmlp.0")), "tmlp.2")
+    vec = lin(gelu(tv), "tproj.1")
+    c = context.reshape(B * Lt, cfg.txtlayers, cfg.txtdim)
+    for i in range(2):
+        c = fusion_block(c, f"txtfusion.layerwise_blocks.{i}")
+    c = F.linear(c.transpose(1, 2), sd["txtfusion.projector.weight"]).reshape(B, Lt, cfg.txtdim)
+    for i in range(2):
+        c = fusion_block(c, f"txtfusion.refiner_blocks.{i}")
+    c = lin(gelu(lin(norm(c, "txtmlp.0"), "txtmlp.1")), "txtmlp.3")
+    x = torch.cat((c, lin(img, "first")), 1)
+    ang = torch.cat([pos[:, a:a + 1] / (cfg.theta ** (torch.arange(0, d, 2).float() / d))[None] for a, d in enumerate(cfg.rope_axes)], -1)
+    for i in range(cfg.layers):
+        p = f"blocks.{i}"
+        s1, b1, g1, s2, b2, g2 = (vec + sd[p + ".mod.lin"])[:, None].chunk(6, -1)
+        x = x + g1 * attn((1 + s1) * norm(x, p + ".prenorm") + b1, p + ".attn", cfg.heads, cfg.kvheads, ang)
+        x = x + g2 * swiglu((1 + s2) * norm(x, p + ".postnorm") + b2, p + ".mlp")
+    sc, sh = (tv[:, None] + sd["last.modulation.lin"][None]).chunk(2, 1)
+    want = lin((1 + sc) * norm(x, "last.norm") + sh, "last.linear")[:, Lt:]
+    assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
+
+    # sampler: one step without guidance equals latent + (t1 - t0) * v; with guidance the two velocities combine as v_c + s (v_c - v_u)
+    from mojodiffusion_b200.sampling.family_schedules import krea2_packed_seq_len, krea2_timesteps
+    ctx1, ctx0 = context[:1], torch.randn(1, 3, cfg.txtlayers, cfg.txtdim)
+    start = torch.randn(1, cfg.channels, 2 * gh, 2 * gw)
+    ts = krea2_timesteps(krea2_packed_seq_len(16 * gh, 16 * gw), 1)
+    out = K.krea2_sample(m, ctx1, ctx0, 16 * gh, 16 * gw, steps=1, cfg_scale=2.0, latent=start)
+    tt = torch.tensor([ts[0]])
+    vc = m(K.patchify(start), ctx1, tt, K.krea2_positions(Lt, gh, gw))
+    vu = m(K.patchify(start), ctx0, tt, K.krea2_positions(3, gh, gw))
+    assert torch.allclose(out, start + (ts[1] - ts[0]) * K.unpatchify(vc + 2.0 * (vc - vu), gh, gw), atol=1e-5)

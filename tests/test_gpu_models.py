@@ -302,3 +302,40 @@ def test_more_video_and_image_families_on_native_kernels():
         got = mg(z.to(DEV), txt.to(DEV), t.to(DEV), control=ctl.to(DEV))
     native.check_status()
     assert (want - base).abs().max() > 1e-3 and _cos(got, want) >= 0.99
+
+
+def test_moe_audio_spine_and_krea2_families_on_native_kernels():
+    """Nucleus-Image (expert-choice MoE), ACE-Step (audio), HiDream-O1 (language-model spine) and Krea-2 (tiny configurations,
+    head width 64) in bf16 on the sm_100a kernels against their fp32 CPU forward."""
+    import dataclasses
+    from mojodiffusion_b200.models.acestep import AceStepDiT, tiny_acestep_config
+    from mojodiffusion_b200.models.hidream_o1 import HiDreamO1, build_mrope_positions, tiny_hidream_o1_config
+    from mojodiffusion_b200.models.krea2 import Krea2DiT, krea2_positions, tiny_krea2_config
+    from mojodiffusion_b200.models.nucleus import NucleusDiT, tiny_nucleus_config
+    g = torch.Generator().manual_seed(12)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    cn = tiny_nucleus_config()
+    _gpu_vs_cpu(lambda dt, dev: NucleusDiT(cn, dt, dev), (rn(1, 8 * 8, cn.in_channels), rn(1, 16, cn.joint_dim), torch.tensor([0.3])),
+                cos_min=0.99, grid=(1, 8, 8))
+    ca = dataclasses.replace(tiny_acestep_config(), hidden=256, head_dim=64)
+    _gpu_vs_cpu(lambda dt, dev: AceStepDiT(ca, dt, dev), (rn(1, 32, ca.acoustic_dim), rn(1, 32, ca.in_channels - ca.acoustic_dim), rn(1, 8, ca.hidden),
+                                                         torch.tensor([0.7]), torch.tensor([0.2])), cos_min=0.99)
+    ck = dataclasses.replace(tiny_krea2_config(), features=256, txtdim=128)
+    gh, gw, Lt = 8, 8, 16
+    pos = krea2_positions(Lt, gh, gw)
+    _gpu_vs_cpu(lambda dt, dev: Krea2DiT(ck, dt, dev), (rn(1, gh * gw, ck.patch_dim), rn(1, Lt, ck.txtlayers, ck.txtdim), torch.tensor([0.6]), pos),
+                cos_min=0.99)
+    chd = tiny_hidream_o1_config()
+    chd = dataclasses.replace(chd, spine=dataclasses.replace(chd.spine, hidden_size=256, head_dim=64))
+    ids = [1, 2, chd.tms_token_id, 3, chd.vision_start_token_id]
+    L = 16
+    ppos = build_mrope_positions(ids + [chd.image_token_id] * L, chd.image_token_id, 4, 4, 10)
+    m32 = HiDreamO1(chd, torch.float32, "cpu").init_weights(0)
+    mg = HiDreamO1(chd, torch.bfloat16, DEV)
+    mg.load_state_dict({k: v.to(torch.bfloat16) for k, v in m32.state_dict().items()})
+    m32.load_state_dict({k: v.float() for k, v in mg.state_dict().items()})
+    patches = rn(1, L, chd.patch_dim)
+    want = m32(ids, patches, ppos, len(ids), 0.4)
+    got = mg(ids, patches.to(DEV), ppos, len(ids), 0.4)
+    native.check_status()
+    assert _cos(got[:, len(ids):], want[:, len(ids):]) >= 0.99
