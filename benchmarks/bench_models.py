@@ -131,6 +131,33 @@ def bench_zimage(dev, tiny, steps, warmup, train):
             "tokens": side * side + S_cap, "metric": "train samples/s", "ms_per_step": ms, "value": 1000.0 / ms}
 
 
+def bench_krea2(dev, tiny, steps, warmup):
+    """Krea-2-shaped 12 B single-stream MMDiT: 1024^2 denoise with guidance (two forwards per step; 114 and 5 text tokens of
+    twelve stacked encoder layers each, as in the reference's sample run)."""
+    import dataclasses
+    from mojodiffusion_b200.models.krea2 import Krea2Config, Krea2DiT, krea2_positions, tiny_krea2_config
+    cfg = dataclasses.replace(tiny_krea2_config(), features=256, txtdim=128) if tiny else Krea2Config()
+    g = 8 if tiny else 64
+    lt_c, lt_u = (16, 8) if tiny else (114, 5)
+    m = Krea2DiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    x = torch.randn(1, g * g, cfg.patch_dim, device=dev)
+    xb = x.to(torch.bfloat16)
+    ctx_c = torch.randn(1, lt_c, cfg.txtlayers, cfg.txtdim, device=dev, dtype=torch.bfloat16)
+    ctx_u = torch.randn(1, lt_u, cfg.txtlayers, cfg.txtdim, device=dev, dtype=torch.bfloat16)
+    pos_c, pos_u = krea2_positions(lt_c, g, g, dev), krea2_positions(lt_u, g, g, dev)
+    t = torch.full((1,), 0.6, device=dev)
+
+    def step():
+        with torch.no_grad():
+            vc = m(xb, ctx_c, t, pos_c)
+            vu = m(xb, ctx_u, t, pos_u)
+            ops.cfg_euler(x, vc, vu, dt=-0.03, s=4.5, mode=2, x_bf16=xb)          # v_c + 4.5 (v_c - v_u)
+
+    ms = timed(step, steps, warmup)
+    return {"model": cfg.name + " guidance 4.5 (2 forwards/step)", "params_b": nparams(m) / 1e9, "tokens": g * g + lt_c,
+            "metric": "denoise it/s", "ms_per_step": ms, "value": 1000.0 / ms}
+
+
 def bench_klein(dev, tiny, steps, warmup, train):
     """FLUX.2 Klein-9B-shaped MMDiT: 1024^2 denoise (4096 + 512 tokens), or the reference's headline training case:
     LoRA r16 on every block projection, 512^2 (1024 image + 512 text tokens = 1536), batch 1, gradient checkpointing."""
@@ -297,6 +324,7 @@ def main():
         "ltx2_mxfp8": lambda: bench_ltx2(dev, args.tiny, args.steps, args.warmup, True, True),
         "ltx2_vae": lambda: bench_ltx2_vae(dev, args.tiny, args.steps, args.warmup),
         "sdxl_train": lambda: bench_sdxl_train(dev, args.tiny, args.steps, args.warmup),
+        "krea2": lambda: bench_krea2(dev, args.tiny, args.steps, args.warmup),
     }
     rows = []
     for name in args.only.split(","):

@@ -29,7 +29,8 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from .layers import Linear, init_module_weights, timestep_embedding
+from ..ops import native
+from .layers import Linear, init_module_weights, packed_projection, timestep_embedding
 
 
 @dataclass
@@ -144,8 +145,34 @@ class Krea2Attention(nn.Module):
         self.wo = Linear(width, width, False, dtype, device)
         self.qknorm = _QKNorm(self.head_dim, eps, dtype, device)
 
+    def _forward_packed(self, x, rope):
+        """Inference on the device kernels: q | k | v land in one buffer (each GEMM stores into its column range), the
+        per-head norm + rotary kernel runs in place on the query heads and on the key heads (two half-ranges per launch),
+        attention writes next to the gate projection and one gated-unit kernel forms ``sigmoid(gate) * attention``."""
+        H, KV, Dh = self.heads, self.kvheads, self.head_dim
+        B, S, D = x.shape
+        qkv = packed_projection(x, (self.wq, self.wk, self.wv))
+        wq = (self.qknorm.qnorm.scale.float() + 1.0).to(x.dtype)
+        wk = (self.qknorm.knorm.scale.float() + 1.0).to(x.dtype)
+        cos, sin = rope if rope is not None else (None, None)
+        eps = self.qknorm.qnorm.eps
+        ops.qk_norm_rope(qkv, H // 2, Dh, wq, wq, cos, sin, eps, True, q_off=0, k_off=(H // 2) * Dh)
+        ops.qk_norm_rope(qkv, KV // 2, Dh, wk, wk, cos, sin, eps, True, q_off=D, k_off=D + (KV // 2) * Dh)
+        q = qkv[..., :D].unflatten(-1, (H, Dh))
+        k = qkv[..., D:D + KV * Dh].unflatten(-1, (KV, Dh))
+        v = qkv[..., D + KV * Dh:].unflatten(-1, (KV, Dh))
+        if KV != H:
+            k, v = k.repeat_interleave(H // KV, 2), v.repeat_interleave(H // KV, 2)
+        pair = torch.empty(B, S, 2 * D, dtype=x.dtype, device=x.device)
+        self.gate(x, out=pair[..., :D])
+        ops.attention(q, k, v, out=pair[..., D:].unflatten(-1, (H, Dh)))
+        return self.wo(ops.glu(pair, "sigmoid"))
+
     def forward(self, x, rope=None):
         H, KV, Dh = self.heads, self.kvheads, self.head_dim
+        if (native.use_native(x) and not torch.is_grad_enabled() and Dh in (64, 128) and H % 2 == 0 and KV % 2 == 0
+                and x.dim() == 3):
+            return self._forward_packed(x, rope)
         q = self.qknorm.qnorm(self.wq(x).unflatten(-1, (H, Dh)))
         k = self.qknorm.knorm(self.wk(x).unflatten(-1, (KV, Dh)))
         v = self.wv(x).unflatten(-1, (KV, Dh))
@@ -166,6 +193,8 @@ class _SwiGLU(nn.Module):
         self.down = Linear(inner, width, False, dtype, device)
 
     def forward(self, x):
+        if native.use_native(x) and not torch.is_grad_enabled():
+            return self.down(ops.glu(packed_projection(x, (self.gate, self.up)), "silu"))
         return self.down(self.gate(x, act="silu") * self.up(x))
 
 
@@ -284,7 +313,12 @@ class Krea2DiT(nn.Module):
         return self.last.linear(h)
 
     def init_weights(self, seed: int = 0, std: float = 0.02):
-        return init_module_weights(self, seed, std)
+        init_module_weights(self, seed, std)
+        with torch.no_grad():
+            for n, p in self.named_parameters():
+                if n.endswith(".scale"):                                           # the norm weight is 1 + scale
+                    p.zero_()
+        return self
 
 
 @torch.no_grad()

@@ -34,6 +34,9 @@ class SingleDiTConfig:
     adaln_dim: int = 256
     norm_eps: float = 1e-5
     name: str = "zimage"
+    patch_key: str = "2-1"         # name of the patch embedder / final layer ("<patch>-<frame patch>")
+    rope_interleaved: bool = False  # True: rotary pairs are (2i, 2i + 1); False: (i, i + Dh / 2)
+    final_layer: bool = True       # False: the trunk ends at the hidden image tokens (a pixel head follows elsewhere)
 
 
 def zimage_config() -> SingleDiTConfig:
@@ -64,9 +67,9 @@ class Attention(nn.Module):
         H, Dh = cfg.heads, cfg.head_dim
         qkv = packed_projection(x, (self.to_q, self.to_k, self.to_v))
         qkv = ops.qk_norm_rope(qkv, H, Dh, self.norm_q.weight, self.norm_k.weight, cos, sin, eps=cfg.norm_eps,
-                               interleaved=False)
+                               interleaved=cfg.rope_interleaved)
         q, k, v = [qkv[..., i * D:(i + 1) * D].unflatten(-1, (H, Dh)) for i in range(3)]
-        return ops.attention(q, k, v, kv_len=kv_len).reshape(B, S, D)
+        return self.to_out[0](ops.attention(q, k, v, kv_len=kv_len).reshape(B, S, D))
 
 
 class FeedForward(nn.Module):
@@ -144,8 +147,9 @@ class SingleStreamDiT(nn.Module):
         self.t_embedder = TimestepEmbedder(min(D, cfg.adaln_dim), 256, 1024 if D > 1024 else D, dtype, device)
         self.cap_embedder = nn.ModuleDict({"0": RMSNorm(cfg.cap_dim, cfg.norm_eps, dtype, device),
                                            "1": Linear(cfg.cap_dim, D, True, dtype, device)})
-        self.all_x_embedder = nn.ModuleDict({"2-1": Linear(cfg.in_channels, D, True, dtype, device)})
-        self.all_final_layer = nn.ModuleDict({"2-1": FinalLayer(cfg, dtype, device)})
+        self.all_x_embedder = nn.ModuleDict({cfg.patch_key: Linear(cfg.in_channels, D, True, dtype, device)})
+        if cfg.final_layer:
+            self.all_final_layer = nn.ModuleDict({cfg.patch_key: FinalLayer(cfg, dtype, device)})
         self.x_pad_token = nn.Parameter(torch.zeros(1, D, dtype=dtype, device=device))
         self.cap_pad_token = nn.Parameter(torch.zeros(1, D, dtype=dtype, device=device))
         self.noise_refiner = nn.ModuleList([Block(cfg, True, dtype, device) for _ in range(cfg.depth_noise_refiner)])
@@ -187,11 +191,11 @@ class SingleStreamDiT(nn.Module):
         if hw is None:
             side = int(round(S_img ** 0.5))
             hw = (side, S_img // side)
-        dt = self.all_x_embedder["2-1"].weight.dtype
+        dt = self.all_x_embedder[cfg.patch_key].weight.dtype
         ids = self.make_ids(hw[0], hw[1], S_cap, img.device)
         cos, sin = ops.rope_table(ids, cfg.axes_dim, cfg.theta)
         c = self.t_embedder(t, cfg.t_scale)                                   # [B, adaln_dim]
-        x = self.all_x_embedder["2-1"](img.to(dt))
+        x = self.all_x_embedder[cfg.patch_key](img.to(dt))
         y = self.cap_embedder["1"](self.cap_embedder["0"](cap.to(dt)))
         if cap_len is not None:                                             # padded captions -> learned pad token
             pad = torch.arange(S_cap, device=img.device)[None, :] >= cap_len[:, None]
@@ -213,7 +217,8 @@ class SingleStreamDiT(nn.Module):
             h = self._run(blk, h, st["cos"], st["sin"], st["c"], st["kv_len"])
             if hints is not None and i in hints:
                 h = h + hints[i]
-        return self.all_final_layer["2-1"](h[:, :st["S_img"]], st["c"])
+        h = h[:, :st["S_img"]]
+        return self.all_final_layer[self.cfg.patch_key](h, st["c"]) if self.cfg.final_layer else h
 
     def init_weights(self, seed: int = 0, std: float = 0.02):
         return init_module_weights(self, seed, std)

@@ -263,6 +263,12 @@ register(ModelManifest(
     notes="the text input is twelve stacked encoder layers per token; `models.krea2.krea2_sample` is the sampling loop"),
     "krea2")
 register(ModelManifest(
+    "zimage-l2p", "zimage_l2p", _M + "zimage_l2p", "ZImageL2P", "zimage_l2p_config", "tiny_zimage_l2p_config",
+    LatentSpec(3, 1, 16, False), TextSpec(512, 2560, 0, ("qwen3",)),
+    ScheduleSpec("shifted", 30, 2.0, shift=3.0), None, "", "", 6.2, ((1024, 1024),), blocked=_NO_PIPELINE,
+    notes="pixel space, no VAE; `models.zimage_l2p.l2p_sample` is the sampling loop"),
+    "l2p")
+register(ModelManifest(
     "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
     ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,

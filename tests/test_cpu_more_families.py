@@ -759,3 +759,103 @@ def test_krea2_single_stream_dit_matches_plain_torch_statement():
     vc = m(K.patchify(start), ctx1, tt, K.krea2_positions(Lt, gh, gw))
     vu = m(K.patchify(start), ctx0, tt, K.krea2_positions(3, gh, gw))
     assert torch.allclose(out, start + (ts[1] - ts[0]) * K.unpatchify(vc + 2.0 * (vc - vu), gh, gw), atol=1e-5)
+
+
+def test_zimage_l2p_pixel_trunk_and_local_decoder_match_plain_torch_statement():
+    """Z-Image L2P: pixel patch order, sigma table, the U-Net pixel head against NCHW torch convolutions, and the whole model
+    against a plain-torch forward in the reference's caption-first token order with interleaved rotary pairs."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import zimage_l2p as Z
+    torch.manual_seed(12)
+    full = Z.zimage_l2p_config()
+    assert full.in_channels == 16 * 16 * 3 and full.hidden == 3840 and full.depth == 30 and not full.final_layer
+    sig = Z.l2p_sigmas(30, 3.0)
+    assert len(sig) == 31 and sig[0] == 1.0 and sig[-1] == 0.0 and abs(sig[15] - 3 * 0.5 / 2.0) < 1e-12
+    px = torch.randn(1, 3, 8, 12)
+    tok = Z.patchify_pixels(px, 4)
+    assert tok.shape == (1, 6, 48) and torch.equal(tok[0, 1 * 3 + 2].reshape(4, 4, 3), px[0, :, 4:8, 8:12].permute(1, 2, 0))
+
+    cfg = Z.tiny_zimage_l2p_config()
+    m = Z.ZImageL2P(cfg, decoder_channels=(8, 16, 24, 32), dtype=torch.float32).init_weights(3)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() == 1 or n.endswith("pad_token"):
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    assert {"all_x_embedder.16-1.weight", "cap_embedder.1.bias", "t_embedder.mlp.0.weight", "noise_refiner.0.adaLN_modulation.0.weight",
+            "layers.1.attention.norm_q.weight", "local_decoder.enc1.0.weight", "local_decoder.bottleneck.0.bias",
+            "local_decoder.up4.1.weight", "local_decoder.dec1.0.bias", "local_decoder.out_conv.weight"} <= set(sd)
+    assert not any(k.startswith("all_final_layer") for k in sd) and not any(k.startswith("context_refiner.0.adaLN") for k in sd)
+    assert sum(1 for k in sd if k.startswith("local_decoder.")) == 28
+    B, H, W, Sc = 2, 32, 48, 5
+    pixels, cap, sigma = torch.randn(B, 3, H, W), torch.randn(B, Sc, cfg.cap_dim), torch.tensor([0.8, 0.35])
+    got = m(pixels, cap, sigma)
+    assert got.shape == (B, 3, H, W)
+
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, n: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.norm_eps) * sd[n + ".weight"]
+    gh, gw, D, Hh, Dh = H // 16, W // 16, cfg.hidden, cfg.heads, cfg.head_dim
+    pos = torch.zeros(Sc + gh * gw, 3)
+    pos[:Sc, 0] = torch.arange(1, Sc + 1).float()
+    pos[Sc:, 0] = Sc + 1
+    pos[Sc:, 1] = torch.arange(gh).float().repeat_interleave(gw)
+    pos[Sc:, 2] = torch.arange(gw).float().repeat(gh)
+    ang = torch.cat([pos[:, a:a + 1] / (cfg.theta ** (torch.arange(d // 2).float() / (d // 2)))[None] for a, d in enumerate(cfg.axes_dim)], -1)
+
+    def rope(v, a):
+        c, s = a.cos()[None, :, None], a.sin()[None, :, None]
+        x0, x1 = v[..., 0::2], v[..., 1::2]
+        return torch.stack((x0 * c - x1 * s, x0 * s + x1 * c), -1).flatten(-2)
+
+    def block(v, p, a, c=None):
+        b, s, _ = v.shape
+        if c is not None:
+            sm, gm, sf, gf = lin(c, p + ".adaLN_modulation.0")[:, None].chunk(4, -1)
+        h = rms(v, p + ".attention_norm1") * ((1 + sm) if c is not None else 1.0)
+        q = rope(rms(lin(h, p + ".attention.to_q").reshape(b, s, Hh, Dh), p + ".attention.norm_q"), a).transpose(1, 2)
+        k = rope(rms(lin(h, p + ".attention.to_k").reshape(b, s, Hh, Dh), p + ".attention.norm_k"), a).transpose(1, 2)
+        vv = lin(h, p + ".attention.to_v").reshape(b, s, Hh, Dh).transpose(1, 2)
+        o = rms(lin(F.scaled_dot_product_attention(q, k, vv).transpose(1, 2).reshape(b, s, D), p + ".attention.to_out.0"), p + ".attention_norm2")
+        v = v + (torch.tanh(gm) * o if c is not None else o)
+        h = rms(v, p + ".ffn_norm1") * ((1 + sf) if c is not None else 1.0)
+        o = rms(lin(F.silu(lin(h, p + ".feed_forward.w1")) * lin(h, p + ".feed_forward.w3"), p + ".feed_forward.w2"), p + ".ffn_norm2")
+        return v + (torch.tanh(gf) * o if c is not None else o)
+
+    half = 128
+    targ = ((1.0 - sigma) * 1000.0)[:, None] * torch.exp(-math.log(10000.0) * torch.arange(half).float() / half)[None]
+    c = lin(F.silu(lin(torch.cat((targ.cos(), targ.sin()), -1), "t_embedder.mlp.0")), "t_embedder.mlp.2")
+    x = lin(Z.patchify_pixels(pixels, 16), "all_x_embedder.16-1")
+    y = lin(rms(cap, "cap_embedder.0"), "cap_embedder.1")
+    y = block(y, "context_refiner.0", ang[:Sc])
+    x = block(x, "noise_refiner.0", ang[Sc:], c)
+    j = torch.cat((y, x), 1)
+    for i in range(cfg.depth):
+        j = block(j, f"layers.{i}", ang, c)
+    feat = j[:, Sc:].reshape(B, gh, gw, D).permute(0, 3, 1, 2)
+
+    conv = lambda v, n, pad: F.conv2d(v, sd[n + ".weight"].permute(0, 3, 1, 2), sd[n + ".bias"], padding=pad)
+    ld = "local_decoder."
+    e1 = F.silu(conv(pixels, ld + "enc1.0", 1))
+    e2 = F.silu(conv(F.max_pool2d(e1, 2), ld + "enc2.0", 1))
+    e3 = F.silu(conv(F.max_pool2d(e2, 2), ld + "enc3.0", 1))
+    e4 = F.silu(conv(F.max_pool2d(e3, 2), ld + "enc4.0", 1))
+    h = F.silu(conv(torch.cat((F.max_pool2d(e4, 2), feat), 1), ld + "bottleneck.0", 0))
+    for lvl, skip in ((4, e4), (3, e3), (2, e2), (1, e1)):
+        h = conv(F.interpolate(h, scale_factor=2, mode="nearest"), ld + f"up{lvl}.1", 1)
+        h = F.silu(conv(torch.cat((h, skip), 1), ld + f"dec{lvl}.0", 1))
+    want = -conv(h, ld + "out_conv", 0)
+    assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
+
+    # checkpoint layout of the convolutions and one guided Euler step
+    raw = {k: (v.permute(0, 3, 1, 2).contiguous() if k.startswith(ld) and v.dim() == 4 else v) for k, v in sd.items()}
+    assert all(torch.equal(v, sd[k]) for k, v in Z.remap_l2p_keys(raw).items())
+    x0 = torch.randn(1, 3, H, W)
+    out = Z.l2p_sample(m, cap[:1], cap[1:, :3], H, W, steps=2, cfg_scale=2.0, shift=3.0, x=x0)
+    s2 = Z.l2p_sigmas(2, 3.0)
+    xx = x0
+    for i in range(2):
+        sg = torch.tensor([s2[i]])
+        pc, pu = m(xx, cap[:1], sg), m(xx, cap[1:, :3], sg)
+        xx = xx + (s2[i + 1] - s2[i]) * (pu + 2.0 * (pc - pu))
+    assert torch.allclose(out, xx, atol=1e-5)
