@@ -108,11 +108,10 @@ class ZImageL2P(SingleStreamDiT):
     """forward(pixels [B, 3, H, W], cap [B, S_cap, cap_dim], sigma [B] in [0, 1]) -> prediction [B, 3, H, W] with
     ``x_next = x + (sigma_next - sigma) * prediction``."""
 
-    def __init__(self, cfg: SingleDiTConfig, patch: int = 16, decoder_channels=(64, 128, 256, 512), dtype=torch.bfloat16, device=None):
+    def __init__(self, cfg: SingleDiTConfig, dtype=torch.bfloat16, device=None, decoder_channels=(64, 128, 256, 512)):
         super().__init__(cfg, dtype, device)
-        assert not cfg.final_layer and cfg.in_channels == 3 * patch * patch
-        assert patch == 16, "the pixel head pools four times: the feature map must be 1 / 16 of the image"
-        self.patch = patch
+        self.patch = 16                      # the pixel head pools four times: the feature map is 1 / 16 of the image
+        assert not cfg.final_layer and cfg.in_channels == 3 * self.patch * self.patch
         self.local_decoder = LocalDecoder(cfg.hidden, tuple(decoder_channels), 3, dtype, device)
 
     def forward(self, pixels, cap, sigma, cap_len: Optional[torch.Tensor] = None):
