@@ -269,6 +269,12 @@ register(ModelManifest(
     notes="pixel space, no VAE; `models.zimage_l2p.l2p_sample` is the sampling loop"),
     "l2p")
 register(ModelManifest(
+    "lens", "lens", _M + "lens", "LensDiT", "LensConfig", "tiny_lens_config",
+    LatentSpec(32, 8, 2, True), TextSpec(415, 11520, 0, ("gpt_oss_layers_5_11_17_23",)),
+    ScheduleSpec("lens_exp_shift", 20, 5.0), None, "flux2_vae_config", "", 3.1, ((1024, 1024),), blocked=_NO_PIPELINE,
+    notes="text features are four encoder layers, each normalised by its own weight, concatenated"),
+    "microsoft-lens")
+register(ModelManifest(
     "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
     ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,

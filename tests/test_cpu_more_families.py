@@ -859,3 +859,80 @@ def test_zimage_l2p_pixel_trunk_and_local_decoder_match_plain_torch_statement():
         pc, pu = m(xx, cap[:1], sg), m(xx, cap[1:, :3], sg)
         xx = xx + (s2[i + 1] - s2[i]) * (pu + 2.0 * (pc - pu))
     assert torch.allclose(out, xx, atol=1e-5)
+
+
+def test_lens_double_stream_dit_matches_plain_torch_statement():
+    """Lens: tensor inventory of the full architecture (1264 tensors, the checkpoint's names and shapes), rotary angles of image
+    and text tokens, the text plan, and the tiny model against a plain-torch forward (weighted RMS pre-norms, fused qkv,
+    SwiGLU, four normalised text layers)."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import lens as Ls
+    torch.manual_seed(21)
+    assert Ls.lens_text_plan() == (415, 4511) and Ls.lens_text_plan(353) == (256, 4352)
+    full = Ls.LensDiT(Ls.LensConfig(), torch.float32, "meta")
+    shapes = {k: tuple(v.shape) for k, v in full.state_dict().items()}
+    assert len(shapes) == 1264
+    for k, s in {"img_in.weight": (1536, 128), "txt_in.weight": (1536, 11520), "txt_norm.3.weight": (2880,),
+                 "transformer_blocks.0.img_mod.1.weight": (9216, 1536), "transformer_blocks.0.txt_norm2.weight": (1536,),
+                 "transformer_blocks.47.attn.img_qkv.bias": (4608,), "transformer_blocks.0.attn.norm_added_k.weight": (64,),
+                 "transformer_blocks.0.attn.to_add_out.bias": (1536,), "transformer_blocks.0.img_mlp.w1.weight": (4096, 1536),
+                 "transformer_blocks.0.txt_mlp.w2.weight": (1536, 4096)}.items():
+        assert shapes[k] == s, k
+    assert "transformer_blocks.0.img_mlp.w1.bias" not in shapes
+
+    # rotary angles: image token (y, x) of a 64 x 64 grid and text token i, per frequency pair
+    ids = Ls.LensDiT.make_ids(64, 64, 8)
+    cos, _ = __import__("mojodiffusion_b200").ops.rope_table(ids, (8, 28, 28), 1.0e4)
+    tok = 5 * 64 + 40
+    for pair, want in ((2, 0.0), (4 + 3, (5 - 32) / 1.0e4 ** (6 / 28.0)), (18 + 5, (40 - 32) / 1.0e4 ** (10 / 28.0))):
+        assert abs(float(cos[tok, pair]) - math.cos(want)) < 1e-5
+    for pair, want in ((1, (32 + 3) / 1.0e4 ** (2 / 8.0)), (4 + 2, (32 + 3) / 1.0e4 ** (4 / 28.0)), (18, 35.0)):
+        assert abs(float(cos[4096 + 3, pair]) - math.cos(want)) < 1e-5
+
+    cfg = Ls.tiny_lens_config()
+    m = Ls.LensDiT(cfg, torch.float32).init_weights(2)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    B, gh, gw, St = 2, 4, 6, 5
+    D, H, Dh = cfg.hidden, cfg.heads, cfg.head_dim
+    img, layers, t = torch.randn(B, gh * gw, cfg.in_channels), torch.randn(B, St, 4, cfg.text_hidden), torch.tensor([0.2, 0.7])
+    got = m(img, layers, t, (gh, gw))
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, n, eps=1e-6: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * sd[n + ".weight"]
+    args = (t * 1000.0)[:, None] * torch.exp(-math.log(1.0e4) * torch.arange(128).float() / 128)[None]
+    temb = F.silu(lin(F.silu(lin(torch.cat((args.cos(), args.sin()), -1), "time_text_embed.timestep_embedder.linear_1")),
+                      "time_text_embed.timestep_embedder.linear_2"))
+    x = lin(img, "img_in")
+    y = lin(torch.cat([rms(layers[:, :, j], f"txt_norm.{j}", 1e-5) for j in range(4)], -1), "txt_in")
+    pos = torch.zeros(gh * gw + St, 3)
+    pos[:gh * gw, 1] = (torch.arange(gh).float() - gh // 2).repeat_interleave(gw)
+    pos[:gh * gw, 2] = (torch.arange(gw).float() - gw // 2).repeat(gh)
+    pos[gh * gw:] = (max(gh, gw) // 2 + torch.arange(St).float())[:, None]
+    ang = torch.cat([pos[:, a:a + 1] / (1.0e4 ** (torch.arange(0, d, 2).float() / d))[None] for a, d in enumerate(cfg.axes_dim)], -1)
+
+    def rope(v):
+        c, s = ang.cos()[None, :, None], ang.sin()[None, :, None]
+        a, b = v[..., 0::2], v[..., 1::2]
+        return torch.stack((a * c - b * s, a * s + b * c), -1).flatten(-2)
+
+    for i in range(cfg.depth):
+        p = f"transformer_blocks.{i}."
+        mi, mt = lin(temb, p + "img_mod.1")[:, None].chunk(6, -1), lin(temb, p + "txt_mod.1")[:, None].chunk(6, -1)
+        qi = lin(rms(x, p + "img_norm1") * (1 + mi[1]) + mi[0], p + "attn.img_qkv").reshape(B, -1, 3, H, Dh)
+        qt = lin(rms(y, p + "txt_norm1") * (1 + mt[1]) + mt[0], p + "attn.txt_qkv").reshape(B, -1, 3, H, Dh)
+        q = rope(torch.cat((rms(qi[:, :, 0], p + "attn.norm_q"), rms(qt[:, :, 0], p + "attn.norm_added_q")), 1))
+        k = rope(torch.cat((rms(qi[:, :, 1], p + "attn.norm_k"), rms(qt[:, :, 1], p + "attn.norm_added_k")), 1))
+        v = torch.cat((qi[:, :, 2], qt[:, :, 2]), 1)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).reshape(B, -1, D)
+        x = x + mi[2] * lin(o[:, :gh * gw], p + "attn.to_out.0")
+        y = y + mt[2] * lin(o[:, gh * gw:], p + "attn.to_add_out")
+        ffn = lambda v_, n: lin(F.silu(lin(v_, n + ".w1")) * lin(v_, n + ".w3"), n + ".w2")
+        x = x + mi[5] * ffn(rms(x, p + "img_norm2") * (1 + mi[4]) + mi[3], p + "img_mlp")
+        y = y + mt[5] * ffn(rms(y, p + "txt_norm2") * (1 + mt[4]) + mt[3], p + "txt_mlp")
+    sc, sh = lin(temb, "norm_out.linear")[:, None].chunk(2, -1)
+    want = lin(F.layer_norm(x, (D,), eps=1e-6) * (1 + sc) + sh, "proj_out")
+    assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5

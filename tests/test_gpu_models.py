@@ -305,7 +305,7 @@ def test_more_video_and_image_families_on_native_kernels():
 
 
 def test_moe_audio_spine_and_krea2_families_on_native_kernels():
-    """Nucleus-Image (expert-choice MoE), ACE-Step (audio), HiDream-O1 (language-model spine) and Krea-2 (tiny configurations,
+    """Nucleus-Image (expert-choice MoE), ACE-Step (audio), HiDream-O1 (language-model spine), Krea-2, Lens and Z-Image L2P (tiny configurations,
     head width 64) in bf16 on the sm_100a kernels against their fp32 CPU forward."""
     import dataclasses
     from mojodiffusion_b200.models.acestep import AceStepDiT, tiny_acestep_config
@@ -325,6 +325,12 @@ def test_moe_audio_spine_and_krea2_families_on_native_kernels():
     pos = krea2_positions(Lt, gh, gw)
     _gpu_vs_cpu(lambda dt, dev: Krea2DiT(ck, dt, dev), (rn(1, gh * gw, ck.patch_dim), rn(1, Lt, ck.txtlayers, ck.txtdim), torch.tensor([0.6]), pos),
                 cos_min=0.99)
+    from mojodiffusion_b200.models.lens import LensDiT, tiny_lens_config
+    from mojodiffusion_b200.models.zimage_l2p import ZImageL2P, tiny_zimage_l2p_config
+    cl = tiny_lens_config()
+    _gpu_vs_cpu(lambda dt, dev: LensDiT(cl, dt, dev), (rn(1, 8 * 8, cl.in_channels), rn(1, 16, 4, cl.text_hidden), torch.tensor([0.4])), cos_min=0.99, hw=(8, 8))
+    cz = tiny_zimage_l2p_config()
+    _gpu_vs_cpu(lambda dt, dev: ZImageL2P(cz, dt, dev, (64, 64, 128, 128)), (rn(1, 3, 64, 64), rn(1, 16, cz.cap_dim), torch.tensor([0.6])), cos_min=0.99)
     chd = tiny_hidream_o1_config()
     chd = dataclasses.replace(chd, spine=dataclasses.replace(chd.spine, hidden_size=256, head_dim=64))
     ids = [1, 2, chd.tms_token_id, 3, chd.vision_start_token_id]
