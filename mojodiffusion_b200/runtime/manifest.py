@@ -275,6 +275,12 @@ register(ModelManifest(
     notes="text features are four encoder layers, each normalised by its own weight, concatenated"),
     "microsoft-lens")
 register(ModelManifest(
+    "lance-3b-video", "lance", _M + "lance", "LanceT2V", "LanceConfig", "tiny_lance_config",
+    LatentSpec(48, 16, 1, True, temporal_factor=4), TextSpec(512, 2048, 0, ()),
+    ScheduleSpec("lance_shifted", 30, 4.0, shift=3.0), None, "", "", 6.5, ((848, 480),), blocked=_NO_PIPELINE,
+    notes="token ids and latent tokens share one decoder; generated rows use the *_moe_gen weights; see runtime/lance_kv_plan.py"),
+    "lance")
+register(ModelManifest(
     "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
     ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,

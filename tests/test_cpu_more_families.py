@@ -936,3 +936,85 @@ def test_lens_double_stream_dit_matches_plain_torch_statement():
     sc, sh = lin(temb, "norm_out.linear")[:, None].chunk(2, -1)
     want = lin(F.layer_norm(x, (D,), eps=1e-6) * (1 + sc) + sh, "proj_out")
     assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
+
+
+def test_lance_t2v_two_expert_spine_matches_plain_torch_statement():
+    """Lance T2V: sequence / position builder, mask, full-width three-axis rotary table, and the model against a plain-torch
+    forward written as "run every row through the text weights, then overwrite the generated rows with the generation
+    weights' result"."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import lance as La
+    torch.manual_seed(31)
+    full = La.LanceConfig()
+    inp = La.build_lance_input(full, [11, 12, 13], 2, 2, 3)
+    assert inp.full_ids[:5] == (full.bos_token_id, 11, 12, 13, full.eos_token_id) and inp.full_ids[5] == full.start_of_image_id
+    assert inp.text_split_len == 5 and inp.gen_start == 6 and inp.gen_len == 12 and inp.full_ids[-1] == full.end_of_image_id
+    assert inp.t_pos[:6] == tuple(range(6)) and (inp.t_pos[6 + 7], inp.h_pos[6 + 7], inp.w_pos[6 + 7]) == (6 + 2, 6 + 0, 6 + 1)
+    assert inp.latent_pos_ids[7] == 1 * 64 * 64 + 0 * 64 + 1 and inp.t_pos[-1] == inp.h_pos[-1] == inp.w_pos[-1] == 6 + 2 + 1
+    mk = La.lance_mask(5, 3)[0, 0]
+    assert mk.tolist() == [[0, -1e4, -1e4, -1e4, -1e4], [0, 0, -1e4, -1e4, -1e4], [0, 0, 0, -1e4, -1e4], [0] * 5, [0] * 5]
+    cos, sin = La.lance_rope_table(inp, 128, 1.0e6, (16, 24, 24))
+    row = 6 + 7
+    for d, axis_pos in ((5, inp.t_pos[row]), (31, inp.t_pos[row]), (32, inp.h_pos[row]), (70, inp.h_pos[row]), (79, inp.h_pos[row]),
+                        (80, inp.w_pos[row]), (127, inp.w_pos[row])):
+        want = axis_pos * math.exp(-math.log(1.0e6) * (d % 64) / 64)
+        assert abs(float(cos[row, d]) - math.cos(want)) < 1e-5 and abs(float(sin[row, d]) - math.sin(want)) < 1e-5
+
+    cfg = La.tiny_lance_config()
+    m = La.LanceT2V(cfg, torch.float32).init_weights(8)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() == 1 or n.endswith("pos_embed"):
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    for k in ("language_model.model.embed_tokens.weight", "language_model.model.norm_moe_gen.weight", "vae2llm.bias", "llm2vae.weight",
+              "time_embedder.mlp.2.bias", "latent_pos_embed.pos_embed", "language_model.model.layers.1.self_attn.q_proj_moe_gen.bias",
+              "language_model.model.layers.0.self_attn.k_norm_moe_gen.weight", "language_model.model.layers.0.mlp_moe_gen.down_proj.weight",
+              "language_model.model.layers.0.post_attention_layernorm_moe_gen.weight", "language_model.model.layers.0.self_attn.o_proj.weight"):
+        assert k in sd, k
+    assert "language_model.model.layers.0.self_attn.o_proj.bias" not in sd
+    inp = La.build_lance_input(cfg, [3, 4, 5, 6], 2, 2, 3)
+    x_t, t = torch.randn(inp.gen_len, cfg.patch_latent_dim), torch.tensor([0.37])
+    got = m(inp, x_t, t)
+    assert got.shape == (inp.gen_len, cfg.patch_latent_dim)
+
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, n: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * sd[n + ".weight"]
+    S, g0, g1 = len(inp.full_ids), inp.gen_start, inp.gen_start + inp.gen_len
+    H, KV, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+
+    def span(all_rows, gen_rows):
+        out = all_rows.clone()
+        out[:, g0:g1] = gen_rows
+        return out
+
+    half = cfg.timestep_dim // 2
+    args = t[:, None] * torch.exp(-math.log(1.0e4) * torch.arange(half).float() / half)[None]
+    temb = lin(F.silu(lin(torch.cat((args.cos(), args.sin()), -1), "time_embedder.mlp.0")), "time_embedder.mlp.2")
+    h = sd["language_model.model.embed_tokens.weight"][list(inp.full_ids)][None]
+    h = span(h, lin(x_t[None], "vae2llm") + temb[:, None] + sd["latent_pos_embed.pos_embed"][list(inp.latent_pos_ids)][None])
+    cos, sin = La.lance_rope_table(inp, Dh, cfg.rope_theta, cfg.mrope)
+    rot = lambda v: v * cos[None, :, None] + torch.cat((-v[..., Dh // 2:], v[..., :Dh // 2]), -1) * sin[None, :, None]
+    mask = La.lance_mask(S, inp.text_split_len)
+    for i in range(cfg.num_layers):
+        p = f"language_model.model.layers.{i}."
+        n1 = span(rms(h, p + "input_layernorm"), rms(h[:, g0:g1], p + "input_layernorm_moe_gen"))
+        q, k, v = (span(lin(n1, p + f"self_attn.{w}_proj"), lin(n1[:, g0:g1], p + f"self_attn.{w}_proj_moe_gen")) for w in "qkv")
+        q, k, v = q.reshape(1, S, H, Dh), k.reshape(1, S, KV, Dh), v.reshape(1, S, KV, Dh)
+        q, k = rms(q, p + "self_attn.q_norm"), rms(k, p + "self_attn.k_norm")
+        q = span(q, rms(q[:, g0:g1], p + "self_attn.q_norm_moe_gen"))
+        k = span(k, rms(k[:, g0:g1], p + "self_attn.k_norm_moe_gen"))
+        q, k = rot(q), rot(k)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask, enable_gqa=True)
+        o = o.transpose(1, 2).reshape(1, S, H * Dh)
+        h = h + span(lin(o, p + "self_attn.o_proj"), lin(o[:, g0:g1], p + "self_attn.o_proj_moe_gen"))
+        ffn = lambda v_, n: lin(F.silu(lin(v_, n + ".gate_proj")) * lin(v_, n + ".up_proj"), n + ".down_proj")
+        h = h + span(ffn(rms(h, p + "post_attention_layernorm"), p + "mlp"),
+                     ffn(rms(h[:, g0:g1], p + "post_attention_layernorm_moe_gen"), p + "mlp_moe_gen"))
+    want = lin(rms(h[:, g0:g1], "language_model.model.norm_moe_gen"), "llm2vae")[0]
+    assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
+    # the single-norm variant differs, and the text prefix is causal: a later text token does not move... the generated rows see all text
+    assert (m(inp, x_t, t, renorm_gen=False) - got).abs().max() > 1e-4
+    inp2 = La.build_lance_input(cfg, [3, 4, 5, 7], 2, 2, 3)
+    assert (m(inp2, x_t, t) - got).abs().max() > 1e-5
