@@ -281,6 +281,12 @@ register(ModelManifest(
     notes="token ids and latent tokens share one decoder; generated rows use the *_moe_gen weights; see runtime/lance_kv_plan.py"),
     "lance")
 register(ModelManifest(
+    "magihuman-15b", "magihuman", _M + "magihuman", "MagiHumanDiT", "MagiHumanConfig", "tiny_magihuman_config",
+    LatentSpec(48, 16, 2, True, temporal_factor=4), TextSpec(512, 3584, 0, ("t5gemma",)),
+    ScheduleSpec("shifted", 8, 1.0, shift=5.0), None, "", "", 30.6, ((448, 256),), blocked=_NO_PIPELINE,
+    notes="video, audio and text tokens in one stream; the 1080p super-resolution checkpoint loads through remap_magihuman_sr_keys"),
+    "magihuman", "magihuman-sr")
+register(ModelManifest(
     "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
     ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,

@@ -1018,3 +1018,114 @@ def test_lance_t2v_two_expert_spine_matches_plain_torch_statement():
     assert (m(inp, x_t, t, renorm_gen=False) - got).abs().max() > 1e-4
     inp2 = La.build_lance_input(cfg, [3, 4, 5, 7], 2, 2, 3)
     assert (m(inp2, x_t, t) - got).abs().max() > 1e-5
+
+
+def test_magihuman_three_modality_dit_matches_plain_torch_statement():
+    """MagiHuman: tensor inventory of the 15 B architecture (331 tensors), SwiGLU7 / GELU7, the Fourier rotary table, the model
+    against a plain-torch forward that picks every token's weight set by a modality index, and the split super-resolution
+    checkpoint layout mapped onto the fused one."""
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import magihuman as M
+    torch.manual_seed(41)
+    full = M.MagiHumanDiT(M.MagiHumanConfig(), torch.float32, "meta")
+    shapes = {k: tuple(v.shape) for k, v in full.state_dict().items()}
+    assert len(shapes) == 331
+    for k, s in {"adapter.rope.bands": (16,), "adapter.text_embedder.weight": (5120, 3584), "block.layers.4.attention.linear_qkv.weight": (7208, 5120),
+                 "block.layers.0.attention.linear_qkv.weight": (3 * 7208, 5120), "block.layers.0.mlp.up_gate_proj.weight": (3 * 20480, 5120),
+                 "block.layers.36.mlp.up_gate_proj.weight": (3 * 27304, 5120), "block.layers.20.mlp.down_proj.weight": (5120, 13652),
+                 "block.layers.39.attention.q_norm.weight": (3 * 128,), "final_linear_audio.weight": (64, 5120)}.items():
+        assert shapes[k] == s, k
+    x = torch.tensor([[8.0, -9.0, -1.0, 0.5]])
+    assert torch.allclose(M.swiglu7(x), torch.tensor([[7.0 * torch.sigmoid(torch.tensor(1.702 * 7.0)) * (-7.0 + 1.0),
+                                                       -1.0 * torch.sigmoid(torch.tensor(-1.702)) * 1.5]]))
+    assert torch.allclose(M.gelu7(torch.tensor([9.0, -2.0])), torch.tensor([7.0, -2.0]) * torch.sigmoid(1.702 * torch.tensor([7.0, -2.0])))
+    coords = torch.tensor([[3.0, 2.0, 5.0, 4.0, 6.0, 8.0, 4.0, 12.0, 16.0]])
+    bands = torch.tensor([1.0, 0.1])
+    cos, sin = M.fourier_rope(coords, bands)
+    cx = [3.0 * (3.0 / 3.0), (2.0 - 2.5) * (11.0 / 5.0), (5.0 - 3.5) * (15.0 / 7.0)]
+    want = torch.tensor([c * b for c in cx for b in (1.0, 0.1)], dtype=torch.float64)
+    assert cos.shape == (1, 6) and torch.allclose(cos[0].double(), want.cos(), atol=1e-6) and torch.allclose(sin[0].double(), want.sin(), atol=1e-6)
+
+    cfg = M.tiny_magihuman_config()
+    m = M.MagiHumanDiT(cfg, torch.float32).init_weights(4)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() == 1 and "bands" not in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    V, A, T = 6, 3, 4
+    L = V + A + T
+    video, audio, text = torch.randn(V, cfg.video_in), torch.randn(A, cfg.audio_in), torch.randn(T, cfg.text_in)
+    coords = torch.cat((torch.stack(torch.meshgrid(torch.arange(1.0), torch.arange(2.0), torch.arange(3.0), indexing="ij"), -1).reshape(V, 3),
+                        torch.stack((torch.arange(A).float(), torch.zeros(A), torch.zeros(A)), 1),
+                        torch.stack((torch.arange(T).float(), torch.zeros(T), torch.zeros(T)), 1)), 0)
+    coords = torch.cat((coords, torch.tensor([[1.0, 2.0, 3.0, 1.0, 4.0, 6.0]]).expand(L, 6)), 1)
+    got = m(video, audio, text, coords)
+    assert got.shape == (L, cfg.video_in) and float(got[V + A:].abs().sum()) == 0 and float(got[V:V + A, cfg.audio_in:].abs().sum()) == 0
+
+    mod = torch.tensor([0] * V + [1] * A + [2] * T)
+    H, KV, Dh, D = cfg.num_heads_q, cfg.num_heads_kv, cfg.head_dim, cfg.hidden_size
+    x = torch.cat((F.linear(video, sd["adapter.video_embedder.weight"], sd["adapter.video_embedder.bias"]),
+                   F.linear(audio, sd["adapter.audio_embedder.weight"], sd["adapter.audio_embedder.bias"]),
+                   F.linear(text, sd["adapter.text_embedder.weight"], sd["adapter.text_embedder.bias"])), 0)
+    cos, sin = M.fourier_rope(coords, sd["adapter.rope.bands"])
+
+    def per_token_linear(v, w, sets):          # v [L, in]; w [sets * out, in]
+        w3 = w.reshape(sets, -1, w.shape[-1])
+        return torch.einsum("li,loi->lo", v, w3[mod if sets == 3 else torch.zeros_like(mod)])
+
+    def per_token_norm(v, w, sets):            # v [L, ..., dim]; w [sets * dim]
+        gain = (w.reshape(sets, -1) + 1.0)[mod if sets == 3 else torch.zeros_like(mod)]
+        gain = gain.reshape(L, *([1] * (v.dim() - 2)), -1)
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * gain
+
+    def rope(v):
+        r = cfg.rope_dim
+        a, b = v[..., :r // 2], v[..., r // 2:r]
+        c, s = cos[:, None], sin[:, None]
+        return torch.cat((a * c - b * s, b * c + a * s, v[..., r:]), -1)
+
+    for i in range(cfg.num_layers):
+        p = f"block.layers.{i}."
+        sets = 3 if i in cfg.mm_layers else 1
+        qkv = per_token_linear(per_token_norm(x, sd[p + "attention.pre_norm.weight"], sets), sd[p + "attention.linear_qkv.weight"], sets)
+        q, k, v, g = qkv.split((H * Dh, KV * Dh, KV * Dh, H), -1)
+        q = rope(per_token_norm(q.reshape(L, H, Dh), sd[p + "attention.q_norm.weight"], sets)).transpose(0, 1)
+        k = rope(per_token_norm(k.reshape(L, KV, Dh), sd[p + "attention.k_norm.weight"], sets)).transpose(0, 1)
+        o = F.scaled_dot_product_attention(q[None], k[None], v.reshape(L, KV, Dh).transpose(0, 1)[None], enable_gqa=True)[0].transpose(0, 1)
+        o = (o * torch.sigmoid(g)[..., None]).reshape(L, H * Dh)
+        x = x + per_token_linear(o, sd[p + "attention.linear_proj.weight"], sets)
+        up = per_token_linear(per_token_norm(x, sd[p + "mlp.pre_norm.weight"], sets), sd[p + "mlp.up_gate_proj.weight"], sets)
+        act = M.gelu7(up) if i in cfg.gelu7_layers else M.swiglu7(up)
+        x = x + per_token_linear(act, sd[p + "mlp.down_proj.weight"], sets)
+    nrm = lambda v, w: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * (w + 1.0)
+    want_v = F.linear(nrm(x[:V], sd["final_norm_video.weight"]), sd["final_linear_video.weight"])
+    want_a = F.linear(nrm(x[V:V + A], sd["final_norm_audio.weight"]), sd["final_linear_audio.weight"])
+    assert F.cosine_similarity(got[:V].flatten(), want_v.flatten(), 0) > 0.99999 and (got[:V] - want_v).abs().max() < 2e-4 * want_v.abs().max() + 1e-5
+    assert (got[V:V + A, :cfg.audio_in] - want_a).abs().max() < 2e-4 * want_a.abs().max() + 1e-5
+
+    # super-resolution layout: split the fused tensors the way that checkpoint stores them, then map back
+    split = {}
+    for k, v in sd.items():
+        if k.endswith("attention.linear_qkv.weight") or (".mlp." in k and "pre_norm" not in k) or k.endswith("attention.linear_proj.weight"):
+            i = int(k.split(".")[2])
+            sets = 3 if i in cfg.mm_layers else 1
+            base = k[:-len(".weight")]
+            chunks = v.reshape(sets, -1, v.shape[-1])
+            for s in range(sets):
+                suffix = ("_" + M.MODALITIES[s]) if sets == 3 else ""
+                if k.endswith("linear_qkv.weight"):
+                    for name, part in zip("qkvg", chunks[s].split((H * Dh, KV * Dh, KV * Dh, H), 0)):
+                        split[base[:-len("linear_qkv")] + f"linear_{name}{suffix}.weight"] = part
+                elif sets == 3:
+                    split[base + suffix + ".weight"] = chunks[s]
+                else:
+                    split[k] = v
+        else:
+            split[k] = v
+    assert "block.layers.1.attention.linear_q.weight" in split and "block.layers.0.mlp.down_proj_text.weight" in split
+    back = M.remap_magihuman_sr_keys(split, cfg)
+    assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) for k in sd)
+    # distilled sampler step
+    xs, vs, ns = torch.randn(4), torch.randn(4), torch.randn(4)
+    assert torch.allclose(M.distilled_step(xs, vs, ns, 0.8, 0.5), 0.5 * ns + 0.5 * (xs - 0.8 * vs))
