@@ -287,6 +287,12 @@ register(ModelManifest(
     notes="video, audio and text tokens in one stream; the 1080p super-resolution checkpoint loads through remap_magihuman_sr_keys"),
     "magihuman", "magihuman-sr")
 register(ModelManifest(
+    "sensenova-u1-8b", "sensenova_u1", _M + "sensenova_u1", "SenseNovaU1", "SenseNovaU1Config", "tiny_sensenova_u1_config",
+    LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
+    ScheduleSpec("shifted", 30, 4.0, shift=3.0), None, "", "", 17.0, ((1024, 1024),), blocked=_NO_PIPELINE,
+    notes="pixel space; the prompt's token ids run through the base weights once (key / value cache), image tokens through the _mot_gen weights; `SenseNovaU1.sample` is the loop"),
+    "sensenova-u1", "sensenova")
+register(ModelManifest(
     "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
     ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,

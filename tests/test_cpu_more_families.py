@@ -1129,3 +1129,117 @@ def test_magihuman_three_modality_dit_matches_plain_torch_statement():
     # distilled sampler step
     xs, vs, ns = torch.randn(4), torch.randn(4), torch.randn(4)
     assert torch.allclose(M.distilled_step(xs, vs, ns, 0.8, 0.5), 0.5 * ns + 0.5 * (xs - 0.8 * vs))
+
+
+def test_sensenova_u1_two_weight_set_pixel_model_matches_plain_torch_statement():
+    """SenseNova-U1: tensor inventory of the text-to-image part (26 tensors per layer + 23 shared), patch orders, noise scale, time
+    table, and prompt pass + image pass + head against a plain-torch forward over ONE joint sequence with an explicit mask
+    (prompt rows causal, image rows see everything), which must equal the cached two-pass form."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import sensenova_u1 as S
+    torch.manual_seed(51)
+    full = S.SenseNovaU1(S.SenseNovaU1Config(), torch.float32, "meta")
+    shapes = {k: tuple(v.shape) for k, v in full.state_dict().items()}
+    assert len(shapes) == 26 * 42 + 3 + 4 + 4 + 4 + 4 and S.SenseNovaU1Config().fm_head_out_dim == 3072
+    for k, s in {"language_model.model.layers.0.self_attn.q_norm.weight": (64,), "language_model.model.layers.41.self_attn.k_norm_hw_mot_gen.weight": (64,),
+                 "language_model.model.layers.3.self_attn.k_proj_mot_gen.weight": (1024, 4096), "language_model.model.norm_mot_gen.weight": (4096,),
+                 "fm_modules.vision_model_mot_gen.embeddings.patch_embedding.weight": (1024, 3, 16, 16),
+                 "fm_modules.vision_model_mot_gen.embeddings.dense_embedding.weight": (4096, 1024, 2, 2),
+                 "fm_modules.noise_scale_embedder.mlp.0.weight": (4096, 256), "fm_modules.fm_head.2.weight": (3072, 4096)}.items():
+        assert shapes[k] == s, k
+    assert abs(full.noise_scale(16, 16) - 1.0) < 1e-6 and abs(full.noise_scale(64, 64) - 4.0) < 1e-6 and full.noise_scale(256, 256) == 8.0
+    ts = S.time_schedule(4, 3.0)
+    assert ts[0] == 0.0 and ts[-1] == 1.0 and abs(ts[2] - (1 - 3 * 0.5 / 2.0)) < 1e-12
+    img = torch.randn(1, 3, 8, 12)
+    pc, pl = S.patchify(img, 4, True), S.patchify(img, 4, False)
+    assert torch.equal(pc[0, 4].reshape(3, 4, 4), img[0, :, 4:8, 4:8]) and torch.equal(pl[0, 4].reshape(4, 4, 3), img[0, :, 4:8, 4:8].permute(1, 2, 0))
+    assert torch.equal(S.unpatchify(pl, 4, 8, 12), img)
+
+    cfg = S.tiny_sensenova_u1_config()
+    m = S.SenseNovaU1(cfg, torch.float32).init_weights(6)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    ids = [5, 9, 2, 7, 11]
+    Hh, Ww = 16, 24
+    gh, gw, th, tw = Hh // 4, Ww // 4, Hh // 8, Ww // 8
+    x_img, t = torch.randn(1, 3, Hh, Ww), 0.3
+    cache = m.forward_und(ids)
+    got = m.predict_clean(x_img, t, cache, len(ids))
+    assert got.shape == (1, th * tw, cfg.fm_head_out_dim)
+
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, n: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * sd[n + ".weight"]
+    gelu = lambda v: F.gelu(v, approximate="tanh")
+    H, KV, Dh, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.hidden_size
+    # image tokens
+    px = S.patchify(x_img, 4, True)[0]
+    f = gelu(F.linear(px, sd["fm_modules.vision_model_mot_gen.embeddings.patch_embedding.weight"].flatten(1),
+                      sd["fm_modules.vision_model_mot_gen.embeddings.patch_embedding.bias"]))
+    vh = cfg.vision_hidden_size
+
+    def pair_rot(v, pos, dim):
+        ang = pos.float()[:, None] / (1.0e4 ** (torch.arange(0, dim, 2).float() / dim))[None]
+        return torch.view_as_real(torch.view_as_complex(v.reshape(v.shape[0], -1, 2).contiguous()) * torch.polar(torch.ones_like(ang), ang)).flatten(1)
+
+    n = torch.arange(gh * gw)
+    f = torch.cat((pair_rot(f[:, :vh // 2], n % gw, vh // 2), pair_rot(f[:, vh // 2:], n // gw, vh // 2)), -1)
+    f = f.reshape(th, 2, tw, 2, vh).permute(0, 2, 4, 1, 3).reshape(th * tw, vh * 4)
+    e = F.linear(f, sd["fm_modules.vision_model_mot_gen.embeddings.dense_embedding.weight"].flatten(1),
+                 sd["fm_modules.vision_model_mot_gen.embeddings.dense_embedding.bias"])
+
+    def scalar(v, name):
+        args = torch.tensor([v])[:, None] * torch.exp(-math.log(1.0e4) * torch.arange(128).float() / 128)[None]
+        return lin(F.silu(lin(torch.cat((args.cos(), args.sin()), -1), name + ".mlp.0")), name + ".mlp.2")
+
+    e = e + scalar(t, "fm_modules.timestep_embedder") + scalar(m.noise_scale(gh, gw) / 8.0, "fm_modules.noise_scale_embedder")
+    # one joint sequence: prompt rows on the base weights, image rows on the generation weights
+    P, L = len(ids), th * tw
+    pos = torch.zeros(P + L, 3)
+    pos[:P, 0] = torch.arange(P).float()
+    pos[P:, 0] = P
+    pos[P:, 1] = (torch.arange(L) // tw).float()
+    pos[P:, 2] = (torch.arange(L) % tw).float()
+    x = torch.cat((sd["language_model.model.embed_tokens.weight"][ids], e), 0)[None]
+    mask = torch.ones(P + L, P + L, dtype=torch.bool).tril()
+    mask[P:] = True
+
+    def rot(v, p_, dim, theta):                # half-split, v [1, S, heads, dim]
+        ang = p_[:, None] / (theta ** (torch.arange(0, dim, 2).float() / dim))[None]
+        c_, s_ = ang.cos()[None, :, None], ang.sin()[None, :, None]
+        a_, b_ = v.chunk(2, -1)
+        return torch.cat((a_ * c_ - b_ * s_, b_ * c_ + a_ * s_), -1)
+
+    def two(fn, v):                            # fn(rows, suffix)
+        return torch.cat((fn(v[:, :P], ""), fn(v[:, P:], "_mot_gen")), 1)
+
+    for i in range(cfg.num_layers):
+        p = f"language_model.model.layers.{i}."
+        h = two(lambda r, s: rms(r, p + "input_layernorm" + s), x)
+
+        def qk(which, heads):
+            raw = two(lambda r, s: lin(r, p + f"self_attn.{which}_proj" + s), h).reshape(1, P + L, heads, Dh)
+            vt = two(lambda r, s: rms(r[..., :Dh // 2], p + f"self_attn.{which}_norm" + s), raw)
+            vhw = two(lambda r, s: rms(r[..., Dh // 2:], p + f"self_attn.{which}_norm_hw" + s), raw)
+            return torch.cat((rot(vt, pos[:, 0], Dh // 2, cfg.rope_theta), rot(vhw[..., :Dh // 4], pos[:, 1], Dh // 4, 1.0e4),
+                              rot(vhw[..., Dh // 4:], pos[:, 2], Dh // 4, 1.0e4)), -1)
+
+        q, k = qk("q", H), qk("k", KV)
+        v = two(lambda r, s: lin(r, p + "self_attn.v_proj" + s), h).reshape(1, P + L, KV, Dh)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask, enable_gqa=True)
+        o = o.transpose(1, 2).reshape(1, P + L, H * Dh)
+        x = x + two(lambda r, s: lin(r, p + "self_attn.o_proj" + s), o)
+        h2 = two(lambda r, s: rms(r, p + "post_attention_layernorm" + s), x)
+        x = x + two(lambda r, s: lin(F.silu(lin(r, p + f"mlp{s}.gate_proj")) * lin(r, p + f"mlp{s}.up_proj"), p + f"mlp{s}.down_proj"), h2)
+    want = lin(gelu(lin(rms(x[:, P:], "language_model.model.norm_mot_gen"), "fm_modules.fm_head.0")), "fm_modules.fm_head.2")
+    assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
+
+    # one guided Euler step of the sampler
+    out = m.sample(ids, [5, 9], Hh, Ww, steps=1, cfg_scale=2.0, shift=3.0, noise=x_img)
+    z = S.patchify(x_img * m.noise_scale(gh, gw), 8, False)
+    vc = (m.predict_clean(x_img * m.noise_scale(gh, gw), 0.0, cache, 5) - z) / 1.0
+    vu = (m.predict_clean(x_img * m.noise_scale(gh, gw), 0.0, m.forward_und([5, 9]), 2) - z) / 1.0
+    assert torch.allclose(out, S.unpatchify(z + 1.0 * (vu + 2.0 * (vc - vu)), 8, Hh, Ww) * 0.5 + 0.5, atol=1e-5)
