@@ -293,6 +293,12 @@ register(ModelManifest(
     notes="pixel space; the prompt's token ids run through the base weights once (key / value cache), image tokens through the _mot_gen weights; `SenseNovaU1.sample` is the loop"),
     "sensenova-u1", "sensenova")
 register(ModelManifest(
+    "boogu-image-0.1", "boogu", _M + "boogu", "BooguDiT", "BooguConfig", "tiny_boogu_config",
+    LatentSpec(16, 8, 2, False), TextSpec(512, 4096, 0, ("qwen3_vl",)),
+    ScheduleSpec("shifted", 30, 4.0, shift=3.0), None, "flux_vae_config", "", 10.0, ((1024, 1024),), blocked=_NO_PIPELINE,
+    notes="head width 120: attention runs on the library kernel on the GPU (the tcgen05 kernel covers 64 and 128)"),
+    "boogu")
+register(ModelManifest(
     "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
     ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,

@@ -1243,3 +1243,108 @@ def test_sensenova_u1_two_weight_set_pixel_model_matches_plain_torch_statement()
     vc = (m.predict_clean(x_img * m.noise_scale(gh, gw), 0.0, cache, 5) - z) / 1.0
     vu = (m.predict_clean(x_img * m.noise_scale(gh, gw), 0.0, m.forward_und([5, 9]), 2) - z) / 1.0
     assert torch.allclose(out, S.unpatchify(z + 1.0 * (vu + 2.0 * (vc - vu)), 8, Hh, Ww) * 0.5 + 0.5, atol=1e-5)
+
+
+def test_boogu_double_then_single_stream_dit_matches_plain_torch_statement():
+    """Boogu-Image: checkpoint names of the full architecture, patch order, positions, and the tiny model against a plain-torch
+    forward (norm-zero modulation chunks, tanh gates, joint attention with per-stream projections plus the image self-attention,
+    feed-forward input built from norm2's output with norm1's scale and norm2's chunk-1 shift)."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import boogu as Bg
+    torch.manual_seed(61)
+    full = Bg.BooguDiT(Bg.BooguConfig(), torch.float32, "meta")
+    shapes = {k: tuple(v.shape) for k, v in full.state_dict().items()}
+    for k, s in {"x_embedder.weight": (3360, 64), "time_caption_embed.timestep_embedder.linear_1.weight": (1024, 256),
+                 "time_caption_embed.caption_embedder.0.weight": (4096,), "time_caption_embed.caption_embedder.1.weight": (3360, 4096),
+                 "context_refiner.1.norm1.weight": (3360,), "noise_refiner.0.norm1.linear.weight": (4 * 3360, 1024),
+                 "single_stream_layers.31.attn.to_k.weight": (840, 3360), "single_stream_layers.0.attn.norm_q.weight": (120,),
+                 "single_stream_layers.0.feed_forward.linear_3.weight": (13568, 3360),
+                 "double_stream_layers.7.img_instruct_attn.processor.instruct_to_v.weight": (840, 3360),
+                 "double_stream_layers.0.img_instruct_attn.processor.img_out.weight": (3360, 3360),
+                 "double_stream_layers.0.img_instruct_attn.to_out.0.weight": (3360, 3360), "double_stream_layers.0.img_norm3.linear.bias": (4 * 3360,),
+                 "double_stream_layers.0.img_self_attn.to_out.0.weight": (3360, 3360), "double_stream_layers.0.instruct_ffn_norm2.weight": (3360,),
+                 "norm_out.linear_1.weight": (3360, 1024), "norm_out.linear_2.bias": (64,)}.items():
+        assert shapes[k] == s, k
+    assert not any(k.endswith("to_q.bias") or k.endswith("linear_1.bias") and "feed_forward" in k for k in shapes)
+    lat = torch.randn(1, 4, 4, 6)
+    tok = Bg.boogu_patchify(lat)
+    assert torch.equal(tok[0, 1 * 3 + 2].reshape(2, 2, 4), lat[0, :, 2:4, 4:6].permute(1, 2, 0)) and torch.equal(Bg.boogu_unpatchify(tok, 2, 3), lat)
+    pos = Bg.boogu_positions(3, 2, 4)
+    assert pos[2].tolist() == [2.0, 2.0, 2.0] and pos[3 + 1 * 4 + 2].tolist() == [3.0, 1.0, 2.0]
+
+    cfg = Bg.tiny_boogu_config()
+    m = Bg.BooguDiT(cfg, torch.float32).init_weights(9)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    B, Hh, Ww, Lc = 2, 4, 6, 5
+    h, w = Hh // 2, Ww // 2
+    latent, ins_in, t = torch.randn(B, cfg.in_channels, Hh, Ww), torch.randn(B, Lc, cfg.instruction_dim), torch.tensor([0.15, 0.8])
+    got = m(latent, ins_in, t)
+    assert got.shape == latent.shape
+
+    D, H, KV, Dh = cfg.hidden, cfg.heads, cfg.kv_heads, cfg.head_dim
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, n: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * sd[n + ".weight"]
+    args = (t * 1000.0)[:, None] * torch.exp(-math.log(1.0e4) * torch.arange(128).float() / 128)[None]
+    temb = lin(F.silu(lin(torch.cat((args.cos(), args.sin()), -1), "time_caption_embed.timestep_embedder.linear_1")),
+               "time_caption_embed.timestep_embedder.linear_2")
+    st = F.silu(temb)
+    cap = lin(rms(ins_in, "time_caption_embed.caption_embedder.0"), "time_caption_embed.caption_embedder.1")
+    pos = Bg.boogu_positions(Lc, h, w)
+    ang = torch.cat([pos[:, a:a + 1] / (1.0e4 ** (torch.arange(0, d, 2).float() / d))[None] for a, d in enumerate(cfg.axes_dim)], -1)
+
+    def rope(v, a):
+        rot = torch.polar(torch.ones_like(a), a)[None, :, None]
+        return torch.view_as_real(torch.view_as_complex(v.reshape(*v.shape[:-1], -1, 2).contiguous()) * rot).flatten(-2)
+
+    def sdpa(q, k, v):
+        return F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), enable_gqa=True).transpose(1, 2).flatten(-2)
+
+    def self_attn(v_, p, a):
+        q = rope(rms(lin(v_, p + ".to_q").unflatten(-1, (H, Dh)), p + ".norm_q"), a)
+        k = rope(rms(lin(v_, p + ".to_k").unflatten(-1, (KV, Dh)), p + ".norm_k"), a)
+        return lin(sdpa(q, k, lin(v_, p + ".to_v").unflatten(-1, (KV, Dh))), p + ".to_out.0")
+
+    ffn = lambda v_, p: lin(F.silu(lin(v_, p + ".linear_1")) * lin(v_, p + ".linear_3"), p + ".linear_2")
+    zero = lambda v_, p: (lambda e: (rms(v_, p + ".norm") * (1 + e[0]), e[1], e[2], e[3]))(lin(st, p + ".linear")[:, None].chunk(4, -1))
+
+    def block(v_, p, a, mod):
+        if not mod:
+            v_ = v_ + rms(self_attn(rms(v_, p + ".norm1"), p + ".attn", a), p + ".norm2")
+            return v_ + rms(ffn(rms(v_, p + ".ffn_norm1"), p + ".feed_forward"), p + ".ffn_norm2")
+        hn, g1, s2, g2 = zero(v_, p + ".norm1")
+        v_ = v_ + torch.tanh(g1) * rms(self_attn(hn, p + ".attn", a), p + ".norm2")
+        return v_ + torch.tanh(g2) * rms(ffn(rms(v_, p + ".ffn_norm1") * (1 + s2), p + ".feed_forward"), p + ".ffn_norm2")
+
+    cap = block(cap, "context_refiner.0", ang[:Lc], False)
+    x = block(lin(Bg.boogu_patchify(latent), "x_embedder"), "noise_refiner.0", ang[Lc:], True)
+    for i in range(cfg.n_double):
+        p = f"double_stream_layers.{i}."
+        jp = p + "img_instruct_attn.processor."
+        i1, ig_msa, is_mlp, ig_mlp = zero(x, p + "img_norm1")
+        i2, i_shift, _, _ = zero(x, p + "img_norm2")
+        i3, ig_self, _, _ = zero(x, p + "img_norm3")
+        t1, tg_msa, ts_mlp, tg_mlp = zero(cap, p + "instruct_norm1")
+        t2, t_shift, _, _ = zero(cap, p + "instruct_norm2")
+        q = torch.cat((lin(t1, jp + "instruct_to_q"), lin(i1, jp + "img_to_q")), 1).unflatten(-1, (H, Dh))
+        k = torch.cat((lin(t1, jp + "instruct_to_k"), lin(i1, jp + "img_to_k")), 1).unflatten(-1, (KV, Dh))
+        v = torch.cat((lin(t1, jp + "instruct_to_v"), lin(i1, jp + "img_to_v")), 1).unflatten(-1, (KV, Dh))
+        o = sdpa(rope(rms(q, p + "img_instruct_attn.norm_q"), ang), rope(rms(k, p + "img_instruct_attn.norm_k"), ang), v)
+        o = lin(torch.cat((lin(o[:, :Lc], jp + "instruct_out"), lin(o[:, Lc:], jp + "img_out")), 1), p + "img_instruct_attn.to_out.0")
+        a_self = self_attn(i3, p + "img_self_attn", ang[Lc:])
+        x = x + torch.tanh(ig_msa) * rms(o[:, Lc:], p + "img_attn_norm")
+        x = x + torch.tanh(ig_self) * rms(a_self, p + "img_self_attn_norm")
+        x = x + torch.tanh(ig_mlp) * rms(ffn(rms((1 + is_mlp) * i2 + i_shift, p + "img_ffn_norm1"), p + "img_feed_forward"), p + "img_ffn_norm2")
+        cap = cap + torch.tanh(tg_msa) * rms(o[:, :Lc], p + "instruct_attn_norm")
+        cap = cap + torch.tanh(tg_mlp) * rms(ffn(rms((1 + ts_mlp) * t2 + t_shift, p + "instruct_ffn_norm1"), p + "instruct_feed_forward"),
+                                              p + "instruct_ffn_norm2")
+    joint = torch.cat((cap, x), 1)
+    for i in range(cfg.n_single):
+        joint = block(joint, f"single_stream_layers.{i}", ang, True)
+    y = F.layer_norm(joint, (D,), eps=1e-6) * (1 + lin(st, "norm_out.linear_1"))[:, None]
+    want = Bg.boogu_unpatchify(lin(y, "norm_out.linear_2")[:, Lc:], h, w)
+    assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
