@@ -305,7 +305,7 @@ def test_more_video_and_image_families_on_native_kernels():
 
 
 def test_moe_audio_spine_and_krea2_families_on_native_kernels():
-    """Nucleus-Image (expert-choice MoE), ACE-Step (audio), HiDream-O1 (language-model spine), Krea-2, Lens and Z-Image L2P (tiny configurations,
+    """Nucleus-Image (expert-choice MoE), ACE-Step (audio), HiDream-O1 (language-model spine), Krea-2, Lens, Z-Image L2P, Boogu-Image, MagiHuman, Lance T2V and SenseNova-U1 (tiny configurations,
     head width 64) in bf16 on the sm_100a kernels against their fp32 CPU forward."""
     import dataclasses
     from mojodiffusion_b200.models.acestep import AceStepDiT, tiny_acestep_config
@@ -331,6 +331,32 @@ def test_moe_audio_spine_and_krea2_families_on_native_kernels():
     _gpu_vs_cpu(lambda dt, dev: LensDiT(cl, dt, dev), (rn(1, 8 * 8, cl.in_channels), rn(1, 16, 4, cl.text_hidden), torch.tensor([0.4])), cos_min=0.99, hw=(8, 8))
     cz = tiny_zimage_l2p_config()
     _gpu_vs_cpu(lambda dt, dev: ZImageL2P(cz, dt, dev, (64, 64, 128, 128)), (rn(1, 3, 64, 64), rn(1, 16, cz.cap_dim), torch.tensor([0.6])), cos_min=0.99)
+    from mojodiffusion_b200.models.boogu import BooguDiT, tiny_boogu_config
+    cb = tiny_boogu_config()
+    _gpu_vs_cpu(lambda dt, dev: BooguDiT(cb, dt, dev), (rn(1, cb.in_channels, 16, 16), rn(1, 16, cb.instruction_dim), torch.tensor([0.3])), cos_min=0.99)
+    from mojodiffusion_b200.models.magihuman import MagiHumanDiT, tiny_magihuman_config
+    cm = dataclasses.replace(tiny_magihuman_config(), hidden_size=256, head_dim=64, rope_dim=48, rope_bands=8)
+    V, A, T = 32, 8, 8
+    coords = torch.cat((torch.stack(torch.meshgrid(torch.arange(2.0), torch.arange(4.0), torch.arange(4.0), indexing="ij"), -1).reshape(V, 3),
+                        torch.stack((torch.arange(A).float(), torch.zeros(A), torch.zeros(A)), 1),
+                        torch.stack((torch.arange(T).float(), torch.zeros(T), torch.zeros(T)), 1)), 0)
+    coords = torch.cat((coords, torch.tensor([[2.0, 4.0, 4.0, 2.0, 8.0, 8.0]]).expand(V + A + T, 6)), 1)
+    _gpu_vs_cpu(lambda dt, dev: MagiHumanDiT(cm, dt, dev), (rn(V, cm.video_in), rn(A, cm.audio_in), rn(T, cm.text_in), coords), cos_min=0.99)
+    from mojodiffusion_b200.models.lance import LanceT2V, build_lance_input, tiny_lance_config
+    from mojodiffusion_b200.models.sensenova_u1 import SenseNovaU1, tiny_sensenova_u1_config
+    for make, run in ((lambda dt, dev: LanceT2V(tiny_lance_config(), dt, dev),
+                       lambda mod, dev: mod(build_lance_input(tiny_lance_config(), [3, 4, 5, 6], 2, 2, 3), xl.to(dev), torch.tensor([0.4], device=dev))),
+                      (lambda dt, dev: SenseNovaU1(dataclasses.replace(tiny_sensenova_u1_config(), head_dim=64), dt, dev),
+                       lambda mod, dev: mod.predict_clean(xs.to(dev), 0.3, mod.forward_und([5, 9, 2, 7]), 4))):
+        xl, xs = rn(12, tiny_lance_config().patch_latent_dim), rn(1, 3, 32, 32)
+        m32 = make(torch.float32, "cpu").init_weights(0)
+        mg = make(torch.bfloat16, DEV)
+        mg.load_state_dict({k: v.to(torch.bfloat16) for k, v in m32.state_dict().items()})
+        m32.load_state_dict({k: v.float() for k, v in mg.state_dict().items()})
+        with torch.no_grad():
+            want, got = run(m32, "cpu"), run(mg, DEV)
+        native.check_status()
+        assert torch.isfinite(got.float()).all() and _cos(got, want) >= 0.99
     chd = tiny_hidream_o1_config()
     chd = dataclasses.replace(chd, spine=dataclasses.replace(chd.spine, hidden_size=256, head_dim=64))
     ids = [1, 2, chd.tms_token_id, 3, chd.vision_start_token_id]
