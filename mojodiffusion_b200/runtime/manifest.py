@@ -299,6 +299,12 @@ register(ModelManifest(
     notes="head width 120: attention runs on the library kernel on the GPU (the tcgen05 kernel covers 64 and 128)"),
     "boogu")
 register(ModelManifest(
+    "nava", "nava", _M + "nava", "NavaDiT", "NavaConfig", "tiny_nava_config",
+    LatentSpec(48, 16, 2, False, temporal_factor=4), TextSpec(512, 4096, 0, ("umt5",)),
+    ScheduleSpec("shifted", 50, 5.0, shift=5.0), None, "", "", 5.9, ((832, 480),), blocked=_NO_PIPELINE,
+    notes="video and audio latents in one sequence; fp8 checkpoint rows are dequantised by remap_nava_keys"),
+    "nava-av")
+register(ModelManifest(
     "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
     ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,

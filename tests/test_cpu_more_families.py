@@ -1348,3 +1348,129 @@ def test_boogu_double_then_single_stream_dit_matches_plain_torch_statement():
     y = F.layer_norm(joint, (D,), eps=1e-6) * (1 + lin(st, "norm_out.linear_1"))[:, None]
     want = Bg.boogu_unpatchify(lin(y, "norm_out.linear_2")[:, Lc:], h, w)
     assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
+
+
+def test_nava_audio_video_dit_matches_plain_torch_statement():
+    """NAVA: checkpoint names of the full architecture, the joint rotary table (video three axes, audio one position on 44
+    columns), the fp8 + prefix key mapping, and the tiny model against a plain-torch forward with per-stream weights in the
+    double blocks."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import nava as Nv
+    torch.manual_seed(71)
+    full = Nv.NavaDiT(Nv.NavaConfig(), torch.float32, "meta")
+    shapes = {k: tuple(v.shape) for k, v in full.state_dict().items()}
+    for k, s in {"patch_embedding.weight": (3072, 48, 1, 2, 2), "patch_embedding_audio.0.weight": (3072, 128, 7), "patch_embedding_audio.0.bias": (3072,),
+                 "patch_embedding_audio.2.w1.weight": (8192, 3072, 7), "patch_embedding_audio.2.w2.weight": (3072, 8192, 7),
+                 "text_embedding.0.weight": (3072, 4096), "time_projection.1.weight": (18432, 3072),
+                 "double_blocks.9.self_attn.q_audio.weight": (3072, 3072), "double_blocks.0.cross_attn.norm_k_audio.weight": (3072,),
+                 "double_blocks.0.modulation_audio.modulation": (1, 6, 3072), "double_blocks.0.modulation.modulation": (1, 6, 3072),
+                 "double_blocks.0.norm3.bias": (3072,), "double_blocks.0.ffn.0.weight": (14336, 3072),
+                 "single_blocks.19.cross_attn.o.bias": (3072,), "single_blocks.0.modulation": (1, 6, 3072),
+                 "head.head.weight": (192, 3072), "head.modulation": (1, 2, 3072), "head_audio.head.weight": (128, 3072)}.items():
+        assert shapes[k] == s, k
+    assert "patch_embedding_audio.2.w1.bias" not in shapes and "single_blocks.0.self_attn.q_audio.weight" not in shapes
+    cos, sin = Nv.nava_rope_table(5, 8, 8, 34, Nv.NavaConfig())
+    assert cos.shape == (354, 64)
+    tok = 2 * 64 + 3 * 8 + 5
+    for pair, want in ((0, 2.0), (21, 2.0 / 1.0e4 ** (42 / 44.0)), (22 + 4, 3.0 / 1.0e4 ** (8 / 42.0)), (43 + 20, 5.0 / 1.0e4 ** (40 / 42.0))):
+        assert abs(float(cos[tok, pair]) - math.cos(want)) < 1e-5
+    a7 = 7 * 0.24
+    assert abs(float(sin[320 + 7, 3]) - math.sin(a7 / 1.0e4 ** (6 / 44.0))) < 1e-5 and float(cos[320 + 7, 22]) == 1.0 and float(sin[320 + 7, 63]) == 0.0
+
+    cfg = Nv.tiny_nava_config()
+    m = Nv.NavaDiT(cfg, torch.float32).init_weights(3)
+    with torch.no_grad():
+        g = torch.Generator().manual_seed(5)
+        for n, p in m.named_parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn(p.shape, generator=g) * 0.1)
+            if p.dim() == 3 and "patch_embedding_audio" in n:
+                p.copy_(torch.randn(p.shape, generator=g) / math.sqrt(p.shape[1] * p.shape[2]))
+    sd = m.state_dict()
+    B, Fr, Hh, Ww, Na, Lt = 1, 2, 4, 6, 5, 7
+    video, audio, text, t = torch.randn(B, cfg.in_dim, Fr, Hh, Ww), torch.randn(B, Na, cfg.audio_dim), torch.randn(B, Lt, cfg.text_dim), torch.tensor([0.45])
+    got_v, got_a = m(video, audio, text, t)
+    assert got_v.shape == video.shape and got_a.shape == audio.shape
+
+    D, H = cfg.dim, cfg.heads
+    Dh = D // H
+    f, h, w = Fr, Hh // 2, Ww // 2
+    V = f * h * w
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, n: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * sd[n + ".weight"]
+    ln = lambda v: F.layer_norm(v, (D,), eps=1e-6)
+    gelu = lambda v: F.gelu(v, approximate="tanh")
+    tokv = video.reshape(B, cfg.in_dim, f, 1, h, 2, w, 2).permute(0, 2, 4, 6, 1, 3, 5, 7).reshape(B, V, -1)       # (c, pt, ph, pw) per token
+    xv = F.linear(tokv, sd["patch_embedding.weight"].flatten(1), sd["patch_embedding.bias"])
+    c1 = lambda v, n, b=None: F.conv1d(v.transpose(1, 2), sd[n + ".weight"], sd.get(n + ".bias"), padding=3).transpose(1, 2)
+    ha = F.silu(c1(audio, "patch_embedding_audio.0"))
+    xa = c1(F.silu(c1(ha, "patch_embedding_audio.2.w1")) * c1(ha, "patch_embedding_audio.2.w3"), "patch_embedding_audio.2.w2")
+    ctx = lin(gelu(lin(torch.cat((text, torch.zeros(B, cfg.text_len - Lt, cfg.text_dim)), 1), "text_embedding.0")), "text_embedding.2")
+    half = cfg.freq_dim // 2
+    args = (t * 1000.0)[:, None] * torch.exp(-math.log(1.0e4) * torch.arange(half).float() / half)[None]
+    e = lin(F.silu(lin(torch.cat((args.cos(), args.sin()), -1), "time_embedding.0")), "time_embedding.2")
+    e0 = lin(F.silu(e), "time_projection.1").reshape(B, 6, D)
+    vpos = torch.stack(torch.meshgrid(torch.arange(f).float(), torch.arange(h).float(), torch.arange(w).float(), indexing="ij"), -1).reshape(V, 3)
+    vang = torch.cat([vpos[:, a:a + 1] / (1.0e4 ** (torch.arange(0, d, 2).float() / d))[None] for a, d in enumerate(cfg.axes_dim)], -1)
+    aang = (torch.arange(Na).float() * 0.24)[:, None] / (1.0e4 ** (torch.arange(0, cfg.audio_rope_dim, 2).float() / cfg.audio_rope_dim))[None]
+
+    def rope(v, ang, width):                       # v [B, S, H, Dh]; rotate the first ``width`` columns in interleaved pairs
+        r = v[..., :width]
+        rot = torch.polar(torch.ones_like(ang), ang)[None, :, None]
+        r = torch.view_as_real(torch.view_as_complex(r.reshape(*r.shape[:-1], -1, 2).contiguous()) * rot).flatten(-2)
+        return torch.cat((r, v[..., width:]), -1)
+
+    sdpa = lambda q, k, v: F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).flatten(-2)
+    heads = lambda v: v.unflatten(-1, (H, Dh))
+
+    def cross(xs, p, sfx):
+        q = heads(rms(lin(ln(xs) * sd[p + "norm3.weight"] + sd[p + "norm3.bias"], p + "cross_attn.q" + sfx), p + "cross_attn.norm_q" + sfx))
+        k = heads(rms(lin(ctx, p + "cross_attn.k" + sfx), p + "cross_attn.norm_k" + sfx))
+        return xs + lin(sdpa(q, k, heads(lin(ctx, p + "cross_attn.v" + sfx))), p + "cross_attn.o" + sfx)
+
+    xv_, xa_ = xv, xa
+    for i in range(cfg.double_depth):
+        p = f"double_blocks.{i}."
+        ev = (sd[p + "modulation.modulation"] + e0)[:, :, None]
+        ea = (sd[p + "modulation_audio.modulation"] + e0)[:, :, None]
+        nv, na = ln(xv_) * (1 + ev[:, 1]) + ev[:, 0], ln(xa_) * (1 + ea[:, 1]) + ea[:, 0]
+        qv = rope(heads(rms(lin(nv, p + "self_attn.q"), p + "self_attn.norm_q")), vang, Dh)
+        kv = rope(heads(rms(lin(nv, p + "self_attn.k"), p + "self_attn.norm_k")), vang, Dh)
+        qa = rope(heads(rms(lin(na, p + "self_attn.q_audio"), p + "self_attn.norm_q_audio")), aang, cfg.audio_rope_dim)
+        ka = rope(heads(rms(lin(na, p + "self_attn.k_audio"), p + "self_attn.norm_k_audio")), aang, cfg.audio_rope_dim)
+        o = sdpa(torch.cat((qv, qa), 1), torch.cat((kv, ka), 1), torch.cat((heads(lin(nv, p + "self_attn.v")), heads(lin(na, p + "self_attn.v_audio"))), 1))
+        xv_ = xv_ + lin(o[:, :V], p + "self_attn.o") * ev[:, 2]
+        xa_ = xa_ + lin(o[:, V:], p + "self_attn.o_audio") * ea[:, 2]
+        xv_, xa_ = cross(xv_, p, ""), cross(xa_, p, "_audio")
+        xv_ = xv_ + lin(gelu(lin(ln(xv_) * (1 + ev[:, 4]) + ev[:, 3], p + "ffn.0")), p + "ffn.2") * ev[:, 5]
+        xa_ = xa_ + lin(gelu(lin(ln(xa_) * (1 + ea[:, 4]) + ea[:, 3], p + "ffn.0")), p + "ffn.2") * ea[:, 5]
+    x = torch.cat((xv_, xa_), 1)
+    for i in range(cfg.depth):
+        p = f"single_blocks.{i}."
+        em = (sd[p + "modulation"] + e0)[:, :, None]
+        n1 = ln(x) * (1 + em[:, 1]) + em[:, 0]
+        q, k = heads(rms(lin(n1, p + "self_attn.q"), p + "self_attn.norm_q")), heads(rms(lin(n1, p + "self_attn.k"), p + "self_attn.norm_k"))
+        q = torch.cat((rope(q[:, :V], vang, Dh), rope(q[:, V:], aang, cfg.audio_rope_dim)), 1)
+        k = torch.cat((rope(k[:, :V], vang, Dh), rope(k[:, V:], aang, cfg.audio_rope_dim)), 1)
+        x = x + lin(sdpa(q, k, heads(lin(n1, p + "self_attn.v"))), p + "self_attn.o") * em[:, 2]
+        x = cross(x, p, "")
+        x = x + lin(gelu(lin(ln(x) * (1 + em[:, 4]) + em[:, 3], p + "ffn.0")), p + "ffn.2") * em[:, 5]
+    hv = (sd["head.modulation"] + e[:, None])[:, :, None]
+    ha_ = (sd["head_audio.modulation"] + e[:, None])[:, :, None]
+    want_v = lin(ln(x[:, :V]) * (1 + hv[:, 1]) + hv[:, 0], "head.head")
+    want_v = want_v.reshape(B, f, h, w, 1, 2, 2, cfg.out_dim).permute(0, 7, 1, 4, 2, 5, 3, 6).reshape(video.shape)
+    want_a = lin(ln(x[:, V:]) * (1 + ha_[:, 1]) + ha_[:, 0], "head_audio.head")
+    for got, want in ((got_v, want_v), (got_a, want_a)):
+        assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
+    # per-modality attention in the double blocks changes the result; the checkpoint mapping strips the prefix and dequantises fp8 rows
+    cfg0 = Nv.tiny_nava_config()
+    cfg0.depth = 0
+    m0 = Nv.NavaDiT(cfg0, torch.float32).init_weights(3)
+    assert (m0(video, audio, text, t, masking_modality=True)[0] - m0(video, audio, text, t)[0]).abs().max() > 1e-6
+    wq = torch.randn(4, 8).clamp(-2, 2).to(torch.float8_e4m3fn)
+    raw = {"backbone.double_blocks.0.ffn.0.weight": wq, "backbone.double_blocks.0.ffn.0.weight_scale": torch.tensor([0.5, 1.0, 2.0, 4.0]),
+           "backbone.double_blocks.0.ffn.0.bias": torch.ones(4), "other.key": torch.zeros(1)}
+    mapped = Nv.remap_nava_keys(raw, torch.float32)
+    assert set(mapped) == {"double_blocks.0.ffn.0.weight", "double_blocks.0.ffn.0.bias"}
+    assert torch.equal(mapped["double_blocks.0.ffn.0.weight"], wq.float() * torch.tensor([0.5, 1.0, 2.0, 4.0])[:, None])
