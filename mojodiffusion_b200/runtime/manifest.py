@@ -305,6 +305,12 @@ register(ModelManifest(
     notes="video and audio latents in one sequence; fp8 checkpoint rows are dequantised by remap_nava_keys"),
     "nava-av")
 register(ModelManifest(
+    "pid-sr4x", "pid", _M + "pid", "PidNet", "PidConfig", "tiny_pid_config",
+    LatentSpec(3, 1, 16, False), TextSpec(300, 2304, 0, ("gemma2_2b",)),
+    ScheduleSpec("pid_distill", 4, 1.0), None, "", "", 1.4, ((2048, 2048),), blocked=_NO_PIPELINE,
+    notes="pixel-space super-resolution decoder conditioned on a low-quality 16-channel latent; `sampling.family_schedules.pid_distill_sample` is its sampler"),
+    "pid", "pixeldit")
+register(ModelManifest(
     "hidream-o1", "hidream_o1", _M + "hidream_o1", "HiDreamO1", "HiDreamO1Config", "tiny_hidream_o1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
     ScheduleSpec("hidream_o1", 28, 5.0), None, "", "", 8.0, ((1024, 1024),), blocked=_NO_PIPELINE,

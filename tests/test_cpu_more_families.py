@@ -1474,3 +1474,106 @@ def test_nava_audio_video_dit_matches_plain_torch_statement():
     mapped = Nv.remap_nava_keys(raw, torch.float32)
     assert set(mapped) == {"double_blocks.0.ffn.0.weight", "double_blocks.0.ffn.0.bias"}
     assert torch.equal(mapped["double_blocks.0.ffn.0.weight"], wq.float() * torch.tensor([0.5, 1.0, 2.0, 4.0])[:, None])
+
+
+def test_pid_pixel_super_resolution_net_matches_plain_torch_statement():
+    """PiD: checkpoint names of the released configuration, the max-period-10 timestep sinusoid, the NTK 2-D rotary table and the
+    sin / cos pixel positions against their formulas, and the tiny net against a plain-torch forward (latent branch with gated
+    injection every second block, dual-stream MMDiT blocks, per-pixel modulated PiT blocks, fold to the image)."""
+    import math
+    import torch.nn.functional as F
+    from mojodiffusion_b200.models import pid as P
+    torch.manual_seed(81)
+    full = P.PidNet(P.PidConfig(), torch.float32, "meta")
+    shapes = {k: tuple(v.shape) for k, v in full.state_dict().items()}
+    for k, s in {"s_embedder.proj.weight": (1536, 768), "t_embedder.mlp.0.weight": (1536, 256), "y_embedder.proj.weight": (1536, 2304),
+                 "y_embedder.norm.weight": (1536,), "y_pos_embedding": (1, 300, 1536), "lq_proj.latent_proj.0.weight": (512, 3, 3, 16),
+                 "lq_proj.latent_proj.6.block.5.bias": (512,), "lq_proj.latent_proj.3.block.0.weight": (512,), "lq_proj.output_heads.6.weight": (1536, 512),
+                 "lq_proj.gate_modules.0.content_proj.weight": (1536, 3072), "lq_proj.gate_modules.6.log_alpha": (),
+                 "patch_blocks.13.adaLN_modulation_txt.0.weight": (9216, 1536), "patch_blocks.0.attn.qkv_y.weight": (4608, 1536),
+                 "patch_blocks.0.attn.k_norm_x.weight": (64,), "patch_blocks.0.attn.proj_y.bias": (1536,), "patch_blocks.0.mlp_x.w3.weight": (4096, 1536),
+                 "pixel_embedder.proj.weight": (16, 3), "pixel_blocks.1.adaLN_modulation.0.weight": (6 * 16 * 256, 1536),
+                 "pixel_blocks.0.compress_to_attn.weight": (1152, 4096), "pixel_blocks.0.expand_from_attn.bias": (4096,),
+                 "pixel_blocks.0.attn.qkv.weight": (3456, 1152), "pixel_blocks.0.attn.q_norm.weight": (72,), "pixel_blocks.0.mlp.fc1.weight": (64, 16),
+                 "final_layer.norm.weight": (16,), "final_layer.linear.weight": (3, 16)}.items():
+        assert shapes[k] == s, k
+    assert len([k for k in shapes if k.startswith("lq_proj.output_heads.")]) == 14 and "patch_blocks.0.attn.qkv_x.bias" not in shapes
+    e = P.pid_timestep_embedding(torch.tensor([0.7]), 8)
+    assert torch.allclose(e[0, :4], torch.cos(0.7 * torch.exp(-math.log(10.0) * torch.arange(4).float() / 4))) and torch.allclose(e[0, 4:], torch.sin(0.7 * torch.exp(-math.log(10.0) * torch.arange(4).float() / 4)))
+    cos, sin = P.ntk_rope_2d(64, 8, 16, 64, 64)
+    th_h, th_w = 1.0e4 * (8 / 64) ** (32 / 30), 1.0e4 * (16 / 64) ** (32 / 30)
+    pos = 3 * 16 + 5
+    assert abs(float(cos[pos, 2 * 4]) - math.cos(16.0 * 5 / 15 / th_w ** (16 / 64))) < 1e-5 and abs(float(sin[pos, 2 * 4 + 1]) - math.sin(16.0 * 3 / 7 / th_h ** (16 / 64))) < 1e-5
+    pp = P.sincos_pos_2d(16, 4, 6)
+    om = 1.0 / 10000.0 ** (torch.arange(4).float() / 4)
+    assert torch.allclose(pp[2 * 6 + 5], torch.cat(((5 * om).sin(), (5 * om).cos(), (2 * om).sin(), (2 * om).cos())), atol=1e-6)
+
+    cfg = P.tiny_pid_config()
+    m = P.PidNet(cfg, torch.float32).init_weights(7)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() <= 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = m.state_dict()
+    B, H, W, Lt, sigma = 2, 8, 12, 5, 0.3
+    ps, D, G, hd = cfg.patch_size, cfg.hidden, cfg.groups, cfg.head_dim
+    ph, pw = H // ps, W // ps
+    L, P2, Cp = ph * pw, ps * ps, cfg.pixel_dim
+    x, t, cap, lat = torch.randn(B, 3, H, W), torch.tensor([0.2, 0.9]), torch.randn(B, Lt, cfg.txt_dim), torch.randn(B, cfg.lq_channels, 1, 3)
+    got = m(x, t, cap, lat, sigma)
+    assert got.shape == x.shape
+
+    lin = lambda v, n: F.linear(v, sd[n + ".weight"], sd.get(n + ".bias"))
+    rms = lambda v, n: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * sd[n + ".weight"]
+    conv = lambda v, n: F.conv2d(v, sd[n + ".weight"].permute(0, 3, 1, 2), sd[n + ".bias"], padding=1)
+    h = conv(F.silu(conv(F.interpolate(lat, size=(ph, pw), mode="nearest"), "lq_proj.latent_proj.0")), "lq_proj.latent_proj.2")
+    for i in range(3, 7):
+        p = f"lq_proj.latent_proj.{i}.block."
+        r = conv(F.silu(F.group_norm(h, 4, sd[p + "0.weight"], sd[p + "0.bias"], 1e-5)), p + "2")
+        h = h + conv(F.silu(F.group_norm(r, 4, sd[p + "3.weight"], sd[p + "3.bias"], 1e-5)), p + "5")
+    lq_tok = h.flatten(2).transpose(1, 2)
+    s = lin(F.unfold(x, ps, stride=ps).transpose(1, 2), "s_embedder.proj")
+    t_emb = lin(F.silu(lin(P.pid_timestep_embedding(t, cfg.freq_dim), "t_embedder.mlp.0")), "t_embedder.mlp.2")
+    cond = F.silu(t_emb)[:, None]
+    y = rms(lin(cap, "y_embedder.proj"), "y_embedder.norm") + sd["y_pos_embedding"][:, :Lt]
+
+    def rope(v, table):                      # v [B, N, heads, d]
+        rot = torch.complex(table[0], table[1])[None, :, None]
+        return torch.view_as_real(torch.view_as_complex(v.reshape(*v.shape[:-1], -1, 2).contiguous()) * rot).flatten(-2)
+
+    sdpa = lambda q, k, v: F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).flatten(-2)
+    img_rope, txt_rope = P.ntk_rope_2d(hd, ph, pw, cfg.rope_ref, cfg.rope_ref), P.text_rope_1d(Lt, hd)
+    for i in range(cfg.patch_depth):
+        if i % 2 == 0:
+            g = f"lq_proj.gate_modules.{i // 2}."
+            lqf = lin(lq_tok, f"lq_proj.output_heads.{i // 2}")
+            s = s + torch.sigmoid(lin(torch.cat((s, lqf), -1), g + "content_proj") - torch.exp(sd[g + "log_alpha"]) * sigma) * lqf
+        p = f"patch_blocks.{i}."
+        mx, my = lin(cond, p + "adaLN_modulation_img.0").chunk(6, -1), lin(cond, p + "adaLN_modulation_txt.0").chunk(6, -1)
+        qx, kx, vx = lin((1 + mx[1]) * rms(s, p + "norm_x1") + mx[0], p + "attn.qkv_x").reshape(B, L, 3, G, hd).unbind(2)
+        qy, ky, vy = lin((1 + my[1]) * rms(y, p + "norm_y1") + my[0], p + "attn.qkv_y").reshape(B, Lt, 3, G, hd).unbind(2)
+        q = torch.cat((rope(rms(qy, p + "attn.q_norm_y"), txt_rope), rope(rms(qx, p + "attn.q_norm_x"), img_rope)), 1)
+        k = torch.cat((rope(rms(ky, p + "attn.k_norm_y"), txt_rope), rope(rms(kx, p + "attn.k_norm_x"), img_rope)), 1)
+        o = sdpa(q, k, torch.cat((vy, vx), 1))
+        s = s + mx[2] * lin(o[:, Lt:], p + "attn.proj_x")
+        y = y + my[2] * lin(o[:, :Lt], p + "attn.proj_y")
+        ffn = lambda v_, n: lin(F.silu(lin(v_, n + ".w1")) * lin(v_, n + ".w3"), n + ".w2")
+        s = s + mx[5] * ffn((1 + mx[4]) * rms(s, p + "norm_x2") + mx[3], p + "mlp_x")
+        y = y + my[5] * ffn((1 + my[4]) * rms(y, p + "norm_y2") + my[3], p + "mlp_y")
+    s_cond = F.silu(s + t_emb[:, None]).reshape(B * L, D)
+    px = lin(x.permute(0, 2, 3, 1), "pixel_embedder.proj") + P.sincos_pos_2d(Cp, H, W).reshape(1, H, W, Cp)
+    px = F.unfold(px.permute(0, 3, 1, 2), ps, stride=ps).reshape(B, Cp, P2, L).permute(0, 3, 2, 1).reshape(B * L, P2, Cp)
+    pix_rope = P.ntk_rope_2d(cfg.pixel_attn // cfg.pixel_groups, ph, pw, cfg.rope_ref, cfg.rope_ref)
+    for j in range(cfg.pixel_depth):
+        p = f"pixel_blocks.{j}."
+        sh1, sc1, g1, sh2, sc2, g2 = lin(s_cond, p + "adaLN_modulation.0").reshape(B * L, P2, 6 * Cp).chunk(6, -1)
+        hcomp = lin((rms(px, p + "norm1") * (1 + sc1) + sh1).reshape(B * L, P2 * Cp), p + "compress_to_attn").reshape(B, L, -1)
+        q, k, v = lin(hcomp, p + "attn.qkv").reshape(B, L, 3, cfg.pixel_groups, -1).unbind(2)
+        a = lin(sdpa(rope(rms(q, p + "attn.q_norm"), pix_rope), rope(rms(k, p + "attn.k_norm"), pix_rope), v), p + "attn.proj")
+        px = px + g1 * lin(a.reshape(B * L, -1), p + "expand_from_attn").reshape(B * L, P2, Cp)
+        px = px + g2 * lin(F.gelu(lin(rms(px, p + "norm2") * (1 + sc2) + sh2, p + "mlp.fc1")), p + "mlp.fc2")
+    out = lin(rms(px, "final_layer.norm"), "final_layer.linear").reshape(B, L, P2, 3).permute(0, 3, 2, 1).reshape(B, 3 * P2, L)
+    want = F.fold(out, (H, W), ps, stride=ps)
+    assert F.cosine_similarity(got.flatten(), want.flatten(), 0) > 0.99999 and (got - want).abs().max() < 2e-4 * want.abs().max() + 1e-5
+    raw = {k: (v.permute(0, 3, 1, 2).contiguous() if v.dim() == 4 else v) for k, v in sd.items()}
+    assert all(torch.equal(v, sd[k]) for k, v in P.remap_pid_keys(raw).items())
