@@ -64,6 +64,88 @@ def test_qwen3_encoder_matches_hf():
     assert torch.allclose(mine(ids, layer=-2, final_norm=False), ref.hidden_states[-2], atol=2e-5)
 
 
+def test_mistral_style_encoder_matches_hf_and_scaled_rotary_frequencies():
+    """The decoder stack without QK norms equals transformers' MistralModel (hidden state of a middle layer included); the scaled
+    inverse frequencies follow the three-band rule, and with the ERNIE encoder's constants every frequency is divided by 16."""
+    import math
+    from mojodiffusion_b200.models.text import qwen3 as Q
+    if not hasattr(transformers, "MistralModel"):
+        pytest.skip("transformers without Mistral")
+    torch.manual_seed(0)
+    hc = transformers.MistralConfig(vocab_size=80, hidden_size=32, intermediate_size=64, num_hidden_layers=4, num_attention_heads=4,
+                                    num_key_value_heads=2, head_dim=8, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=64,
+                                    sliding_window=None)
+    hf = transformers.MistralModel(hc).eval()
+    mine = Qwen3Encoder(Qwen3Config(80, 32, 64, 4, 4, 2, 8, 1e-5, 10000.0, qk_norm=False))
+    raw = {"language_model.model." + k: v for k, v in hf.state_dict().items()}
+    raw["vision_tower.x"] = torch.zeros(1)
+    missing, unexpected = mine.load_state_dict(Q.remap_mistral3b_keys(raw), strict=False)
+    assert not missing and not unexpected
+    ids, real = Q.pad_or_trim_ids([1, 5, 9, 33, 7], 9)
+    assert ids == [1, 5, 9, 33, 7, 0, 0, 0, 0] and real == 5 and Q.pad_or_trim_ids(range(20), 4) == ([0, 1, 2, 3], 4)
+    t = torch.tensor([ids])
+    with torch.no_grad():
+        ref = hf(input_ids=t, output_hidden_states=True)
+    assert torch.allclose(mine(t, layer=3, final_norm=False), ref.hidden_states[3], atol=2e-5)
+    assert torch.allclose(mine(t), ref.last_hidden_state, atol=2e-5)
+
+    c = Q.mistral3b_config()
+    assert (c.num_hidden_layers, c.hidden_size, c.num_key_value_heads, Q.MISTRAL3B_EXTRACT_LAYER) == (26, 3072, 8, 24) and not c.qk_norm
+    base = 1.0 / (1.0e6 ** (torch.arange(0, 128, 2, dtype=torch.float64) / 128))
+    assert torch.allclose(Q.scaled_inv_freq(128, 1.0e6, c.rope_scaling).double(), base / 16.0, rtol=1e-6)
+    assert torch.allclose(Q.scaled_inv_freq(128, 1.0e6, None).double(), base, rtol=1e-6)
+    # a setting that exercises all three bands: orig 64 positions, beta_fast 4 -> low 41, beta_slow 0.2 -> high 2
+    got = Q.scaled_inv_freq(16, 100.0, (8.0, 64, 4.0, 0.2)).double()
+    low, high = float(int(64 / (2 * math.pi / 4.0) + 0.5)), float(int(64 / (2 * math.pi / 0.2) + 0.5))
+    for i in range(8):
+        f = 1.0 / 100.0 ** (2 * i / 16)
+        wl = 2 * math.pi / f
+        if wl < 64 / high:
+            want = f
+        elif wl > 64 / low:
+            want = f / 8.0
+        else:
+            sm = (64 / wl - low) / (high - low)
+            want = (1 - sm) * f / 8.0 + sm * f
+        assert abs(float(got[i]) - want) < 1e-7 * max(1.0, want)
+
+
+def test_qwen3vl_text_paths_layer_stacks_and_key_mapping():
+    """Layer outputs equal transformers' hidden_states; Krea-2 stacks twelve of them and drops the template rows; Ideogram-4
+    interleaves thirteen taps per feature; checkpoint prefixes and fp8 rows map onto the encoder's names."""
+    from mojodiffusion_b200.models.text import qwen3 as Q
+    if not hasattr(transformers, "Qwen3Model"):
+        pytest.skip("transformers without Qwen3")
+    torch.manual_seed(1)
+    hc = transformers.Qwen3Config(vocab_size=80, hidden_size=32, intermediate_size=64, num_hidden_layers=36, num_attention_heads=4,
+                                  num_key_value_heads=2, head_dim=8, rms_norm_eps=1e-6, rope_theta=5.0e6, max_position_embeddings=128)
+    hf = transformers.Qwen3Model(hc).eval()
+    mine = Qwen3Encoder(Qwen3Config(80, 32, 64, 36, 4, 2, 8, 1e-6, 5.0e6))
+    raw = {"model.language_model." + k: v for k, v in hf.state_dict().items()}
+    raw["model.visual.patch_embed.weight"] = torch.zeros(2)
+    missing, unexpected = mine.load_state_dict(Q.remap_qwen3vl_text_keys(raw, torch.float32), strict=False)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 80, (1, 40))
+    with torch.no_grad():
+        ref = hf(input_ids=ids, output_hidden_states=True).hidden_states
+    states = mine.layer_states(ids)
+    assert len(states) == 36 and all(torch.allclose(states[i], ref[i + 1], atol=5e-5) for i in (0, 7, 34))
+    k = Q.krea2_text_features(mine, ids)
+    assert k.shape == (1, 6, 12, 32) and torch.allclose(k[0, :, 3], ref[11][0, 34:], atol=5e-5) and torch.allclose(k[0, :, 11], ref[35][0, 34:], atol=5e-5)
+    with pytest.raises(ValueError):
+        Q.krea2_text_features(mine, ids[:, :30])
+    f = Q.ideogram_text_features(mine, ids)
+    assert f.shape == (1, 40, 13 * 32) and torch.allclose(f[0, :, 5 * 13 + 2], ref[7][0, :, 5], atol=5e-5) and torch.allclose(f[0, :, 12], ref[36 - 0][0, :, 0] * 0 + states[35][0, :, 0], atol=5e-5)
+    assert torch.allclose(Q.boogu_text_features(mine, ids), hf(input_ids=ids).last_hidden_state, atol=5e-5)
+    assert Q.qwen3vl_text_config("4b").hidden_size == 2560 and Q.qwen3vl_text_config().intermediate_size == 12288 and Q.qwen3vl_text_config().rope_theta == 5.0e6
+    w8 = torch.randn(4, 8).clamp(-3, 3).to(torch.float8_e4m3fn)
+    m = Q.remap_qwen3vl_text_keys({"language_model.layers.0.self_attn.q_proj.weight": w8,
+                                   "language_model.layers.0.self_attn.q_proj.weight_scale": torch.tensor([1.0, 2.0, 0.5, 4.0]),
+                                   "language_model.norm.weight": torch.ones(3)}, torch.float32)
+    assert set(m) == {"model.layers.0.self_attn.q_proj.weight", "model.norm.weight"}
+    assert torch.equal(m["model.layers.0.self_attn.q_proj.weight"], w8.float() * torch.tensor([1.0, 2.0, 0.5, 4.0])[:, None])
+
+
 def test_tokenizers_on_synthetic_vocab(tmp_path):
     b2u = bytes_to_unicode()
     assert len(b2u) == 256 and len(set(b2u.values())) == 256
