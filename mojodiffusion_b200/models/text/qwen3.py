@@ -27,6 +27,14 @@ class Qwen3Config:
     rope_theta: float = 1_000_000.0
     qk_norm: bool = True                       # per-head RMSNorm of q and k (Qwen3); Mistral-family stacks have none
     rope_scaling: Optional[Tuple[float, int, float, float]] = None   # (factor, original positions, beta_fast, beta_slow)
+    qkv_bias: bool = False                     # biases on the q / k / v projections (the Qwen2 family)
+
+
+def qwen25vl_text_config() -> Qwen3Config:
+    """Language stack of Qwen2.5-VL-7B, Qwen-Image's text encoder: 28 layers, width 3584, 28 query / 4 key-value heads, biased
+    q / k / v projections, no QK norms (serenitymojo/models/text_encoder/qwen25vl_encoder.mojo:10-19)."""
+    return Qwen3Config(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28,
+                       num_key_value_heads=4, head_dim=128, rms_norm_eps=1e-6, rope_theta=1.0e6, qk_norm=False, qkv_bias=True)
 
 
 def mistral3b_config() -> Qwen3Config:
@@ -66,12 +74,13 @@ def pad_or_trim_ids(ids: Sequence[int], max_len: int, pad_id: int = 0):
 
 
 class _W(nn.Module):
-    def __init__(self, i, o, dtype, device):
+    def __init__(self, i, o, dtype, device, bias: bool = False):
         super().__init__()
         self.weight = nn.Parameter(torch.empty(o, i, dtype=dtype, device=device).normal_(0, 0.02))
+        self.bias = nn.Parameter(torch.zeros(o, dtype=dtype, device=device)) if bias else None
 
     def forward(self, x):
-        return ops.linear(x, self.weight)
+        return ops.linear(x, self.weight, self.bias)
 
 
 class _Norm(nn.Module):
@@ -95,9 +104,9 @@ class _Attn(nn.Module):
     def __init__(self, c, dtype, device):
         super().__init__()
         self.c = c
-        self.q_proj = _W(c.hidden_size, c.num_attention_heads * c.head_dim, dtype, device)
-        self.k_proj = _W(c.hidden_size, c.num_key_value_heads * c.head_dim, dtype, device)
-        self.v_proj = _W(c.hidden_size, c.num_key_value_heads * c.head_dim, dtype, device)
+        self.q_proj = _W(c.hidden_size, c.num_attention_heads * c.head_dim, dtype, device, c.qkv_bias)
+        self.k_proj = _W(c.hidden_size, c.num_key_value_heads * c.head_dim, dtype, device, c.qkv_bias)
+        self.v_proj = _W(c.hidden_size, c.num_key_value_heads * c.head_dim, dtype, device, c.qkv_bias)
         self.o_proj = _W(c.num_attention_heads * c.head_dim, c.hidden_size, dtype, device)
         if c.qk_norm:
             self.q_norm, self.k_norm = _Norm(c.head_dim, c.rms_norm_eps, dtype, device), _Norm(c.head_dim, c.rms_norm_eps, dtype, device)

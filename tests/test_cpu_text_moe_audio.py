@@ -110,6 +110,32 @@ def test_mistral_style_encoder_matches_hf_and_scaled_rotary_frequencies():
         assert abs(float(got[i]) - want) < 1e-7 * max(1.0, want)
 
 
+def test_qwen25vl_language_stack_matches_hf_qwen2():
+    """Biased q / k / v projections without QK norms: the Qwen2.5-VL language stack equals transformers' Qwen2Model."""
+    from mojodiffusion_b200.models.text import qwen3 as Q
+    if not hasattr(transformers, "Qwen2Model"):
+        pytest.skip("transformers without Qwen2")
+    torch.manual_seed(2)
+    hc = transformers.Qwen2Config(vocab_size=80, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                                  num_key_value_heads=2, rms_norm_eps=1e-6, rope_theta=1.0e6, max_position_embeddings=64, use_sliding_window=False)
+    hf = transformers.Qwen2Model(hc).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("_proj.bias"):
+                p.normal_(0, 0.1)
+    mine = Qwen3Encoder(Qwen3Config(80, 32, 64, 3, 4, 2, 8, 1e-6, 1.0e6, qk_norm=False, qkv_bias=True))
+    missing, unexpected = mine.load_state_dict(Q.remap_qwen3vl_text_keys({"model.language_model." + k: v for k, v in hf.state_dict().items()}, torch.float32), strict=False)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 80, (2, 11))
+    with torch.no_grad():
+        ref = hf(input_ids=ids, output_hidden_states=True)
+    assert torch.allclose(mine(ids), ref.last_hidden_state, atol=3e-5) and torch.allclose(mine.layer_states(ids)[1], ref.hidden_states[2], atol=3e-5)
+    c = Q.qwen25vl_text_config()
+    assert (c.num_hidden_layers, c.hidden_size, c.num_attention_heads, c.num_key_value_heads, c.intermediate_size) == (28, 3584, 28, 4, 18944)
+    full = Qwen3Encoder(c, torch.float32, "meta").state_dict()
+    assert full["model.layers.0.self_attn.k_proj.bias"].shape == (512,) and "model.layers.0.self_attn.o_proj.bias" not in full and "model.layers.0.self_attn.q_norm.weight" not in full
+
+
 def test_qwen3vl_text_paths_layer_stacks_and_key_mapping():
     """Layer outputs equal transformers' hidden_states; Krea-2 stacks twelve of them and drops the template rows; Ideogram-4
     interleaves thirteen taps per feature; checkpoint prefixes and fp8 rows map onto the encoder's names."""
