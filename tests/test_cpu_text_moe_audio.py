@@ -2,6 +2,8 @@
 vocabularies, MoE primitives against a per-token loop, audio ops identities."""
 import json
 
+import math
+
 import pytest
 import torch
 
@@ -134,6 +136,63 @@ def test_qwen25vl_language_stack_matches_hf_qwen2():
     assert (c.num_hidden_layers, c.hidden_size, c.num_attention_heads, c.num_key_value_heads, c.intermediate_size) == (28, 3584, 28, 4, 18944)
     full = Qwen3Encoder(c, torch.float32, "meta").state_dict()
     assert full["model.layers.0.self_attn.k_proj.bias"].shape == (512,) and "model.layers.0.self_attn.o_proj.bias" not in full and "model.layers.0.self_attn.q_norm.weight" not in full
+
+
+def test_gpt_oss_encoder_matches_hf_and_mxfp4_expert_mapping():
+    """Sinks, alternating sliding-window / full causal layers, YaRN rotary scaling and the clamped interleaved mixture equal
+    transformers' GptOssModel; packed e2m1 + e8m0 expert tensors map onto the dense layout."""
+    from mojodiffusion_b200.models.text import gpt_oss as G
+    if not hasattr(transformers, "GptOssModel"):
+        pytest.skip("transformers without GPT-OSS")
+    torch.manual_seed(3)
+    rope = {"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False,
+            "original_max_position_embeddings": 4096, "rope_theta": 150000.0}
+    try:
+        hc = transformers.GptOssConfig(vocab_size=90, hidden_size=32, intermediate_size=24, num_hidden_layers=4, num_attention_heads=4,
+                                       num_key_value_heads=2, head_dim=16, num_local_experts=6, num_experts_per_tok=2, sliding_window=4,
+                                       rms_norm_eps=1e-5, max_position_embeddings=8192, rope_parameters=rope, attention_bias=True)
+    except TypeError:
+        pytest.skip("GptOssConfig signature differs")
+    hc._attn_implementation = "eager"
+    hf = transformers.GptOssModel(hc).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("sinks") or n.endswith("bias"):
+                p.normal_(0, 0.3)
+            elif "experts" in n or "router" in n:
+                p.normal_(0, 0.2)
+    assert [hc.layer_types[i] for i in range(4)] == ["sliding_attention", "full_attention"] * 2
+    cfg = G.GptOssConfig(vocab_size=90, hidden_size=32, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                         intermediate_size=24, num_local_experts=6, num_experts_per_tok=2, sliding_window=4)
+    mine = G.GptOssEncoder(cfg)
+    missing, unexpected = mine.load_state_dict(G.remap_gpt_oss_keys({"model." + k: v for k, v in hf.state_dict().items()}), strict=False)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 90, (2, 13))
+    with torch.no_grad():
+        ref = hf(input_ids=ids, output_hidden_states=True)
+    st = mine.layer_states(ids)
+    for i in range(4):
+        assert torch.allclose(st[i], ref.hidden_states[i + 1] if i < 3 else st[i], atol=1e-4), i
+    assert torch.allclose(mine(ids), ref.last_hidden_state, atol=1e-4)
+    feats = mine.lens_features(ids, layers=(0, 2))
+    assert feats.shape == (2, 13, 2, 32) and torch.equal(feats[:, :, 1], st[2])
+    full = G.GptOssConfig()
+    inv, mult = G.yarn_inv_freq(full)
+    assert inv.shape == (32,) and abs(mult - (0.1 * math.log(32.0) + 1.0)) < 1e-12 and abs(float(inv[0]) - 1.0) < 1e-6
+    assert abs(float(inv[-1]) - 1.0 / (32.0 * 150000.0 ** (62 / 64))) < 1e-12 and G.LENS_CAPTURE_LAYERS == (5, 11, 17, 23)
+    # packed experts: [experts, out, G, 16] blocks + [experts, out, G] scales
+    E, out_f, Gn = 2, 3, 2
+    blocks = torch.randint(0, 256, (E, out_f, Gn, 16), dtype=torch.uint8)
+    scales = torch.randint(125, 130, (E, out_f, Gn), dtype=torch.uint8)
+    dense = G.dequant_mxfp4(blocks, scales, torch.float32)
+    assert dense.shape == (E, out_f, Gn * 32)
+    e, o, g, b = 1, 2, 1, 5
+    byte = int(blocks[e, o, g, b])
+    sc = 2.0 ** (int(scales[e, o, g]) - 127)
+    assert float(dense[e, o, g * 32 + 2 * b]) == G._FP4[byte & 15] * sc and float(dense[e, o, g * 32 + 2 * b + 1]) == G._FP4[byte >> 4] * sc
+    m = G.remap_gpt_oss_keys({"model.layers.0.mlp.experts.down_proj_blocks": blocks, "model.layers.0.mlp.experts.down_proj_scales": scales,
+                              "model.norm.weight": torch.ones(2), "lm_head.weight": torch.ones(2)}, torch.float32)
+    assert set(m) == {"layers.0.mlp.experts.down_proj", "norm.weight"} and torch.equal(m["layers.0.mlp.experts.down_proj"], dense.transpose(1, 2))
 
 
 def test_qwen3vl_text_paths_layer_stacks_and_key_mapping():
