@@ -158,6 +158,117 @@ def bench_krea2(dev, tiny, steps, warmup):
             "metric": "denoise it/s", "ms_per_step": ms, "value": 1000.0 / ms}
 
 
+def _row(name, m, tokens, ms, what="denoise it/s"):
+    return {"model": name, "params_b": nparams(m) / 1e9, "tokens": tokens, "metric": what, "ms_per_step": ms, "value": 1000.0 / ms}
+
+
+def bench_lens(dev, tiny, steps, warmup):
+    """Lens-shaped 48-block double-stream DiT (width 1536, 24 x 64), 1024^2 (4096 image + 415 text tokens), guidance."""
+    from mojodiffusion_b200.models.lens import LensConfig, LensDiT, tiny_lens_config
+    cfg = tiny_lens_config() if tiny else LensConfig()
+    g, lt = (8, 16) if tiny else (64, 415)
+    m = LensDiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    x = torch.randn(1, g * g, cfg.in_channels, device=dev)
+    xb = x.to(torch.bfloat16)
+    tc, tu = (torch.randn(1, lt, cfg.text_layers, cfg.text_hidden, device=dev, dtype=torch.bfloat16) for _ in range(2))
+    t = torch.full((1,), 0.6, device=dev)
+
+    def step():
+        with torch.no_grad():
+            ops.cfg_euler(x, m(xb, tc, t, (g, g)), m(xb, tu, t, (g, g)), dt=-0.03, s=5.0, mode=1, x_bf16=xb)
+
+    return _row(cfg.name + " guidance 5 (2 forwards/step)", m, g * g + lt, timed(step, steps, warmup))
+
+
+def bench_boogu(dev, tiny, steps, warmup):
+    """Boogu-Image-shaped DiT (width 3360, 28 / 7 heads of 120; 2 + 2 refiner, 8 double, 32 single blocks), 1024^2, guidance."""
+    from mojodiffusion_b200.models.boogu import BooguConfig, BooguDiT, tiny_boogu_config
+    cfg = tiny_boogu_config() if tiny else BooguConfig()
+    side, lt = (16, 16) if tiny else (128, 256)
+    m = BooguDiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    x = torch.randn(1, cfg.in_channels, side, side, device=dev)
+    tc, tu = (torch.randn(1, lt, cfg.instruction_dim, device=dev, dtype=torch.bfloat16) for _ in range(2))
+    t = torch.full((1,), 0.6, device=dev)
+
+    def step():
+        with torch.no_grad():
+            vc, vu = m(x, tc, t), m(x, tu, t)
+            x.add_((vu + 4.0 * (vc - vu)).float(), alpha=-0.03)
+
+    return _row(cfg.name + " guidance 4 (2 forwards/step)", m, (side // 2) ** 2 + lt, timed(step, steps, warmup))
+
+
+def bench_magihuman(dev, tiny, steps, warmup):
+    """MagiHuman-shaped 15 B DiT: 4096 video + 64 audio + 64 text tokens in one stream, one forward per (distilled) step."""
+    import dataclasses
+    from mojodiffusion_b200.models.magihuman import MagiHumanConfig, MagiHumanDiT, tiny_magihuman_config
+    cfg = dataclasses.replace(tiny_magihuman_config(), hidden_size=256, head_dim=64, rope_dim=48, rope_bands=8) if tiny else MagiHumanConfig()
+    f, h, w = (2, 4, 4) if tiny else (4, 32, 32)
+    V, A, T = f * h * w, (8 if tiny else 64), (8 if tiny else 64)
+    m = MagiHumanDiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    coords = torch.cat((torch.stack(torch.meshgrid(torch.arange(float(f)), torch.arange(float(h)), torch.arange(float(w)), indexing="ij"), -1).reshape(V, 3),
+                        torch.stack((torch.arange(A + T).float(), torch.zeros(A + T), torch.zeros(A + T)), 1)), 0)
+    coords = torch.cat((coords, torch.tensor([[float(f), float(h), float(w), float(f), float(h), float(w)]]).expand(V + A + T, 6)), 1).to(dev)
+    xv, xa, xt = (torch.randn(n, d, device=dev, dtype=torch.bfloat16) for n, d in ((V, cfg.video_in), (A, cfg.audio_in), (T, cfg.text_in)))
+
+    def step():
+        m(xv, xa, xt, coords)
+
+    return _row(cfg.name + " (1 forward/step)", m, V + A + T, timed(step, steps, warmup))
+
+
+def bench_sensenova(dev, tiny, steps, warmup):
+    """SenseNova-U1-shaped 8 B (two weight sets) pixel model, 1024^2: 1024 image tokens over a cached 64-token prompt, guidance."""
+    import dataclasses
+    from mojodiffusion_b200.models.sensenova_u1 import SenseNovaU1, SenseNovaU1Config, tiny_sensenova_u1_config
+    cfg = dataclasses.replace(tiny_sensenova_u1_config(), head_dim=64) if tiny else SenseNovaU1Config()
+    side, lt = (32, 8) if tiny else (1024, 64)
+    m = SenseNovaU1(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    ids_c, ids_u = list(range(1, lt + 1)), list(range(1, 9))
+    cc, cu = m.forward_und(ids_c), m.forward_und(ids_u)
+    img = torch.randn(1, 3, side, side, device=dev, dtype=torch.bfloat16)
+
+    def step():
+        m.predict_clean(img, 0.4, cc, len(ids_c))
+        m.predict_clean(img, 0.4, cu, len(ids_u))
+
+    return _row(cfg.name + " guidance (2 image passes/step, prompt cached)", m, (side // (cfg.patch_size * cfg.merge_size)) ** 2 + lt, timed(step, steps, warmup))
+
+
+def bench_nava(dev, tiny, steps, warmup):
+    """NAVA-shaped audio + video DiT (10 double + 20 joint Wan blocks, width 3072), 832 x 480 x 17 frames: 1950 video + 34 audio tokens."""
+    from mojodiffusion_b200.models.nava import NavaConfig, NavaDiT, tiny_nava_config
+    cfg = tiny_nava_config() if tiny else NavaConfig()
+    F_, Hh, Ww, Na, Lt = (2, 8, 8, 6, 8) if tiny else (5, 30, 52, 34, 64)
+    m = NavaDiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    v, a = torch.randn(1, cfg.in_dim, F_, Hh, Ww, device=dev), torch.randn(1, Na, cfg.audio_dim, device=dev)
+    tc, tu = (torch.randn(1, Lt, cfg.text_dim, device=dev, dtype=torch.bfloat16) for _ in range(2))
+    t = torch.full((1,), 0.5, device=dev)
+
+    def step():
+        m(v, a, tc, t)
+        m(v, a, tu, t)
+
+    return _row(cfg.name + " guidance (2 forwards/step)", m, F_ * (Hh // 2) * (Ww // 2) + Na, timed(step, steps, warmup))
+
+
+def bench_pid(dev, tiny, steps, warmup):
+    """PiD super-resolution decoder at 1024^2 output (4096 patches, 64-token caption), one forward per distilled step."""
+    from mojodiffusion_b200.models.pid import PidConfig, PidNet, tiny_pid_config
+    cfg = tiny_pid_config() if tiny else PidConfig()
+    side, lt = (32, 8) if tiny else (1024, 64)
+    m = PidNet(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    x = torch.randn(1, 3, side, side, device=dev)
+    cap = torch.randn(1, lt, cfg.txt_dim, device=dev, dtype=torch.bfloat16)
+    lat = torch.randn(1, cfg.lq_channels, side // 32, side // 32, device=dev)
+    t = torch.full((1,), 0.7, device=dev)
+
+    def step():
+        m(x, t, cap, lat, 0.0)
+
+    return _row(cfg.name + " (1 forward/step)", m, (side // cfg.patch_size) ** 2 + lt, timed(step, steps, warmup))
+
+
 def bench_klein(dev, tiny, steps, warmup, train):
     """FLUX.2 Klein-9B-shaped MMDiT: 1024^2 denoise (4096 + 512 tokens), or the reference's headline training case:
     LoRA r16 on every block projection, 512^2 (1024 image + 512 text tokens = 1536), batch 1, gradient checkpointing."""
@@ -325,6 +436,12 @@ def main():
         "ltx2_vae": lambda: bench_ltx2_vae(dev, args.tiny, args.steps, args.warmup),
         "sdxl_train": lambda: bench_sdxl_train(dev, args.tiny, args.steps, args.warmup),
         "krea2": lambda: bench_krea2(dev, args.tiny, args.steps, args.warmup),
+        "lens": lambda: bench_lens(dev, args.tiny, args.steps, args.warmup),
+        "boogu": lambda: bench_boogu(dev, args.tiny, args.steps, args.warmup),
+        "magihuman": lambda: bench_magihuman(dev, args.tiny, args.steps, args.warmup),
+        "sensenova": lambda: bench_sensenova(dev, args.tiny, args.steps, args.warmup),
+        "nava": lambda: bench_nava(dev, args.tiny, args.steps, args.warmup),
+        "pid": lambda: bench_pid(dev, args.tiny, args.steps, args.warmup),
     }
     rows = []
     for name in args.only.split(","):

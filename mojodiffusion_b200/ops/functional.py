@@ -545,7 +545,7 @@ def norm_modulate(x, weight=None, bias=None, scale=None, shift=None, rows_per_gr
         rows_per_group = x.shape[-2] if x.dim() >= 3 else x.shape[0]
     sc = scale.reshape(-1, D) if scale is not None else None
     sh = shift.reshape(-1, D) if shift is not None else None
-    if not native.use_native(x):
+    if not native.use_native(x) or D % 8 or D > 16384:      # the kernel covers rows of 8 .. 16384 elements in steps of 8
         return ref.norm_modulate(x.reshape(-1, D), weight, bias, sc, sh, rows_per_group, eps, rms).reshape(x.shape)
     x2 = _flat2d(x)
     if sc is not None and sh is not None and sc.stride(0) != sh.stride(0):

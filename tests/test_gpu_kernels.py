@@ -345,6 +345,16 @@ def test_norm_modulate(rows, D, rms):
     _check(xg.grad, xr.grad, cos=0.995, rel=5e-2, name="norm dx")
 
 
+@pytest.mark.parametrize("D", [4, 20, 53248])
+def test_norm_modulate_widths_outside_the_kernel_use_the_torch_statement(D):
+    """Rows that are not a multiple of 8 wide, or wider than 16 384 (Ideogram-4's stacked text features), still normalise."""
+    x = _rand(6, D, seed=60, scale=2.0)
+    w = _rand(D, seed=61)
+    out = O.norm_modulate(x, w, eps=1e-6, rms=True)
+    native.check_status()
+    _check(out, ref.norm_modulate(x.float(), w.float(), None, None, None, 6, 1e-6, True), name="norm fallback")
+
+
 @pytest.mark.parametrize("Dh", [64, 128, 256])
 @pytest.mark.parametrize("interleaved", [True, False])
 def test_qk_norm_rope(Dh, interleaved):
