@@ -180,6 +180,31 @@ def bench_lens(dev, tiny, steps, warmup):
     return _row(cfg.name + " guidance 5 (2 forwards/step)", m, g * g + lt, timed(step, steps, warmup))
 
 
+def bench_ideogram4(dev, tiny, steps, warmup):
+    """Ideogram-4-shaped 34-block single-stream DiT (width 4608, 18 heads of 256: attention on the library kernel), 1024^2:
+    4096 image + 512 text positions in one sequence, one forward per step."""
+    from mojodiffusion_b200.models.ideogram4 import IND_IMAGE, IND_TEXT, Ideogram4Config, Ideogram4DiT, tiny_ideogram4_config
+    cfg = tiny_ideogram4_config() if tiny else Ideogram4Config()
+    g, lt = (8, 16) if tiny else (64, 512)
+    L = lt + g * g
+    m = Ideogram4DiT(cfg, torch.bfloat16, dev).init_weights(0).eval()
+    x = torch.randn(1, L, cfg.in_channels, device=dev, dtype=torch.bfloat16)
+    llm = torch.randn(1, L, cfg.llm_dim, device=dev, dtype=torch.bfloat16)
+    ind = torch.tensor([[IND_TEXT] * lt + [IND_IMAGE] * (g * g)], device=dev)
+    pos = torch.zeros(L, 3)
+    pos[:lt, 0] = torch.arange(lt).float()
+    pos[lt:, 1] = torch.arange(g).float().repeat_interleave(g)
+    pos[lt:, 2] = torch.arange(g).float().repeat(g)
+    pos = pos.to(dev)
+    t = torch.full((1,), 0.6, device=dev)
+
+    def step():
+        with torch.no_grad():
+            m(x, llm, t, ind, pos)
+
+    return _row(cfg.name + " (1 forward/step)", m, L, timed(step, steps, warmup))
+
+
 def bench_boogu(dev, tiny, steps, warmup):
     """Boogu-Image-shaped DiT (width 3360, 28 / 7 heads of 120; 2 + 2 refiner, 8 double, 32 single blocks), 1024^2, guidance."""
     from mojodiffusion_b200.models.boogu import BooguConfig, BooguDiT, tiny_boogu_config
@@ -438,6 +463,7 @@ def main():
         "krea2": lambda: bench_krea2(dev, args.tiny, args.steps, args.warmup),
         "lens": lambda: bench_lens(dev, args.tiny, args.steps, args.warmup),
         "boogu": lambda: bench_boogu(dev, args.tiny, args.steps, args.warmup),
+        "ideogram4": lambda: bench_ideogram4(dev, args.tiny, args.steps, args.warmup),
         "magihuman": lambda: bench_magihuman(dev, args.tiny, args.steps, args.warmup),
         "sensenova": lambda: bench_sensenova(dev, args.tiny, args.steps, args.warmup),
         "nava": lambda: bench_nava(dev, args.tiny, args.steps, args.warmup),

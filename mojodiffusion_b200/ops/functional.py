@@ -362,7 +362,7 @@ def qkv_attention(qkv: torch.Tensor, H: int, Dh: int, wq, wk, cos, sin, split: i
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(Dh)
     wq_first = wq if wq_first is None else wq_first
     wk_first = wk if wk_first is None else wk_first
-    if native.use_native(qkv) and torch.is_grad_enabled() and qkv.requires_grad:
+    if native.use_native(qkv) and torch.is_grad_enabled() and qkv.requires_grad and Dh in (64, 128):
         return _QKVAttentionFn.apply(qkv, wq_first, wk_first, wq, wk, cos, sin, H, Dh, split, interleaved, scale, eps)
     if split > 0:
         a = qk_norm_rope(qkv[:, :split], H, Dh, wq_first, wk_first, cos, sin, eps, interleaved, pos_offset=0)
@@ -474,7 +474,7 @@ def attention(q, k, v, scale: Optional[float] = None, kv_len: Optional[torch.Ten
     """
     Dh = q.shape[-1]
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(Dh)
-    if not native.use_native(q):
+    if not native.use_native(q) or Dh not in (64, 128):     # other head widths (120, 256, ...): the torch statement / library kernel
         o = ref.attention(q, k, v, scale, kv_len)
         if out is not None:
             out.copy_(o)

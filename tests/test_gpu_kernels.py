@@ -345,6 +345,18 @@ def test_norm_modulate(rows, D, rms):
     _check(xg.grad, xr.grad, cos=0.995, rel=5e-2, name="norm dx")
 
 
+@pytest.mark.parametrize("Dh", [120, 256])
+def test_attention_head_widths_outside_the_kernel_use_the_library(Dh):
+    """Head widths other than 64 / 128 (Boogu-Image 120, Ideogram-4 256) run instead of failing, with and without a key length."""
+    q, k, v = (_rand(2, 70, 3, Dh, seed=70 + i) for i in range(3))
+    want = ref.attention(q.float().cpu(), k.float().cpu(), v.float().cpu())
+    _check(O.attention(q, k, v), want.to(q.device), cos=0.999, rel=3e-2, name="attention fallback")
+    kv_len = torch.tensor([70, 33], dtype=torch.int32, device=q.device)
+    want = ref.attention(q.float().cpu(), k.float().cpu(), v.float().cpu(), None, kv_len.cpu())
+    _check(O.attention(q, k, v, kv_len=kv_len), want.to(q.device), cos=0.999, rel=3e-2, name="attention fallback masked")
+    native.check_status()
+
+
 @pytest.mark.parametrize("D", [4, 20, 53248])
 def test_norm_modulate_widths_outside_the_kernel_use_the_torch_statement(D):
     """Rows that are not a multiple of 8 wide, or wider than 16 384 (Ideogram-4's stacked text features), still normalise."""
