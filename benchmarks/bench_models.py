@@ -205,6 +205,77 @@ def bench_ideogram4(dev, tiny, steps, warmup):
     return _row(cfg.name + " (1 forward/step)", m, L, timed(step, steps, warmup))
 
 
+def bench_more(dev, tiny, steps, warmup, which):
+    """One forward per step of a family that has no packed fast path, at its real size (``which``: hunyuan15, kandinsky5, cosmos,
+    wan_vace, nucleus, acestep, hidream_o1). Video grids hold 6144 tokens, image grids 4096."""
+    bf = torch.bfloat16
+    rn = lambda *sh, dtype=bf: torch.randn(*sh, device=dev, dtype=dtype)
+    t = torch.full((1,), 0.6, device=dev)
+    if which == "hunyuan15":
+        from mojodiffusion_b200.models.hunyuan15 import Hunyuan15Config, Hunyuan15DiT, tiny_hunyuan15_config
+        cfg = tiny_hunyuan15_config() if tiny else Hunyuan15Config()
+        m = Hunyuan15DiT(cfg, bf, dev).init_weights(0).eval()
+        f, h, w = (2, 4, 8) if tiny else (4, 32, 48)
+        args, tokens = (rn(1, cfg.in_channels, f, h, w), rn(1, 16 if tiny else 256, cfg.hidden), t), f * h * w
+    elif which == "kandinsky5":
+        from mojodiffusion_b200.models.kandinsky5 import Kandinsky5Config, Kandinsky5DiT, tiny_kandinsky5_config
+        cfg = tiny_kandinsky5_config() if tiny else Kandinsky5Config()
+        m = Kandinsky5DiT(cfg, bf, dev).init_weights(0).eval()
+        f, h, w = (2, 8, 8) if tiny else (4, 64, 96)
+        args, tokens = (rn(1, cfg.in_visual_dim, f, h, w), rn(1, 16 if tiny else 256, cfg.in_text_dim), rn(1, cfg.in_text_dim2),
+                        torch.full((1,), 417.0, device=dev)), f * (h // 2) * (w // 2)
+    elif which == "cosmos":
+        from mojodiffusion_b200.models.cosmos import CosmosConfig, CosmosDiT, tiny_cosmos_config
+        cfg = tiny_cosmos_config() if tiny else CosmosConfig()
+        m = CosmosDiT(cfg, bf, dev).init_weights(0).eval()
+        f, h, w = (2, 8, 8) if tiny else (4, 64, 96)
+        args, tokens = (rn(1, cfg.in_channels, f, h, w), rn(1, 16 if tiny else 512, cfg.text_in_dim), t), f * (h // 2) * (w // 2)
+    elif which == "wan_vace":
+        from mojodiffusion_b200.models.wan import WanVaceDiT, tiny_wan_vace_config, wan21_vace_14b_config
+        cfg = tiny_wan_vace_config() if tiny else wan21_vace_14b_config()
+        m = WanVaceDiT(cfg, bf, dev).init_weights(0).eval()
+        f, h, w = (2, 8, 8) if tiny else (4, 64, 96)
+        ctl = rn(1, cfg.vace_in_dim, f, h, w)
+        args, tokens = (rn(1, cfg.in_dim, f, h, w), rn(1, 16 if tiny else 512, cfg.text_dim), t), f * (h // 2) * (w // 2)
+        fwd = lambda: m(*args, control=ctl)
+    elif which == "nucleus":
+        from mojodiffusion_b200.models.nucleus import NucleusConfig, NucleusDiT, tiny_nucleus_config
+        cfg = tiny_nucleus_config() if tiny else NucleusConfig()
+        m = NucleusDiT(cfg, bf, dev).init_weights(0).eval()
+        g = 8 if tiny else 64
+        args, tokens = (rn(1, g * g, cfg.in_channels), rn(1, 16 if tiny else 256, cfg.joint_dim), t), g * g
+        fwd = lambda: m(*args, grid=(1, g, g))
+    elif which == "acestep":
+        import dataclasses
+        from mojodiffusion_b200.models.acestep import AceStepConfig, AceStepDiT, tiny_acestep_config
+        cfg = dataclasses.replace(tiny_acestep_config(), hidden=256, head_dim=64) if tiny else AceStepConfig()
+        m = AceStepDiT(cfg, bf, dev).init_weights(0).eval()
+        T = 32 if tiny else 3000                                                  # 2 minutes of audio at 25 latent frames / s
+        args, tokens = (rn(1, T, cfg.acoustic_dim), rn(1, T, cfg.in_channels - cfg.acoustic_dim), rn(1, 8 if tiny else 256, cfg.hidden), t,
+                        torch.full((1,), 0.2, device=dev)), T // cfg.patch
+    else:
+        import dataclasses
+        from mojodiffusion_b200.models.hidream_o1 import HiDreamO1, HiDreamO1Config, build_mrope_positions, tiny_hidream_o1_config
+        cfg = tiny_hidream_o1_config() if tiny else HiDreamO1Config()
+        if tiny:
+            cfg = dataclasses.replace(cfg, spine=dataclasses.replace(cfg.spine, hidden_size=256, head_dim=64))
+        m = HiDreamO1(cfg, bf, dev).init_weights(0).eval()
+        g, lt = (4, 5) if tiny else (32, 64)
+        ids = [1] * (lt - 2) + [cfg.tms_token_id, cfg.vision_start_token_id]
+        pos = build_mrope_positions(ids + [cfg.image_token_id] * (g * g), cfg.image_token_id, g, g, lt + 8)
+        patches = rn(1, g * g, cfg.patch_dim)
+        tokens = g * g + lt
+        fwd = lambda: m(ids, patches, pos, lt, 0.4)
+    if which not in ("wan_vace", "nucleus", "hidream_o1"):
+        fwd = lambda: m(*args)
+
+    def step():
+        with torch.no_grad():
+            fwd()
+
+    return _row(getattr(cfg, "name", which) + " (1 forward/step)", m, tokens, timed(step, steps, warmup))
+
+
 def bench_boogu(dev, tiny, steps, warmup):
     """Boogu-Image-shaped DiT (width 3360, 28 / 7 heads of 120; 2 + 2 refiner, 8 double, 32 single blocks), 1024^2, guidance."""
     from mojodiffusion_b200.models.boogu import BooguConfig, BooguDiT, tiny_boogu_config
@@ -463,6 +534,8 @@ def main():
         "krea2": lambda: bench_krea2(dev, args.tiny, args.steps, args.warmup),
         "lens": lambda: bench_lens(dev, args.tiny, args.steps, args.warmup),
         "boogu": lambda: bench_boogu(dev, args.tiny, args.steps, args.warmup),
+        **{k: (lambda k=k: bench_more(dev, args.tiny, args.steps, args.warmup, k))
+           for k in ("hunyuan15", "kandinsky5", "cosmos", "wan_vace", "nucleus", "acestep", "hidream_o1")},
         "ideogram4": lambda: bench_ideogram4(dev, args.tiny, args.steps, args.warmup),
         "magihuman": lambda: bench_magihuman(dev, args.tiny, args.steps, args.warmup),
         "sensenova": lambda: bench_sensenova(dev, args.tiny, args.steps, args.warmup),
