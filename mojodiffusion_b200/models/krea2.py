@@ -64,6 +64,11 @@ class Krea2Config:
     def patch_dim(self) -> int:
         return self.channels * self.patch * self.patch
 
+    @property
+    def in_channels(self) -> int:
+        """Width of one packed image token (the name the shared sampler and adapters read)."""
+        return self.patch_dim
+
 
 def tiny_krea2_config() -> Krea2Config:
     return Krea2Config(features=128, tdim=32, txtdim=64, heads=4, kvheads=2, multiplier=2, layers=2, channels=4, txtheads=2,

@@ -77,6 +77,14 @@ class FamilyAdapter:
             cond.pooled = pooled.to(text.device, text.dtype)
         return cond
 
+    def text_dim(self, model_cfg) -> int:
+        """Width of the text features one token carries in a cache file or a hash embedding."""
+        if self.family == "lens":
+            return model_cfg.text_layers * model_cfg.text_hidden
+        if self.family == "krea2":
+            return model_cfg.txtlayers * model_cfg.txtdim
+        return getattr(model_cfg, "context_dim", None) or getattr(model_cfg, "cap_dim", None) or self.m.text.dim
+
     def pooled_dim(self, model_cfg) -> int:
         if self.family == "flux":
             return model_cfg.vec_dim
@@ -114,6 +122,14 @@ class FamilyAdapter:
             return model(x, c.txt, sigma, c.hw, c.txt_len)
         if f == "anima":
             return model(x, c.txt, sigma, c.txt_len)
+        if f == "lens":           # text features arrive as the concatenation of the captured encoder layers
+            mc = model.cfg
+            return model(x, c.txt.unflatten(-1, (mc.text_layers, mc.text_hidden)), sigma, c.hw, c.txt_len)
+        if f == "krea2":          # twelve stacked encoder layers per token; text rows sit at position 0, image rows at (0, r, c)
+            from ..models.krea2 import krea2_positions
+            mc = model.cfg
+            ctx = c.txt.unflatten(-1, (mc.txtlayers, mc.txtdim))
+            return model(x, ctx, sigma, krea2_positions(ctx.shape[1], c.hw[0], c.hw[1], x.device))
         raise NotImplementedError(f"no adapter for family '{f}'")
 
     # ---- adapters --------------------------------------------------------------------------------------------------
@@ -149,4 +165,10 @@ def schedule_for(m: ModelManifest, steps: int, image_tokens: int, shift: float =
         return fm.ltx2_linear_quadratic_sigmas(steps)
     if k == "shifted":
         return fm.shifted_sigmas(steps, shift or m.schedule.shift)
+    if k == "lens_exp_shift":
+        from ..sampling.family_schedules import lens_sigmas
+        return list(lens_sigmas(steps, image_tokens)) + [0.0]
+    if k == "krea2_exp_shift":
+        from ..sampling.family_schedules import krea2_timesteps
+        return krea2_timesteps(image_tokens, steps)
     raise ValueError(f"{m.model_id}: schedule kind '{k}' has no sigma table (DDPM families use sampling.ddpm)")

@@ -25,7 +25,7 @@ from ..io.png import encode_png, tensor_to_uint8
 from ..io.safetensors_io import load_safetensors
 from ..runtime.adapters import Cond, adapter_for, schedule_for
 from ..runtime.manifest import ModelManifest, ProductionGuard, ShapeProfile
-from ..sampling.guidance import cfg_textbook, cfg_true_with_norm_rescale
+from ..sampling.guidance import cfg_cond_anchored, cfg_textbook, cfg_true_with_norm_rescale
 
 
 def _hash_text(prompt: str, tokens: int, dim: int, pooled: int):
@@ -49,7 +49,7 @@ class ValidationSampler:
     def _text(self, sp: SamplePrompt, negative: bool):
         cfg = self.model.cfg
         T = 32 if self.tiny else self.m.text.tokens
-        D = getattr(cfg, "context_dim", None) or getattr(cfg, "cap_dim", None) or self.m.text.dim
+        D = self.a.text_dim(cfg)
         P = self.a.pooled_dim(cfg)
         path = sp.caps_negative if negative else sp.caps_positive
         prompt = sp.negative if negative else sp.prompt
@@ -153,7 +153,9 @@ class ValidationSampler:
                     v = self.a.predict(self.model, xb, t, cond).float()
                     if cond_u is not None:
                         vu = self.a.predict(self.model, xb, t, cond_u).float()
-                        v = cfg_true_with_norm_rescale(v, vu, sp.cfg) if m.schedule.cfg_rule == "true_norm_rescale" else cfg_textbook(v, vu, sp.cfg)
+                        rule = m.schedule.cfg_rule
+                        v = (cfg_true_with_norm_rescale(v, vu, sp.cfg) if rule == "true_norm_rescale" else
+                             cfg_cond_anchored(v, vu, sp.cfg) if rule == "cond_anchored" else cfg_textbook(v, vu, sp.cfg))
                     last = m.family == "ltx2" and i == sp.steps - 1
                     x = x + ((0.0 - s) if last else (s_next - s)) * v
         finally:

@@ -191,3 +191,29 @@ def test_preset_catalogue_and_contracts(tmp_path):
     assert p["step_file"].endswith("out/my_lora_step500.safetensors")
     rep = dry_run_report(cfg, "ernie_lora_8gb")
     assert not rep["ok"] and any("no runnable loop" in x for x in rep["problems"]) and any("cache" in x for x in rep["problems"])
+
+
+@pytest.mark.parametrize("family", ["lens", "krea2"])
+def test_sample_cli_drives_lens_and_krea2_through_their_own_schedules(tmp_path, family):
+    """The sampler entry point runs the two families whose text features are stacks of encoder layers: tiny architecture,
+    hash text features of the stacked width, the family's exponential-shift time table and guidance rule, PNG out."""
+    from mojodiffusion_b200.runtime.adapters import adapter_for, schedule_for
+    from mojodiffusion_b200.sampling.family_schedules import krea2_timesteps, lens_sigmas
+    tmp = str(tmp_path)
+    cfg_path, ws, prompts = _write_cfg(tmp, family)
+    out = os.path.join(tmp, "img", "p1.png")
+    rep = _run("mojodiffusion_b200.cli.sample", family, cfg_path, "-", prompts, "p1", out, "--tiny")
+    assert rep["family"] == family and rep["weights"] == "random-init" and rep["text"] == "hash-embedding" and rep["lora"] == "none"
+    img, meta = load_png(out)
+    assert img.shape[:2] == (64, 64) and img.std() > 0
+    gen = json.loads(meta["serenity.genparams.v1"])
+    assert gen["steps"] == 2 and gen["cfg"] == 2.0 and gen["prompt"] == "a red bicycle"
+    m = default_manifest_by_id(family)
+    a = adapter_for(m)
+    tiny = m.config(tiny=True)
+    if family == "lens":
+        assert a.text_dim(tiny) == tiny.text_layers * tiny.text_hidden and m.schedule.cfg_rule == "textbook"
+        assert schedule_for(m, 5, 4096) == list(lens_sigmas(5, 4096)) + [0.0]
+    else:
+        assert a.text_dim(tiny) == tiny.txtlayers * tiny.txtdim and m.schedule.cfg_rule == "cond_anchored"
+        assert schedule_for(m, 5, 4096) == krea2_timesteps(4096, 5)
