@@ -259,9 +259,10 @@ register(ModelManifest(
 register(ModelManifest(
     "krea-2", "krea2", _M + "krea2", "Krea2DiT", "Krea2Config", "tiny_krea2_config",
     LatentSpec(16, 8, 2, True), TextSpec(512, 2560, 0, ("qwen3_vl_4b_12_layers",)),
-    ScheduleSpec("krea2_exp_shift", 20, 4.5, cfg_rule="cond_anchored"), None, "qwen_image_vae_config", "", 13.0, ((1024, 1024),),
-    blocked="sampling through cli.sample and the validation sampler is wired (text features: twelve stacked encoder layers per token, "
-            "flattened); no serving backend or trainer adapter",
+    ScheduleSpec("krea2_exp_shift", 20, 4.5, cfg_rule="cond_anchored"), LoraSpec("inject_krea2_lora", "peft"), "qwen_image_vae_config", "", 13.0,
+    ((1024, 1024),),
+    blocked="cli.sample, cli.train (LoRA on the single-stream blocks) and the validation sampler are wired (text features: twelve "
+            "stacked encoder layers per token, flattened); no serving backend",
     notes="`models.krea2.krea2_sample` is the stand-alone sampling loop"),
     "krea2")
 register(ModelManifest(
@@ -273,9 +274,9 @@ register(ModelManifest(
 register(ModelManifest(
     "lens", "lens", _M + "lens", "LensDiT", "LensConfig", "tiny_lens_config",
     LatentSpec(32, 8, 2, True), TextSpec(415, 11520, 0, ("gpt_oss_layers_5_11_17_23",)),
-    ScheduleSpec("lens_exp_shift", 20, 5.0), None, "flux2_vae_config", "", 3.1, ((1024, 1024),),
-    blocked="sampling through cli.sample and the validation sampler is wired (text features: four encoder layers concatenated); "
-            "no serving backend or trainer adapter",
+    ScheduleSpec("lens_exp_shift", 20, 5.0), LoraSpec("inject_lens_lora", "peft"), "flux2_vae_config", "", 3.1, ((1024, 1024),),
+    blocked="cli.sample, cli.train (LoRA on both streams' projections) and the validation sampler are wired (text features: four "
+            "encoder layers concatenated); no serving backend",
     notes="each of the four text layers is normalised by its own weight inside the model"),
     "microsoft-lens")
 register(ModelManifest(

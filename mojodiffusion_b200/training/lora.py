@@ -201,6 +201,30 @@ def inject_anima_lora(model, rank: int = 16, alpha: float = 16.0, seed: int = 0)
     return _finish(model, [mods[n].add_lora("diffusion_model." + n, rank, alpha, None, seed) for n in anima_lora_targets(len(model.net.blocks))])
 
 
+KREA2_BLOCK = ("attn.wq", "attn.wk", "attn.wv", "attn.gate", "attn.wo", "mlp.gate", "mlp.up", "mlp.down")
+LENS_BLOCK = ("attn.img_qkv", "attn.txt_qkv", "attn.to_out.0", "attn.to_add_out", "img_mlp.w1", "img_mlp.w2", "img_mlp.w3",
+              "txt_mlp.w1", "txt_mlp.w2", "txt_mlp.w3")
+
+
+def inject_krea2_lora(model, rank: int = 16, alpha: float = 16.0, seed: int = 0) -> List[LoRASlot]:
+    """Krea-2 adapters: eight per single-stream block (the five attention projections and the three feed-forward ones); the
+    embedders, the text fusion and the last layer stay frozen (serenitymojo/models/krea2/krea2_stack.mojo:12-18,124)."""
+    _freeze(model)
+    mods = dict(model.named_modules())
+    slots = [mods[f"blocks.{i}.{n}"].add_lora(f"blocks.{i}.{n}", rank, alpha, None, seed)
+             for i in range(len(model.blocks)) for n in KREA2_BLOCK]
+    return _finish(model, slots)
+
+
+def inject_lens_lora(model, rank: int = 16, alpha: float = 16.0, seed: int = 0) -> List[LoRASlot]:
+    """Lens adapters on the attention and feed-forward projections of both streams of every block."""
+    _freeze(model)
+    mods = dict(model.named_modules())
+    slots = [mods[f"transformer_blocks.{i}.{n}"].add_lora(f"transformer_blocks.{i}.{n}", rank, alpha, None, seed)
+             for i in range(len(model.transformer_blocks)) for n in LENS_BLOCK]
+    return _finish(model, slots)
+
+
 def inject_lora_by_name(model: nn.Module, name_to_key: Dict[str, str], rank: int, alpha: float) -> List[LoRASlot]:
     """Generic injection: ``name_to_key`` maps a module path of a :class:`Linear` to its checkpoint prefix."""
     for p in model.parameters():

@@ -35,8 +35,8 @@ def _tiny_dims(family):
     if family == "sdxl":
         return 4, cfg.context_dim, 8, cfg.adm_in_channels
     C = cfg.in_channels // (m.latent.patch ** 2) if m.latent.packed else cfg.in_channels
-    D = getattr(cfg, "context_dim", None) or getattr(cfg, "cap_dim")
-    return C, D, 16, 0
+    from mojodiffusion_b200.runtime.adapters import adapter_for
+    return C, adapter_for(m).text_dim(cfg), 16, 0
 
 
 def _make_cache(d, family, n=4, hw=8):
@@ -64,12 +64,13 @@ def _write_cfg(tmp, family, **over):
     return path, ws, prompts
 
 
-KEY_PREFIX = {"flux": "lora_transformer_", "klein": "transformer.", "zimage": "layers.", "qwenimage": "transformer.", "sdxl": "lora_unet_"}
+KEY_PREFIX = {"flux": "lora_transformer_", "klein": "transformer.", "zimage": "layers.", "qwenimage": "transformer.", "sdxl": "lora_unet_",
+              "lens": "transformer_blocks.", "krea2": "blocks."}
 KEY_SUFFIX = {"flux": ".lora_down.weight", "klein": ".lora_A.weight", "zimage": ".lora_A.weight", "qwenimage": ".lora_down.weight",
-              "sdxl": ".lora_down.weight"}
+              "sdxl": ".lora_down.weight", "lens": ".lora_A.weight", "krea2": ".lora_A.weight"}
 
 
-@pytest.mark.parametrize("family", ["flux", "klein", "zimage", "qwenimage", "sdxl"])
+@pytest.mark.parametrize("family", ["flux", "klein", "zimage", "qwenimage", "sdxl", "lens", "krea2"])
 def test_train_then_resume_then_sample(tmp_path, family):
     tmp = str(tmp_path)
     _make_cache(os.path.join(tmp, "cache"), family)
