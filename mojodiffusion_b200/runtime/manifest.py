@@ -268,8 +268,9 @@ register(ModelManifest(
 register(ModelManifest(
     "zimage-l2p", "zimage_l2p", _M + "zimage_l2p", "ZImageL2P", "zimage_l2p_config", "tiny_zimage_l2p_config",
     LatentSpec(3, 1, 16, False), TextSpec(512, 2560, 0, ("qwen3",)),
-    ScheduleSpec("shifted", 30, 2.0, shift=3.0), None, "", "", 6.2, ((1024, 1024),), blocked=_NO_PIPELINE,
-    notes="pixel space, no VAE; `models.zimage_l2p.l2p_sample` is the sampling loop"),
+    ScheduleSpec("shifted", 30, 2.0, shift=3.0), None, "", "", 6.2, ((1024, 1024),),
+    blocked="cli.sample and the validation sampler run the model's own pixel-space loop (no VAE); no serving backend or trainer adapter",
+    notes="`models.zimage_l2p.l2p_sample` is the sampling loop"),
     "l2p")
 register(ModelManifest(
     "lens", "lens", _M + "lens", "LensDiT", "LensConfig", "tiny_lens_config",
@@ -294,8 +295,9 @@ register(ModelManifest(
 register(ModelManifest(
     "sensenova-u1-8b", "sensenova_u1", _M + "sensenova_u1", "SenseNovaU1", "SenseNovaU1Config", "tiny_sensenova_u1_config",
     LatentSpec(3, 1, 32, True), TextSpec(512, 4096, 0, ()),
-    ScheduleSpec("shifted", 30, 4.0, shift=3.0), None, "", "", 17.0, ((1024, 1024),), blocked=_NO_PIPELINE,
-    notes="pixel space; the prompt's token ids run through the base weights once (key / value cache), image tokens through the _mot_gen weights; `SenseNovaU1.sample` is the loop"),
+    ScheduleSpec("shifted", 30, 4.0, shift=3.0), None, "", "", 17.0, ((1024, 1024),),
+    blocked="cli.sample and the validation sampler run the model's own pixel-space loop (no VAE, token ids in); no serving backend or trainer adapter",
+    notes="the prompt's token ids run through the base weights once (key / value cache), image tokens through the _mot_gen weights; `SenseNovaU1.sample` is the loop"),
     "sensenova-u1", "sensenova")
 register(ModelManifest(
     "boogu-image-0.1", "boogu", _M + "boogu", "BooguDiT", "BooguConfig", "tiny_boogu_config",

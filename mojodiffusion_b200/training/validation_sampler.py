@@ -16,6 +16,7 @@ import dataclasses
 import json
 import os
 import time
+import zlib
 from typing import Callable, List, Optional
 
 import torch
@@ -190,7 +191,53 @@ class ValidationSampler:
                 torch.cuda.empty_cache()
         return out_png
 
+    # ---- pixel-space families (no VAE): the model's own sampling loop gives the image ------------------------------------
+    PIXEL_FAMILIES = ("zimage_l2p", "sensenova_u1")
+
+    @torch.no_grad()
+    def _pixel_image(self, sp: SamplePrompt) -> tuple:
+        """-> (image [1, 3, H, W] in [-1, 1], text kind)."""
+        dev, dt, fam = self.device, self.dtype, self.m.family
+        seed = int(sp.seed) & 0x7FFFFFFFFFFFFFFF
+        noise = torch.randn(1, 3, sp.height, sp.width, generator=torch.Generator().manual_seed(seed)).to(dev)
+        if fam == "zimage_l2p":
+            from ..models.zimage_l2p import l2p_sample
+            txt, _, kind = self._text(sp, False)
+            un = self._text(sp, True)[0].to(dev, dt) if sp.cfg > 1.0 else None
+            img = l2p_sample(self.model, txt.to(dev, dt), un, sp.height, sp.width, steps=sp.steps, cfg_scale=sp.cfg,
+                             shift=self.m.schedule.shift, x=noise)
+            return img.float().clamp(-1, 1), kind
+        # SenseNova-U1: the prompt is token ids (the model embeds them itself); without a tokenizer the ids are a hash of the words
+        vocab = self.model.cfg.vocab_size
+        ids = lambda s: [1 + (zlib.crc32(w.encode()) % (vocab - 1)) for w in (s.split() or ["<empty>"])][:self.m.text.tokens]
+        img = self.model.sample(ids(sp.prompt), ids(sp.negative or ""), sp.height, sp.width, steps=sp.steps, cfg_scale=max(sp.cfg, 1.0),
+                                shift=self.m.schedule.shift, noise=noise)
+        return (img.float() * 2.0 - 1.0).clamp(-1, 1), "hash-token-ids"
+
+    def _sample_pixels(self, sp: SamplePrompt, out_png: str, gen: dict) -> str:
+        t0 = time.perf_counter()
+        was_training = self.model.training
+        self.model.eval()
+        try:
+            img, kind = self._pixel_image(sp)
+        finally:
+            self.model.train(was_training)
+        os.makedirs(os.path.dirname(out_png) or ".", exist_ok=True)
+        arr = tensor_to_uint8(img[0].permute(1, 2, 0).cpu()).numpy()
+        tmp = out_png + ".tmp"
+        with open(tmp, "wb") as fh:
+            fh.write(encode_png(arr, {"serenity.genparams.v1": json.dumps(gen, separators=(",", ":"))}))
+        os.replace(tmp, out_png)
+        self.last_report = {"text": kind, "denoise_s": round(time.perf_counter() - t0, 4), "decode_s": 0.0, "vae_weights": "none (pixel space)"}
+        return out_png
+
     def sample(self, sp: SamplePrompt, out_png: str, extra: Optional[dict] = None) -> str:
+        if self.m.family in self.PIXEL_FAMILIES:
+            gen = {"schema": "serenity.genparams.v1", "model": self.m.model_id, "prompt": sp.prompt, "negative": sp.negative,
+                   "width": sp.width, "height": sp.height, "frames": sp.frames, "steps": sp.steps, "cfg": sp.cfg, "seed": sp.seed,
+                   "sampler": "euler", "prompt_id": sp.id}
+            gen.update(extra or {})
+            return self._sample_pixels(sp, out_png, gen)
         t0 = time.perf_counter()
         z, kind = self.denoise(sp)
         t1 = time.perf_counter()

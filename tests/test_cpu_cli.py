@@ -194,6 +194,18 @@ def test_preset_catalogue_and_contracts(tmp_path):
     assert not rep["ok"] and any("no runnable loop" in x for x in rep["problems"]) and any("cache" in x for x in rep["problems"])
 
 
+@pytest.mark.parametrize("family", ["zimage_l2p", "sensenova_u1"])
+def test_sample_cli_runs_the_pixel_space_families_without_a_vae(tmp_path, family):
+    """Z-Image L2P and SenseNova-U1 produce pixels directly: the sampler entry point calls the model's own loop and writes the PNG."""
+    tmp = str(tmp_path)
+    cfg_path, ws, prompts = _write_cfg(tmp, family)
+    out = os.path.join(tmp, "img", "p1.png")
+    rep = _run("mojodiffusion_b200.cli.sample", family, cfg_path, "-", prompts, "p1", out, "--tiny")
+    assert rep["family"] == family and rep["vae_weights"] == "none (pixel space)" and rep["text"] in ("hash-embedding", "hash-token-ids")
+    img, meta = load_png(out)
+    assert img.shape[:2] == (64, 64) and img.std() > 0 and json.loads(meta["serenity.genparams.v1"])["seed"] == 7
+
+
 @pytest.mark.parametrize("family", ["lens", "krea2"])
 def test_sample_cli_drives_lens_and_krea2_through_their_own_schedules(tmp_path, family):
     """The sampler entry point runs the two families whose text features are stacks of encoder layers: tiny architecture,
