@@ -158,6 +158,36 @@ def bench_krea2(dev, tiny, steps, warmup):
             "metric": "denoise it/s", "ms_per_step": ms, "value": 1000.0 / ms}
 
 
+def bench_krea2_train(dev, tiny, steps, warmup):
+    """Krea-2-shaped 12.8 B model, LoRA r16 on the eight projections of every single-stream block (the reference's surface),
+    512^2 (1024 image + 114 text tokens), batch 1, per-block recompute, AdamW."""
+    import dataclasses
+    from mojodiffusion_b200.models.krea2 import Krea2Config, Krea2DiT, krea2_positions, tiny_krea2_config
+    from mojodiffusion_b200.training import lora as L
+    from mojodiffusion_b200.training.optim import FusedAdamW
+    cfg = dataclasses.replace(tiny_krea2_config(), features=256, txtdim=128) if tiny else Krea2Config()
+    g, lt = (8, 16) if tiny else (32, 114)
+    m = Krea2DiT(cfg, torch.bfloat16, dev).init_weights(0)
+    slots = L.inject_krea2_lora(m, rank=16, alpha=16.0)
+    opt = FusedAdamW(L.lora_parameters(slots), lr=1e-4, max_grad_norm=1.0)
+    m.gradient_checkpointing = True
+    m.train()
+    x0, eps = torch.randn(1, g * g, cfg.patch_dim, device=dev), torch.randn(1, g * g, cfg.patch_dim, device=dev)
+    ctx = torch.randn(1, lt, cfg.txtlayers, cfg.txtdim, device=dev, dtype=torch.bfloat16)
+    pos = krea2_positions(lt, g, g, dev)
+    t = torch.full((1,), 0.6, device=dev)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        xt, target = ops.flow_match(x0, eps, t)
+        ops.mse_loss(m(xt.to(torch.bfloat16), ctx, t, pos), target).backward()
+        opt.step()
+
+    ms = timed(step, steps, warmup)
+    return {"model": cfg.name + f" LoRA r16 ({len(slots)} adapters), {g * 16}^2, grad ckpt", "params_b": nparams(m) / 1e9,
+            "tokens": g * g + lt, "metric": "train samples/s", "ms_per_step": ms, "value": 1000.0 / ms}
+
+
 def _row(name, m, tokens, ms, what="denoise it/s"):
     return {"model": name, "params_b": nparams(m) / 1e9, "tokens": tokens, "metric": what, "ms_per_step": ms, "value": 1000.0 / ms}
 
@@ -532,6 +562,7 @@ def main():
         "ltx2_vae": lambda: bench_ltx2_vae(dev, args.tiny, args.steps, args.warmup),
         "sdxl_train": lambda: bench_sdxl_train(dev, args.tiny, args.steps, args.warmup),
         "krea2": lambda: bench_krea2(dev, args.tiny, args.steps, args.warmup),
+        "krea2_train": lambda: bench_krea2_train(dev, args.tiny, args.steps, args.warmup),
         "lens": lambda: bench_lens(dev, args.tiny, args.steps, args.warmup),
         "boogu": lambda: bench_boogu(dev, args.tiny, args.steps, args.warmup),
         **{k: (lambda k=k: bench_more(dev, args.tiny, args.steps, args.warmup, k))
