@@ -64,7 +64,7 @@ def summarize(path, first_marker, last_marker):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "gemm_trace", "attention_trace", "attention", "attention_bwd", "norm", "gemm_fp8", "gemm_mxfp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "gemm_prof", "gemm_trace", "attention_trace", "attention", "attention_bwd", "norm", "qk_norm_rope", "gemm_fp8", "gemm_mxfp8", "flux_step", "flux_train_step", "tp_fused_local", "ulysses_fused_local", "dp_fused_local"])
     ap.add_argument("--shape", default="")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--summarize", default="", help="no GPU work: read an `ncu --metrics gpu__time_duration.sum --csv` launch list and "
@@ -294,6 +294,14 @@ def main():
             def fn():
                 o = O.attention(q, k, v)
                 o.backward(torch.ones_like(o))
+    elif a.op == "qk_norm_rope":
+        B, S, H, Dh = dims or [8, 4608, 24, 128]                 # packed q | k | v buffer of 8 FLUX samples: 340 MB
+        qkv = torch.randn(B, S, 3 * H * Dh, device=dev, dtype=torch.bfloat16)
+        wq, wk = torch.ones(Dh, device=dev, dtype=torch.bfloat16), torch.ones(Dh, device=dev, dtype=torch.bfloat16)
+        ids = torch.zeros(S, 3, device=dev)
+        ids[:, 1], ids[:, 2] = torch.arange(S, device=dev) // 64, torch.arange(S, device=dev) % 64
+        cos, sin = O.rope_table(ids, (16, 56, 56), 10000.0)
+        fn = lambda: O.qk_norm_rope(qkv, H, Dh, wq, wk, cos, sin)
     else:
         rows, D = dims or [36864, 3072]
         x = torch.randn(rows, D, device=dev, dtype=torch.bfloat16)
