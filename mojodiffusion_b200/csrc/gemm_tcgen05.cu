@@ -319,7 +319,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     const int chunk = lane & 15;
 #pragma unroll 4
     for (int i = 0; i < 16; ++i) {
-      const int rl = 2 * i + (lane >> 4);                       // row of the warp this lane copies in this round
+      const int rl = 2 * i + (lane >> 4);                       // row of the warp this lane copies in this pass
       const int rr = __shfl_sync(0xffffffffu, row, rl);         // its global output row (p.M or more: not stored)
       const uint4 v = reinterpret_cast<const uint4*>(stage_warp + rl * 256)[chunk ^ (rl & 15)];
       if (rr < p.M) *reinterpret_cast<uint4*>(out_slab_ptr(p, rr, n0 + g * 128 + chunk * 8, 2)) = v;
